@@ -1,0 +1,167 @@
+/*
+ * tcab.h -- C ABI of the B200 (sm_100a) map / reduce / contraction kernel library.
+ *
+ * This is the boundary a host written in another language (Go through cgo, C++,
+ * Python through ctypes) binds. It replaces, for the operator classes below, the
+ * launch layer the reference generates and links per kernel:
+ *
+ *   void <Name>Launch(const tca::Tensor<T,R>& in..., tca::Tensor<T,R>& out,
+ *                     <scalar> s..., cudaStream_t stream);
+ *       -- internal/cg/cxx/launch.go:23-156 (example: internal/cg/cxx/testdata/reduce_warp.cu:66-73)
+ *
+ * Conventions, mirroring that launcher:
+ *   - tensors are NON-OWNING views of row-major contiguous device memory
+ *     (runtime/tca/tensor.h:16-40); extents are 32-bit, element counts must stay
+ *     below 2^32 (the reference indexes with u32);
+ *   - every call is asynchronous on the CUDA stream passed in (NULL = the default
+ *     stream) and runs on the CURRENT device; the caller synchronises;
+ *   - shape agreement is checked before any launch, like the launcher's named
+ *     TCA_REQUIREs (internal/cg/cxx/launch.go:23-156, runtime/tca/check.h:18-44);
+ *   - where the reference throws std::runtime_error, these functions return a
+ *     status code and leave a message for tcab_last_error() (a foreign caller
+ *     cannot catch a C++ exception);
+ *   - no entry point allocates device memory, except where its comment says so.
+ *
+ * There is no CPU fallback: without a CUDA device every compute entry point
+ * returns TCAB_ERR_CUDA.
+ */
+#ifndef TCAB_H_
+#define TCAB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TCAB_API __attribute__((visibility("default")))
+#else
+#define TCAB_API
+#endif
+
+#define TCAB_ABI_VERSION 1
+#define TCAB_MAX_RANK 4
+#define TCAB_MAX_INPUTS 4
+#define TCAB_MAX_CAPTURES 8
+
+/* Status codes. 0 is success; everything else leaves a message for tcab_last_error(). */
+typedef enum tcab_status {
+  TCAB_OK = 0,
+  TCAB_ERR_INVALID_ARG = 1, /* null pointer, bad enum value, rank out of range            */
+  TCAB_ERR_SHAPE = 2,       /* operand shapes disagree (the launcher's TCA_REQUIRE class)  */
+  TCAB_ERR_DTYPE = 3,       /* element type not supported by this operator class           */
+  TCAB_ERR_ALIGNMENT = 4,   /* a pointer or extent breaks an alignment the kernel needs    */
+  TCAB_ERR_UNSUPPORTED = 5, /* a lambda or size this build has no kernel for               */
+  TCAB_ERR_CUDA = 6,        /* a CUDA runtime call or the launch itself failed             */
+  TCAB_ERR_TOO_LARGE = 7    /* an extent beyond what the entry point states it accepts     */
+} tcab_status;
+
+/* Element types: the subset of internal/ir/types.go:13-24 these kernels move. */
+typedef enum tcab_dtype {
+  TCAB_F32 = 0,
+  TCAB_BF16 = 1,
+  TCAB_I32 = 2
+} tcab_dtype;
+
+/* Non-owning tensor view: the C spelling of tca::Tensor<T,R> (runtime/tca/tensor.h:16-40).
+ * `data` is a device pointer; dims[0..rank) are the extents, slowest first. */
+typedef struct tcab_tensor {
+  void* data;
+  int32_t dtype; /* tcab_dtype */
+  uint32_t rank; /* 1..TCAB_MAX_RANK */
+  uint32_t dims[TCAB_MAX_RANK];
+} tcab_tensor;
+
+/* A map | reduce | map chain, as the builder's rungs describe it
+ * (pkg/chain.go:360-559: Iter -> Map -> As -> Reduce -> [Map -> As] -> Store).
+ * Lambdas travel as fully parenthesised C expressions in the reference's own
+ * operator and builtin vocabulary (internal/cg/cxx/naming.go:126-198):
+ *   map_expr      over p0..p{n-1}, the operand values at the current point,
+ *                 and c0..c{m-1}, the scalar captures;            e.g. "(p0 * p1)"
+ *   combine_expr  over p0 = accumulator, p1 = mapped value;        "(p0 + p1)", "fmaxf(p0, p1)", "fminf(p0, p1)"
+ *   post_expr     piped map over p0 = the reduced value and c*; NULL when the chain stores the reduction as it is
+ * `init` is the reduction's initial value (an empty reduction returns it,
+ * design/tca.md:299). All arithmetic is fp32 (design/syntax-design.md:601-607). */
+typedef struct tcab_chain {
+  const char* map_expr;
+  const char* combine_expr;
+  const char* post_expr;
+  float init;
+  uint32_t n_captures;
+  float captures[TCAB_MAX_CAPTURES];
+} tcab_chain;
+
+/* Epilogue of the contraction (the piped map after the K reduction). */
+typedef enum tcab_act {
+  TCAB_ACT_NONE = 0,
+  TCAB_ACT_RELU = 1 /* fmaxf(v, 0) */
+} tcab_act;
+
+/* Message of the calling thread's last failed call ("" if none). Replaces the text of the
+ * std::runtime_error the reference throws (runtime/tca/check.h:18-44). */
+TCAB_API const char* tcab_last_error(void);
+TCAB_API const char* tcab_status_string(int status);
+TCAB_API int tcab_abi_version(void);
+
+/* Number of kernels this library has launched in the calling process (all threads). */
+TCAB_API uint64_t tcab_launch_count(void);
+
+/* Fused map + reduce over ONE axis of identically shaped operands, with an optional piped map:
+ *   out[...] = post( fold_{k along reduce_axis} map(ins[0][..k..], ins[1][..k..], ...) )
+ * Replaces the emitted reduce kernels and their launchers: one-tier sequential
+ * (internal/cg/cxx/testdata/reduce_warp.cu:12-73), split-K warp reduce
+ * (testdata/reduce_splitk.cu:13-91), amortised brackets (testdata/bracket_amort.cu:7-90),
+ * i.e. SeqReducer / WarpReducer brackets (runtime/tca/reducer.h:36-181).
+ * All operands: fp32, same rank (1..4) and extents. `out` is fp32 with the operands' extents
+ * minus the reduced axis (a rank-1 operand gives a rank-1 output of extent 1).
+ * reduce_axis == rank-1 selects the innermost-axis kernel, any other axis the outer-axis kernel.
+ * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative. */
+TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
+                      uint32_t reduce_axis, const tcab_tensor* out, void* stream);
+
+/* Outer-axis reduce of t[b, k, c] over k in ONE pass: any of sum (fp32), max (fp32) and argmax
+ * (int32, lowest index among equal maxima) may be NULL. Each output is [b, c].
+ * The reference's class: the middle-axis kernels of testing/kernels/runtime/row_sum.tca:18-33 and
+ * testing/kernels/fusion/softmax.tca; argmax has no spelling in the reference's reducers
+ * (pkg/chain.go:242-260 admits homogeneous scalar reducers only), so it is offered here directly. */
+TCAB_API int tcab_reduce_outer(const tcab_tensor* t, const tcab_tensor* sum, const tcab_tensor* max,
+                      const tcab_tensor* argmax, void* stream);
+
+/* Row softmax, y[i,j] = expf(x[i,j]-m_i) / sum_j expf(x[i,j]-m_i), m_i = max_j x[i,j]:
+ * the map | reduce | map chain over the innermost axis with a rank-preserving store. The reference's
+ * rungs cannot store a rank-preserving map (pkg/chain.go:433-438; the shipped
+ * testing/kernels/fusion/softmax.tca is its fallback), so the chain is one entry point.
+ * x, y: fp32, same shape, rank 1..4; rows are the innermost axis. */
+TCAB_API int tcab_softmax_rows(const tcab_tensor* x, const tcab_tensor* y, void* stream);
+
+/* Layer-norm over the innermost axis with fp32 statistics:
+ *   y = (x - mean) / sqrtf(var + eps) * gamma + beta,  mean = sum(x)/n,  var = sum((x-mean)^2)/n.
+ * x, y: bf16 or fp32 (same type and shape); gamma, beta: rank 1, extent = the innermost extent,
+ * same element type as x. The reference's fallback for this chain is
+ * testing/kernels/llm/layernorm.tca:1-40 (runner testing/runners/layernorm.cu:47-58). */
+TCAB_API int tcab_layernorm_rows(const tcab_tensor* x, const tcab_tensor* gamma, const tcab_tensor* beta,
+                        float eps, const tcab_tensor* y, void* stream);
+
+/* Tiled contraction with a fused epilogue: c = act(a @ b + bias).
+ * a [M,K] bf16, b [K,N] bf16, bias [N] fp32 or NULL, c [M,N] bf16; fp32 accumulation.
+ * Replaces the emitted GEMM (one output element per CTA bracket; the suite's
+ * testing/kernels/llm/gemm.tca, runner testing/runners/gemm.cu:44-56) plus the piped map the
+ * reference's final-lower cannot bind a tensor operand to (design/RELEASE-v0.0.0.md:150).
+ * Requires K % 8 == 0, N % 8 == 0 and 16-byte aligned base pointers (TMA tensor maps). */
+TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias,
+                       int act, const tcab_tensor* c, void* stream);
+
+/* Tuning hook, no counterpart in the reference: overrides the heuristic launch shape of one kernel
+ * family ("softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm") for this process:
+ * p0, p1 = the launch shape (threads per row and vectors per thread for the row kernels, vectors per lane and
+ * k-splitting warps for reduce_outer), p2 = CTAs per SM, p3 = a variant switch of the family.
+ * Values <= 0 restore the heuristic. Meant for benchmarking sweeps; results never depend on it
+ * beyond the fold order. */
+TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TCAB_H_ */

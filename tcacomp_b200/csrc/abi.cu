@@ -1,0 +1,346 @@
+// abi.cu -- the extern "C" surface declared in include/tcab.h: argument and shape
+// validation, then one launch into the operator-class kernels.
+//
+// The checks stand where the reference's generated launcher derives every
+// extent from its first tensor occurrence and TCA_REQUIREs the others to agree
+// (internal/cg/cxx/launch.go:23-156), and where ValidateLaunch traps bad launch
+// geometry (runtime/tca/launch.h:37-58). A failure is a status code plus a
+// thread-local message; nothing throws across the boundary.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
+
+#include "common.cuh"
+
+namespace tcab {
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<uint64_t> g_launches{0};
+Tune g_tune[kFamilies];
+
+struct DevFacts {
+  int sms = 0;
+  int optin_smem = 0;
+};
+std::mutex g_mu;
+std::map<int, DevFacts> g_dev;
+std::map<std::pair<std::pair<int, const void*>, std::pair<int, size_t>>, int> g_occ;
+
+int current_device() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return d;
+}
+
+const DevFacts& facts() {
+  static const DevFacts none{};
+  const int d = current_device();
+  if (d < 0) return none;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_dev.find(d);
+  if (it == g_dev.end()) {
+    DevFacts f;
+    cudaDeviceGetAttribute(&f.sms, cudaDevAttrMultiProcessorCount, d);
+    cudaDeviceGetAttribute(&f.optin_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, d);
+    it = g_dev.emplace(d, f).first;
+  }
+  return it->second;
+}
+
+}  // namespace
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  std::vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+void count_launch(unsigned n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+int sm_count() {
+  const int n = facts().sms;
+  return n > 0 ? n : 1;
+}
+
+int max_optin_smem() { return facts().optin_smem; }
+
+int check_launch(const char* what) {
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(TCAB_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  return TCAB_OK;
+}
+
+const Tune& tune(int family) { return g_tune[family]; }
+
+int occupancy(const void* fn, int block, size_t smem) {
+  const int d = current_device();
+  const auto key = std::make_pair(std::make_pair(d, fn), std::make_pair(block, smem));
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_occ.find(key);
+    if (it != g_occ.end()) return it->second;
+  }
+  int n = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, fn, block, smem) != cudaSuccess) {
+    cudaGetLastError();
+    n = 1;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_occ[key] = n;
+  return n;
+}
+
+namespace {
+
+// ---- validation helpers ----------------------------------------------------
+
+int check_tensor(const char* op, const char* name, const tcab_tensor* t, bool need_data = true) {
+  if (t == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: tensor '%s' is null", op, name);
+  if (t->rank < 1 || t->rank > TCAB_MAX_RANK)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: tensor '%s' has rank %u (want 1..%d)", op, name, t->rank, TCAB_MAX_RANK);
+  uint64_t n = 1;
+  for (uint32_t i = 0; i < t->rank; ++i) {
+    n *= t->dims[i];
+    if (n >= (1ull << 32))
+      return fail(TCAB_ERR_TOO_LARGE, "%s: tensor '%s' has 2^32 or more elements", op, name);
+  }
+  if (need_data && n > 0 && t->data == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: tensor '%s' has a null data pointer", op, name);
+  return TCAB_OK;
+}
+
+uint64_t count(const tcab_tensor* t, uint32_t from, uint32_t to) {
+  uint64_t n = 1;
+  for (uint32_t i = from; i < to; ++i) n *= t->dims[i];
+  return n;
+}
+
+bool same_shape(const tcab_tensor* a, const tcab_tensor* b) {
+  if (a->rank != b->rank) return false;
+  for (uint32_t i = 0; i < a->rank; ++i)
+    if (a->dims[i] != b->dims[i]) return false;
+  return true;
+}
+
+int need_dtype(const char* op, const char* name, const tcab_tensor* t, int dtype, const char* spelled) {
+  if (t->dtype != dtype) return fail(TCAB_ERR_DTYPE, "%s: tensor '%s' must be %s", op, name, spelled);
+  return TCAB_OK;
+}
+
+int need_elem_align(const char* op, const char* name, const tcab_tensor* t, unsigned bytes) {
+  if (reinterpret_cast<uintptr_t>(t->data) % bytes != 0)
+    return fail(TCAB_ERR_ALIGNMENT, "%s: tensor '%s' is not %u-byte aligned", op, name, bytes);
+  return TCAB_OK;
+}
+
+int have_device(const char* op) {
+  if (current_device() < 0) return fail(TCAB_ERR_CUDA, "%s: no CUDA device (this library has no CPU path)", op);
+  return TCAB_OK;
+}
+
+#define TCAB_TRY(expr)              \
+  do {                              \
+    const int tcab_rc_ = (expr);    \
+    if (tcab_rc_ != TCAB_OK) return tcab_rc_; \
+  } while (0)
+
+}  // namespace
+}  // namespace tcab
+
+using namespace tcab;
+
+extern "C" {
+
+const char* tcab_last_error(void) { return g_err; }
+
+const char* tcab_status_string(int status) {
+  switch (status) {
+    case TCAB_OK: return "ok";
+    case TCAB_ERR_INVALID_ARG: return "invalid argument";
+    case TCAB_ERR_SHAPE: return "shape mismatch";
+    case TCAB_ERR_DTYPE: return "unsupported element type";
+    case TCAB_ERR_ALIGNMENT: return "misaligned operand";
+    case TCAB_ERR_UNSUPPORTED: return "unsupported by this build";
+    case TCAB_ERR_CUDA: return "CUDA failure";
+    case TCAB_ERR_TOO_LARGE: return "extent too large";
+    default: return "unknown status";
+  }
+}
+
+int tcab_abi_version(void) { return TCAB_ABI_VERSION; }
+
+uint64_t tcab_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {
+  static const char* names[kFamilies] = {"softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm"};
+  if (family == nullptr) return fail(TCAB_ERR_INVALID_ARG, "tune: null family");
+  for (int i = 0; i < kFamilies; ++i) {
+    if (std::strcmp(family, names[i]) == 0) {
+      g_tune[i].p0 = p0 > 0 ? p0 : 0;
+      g_tune[i].p1 = p1 > 0 ? p1 : 0;
+      g_tune[i].p2 = p2 > 0 ? p2 : 0;
+      g_tune[i].p3 = p3 > 0 ? p3 : 0;
+      return TCAB_OK;
+    }
+  }
+  return fail(TCAB_ERR_INVALID_ARG, "tune: unknown family '%s'", family);
+}
+
+int tcab_softmax_rows(const tcab_tensor* x, const tcab_tensor* y, void* stream) {
+  const char* op = "softmax_rows";
+  TCAB_TRY(check_tensor(op, "x", x));
+  TCAB_TRY(check_tensor(op, "y", y));
+  TCAB_TRY(need_dtype(op, "x", x, TCAB_F32, "f32"));
+  TCAB_TRY(need_dtype(op, "y", y, TCAB_F32, "f32"));
+  if (!same_shape(x, y)) return fail(TCAB_ERR_SHAPE, "%s: y must have the shape of x", op);
+  TCAB_TRY(need_elem_align(op, "x", x, 4));
+  TCAB_TRY(need_elem_align(op, "y", y, 4));
+  TCAB_TRY(have_device(op));
+  const uint32_t cols = x->dims[x->rank - 1];
+  return launch_softmax_rows(static_cast<const float*>(x->data), static_cast<float*>(y->data),
+                             count(x, 0, x->rank - 1), cols, static_cast<cudaStream_t>(stream));
+}
+
+int tcab_layernorm_rows(const tcab_tensor* x, const tcab_tensor* gamma, const tcab_tensor* beta, float eps,
+                        const tcab_tensor* y, void* stream) {
+  const char* op = "layernorm_rows";
+  TCAB_TRY(check_tensor(op, "x", x));
+  TCAB_TRY(check_tensor(op, "gamma", gamma));
+  TCAB_TRY(check_tensor(op, "beta", beta));
+  TCAB_TRY(check_tensor(op, "y", y));
+  if (x->dtype != TCAB_F32 && x->dtype != TCAB_BF16) return fail(TCAB_ERR_DTYPE, "%s: x must be f32 or bf16", op);
+  if (y->dtype != x->dtype || gamma->dtype != x->dtype || beta->dtype != x->dtype)
+    return fail(TCAB_ERR_DTYPE, "%s: gamma, beta and y must have the element type of x", op);
+  if (!same_shape(x, y)) return fail(TCAB_ERR_SHAPE, "%s: y must have the shape of x", op);
+  const uint32_t cols = x->dims[x->rank - 1];
+  if (gamma->rank != 1 || gamma->dims[0] != cols)
+    return fail(TCAB_ERR_SHAPE, "%s: gamma must be rank 1 with extent %u (the innermost extent of x)", op, cols);
+  if (beta->rank != 1 || beta->dims[0] != cols)
+    return fail(TCAB_ERR_SHAPE, "%s: beta must be rank 1 with extent %u (the innermost extent of x)", op, cols);
+  const unsigned es = x->dtype == TCAB_F32 ? 4 : 2;
+  TCAB_TRY(need_elem_align(op, "x", x, es));
+  TCAB_TRY(need_elem_align(op, "y", y, es));
+  TCAB_TRY(need_elem_align(op, "gamma", gamma, es));
+  TCAB_TRY(need_elem_align(op, "beta", beta, es));
+  TCAB_TRY(have_device(op));
+  const uint64_t rows = count(x, 0, x->rank - 1);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x->dtype == TCAB_BF16)
+    return launch_layernorm_rows_bf16(static_cast<const __nv_bfloat16*>(x->data),
+                                      static_cast<const __nv_bfloat16*>(gamma->data),
+                                      static_cast<const __nv_bfloat16*>(beta->data), eps,
+                                      static_cast<__nv_bfloat16*>(y->data), rows, cols, s);
+  return launch_layernorm_rows_f32(static_cast<const float*>(x->data), static_cast<const float*>(gamma->data),
+                                   static_cast<const float*>(beta->data), eps, static_cast<float*>(y->data), rows,
+                                   cols, s);
+}
+
+int tcab_reduce_outer(const tcab_tensor* t, const tcab_tensor* sum, const tcab_tensor* max,
+                      const tcab_tensor* argmax, void* stream) {
+  const char* op = "reduce_outer";
+  TCAB_TRY(check_tensor(op, "t", t));
+  TCAB_TRY(need_dtype(op, "t", t, TCAB_F32, "f32"));
+  if (t->rank != 3) return fail(TCAB_ERR_SHAPE, "%s: t must be rank 3 [b, k, c]", op);
+  if (sum == nullptr && max == nullptr && argmax == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: at least one of sum, max, argmax is required", op);
+  const tcab_tensor* outs[3] = {sum, max, argmax};
+  const char* names[3] = {"sum", "max", "argmax"};
+  for (int i = 0; i < 3; ++i) {
+    if (outs[i] == nullptr) continue;
+    TCAB_TRY(check_tensor(op, names[i], outs[i]));
+    TCAB_TRY(need_dtype(op, names[i], outs[i], i == 2 ? TCAB_I32 : TCAB_F32, i == 2 ? "i32" : "f32"));
+    if (outs[i]->rank != 2 || outs[i]->dims[0] != t->dims[0] || outs[i]->dims[1] != t->dims[2])
+      return fail(TCAB_ERR_SHAPE, "%s: %s must be [%u, %u]", op, names[i], t->dims[0], t->dims[2]);
+    TCAB_TRY(need_elem_align(op, names[i], outs[i], 4));
+  }
+  TCAB_TRY(need_elem_align(op, "t", t, 4));
+  TCAB_TRY(have_device(op));
+  return launch_reduce_outer(static_cast<const float*>(t->data), sum ? static_cast<float*>(sum->data) : nullptr,
+                             max ? static_cast<float*>(max->data) : nullptr,
+                             argmax ? static_cast<int32_t*>(argmax->data) : nullptr, t->dims[0], t->dims[1],
+                             t->dims[2], static_cast<cudaStream_t>(stream));
+}
+
+int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, uint32_t reduce_axis,
+                      const tcab_tensor* out, void* stream) {
+  const char* op = "chain_reduce";
+  if (chain == nullptr || chain->map_expr == nullptr || chain->combine_expr == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: chain, map_expr and combine_expr are required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
+  const float* ptrs[TCAB_MAX_INPUTS] = {};
+  for (uint32_t i = 0; i < n_ins; ++i) {
+    char name[16];
+    std::snprintf(name, sizeof(name), "ins[%u]", i);
+    TCAB_TRY(check_tensor(op, name, &ins[i]));
+    TCAB_TRY(need_dtype(op, name, &ins[i], TCAB_F32, "f32"));
+    TCAB_TRY(need_elem_align(op, name, &ins[i], 4));
+    if (i > 0 && !same_shape(&ins[0], &ins[i]))
+      return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0]", op, name);
+    ptrs[i] = static_cast<const float*>(ins[i].data);
+  }
+  const tcab_tensor* t = &ins[0];
+  if (reduce_axis >= t->rank) return fail(TCAB_ERR_INVALID_ARG, "%s: reduce_axis %u out of range", op, reduce_axis);
+  TCAB_TRY(check_tensor(op, "out", out));
+  TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
+  TCAB_TRY(need_elem_align(op, "out", out, 4));
+  // out = the operands' extents minus the reduced axis (rank 1 -> [1]).
+  uint32_t want[TCAB_MAX_RANK], wr = 0;
+  for (uint32_t i = 0; i < t->rank; ++i)
+    if (i != reduce_axis) want[wr++] = t->dims[i];
+  if (wr == 0) want[wr++] = 1;
+  bool ok = out->rank == wr;
+  for (uint32_t i = 0; ok && i < wr; ++i) ok = out->dims[i] == want[i];
+  if (!ok) return fail(TCAB_ERR_SHAPE, "%s: out must have the operands' extents without axis %u", op, reduce_axis);
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
+  TCAB_TRY(have_device(op));
+  return launch_chain_reduce(pc, ptrs, count(t, 0, reduce_axis), t->dims[reduce_axis],
+                             count(t, reduce_axis + 1, t->rank), static_cast<float*>(out->data),
+                             static_cast<cudaStream_t>(stream));
+}
+
+int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias, int act,
+                       const tcab_tensor* c, void* stream) {
+  const char* op = "gemm_bias_act";
+  TCAB_TRY(check_tensor(op, "a", a));
+  TCAB_TRY(check_tensor(op, "b", b));
+  TCAB_TRY(check_tensor(op, "c", c));
+  TCAB_TRY(need_dtype(op, "a", a, TCAB_BF16, "bf16"));
+  TCAB_TRY(need_dtype(op, "b", b, TCAB_BF16, "bf16"));
+  TCAB_TRY(need_dtype(op, "c", c, TCAB_BF16, "bf16"));
+  if (a->rank != 2 || b->rank != 2 || c->rank != 2) return fail(TCAB_ERR_SHAPE, "%s: a, b and c must be rank 2", op);
+  const uint32_t m = a->dims[0], k = a->dims[1], n = b->dims[1];
+  if (b->dims[0] != k) return fail(TCAB_ERR_SHAPE, "%s: b.Dim(0) must equal a.Dim(1) (dim k)", op);
+  if (c->dims[0] != m || c->dims[1] != n) return fail(TCAB_ERR_SHAPE, "%s: c must be [%u, %u]", op, m, n);
+  if (bias != nullptr) {
+    TCAB_TRY(check_tensor(op, "bias", bias));
+    TCAB_TRY(need_dtype(op, "bias", bias, TCAB_F32, "f32"));
+    if (bias->rank != 1 || bias->dims[0] != n) return fail(TCAB_ERR_SHAPE, "%s: bias must be [%u]", op, n);
+    TCAB_TRY(need_elem_align(op, "bias", bias, 4));
+  }
+  if (act != TCAB_ACT_NONE && act != TCAB_ACT_RELU) return fail(TCAB_ERR_INVALID_ARG, "%s: unknown activation %d", op, act);
+  if (k % 8 != 0 || n % 8 != 0)
+    return fail(TCAB_ERR_ALIGNMENT, "%s: K and N must be multiples of 8 (16-byte rows for the tensor maps)", op);
+  TCAB_TRY(need_elem_align(op, "a", a, 16));
+  TCAB_TRY(need_elem_align(op, "b", b, 16));
+  TCAB_TRY(need_elem_align(op, "c", c, 16));
+  TCAB_TRY(have_device(op));
+  return launch_gemm_bias_act(static_cast<const __nv_bfloat16*>(a->data), static_cast<const __nv_bfloat16*>(b->data),
+                              bias ? static_cast<const float*>(bias->data) : nullptr, act,
+                              static_cast<__nv_bfloat16*>(c->data), m, n, k, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,202 @@
+// chain_kernels.cuh -- map | reduce | map chains over one axis, generic in the lambdas.
+//
+// Self-contained device code (no includes): the same text is compiled ahead of
+// time with the precompiled lambdas (chain_reduce.cu) and at run time with a
+// lambda printed from the caller's expression (the run-time compiler prepends
+// nothing but the two functor structs).
+//
+// The kernels replace the reference's emitted reduce kernels
+// (internal/cg/cxx/testdata/reduce_warp.cu:12-62, reduce_splitk.cu:13-80,
+// bracket_amort.cu:7-78) and its reducer brackets (runtime/tca/reducer.h:36-181):
+// every thread folds its share of the reduced axis in registers and the partials
+// meet in ONE tree per output, instead of one shuffle tree and two barriers per
+// reduced ELEMENT. Padded points never reach the map lambda (design/tca.md:297-299);
+// an empty reduction returns init (design/tca.md:299).
+//
+// Functor contract:
+//   struct Map  { static __device__ float apply(const float* p, const float* c); }  p[i] = operand i
+//   struct Post { static __device__ float apply(const float* p, const float* c); }  p[0] = reduced value
+// COMBINE: 0 = p0 + p1, 1 = fmaxf(p0, p1), 2 = fminf(p0, p1).
+#pragma once
+
+namespace tcabk {
+
+typedef unsigned int u32;
+typedef unsigned long long u64;
+
+constexpr int kMaxCaptures = 16;  // user captures plus lifted literals
+
+template <int NIN>
+struct Ptrs {
+  const float* p[NIN];
+};
+struct Caps {
+  float c[kMaxCaptures];
+};
+
+template <int COMBINE>
+struct Comb;
+template <>
+struct Comb<0> {
+  static __device__ __forceinline__ float identity() { return 0.0f; }
+  static __device__ __forceinline__ float apply(float a, float b) { return a + b; }
+};
+template <>
+struct Comb<1> {
+  static __device__ __forceinline__ float identity() { return -__int_as_float(0x7f800000); }
+  static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); }
+};
+template <>
+struct Comb<2> {
+  static __device__ __forceinline__ float identity() { return __int_as_float(0x7f800000); }
+  static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); }
+};
+
+struct PostNone {
+  static __device__ __forceinline__ float apply(const float* p, const float*) { return p[0]; }
+};
+
+template <int V>
+struct Ld;
+template <>
+struct Ld<4> {
+  static __device__ __forceinline__ void load(const float* base, u64 vec_index, float* f) {
+    const float4 q = __ldcs(reinterpret_cast<const float4*>(base) + vec_index);
+    f[0] = q.x; f[1] = q.y; f[2] = q.z; f[3] = q.w;
+  }
+};
+template <>
+struct Ld<1> {
+  static __device__ __forceinline__ void load(const float* base, u64 vec_index, float* f) {
+    f[0] = __ldcs(base + vec_index);
+  }
+};
+
+template <class C, int WIDTH>
+__device__ __forceinline__ float lanes_allreduce(float v) {
+#pragma unroll
+  for (int off = WIDTH / 2; off > 0; off >>= 1) v = C::apply(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+__host__ __device__ constexpr int inner_cta_threads(int tpr) { return tpr > 128 ? tpr : 128; }
+
+// Reduce over the INNERMOST axis: operands are [rows, nk]; a group of TPR
+// threads folds one row. TPR == 1 is a plain sequential ascending fold per
+// thread (bit-identical to the reference's SeqReducer order).
+template <class Map, class Post, int COMBINE, int NIN, int TPR, int V>
+__global__ void __launch_bounds__(inner_cta_threads(TPR))
+chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  constexpr int THREADS = inner_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  __shared__ float slots[2][32];
+
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const u32 nvec = nk / V;
+  u32 iter = 0;
+
+  for (u64 row0 = static_cast<u64>(blockIdx.x) * GROUPS; row0 < rows;
+       row0 += static_cast<u64>(gridDim.x) * GROUPS, ++iter) {
+    const u64 row = row0 + g;
+    const bool live = row < rows;
+    const u64 vbase = row * nvec;  // first vector of the row (nk % V == 0)
+    float acc = C::identity();
+    if (live) {
+#pragma unroll 4
+      for (u32 idx = t; idx < nvec; idx += TPR) {
+        float f[NIN][V];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a], vbase + idx, f[a]);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float p[NIN];
+#pragma unroll
+          for (int a = 0; a < NIN; ++a) p[a] = f[a][j];
+          acc = C::apply(acc, Map::apply(p, caps.c));
+        }
+      }
+    }
+    if constexpr (TPR > 1 && TPR <= 32) {
+      acc = lanes_allreduce<C, TPR>(acc);
+    } else if constexpr (TPR > 32) {
+      constexpr int NW = TPR / 32;
+      float* sl = slots[iter & 1];  // alternate: a slot is rewritten only after everyone read it
+      acc = lanes_allreduce<C, 32>(acc);
+      if ((threadIdx.x & 31) == 0) sl[threadIdx.x >> 5] = acc;
+      __syncthreads();
+      acc = lanes_allreduce<C, NW>(sl[threadIdx.x & (NW - 1)]);
+    }
+    if (live && t == 0) {
+      float r[1] = {C::apply(init, acc)};
+      out[row] = Post::apply(r, caps.c + 8);
+    }
+  }
+}
+
+// Reduce over a MIDDLE axis: operands are [nb, nk, nc]; a CTA owns (one b, a
+// tile of 32*V columns), lane l owns V columns, warp w owns k = w, w+KW, ...
+template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL>
+__global__ void __launch_bounds__(32 * KW)
+chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, float init,
+            Caps caps) {
+  typedef Comb<COMBINE> C;
+  constexpr int TILE_C = 32 * V;
+  __shared__ float s_part[KW][TILE_C];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (u32 tile = blockIdx.x; tile < nb * tiles_per_b; tile += gridDim.x) {
+    const u32 b = tile / tiles_per_b;
+    const u32 c0 = (tile % tiles_per_b) * TILE_C;
+    const u32 col = c0 + lane * V;
+    const bool colok = col < nc;  // nc % V == 0 when V == 4
+    const u64 base = static_cast<u64>(b) * nk * nc + col;
+
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = C::identity();
+
+    if (colok) {
+      for (u32 k0 = warp; k0 < nk; k0 += KW * UNROLL) {
+        float f[UNROLL][NIN][V];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const u32 k = k0 + u * KW;
+          if (k < nk) {
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a] + base + static_cast<u64>(k) * nc, 0, f[u][a]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const u32 k = k0 + u * KW;
+          if (k < nk) {
+#pragma unroll
+            for (int j = 0; j < V; ++j) {
+              float p[NIN];
+#pragma unroll
+              for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
+              acc[j] = C::apply(acc[j], Map::apply(p, caps.c));
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) s_part[warp][lane * V + j] = acc[j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < TILE_C; c += 32 * KW) {
+      if (c0 + c < nc) {
+        float a = init;
+#pragma unroll
+        for (int w = 0; w < KW; ++w) a = C::apply(a, s_part[w][c]);
+        float r[1] = {a};
+        out[static_cast<u64>(b) * nc + c0 + c] = Post::apply(r, caps.c + 8);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace tcabk

@@ -1,0 +1,199 @@
+// chain_reduce.cu -- ahead-of-time instances of the chain kernels and their dispatch.
+//
+// A chain arrives as canonical lambda text (expr.h). The table below holds the
+// lambdas this build has compiled ahead of time, written as the same text the
+// canonicaliser prints, so that the key and the code cannot drift apart: the
+// macro stringifies the expression it compiles. A chain whose lambdas are not in
+// the table is reported as unsupported by this build.
+#include <string>
+#include <vector>
+
+#include "chain_kernels.cuh"
+#include "common.cuh"
+#include "expr.h"
+
+namespace tcab {
+namespace {
+
+using tcabk::Caps;
+using tcabk::Ptrs;
+
+// A lambda as device code: p0..p3 are the operands, c0..c7 the captures.
+#define TCAB_LAMBDA(NAME, NIN, ...)                                                           \
+  struct NAME {                                                                               \
+    static constexpr int kIn = NIN;                                                           \
+    static const char* text() { return #__VA_ARGS__; }                                        \
+    static __device__ __forceinline__ float apply(const float* p, const float* c) {           \
+      const float p0 = p[0], p1 = p[NIN > 1 ? 1 : 0], p2 = p[NIN > 2 ? 2 : 0], p3 = p[NIN > 3 ? 3 : 0]; \
+      const float c0 = c[0], c1 = c[1], c2 = c[2], c3 = c[3], c4 = c[4], c5 = c[5], c6 = c[6], c7 = c[7]; \
+      (void)p0; (void)p1; (void)p2; (void)p3;                                                 \
+      (void)c0; (void)c1; (void)c2; (void)c3; (void)c4; (void)c5; (void)c6; (void)c7;         \
+      return __VA_ARGS__;                                                                     \
+    }                                                                                         \
+  };
+
+TCAB_LAMBDA(MapIdent, 1, p0)
+TCAB_LAMBDA(MapAffineSq, 1, (((c0 * p0) + c1) * ((c0 * p0) + c1)))
+TCAB_LAMBDA(MapMul2, 2, (p0 * p1))
+TCAB_LAMBDA(MapExpMul, 2, (expf(p0) * p1))
+TCAB_LAMBDA(MapSqMul, 2, ((p0 * p0) * p1))
+TCAB_LAMBDA(MapAxpy, 2, ((c0 * p0) + (c1 * p1)))
+TCAB_LAMBDA(MapScaleMul, 2, (((c0 * p0) + c1) * p1))
+TCAB_LAMBDA(PostSelfRsqrt, 1, (p0 * rsqrtf(((p0 * c0) + c1))))
+TCAB_LAMBDA(PostAddTanh, 1, (p0 + (c0 * tanhf(p0))))
+TCAB_LAMBDA(PostScale, 1, (p0 * c0))
+
+struct Args {
+  const float* const* ins;
+  float* out;
+  uint64_t outer;
+  uint32_t nk;
+  uint64_t inner;
+  float init;
+  Caps caps;
+  cudaStream_t stream;
+};
+
+template <class Map, class Post, int COMBINE, int TPR, int V>
+int launch_inner(const Args& a) {
+  constexpr int NIN = Map::kIn;
+  constexpr int THREADS = tcabk::inner_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  int occ = occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
+  if (occ < 1) occ = 1;
+  const uint64_t need = (a.outer + GROUPS - 1) / GROUPS;
+  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  if (grid > need) grid = need;
+  fn<<<static_cast<unsigned>(grid), THREADS, 0, a.stream>>>(ptrs, a.out, a.outer, a.nk, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_inner");
+}
+
+template <class Map, class Post, int COMBINE, int V>
+int launch_outer(const Args& a) {
+  constexpr int NIN = Map::kIn;
+  constexpr int KW = 8, UNROLL = 4;
+  auto* fn = tcabk::chain_outer<Map, Post, COMBINE, NIN, V, KW, UNROLL>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  const uint32_t nc = static_cast<uint32_t>(a.inner);
+  const uint32_t tiles_per_b = (nc + 32 * V - 1) / (32 * V);
+  const uint64_t tiles = a.outer * tiles_per_b;
+  if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
+  int occ = occupancy(reinterpret_cast<const void*>(fn), 32 * KW, 0);
+  if (occ < 1) occ = 1;
+  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  if (grid > tiles) grid = tiles;
+  fn<<<static_cast<unsigned>(grid), 32 * KW, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,
+                                                          tiles_per_b, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_outer");
+}
+
+template <class Map, class Post, int COMBINE>
+int launch_chain(const Args& a) {
+  constexpr int NIN = Map::kIn;
+  bool al = true;
+  for (int i = 0; i < NIN; ++i) al = al && aligned16(a.ins[i]);
+  if (a.inner == 1) {
+    const bool vec = al && (a.nk % 4 == 0);
+    const uint32_t nvec = vec ? a.nk / 4 : a.nk;
+    int tpr = nvec <= 8 ? 1 : nvec <= 64 ? 4 : nvec <= 2048 ? 32 : 256;
+    const Tune& tn = tune(kReduceInner);
+    if (tn.p0 == 1 || tn.p0 == 4 || tn.p0 == 32 || tn.p0 == 256) tpr = tn.p0;
+    if (vec) {
+      switch (tpr) {
+        case 1: return launch_inner<Map, Post, COMBINE, 1, 4>(a);
+        case 4: return launch_inner<Map, Post, COMBINE, 4, 4>(a);
+        case 32: return launch_inner<Map, Post, COMBINE, 32, 4>(a);
+        default: return launch_inner<Map, Post, COMBINE, 256, 4>(a);
+      }
+    }
+    switch (tpr) {
+      case 1: return launch_inner<Map, Post, COMBINE, 1, 1>(a);
+      case 4: return launch_inner<Map, Post, COMBINE, 4, 1>(a);
+      case 32: return launch_inner<Map, Post, COMBINE, 32, 1>(a);
+      default: return launch_inner<Map, Post, COMBINE, 256, 1>(a);
+    }
+  }
+  if (a.inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
+  const bool vec = al && (a.inner % 4 == 0);
+  return vec ? launch_outer<Map, Post, COMBINE, 4>(a) : launch_outer<Map, Post, COMBINE, 1>(a);
+}
+
+struct Entry {
+  const char* map;
+  const char* post;  // "" = the reduction is stored as it is
+  int combine;
+  int n_in;
+  int (*launch)(const Args&);
+};
+
+#define TCAB_ENTRY(MAP, POST, COMBINE) \
+  { MAP::text(), POST::text(), COMBINE, MAP::kIn, &launch_chain<MAP, POST, COMBINE> }
+#define TCAB_ENTRY_NOPOST(MAP, COMBINE) \
+  { MAP::text(), "", COMBINE, MAP::kIn, &launch_chain<MAP, tcabk::PostNone, COMBINE> }
+
+const Entry kTable[] = {
+    TCAB_ENTRY_NOPOST(MapIdent, 0),    TCAB_ENTRY_NOPOST(MapIdent, 1),    TCAB_ENTRY_NOPOST(MapIdent, 2),
+    TCAB_ENTRY_NOPOST(MapAffineSq, 0), TCAB_ENTRY_NOPOST(MapMul2, 0),     TCAB_ENTRY_NOPOST(MapExpMul, 0),
+    TCAB_ENTRY_NOPOST(MapScaleMul, 0), TCAB_ENTRY(MapSqMul, PostSelfRsqrt, 0),
+    TCAB_ENTRY(MapAxpy, PostAddTanh, 0), TCAB_ENTRY(MapMul2, PostScale, 0),
+};
+
+int combine_id(const std::string& text) {
+  if (text == "(p0 + p1)" || text == "(p1 + p0)") return 0;
+  if (text == "fmaxf(p0, p1)" || text == "fmaxf(p1, p0)") return 1;
+  if (text == "fminf(p0, p1)" || text == "fminf(p1, p0)") return 2;
+  return -1;
+}
+
+}  // namespace
+
+int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc) {
+  std::vector<float> user(chain->captures, chain->captures + chain->n_captures);
+  CanonExpr map, comb, post;
+  std::string err;
+  if (!canonicalize(chain->map_expr, static_cast<int>(n_ins), user, &map, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: map_expr: %s", err.c_str());
+  if (!canonicalize(chain->combine_expr, 2, {}, &comb, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: combine_expr: %s", err.c_str());
+  const bool has_post = chain->post_expr != nullptr && chain->post_expr[0] != '\0';
+  if (has_post && !canonicalize(chain->post_expr, 1, user, &post, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: post_expr: %s", err.c_str());
+  if (map.n_operands != static_cast<int>(n_ins))
+    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: map_expr uses %d operands, %u given", map.n_operands, n_ins);
+  const int cid = combine_id(comb.text);
+  if (cid < 0)
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: combiner '%s' is not sum/fmaxf/fminf", comb.text.c_str());
+  if (map.captures.size() > 8 || post.captures.size() > 8)
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: more than 8 distinct constants in one lambda");
+  for (int i = 0; i < 16; ++i) pc->caps[i] = 0.0f;
+  for (size_t i = 0; i < map.captures.size(); ++i) pc->caps[i] = map.captures[i];
+  for (size_t i = 0; i < post.captures.size(); ++i) pc->caps[8 + i] = post.captures[i];
+  pc->init = chain->init;
+  pc->entry = -1;
+  const std::string post_text = has_post ? post.text : std::string();
+  for (size_t i = 0; i < sizeof(kTable) / sizeof(kTable[0]); ++i) {
+    const Entry& e = kTable[i];
+    if (e.combine == cid && e.n_in == static_cast<int>(n_ins) && map.text == e.map && post_text == e.post) {
+      pc->entry = static_cast<int>(i);
+      return TCAB_OK;
+    }
+  }
+  return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: no kernel in this build for map '%s' post '%s'", map.text.c_str(),
+              post_text.c_str());
+}
+
+int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
+                        uint64_t inner, float* out, cudaStream_t s) {
+  if (outer == 0 || inner == 0) return TCAB_OK;
+  Args a{ins, out, outer, nk, inner, pc.init, {}, s};
+  for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
+  return kTable[pc.entry].launch(a);
+}
+
+}  // namespace tcab

@@ -1,0 +1,129 @@
+// common.cuh -- shared host and device helpers of the kernel library.
+//
+// Host side: status/error plumbing for the C ABI (the status-code replacement of
+// the reference's TCA_REQUIRE / TCA_CUDA_CHECK exceptions, runtime/tca/check.h:18-44),
+// per-device facts (SM count, opt-in shared memory -- the reference queries the
+// latter per launch in ValidateLaunch, runtime/tca/launch.h:37-58; here it is
+// queried once per device) and the launch counter.
+// Device side: 128-bit streaming loads/stores and the shuffle / shared-memory
+// reduction trees that replace the per-element WarpReducer brackets
+// (runtime/tca/reducer.h:81-181) with ONE tree per row.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tcab.h"
+
+namespace tcab {
+
+// ---------------------------------------------------------------------------
+// host plumbing (defined in abi.cu)
+// ---------------------------------------------------------------------------
+int fail(int status, const char* fmt, ...);
+void count_launch(unsigned n = 1);
+int sm_count();             // SMs of the current device (cached per device)
+int max_optin_smem();       // opt-in shared memory per block of the current device
+int check_launch(const char* what);  // cudaGetLastError -> status
+
+struct Tune {
+  int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+};
+const Tune& tune(int family);
+enum Family { kSoftmax = 0, kLayernorm = 1, kReduceInner = 2, kReduceOuter = 3, kGemm = 4, kFamilies = 5 };
+
+// Resident CTAs per SM of a kernel at a block size / dynamic smem, cached per (function, block).
+int occupancy(const void* fn, int block, size_t smem);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline uint32_t pow2_ceil(uint32_t v) {
+  uint32_t p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// Entry points of the operator classes (one .cu each).
+int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
+int launch_layernorm_rows_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma,
+                               const __nv_bfloat16* beta, float eps, __nv_bfloat16* y,
+                               uint64_t rows, uint32_t cols, cudaStream_t s);
+int launch_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float eps,
+                              float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
+int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb,
+                        uint32_t nk, uint32_t nc, cudaStream_t s);
+// A chain whose lambdas were validated, canonicalised and matched to a compiled kernel.
+struct PreparedChain {
+  int entry = -1;   // index into the table of compiled chains
+  float init = 0.0f;
+  float caps[16];   // map captures in [0,8), piped-map captures in [8,16)
+};
+// Host-only step (no device needed): parse, canonicalise and look the chain up.
+int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc);
+int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
+                        uint64_t inner, float* out, cudaStream_t s);
+int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias,
+                         int act, __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k,
+                         cudaStream_t s);
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// 128-bit loads/stores for data that is touched once: evict-first in L1/L2.
+__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+__device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }
+
+struct OpSum {
+  static __device__ __forceinline__ float identity() { return 0.0f; }
+  static __device__ __forceinline__ float apply(float a, float b) { return a + b; }
+};
+struct OpMax {
+  static __device__ __forceinline__ float identity() { return -INFINITY; }
+  static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); }
+};
+struct OpMin {
+  static __device__ __forceinline__ float identity() { return INFINITY; }
+  static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); }
+};
+
+// Butterfly over the low `WIDTH` lanes of each aligned lane group: every lane
+// of the group ends with the group's result.
+template <typename Op, int WIDTH = 32>
+__device__ __forceinline__ float warp_allreduce(float v) {
+#pragma unroll
+  for (int off = WIDTH / 2; off > 0; off >>= 1) v = Op::apply(v, __shfl_xor_sync(kFullMask, v, off));
+  return v;
+}
+
+// All `NWARPS` warps of the CTA combine one value each through `slots`
+// (NWARPS floats of shared memory); every thread returns the result. ONE
+// barrier: the caller alternates between two slot arrays so that a slot is
+// never rewritten before every thread has read it (see the row kernels).
+template <typename Op, int NWARPS>
+__device__ __forceinline__ float cta_allreduce(float v, float* slots) {
+  v = warp_allreduce<Op>(v);
+  if constexpr (NWARPS == 1) {
+    return v;
+  } else {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) slots[warp] = v;
+    __syncthreads();
+    static_assert((NWARPS & (NWARPS - 1)) == 0 && NWARPS <= 32, "NWARPS must be a power of two");
+    // Every aligned group of NWARPS lanes holds all the partials, so the
+    // narrow butterfly leaves the full result in every lane.
+    return warp_allreduce<Op, NWARPS>(slots[lane & (NWARPS - 1)]);
+  }
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tcab

@@ -1,0 +1,242 @@
+// layernorm_rows.cu -- layer-norm over the innermost axis as ONE fused
+// map | reduce | map | reduce | map kernel with fp32 statistics.
+//
+//   mean = sum_j x / n;  var = sum_j (x - mean)^2 / n;
+//   y = (x - mean) * (1 / sqrtf(var + eps)) * gamma + beta
+//
+// The reference's builder cannot express the rank-preserving store and ships an
+// RMS-flavoured reduction core instead (testing/kernels/llm/layernorm.tca:1-40,
+// runner testing/runners/layernorm.cu:47-58). bf16 rows are widened to fp32 on
+// load and rounded to nearest even on store (design/syntax-design.md:601-607).
+//
+// The row lives in registers, so x is read once and y written once (4 bytes per
+// bf16 element, 8 per fp32 element: the roofline figure). The CTAs are
+// persistent. gamma and beta are either re-read per row through the read-only
+// L1 path (they total a few KB and stay L1-resident; the row itself streams past
+// L1), or, with CACHE_GB, kept in registers as raw 16-byte vectors across all the
+// rows a thread processes. The first costs load-store issue slots, the second
+// registers and therefore resident rows per SM; the launcher picks.
+#include "rowvec.cuh"
+
+namespace tcab {
+namespace {
+
+template <typename T, int TPR, int VPT, int V, bool CACHE_GB>
+__global__ void __launch_bounds__(row_cta_threads(TPR))
+layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                   float eps, T* __restrict__ y, uint64_t rows, uint32_t cols) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  using IO = VecIO<T, V>;
+  using Raw = typename IO::Raw;
+  __shared__ float slots[2][32];
+
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const uint32_t nvec = cols / V;
+  const float n = static_cast<float>(cols);
+
+  Raw gv[CACHE_GB ? VPT : 1], bv[CACHE_GB ? VPT : 1];
+#pragma unroll
+  for (int i = 0; i < (CACHE_GB ? VPT : 0); ++i) {
+    const uint32_t idx = t + i * TPR;
+    if (idx < nvec) {
+      gv[i] = IO::load_keep(gamma, idx);
+      bv[i] = IO::load_keep(beta, idx);
+    } else {
+      float z[V];
+#pragma unroll
+      for (int j = 0; j < V; ++j) z[j] = 0.0f;
+      gv[i] = IO::pack(z);
+      bv[i] = IO::pack(z);
+    }
+  }
+
+  for (uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * GROUPS; row0 < rows;
+       row0 += static_cast<uint64_t>(gridDim.x) * GROUPS) {
+    const uint64_t row = row0 + g;
+    const bool live = row < rows;
+    const T* xr = x + row * cols;
+    T* yr = y + row * cols;
+
+    float v[VPT][V];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < nvec) {
+        IO::unpack(IO::load(xr, idx), v[i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = 0.0f;
+      }
+    }
+
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += v[i][j];
+    s = group_allreduce<OpSum, TPR>(s, slots[0]);
+    const float mean = s / n;
+
+    float q = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (idx < nvec) {  // padded points never reach the lambda (design/tca.md:297-299)
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          v[i][j] -= mean;
+          q += v[i][j] * v[i][j];
+        }
+      }
+    }
+    q = group_allreduce<OpSum, TPR>(q, slots[1]);
+    const float rstd = 1.0f / sqrtf(q / n + eps);
+
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < nvec) {
+        float gf[V], bf[V];
+        if constexpr (CACHE_GB) {
+          IO::unpack(gv[i], gf);
+          IO::unpack(bv[i], bf);
+        } else {
+          IO::unpack(IO::load_keep(gamma, idx), gf);
+          IO::unpack(IO::load_keep(beta, idx), bf);
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = v[i][j] * rstd * gf[j] + bf[j];
+        IO::store(yr, idx, IO::pack(v[i]));
+      }
+    }
+  }
+}
+
+// Rows too long for registers: one CTA per row, three streaming passes (sum,
+// centred squares, normalise); passes two and three re-read the row from L2.
+template <typename T, int THREADS, int V>
+__global__ void __launch_bounds__(THREADS)
+layernorm_rows_stream(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                      float eps, T* __restrict__ y, uint64_t rows, uint32_t cols) {
+  using IO = VecIO<T, V>;
+  __shared__ float slots[2][32];
+  const uint32_t nvec = cols / V;
+  const float n = static_cast<float>(cols);
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * cols;
+    T* yr = y + row * cols;
+    float s = 0.0f;
+    for (uint32_t idx = threadIdx.x; idx < nvec; idx += THREADS) {
+      float f[V];
+      IO::unpack(IO::load_keep(xr, idx), f);
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += f[j];
+    }
+    const float mean = cta_allreduce<OpSum, THREADS / 32>(s, slots[0]) / n;
+    float q = 0.0f;
+    for (uint32_t idx = threadIdx.x; idx < nvec; idx += THREADS) {
+      float f[V];
+      IO::unpack(IO::load_keep(xr, idx), f);
+#pragma unroll
+      for (int j = 0; j < V; ++j) q += (f[j] - mean) * (f[j] - mean);
+    }
+    const float rstd = 1.0f / sqrtf(cta_allreduce<OpSum, THREADS / 32>(q, slots[1]) / n + eps);
+    for (uint32_t idx = threadIdx.x; idx < nvec; idx += THREADS) {
+      float f[V], gf[V], bf[V];
+      IO::unpack(IO::load(xr, idx), f);
+      IO::unpack(IO::load_keep(gamma, idx), gf);
+      IO::unpack(IO::load_keep(beta, idx), bf);
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[j] = (f[j] - mean) * rstd * gf[j] + bf[j];
+      IO::store(yr, idx, IO::pack(f));
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int TPR, int VPT, int V, bool CACHE_GB>
+int launch_reg2(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                int ctas_per_sm, cudaStream_t s) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  auto* fn = layernorm_rows_reg<T, TPR, VPT, V, CACHE_GB>;
+  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
+  if (occ < 1) occ = 1;
+  const uint64_t need = (rows + GROUPS - 1) / GROUPS;
+  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  if (grid > need) grid = need;
+  fn<<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, gamma, beta, eps, y, rows, cols);
+  count_launch();
+  return check_launch("layernorm_rows_reg");
+}
+
+// tune p3 == 1 selects the register-cached gamma/beta variant.
+template <typename T, int TPR, int VPT, int V>
+int launch_reg(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+               int ctas_per_sm, cudaStream_t s) {
+  if (tune(kLayernorm).p3 == 1)
+    return launch_reg2<T, TPR, VPT, V, true>(x, gamma, beta, eps, y, rows, cols, ctas_per_sm, s);
+  return launch_reg2<T, TPR, VPT, V, false>(x, gamma, beta, eps, y, rows, cols, ctas_per_sm, s);
+}
+
+#define TCAB_LN_SHAPES_BASE(X) \
+  X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
+  X(1024, 8) X(1024, 16)
+#define TCAB_LN_SHAPES_EXTRA(X) \
+  X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(1024, 1) X(256, 8) X(512, 8) X(64, 8) X(128, 2) X(256, 2)
+
+template <typename T, int VW>
+int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+             cudaStream_t s) {
+  if (rows == 0 || cols == 0) return TCAB_OK;
+  const bool vec = (cols % VW == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
+  const uint32_t nvec = vec ? cols / VW : cols;
+  const Tune& tn = tune(kLayernorm);
+  int tpr = 0, vpt = 0;
+  bool fits = choose_row_shape(nvec, 4, &tpr, &vpt);
+  if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
+    tpr = tn.p0;
+    vpt = tn.p1;
+    fits = true;
+  }
+  if (fits) {
+#define TCAB_CASE(TP, P)                                                                         \
+  if (tpr == TP && vpt == P)                                                                     \
+    return vec ? launch_reg<T, TP, P, VW>(x, gamma, beta, eps, y, rows, cols, tn.p2, s)          \
+               : launch_reg<T, TP, P, 1>(x, gamma, beta, eps, y, rows, cols, tn.p2, s);
+    TCAB_LN_SHAPES_BASE(TCAB_CASE)
+#undef TCAB_CASE
+#define TCAB_CASE(TP, P) \
+  if (vec && tpr == TP && vpt == P) return launch_reg<T, TP, P, VW>(x, gamma, beta, eps, y, rows, cols, tn.p2, s);
+    TCAB_LN_SHAPES_EXTRA(TCAB_CASE)
+#undef TCAB_CASE
+    if (tn.p0 > 0) return fail(TCAB_ERR_UNSUPPORTED, "layernorm: no kernel for tuned shape %d x %d", tpr, vpt);
+  }
+  constexpr int THREADS = 512;
+  const uint64_t cap = static_cast<uint64_t>(sm_count()) * 4;
+  const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
+  if (vec) {
+    layernorm_rows_stream<T, THREADS, VW><<<grid, THREADS, 0, s>>>(x, gamma, beta, eps, y, rows, cols);
+  } else {
+    layernorm_rows_stream<T, THREADS, 1><<<grid, THREADS, 0, s>>>(x, gamma, beta, eps, y, rows, cols);
+  }
+  count_launch();
+  return check_launch("layernorm_rows_stream");
+}
+
+}  // namespace
+
+int launch_layernorm_rows_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma,
+                               const __nv_bfloat16* beta, float eps, __nv_bfloat16* y,
+                               uint64_t rows, uint32_t cols, cudaStream_t s) {
+  return dispatch<__nv_bfloat16, 8>(x, gamma, beta, eps, y, rows, cols, s);
+}
+
+int launch_layernorm_rows_f32(const float* x, const float* gamma, const float* beta, float eps,
+                              float* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
+  return dispatch<float, 4>(x, gamma, beta, eps, y, rows, cols, s);
+}
+
+}  // namespace tcab

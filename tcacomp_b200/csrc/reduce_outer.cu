@@ -1,0 +1,185 @@
+// reduce_outer.cu -- reduce t[b, k, c] over the MIDDLE axis k in one pass:
+// sum (fp32), max (fp32) and argmax (int32, lowest index among equal maxima).
+//
+// This is the class of the reference's middle-axis kernels (the reduced axis is
+// parked last by `as`: testing/kernels/runtime/row_sum.tca:18-33, emitted form
+// internal/cg/cxx/testdata/bracket_amort.cu:7-78 with per-thread Frag
+// accumulators). There, one thread walks the reduced axis of one output with
+// scalar loads; here a warp reads 512 contiguous bytes of one k-row per load
+// instruction and the k axis is split over the warps of the CTA.
+//
+// Layout: a CTA owns (one b, a tile of 32*V*CV columns). Lane l owns CV vectors
+// of V columns; warp w owns k = w, w+KW, w+2*KW, ... The per-thread state is
+// (sum, best, best_index) per owned column. Each thread issues UNROLL
+// independent 16-byte loads before folding them, so a CTA keeps
+// 32*KW*UNROLL*CV*16 bytes in flight. The KW partial states per column are then
+// combined through shared memory in ascending warp order with the tie rule
+// "greater value, or equal value and lower index", which makes max and argmax
+// bit-exact against a sequential ascending fold with a strict `>` update.
+// Algorithmic bytes: 4 per input element plus 12 per output column.
+#include "common.cuh"
+
+namespace tcab {
+namespace {
+
+template <int V>
+struct ColVec;
+template <>
+struct ColVec<4> {
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 q = ld_stream(reinterpret_cast<const float4*>(p));
+    f[0] = q.x; f[1] = q.y; f[2] = q.z; f[3] = q.w;
+  }
+};
+template <>
+struct ColVec<1> {
+  static __device__ __forceinline__ void load(const float* p, float* f) { f[0] = ld_stream(p); }
+};
+
+template <int V, int CV, int KW, int UNROLL>
+__global__ void __launch_bounds__(32 * KW)
+reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float* __restrict__ mx,
+                    int32_t* __restrict__ amax, uint32_t nb, uint32_t nk, uint32_t nc,
+                    uint32_t tiles_per_b) {
+  constexpr int TILE_C = 32 * V * CV;
+  constexpr int NCOL = V * CV;  // columns owned by a thread
+  extern __shared__ float smem[];
+  float* s_sum = smem;                                   // [KW][TILE_C]
+  float* s_max = smem + KW * TILE_C;                     // [KW][TILE_C]
+  int32_t* s_idx = reinterpret_cast<int32_t*>(smem + 2 * KW * TILE_C);  // [KW][TILE_C]
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  for (uint32_t tile = blockIdx.x; tile < nb * tiles_per_b; tile += gridDim.x) {
+    const uint32_t b = tile / tiles_per_b;
+    const uint32_t c0 = (tile % tiles_per_b) * TILE_C;
+    const float* base = t + static_cast<size_t>(b) * nk * nc;
+
+    float acc[NCOL], best[NCOL];
+    int32_t bidx[NCOL];
+#pragma unroll
+    for (int j = 0; j < NCOL; ++j) {
+      acc[j] = 0.0f;
+      best[j] = -INFINITY;
+      bidx[j] = 0;
+    }
+    // Column of vector i of this lane: c0 + (i*32 + lane)*V
+    bool colok[CV];
+#pragma unroll
+    for (int i = 0; i < CV; ++i) colok[i] = c0 + (i * 32 + lane) * V < nc;  // nc % V == 0 when V == 4
+
+    for (uint32_t k0 = warp; k0 < nk; k0 += KW * UNROLL) {
+      float f[UNROLL][NCOL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const uint32_t k = k0 + u * KW;
+#pragma unroll
+        for (int i = 0; i < CV; ++i) {
+          if (k < nk && colok[i]) {
+            ColVec<V>::load(base + static_cast<size_t>(k) * nc + c0 + (i * 32 + lane) * V, &f[u][i * V]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < V; ++j) f[u][i * V + j] = 0.0f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const uint32_t k = k0 + u * KW;
+        if (k < nk) {
+#pragma unroll
+          for (int j = 0; j < NCOL; ++j) {
+            const float v = f[u][j];
+            acc[j] += v;
+            if (v > best[j]) {  // strict: the lowest index among equals survives
+              best[j] = v;
+              bidx[j] = static_cast<int32_t>(k);
+            }
+          }
+        }
+      }
+    }
+
+#pragma unroll
+    for (int i = 0; i < CV; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const int col = (i * 32 + lane) * V + j;
+        s_sum[warp * TILE_C + col] = acc[i * V + j];
+        s_max[warp * TILE_C + col] = best[i * V + j];
+        s_idx[warp * TILE_C + col] = bidx[i * V + j];
+      }
+    __syncthreads();
+    for (int col = threadIdx.x; col < TILE_C; col += 32 * KW) {
+      if (c0 + col < nc) {
+        float a = 0.0f, bv = -INFINITY;
+        int32_t bi = 0;
+#pragma unroll
+        for (int w = 0; w < KW; ++w) {
+          a += s_sum[w * TILE_C + col];
+          const float v = s_max[w * TILE_C + col];
+          const int32_t vi = s_idx[w * TILE_C + col];
+          // a warp that saw no k (nk < KW) still holds (-inf, 0): never preferred over a real entry,
+          // and equal to the initial state otherwise
+          if (v > bv || (v == bv && vi < bi)) {
+            bv = v;
+            bi = vi;
+          }
+        }
+        const size_t o = static_cast<size_t>(b) * nc + c0 + col;
+        if (sum) sum[o] = a;
+        if (mx) mx[o] = bv;
+        if (amax) amax[o] = bi;
+      }
+    }
+    __syncthreads();  // shared memory is rewritten by the next tile
+  }
+}
+
+template <int V, int CV, int KW, int UNROLL>
+int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, uint32_t nk, uint32_t nc,
+           int ctas_per_sm, cudaStream_t s) {
+  constexpr int TILE_C = 32 * V * CV;
+  constexpr int THREADS = 32 * KW;
+  const size_t smem = static_cast<size_t>(3) * KW * TILE_C * sizeof(float);
+  auto* fn = reduce_outer_kernel<V, CV, KW, UNROLL>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return fail(TCAB_ERR_CUDA, "reduce_outer: cannot reserve %zu bytes of shared memory", smem);
+  }
+  const uint32_t tiles_per_b = (nc + TILE_C - 1) / TILE_C;
+  const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
+  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, smem);
+  if (occ < 1) occ = 1;
+  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  if (grid > tiles) grid = tiles;
+  fn<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b);
+  count_launch();
+  return check_launch("reduce_outer_kernel");
+}
+
+}  // namespace
+
+int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, uint32_t nk,
+                        uint32_t nc, cudaStream_t s) {
+  if (nb == 0 || nc == 0) return TCAB_OK;
+  if (static_cast<uint64_t>(nb) * ((nc + 31) / 32) > 0xffffffffull)
+    return fail(TCAB_ERR_TOO_LARGE, "reduce_outer: too many column tiles");
+  const bool vec = (nc % 4 == 0) && aligned16(t);
+  const Tune& tn = tune(kReduceOuter);
+  // p0: vectors per lane (1|2), p1: warps splitting k (4|8|16), p2: CTAs per SM.
+  const int cv = tn.p0 > 0 ? tn.p0 : 1;
+  const int kw = tn.p1 > 0 ? tn.p1 : 8;
+  if (vec) {
+    if (cv == 1 && kw == 8) return launch<4, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 2 && kw == 8) return launch<4, 2, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 1 && kw == 16) return launch<4, 1, 16, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 2 && kw == 16) return launch<4, 2, 16, 2>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 1 && kw == 4) return launch<4, 1, 4, 8>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 2 && kw == 4) return launch<4, 2, 4, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    return fail(TCAB_ERR_UNSUPPORTED, "reduce_outer: no kernel for tuned shape %d x %d", cv, kw);
+  }
+  return launch<1, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+}
+
+}  // namespace tcab

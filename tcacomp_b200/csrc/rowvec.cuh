@@ -1,0 +1,125 @@
+// rowvec.cuh -- element/vector adaptors and launch-shape choice for the row kernels
+// (softmax, layer-norm, innermost-axis chains).
+//
+// A row is processed by a GROUP of TPR threads; thread t of the group owns the
+// vectors t, t+TPR, t+2*TPR, ... of the row, so that one load instruction of a
+// warp covers 32 consecutive 16-byte vectors (512 contiguous bytes). The
+// reference's views read one bounds-checked scalar per access
+// (runtime/tca/view.h:104-112); here the bounds test is one compare per vector.
+#pragma once
+
+#include "common.cuh"
+
+namespace tcab {
+
+#ifdef __CUDACC__
+
+// VecIO<T, V>: V elements of type T moved as one access, unpacked to fp32.
+template <typename T, int V>
+struct VecIO;
+
+template <>
+struct VecIO<float, 4> {
+  using Raw = float4;
+  static __device__ __forceinline__ Raw load(const float* row, uint32_t i) {
+    return ld_stream(reinterpret_cast<const float4*>(row) + i);
+  }
+  static __device__ __forceinline__ Raw load_keep(const float* row, uint32_t i) {
+    return __ldg(reinterpret_cast<const float4*>(row) + i);
+  }
+  static __device__ __forceinline__ void store(float* row, uint32_t i, Raw r) {
+    st_stream(reinterpret_cast<float4*>(row) + i, r);
+  }
+  static __device__ __forceinline__ void unpack(Raw r, float* f) {
+    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  }
+  static __device__ __forceinline__ Raw pack(const float* f) { return make_float4(f[0], f[1], f[2], f[3]); }
+};
+
+template <>
+struct VecIO<float, 1> {
+  using Raw = float;
+  static __device__ __forceinline__ Raw load(const float* row, uint32_t i) { return ld_stream(row + i); }
+  static __device__ __forceinline__ Raw load_keep(const float* row, uint32_t i) { return __ldg(row + i); }
+  static __device__ __forceinline__ void store(float* row, uint32_t i, Raw r) { st_stream(row + i, r); }
+  static __device__ __forceinline__ void unpack(Raw r, float* f) { f[0] = r; }
+  static __device__ __forceinline__ Raw pack(const float* f) { return f[0]; }
+};
+
+// bf16 is a storage type: widened to fp32 on load, rounded to nearest even on
+// store (design/syntax-design.md:601-607).
+template <>
+struct VecIO<__nv_bfloat16, 8> {
+  using Raw = uint4;
+  static __device__ __forceinline__ Raw load(const __nv_bfloat16* row, uint32_t i) {
+    return ld_stream(reinterpret_cast<const uint4*>(row) + i);
+  }
+  static __device__ __forceinline__ Raw load_keep(const __nv_bfloat16* row, uint32_t i) {
+    return __ldg(reinterpret_cast<const uint4*>(row) + i);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* row, uint32_t i, Raw r) {
+    st_stream(reinterpret_cast<uint4*>(row) + i, r);
+  }
+  static __device__ __forceinline__ void unpack(Raw r, float* f) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[2 * j] = __uint_as_float(w[j] << 16);
+      f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+  static __device__ __forceinline__ Raw pack(const float* f) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+      w[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <>
+struct VecIO<__nv_bfloat16, 1> {
+  using Raw = __nv_bfloat16;
+  static __device__ __forceinline__ Raw load(const __nv_bfloat16* row, uint32_t i) { return row[i]; }
+  static __device__ __forceinline__ Raw load_keep(const __nv_bfloat16* row, uint32_t i) { return row[i]; }
+  static __device__ __forceinline__ void store(__nv_bfloat16* row, uint32_t i, Raw r) { row[i] = r; }
+  static __device__ __forceinline__ void unpack(Raw r, float* f) { f[0] = __bfloat162float(r); }
+  static __device__ __forceinline__ Raw pack(const float* f) { return __float2bfloat16_rn(f[0]); }
+};
+
+// Reduction across the TPR threads of a row group; every thread gets the result.
+// TPR <= 32: shuffles only. TPR > 32: the group is the whole CTA.
+template <typename Op, int TPR>
+__device__ __forceinline__ float group_allreduce(float v, float* slots) {
+  if constexpr (TPR <= 32) {
+    return warp_allreduce<Op, TPR>(v);
+  } else {
+    return cta_allreduce<Op, TPR / 32>(v, slots);
+  }
+}
+
+#endif  // __CUDACC__
+
+// CTA size of a row kernel whose groups have TPR threads: at least 128 threads,
+// so that short rows still fill a CTA with several rows.
+__host__ __device__ constexpr int row_cta_threads(int tpr) { return tpr > 128 ? tpr : 128; }
+
+// Launch shape for a register-resident row: the smallest group (power of two,
+// 8..1024 threads) whose threads hold at most `vpt_target` vectors each, and
+// the power-of-two vector count per thread that then covers the row.
+// Returns false when the row does not fit 1024 threads x 32 vectors.
+inline bool choose_row_shape(uint32_t nvec, int vpt_target, int* tpr, int* vpt) {
+  if (nvec == 0) nvec = 1;
+  uint32_t t = pow2_ceil((nvec + vpt_target - 1) / vpt_target);
+  if (t < 8) t = 8;
+  if (t > 1024) t = 1024;
+  uint32_t v = pow2_ceil((nvec + t - 1) / t);
+  if (v > 32) return false;
+  *tpr = static_cast<int>(t);
+  *vpt = static_cast<int>(v);
+  return true;
+}
+
+}  // namespace tcab

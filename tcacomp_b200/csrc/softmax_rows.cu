@@ -1,0 +1,192 @@
+// softmax_rows.cu -- row softmax as ONE fused map | reduce | map kernel.
+//
+//   m_i = max_j x[i,j];  s_i = sum_j expf(x[i,j] - m_i);  y[i,j] = expf(x[i,j] - m_i) / s_i
+//
+// The reference cannot store a rank-preserving map (pkg/chain.go:433-438) and
+// ships only the reduction core of this chain (testing/kernels/fusion/softmax.tca,
+// runner testing/runners/softmax.cu:49-61); its reducers run one shuffle tree and
+// two barriers PER ELEMENT (runtime/tca/reducer.h:109-167).
+//
+// Two kernels:
+//   softmax_rows_reg     the row lives in registers: x is read from HBM once and
+//                        y written once (8 bytes per element, the roofline figure);
+//                        one shuffle/shared-memory tree per reduction per ROW.
+//   softmax_rows_online  rows too long for registers: a single streaming pass
+//                        keeps a running (max, sum) pair per thread, rescaling
+//                        the sum when the max moves, then a second pass over the
+//                        row (L2-resident for any realistic row) writes y.
+// expf is the accurate CUDA expf (no fast-math); y multiplies by 1/s_i, which
+// differs from the division by at most 1 ulp.
+#include "rowvec.cuh"
+
+namespace tcab {
+namespace {
+
+template <int TPR, int VPT, int V>
+__global__ void __launch_bounds__(row_cta_threads(TPR))
+softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  using IO = VecIO<float, V>;
+  __shared__ float slots[2][32];
+
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const uint32_t nvec = cols / V;
+
+  for (uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * GROUPS; row0 < rows;
+       row0 += static_cast<uint64_t>(gridDim.x) * GROUPS) {
+    const uint64_t row = row0 + g;
+    const bool live = row < rows;
+    const float* xr = x + row * cols;
+    float* yr = y + row * cols;
+
+    float v[VPT][V];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < nvec) {
+        IO::unpack(IO::load(xr, idx), v[i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;  // identity of max; expf(-inf - m) = 0
+      }
+    }
+
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+    m = group_allreduce<OpMax, TPR>(m, slots[0]);
+
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        v[i][j] = expf(v[i][j] - m);
+        s += v[i][j];
+      }
+    s = group_allreduce<OpSum, TPR>(s, slots[1]);
+    const float inv = 1.0f / s;
+
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < nvec) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] *= inv;
+        IO::store(yr, idx, IO::pack(v[i]));
+      }
+    }
+  }
+}
+
+// One CTA per row, any length. Pass 1 is the single-pass online max/sum.
+template <int THREADS, int V>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_online(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols) {
+  using IO = VecIO<float, V>;
+  __shared__ float slots[2][32];
+  const uint32_t nvec = cols / V;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * cols;
+    float* yr = y + row * cols;
+    float m = -INFINITY, s = 0.0f;
+    for (uint32_t idx = threadIdx.x; idx < nvec; idx += THREADS) {
+      float f[V];
+      IO::unpack(IO::load_keep(xr, idx), f);
+      float lm = f[0];
+#pragma unroll
+      for (int j = 1; j < V; ++j) lm = fmaxf(lm, f[j]);
+      if (lm > m) {  // the running max moves: rescale what was summed so far
+        s *= expf(m - lm);
+        m = lm;
+      }
+      if (m != -INFINITY) {  // nothing finite seen yet: -inf entries add 0, as in the plain formula
+#pragma unroll
+        for (int j = 0; j < V; ++j) s += expf(f[j] - m);
+      }
+    }
+    const float gm = cta_allreduce<OpMax, THREADS / 32>(m, slots[0]);
+    // A thread that saw nothing has m = -inf and s = 0; expf(-inf - gm) = 0 keeps it neutral
+    // unless gm is -inf too (an all -inf row), which yields NaN exactly like the plain formula.
+    s = (m == -INFINITY && gm != -INFINITY) ? 0.0f : s * expf(m - gm);
+    const float gs = cta_allreduce<OpSum, THREADS / 32>(s, slots[1]);
+    const float inv = 1.0f / gs;
+    for (uint32_t idx = threadIdx.x; idx < nvec; idx += THREADS) {
+      float f[V];
+      IO::unpack(IO::load(xr, idx), f);
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[j] = expf(f[j] - gm) * inv;
+      IO::store(yr, idx, IO::pack(f));
+    }
+    __syncthreads();  // slots are rewritten by the next row
+  }
+}
+
+template <int TPR, int VPT, int V>
+int launch_reg(const float* x, float* y, uint64_t rows, uint32_t cols, int ctas_per_sm, cudaStream_t s) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  auto* fn = softmax_rows_reg<TPR, VPT, V>;
+  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
+  if (occ < 1) occ = 1;
+  const uint64_t need = (rows + GROUPS - 1) / GROUPS;
+  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  if (grid > need) grid = need;
+  fn<<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, y, rows, cols);
+  count_launch();
+  return check_launch("softmax_rows_reg");
+}
+
+// The (TPR, VPT) shapes choose_row_shape(nvec, 8) can return, plus the other
+// covers of a 1024-vector row that the tuning hook may select.
+#define TCAB_ROW_SHAPES_BASE(X) \
+  X(8, 1) X(8, 2) X(8, 4) X(8, 8) X(16, 8) X(32, 8) X(64, 8) X(128, 8) X(256, 8) X(512, 8) \
+  X(1024, 8) X(1024, 16) X(1024, 32)
+#define TCAB_ROW_SHAPES_EXTRA(X) \
+  X(32, 16) X(32, 32) X(64, 16) X(128, 4) X(256, 4) X(256, 2) X(512, 2) X(512, 4) X(1024, 1) \
+  X(1024, 2) X(1024, 4) X(64, 4) X(128, 2) X(128, 16) X(256, 16)
+
+}  // namespace
+
+int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
+  if (rows == 0 || cols == 0) return TCAB_OK;  // nothing to write (design/tca.md:297-299)
+  const bool vec = (cols % 4 == 0) && aligned16(x) && aligned16(y);
+  const uint32_t nvec = vec ? cols / 4 : cols;
+  const Tune& tn = tune(kSoftmax);
+  int tpr = 0, vpt = 0;
+  bool fits = choose_row_shape(nvec, 8, &tpr, &vpt);
+  if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
+    tpr = tn.p0;
+    vpt = tn.p1;
+    fits = true;
+  }
+  if (fits) {
+#define TCAB_CASE(T, P) \
+  if (tpr == T && vpt == P) return vec ? launch_reg<T, P, 4>(x, y, rows, cols, tn.p2, s) \
+                                       : launch_reg<T, P, 1>(x, y, rows, cols, tn.p2, s);
+    TCAB_ROW_SHAPES_BASE(TCAB_CASE)
+#undef TCAB_CASE
+#define TCAB_CASE(T, P) \
+  if (vec && tpr == T && vpt == P) return launch_reg<T, P, 4>(x, y, rows, cols, tn.p2, s);
+    TCAB_ROW_SHAPES_EXTRA(TCAB_CASE)
+#undef TCAB_CASE
+    if (tn.p0 > 0) return fail(TCAB_ERR_UNSUPPORTED, "softmax: no kernel for tuned shape %d x %d", tpr, vpt);
+  }
+  // Long rows: one CTA per row, online pass.
+  constexpr int THREADS = 512;
+  const uint64_t cap = static_cast<uint64_t>(sm_count()) * 4;
+  const unsigned grid = static_cast<unsigned>(rows < cap ? rows : cap);
+  if (vec) {
+    softmax_rows_online<THREADS, 4><<<grid, THREADS, 0, s>>>(x, y, rows, cols);
+  } else {
+    softmax_rows_online<THREADS, 1><<<grid, THREADS, 0, s>>>(x, y, rows, cols);
+  }
+  count_launch();
+  return check_launch("softmax_rows_online");
+}
+
+}  // namespace tcab

@@ -1,0 +1,155 @@
+"""Operators over torch CUDA tensors; each is exactly one call through the C ABI.
+
+Arguments mirror the reference's generated launchers (inputs, then the output,
+then scalars, then the stream -- internal/cg/cxx/launch.go:23-156): the caller
+owns all memory, outputs may be passed in to avoid an allocation, calls are
+asynchronous on the given (or current) torch stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int32: _lib.I32}
+
+
+def _view(t: torch.Tensor, name: str) -> _lib.Tensor:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.device.type != "cuda":
+        raise ValueError(f"{name} must live on a CUDA device (this library has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous (row-major), as the reference's tensors are")
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"{name}: unsupported dtype {t.dtype}")
+    if t.dim() < 1 or t.dim() > _lib.MAX_RANK:
+        raise ValueError(f"{name}: rank {t.dim()} outside 1..{_lib.MAX_RANK}")
+    v = _lib.Tensor()
+    v.data = t.data_ptr()
+    v.dtype = _DTYPES[t.dtype]
+    v.rank = t.dim()
+    for i, d in enumerate(t.shape):
+        v.dims[i] = d
+    return v
+
+
+def _stream(stream: Optional[torch.cuda.Stream], ref: torch.Tensor) -> C.c_void_p:
+    s = stream if stream is not None else torch.cuda.current_stream(ref.device)
+    return C.c_void_p(s.cuda_stream)
+
+
+def _on_device(t: torch.Tensor):
+    return torch.cuda.device(t.device)
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process."""
+    return int(_lib.load().tcab_launch_count())
+
+
+def tune(family: str, p0: int = 0, p1: int = 0, p2: int = 0, p3: int = 0) -> None:
+    """Override (or with zeros, restore) the launch shape of one kernel family."""
+    _lib.check(_lib.load().tcab_tune(family.encode(), p0, p1, p2, p3))
+
+
+def softmax_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Row softmax over the innermost axis (fp32)."""
+    if out is None:
+        out = torch.empty_like(x)
+    xv, yv = _view(x, "x"), _view(out, "out")
+    with _on_device(x):
+        _lib.check(_lib.load().tcab_softmax_rows(C.byref(xv), C.byref(yv), _stream(stream, x)))
+    return out
+
+
+def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float = 1e-5,
+                   out: Optional[torch.Tensor] = None,
+                   stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Layer-norm over the innermost axis, fp32 statistics, bf16 or fp32 rows."""
+    if out is None:
+        out = torch.empty_like(x)
+    xv, gv, bv, yv = _view(x, "x"), _view(gamma, "gamma"), _view(beta, "beta"), _view(out, "out")
+    with _on_device(x):
+        _lib.check(_lib.load().tcab_layernorm_rows(C.byref(xv), C.byref(gv), C.byref(bv),
+                                                   C.c_float(eps), C.byref(yv), _stream(stream, x)))
+    return out
+
+
+def reduce_outer(t: torch.Tensor, want: Sequence[str] = ("sum", "max", "argmax"),
+                 out: Optional[dict] = None, stream: Optional[torch.cuda.Stream] = None) -> dict:
+    """Reduce t[b, k, c] over k in one pass; returns {"sum", "max", "argmax"} as requested."""
+    if t.dim() != 3:
+        raise ValueError("t must be rank 3 [b, k, c]")
+    res = dict(out or {})
+    for name in want:
+        if name not in ("sum", "max", "argmax"):
+            raise ValueError(f"unknown output {name!r}")
+        if name not in res:
+            res[name] = torch.empty((t.shape[0], t.shape[2]), device=t.device,
+                                    dtype=torch.int32 if name == "argmax" else torch.float32)
+    tv = _view(t, "t")
+    views = {k: _view(v, k) for k, v in res.items()}
+
+    def ref(k):
+        return C.byref(views[k]) if k in views else None
+
+    with _on_device(t):
+        _lib.check(_lib.load().tcab_reduce_outer(C.byref(tv), ref("sum"), ref("max"), ref("argmax"),
+                                                 _stream(stream, t)))
+    return res
+
+
+def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str = "(p0 + p1)",
+                 init: float = 0.0, post_expr: Optional[str] = None, captures: Sequence[float] = (),
+                 axis: int = -1, out: Optional[torch.Tensor] = None,
+                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """map | reduce | [map] over one axis of identically shaped fp32 operands.
+
+    The lambdas are C expressions over p0.. (operands), c0.. (captures) in the
+    reference's operator and builtin vocabulary, e.g. map_expr="(p0 * p1)".
+    """
+    ins = list(ins)
+    if not 1 <= len(ins) <= _lib.MAX_INPUTS:
+        raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
+    if len(captures) > _lib.MAX_CAPTURES:
+        raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
+    t0 = ins[0]
+    ax = axis % t0.dim()
+    if out is None:
+        shape = [d for i, d in enumerate(t0.shape) if i != ax] or [1]
+        out = torch.empty(shape, device=t0.device, dtype=torch.float32)
+    chain = _lib.Chain()
+    chain.map_expr = map_expr.encode()
+    chain.combine_expr = combine_expr.encode()
+    chain.post_expr = post_expr.encode() if post_expr else None
+    chain.init = init
+    chain.n_captures = len(captures)
+    for i, c in enumerate(captures):
+        chain.captures[i] = c
+    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    ov = _view(out, "out")
+    with _on_device(t0):
+        _lib.check(_lib.load().tcab_chain_reduce(C.byref(chain), arr, len(ins), ax, C.byref(ov),
+                                                 _stream(stream, t0)))
+    return out
+
+
+def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  act: str = "relu", out: Optional[torch.Tensor] = None,
+                  stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """c = act(a @ b + bias): a [M,K] bf16, b [K,N] bf16, bias [N] fp32, c [M,N] bf16."""
+    if out is None:
+        out = torch.empty((a.shape[0], b.shape[1]), device=a.device, dtype=torch.bfloat16)
+    av, bv, cv = _view(a, "a"), _view(b, "b"), _view(out, "out")
+    biasv = _view(bias, "bias") if bias is not None else None
+    code = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU}[act]
+    with _on_device(a):
+        _lib.check(_lib.load().tcab_gemm_bias_act(C.byref(av), C.byref(bv),
+                                                  C.byref(biasv) if biasv is not None else None, code,
+                                                  C.byref(cv), _stream(stream, a)))
+    return out

@@ -1,0 +1,382 @@
+"""Parity of the CUDA kernels (through the C ABI) with the CPU oracle on a B200.
+
+Tolerances, as stated for this path:
+  * integer / index outputs (argmax) and max: bit-exact;
+  * fp32 reductions: |gpu - oracle| <= 1e-5 relative, with the denominators
+    written at each test (normwise max|ref|, and per element sum|x_i| where the
+    sum cancels);
+  * softmax / layer-norm outputs (a map after reductions): 1e-5 relative for
+    fp32, one bf16 ulp for bf16 outputs.
+Every output buffer is prefilled with a canary and padded with guard bands, the
+reference's own way of proving that every element was written and nothing else
+(internal/e2e/harness.go:158-181, testing/runners/common.cuh).
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tcacomp_b200 as T
+
+pytestmark = pytest.mark.gpu
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLDEN = json.load(open(os.path.join(HERE, "golden", "suite_golden.json")))
+CANARY = -12345.0
+GUARD = 64
+
+
+def guarded(shape, dtype, dev):
+    """An output view with CANARY-filled guard bands on both sides of it."""
+    n = int(np.prod(shape))
+    buf = torch.full((n + 2 * GUARD,), CANARY, dtype=torch.float32, device=dev).to(dtype)
+    return buf, buf[GUARD:GUARD + n].view(*shape)
+
+
+def check_guards(buf, dtype):
+    b = buf.float().cpu().numpy()
+    want = torch.tensor(CANARY).to(dtype).float().item()
+    assert (b[:GUARD] == want).all() and (b[-GUARD:] == want).all(), "kernel wrote outside its output"
+
+
+def dev_f32(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def dev_bf16(bits, dev):
+    return torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
+
+
+def host_bits(t):
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+# ----------------------------------------------------------------------------
+# fused map + innermost-axis reduce
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(4096, 1024), (1, 1), (3, 5), (37, 130), (64, 32), (129, 264),
+                                       (5, 9000), (2, 70001), (1000, 4)])
+def test_map_rowsum(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(rows * 131 + cols)
+    x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    want = oracle.map_rowsum_affine_sq(x)
+    buf, out = guarded((rows,), torch.float32, cuda)
+    T.chain_reduce([dev_f32(x, cuda)], "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)", out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert (got != CANARY).all()
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    assert (np.abs(got - want) <= 1e-5 * np.abs(want)).all()  # all terms positive: per element too
+
+
+def test_map_rowsum_unaligned_and_captures(oracle, cuda):
+    rng = np.random.default_rng(1)
+    x = rng.uniform(-1, 1, (33, 1024)).astype(np.float32)
+    base = torch.zeros(33 * 1024 + 1, device=cuda)
+    xd = base[1:].view(33, 1024)  # 4-byte aligned only: the scalar path
+    xd.copy_(dev_f32(x, cuda))
+    got = T.chain_reduce([xd], "(c0*p0 + c1) * (c0*p0 + c1)", captures=(0.5, 0.25)).cpu().numpy()
+    want = oracle.map_rowsum_affine_sq(x)
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("op,expr,init", [("sum", "(p0 + p1)", 0.0), ("max", "fmaxf(p0, p1)", -np.inf),
+                                          ("min", "fminf(p0, p1)", np.inf), ("sum", "(p0 + p1)", 2.5)])
+def test_row_reduce_ops_and_init(oracle, cuda, op, expr, init):
+    rng = np.random.default_rng(2)
+    for rows, cols in [(17, 300), (4, 4), (2, 5000)]:
+        x = rng.normal(0, 3, (rows, cols)).astype(np.float32)
+        want = oracle.row_reduce(x, op, init)
+        got = T.chain_reduce([dev_f32(x, cuda)], "p0", combine_expr=expr, init=float(init)).cpu().numpy()
+        if op == "sum":
+            assert (np.abs(got - want) <= 1e-5 * np.abs(x).sum(1)).all()
+        else:
+            assert np.array_equal(got, want)  # max/min are order-independent: bit-exact
+    # empty reduction returns init (design/tca.md:299)
+    e = torch.zeros((6, 0), device=cuda)
+    got = T.chain_reduce([e], "p0", combine_expr=expr, init=float(init)).cpu().numpy()
+    assert np.array_equal(got, np.full(6, init, np.float32))
+
+
+def test_thread_per_row_is_bit_exact(oracle, cuda):
+    # rows of <= 32 elements are folded by one thread in ascending order: the reference's
+    # SeqReducer order (runtime/tca/reducer.h:45-51), so even sums match bit for bit
+    rng = np.random.default_rng(4)
+    x = rng.uniform(-1, 1, (513, 32)).astype(np.float32)
+    got = T.chain_reduce([dev_f32(x, cuda)], "p0").cpu().numpy()
+    assert np.array_equal(got, oracle.row_reduce(x, "sum", 0.0))
+
+
+# ----------------------------------------------------------------------------
+# the reference's suite kernels that are reductions of identically shaped operands
+# ----------------------------------------------------------------------------
+SUITE_CHAINS = {
+    # name: (map, post, axis, captures)
+    "row_sum": ("(p0 * p1)", None, 1, ()),
+    "softmax": ("(expf(p0) * p1)", None, 1, ()),
+    "transpose": ("(p0 * p1)", None, 2, ()),
+    "scale_copy": ("((c0 * p0) + c1) * p1", None, 2, (1.25, -0.125)),
+    "axpy3": ("c0 * p0 + c1 * p1", "p0 + c2 * tanhf(p0)", 2, (2.0, 0.5, 0.75)),
+    "layernorm": ("(p0 * p0) * p1", "p0 * rsqrtf(p0 * c0 + c1)", 2, (1.0 / 64.0, 1e-5)),
+}
+SUITE_TOL = {"row_sum": 2e-3, "softmax": 2e-3, "transpose": 1e-5, "scale_copy": 1e-5, "axpy3": 1e-5,
+             "layernorm": 1e-5}  # testing/suite.toml tolerances (max abs diff)
+
+
+@pytest.mark.parametrize("name", sorted(SUITE_CHAINS))
+def test_reference_suite_kernels(oracle, cuda, name):
+    mp, post, axis, caps = SUITE_CHAINS[name]
+    x, z = oracle.suite_inputs(name)
+    want = oracle.suite(name)
+    g = GOLDEN[name]
+    assert abs(want.astype(np.float64).sum() - g["checksum"]) <= 1e-6 * abs(g["checksum"])
+    buf, out = guarded(want.shape, torch.float32, cuda)
+    T.chain_reduce([dev_f32(x, cuda), dev_f32(z, cuda)], mp, post_expr=post, captures=caps, axis=axis, out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert (got == CANARY).sum() == 0  # the runner's CANARY line
+    assert np.abs(got.astype(np.float64) - want).max() <= SUITE_TOL[name]  # the runner's MAXDIFF line
+    assert abs(got.astype(np.float64).sum() - g["checksum"]) <= 1e-5 * abs(g["checksum"])
+
+
+def test_e2e_row_sum_fixture(oracle, cuda):
+    # internal/e2e/e2e_test.go:15-21,300-330: 1024 x 512 row sums of elem(i), tolerance 2e-3 absolute
+    x = oracle.elem_fill(1024 * 512).reshape(1024, 512)
+    got = T.chain_reduce([dev_f32(x, cuda)], "p0").cpu().numpy()
+    g = GOLDEN["e2e_row_sum_1024x512"]
+    assert np.abs(got - oracle.row_reduce(x, "sum", 0.0)).max() <= 2e-3
+    assert abs(got.astype(np.float64).sum() - g["checksum"]) <= 1e-5 * g["checksum"]
+
+
+# ----------------------------------------------------------------------------
+# row softmax
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (1, 1), (3, 7), (33, 517), (130, 32), (7, 1000), (5, 12288),
+                                       (3, 40000), (2, 140004), (2, 140001)])
+def test_softmax_rows(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(rows * 7 + cols)
+    x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
+    want = oracle.softmax_rows(x)
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    T.softmax_rows(dev_f32(x, cuda), out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    # a map after fp32 reductions: 1e-5 relative per element (plus a floor at the smallest normal)
+    assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-37).all()
+    assert np.abs(got.astype(np.float64).sum(1) - 1.0).max() <= 1e-5
+
+
+def test_softmax_unaligned_view(oracle, cuda):
+    rng = np.random.default_rng(12)
+    x = (4 * rng.normal(0, 1, (9, 256))).astype(np.float32)
+    base = torch.zeros(9 * 256 + 3, device=cuda)
+    xd = base[3:].view(9, 256)
+    xd.copy_(dev_f32(x, cuda))
+    got = T.softmax_rows(xd).cpu().numpy()
+    assert (np.abs(got - oracle.softmax_rows(x)) <= 1e-5 * oracle.softmax_rows(x) + 1e-37).all()
+
+
+def test_softmax_extremes(oracle, cuda):
+    x = np.array([[1e4, -1e4, 0, 88.0], [-np.inf, 0.0, 1.0, -np.inf], [3.0, 3.0, 3.0, 3.0]], np.float32)
+    got = T.softmax_rows(dev_f32(x, cuda)).cpu().numpy()
+    want = oracle.softmax_rows(x)
+    assert np.allclose(got, want, rtol=1e-5, atol=0)
+    for cols in (4, 140004):  # the register-resident kernel and the online one
+        xx = np.full((2, cols), -np.inf, np.float32)
+        xx[1, cols // 2] = 5.0
+        g = T.softmax_rows(dev_f32(xx, cuda)).cpu().numpy()
+        assert np.isnan(g[0]).all() and g[1, cols // 2] == 1.0 and g[1].sum() == 1.0
+
+
+def test_softmax_full_size_properties_and_sampled_rows(oracle, cuda):
+    # the benchmark configuration: fp32 [16384, 4096] ~ 4*N(0,1)
+    gen = torch.Generator(device=cuda).manual_seed(2024)
+    x = 4 * torch.randn((16384, 4096), generator=gen, device=cuda)
+    y = T.softmax_rows(x)
+    s = y.double().sum(1)
+    assert (s - 1).abs().max().item() <= 1e-5
+    # the largest input of a row receives the largest output
+    assert (y >= 0).all() and torch.equal(y.gather(1, x.argmax(1, keepdim=True)).squeeze(1), y.amax(1))
+    idx = torch.tensor([0, 1, 4097, 9999, 16383], device=cuda)
+    want = oracle.softmax_rows(x[idx].cpu().numpy())
+    got = y[idx].cpu().numpy()
+    assert (np.abs(got - want) <= 1e-5 * want + 1e-37).all()
+
+
+# ----------------------------------------------------------------------------
+# layer-norm
+# ----------------------------------------------------------------------------
+def bf16_ulp_diff(a_bits, b_bits):
+    def key(u):
+        u = u.astype(np.int32)
+        return np.where(u & 0x8000, 0x8000 - u, u)
+    return np.abs(key(a_bits) - key(b_bits))
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 8192), (1, 1), (3, 7), (17, 264), (130, 64), (9, 1000), (4, 16384),
+                                       (3, 70000), (2, 300008)])
+def test_layernorm_rows_bf16(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(rows * 3 + cols)
+    x = oracle.f32_to_bf16(rng.normal(0, 1, (rows, cols)).astype(np.float32))
+    g = oracle.f32_to_bf16(rng.normal(1, 0.1, cols).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.normal(0, 0.1, cols).astype(np.float32))
+    want = oracle.layernorm_rows_bf16(x, g, b, 1e-5)
+    buf, out = guarded((rows, cols), torch.bfloat16, cuda)
+    T.layernorm_rows(dev_bf16(x, cuda), dev_bf16(g, cuda), dev_bf16(b, cuda), 1e-5, out=out)
+    got = host_bits(out)
+    check_guards(buf, torch.bfloat16)
+    d = bf16_ulp_diff(got, want)
+    # the fp32 statistics differ in the last bits (tree vs sequential fold), which can move a value
+    # across a bf16 rounding boundary: at most one bf16 ulp, and only rarely
+    assert d.max() <= 1
+    assert (d != 0).mean() <= 0.02
+
+
+@pytest.mark.parametrize("rows,cols", [(33, 1024), (5, 77), (3, 20000)])
+def test_layernorm_rows_f32(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(cols)
+    x = rng.normal(0, 1, (rows, cols)).astype(np.float32)
+    g = rng.normal(1, 0.1, cols).astype(np.float32)
+    b = rng.normal(0, 0.1, cols).astype(np.float32)
+    want = oracle.layernorm_rows_f32(x, g, b, 1e-5)
+    got = T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5).cpu().numpy()
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+
+@pytest.mark.parametrize("cache", [0, 1])
+def test_layernorm_variants_agree(oracle, cuda, cache):
+    rng = np.random.default_rng(77)
+    x = oracle.f32_to_bf16(rng.normal(0, 1, (300, 8192)).astype(np.float32))
+    g = oracle.f32_to_bf16(rng.normal(1, 0.1, 8192).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.normal(0, 0.1, 8192).astype(np.float32))
+    try:
+        T.tune("layernorm", 0, 0, 0, cache)
+        got = host_bits(T.layernorm_rows(dev_bf16(x, cuda), dev_bf16(g, cuda), dev_bf16(b, cuda)))
+    finally:
+        T.tune("layernorm")
+    assert bf16_ulp_diff(got, oracle.layernorm_rows_bf16(x, g, b, 1e-5)).max() <= 1
+
+
+def test_layernorm_full_size_sampled_rows(oracle, cuda):
+    # the benchmark configuration: bf16 [65536, 8192]
+    gen = torch.Generator(device=cuda).manual_seed(7)
+    x = torch.randn((65536, 8192), generator=gen, device=cuda, dtype=torch.float32).to(torch.bfloat16)
+    g = (1 + 0.1 * torch.randn(8192, generator=gen, device=cuda)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(8192, generator=gen, device=cuda)).to(torch.bfloat16)
+    y = T.layernorm_rows(x, g, b, 1e-5)
+    idx = torch.tensor([0, 1, 32767, 40000, 65535], device=cuda)
+    want = oracle.layernorm_rows_bf16(host_bits(x[idx]), host_bits(g), host_bits(b), 1e-5)
+    assert bf16_ulp_diff(host_bits(y[idx]), want).max() <= 1
+    # with gamma = 1, beta = 0 every output row has mean ~0 and variance ~1
+    one, zero = torch.ones_like(g), torch.zeros_like(b)
+    y1 = T.layernorm_rows(x[:4096], one, zero, 1e-5).float()
+    assert y1.mean(1).abs().max().item() < 5e-3 and (y1.var(1, unbiased=False) - 1).abs().max().item() < 2e-2
+
+
+# ----------------------------------------------------------------------------
+# outer-axis reduce: sum / max / argmax
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("nb,nk,nc", [(4, 1024, 1024), (1, 1, 1), (3, 37, 50), (2, 5, 129), (5, 300, 4), (2, 1000, 260),
+                                      (1, 9, 2000)])
+def test_reduce_outer(oracle, cuda, nb, nk, nc):
+    rng = np.random.default_rng(nb * 1000 + nk + nc)
+    t = rng.uniform(-100, 100, (nb, nk, nc)).astype(np.float32)
+    s, m, a = oracle.reduce_outer(t)
+    bs, os_ = guarded((nb, nc), torch.float32, cuda)
+    bm, om = guarded((nb, nc), torch.float32, cuda)
+    oa_i = torch.full((nb, nc), -7, dtype=torch.int32, device=cuda)
+    T.reduce_outer(dev_f32(t, cuda), out={"sum": os_, "max": om, "argmax": oa_i})
+    check_guards(bs, torch.float32)
+    check_guards(bm, torch.float32)
+    assert np.array_equal(om.cpu().numpy(), m)            # bit-exact
+    assert np.array_equal(oa_i.cpu().numpy(), a)          # bit-exact, lowest index on ties
+    got = os_.cpu().numpy()
+    _, sabs = oracle.reduce_outer_sum_f64(t)
+    assert (np.abs(got - s) <= 1e-5 * sabs).all()          # per element against sum|x_i|
+    assert np.abs(got - s).max() <= 1e-5 * max(np.abs(s).max(), 1.0)  # normwise
+
+
+def test_reduce_outer_ties_and_subsets(oracle, cuda):
+    rng = np.random.default_rng(99)
+    t = rng.integers(-3, 4, (6, 200, 132)).astype(np.float32)  # many equal maxima
+    t[0, :, 0] = 2.0
+    t[1, 150:, 5] = 3.0
+    s, m, a = oracle.reduce_outer(t)
+    td = dev_f32(t, cuda)
+    r = T.reduce_outer(td)
+    assert np.array_equal(r["argmax"].cpu().numpy(), a) and np.array_equal(r["max"].cpu().numpy(), m)
+    assert np.array_equal(r["sum"].cpu().numpy(), s)  # small integers: every order gives the exact sum
+    only = T.reduce_outer(td, want=("argmax",))
+    assert set(only) == {"argmax"} and np.array_equal(only["argmax"].cpu().numpy(), a)
+    # NaN never wins a strict '>' comparison; an all-NaN column keeps (-inf, 0)
+    t2 = t.copy()
+    t2[2, 3, 7] = np.nan
+    t2[3, :, 9] = np.nan
+    s2, m2, a2 = oracle.reduce_outer(t2)
+    r2 = T.reduce_outer(dev_f32(t2, cuda), want=("max", "argmax"))
+    assert np.array_equal(r2["argmax"].cpu().numpy(), a2)
+    assert np.array_equal(r2["max"].cpu().numpy(), m2, equal_nan=True)
+    # empty reduction: the inits (design/tca.md:299)
+    e = T.reduce_outer(torch.zeros((2, 0, 8), device=cuda))
+    assert (e["sum"] == 0).all() and torch.isneginf(e["max"]).all() and (e["argmax"] == 0).all()
+
+
+@pytest.mark.parametrize("cv,kw", [(1, 8), (2, 8), (1, 16), (2, 16), (1, 4), (2, 4)])
+def test_reduce_outer_all_launch_shapes(oracle, cuda, cv, kw):
+    rng = np.random.default_rng(cv * 10 + kw)
+    t = rng.uniform(-100, 100, (3, 77, 392)).astype(np.float32)
+    s, m, a = oracle.reduce_outer(t)
+    try:
+        T.tune("reduce_outer", cv, kw)
+        r = T.reduce_outer(dev_f32(t, cuda))
+    finally:
+        T.tune("reduce_outer")
+    assert np.array_equal(r["argmax"].cpu().numpy(), a) and np.array_equal(r["max"].cpu().numpy(), m)
+    assert np.abs(r["sum"].cpu().numpy() - s).max() <= 1e-5 * np.abs(t).sum(1).max()
+
+
+def test_reduce_outer_full_size_properties(oracle, cuda):
+    # the benchmark configuration: fp32 [256, 1024, 1024] ~ U(-100, 100)
+    gen = torch.Generator(device=cuda).manual_seed(5)
+    t = torch.rand((256, 1024, 1024), generator=gen, device=cuda) * 200 - 100
+    r = T.reduce_outer(t)
+    # argmax indexes the max: gather(t, argmax) == max, bit for bit; and max >= every element
+    picked = torch.gather(t, 1, r["argmax"].long().unsqueeze(1)).squeeze(1)
+    assert torch.equal(picked, r["max"])
+    assert torch.equal(r["max"], t.amax(1))
+    # linearity of the sum: sum(2*t) == 2*sum(t) exactly (scaling by 2 is exact in fp32)
+    r2 = T.reduce_outer(t * 2, want=("sum",))
+    assert torch.equal(r2["sum"], r["sum"] * 2)
+    sl = t[:2].cpu().numpy()
+    s, m, a = oracle.reduce_outer(sl)
+    assert np.array_equal(r["argmax"][:2].cpu().numpy(), a)
+    assert (np.abs(r["sum"][:2].cpu().numpy() - s) <= 1e-5 * np.abs(sl).sum(1)).all()
+
+
+def test_chain_outer_generic(oracle, cuda):
+    rng = np.random.default_rng(31)
+    x = rng.normal(0, 2, (5, 61, 70)).astype(np.float32)
+    got = T.chain_reduce([dev_f32(x, cuda)], "p0", combine_expr="fmaxf(p0, p1)", init=-np.inf, axis=1).cpu().numpy()
+    assert np.array_equal(got, x.max(1))
+    got0 = T.chain_reduce([dev_f32(x, cuda)], "p0", axis=0).cpu().numpy()
+    assert np.abs(got0 - x.sum(0)).max() <= 1e-5 * np.abs(x).sum(0).max()
+
+
+# ----------------------------------------------------------------------------
+# errors reach the caller as status codes, never as a device fault
+# ----------------------------------------------------------------------------
+def test_errors_through_the_python_host(cuda):
+    x = torch.zeros((4, 8), device=cuda)
+    with pytest.raises(T.TcabError) as e:
+        T.softmax_rows(x, out=torch.zeros((4, 9), device=cuda))
+    assert e.value.status == T._lib.ERR_SHAPE
+    with pytest.raises(ValueError, match="contiguous"):
+        T.softmax_rows(x.t())
+    with pytest.raises(T.TcabError) as e:
+        T.chain_reduce([x], "sinf(cosf(p0))")
+    assert e.value.status == T._lib.ERR_UNSUPPORTED
+    n0 = T.launch_count()
+    T.softmax_rows(x)
+    assert T.launch_count() == n0 + 1

@@ -1,0 +1,66 @@
+"""The multi-rank host logic on CPU: world_size-2 gloo processes partition the
+independent axis, each 'computes' its block (here with the oracle standing in
+for a device), and the union equals the single-rank result. No data-path
+collective is involved; gloo only carries the check."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_blocks_cover_exactly_once():
+    from tcacomp_b200.shard import block, blocks
+    for n in (0, 1, 7, 8, 16384, 65537):
+        for w in (1, 2, 3, 4, 8):
+            bl = blocks(n, w)
+            assert bl[0][0] == 0 and bl[-1][1] == n
+            assert all(bl[i][1] == bl[i + 1][0] for i in range(w - 1))
+            sizes = [hi - lo for lo, hi in bl]
+            assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        block(4, 2, 2)
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import binding as O
+        from tcacomp_b200.shard import block
+        rng = np.random.default_rng(123)  # identical seeded input on every rank
+        x = (4 * rng.normal(0, 1, (101, 64))).astype(np.float32)
+        lo, hi = block(x.shape[0], world, rank)
+        mine = O.softmax_rows(np.ascontiguousarray(x[lo:hi]))
+        # gather only to verify; the timed path never exchanges data
+        parts = [None] * world
+        dist.all_gather_object(parts, (lo, hi, mine))
+        # max-over-ranks timing reduction, as the benchmark does it
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            full = np.concatenate([p[2] for p in sorted(parts, key=lambda p: p[0])])
+            q.put((np.array_equal(full, O.softmax_rows(x)), float(t.item())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_partition_matches_single_rank():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok, tmax = q.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert ok and tmax == 2.0
