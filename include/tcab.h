@@ -152,6 +152,13 @@ TCAB_API int tcab_layernorm_rows(const tcab_tensor* x, const tcab_tensor* gamma,
 TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias,
                        int act, const tcab_tensor* c, void* stream);
 
+/* Reads the device-side status word of the current device into *status (a synchronous copy):
+ * 0 = no kernel of this library has given up on a bounded wait since the library was loaded,
+ * non-zero = a contraction kernel abandoned a barrier wait and returned early (its output is then
+ * incomplete). The reference's device-side failure path is a device assert (runtime/tca/reducer.h:198-206);
+ * this library never traps: it reports here. */
+TCAB_API int tcab_device_status(int* status);
+
 /* Tuning hook, no counterpart in the reference: overrides the heuristic launch shape of one kernel
  * family ("softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm") for this process:
  * p0, p1 = the launch shape (threads per row and vectors per thread for the row kernels, vectors per lane and

@@ -56,6 +56,7 @@ SYMBOLS = [
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_float, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_gemm_bias_act", C.c_int,
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_int, C.POINTER(Tensor), C.c_void_p]),
+    ("tcab_device_status", C.c_int, [C.POINTER(C.c_int)]),
     ("tcab_tune", C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]),
 ]
 

@@ -181,6 +181,12 @@ int tcab_abi_version(void) { return TCAB_ABI_VERSION; }
 
 uint64_t tcab_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int tcab_device_status(int* status) {
+  if (status == nullptr) return fail(TCAB_ERR_INVALID_ARG, "device_status: null output");
+  TCAB_TRY(have_device("device_status"));
+  return gemm_device_status(status);
+}
+
 int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {
   static const char* names[kFamilies] = {"softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm"};
   if (family == nullptr) return fail(TCAB_ERR_INVALID_ARG, "tune: null family");

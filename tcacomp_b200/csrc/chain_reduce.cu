@@ -101,7 +101,8 @@ int launch_chain(const Args& a) {
   if (a.inner == 1) {
     const bool vec = al && (a.nk % 4 == 0);
     const uint32_t nvec = vec ? a.nk / 4 : a.nk;
-    int tpr = nvec <= 8 ? 1 : nvec <= 64 ? 4 : nvec <= 2048 ? 32 : 256;
+    // short rows: one thread folds a row sequentially, which is the reference's SeqReducer order exactly
+    int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec <= 2048 ? 32 : 256;
     const Tune& tn = tune(kReduceInner);
     if (tn.p0 == 1 || tn.p0 == 4 || tn.p0 == 32 || tn.p0 == 256) tpr = tn.p0;
     if (vec) {

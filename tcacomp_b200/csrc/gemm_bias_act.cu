@@ -1,8 +1,307 @@
-// gemm_bias_act.cu -- placeholder until the tcgen05 contraction lands.
+// gemm_bias_act.cu -- tiled bf16 contraction with a fused epilogue on the 5th-generation
+// tensor cores: c = act(a @ b + bias), fp32 accumulation in TMEM, bf16 result.
+//
+// The reference emits a GEMM that produces ONE output element per CTA bracket with a
+// K split over warps and scalar FMAs (the suite's testing/kernels/llm/gemm.tca, runner
+// testing/runners/gemm.cu:44-56) and cannot bind the bias operand of the piped map
+// (design/RELEASE-v0.0.0.md:150). Here:
+//
+//   * a persistent CTA per SM walks 256x256 output tiles; K is cut into 64-wide blocks;
+//   * warp 0 (one lane) is the TMA producer: per K block it loads a 256x64 slab of A
+//     (K-major, rows of 128 bytes) and four 64x64 boxes of B (b is [K,N] row-major, i.e.
+//     N-major: each box is 64 k-rows of 64 contiguous n) into a 3-stage shared-memory ring,
+//     all with the 128-byte swizzle the tensor core expects;
+//   * warp 1 (one lane) issues tcgen05.mma (M=128, N=256, K=16) into two TMEM accumulators
+//     (rows 0-127 and 128-255 of the tile, 256 fp32 columns each = all 512 TMEM columns),
+//     frees a ring stage with tcgen05.commit, and signals the epilogue per tile;
+//   * warps 2-9 are the epilogue: tcgen05.ld 32 lanes x 32 columns at a time, add bias,
+//     ReLU, round to bf16, 16-byte stores. Each accumulator is handed back to the MMA warp
+//     as soon as it is drained, so the next tile's first K blocks overlap the second drain.
+//
+// Per K block a CTA moves 64 KB into shared memory for 8.4 MFLOP (131 flop per byte), which
+// is what lets one CTA per SM run without cluster multicast. Every wait is bounded (see
+// sm100_ptx.cuh); a wait that gives up makes the kernel write a status word and return.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+#include "sm100_ptx.cuh"
+
 namespace tcab {
-int launch_gemm_bias_act(const __nv_bfloat16*, const __nv_bfloat16*, const float*, int, __nv_bfloat16*, uint32_t,
-                         uint32_t, uint32_t, cudaStream_t) {
-  return fail(TCAB_ERR_UNSUPPORTED, "gemm_bias_act: not built yet");
+namespace {
+
+constexpr int BM = 256, BN = 256, BK = 64;
+constexpr int UMMA_M = 128, UMMA_N = 256, UMMA_K = 16;
+constexpr int STAGES = 3;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 32 KB: 256 rows x 128 B
+constexpr int B_STAGE_BYTES = BK * BN * 2;  // 32 KB: 4 atoms x (64 k-rows x 128 B)
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int B_ATOM_BYTES = BK * 128;      // one 64(n) x 64(k) box
+constexpr int EPI_WARPS = 8;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int TMEM_COLS = 512;
+constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;  // + alignment slack
+
+// Device status of the last contraction kernel that gave up on a wait (0 = none).
+__device__ int g_gemm_status = 0;
+
+struct TileCoord {
+  uint32_t m, n;
+};
+// Tiles are walked in bands of 8 tile-rows so that the CTAs running at the same time share
+// A slabs and B slabs in L2.
+__device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, uint32_t tiles_n) {
+  const uint32_t band = 8 * tiles_n;
+  const uint32_t first_m = (t / band) * 8;
+  const uint32_t rows = min(8u, tiles_m - first_m);
+  const uint32_t r = t % band;
+  return {first_m + r % rows, r / rows};
 }
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const float* __restrict__ bias, __nv_bfloat16* __restrict__ c, uint32_t M, uint32_t N,
+                     uint32_t K, int act) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[STAGES];
+  __shared__ __align__(8) uint64_t bar_tmem_full;
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;  // the swizzle needs 1024-byte tiles
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_p = &abort_flag;
+
+  const uint32_t tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const uint32_t num_tiles = tiles_m * tiles_n;
+  const uint32_t num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[0]), EPI_WARPS);
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[1]), EPI_WARPS);
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, abort_p)) { ok = false; break; }
+          const uint32_t full = ptx::smem_u32(&bar_full[stage]);
+          const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          ptx::mbar_expect_tx(full, STAGE_BYTES);
+          ptx::tma_load_2d(a_dst, &tmap_a, full, static_cast<int32_t>(kb * BK), static_cast<int32_t>(tc.m * BM));
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j)
+            ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, static_cast<int32_t>(tc.n * BN + j * 64),
+                             static_cast<int32_t>(kb * BK));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      uint32_t stage = 0, phase = 0, tile_iter = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
+        for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_src = smem_base + stage * STAGE_BYTES;
+          const uint32_t b_src = a_src + A_STAGE_BYTES;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            if (kb == 0) {  // the epilogue must have drained this accumulator (previous tile)
+              if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[a]), (tile_iter & 1u) ^ 1u, abort_p)) { ok = false; break; }
+              ptx::tc_fence_after();
+            }
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // A: K-major, 8-row groups 1024 B apart; one UMMA_K step is 32 B inside the 128-B swizzle row.
+              const uint64_t adesc = ptx::smem_desc_sw128(a_src + a * (UMMA_M * 128) + k * (UMMA_K * 2), 16, 1024);
+              // B: N-major, 64-wide n atoms B_ATOM_BYTES apart, 8-k-row groups 1024 B apart; one step is 16 k-rows.
+              const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+              ptx::mma_bf16(tmem_base + a * UMMA_N, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
+            }
+          }
+          if (!ok) break;
+          ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::mma_commit(ptx::smem_u32(&bar_tmem_full));  // both accumulators complete
+      }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int e = warp - 2;
+    const uint32_t quad = static_cast<uint32_t>(warp) & 3u;  // TMEM lanes a warp may read: 32 * (warp % 4)
+    const uint32_t half = static_cast<uint32_t>(e) >> 2;     // which 128 of the 256 columns
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      if (num_kb > 0) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) { ok = false; break; }
+        ptx::tc_fence_after();
+      }
+#pragma unroll 1
+      for (uint32_t a = 0; a < 2; ++a) {
+        const uint32_t row = tc.m * BM + a * UMMA_M + quad * 32 + lane;
+#pragma unroll 1
+        for (uint32_t ch = 0; ch < 4; ++ch) {
+          const uint32_t col = tc.n * BN + half * 128 + ch * 32;
+          uint32_t r[32];
+          if (num_kb > 0) {
+            ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + ch * 32, r);
+            ptx::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty reduction: the accumulator's init
+          }
+          if (row < M && col < N) {
+            __nv_bfloat16* dst = c + static_cast<size_t>(row) * N + col;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < N) {  // N % 8 == 0: 8-column groups are whole
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float f0 = __uint_as_float(r[v * 8 + 2 * j]), f1 = __uint_as_float(r[v * 8 + 2 * j + 1]);
+                  if (bias != nullptr) {
+                    f0 += __ldg(bias + col + v * 8 + 2 * j);
+                    f1 += __ldg(bias + col + v * 8 + 2 * j + 1);
+                  }
+                  if (act == TCAB_ACT_RELU) {
+                    f0 = fmaxf(f0, 0.0f);
+                    f1 = fmaxf(f1, 0.0f);
+                  }
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
+                  w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+          }
+        }
+        // this accumulator is drained: hand it back to the MMA warp
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[a]));
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = 1;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not
+// link libcuda, so it still loads (and reports TCAB_ERR_CUDA) on a box without a driver.
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// A 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of box_rows x 64 columns.
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return fail(TCAB_ERR_CUDA, "gemm_bias_act: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TCAB_ERR_CUDA, "gemm_bias_act: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return TCAB_OK;
+}
+
+}  // namespace
+
+int gemm_device_status(int* out) {
+  if (cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "device_status: cannot read the status word");
+  }
+  return TCAB_OK;
+}
+
+int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias, int act,
+                         __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
+  if (m == 0 || n == 0) return TCAB_OK;
+  CUtensorMap ta, tb;
+  if (k > 0) {
+    int rc = make_map(&ta, a, m, k, BM);
+    if (rc != TCAB_OK) return rc;
+    rc = make_map(&tb, b, k, n, BK);
+    if (rc != TCAB_OK) return rc;
+  } else {
+    // no K blocks: the kernel never touches the maps; encode them over c to keep them valid
+    int rc = make_map(&ta, c, m, n, BM);
+    if (rc != TCAB_OK) return rc;
+    tb = ta;
+  }
+  // per launch, like the reference's launcher does above 48 KB (internal/cg/cxx/launch.go:145-155):
+  // the attribute belongs to the current device's copy of the function
+  const cudaError_t attr_err = cudaFuncSetAttribute(gemm_bias_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    static_cast<int>(SMEM_BYTES));
+  if (attr_err != cudaSuccess)
+    return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
+                cudaGetErrorString(attr_err));
+  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const Tune& tn = tune(kGemm);
+  uint64_t grid = tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count());
+  if (grid > tiles) grid = tiles;
+  gemm_bias_act_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, bias, c, m, n, k, act);
+  count_launch();
+  return check_launch("gemm_bias_act_kernel");
+}
+
 }  // namespace tcab

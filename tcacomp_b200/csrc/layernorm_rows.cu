@@ -76,7 +76,7 @@ layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < V; ++j) s += v[i][j];
-    s = group_allreduce<OpSum, TPR>(s, slots[0]);
+    s = group_allreduce<OpSum, TPR>(s, slots[0], g);
     const float mean = s / n;
 
     float q = 0.0f;
@@ -91,7 +91,7 @@ layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T
         }
       }
     }
-    q = group_allreduce<OpSum, TPR>(q, slots[1]);
+    q = group_allreduce<OpSum, TPR>(q, slots[1], g);
     const float rstd = 1.0f / sqrtf(q / n + eps);
 
 #pragma unroll

@@ -89,14 +89,24 @@ struct VecIO<__nv_bfloat16, 1> {
   static __device__ __forceinline__ Raw pack(const float* f) { return __float2bfloat16_rn(f[0]); }
 };
 
-// Reduction across the TPR threads of a row group; every thread gets the result.
-// TPR <= 32: shuffles only. TPR > 32: the group is the whole CTA.
+// Reduction across the TPR threads of row group `g` of the CTA; every thread of the group gets
+// the result. TPR <= 32: shuffles only. TPR > 32: the group's TPR/32 warps meet in `slots`
+// (one float per warp of the CTA) behind ONE CTA-wide barrier, so every group of the CTA must
+// call this the same number of times; the caller alternates between two slot arrays so that a
+// slot is never rewritten before every thread has read it.
 template <typename Op, int TPR>
-__device__ __forceinline__ float group_allreduce(float v, float* slots) {
+__device__ __forceinline__ float group_allreduce(float v, float* slots, int g) {
   if constexpr (TPR <= 32) {
     return warp_allreduce<Op, TPR>(v);
   } else {
-    return cta_allreduce<Op, TPR / 32>(v, slots);
+    constexpr int NW = TPR / 32;
+    static_assert((NW & (NW - 1)) == 0 && NW <= 32, "a row group is a power-of-two number of warps");
+    const int lane = threadIdx.x & 31, wg = (threadIdx.x % TPR) >> 5;
+    v = warp_allreduce<Op>(v);
+    if (lane == 0) slots[g * NW + wg] = v;
+    __syncthreads();
+    // every aligned group of NW lanes holds all the partials of the row group
+    return warp_allreduce<Op, NW>(slots[g * NW + (lane & (NW - 1))]);
   }
 }
 

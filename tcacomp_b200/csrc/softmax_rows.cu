@@ -58,7 +58,7 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
-    m = group_allreduce<OpMax, TPR>(m, slots[0]);
+    m = group_allreduce<OpMax, TPR>(m, slots[0], g);
 
     float s = 0.0f;
 #pragma unroll
@@ -68,7 +68,7 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
         v[i][j] = expf(v[i][j] - m);
         s += v[i][j];
       }
-    s = group_allreduce<OpSum, TPR>(s, slots[1]);
+    s = group_allreduce<OpSum, TPR>(s, slots[1], g);
     const float inv = 1.0f / s;
 
 #pragma unroll

@@ -51,6 +51,13 @@ def launch_count() -> int:
     return int(_lib.load().tcab_launch_count())
 
 
+def device_status() -> int:
+    """0 unless a kernel gave up on a bounded device-side wait (synchronises the device)."""
+    v = C.c_int(0)
+    _lib.check(_lib.load().tcab_device_status(C.byref(v)))
+    return int(v.value)
+
+
 def tune(family: str, p0: int = 0, p1: int = 0, p2: int = 0, p3: int = 0) -> None:
     """Override (or with zeros, restore) the launch shape of one kernel family."""
     _lib.check(_lib.load().tcab_tune(family.encode(), p0, p1, p2, p3))

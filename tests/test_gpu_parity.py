@@ -4,9 +4,15 @@ Tolerances, as stated for this path:
   * integer / index outputs (argmax) and max: bit-exact;
   * fp32 reductions: |gpu - oracle| <= 1e-5 relative, with the denominators
     written at each test (normwise max|ref|, and per element sum|x_i| where the
-    sum cancels);
-  * softmax / layer-norm outputs (a map after reductions): 1e-5 relative for
-    fp32, one bf16 ulp for bf16 outputs.
+    sum cancels). The oracle folds sequentially in fp32, as the reference's
+    loops do, and for long rows that fold is itself further than 1e-5 from the
+    exact value (measured: 1.5e-5 at 4096 terms, 1.8e-5 at 70001) while the
+    kernel's tree is within 3e-6. Where that matters the bound is
+        |gpu - oracle| <= 1e-5*|oracle| + |oracle - fp64|   and   |gpu - fp64| <= 1e-5*|fp64|,
+    fp64 being the same formula evaluated in double precision on the same inputs;
+  * softmax / layer-norm outputs (a map after reductions): the same bound for
+    fp32; for bf16 outputs one bf16 ulp of the value plus the fp32 error of the
+    terms that cancel in x_hat*gamma + beta.
 Every output buffer is prefilled with a canary and padded with guard bands, the
 reference's own way of proving that every element was written and nothing else
 (internal/e2e/harness.go:158-181, testing/runners/common.cuh).
@@ -67,8 +73,8 @@ def test_map_rowsum(oracle, cuda, rows, cols):
     got = out.cpu().numpy()
     check_guards(buf, torch.float32)
     assert (got != CANARY).all()
-    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
-    assert (np.abs(got - want) <= 1e-5 * np.abs(want)).all()  # all terms positive: per element too
+    from oracle import checks
+    assert checks.rowsum_close(got, x)
 
 
 def test_map_rowsum_unaligned_and_captures(oracle, cuda):
@@ -153,6 +159,11 @@ def test_e2e_row_sum_fixture(oracle, cuda):
 # ----------------------------------------------------------------------------
 # row softmax
 # ----------------------------------------------------------------------------
+def assert_softmax_close(got, want, x):
+    from oracle import checks
+    assert checks.softmax_close(got, x, want)
+
+
 @pytest.mark.parametrize("rows,cols", [(64, 4096), (1, 1), (3, 7), (33, 517), (130, 32), (7, 1000), (5, 12288),
                                        (3, 40000), (2, 140004), (2, 140001)])
 def test_softmax_rows(oracle, cuda, rows, cols):
@@ -163,8 +174,7 @@ def test_softmax_rows(oracle, cuda, rows, cols):
     T.softmax_rows(dev_f32(x, cuda), out=out)
     got = out.cpu().numpy()
     check_guards(buf, torch.float32)
-    # a map after fp32 reductions: 1e-5 relative per element (plus a floor at the smallest normal)
-    assert (np.abs(got - want) <= 1e-5 * np.abs(want) + 1e-37).all()
+    assert_softmax_close(got, want, x)
     assert np.abs(got.astype(np.float64).sum(1) - 1.0).max() <= 1e-5
 
 
@@ -175,7 +185,7 @@ def test_softmax_unaligned_view(oracle, cuda):
     xd = base[3:].view(9, 256)
     xd.copy_(dev_f32(x, cuda))
     got = T.softmax_rows(xd).cpu().numpy()
-    assert (np.abs(got - oracle.softmax_rows(x)) <= 1e-5 * oracle.softmax_rows(x) + 1e-37).all()
+    assert_softmax_close(got, oracle.softmax_rows(x), x)
 
 
 def test_softmax_extremes(oracle, cuda):
@@ -200,19 +210,16 @@ def test_softmax_full_size_properties_and_sampled_rows(oracle, cuda):
     # the largest input of a row receives the largest output
     assert (y >= 0).all() and torch.equal(y.gather(1, x.argmax(1, keepdim=True)).squeeze(1), y.amax(1))
     idx = torch.tensor([0, 1, 4097, 9999, 16383], device=cuda)
-    want = oracle.softmax_rows(x[idx].cpu().numpy())
-    got = y[idx].cpu().numpy()
-    assert (np.abs(got - want) <= 1e-5 * want + 1e-37).all()
+    xs = x[idx].cpu().numpy()
+    assert_softmax_close(y[idx].cpu().numpy(), oracle.softmax_rows(xs), xs)
 
 
 # ----------------------------------------------------------------------------
 # layer-norm
 # ----------------------------------------------------------------------------
-def bf16_ulp_diff(a_bits, b_bits):
-    def key(u):
-        u = u.astype(np.int32)
-        return np.where(u & 0x8000, 0x8000 - u, u)
-    return np.abs(key(a_bits) - key(b_bits))
+def assert_layernorm_bf16_close(oracle, got_bits, want_bits, x_bits, g_bits, b_bits, eps=1e-5):
+    from oracle import checks
+    assert checks.layernorm_bf16_close(got_bits, x_bits, g_bits, b_bits, eps, want_bits)
 
 
 @pytest.mark.parametrize("rows,cols", [(64, 8192), (1, 1), (3, 7), (17, 264), (130, 64), (9, 1000), (4, 16384),
@@ -227,11 +234,7 @@ def test_layernorm_rows_bf16(oracle, cuda, rows, cols):
     T.layernorm_rows(dev_bf16(x, cuda), dev_bf16(g, cuda), dev_bf16(b, cuda), 1e-5, out=out)
     got = host_bits(out)
     check_guards(buf, torch.bfloat16)
-    d = bf16_ulp_diff(got, want)
-    # the fp32 statistics differ in the last bits (tree vs sequential fold), which can move a value
-    # across a bf16 rounding boundary: at most one bf16 ulp, and only rarely
-    assert d.max() <= 1
-    assert (d != 0).mean() <= 0.02
+    assert_layernorm_bf16_close(oracle, got, want, x, g, b)
 
 
 @pytest.mark.parametrize("rows,cols", [(33, 1024), (5, 77), (3, 20000)])
@@ -256,7 +259,7 @@ def test_layernorm_variants_agree(oracle, cuda, cache):
         got = host_bits(T.layernorm_rows(dev_bf16(x, cuda), dev_bf16(g, cuda), dev_bf16(b, cuda)))
     finally:
         T.tune("layernorm")
-    assert bf16_ulp_diff(got, oracle.layernorm_rows_bf16(x, g, b, 1e-5)).max() <= 1
+    assert_layernorm_bf16_close(oracle, got, oracle.layernorm_rows_bf16(x, g, b, 1e-5), x, g, b)
 
 
 def test_layernorm_full_size_sampled_rows(oracle, cuda):
@@ -267,8 +270,8 @@ def test_layernorm_full_size_sampled_rows(oracle, cuda):
     b = (0.1 * torch.randn(8192, generator=gen, device=cuda)).to(torch.bfloat16)
     y = T.layernorm_rows(x, g, b, 1e-5)
     idx = torch.tensor([0, 1, 32767, 40000, 65535], device=cuda)
-    want = oracle.layernorm_rows_bf16(host_bits(x[idx]), host_bits(g), host_bits(b), 1e-5)
-    assert bf16_ulp_diff(host_bits(y[idx]), want).max() <= 1
+    xs, gs, bs = host_bits(x[idx]), host_bits(g), host_bits(b)
+    assert_layernorm_bf16_close(oracle, host_bits(y[idx]), oracle.layernorm_rows_bf16(xs, gs, bs, 1e-5), xs, gs, bs)
     # with gamma = 1, beta = 0 every output row has mean ~0 and variance ~1
     one, zero = torch.ones_like(g), torch.zeros_like(b)
     y1 = T.layernorm_rows(x[:4096], one, zero, 1e-5).float()
@@ -380,3 +383,79 @@ def test_errors_through_the_python_host(cuda):
     n0 = T.launch_count()
     T.softmax_rows(x)
     assert T.launch_count() == n0 + 1
+
+
+# ----------------------------------------------------------------------------
+# contraction with fused bias + ReLU (bf16 in, fp32 accumulate, bf16 out)
+# ----------------------------------------------------------------------------
+def gemm_inputs(oracle, m, k, n, seed):
+    rng = np.random.default_rng(seed)
+    sc = 1.0 / np.sqrt(max(k, 1))
+    a = oracle.f32_to_bf16((rng.normal(0, 1, (m, k)) * sc).astype(np.float32))
+    b = oracle.f32_to_bf16((rng.normal(0, 1, (k, n)) * sc).astype(np.float32))
+    bias = rng.normal(0, 0.02, n).astype(np.float32)
+    return a, b, bias
+
+
+def rel_frobenius(got, want):
+    return np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)
+
+
+@pytest.mark.parametrize("m,k,n", [(256, 64, 256), (128, 128, 64), (256, 512, 256), (300, 200, 520), (1, 8, 8),
+                                   (513, 1032, 264), (1024, 2048, 1536)])
+@pytest.mark.parametrize("act", ["relu", "none"])
+def test_gemm_bias_act(oracle, cuda, m, k, n, act):
+    a, b, bias = gemm_inputs(oracle, m, k, n, m * 7 + k * 3 + n)
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, act))
+    buf, out = guarded((m, n), torch.bfloat16, cuda)
+    T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), act, out=out)
+    got = out.float().cpu().numpy()
+    check_guards(buf, torch.bfloat16)
+    assert T.device_status() == 0
+    assert (got != torch.tensor(CANARY).to(torch.bfloat16).float().item()).all()
+    assert rel_frobenius(got, want) <= 1e-3  # bf16-in / fp32-accumulate contraction: relative Frobenius error
+    # element-wise: one bf16 ulp of the value plus the fp32 accumulation error of k products
+    assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
+
+
+def test_gemm_without_bias_and_empty_k(oracle, cuda):
+    a, b, bias = gemm_inputs(oracle, 256, 128, 256, 5)
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
+    got = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), None, "none").float().cpu().numpy()
+    assert rel_frobenius(got, want) <= 1e-3
+    # K = 0: an empty reduction returns init = 0, so c = act(bias) (design/tca.md:299)
+    a0 = torch.zeros((64, 0), device=cuda, dtype=torch.bfloat16)
+    b0 = torch.zeros((0, 64), device=cuda, dtype=torch.bfloat16)
+    c0 = T.gemm_bias_act(a0, b0, dev_f32(bias[:64], cuda), "relu").float().cpu().numpy()
+    want0 = oracle.bf16_to_f32(oracle.f32_to_bf16(np.maximum(bias[:64], 0)))
+    assert np.array_equal(c0, np.broadcast_to(want0, (64, 64)))
+
+
+def test_gemm_exact_on_small_integers(oracle, cuda):
+    # products and sums of small integers are exact in bf16/fp32: every accumulation order agrees bit for bit
+    rng = np.random.default_rng(3)
+    m, k, n = 512, 256, 512
+    a = oracle.f32_to_bf16(rng.integers(-2, 3, (m, k)).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.integers(-2, 3, (k, n)).astype(np.float32))
+    bias = rng.integers(-4, 5, n).astype(np.float32)
+    want = oracle.gemm_bias_act_bf16(a, b, bias, "relu")
+    got = host_bits(T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu"))
+    assert np.array_equal(got, want)
+
+
+def test_gemm_full_size_sampled_rows_and_linearity(oracle, cuda):
+    # the benchmark configuration: 8192^3, a,b ~ N(0,1)/sqrt(8192), bias ~ N(0,0.02)
+    gen = torch.Generator(device=cuda).manual_seed(11)
+    sc = 1.0 / np.sqrt(8192)
+    a = (torch.randn((8192, 8192), generator=gen, device=cuda) * sc).to(torch.bfloat16)
+    b = (torch.randn((8192, 8192), generator=gen, device=cuda) * sc).to(torch.bfloat16)
+    bias = torch.randn((8192,), generator=gen, device=cuda) * 0.02
+    c = T.gemm_bias_act(a, b, bias, "relu")
+    assert T.device_status() == 0
+    rows = torch.tensor([0, 1, 255, 256, 4095, 4096, 8191], device=cuda)
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(host_bits(a[rows]), host_bits(b), bias.cpu().numpy(), "relu"))
+    assert rel_frobenius(c[rows].float().cpu().numpy(), want) <= 1e-3
+    # linearity without the epilogue: (2a) @ b == 2 (a @ b) exactly (scaling by 2 is exact in bf16 and fp32)
+    c1 = T.gemm_bias_act(a, b, None, "none")
+    c2 = T.gemm_bias_act(a * 2, b, None, "none")
+    assert torch.equal(c2.float(), c1.float() * 2)
