@@ -499,7 +499,7 @@ def run_ours(args) -> dict:
     # keep the GPU under the same load for a moment before timing, so that the clocks have settled
     # and the sampler sees them under load even when the timed region lasts a few milliseconds
     t_load0 = time.perf_counter()
-    while time.perf_counter() - t_load0 < 0.3:
+    while time.perf_counter() - t_load0 < args.preload_ms * 1e-3:
         for _ in range(8):
             wl.step()
         torch.cuda.synchronize()
@@ -629,6 +629,8 @@ def main(argv=None) -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT)
     ap.add_argument("--no-others", action="store_true", help="skip the kernel-only lines of the other workloads")
+    ap.add_argument("--preload-ms", type=float, default=300.0,
+                    help="untimed load before the timed region so that the clocks settle (0 for profiler runs)")
     args = ap.parse_args(argv)
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3  # timing hygiene: at least three untimed steps

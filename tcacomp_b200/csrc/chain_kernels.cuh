@@ -104,7 +104,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
     const u64 vbase = row * nvec;  // first vector of the row (nk % V == 0)
     float acc = C::identity();
     if (live) {
-#pragma unroll 4
+#pragma unroll 8
       for (u32 idx = t; idx < nvec; idx += TPR) {
         float f[NIN][V];
 #pragma unroll

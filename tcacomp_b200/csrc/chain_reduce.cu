@@ -62,11 +62,9 @@ int launch_inner(const Args& a) {
   auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
-  int occ = occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
-  if (occ < 1) occ = 1;
+  // one CTA per group of rows; the kernel's row loop only matters beyond 2^31 - 1 CTAs
   const uint64_t need = (a.outer + GROUPS - 1) / GROUPS;
-  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
-  if (grid > need) grid = need;
+  const uint64_t grid = need > 0x7fffffffull ? 0x7fffffffull : need;
   fn<<<static_cast<unsigned>(grid), THREADS, 0, a.stream>>>(ptrs, a.out, a.outer, a.nk, a.init, a.caps);
   count_launch();
   return check_launch("chain_inner");
@@ -83,10 +81,7 @@ int launch_outer(const Args& a) {
   const uint32_t tiles_per_b = (nc + 32 * V - 1) / (32 * V);
   const uint64_t tiles = a.outer * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
-  int occ = occupancy(reinterpret_cast<const void*>(fn), 32 * KW, 0);
-  if (occ < 1) occ = 1;
-  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
-  if (grid > tiles) grid = tiles;
+  const uint64_t grid = tiles > 0x7fffffffull ? 0x7fffffffull : tiles;  // one CTA per tile
   fn<<<static_cast<unsigned>(grid), 32 * KW, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,
                                                           tiles_per_b, a.init, a.caps);
   count_launch();

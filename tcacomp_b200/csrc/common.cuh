@@ -76,12 +76,54 @@ int gemm_device_status(int* out);  // status word of the contraction kernel (syn
 
 constexpr unsigned kFullMask = 0xffffffffu;
 
-// 128-bit loads/stores for data that is touched once: evict-first in L1/L2.
-__device__ __forceinline__ float4 ld_stream(const float4* p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(float4* p, float4 v) { __stcs(p, v); }
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
-__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+// 128-bit loads/stores for data that is touched once. The cache policy is a build-time
+// choice (TCAB_LD_POLICY / TCAB_ST_POLICY: 0 = evict-first "streaming", 1 = default,
+// 2 = loads through the non-coherent path without L1 allocation).
+#ifndef TCAB_LD_POLICY
+#define TCAB_LD_POLICY 0
+#endif
+#ifndef TCAB_ST_POLICY
+#define TCAB_ST_POLICY 0
+#endif
+__device__ __forceinline__ float4 ld_stream(const float4* p) {
+#if TCAB_LD_POLICY == 0
+  return __ldcs(p);
+#elif TCAB_LD_POLICY == 1
+  return *p;
+#else
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+#endif
+}
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+#if TCAB_LD_POLICY == 0
+  return __ldcs(p);
+#elif TCAB_LD_POLICY == 1
+  return *p;
+#else
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+#endif
+}
 __device__ __forceinline__ float ld_stream(const float* p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4* p, float4 v) {
+#if TCAB_ST_POLICY == 0
+  __stcs(p, v);
+#else
+  *p = v;
+#endif
+}
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) {
+#if TCAB_ST_POLICY == 0
+  __stcs(p, v);
+#else
+  *p = v;
+#endif
+}
 __device__ __forceinline__ void st_stream(float* p, float v) { __stcs(p, v); }
 
 struct OpSum {

@@ -10,8 +10,7 @@
 // load and rounded to nearest even on store (design/syntax-design.md:601-607).
 //
 // The row lives in registers, so x is read once and y written once (4 bytes per
-// bf16 element, 8 per fp32 element: the roofline figure). The CTAs are
-// persistent. gamma and beta are either re-read per row through the read-only
+// bf16 element, 8 per fp32 element: the roofline figure). gamma and beta are either re-read per row through the read-only
 // L1 path (they total a few KB and stay L1-resident; the row itself streams past
 // L1), or, with CACHE_GB, kept in registers as raw 16-byte vectors across all the
 // rows a thread processes. The first costs load-store issue slots, the second
@@ -162,11 +161,12 @@ int launch_reg2(const T* x, const T* gamma, const T* beta, float eps, T* y, uint
   constexpr int THREADS = row_cta_threads(TPR);
   constexpr int GROUPS = THREADS / TPR;
   auto* fn = layernorm_rows_reg<T, TPR, VPT, V, CACHE_GB>;
-  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
-  if (occ < 1) occ = 1;
+  // One CTA per group of rows (see softmax_rows.cu: the hardware block scheduler staggers the CTAs,
+  // a persistent grid runs them in lock step); a positive ctas_per_sm caps the grid.
   const uint64_t need = (rows + GROUPS - 1) / GROUPS;
-  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  uint64_t grid = ctas_per_sm > 0 ? static_cast<uint64_t>(sm_count()) * ctas_per_sm : need;
   if (grid > need) grid = need;
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
   fn<<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, gamma, beta, eps, y, rows, cols);
   count_launch();
   return check_launch("layernorm_rows_reg");

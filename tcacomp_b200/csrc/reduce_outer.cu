@@ -149,10 +149,10 @@ int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, ui
   }
   const uint32_t tiles_per_b = (nc + TILE_C - 1) / TILE_C;
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
-  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, smem);
-  if (occ < 1) occ = 1;
-  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  // one CTA per tile unless the tuning hook caps the grid (the tile loop then takes over)
+  uint64_t grid = ctas_per_sm > 0 ? static_cast<uint64_t>(sm_count()) * ctas_per_sm : tiles;
   if (grid > tiles) grid = tiles;
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
   fn<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b);
   count_launch();
   return check_launch("reduce_outer_kernel");

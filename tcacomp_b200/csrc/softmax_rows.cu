@@ -8,7 +8,7 @@
 // two barriers PER ELEMENT (runtime/tca/reducer.h:109-167).
 //
 // Two kernels:
-//   softmax_rows_reg     the row lives in registers: x is read from HBM once and
+//   softmax_rows_reg     the row lives in registers (4 vectors of 4 fp32 per thread): x is read from HBM once and
 //                        y written once (8 bytes per element, the roofline figure);
 //                        one shuffle/shared-memory tree per reduction per ROW.
 //   softmax_rows_online  rows too long for registers: a single streaming pass
@@ -131,24 +131,25 @@ int launch_reg(const float* x, float* y, uint64_t rows, uint32_t cols, int ctas_
   constexpr int THREADS = row_cta_threads(TPR);
   constexpr int GROUPS = THREADS / TPR;
   auto* fn = softmax_rows_reg<TPR, VPT, V>;
-  int occ = ctas_per_sm > 0 ? ctas_per_sm : occupancy(reinterpret_cast<const void*>(fn), THREADS, 0);
-  if (occ < 1) occ = 1;
+  // One CTA per group of rows, left to the hardware block scheduler: measured on B200 this beats a
+  // persistent grid-stride grid (6.6 vs 5.7 TB/s at 16384 x 4096), whose CTAs move through their
+  // load / reduce / store phases in lock step. A positive ctas_per_sm (tuning hook) caps the grid;
+  // the kernel's row loop then takes over.
   const uint64_t need = (rows + GROUPS - 1) / GROUPS;
-  uint64_t grid = static_cast<uint64_t>(sm_count()) * occ;
+  uint64_t grid = ctas_per_sm > 0 ? static_cast<uint64_t>(sm_count()) * ctas_per_sm : need;
   if (grid > need) grid = need;
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
   fn<<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, y, rows, cols);
   count_launch();
   return check_launch("softmax_rows_reg");
 }
 
-// The (TPR, VPT) shapes choose_row_shape(nvec, 8) can return, plus the other
-// covers of a 1024-vector row that the tuning hook may select.
+// The (TPR, VPT) shapes choose_row_shape(nvec, 4) can return, plus other covers of a
+// 1024-vector row that the tuning hook may select.
 #define TCAB_ROW_SHAPES_BASE(X) \
-  X(8, 1) X(8, 2) X(8, 4) X(8, 8) X(16, 8) X(32, 8) X(64, 8) X(128, 8) X(256, 8) X(512, 8) \
+  X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
   X(1024, 8) X(1024, 16) X(1024, 32)
-#define TCAB_ROW_SHAPES_EXTRA(X) \
-  X(32, 16) X(32, 32) X(64, 16) X(128, 4) X(256, 4) X(256, 2) X(512, 2) X(512, 4) X(1024, 1) \
-  X(1024, 2) X(1024, 4) X(64, 4) X(128, 2) X(128, 16) X(256, 16)
+#define TCAB_ROW_SHAPES_EXTRA(X) X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(256, 8) X(1024, 1)
 
 }  // namespace
 
@@ -158,7 +159,7 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   const uint32_t nvec = vec ? cols / 4 : cols;
   const Tune& tn = tune(kSoftmax);
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape(nvec, 8, &tpr, &vpt);
+  bool fits = choose_row_shape(nvec, 4, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;
