@@ -40,13 +40,13 @@ import torch  # noqa: E402
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's kernel, from the ncu
-# captures summarised under profiles/ (None until a capture exists).
+# captures summarised under profiles/ (mean of the two captured launches).
 NCU_TRAFFIC_BYTES = {
-    "softmax_rows_f32_16384x4096": None,
-    "layernorm_rows_bf16_65536x8192": None,
-    "reduce_outer_f32_256x1024x1024": None,
-    "map_rowsum_f32_4096x1024": None,
-    "gemm_bias_relu_bf16_8192": None,
+    "softmax_rows_f32_16384x4096": 481820544,      # read 268.4 MB + write 213.4 MB (the rest of y still in L2)
+    "layernorm_rows_bf16_65536x8192": 2097888000,
+    "reduce_outer_f32_256x1024x1024": 1078140828,
+    "map_rowsum_f32_4096x1024": 16783488,
+    "gemm_bias_relu_bf16_8192": 1001582720,
 }
 
 

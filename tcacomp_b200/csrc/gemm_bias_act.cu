@@ -15,7 +15,9 @@
 //     (rows 0-127 and 128-255 of the tile, 256 fp32 columns each = all 512 TMEM columns),
 //     frees a ring stage with tcgen05.commit, and signals the epilogue per tile;
 //   * warps 2-9 are the epilogue: tcgen05.ld 32 lanes x 32 columns at a time, add bias,
-//     ReLU, round to bf16, 16-byte stores. Each accumulator is handed back to the MMA warp
+//     ReLU, round to bf16, stage a 32-row x 64-column box in shared memory (128-byte swizzle,
+//     conflict-free 16-byte stores) and hand it to a TMA store, which writes whole 128-byte
+//     row segments and clips ragged edges. Each accumulator is handed back to the MMA warp
 //     as soon as it is drained, so the next tile's first K blocks overlap the second drain.
 //
 // Per K block a CTA moves 64 KB into shared memory for 8.4 MFLOP (131 flop per byte), which
@@ -41,7 +43,9 @@ constexpr int B_ATOM_BYTES = BK * 128;      // one 64(n) x 64(k) box
 constexpr int EPI_WARPS = 8;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_BYTES + 1024;  // + alignment slack
+constexpr int EPI_BOX_BYTES = 32 * 128;     // one warp's staging box: 32 rows x 64 bf16
+constexpr size_t SMEM_BYTES =
+    static_cast<size_t>(STAGES) * STAGE_BYTES + EPI_WARPS * EPI_BOX_BYTES + 1024;  // + alignment slack
 
 // Device status of the last contraction kernel that gave up on a wait (0 = none).
 __device__ int g_gemm_status = 0;
@@ -61,8 +65,8 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, ui
 
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                     const float* __restrict__ bias, __nv_bfloat16* __restrict__ c, uint32_t M, uint32_t N,
-                     uint32_t K, int act) {
+                     const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
+                     uint32_t N, uint32_t K, int act) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
   __shared__ __align__(8) uint64_t bar_empty[STAGES];
@@ -92,6 +96,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     ptx::fence_proxy_async();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_c);
   }
   if (warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), TMEM_COLS);
@@ -163,6 +168,9 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const int e = warp - 2;
     const uint32_t quad = static_cast<uint32_t>(warp) & 3u;  // TMEM lanes a warp may read: 32 * (warp % 4)
     const uint32_t half = static_cast<uint32_t>(e) >> 2;     // which 128 of the 256 columns
+    const uint32_t stage_box = smem_base + STAGES * STAGE_BYTES + e * EPI_BOX_BYTES;  // 1024-byte aligned
+    const uint32_t my_row = stage_box + lane * 128;
+    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
     uint32_t tile_iter = 0;
     bool ok = true;
     for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
@@ -173,49 +181,73 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
 #pragma unroll 1
       for (uint32_t a = 0; a < 2; ++a) {
-        const uint32_t row = tc.m * BM + a * UMMA_M + quad * 32 + lane;
+        const uint32_t row0 = tc.m * BM + a * UMMA_M + quad * 32;
 #pragma unroll 1
-        for (uint32_t ch = 0; ch < 4; ++ch) {
-          const uint32_t col = tc.n * BN + half * 128 + ch * 32;
-          uint32_t r[32];
-          if (num_kb > 0) {
-            ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + ch * 32, r);
-            ptx::tmem_ld_wait();
-          } else {
+        for (uint32_t grp = 0; grp < 2; ++grp) {  // two 64-column boxes per warp and accumulator
+          const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
+          // the previous box must have left shared memory before it is overwritten
+          if (lane == 0) ptx::tma_store_wait_read();
+          __syncwarp();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty reduction: the accumulator's init
-          }
-          if (row < M && col < N) {
-            __nv_bfloat16* dst = c + static_cast<size_t>(row) * N + col;
+          for (uint32_t h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            if (num_kb > 0) {
+              ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64 + h * 32, r);
+              ptx::tmem_ld_wait();
+            } else {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col + v * 8 < N) {  // N % 8 == 0: 8-column groups are whole
-                uint32_t w[4];
+              for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty reduction: the accumulator's init
+            }
+            const uint32_t col = col0 + h * 32;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  float f0 = __uint_as_float(r[v * 8 + 2 * j]), f1 = __uint_as_float(r[v * 8 + 2 * j + 1]);
-                  if (bias != nullptr) {
-                    f0 += __ldg(bias + col + v * 8 + 2 * j);
-                    f1 += __ldg(bias + col + v * 8 + 2 * j + 1);
-                  }
-                  if (act == TCAB_ACT_RELU) {
-                    f0 = fmaxf(f0, 0.0f);
-                    f1 = fmaxf(f1, 0.0f);
-                  }
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-                  w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            for (int v = 0; v < 4; ++v) {  // four 16-byte chunks of 8 columns
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (bias != nullptr && col + v * 8 < N) {  // N % 8 == 0: 8-column groups are whole
+                if (bias_vec) {
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8) + 1);
+                  f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+                  f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] += __ldg(bias + col + v * 8 + j);
                 }
-                *reinterpret_cast<uint4*>(dst + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
               }
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f0 = f[2 * j], f1 = f[2 * j + 1];
+                if (act == TCAB_ACT_RELU) {
+                  f0 = fmaxf(f0, 0.0f);
+                  f1 = fmaxf(f1, 0.0f);
+                }
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+              // 128-byte swizzle: 16-byte chunk c of row r lives at chunk position c ^ (r % 8)
+              const uint32_t chunk = (h * 4 + v) ^ (static_cast<uint32_t>(lane) & 7u);
+              ptx::st_shared_v4(my_row + chunk * 16, w[0], w[1], w[2], w[3]);
+            }
+          }
+          if (grp == 1) {
+            // both halves of this accumulator that this warp owns are in registers/shared memory now
+            ptx::tc_fence_before();
+          }
+          ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
+          __syncwarp();
+          if (lane == 0) {
+            if (grp == 1) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[a]));  // hand the accumulator back
+            if (row0 < M && col0 < N) {  // a box that starts inside the tensor; the hardware clips its edges
+              ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+              ptx::tma_store_commit();
             }
           }
         }
-        // this accumulator is drained: hand it back to the MMA warp
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[a]));
       }
     }
+    if (lane == 0) ptx::tma_store_wait_all();  // every box has reached global memory before the CTA exits
   }
 
   ptx::tc_fence_before();
@@ -248,7 +280,8 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// A 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of box_rows x 64 columns.
+// A 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of box_rows x 64 columns
+// (128 bytes, swizzled).
 int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return fail(TCAB_ERR_CUDA, "gemm_bias_act: cuTensorMapEncodeTiled is not available");
@@ -276,7 +309,11 @@ int gemm_device_status(int* out) {
 int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias, int act,
                          __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
   if (m == 0 || n == 0) return TCAB_OK;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tcm;
+  {
+    const int rc = make_map(&tcm, c, m, n, 32);
+    if (rc != TCAB_OK) return rc;
+  }
   if (k > 0) {
     int rc = make_map(&ta, a, m, k, BM);
     if (rc != TCAB_OK) return rc;
@@ -299,7 +336,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   const Tune& tn = tune(kGemm);
   uint64_t grid = tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count());
   if (grid > tiles) grid = tiles;
-  gemm_bias_act_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, bias, c, m, n, k, act);
+  gemm_bias_act_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, tcm, bias, m, n, k, act);
   count_launch();
   return check_launch("gemm_bias_act_kernel");
 }
