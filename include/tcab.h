@@ -116,7 +116,12 @@ TCAB_API uint64_t tcab_launch_count(void);
  * All operands: fp32, same rank (1..4) and extents. `out` is fp32 with the operands' extents
  * minus the reduced axis (a rank-1 operand gives a rank-1 output of extent 1).
  * reduce_axis == rank-1 selects the innermost-axis kernel, any other axis the outer-axis kernel.
- * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative. */
+ * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative.
+ * Allocation: when there are fewer rows than SMs and the rows are long, a row is split over several
+ * CTAs (the multi-CTA reduction the reference stubs as GlobalReducer, runtime/tca/reducer.h:187-213) and
+ * the partial results pass through 64 KiB of scratch memory that the library allocates with cudaMalloc
+ * the first time a (device, stream) pair needs it and keeps until the process exits. Make that first
+ * call outside any stream capture. */
 TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                       uint32_t reduce_axis, const tcab_tensor* out, void* stream);
 

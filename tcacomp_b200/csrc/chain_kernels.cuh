@@ -135,6 +135,59 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   }
 }
 
+// A long row split over several CTAs (the multi-CTA reduction the reference stubs as
+// GlobalReducer, runtime/tca/reducer.h:187-213). Pass 1: CTA (row, s) folds vectors
+// [s*vec_per_split, (s+1)*vec_per_split) of its row and writes ONE partial to
+// partials[row*splits + s] (global scratch memory). Pass 2 (chain_split_finish) folds the
+// partials of a row in ascending order, applies init and the piped map.
+template <class Map, int COMBINE, int NIN, int V>
+__global__ void __launch_bounds__(256)
+chain_inner_split(Ptrs<NIN> ins, float* __restrict__ partials, u32 nk, u32 splits, u32 vec_per_split, Caps caps) {
+  typedef Comb<COMBINE> C;
+  __shared__ float slots[8];
+  const u32 row = blockIdx.x / splits, s = blockIdx.x % splits;
+  const u32 nvec = nk / V;
+  const u64 vbase = static_cast<u64>(row) * nvec;
+  const u32 v0 = s * vec_per_split;
+  const u32 v1 = (nvec - v0 < vec_per_split) ? nvec : v0 + vec_per_split;
+  float acc = C::identity();
+  if (v0 < nvec) {
+#pragma unroll 4
+    for (u32 idx = v0 + threadIdx.x; idx < v1; idx += 256) {
+      float f[NIN][V];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a], vbase + idx, f[a]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float p[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) p[a] = f[a][j];
+        acc = C::apply(acc, Map::apply(p, caps.c));
+      }
+    }
+  }
+  acc = lanes_allreduce<C, 32>(acc);
+  if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    acc = lanes_allreduce<C, 8>(slots[threadIdx.x & 7]);
+    if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+  }
+}
+
+template <class Post, int COMBINE>
+__global__ void __launch_bounds__(128)
+chain_split_finish(const float* __restrict__ partials, float* __restrict__ out, u32 rows, u32 splits, float init,
+                   Caps caps) {
+  typedef Comb<COMBINE> C;
+  const u32 row = blockIdx.x * 128 + threadIdx.x;
+  if (row >= rows) return;
+  float a = init;
+  for (u32 s = 0; s < splits; ++s) a = C::apply(a, partials[static_cast<u64>(row) * splits + s]);
+  float r[1] = {a};
+  out[row] = Post::apply(r, caps.c + 8);
+}
+
 // Reduce over a MIDDLE axis: operands are [nb, nk, nc]; a CTA owns (one b, a
 // tile of 32*V columns), lane l owns V columns, warp w owns k = w, w+KW, ...
 template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL>

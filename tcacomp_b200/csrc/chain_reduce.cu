@@ -5,7 +5,10 @@
 // canonicaliser prints, so that the key and the code cannot drift apart: the
 // macro stringifies the expression it compiles. A chain whose lambdas are not in
 // the table is reported as unsupported by this build.
+#include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "chain_kernels.cuh"
@@ -42,6 +45,11 @@ TCAB_LAMBDA(MapScaleMul, 2, (((c0 * p0) + c1) * p1))
 TCAB_LAMBDA(PostSelfRsqrt, 1, (p0 * rsqrtf(((p0 * c0) + c1))))
 TCAB_LAMBDA(PostAddTanh, 1, (p0 + (c0 * tanhf(p0))))
 TCAB_LAMBDA(PostScale, 1, (p0 * c0))
+
+// Partials of the multi-CTA split: at most this many per launch.
+constexpr uint32_t kMaxSplitPartials = 16384;
+
+float* split_scratch(cudaStream_t stream);
 
 struct Args {
   const float* const* ins;
@@ -88,6 +96,43 @@ int launch_outer(const Args& a) {
   return check_launch("chain_outer");
 }
 
+// How many CTAs share one row: 1 = no split. A split pays off when there are fewer rows than SMs and
+// the rows are long; the number of partials is bounded by the scratch buffer.
+uint32_t choose_splits(uint64_t rows, uint32_t nvec) {
+  const Tune& tn = tune(kReduceInner);
+  if (rows == 0 || rows > kMaxSplitPartials) return 1;
+  uint64_t s;
+  if (tn.p1 > 0) {
+    s = static_cast<uint64_t>(tn.p1);
+  } else {
+    if (rows >= static_cast<uint64_t>(sm_count()) || nvec < 4096) return 1;
+    s = (4ull * sm_count() + rows - 1) / rows;           // about four CTAs per SM in total
+    const uint64_t by_len = (nvec + 1023) / 1024;         // at least 1024 vectors per CTA
+    if (s > by_len) s = by_len;
+  }
+  if (s > nvec) s = nvec;
+  if (s * rows > kMaxSplitPartials) s = kMaxSplitPartials / rows;
+  return s < 1 ? 1u : static_cast<uint32_t>(s);
+}
+
+template <class Map, class Post, int COMBINE, int V>
+int launch_split(const Args& a, float* scratch, uint32_t nvec, uint32_t splits) {
+  constexpr int NIN = Map::kIn;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  const uint32_t rows = static_cast<uint32_t>(a.outer);
+  const uint32_t vec_per_split = (nvec + splits - 1) / splits;
+  tcabk::chain_inner_split<Map, COMBINE, NIN, V>
+      <<<rows * splits, 256, 0, a.stream>>>(ptrs, scratch, a.nk, splits, vec_per_split, a.caps);
+  count_launch();
+  int rc = check_launch("chain_inner_split");
+  if (rc != TCAB_OK) return rc;
+  tcabk::chain_split_finish<Post, COMBINE>
+      <<<(rows + 127) / 128, 128, 0, a.stream>>>(scratch, a.out, rows, splits, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_split_finish");
+}
+
 template <class Map, class Post, int COMBINE>
 int launch_chain(const Args& a) {
   constexpr int NIN = Map::kIn;
@@ -96,6 +141,13 @@ int launch_chain(const Args& a) {
   if (a.inner == 1) {
     const bool vec = al && (a.nk % 4 == 0);
     const uint32_t nvec = vec ? a.nk / 4 : a.nk;
+    const uint32_t splits = choose_splits(a.outer, nvec);
+    if (splits > 1) {
+      float* scratch = split_scratch(a.stream);  // null only if the allocation failed: no split then
+      if (scratch != nullptr)
+        return vec ? launch_split<Map, Post, COMBINE, 4>(a, scratch, nvec, splits)
+                   : launch_split<Map, Post, COMBINE, 1>(a, scratch, nvec, splits);
+    }
     // short rows: one thread folds a row sequentially, which is the reference's SeqReducer order exactly
     int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec <= 2048 ? 32 : 256;
     const Tune& tn = tune(kReduceInner);
@@ -139,6 +191,30 @@ const Entry kTable[] = {
     TCAB_ENTRY_NOPOST(MapScaleMul, 0), TCAB_ENTRY(MapSqMul, PostSelfRsqrt, 0),
     TCAB_ENTRY(MapAxpy, PostAddTanh, 0), TCAB_ENTRY(MapMul2, PostScale, 0),
 };
+
+// Scratch for the partials of the split path: one buffer of kMaxSplitPartials floats per
+// (device, stream), allocated with cudaMalloc the first time a stream needs it and kept until the
+// process exits. Per stream, because launches on different streams may overlap on the GPU.
+float* split_scratch(cudaStream_t stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, float*> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair(dev, stream);
+  auto it = table.find(key);
+  if (it != table.end()) return it->second;
+  float* p = nullptr;
+  if (cudaMalloc(&p, kMaxSplitPartials * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    p = nullptr;  // not fatal: the caller falls back to the single-CTA-per-row kernels
+  }
+  table[key] = p;
+  return p;
+}
 
 int combine_id(const std::string& text) {
   if (text == "(p0 + p1)" || text == "(p1 + p0)") return 0;

@@ -459,3 +459,41 @@ def test_gemm_full_size_sampled_rows_and_linearity(oracle, cuda):
     c1 = T.gemm_bias_act(a, b, None, "none")
     c2 = T.gemm_bias_act(a * 2, b, None, "none")
     assert torch.equal(c2.float(), c1.float() * 2)
+
+
+# ----------------------------------------------------------------------------
+# long rows split over several CTAs (partials through the library's scratch buffer)
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(1, 1 << 20), (2, 70001), (3, 262144), (7, 1000003), (100, 40000)])
+def test_split_reduction_long_rows(oracle, cuda, rows, cols):
+    from oracle import checks
+    rng = np.random.default_rng(rows + cols)
+    x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    xd = dev_f32(x, cuda)
+    n0 = T.launch_count()
+    got = T.chain_reduce([xd], "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)").cpu().numpy()
+    assert T.launch_count() - n0 == 2  # the split pass and the finishing pass
+    assert checks.rowsum_close(got, x)
+    # max is order-independent: bit-exact whatever the split, and init takes part exactly once
+    gm = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.5).cpu().numpy()
+    assert np.array_equal(gm, np.maximum(x.max(1), np.float32(0.5)))
+    # the same rows with the split switched off agree to rounding; with a forced odd split as well
+    try:
+        T.tune("reduce_inner", 0, 1)
+        one = T.chain_reduce([xd], "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)").cpu().numpy()
+        T.tune("reduce_inner", 0, 7)
+        odd = T.chain_reduce([xd], "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)").cpu().numpy()
+    finally:
+        T.tune("reduce_inner")
+    assert checks.rowsum_close(one, x) and checks.rowsum_close(odd, x)
+
+
+def test_split_reduction_with_piped_map_and_two_operands(oracle, cuda):
+    rng = np.random.default_rng(17)
+    x = rng.uniform(0, 1, (2, 300000)).astype(np.float32)
+    z = rng.uniform(0, 1, (2, 300000)).astype(np.float32)
+    got = T.chain_reduce([dev_f32(x, cuda), dev_f32(z, cuda)], "(p0 * p0) * p1", post_expr="p0 * rsqrtf(p0 * c0 + c1)",
+                         captures=(1.0 / 300000, 1e-5)).cpu().numpy()
+    s = ((x.astype(np.float64) ** 2) * z).sum(1)
+    want = s / np.sqrt(s / 300000 + 1e-5)
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
