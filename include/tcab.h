@@ -44,6 +44,7 @@ extern "C" {
 #define TCAB_MAX_RANK 4
 #define TCAB_MAX_INPUTS 4
 #define TCAB_MAX_CAPTURES 8
+#define TCAB_NOALLOC_MAX_ROWS 4096 /* rows tcab_chain_reduce_noalloc accepts (its fixed scratch array) */
 
 /* Status codes. 0 is success; everything else leaves a message for tcab_last_error(). */
 typedef enum tcab_status {
@@ -124,6 +125,27 @@ TCAB_API uint64_t tcab_launch_count(void);
  * call outside any stream capture. */
 TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                       uint32_t reduce_axis, const tcab_tensor* out, void* stream);
+
+/* tcab_chain_reduce over the INNERMOST axis for callers that must not trigger a device allocation.
+ * It has no counterpart in the reference. Who needs it: a host that runs under a memory budget it
+ * has already handed out in full (an embedding framework with its own arena, a serving process whose
+ * pool was sized at start-up), code that runs while a CUDA graph is being captured, or a real-time
+ * loop in which cudaMalloc's implicit device synchronisation is not acceptable. tcab_chain_reduce may
+ * allocate 64 KiB per (device, stream) for the partial results of its multi-CTA split; this variant
+ * runs the same split kernels with the partials in a fixed 16 KiB array that is part of the library's
+ * device image (every GPU that loads the library holds it until the process exits), and calls neither
+ * cudaMalloc nor cudaFree nor any allocating library routine.
+ *   - operands: fp32, identical shape; the reduced axis is the innermost one; the rows (the product of
+ *     the other extents) may number at most TCAB_NOALLOC_MAX_ROWS, because every row needs at least one
+ *     slot of the array. More rows are rejected with TCAB_ERR_TOO_LARGE; use tcab_chain_reduce then.
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current). Make that first call before any stream capture begins.
+ *   - all calls on a device share the one array. It keeps the previous call's partial results; nothing
+ *     in it needs clearing, because a call writes every slot it later reads. Two calls that overlap on
+ *     the GPU (different streams, or different host threads on different streams) race on it: order
+ *     them on one stream or with events. */
+TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
+                                       const tcab_tensor* out, void* stream);
 
 /* Outer-axis reduce of t[b, k, c] over k in ONE pass: any of sum (fp32), max (fp32) and argmax
  * (int32, lowest index among equal maxima) may be NULL. Each output is [b, c].

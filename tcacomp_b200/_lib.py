@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libtcab.so")
 MAX_RANK = 4
 MAX_INPUTS = 4
 MAX_CAPTURES = 8
+NOALLOC_MAX_ROWS = 4096
 
 OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE = range(8)
 F32, BF16, I32 = 0, 1, 2
@@ -49,6 +50,8 @@ SYMBOLS = [
     ("tcab_launch_count", C.c_uint64, []),
     ("tcab_chain_reduce", C.c_int,
      [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
+    ("tcab_chain_reduce_noalloc", C.c_int,
+     [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_reduce_outer", C.c_int,
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
     ("tcab_softmax_rows", C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),

@@ -318,6 +318,45 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
                              static_cast<cudaStream_t>(stream));
 }
 
+int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
+                              const tcab_tensor* out, void* stream) {
+  const char* op = "chain_reduce_noalloc";
+  if (chain == nullptr || chain->map_expr == nullptr || chain->combine_expr == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: chain, map_expr and combine_expr are required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
+  const float* ptrs[TCAB_MAX_INPUTS] = {};
+  for (uint32_t i = 0; i < n_ins; ++i) {
+    char name[16];
+    std::snprintf(name, sizeof(name), "ins[%u]", i);
+    TCAB_TRY(check_tensor(op, name, &ins[i]));
+    TCAB_TRY(need_dtype(op, name, &ins[i], TCAB_F32, "f32"));
+    TCAB_TRY(need_elem_align(op, name, &ins[i], 4));
+    if (i > 0 && !same_shape(&ins[0], &ins[i]))
+      return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0]", op, name);
+    ptrs[i] = static_cast<const float*>(ins[i].data);
+  }
+  const tcab_tensor* t = &ins[0];
+  TCAB_TRY(check_tensor(op, "out", out));
+  TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
+  TCAB_TRY(need_elem_align(op, "out", out, 4));
+  const uint64_t rows = count(t, 0, t->rank - 1);
+  bool ok = t->rank == 1 ? (out->rank == 1 && out->dims[0] == 1) : out->rank == t->rank - 1;
+  for (uint32_t i = 0; ok && t->rank > 1 && i + 1 < t->rank; ++i) ok = out->dims[i] == t->dims[i];
+  if (!ok) return fail(TCAB_ERR_SHAPE, "%s: out must have the operands' extents without the innermost axis", op);
+  if (rows > TCAB_NOALLOC_MAX_ROWS)
+    return fail(TCAB_ERR_TOO_LARGE,
+                "%s: %llu rows exceed TCAB_NOALLOC_MAX_ROWS = %d (the fixed scratch array); use tcab_chain_reduce",
+                op, static_cast<unsigned long long>(rows), TCAB_NOALLOC_MAX_ROWS);
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
+  TCAB_TRY(have_device(op));
+  return launch_chain_reduce_noalloc(pc, ptrs, rows, t->dims[t->rank - 1], static_cast<float*>(out->data),
+                                     static_cast<cudaStream_t>(stream));
+}
+
 int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias, int act,
                        const tcab_tensor* c, void* stream) {
   const char* op = "gemm_bias_act";

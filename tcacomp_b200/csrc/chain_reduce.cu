@@ -172,18 +172,35 @@ int launch_chain(const Args& a) {
   return vec ? launch_outer<Map, Post, COMBINE, 4>(a) : launch_outer<Map, Post, COMBINE, 1>(a);
 }
 
+// The split path on a scratch buffer the caller of this function provides (used by the entry point
+// that allocates nothing): always two launches, whatever the shape.
+template <class Map, class Post, int COMBINE>
+int launch_split_on(const Args& a, float* scratch, uint32_t splits) {
+  constexpr int NIN = Map::kIn;
+  bool al = true;
+  for (int i = 0; i < NIN; ++i) al = al && aligned16(a.ins[i]);
+  const bool vec = al && (a.nk % 4 == 0);
+  const uint32_t nvec = vec ? a.nk / 4 : a.nk;
+  if (splits > nvec) splits = nvec > 0 ? nvec : 1;
+  return vec ? launch_split<Map, Post, COMBINE, 4>(a, scratch, nvec, splits)
+             : launch_split<Map, Post, COMBINE, 1>(a, scratch, nvec, splits);
+}
+
 struct Entry {
   const char* map;
   const char* post;  // "" = the reduction is stored as it is
   int combine;
   int n_in;
   int (*launch)(const Args&);
+  int (*launch_noalloc)(const Args&, float* scratch, uint32_t splits);  // split path on caller-free scratch
 };
 
-#define TCAB_ENTRY(MAP, POST, COMBINE) \
-  { MAP::text(), POST::text(), COMBINE, MAP::kIn, &launch_chain<MAP, POST, COMBINE> }
-#define TCAB_ENTRY_NOPOST(MAP, COMBINE) \
-  { MAP::text(), "", COMBINE, MAP::kIn, &launch_chain<MAP, tcabk::PostNone, COMBINE> }
+#define TCAB_ENTRY(MAP, POST, COMBINE)                                            \
+  { MAP::text(), POST::text(), COMBINE, MAP::kIn, &launch_chain<MAP, POST, COMBINE>, \
+    &launch_split_on<MAP, POST, COMBINE> }
+#define TCAB_ENTRY_NOPOST(MAP, COMBINE)                                                  \
+  { MAP::text(), "", COMBINE, MAP::kIn, &launch_chain<MAP, tcabk::PostNone, COMBINE>,    \
+    &launch_split_on<MAP, tcabk::PostNone, COMBINE> }
 
 const Entry kTable[] = {
     TCAB_ENTRY_NOPOST(MapIdent, 0),    TCAB_ENTRY_NOPOST(MapIdent, 1),    TCAB_ENTRY_NOPOST(MapIdent, 2),
@@ -266,6 +283,73 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   Args a{ins, out, outer, nk, inner, pc.init, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
   return kTable[pc.entry].launch(a);
+}
+
+// ---------------------------------------------------------------------------
+// The entry point that allocates nothing
+// ---------------------------------------------------------------------------
+// Scratch for the split path when the caller cannot let the library allocate: a fixed array in
+// device memory, part of the library image. Every GPU that loads the library holds these 16 KiB
+// until the process exits. Every call on a device shares the array.
+constexpr uint32_t kNoAllocMaxPartials = TCAB_NOALLOC_MAX_ROWS;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxPartials];
+
+namespace {
+
+// In host code `g_noalloc_scratch` names a host-side shadow of the array, not its device address;
+// a kernel handed that name would read and write the wrong memory. The device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "chain_reduce_noalloc: no current CUDA device");
+  }
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce_noalloc: device ordinal %d beyond %d", dev, kMaxDevices - 1);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return fail(TCAB_ERR_CUDA, "chain_reduce_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    g_noalloc_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return TCAB_OK;
+}
+
+}  // namespace
+
+int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins, uint64_t rows, uint32_t nk,
+                                float* out, cudaStream_t s) {
+  if (rows > kNoAllocMaxPartials)
+    return fail(TCAB_ERR_TOO_LARGE,
+                "chain_reduce_noalloc: %llu rows, but the fixed scratch array holds %u partial results "
+                "(one per row at least); use tcab_chain_reduce for larger problems",
+                static_cast<unsigned long long>(rows), kNoAllocMaxPartials);
+  if (rows == 0) return TCAB_OK;
+  float* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != TCAB_OK) return rc;
+  // As many CTAs per row as the array has room for, up to about four CTAs per SM in total and at
+  // least 1024 vectors per CTA. Every partial that pass 2 reads is written by pass 1 of the same call
+  // (a CTA with an empty range writes the combiner's identity), so nothing in the array has to be
+  // cleared between calls.
+  uint64_t splits = (4ull * sm_count() + rows - 1) / rows;
+  const uint64_t by_len = (static_cast<uint64_t>(nk) / 4 + 1023) / 1024;
+  if (splits > by_len) splits = by_len;
+  if (splits * rows > kNoAllocMaxPartials) splits = kNoAllocMaxPartials / rows;
+  if (splits < 1) splits = 1;
+  Args a{ins, out, rows, nk, 1, pc.init, {}, s};
+  for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
+  return kTable[pc.entry].launch_noalloc(a, scratch, static_cast<uint32_t>(splits));
 }
 
 }  // namespace tcab

@@ -146,6 +146,38 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
     return out
 
 
+def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.Tensor,
+                         combine_expr: str = "(p0 + p1)", init: float = 0.0, post_expr: Optional[str] = None,
+                         captures: Sequence[float] = (), stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """chain_reduce over the innermost axis through the entry point that never allocates.
+
+    For hosts that cannot let the library call cudaMalloc (a memory budget that is already handed
+    out, a stream capture in progress, a loop that cannot afford cudaMalloc's device
+    synchronisation). The caller passes `out`; nothing is allocated here either, on the host side
+    only the small ctypes argument structs are built. At most `_lib.NOALLOC_MAX_ROWS` rows; calls on
+    one device share a fixed scratch array, so do not let two of them overlap on the GPU.
+    """
+    ins = list(ins)
+    if not 1 <= len(ins) <= _lib.MAX_INPUTS:
+        raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
+    if len(captures) > _lib.MAX_CAPTURES:
+        raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
+    chain = _lib.Chain()
+    chain.map_expr = map_expr.encode()
+    chain.combine_expr = combine_expr.encode()
+    chain.post_expr = post_expr.encode() if post_expr else None
+    chain.init = init
+    chain.n_captures = len(captures)
+    for i, c in enumerate(captures):
+        chain.captures[i] = c
+    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    ov = _view(out, "out")
+    with _on_device(ins[0]):
+        _lib.check(_lib.load().tcab_chain_reduce_noalloc(C.byref(chain), arr, len(ins), C.byref(ov),
+                                                         _stream(stream, ins[0])))
+    return out
+
+
 def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   act: str = "relu", out: Optional[torch.Tensor] = None,
                   stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
