@@ -22,10 +22,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libtcab.so")
+HOST_LIB = os.path.join(HERE, "libtcab_host.so")  # the C++ builder mirror above the C ABI (csrc/host/)
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-I", OBJ,
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden"]
 
@@ -49,6 +50,17 @@ def _digest(path: str, deps: list[str]) -> str:
         with open(p, "rb") as f:
             h.update(f.read())
     return h.hexdigest()
+
+
+def _embed_kernel_text() -> None:
+    """chain_kernels.cuh as a raw string literal for the run-time compiler (chain_jit.cu)."""
+    text = open(os.path.join(CSRC, "chain_kernels.cuh")).read().replace("#pragma once\n", "")
+    assert ")TCABSRC\"" not in text
+    out = os.path.join(OBJ, "chain_kernels_text.inc")
+    new = 'R"TCABSRC(' + text + ')TCABSRC"\n'
+    if not os.path.exists(out) or open(out).read() != new:
+        with open(out, "w") as f:
+            f.write(new)
 
 
 def _compile(src: str, force: bool, verbose: bool) -> str:
@@ -78,6 +90,7 @@ def _compile(src: str, force: bool, verbose: bool) -> str:
 
 def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
+    _embed_kernel_text()
     cu, cpp = _sources()
     jobs = jobs or min(8, os.cpu_count() or 1)
     before = {s: os.path.getmtime(os.path.join(OBJ, s + ".o")) if os.path.exists(os.path.join(OBJ, s + ".o")) else 0
@@ -86,11 +99,27 @@ def build(force: bool = False, jobs: int | None = None, verbose: bool = False) -
         objs = list(ex.map(lambda s: _compile(s, force, verbose), cu + cpp))
     changed = any(os.path.getmtime(o) != before[s] for o, s in zip(objs, cu + cpp))
     if force or changed or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"linking libtcab.so failed:\n{r.stderr[-4000:]}")
+    build_host(force or changed)
     return LIB
+
+
+def build_host(force: bool = False) -> str:
+    """g++ build of csrc/host/*.cpp into libtcab_host.so, linked against libtcab.so beside it."""
+    hdir = os.path.join(CSRC, "host")
+    srcs = sorted(os.path.join(hdir, f) for f in os.listdir(hdir) if f.endswith(".cpp"))
+    deps = srcs + [os.path.join(hdir, "pkg.h"), os.path.join(HERE, "..", "include", "tcab.h")]
+    if not force and os.path.exists(HOST_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(HOST_LIB) for d in deps):
+        return HOST_LIB
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-o", HOST_LIB] + srcs + \
+          ["-L" + HERE, "-ltcab", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building libtcab_host.so failed:\n{r.stderr[-4000:]}")
+    return HOST_LIB
 
 
 def main(argv=None) -> int:

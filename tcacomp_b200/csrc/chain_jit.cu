@@ -1,0 +1,246 @@
+// chain_jit.cu -- run-time compilation of the chain kernels for lambdas that have no
+// ahead-of-time instance.
+//
+// The reference compiles every kernel from its lambdas (internal/cg/cxx/emit.go:85-190 prints the
+// translation unit, the user runs nvcc). Here the kernels are fixed text (chain_kernels.cuh, embedded
+// in the library at build time) and only the two functor structs are printed from the caller's
+// canonical lambda text, which expr.cpp has validated token by token: nothing but + - * /, unary
+// minus, p#/c# and the reference's fp32 builtins can appear in it. NVRTC (libnvrtc, opened with
+// dlopen on first need) compiles that for sm_100a; the cubin is loaded once per process with
+// cudaLibraryLoadData and cached by lambda text. Compilation happens on the first call with a new
+// lambda (a few hundred milliseconds); later calls only look the kernels up.
+#include <dlfcn.h>
+#include <nvrtc.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "chain_kernels.cuh"
+#include "common.cuh"
+
+namespace tcab {
+namespace {
+
+const char kKernelText[] =
+#include "chain_kernels_text.inc"
+    ;
+
+struct Nvrtc {
+  void* handle = nullptr;
+  decltype(&nvrtcCreateProgram) create = nullptr;
+  decltype(&nvrtcDestroyProgram) destroy = nullptr;
+  decltype(&nvrtcCompileProgram) compile = nullptr;
+  decltype(&nvrtcAddNameExpression) add_name = nullptr;
+  decltype(&nvrtcGetLoweredName) lowered = nullptr;
+  decltype(&nvrtcGetCUBINSize) cubin_size = nullptr;
+  decltype(&nvrtcGetCUBIN) cubin = nullptr;
+  decltype(&nvrtcGetProgramLogSize) log_size = nullptr;
+  decltype(&nvrtcGetProgramLog) log = nullptr;
+  bool ok = false;
+};
+
+const Nvrtc& nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    for (const char* name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"}) {
+      n.handle = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+      if (n.handle) break;
+    }
+    if (!n.handle) return;
+#define TCAB_SYM(field, sym) n.field = reinterpret_cast<decltype(n.field)>(dlsym(n.handle, #sym))
+    TCAB_SYM(create, nvrtcCreateProgram);
+    TCAB_SYM(destroy, nvrtcDestroyProgram);
+    TCAB_SYM(compile, nvrtcCompileProgram);
+    TCAB_SYM(add_name, nvrtcAddNameExpression);
+    TCAB_SYM(lowered, nvrtcGetLoweredName);
+    TCAB_SYM(cubin_size, nvrtcGetCUBINSize);
+    TCAB_SYM(cubin, nvrtcGetCUBIN);
+    TCAB_SYM(log_size, nvrtcGetProgramLogSize);
+    TCAB_SYM(log, nvrtcGetProgramLog);
+#undef TCAB_SYM
+    n.ok = n.create && n.destroy && n.compile && n.add_name && n.lowered && n.cubin_size && n.cubin && n.log_size &&
+           n.log;
+  });
+  return n;
+}
+
+// The kernels one chain needs, in the order of JitChain::k.
+enum Slot {
+  kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
+  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kSlots
+};
+
+struct JitChain {
+  cudaLibrary_t lib = nullptr;
+  cudaKernel_t k[kSlots] = {};
+  int n_in = 0;
+};
+
+std::mutex g_mu;
+std::map<std::string, JitChain*> g_cache;   // key: n_in | combine | map text | post text
+std::map<std::string, std::string> g_failed;  // key -> compiler message (do not recompile a failing lambda)
+
+std::string functor(const char* name, const std::string& expr, int n_in) {
+  std::string s = "struct ";
+  s += name;
+  s += " {\n  static __device__ __forceinline__ float apply(const float* p, const float* c) {\n";
+  for (int i = 0; i < 4; ++i)
+    s += "    const float p" + std::to_string(i) + " = p[" + std::to_string(i < n_in ? i : 0) + "];\n";
+  for (int i = 0; i < 8; ++i) s += "    const float c" + std::to_string(i) + " = c[" + std::to_string(i) + "];\n";
+  s += "    (void)p0; (void)p1; (void)p2; (void)p3;\n";
+  s += "    (void)c0; (void)c1; (void)c2; (void)c3; (void)c4; (void)c5; (void)c6; (void)c7;\n";
+  s += "    return " + expr + ";\n  }\n};\n";
+  return s;
+}
+
+int compile(const std::string& key, const std::string& map_text, const std::string& post_text, int combine, int n_in,
+            JitChain** out) {
+  const Nvrtc& nv = nvrtc();
+  if (!nv.ok)
+    return fail(TCAB_ERR_UNSUPPORTED,
+                "chain_reduce: no kernel in this build for map '%s' post '%s', and libnvrtc is not available to "
+                "compile one", map_text.c_str(), post_text.c_str());
+  std::string src = kKernelText;
+  src += "\nnamespace tcabj {\n";
+  src += functor("Map", map_text, n_in);
+  src += post_text.empty() ? "typedef tcabk::PostNone Post;\n" : functor("Post", post_text, 1);
+  src += "}\n";
+  const std::string n = std::to_string(n_in), c = std::to_string(combine);
+  std::vector<std::string> names(kSlots);
+  const int tprs[4] = {1, 4, 32, 256};
+  for (int v = 0; v < 2; ++v)
+    for (int t = 0; t < 4; ++t)
+      names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
+                                                    std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ">";
+  names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4>";
+  names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1>";
+  names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
+  names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4>";
+  names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4>";
+
+  nvrtcProgram prog = nullptr;
+  if (nv.create(&prog, src.c_str(), "tcab_chain_jit.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+    return fail(TCAB_ERR_CUDA, "chain_reduce: nvrtcCreateProgram failed");
+  for (const std::string& e : names) nv.add_name(prog, e.c_str());
+  const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
+  const nvrtcResult res = nv.compile(prog, 3, opts);
+  if (res != NVRTC_SUCCESS) {
+    size_t ls = 0;
+    nv.log_size(prog, &ls);
+    std::string log(ls, '\0');
+    if (ls) nv.log(prog, &log[0]);
+    nv.destroy(&prog);
+    g_failed[key] = log.substr(0, 300);
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: run-time compilation of map '%s' post '%s' failed: %s",
+                map_text.c_str(), post_text.c_str(), log.substr(0, 300).c_str());
+  }
+  size_t cs = 0;
+  nv.cubin_size(prog, &cs);
+  std::vector<char> cubin(cs);
+  nv.cubin(prog, cubin.data());
+  auto* jc = new JitChain();
+  jc->n_in = n_in;
+  cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+  for (int i = 0; e == cudaSuccess && i < kSlots; ++i) {
+    const char* low = nullptr;
+    if (nv.lowered(prog, names[i].c_str(), &low) != NVRTC_SUCCESS || low == nullptr) {
+      e = cudaErrorSymbolNotFound;
+      break;
+    }
+    e = cudaLibraryGetKernel(&jc->k[i], jc->lib, low);
+  }
+  nv.destroy(&prog);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (jc->lib) cudaLibraryUnload(jc->lib);
+    delete jc;
+    return fail(TCAB_ERR_CUDA, "chain_reduce: loading the compiled kernels failed: %s", cudaGetErrorString(e));
+  }
+  *out = jc;
+  return TCAB_OK;
+}
+
+int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStream_t s, const char* what) {
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
+  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(static_cast<unsigned>(grid)),
+                                         dim3(block), args, 0, s);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
+}  // namespace
+
+bool jit_available() { return nvrtc().ok; }
+
+int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, void** handle) {
+  const std::string key = std::to_string(n_in) + "|" + std::to_string(combine) + "|" + map_text + "|" + post_text;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_cache.find(key);
+  if (it != g_cache.end()) {
+    *handle = it->second;
+    return TCAB_OK;
+  }
+  auto f = g_failed.find(key);
+  if (f != g_failed.end())
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: run-time compilation of map '%s' failed earlier: %s",
+                map_text.c_str(), f->second.c_str());
+  JitChain* jc = nullptr;
+  const int rc = compile(key, map_text, post_text, combine, n_in, &jc);
+  if (rc != TCAB_OK) return rc;
+  g_cache[key] = jc;
+  *handle = jc;
+  return TCAB_OK;
+}
+
+// Mirrors the ahead-of-time dispatch of chain_reduce.cu (launch_chain / launch_split / launch_outer).
+int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
+               const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s) {
+  // splits: CTAs per row for the split path (1 = none); top bit set = take the split path even with 1
+  JitChain* jc = static_cast<JitChain*>(handle);
+  tcabk::Caps caps;
+  for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
+  const float* ptrs[4] = {ins[0], jc->n_in > 1 ? ins[1] : ins[0], jc->n_in > 2 ? ins[2] : ins[0],
+                          jc->n_in > 3 ? ins[3] : ins[0]};  // Ptrs<NIN> is NIN pointers: a prefix of this array
+  bool al = true;
+  for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
+  if (inner == 1) {
+    const bool vec = al && (nk % 4 == 0);
+    const uint32_t nvec = vec ? nk / 4 : nk;
+    const bool force_split = (splits & 0x80000000u) != 0;  // the entry point that allocates nothing
+    splits &= 0x7fffffffu;
+    if ((splits > 1 || force_split) && split_scratch_or_null != nullptr) {
+      const uint32_t rows = static_cast<uint32_t>(outer);
+      uint32_t sp = splits > nvec ? (nvec ? nvec : 1) : splits;
+      uint32_t vec_per_split = (nvec + sp - 1) / sp;
+      void* a1[] = {ptrs, &split_scratch_or_null, &nk, &sp, &vec_per_split, &caps};
+      int rc = launch(jc->k[vec ? kSplitV4 : kSplitV1], static_cast<uint64_t>(rows) * sp, 256, a1, s, "chain_inner_split");
+      if (rc != TCAB_OK) return rc;
+      uint32_t rows32 = rows;
+      void* a2[] = {&split_scratch_or_null, &out, &rows32, &sp, &init, &caps};
+      return launch(jc->k[kFinish], (rows + 127) / 128, 128, a2, s, "chain_split_finish");
+    }
+    const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec <= 2048 ? 2 : 3;
+    const int tpr = t == 0 ? 1 : t == 1 ? 4 : t == 2 ? 32 : 256;
+    const int threads = tpr > 128 ? tpr : 128;
+    const uint64_t groups = threads / tpr;
+    void* a[] = {ptrs, &out, &outer, &nk, &init, &caps};
+    return launch(jc->k[(vec ? kInner1V4 : kInner1V1) + t], (outer + groups - 1) / groups, threads, a, s, "chain_inner");
+  }
+  if (inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
+  const bool vec = al && (inner % 4 == 0);
+  uint32_t nb = static_cast<uint32_t>(outer), nc = static_cast<uint32_t>(inner);
+  uint32_t tiles_per_b = (nc + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
+  const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
+  if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
+  void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps};
+  return launch(jc->k[vec ? kOuterV4 : kOuterV1], tiles, 256, a, s, "chain_outer");
+}
+
+}  // namespace tcab

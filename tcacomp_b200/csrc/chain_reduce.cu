@@ -273,13 +273,32 @@ int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc) {
       return TCAB_OK;
     }
   }
-  return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: no kernel in this build for map '%s' post '%s'", map.text.c_str(),
-              post_text.c_str());
+  // no ahead-of-time instance: compiled at run time on the first launch (chain_jit.cu)
+  pc->entry = kJitEntry;
+  pc->combine = cid;
+  pc->n_in = static_cast<int>(n_ins);
+  pc->map_text = map.text;
+  pc->post_text = post_text;
+  return TCAB_OK;
 }
 
 int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
                         uint64_t inner, float* out, cudaStream_t s) {
   if (outer == 0 || inner == 0) return TCAB_OK;
+  if (pc.entry == kJitEntry) {
+    void* h = nullptr;
+    const int rc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, &h);
+    if (rc != TCAB_OK) return rc;
+    uint32_t splits = 1;
+    float* scratch = nullptr;
+    if (inner == 1) {
+      bool al = true;
+      for (int i = 0; i < pc.n_in; ++i) al = al && aligned16(ins[i]);
+      splits = choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
+      if (splits > 1) scratch = split_scratch(s);
+    }
+    return jit_launch(h, ins, outer, nk, inner, pc.init, pc.caps, out, scratch, splits, s);
+  }
   Args a{ins, out, outer, nk, inner, pc.init, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
   return kTable[pc.entry].launch(a);
@@ -347,6 +366,13 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
   if (splits > by_len) splits = by_len;
   if (splits * rows > kNoAllocMaxPartials) splits = kNoAllocMaxPartials / rows;
   if (splits < 1) splits = 1;
+  if (pc.entry == kJitEntry) {
+    void* h = nullptr;
+    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, &h);
+    if (jrc != TCAB_OK) return jrc;
+    // the split kernels always: splits may be 1, the partials still pass through the fixed array
+    return jit_launch(h, ins, rows, nk, 1, pc.init, pc.caps, out, scratch, static_cast<uint32_t>(splits) | 0x80000000u, s);
+  }
   Args a{ins, out, rows, nk, 1, pc.init, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
   return kTable[pc.entry].launch_noalloc(a, scratch, static_cast<uint32_t>(splits));

@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string>
+
 #include "../../include/tcab.h"
 
 namespace tcab {
@@ -55,10 +57,19 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
                         uint32_t nk, uint32_t nc, cudaStream_t s);
 // A chain whose lambdas were validated, canonicalised and matched to a compiled kernel.
 struct PreparedChain {
-  int entry = -1;   // index into the table of compiled chains
+  int entry = -1;   // index into the table of ahead-of-time chains, or kJitEntry
   float init = 0.0f;
   float caps[16];   // map captures in [0,8), piped-map captures in [8,16)
+  // for a chain that has to be compiled at run time: its canonical lambdas
+  int combine = 0, n_in = 0;
+  std::string map_text, post_text;
 };
+constexpr int kJitEntry = -2;
+// Run-time compilation of chains without an ahead-of-time instance (chain_jit.cu).
+bool jit_available();
+int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, void** handle);
+int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
+               const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s);
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
 int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc);
 int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,

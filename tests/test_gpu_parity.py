@@ -378,7 +378,7 @@ def test_errors_through_the_python_host(cuda):
     with pytest.raises(ValueError, match="contiguous"):
         T.softmax_rows(x.t())
     with pytest.raises(T.TcabError) as e:
-        T.chain_reduce([x], "sinf(cosf(p0))")
+        T.chain_reduce([x], "p0", combine_expr="(p0 * p1)")  # a product reducer has no kernel
     assert e.value.status == T._lib.ERR_UNSUPPORTED
     n0 = T.launch_count()
     T.softmax_rows(x)
@@ -497,3 +497,57 @@ def test_split_reduction_with_piped_map_and_two_operands(oracle, cuda):
     s = ((x.astype(np.float64) ** 2) * z).sum(1)
     want = s / np.sqrt(s / 300000 + 1e-5)
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+
+
+# ----------------------------------------------------------------------------
+# lambdas without an ahead-of-time kernel: compiled at run time from the same kernel text
+# ----------------------------------------------------------------------------
+JIT_SUITE = {
+    # testing/kernels/dedup/dup_expr.tca and dup_const.tca, lambdas as the .tca files spell them
+    "dup_expr": ("((p0*p0 + p0*p0) * c0 + (p0*p0 + p0*p0) * c1) * p1", (1.5, 0.25), 1e-5),
+    "dup_const": ("(0.5f * (p0 + 0.5f * p0 * p0) * (1.0f + 0.044715f * p0) + tanhf(0.79788456f * (p0 + 0.044715f * p0)"
+                  " + 0.79788456f * 0.5f * p0) * (1.0f - 0.5f)) * p1", (), 1e-5),
+}
+
+
+@pytest.mark.parametrize("name", sorted(JIT_SUITE))
+def test_reference_suite_kernels_compiled_at_run_time(oracle, cuda, name):
+    expr, caps, tol = JIT_SUITE[name]
+    x, z = oracle.suite_inputs(name)
+    want = oracle.suite(name)
+    buf, out = guarded(want.shape, torch.float32, cuda)
+    T.chain_reduce([dev_f32(x, cuda), dev_f32(z, cuda)], expr, captures=caps, axis=2, out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert (got == CANARY).sum() == 0
+    assert np.abs(got.astype(np.float64) - want).max() <= tol
+    g = GOLDEN[name]
+    assert abs(got.astype(np.float64).sum() - g["checksum"]) <= 1e-5 * abs(g["checksum"])
+
+
+def test_run_time_compiled_lambdas_every_kernel_shape(oracle, cuda):
+    rng = np.random.default_rng(41)
+    expr, post = "sinf(p0) * cosf(p1) + c0", "sqrtf(fabsf(p0)) - c1"
+    f = lambda a, b: np.sin(a.astype(np.float64)) * np.cos(b.astype(np.float64)) + 0.5  # noqa: E731
+    # innermost axis at every group size, vector and scalar paths, the split path, and a middle axis
+    for shape, axis in [((300, 8), 1), ((50, 200), 1), ((20, 3000), 1), ((6, 20000), 1), ((9, 77), 1),
+                        ((2, 400000), 1), ((5, 40, 260), 1), ((3, 33, 50), 1), ((4, 10, 6), 0)]:
+        a = rng.uniform(-2, 2, shape).astype(np.float32)
+        b = rng.uniform(-2, 2, shape).astype(np.float32)
+        got = T.chain_reduce([dev_f32(a, cuda), dev_f32(b, cuda)], expr, post_expr=post, captures=(0.5, 0.25),
+                             axis=axis).cpu().numpy()
+        want = np.sqrt(np.abs(f(a, b).sum(axis))) - 0.25
+        scale = np.abs(f(a, b)).sum(axis)
+        assert (np.abs(got - want) <= 2e-5 * np.sqrt(scale) + 1e-5).all(), (shape, axis)
+    # max and min combiners, bit-exact against numpy on an exactly representable map
+    a = rng.integers(-50, 50, (17, 513)).astype(np.float32)
+    got = T.chain_reduce([dev_f32(a, cuda)], "p0 * 0.5f - 3.0f", combine_expr="fminf(p0, p1)", init=np.inf).cpu().numpy()
+    assert np.array_equal(got, (a * 0.5 - 3.0).min(1).astype(np.float32))
+    # a lambda the validator refuses never reaches the compiler
+    with pytest.raises(T.TcabError) as e:
+        T.chain_reduce([dev_f32(a, cuda)], "p0); } __global__ void k() { (void)(0")
+    assert e.value.status == T._lib.ERR_INVALID_ARG
+    # the entry point that allocates nothing runs compiled lambdas too
+    out = torch.empty((17,), device=cuda)
+    T.chain_reduce_noalloc([dev_f32(a, cuda)], "cosf(p0) * cosf(p0)", out=out)
+    assert np.allclose(out.cpu().numpy(), (np.cos(a.astype(np.float64)) ** 2).sum(1), rtol=1e-5)
