@@ -147,6 +147,18 @@ TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, 
 TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                                        const tcab_tensor* out, void* stream);
 
+/* Contraction chain over fp32 operands indexed by different dim subsets:
+ *   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )   rhs_is_nk == 0, rhs is [K,N]
+ *   out[m,n] = post( fold_k map(lhs[m,k], rhs[n,k]) )   rhs_is_nk != 0, rhs is [N,K]
+ * with the lambdas of tcab_chain (map over p0 = the lhs value, p1 = the rhs value). Replaces the emitted
+ * matmul-shaped kernels of the reference's suite (testing/kernels/llm/gemm.tca, llm/qk_score.tca,
+ * tiling/mm_small.tca, mm_mid.tca, mm_splitk.tca, fusion/mlp.tca; launcher form
+ * internal/cg/cxx/launch.go:23-156). Each output is folded over k in ascending order, the order of the
+ * reference's CPU loops (testing/runners/gemm.cu:44-56). SIMT fp32: the tensor-core path is
+ * tcab_gemm_bias_act, which takes bf16 operands. */
+TCAB_API int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs,
+                                 int rhs_is_nk, const tcab_tensor* out, void* stream);
+
 /* Outer-axis reduce of t[b, k, c] over k in ONE pass: any of sum (fp32), max (fp32) and argmax
  * (int32, lowest index among equal maxima) may be NULL. Each output is [b, c].
  * The reference's class: the middle-axis kernels of testing/kernels/runtime/row_sum.tca:18-33 and

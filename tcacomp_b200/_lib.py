@@ -52,6 +52,8 @@ SYMBOLS = [
      [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_chain_reduce_noalloc", C.c_int,
      [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
+    ("tcab_chain_contract", C.c_int,
+     [C.POINTER(Chain), C.POINTER(Tensor), C.POINTER(Tensor), C.c_int, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_reduce_outer", C.c_int,
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),
     ("tcab_softmax_rows", C.c_int, [C.POINTER(Tensor), C.POINTER(Tensor), C.c_void_p]),

@@ -357,6 +357,36 @@ int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, u
                                      static_cast<cudaStream_t>(stream));
 }
 
+int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs, int rhs_is_nk,
+                        const tcab_tensor* out, void* stream) {
+  const char* op = "chain_contract";
+  if (chain == nullptr || chain->map_expr == nullptr || chain->combine_expr == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: chain, map_expr and combine_expr are required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  TCAB_TRY(check_tensor(op, "lhs", lhs));
+  TCAB_TRY(check_tensor(op, "rhs", rhs));
+  TCAB_TRY(check_tensor(op, "out", out));
+  TCAB_TRY(need_dtype(op, "lhs", lhs, TCAB_F32, "f32"));
+  TCAB_TRY(need_dtype(op, "rhs", rhs, TCAB_F32, "f32"));
+  TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
+  if (lhs->rank != 2 || rhs->rank != 2 || out->rank != 2)
+    return fail(TCAB_ERR_SHAPE, "%s: lhs, rhs and out must be rank 2", op);
+  const uint32_t m = lhs->dims[0], k = lhs->dims[1];
+  const uint32_t rk = rhs_is_nk ? rhs->dims[1] : rhs->dims[0], n = rhs_is_nk ? rhs->dims[0] : rhs->dims[1];
+  if (rk != k) return fail(TCAB_ERR_SHAPE, "%s: rhs.Dim(%d) must equal lhs.Dim(1) (dim k)", op, rhs_is_nk ? 1 : 0);
+  if (out->dims[0] != m || out->dims[1] != n) return fail(TCAB_ERR_SHAPE, "%s: out must be [%u, %u]", op, m, n);
+  TCAB_TRY(need_elem_align(op, "lhs", lhs, 4));
+  TCAB_TRY(need_elem_align(op, "rhs", rhs, 4));
+  TCAB_TRY(need_elem_align(op, "out", out, 4));
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, 2, &pc));
+  TCAB_TRY(have_device(op));
+  return launch_chain_contract(pc, static_cast<const float*>(lhs->data), static_cast<const float*>(rhs->data),
+                               rhs_is_nk ? 1 : 0, static_cast<float*>(out->data), m, n, k,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias, int act,
                        const tcab_tensor* c, void* stream) {
   const char* op = "gemm_bias_act";

@@ -70,7 +70,7 @@ const Nvrtc& nvrtc() {
 // The kernels one chain needs, in the order of JitChain::k.
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
-  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kSlots
+  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kSlots
 };
 
 struct JitChain {
@@ -120,6 +120,12 @@ int compile(const std::string& key, const std::string& map_text, const std::stri
   names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
   names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4>";
   names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4>";
+  if (n_in == 2) {
+    names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0>";
+    names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1>";
+  } else {
+    names.resize(kContractKN);
+  }
 
   nvrtcProgram prog = nullptr;
   if (nv.create(&prog, src.c_str(), "tcab_chain_jit.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
@@ -144,7 +150,7 @@ int compile(const std::string& key, const std::string& map_text, const std::stri
   auto* jc = new JitChain();
   jc->n_in = n_in;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
-  for (int i = 0; e == cudaSuccess && i < kSlots; ++i) {
+  for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
     const char* low = nullptr;
     if (nv.lowered(prog, names[i].c_str(), &low) != NVRTC_SUCCESS || low == nullptr) {
       e = cudaErrorSymbolNotFound;
@@ -241,6 +247,24 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
   void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps};
   return launch(jc->k[vec ? kOuterV4 : kOuterV1], tiles, 256, a, s, "chain_outer");
+}
+
+int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
+                        uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s) {
+  JitChain* jc = static_cast<JitChain*>(handle);
+  if (jc->n_in != 2 || jc->k[kContractKN] == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "chain_contract: the map lambda must take exactly two operands");
+  tcabk::Caps caps;
+  for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
+  void* a[] = {&lhs, &rhs, &out, &m, &n, &k, &init, &caps};
+  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(jc->k[rhs_nk ? kContractNK : kContractKN]),
+                                         dim3((n + 63) / 64, (m + 63) / 64), dim3(256), a, 0, s);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "chain_contract: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
 }
 
 }  // namespace tcab

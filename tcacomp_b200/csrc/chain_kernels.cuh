@@ -252,4 +252,79 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
   }
 }
 
+// Contraction of two fp32 operands indexed by different dim subsets (the reference's matmul-shaped
+// chains: testing/kernels/llm/gemm.tca, tiling/mm_*.tca, fusion/mlp.tca, llm/qk_score.tca):
+//   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )         RHS_NK == 0, rhs is [K,N]
+//   out[m,n] = post( fold_k map(lhs[m,k], rhs[n,k]) )         RHS_NK == 1, rhs is [N,K]
+// A CTA owns a 64x64 output tile, a thread a 4x4 block of it; K advances in shared-memory tiles
+// of 16. Each output is folded over k in ascending order by one thread -- the order of the
+// reference's CPU loops (testing/runners/gemm.cu:44-56). Rows and columns past the edge are
+// computed on zero padding and never stored; k past the edge never reaches the lambda.
+template <class Map, class Post, int COMBINE, int RHS_NK>
+__global__ void __launch_bounds__(256)
+chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, float* __restrict__ out, u32 M, u32 N,
+               u32 K, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const u32 m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = C::identity();
+
+  for (u32 k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      {  // A: 64 rows x 16 k, k fastest in memory
+        const int r = idx >> 4, c = idx & 15;
+        const bool ok = (m0 + r < M) && (k0 + c < K);
+        As[c][r] = ok ? lhs[static_cast<u64>(m0 + r) * K + k0 + c] : 0.0f;
+      }
+      if (RHS_NK) {  // B as [N,K]: 64 n x 16 k, k fastest in memory
+        const int c = idx >> 4, r = idx & 15;
+        const bool ok = (n0 + c < N) && (k0 + r < K);
+        Bs[r][c] = ok ? rhs[static_cast<u64>(n0 + c) * K + k0 + r] : 0.0f;
+      } else {       // B as [K,N]: 16 k x 64 n, n fastest in memory
+        const int r = idx >> 6, c = idx & 63;
+        const bool ok = (k0 + r < K) && (n0 + c < N);
+        Bs[r][c] = ok ? rhs[static_cast<u64>(k0 + r) * N + n0 + c] : 0.0f;
+      }
+    }
+    __syncthreads();
+    const int kmax = (K - k0 < static_cast<u32>(BK)) ? static_cast<int>(K - k0) : BK;
+    for (int kk = 0; kk < kmax; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float p[2] = {a[i], b[j]};
+          acc[i][j] = C::apply(acc[i][j], Map::apply(p, caps.c));
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const u32 m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const u32 n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      const float r[1] = {C::apply(init, acc[i][j])};
+      out[static_cast<u64>(m) * N + n] = Post::apply(r, caps.c + 8);
+    }
+  }
+}
+
 }  // namespace tcabk

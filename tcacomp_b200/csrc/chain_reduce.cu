@@ -305,6 +305,53 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
 }
 
 // ---------------------------------------------------------------------------
+// fp32 contraction chains
+// ---------------------------------------------------------------------------
+namespace {
+
+template <class Map, class Post, int COMBINE>
+int launch_contract_aot(const float* lhs, const float* rhs, float* out, uint32_t m, uint32_t n, uint32_t k,
+                        int rhs_nk, float init, const Caps& caps, cudaStream_t s) {
+  const dim3 grid((n + 63) / 64, (m + 63) / 64);
+  if (rhs_nk)
+    tcabk::chain_contract<Map, Post, COMBINE, 1><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+  else
+    tcabk::chain_contract<Map, Post, COMBINE, 0><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+  count_launch();
+  return check_launch("chain_contract");
+}
+
+}  // namespace
+
+int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,
+                          uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
+  if (m == 0 || n == 0) return TCAB_OK;
+  if ((n + 63) / 64 > 65535u * 64u || (m + 63) / 64 > 65535u)
+    return fail(TCAB_ERR_TOO_LARGE, "chain_contract: more than 65535 row tiles");
+  Caps caps;
+  for (int i = 0; i < 16; ++i) caps.c[i] = pc.caps[i];
+  // ahead-of-time: the plain product with a sum reducer, stored as it is or scaled
+  if (pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text()) {
+    const std::string post = kTable[pc.entry].post;
+    if (post.empty())
+      return launch_contract_aot<MapMul2, tcabk::PostNone, 0>(lhs, rhs, out, m, n, k, rhs_nk, pc.init, caps, s);
+    if (post == PostScale::text())
+      return launch_contract_aot<MapMul2, PostScale, 0>(lhs, rhs, out, m, n, k, rhs_nk, pc.init, caps, s);
+  }
+  std::string map_text = pc.map_text, post_text = pc.post_text;
+  int combine = pc.combine;
+  if (pc.entry >= 0) {  // in the reduce table but without a contraction instance: compile it
+    map_text = kTable[pc.entry].map;
+    post_text = kTable[pc.entry].post;
+    combine = kTable[pc.entry].combine;
+  }
+  void* h = nullptr;
+  const int rc = jit_prepare(map_text, post_text, combine, 2, &h);
+  if (rc != TCAB_OK) return rc;
+  return jit_launch_contract(h, lhs, rhs, rhs_nk, out, m, n, k, pc.init, pc.caps, s);
+}
+
+// ---------------------------------------------------------------------------
 // The entry point that allocates nothing
 // ---------------------------------------------------------------------------
 // Scratch for the split path when the caller cannot let the library allocate: a fixed array in

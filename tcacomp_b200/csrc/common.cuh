@@ -80,6 +80,10 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
 
 int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins, uint64_t rows, uint32_t nk,
                                 float* out, cudaStream_t s);
+int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
+                        uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s);
+int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,
+                          uint32_t m, uint32_t n, uint32_t k, cudaStream_t s);
 int gemm_device_status(int* out);  // status word of the contraction kernel (synchronous read)
 
 // ---------------------------------------------------------------------------

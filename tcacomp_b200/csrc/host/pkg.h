@@ -288,13 +288,14 @@ Tail AfterMap::As(D... dims) { return AsV(std::vector<Dim>{dims...}); }
 std::string PrintLambda(const Expr& body, std::vector<std::string>* captures);
 
 struct Plan {
-  enum Kind { ChainReduce, GemmBiasAct } kind = ChainReduce;
+  enum Kind { ChainReduce, ChainContract, GemmBiasAct } kind = ChainReduce;
   // ChainReduce
   std::string map_expr, combine_expr, post_expr;
   float init = 0.0f;
   std::vector<std::string> capture_names;  // scalar parameter of capture slot i
   std::vector<std::string> inputs;         // tensor names, in operand order
   uint32_t reduce_axis = 0;                // position of the reduced dim in the operands
+  bool rhs_is_nk = false;                  // ChainContract: the second operand is [n,k] rather than [k,n]
   // GemmBiasAct
   std::string a, b, bias;                  // bias empty = none
   int act = TCAB_ACT_NONE;

@@ -143,8 +143,38 @@ Result<Plan> Classify(const Statement& st) {
   Result<Plan> r;
   if (match_gemm(st, &r.value)) return r;
 
-  // fp32 map | reduce | [map] over identically indexed operands
   Plan& p = r.value;
+  // fp32 contraction: lhs[m,k] with rhs[k,n] or rhs[n,k], as (m, n, k), out[m,n], piped map without operands
+  if (st.operands.size() == 2 && st.reduces.size() == 1 && st.as.size() == 3 && st.iters.size() == 3 &&
+      st.operands[0].t.elem == Elem::F32 && st.operands[1].t.elem == Elem::F32 && st.operands[0].axes.size() == 2 &&
+      st.operands[1].axes.size() == 2 && st.out.elem == Elem::F32 && st.elem == Elem::F32 &&
+      (!st.has_post || st.post_operands.empty())) {
+    const std::string m = st.as[0].name, n = st.as[1].name, k = st.as[2].name;
+    const auto& la = st.operands[0].axes;
+    const auto& ra = st.operands[1].axes;
+    const bool kn = ra[0].name == k && ra[1].name == n, nk = ra[0].name == n && ra[1].name == k;
+    if (la[0].name == m && la[1].name == k && (kn || nk) && st.out_axes.size() == 2 && st.out_axes[0].name == m &&
+        st.out_axes[1].name == n && st.reduces[0].init.node && st.reduces[0].init.node->kind == Node::Const) {
+      p.kind = Plan::ChainContract;
+      p.rhs_is_nk = nk;
+      p.init = static_cast<float>(st.reduces[0].init.node->value);
+      std::string err;
+      std::vector<std::string> none;
+      p.map_expr = print_node(*st.map_body.node, &p.capture_names, &err);
+      if (err.empty()) p.combine_expr = print_node(*st.reduces[0].body.node, &none, &err);
+      if (err.empty() && !none.empty()) err = "a combiner may not capture scalar parameters";
+      if (err.empty() && st.has_post) p.post_expr = print_node(*st.post_body.node, &p.capture_names, &err);
+      if (!err.empty()) {
+        r.err = "classify: " + err;
+        return r;
+      }
+      p.inputs = {st.operands[0].t.name, st.operands[1].t.name};
+      p.out = st.out.name;
+      return r;
+    }
+  }
+
+  // fp32 map | reduce | [map] over identically indexed operands
   p.kind = Plan::ChainReduce;
   if (st.reduces.size() != 1) {
     r.err = "classify: " + std::to_string(st.reduces.size()) +
@@ -307,7 +337,10 @@ int Launch(const Graph& g, const Bindings& bind, void* stream) {
         return fail(TCAB_ERR_INVALID_ARG, "launch: scalar " + p.capture_names[i] + " is not bound");
       ch.captures[i] = it->second;
     }
-    rc = tcab_chain_reduce(&ch, ins, static_cast<uint32_t>(p.inputs.size()), p.reduce_axis, &out, stream);
+    if (p.kind == Plan::ChainContract)
+      rc = tcab_chain_contract(&ch, &ins[0], &ins[1], p.rhs_is_nk ? 1 : 0, &out, stream);
+    else
+      rc = tcab_chain_reduce(&ch, ins, static_cast<uint32_t>(p.inputs.size()), p.reduce_axis, &out, stream);
     if (rc != TCAB_OK) return fail(rc, tcab_last_error());
   }
   return TCAB_OK;

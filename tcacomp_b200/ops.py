@@ -178,6 +178,29 @@ def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.
     return out
 
 
+def chain_contract(lhs: torch.Tensor, rhs: torch.Tensor, map_expr: str = "(p0 * p1)", rhs_is_nk: bool = False,
+                   combine_expr: str = "(p0 + p1)", init: float = 0.0, post_expr: Optional[str] = None,
+                   captures: Sequence[float] = (), out: Optional[torch.Tensor] = None,
+                   stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """out[m,n] = post(fold_k map(lhs[m,k], rhs[k,n]))  (rhs[n,k] with rhs_is_nk), fp32."""
+    n = rhs.shape[0] if rhs_is_nk else rhs.shape[1]
+    if out is None:
+        out = torch.empty((lhs.shape[0], n), device=lhs.device, dtype=torch.float32)
+    chain = _lib.Chain()
+    chain.map_expr = map_expr.encode()
+    chain.combine_expr = combine_expr.encode()
+    chain.post_expr = post_expr.encode() if post_expr else None
+    chain.init = init
+    chain.n_captures = len(captures)
+    for i, c in enumerate(captures):
+        chain.captures[i] = c
+    lv, rv, ov = _view(lhs, "lhs"), _view(rhs, "rhs"), _view(out, "out")
+    with _on_device(lhs):
+        _lib.check(_lib.load().tcab_chain_contract(C.byref(chain), C.byref(lv), C.byref(rv), int(bool(rhs_is_nk)),
+                                                   C.byref(ov), _stream(stream, lhs)))
+    return out
+
+
 def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   act: str = "relu", out: Optional[torch.Tensor] = None,
                   stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:

@@ -61,9 +61,11 @@ static void test_matmul_scale_builds() {
   auto g = b.Build();
   CHECK(g.ok());
   CHECK(g.value.statements.size() == 1);
-  // the chain is a contraction of fp32 operands: it builds, and the classifier says which class is missing
+  // a contraction of fp32 operands: lhs[m,n] with rhs[n,k], reduced over n, piped scale
   auto plan = Classify(g.value.statements[0]);
-  CHECK(!plan.ok() && contains(plan.err, "different index sets"));
+  CHECK(plan.ok() && plan.value.kind == Plan::ChainContract && !plan.value.rhs_is_nk);
+  CHECK(plan.value.map_expr == "(p0 * p1)" && plan.value.post_expr == "(p0 * c0)");
+  CHECK(plan.value.capture_names.size() == 1 && plan.value.capture_names[0] == "scale");
 }
 
 // pkg/builder_test.go:21-160
@@ -483,6 +485,32 @@ static bool gpu_tests() {
     ok &= st.ok() && g.ok() &&
           run_and_report("RowSumE2E", g.value, {{"lhs", view(TCAB_F32, {1024, 512})}, {"out", view(TCAB_F32, {1024})}},
                          {h.data(), nullptr}, {}, "out", ref, false);
+  }
+  {  // pkg/oracle_test.go:17-63 + internal/e2e/frontend_test.go:33-34,194-209: matmul_scale, 64 x 128 x 64, scale 1.5
+    const unsigned M = 64, N = 128, Q = 64;
+    Builder b("MatmulScale");
+    Dim m = b.Dim("m", 0), k = b.Dim("k", 0), n = b.Dim("n", 0);
+    Tensor lhs = b.Tensor("lhs", Elem::F32, m, n), rhs = b.Tensor("rhs", Elem::F32, n, k);
+    Tensor out = b.Tensor("output", Elem::F32, m, k);
+    Expr scale = b.ScalarParam("scale", Elem::F32);
+    auto root = b.Stmt().Iter(m, k, n).Map({At(lhs, m, n), At(rhs, n, k)}, [&](Expr l, Expr r) { return b.Mul(l, r); });
+    auto ar = root.value.As(m, k, n).Reduce(b.Float32(0.0f), [&](Expr acc, Expr v) { return b.Add(acc, v); });
+    auto am = ar.value.Map({}, [&](Expr v) { return b.Mul(v, scale); });
+    auto st = am.value.As(m, k).Store(out, m, k);
+    auto g = b.Build();
+    std::vector<float> hl(M * N), hr(N * Q), ref(M * Q);
+    for (unsigned i = 0; i < M * N; ++i) hl[i] = elem(i);
+    for (unsigned i = 0; i < N * Q; ++i) hr[i] = elem(i);
+    for (unsigned mi = 0; mi < M; ++mi)
+      for (unsigned qi = 0; qi < Q; ++qi) {
+        float acc = 0.0f;
+        for (unsigned ni = 0; ni < N; ++ni) acc += hl[mi * N + ni] * hr[ni * Q + qi];
+        ref[mi * Q + qi] = acc * 1.5f;
+      }
+    ok &= st.ok() && g.ok() &&
+          run_and_report("MatmulScale", g.value,
+                         {{"lhs", view(TCAB_F32, {M, N})}, {"rhs", view(TCAB_F32, {N, Q})}, {"output", view(TCAB_F32, {M, Q})}},
+                         {hl.data(), hr.data(), nullptr}, {{"scale", 1.5f}}, "output", ref, false);
   }
   {  // the bf16 contraction with bias + ReLU, built through the rungs
     const unsigned M = 256, K = 512, N = 256;

@@ -551,3 +551,61 @@ def test_run_time_compiled_lambdas_every_kernel_shape(oracle, cuda):
     out = torch.empty((17,), device=cuda)
     T.chain_reduce_noalloc([dev_f32(a, cuda)], "cosf(p0) * cosf(p0)", out=out)
     assert np.allclose(out.cpu().numpy(), (np.cos(a.astype(np.float64)) ** 2).sum(1), rtol=1e-5)
+
+
+# ----------------------------------------------------------------------------
+# the reference's matmul-shaped suite kernels: fp32 contraction chains
+# ----------------------------------------------------------------------------
+GELU = "0.5f*p0*(1.0f + tanhf(0.79788456f*(p0 + 0.044715f*p0*p0*p0)))"   # testing/kernels/fusion/mlp.tca
+CONTRACT_SUITE = {
+    # name: (rhs_is_nk, post, captures)  -- tolerance 2e-3 for all of them (testing/suite.toml)
+    "mm_small": (False, None, ()), "mm_mid": (False, None, ()), "mm_splitk": (False, None, ()),
+    "gemm": (False, None, ()), "mlp": (False, GELU, ()), "qk_score": (True, "p0 * c0", (0.125,)),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CONTRACT_SUITE))
+def test_reference_suite_contractions(oracle, cuda, name):
+    nk, post, caps = CONTRACT_SUITE[name]
+    x, z = oracle.suite_inputs(name)
+    want = oracle.suite(name)
+    buf, out = guarded(want.shape, torch.float32, cuda)
+    T.chain_contract(dev_f32(x, cuda), dev_f32(z, cuda), "(p0 * p1)", rhs_is_nk=nk, post_expr=post, captures=caps,
+                     out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert (got == CANARY).sum() == 0
+    assert np.abs(got.astype(np.float64) - want).max() <= 2e-3
+    g = GOLDEN[name]
+    assert abs(got.astype(np.float64).sum() - g["checksum"]) <= 1e-5 * abs(g["checksum"])
+
+
+def test_e2e_matmul_scale_fixture(oracle, cuda):
+    # internal/e2e/frontend_test.go:33-34,194-209: 64 x 128 x 64, scale 1.5, tolerance 2e-3
+    a = oracle.elem_fill(64 * 128).reshape(64, 128)
+    b = oracle.elem_fill(128 * 64).reshape(128, 64)
+    got = T.chain_contract(dev_f32(a, cuda), dev_f32(b, cuda), post_expr="p0 * c0", captures=(1.5,)).cpu().numpy()
+    assert np.abs(got - oracle.matmul_scale_f32(a, b, 1.5)).max() <= 2e-3
+    g = GOLDEN["e2e_matmul_scale_64x128x64"]
+    assert abs(got.astype(np.float64).sum() - g["checksum"]) <= 1e-5 * g["checksum"]
+
+
+def test_contraction_ragged_and_other_combiners(oracle, cuda):
+    rng = np.random.default_rng(23)
+    for m, k, n in [(1, 1, 1), (65, 17, 130), (200, 300, 7), (64, 0, 64)]:
+        a = rng.normal(0, 1, (m, k)).astype(np.float32)
+        b = rng.normal(0, 1, (k, n)).astype(np.float32)
+        got = T.chain_contract(dev_f32(a, cuda), dev_f32(b, cuda)).cpu().numpy()
+        want = oracle.matmul_scale_f32(a, b, 1.0) if k else np.zeros((m, n), np.float32)
+        assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+        gt = T.chain_contract(dev_f32(a, cuda), dev_f32(np.ascontiguousarray(b.T), cuda), rhs_is_nk=True).cpu().numpy()
+        assert np.abs(gt - want).max() <= 1e-5 * max(1.0, np.abs(want).max())
+    # a max-plus contraction (tropical product): out[m,n] = max_k (a[m,k] + b[k,n]), order-independent
+    a = rng.integers(-9, 9, (70, 33)).astype(np.float32)
+    b = rng.integers(-9, 9, (33, 45)).astype(np.float32)
+    got = T.chain_contract(dev_f32(a, cuda), dev_f32(b, cuda), "p0 + p1", combine_expr="fmaxf(p0, p1)",
+                           init=-np.inf).cpu().numpy()
+    assert np.array_equal(got, (a[:, :, None] + b[None, :, :]).max(1))
+    with pytest.raises(T.TcabError) as e:
+        T.chain_contract(dev_f32(a, cuda), dev_f32(a, cuda))
+    assert e.value.status == T._lib.ERR_SHAPE and "dim k" in e.value.message

@@ -15,7 +15,7 @@ OUT = os.path.join(ROOT, "tests", "cpp", "_build")
 
 # testing/suite.toml tolerances (max abs diff); the e2e row sum uses internal/e2e/e2e_test.go:15-21
 TOL = {"RowSum": 2e-3, "Softmax": 2e-3, "Transpose": 1e-5, "ScaleCopy": 1e-5, "Axpy3": 1e-5, "Layernorm": 1e-5,
-       "RowSumE2E": 2e-3, "GemmBiasRelu": 2e-2}
+       "RowSumE2E": 2e-3, "MatmulScale": 2e-3, "GemmBiasRelu": 2e-2}
 
 
 def build_binary(with_cuda: bool) -> str:
