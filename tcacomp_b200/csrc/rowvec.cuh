@@ -116,6 +116,15 @@ __device__ __forceinline__ float group_allreduce(float v, float* slots, int g) {
 // so that short rows still fill a CTA with several rows.
 __host__ __device__ constexpr int row_cta_threads(int tpr) { return tpr > 128 ? tpr : 128; }
 
+// Resident CTAs per SM to ask the compiler for. While a thread holds at most `limit` row values the
+// kernel fits 48 registers, which lets 1280 threads (five 256-thread CTAs) share an SM instead of
+// 1024: measured on B200, layer-norm over bf16 [65536, 8192] goes from 6.2 to 6.6 TB/s. Wider
+// per-thread rows are left unconstrained (the cap would spill).
+__host__ __device__ constexpr int row_min_ctas(int tpr, int values_per_thread, int limit, int threads_per_sm = 1280) {
+  return values_per_thread <= limit && row_cta_threads(tpr) <= threads_per_sm ? threads_per_sm / row_cta_threads(tpr)
+                                                                              : 1;
+}
+
 // Launch shape for a register-resident row: the smallest group (power of two,
 // 8..1024 threads) whose threads hold at most `vpt_target` vectors each, and
 // the power-of-two vector count per thread that then covers the row.

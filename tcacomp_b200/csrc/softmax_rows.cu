@@ -23,7 +23,7 @@ namespace tcab {
 namespace {
 
 template <int TPR, int VPT, int V>
-__global__ void __launch_bounds__(row_cta_threads(TPR))
+__global__ void __launch_bounds__(row_cta_threads(TPR), row_min_ctas(TPR, VPT * V, 16, 1536))
 softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols) {
   constexpr int THREADS = row_cta_threads(TPR);
   constexpr int GROUPS = THREADS / TPR;
