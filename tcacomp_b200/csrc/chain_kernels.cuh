@@ -96,6 +96,11 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   const int t = threadIdx.x % TPR;
   const u32 nvec = nk / V;
   u32 iter = 0;
+  // Programmatic dependent launch: when the launcher allowed this grid to start before the previous
+  // grid of the stream has finished, wait here (before the first global access) until it has, and let
+  // the next grid of the stream begin its own launch now. Both are no-ops for an ordinary launch.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   for (u64 row0 = static_cast<u64>(blockIdx.x) * GROUPS; row0 < rows;
        row0 += static_cast<u64>(gridDim.x) * GROUPS, ++iter) {

@@ -73,9 +73,25 @@ int launch_inner(const Args& a) {
   // one CTA per group of rows; the kernel's row loop only matters beyond 2^31 - 1 CTAs
   const uint64_t need = (a.outer + GROUPS - 1) / GROUPS;
   const uint64_t grid = need > 0x7fffffffull ? 0x7fffffffull : need;
-  fn<<<static_cast<unsigned>(grid), THREADS, 0, a.stream>>>(ptrs, a.out, a.outer, a.nk, a.init, a.caps);
+  // Programmatic dependent launch: the grid may be scheduled while the previous kernel of the stream
+  // drains (the kernel itself waits for it before touching memory), which hides most of the launch
+  // gap between back-to-back small reductions. tune("reduce_inner", _, _, 2) switches it off.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tune(kReduceInner).p2 == 2 ? 0 : 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, ptrs, a.out, a.outer, a.nk, a.init, a.caps);
   count_launch();
-  return check_launch("chain_inner");
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "chain_inner: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
 }
 
 template <class Map, class Post, int COMBINE, int V>

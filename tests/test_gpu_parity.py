@@ -609,3 +609,31 @@ def test_contraction_ragged_and_other_combiners(oracle, cuda):
     with pytest.raises(T.TcabError) as e:
         T.chain_contract(dev_f32(a, cuda), dev_f32(a, cuda))
     assert e.value.status == T._lib.ERR_SHAPE and "dim k" in e.value.message
+
+
+# ----------------------------------------------------------------------------
+# host buffers: H2D, kernel and D2H pipelined over row chunks
+# ----------------------------------------------------------------------------
+def test_row_pipeline_matches_direct_call(oracle, cuda):
+    from tcacomp_b200.pipeline import RowPipeline
+    rng = np.random.default_rng(8)
+    x = (4 * rng.normal(0, 1, (1000, 512))).astype(np.float32)   # 1000 rows in chunks of 96: a ragged last chunk
+    hx = torch.from_numpy(x).pin_memory()
+    hy = torch.full_like(hx, CANARY).pin_memory()
+    pipe = RowPipeline(cuda, 96, (512,), torch.float32, {"y": ((512,), torch.float32)}, depth=3)
+    for _ in range(2):  # twice: the staging slots are reused
+        pipe.run(hx, {"y": hy}, lambda din, dout: T.softmax_rows(din, out=dout["y"]))
+    torch.cuda.current_stream(cuda).synchronize()
+    direct = T.softmax_rows(hx.to(cuda)).cpu()
+    assert torch.equal(hy, direct)
+    # several outputs per chunk (outer-axis reduce over batch chunks)
+    t = rng.uniform(-100, 100, (10, 64, 96)).astype(np.float32)
+    ht = torch.from_numpy(t).pin_memory()
+    ho = {"sum": torch.empty((10, 96)).pin_memory(), "max": torch.empty((10, 96)).pin_memory(),
+          "argmax": torch.empty((10, 96), dtype=torch.int32).pin_memory()}
+    p2 = RowPipeline(cuda, 3, (64, 96), torch.float32, {"sum": ((96,), torch.float32), "max": ((96,), torch.float32),
+                                                      "argmax": ((96,), torch.int32)})
+    p2.run(ht, ho, lambda din, dout: T.reduce_outer(din, out=dout))
+    torch.cuda.current_stream(cuda).synchronize()
+    s, m, a = oracle.reduce_outer(t)
+    assert np.array_equal(ho["argmax"].numpy(), a) and np.array_equal(ho["max"].numpy(), m)
