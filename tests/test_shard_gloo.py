@@ -64,3 +64,47 @@ def test_two_rank_partition_matches_single_rank():
         p.join(60)
         assert p.exitcode == 0
     assert ok and tmax == 2.0
+
+
+def _sharded_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import binding as O
+        from tcacomp_b200.shard import block
+        from tcacomp_b200.sharded import combine_partials
+        rng = np.random.default_rng(5)
+        t = rng.integers(-4, 5, (3, 40, 17)).astype(np.float32)   # many equal maxima across the two shards
+        t[0, :, 0] = 2.0                 # a tie spanning both shards: global index 0 must win
+        t[1, 25:, 1] = 9.0               # the maximum lives only in the second shard
+        t[2, :, 2] = -np.inf             # -inf everywhere: index 0
+        t[2, 3, 3] = np.nan              # a NaN never wins
+        lo, hi = block(t.shape[1], world, rank)
+        s, m, a = O.reduce_outer(np.ascontiguousarray(t[:, lo:hi]))   # the oracle stands in for the device kernel
+        part = {"sum": torch.from_numpy(s), "max": torch.from_numpy(m), "argmax": torch.from_numpy(a)}
+        out = combine_partials(part, lo)
+        if rank == 0:
+            fs, fm, fa = O.reduce_outer(t)
+            ok_idx = np.array_equal(out["argmax"].numpy(), fa)
+            ok_max = np.array_equal(out["max"].numpy(), fm)
+            both = np.isfinite(fs)
+            ok_sum = np.array_equal(out["sum"].numpy()[both], fs[both])   # small integers: exact in any order
+            q.put((ok_idx, ok_max, ok_sum))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reduction_along_the_sharded_axis_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_sharded_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=120)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert res == (True, True, True)
