@@ -259,6 +259,224 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = 1;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same contraction on CTA PAIRS (cta_group::2): a cluster of two CTAs owns a 512x256 output
+// tile. Each tcgen05.mma has M = 256 -- 128 rows in each CTA's TMEM -- and N = 256; every CTA loads
+// only ITS rows of A and ITS half of B's columns (the tensor cores read the other half from the
+// peer's shared memory), so a K block costs a CTA 48 KB instead of 64 KB for the same 8.4 MFLOP and
+// the ring holds four stages instead of three. Only the leader CTA (cluster rank 0) issues MMAs; its
+// commits arrive on the barriers of both CTAs. No load has more than one destination.
+// ---------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 4;
+constexpr int P_A_STAGE_BYTES = 2 * UMMA_M * 128;   // this CTA's 128 rows of both accumulators: 32 KB
+constexpr int P_B_STAGE_BYTES = BK * (BN / 2) * 2;  // this CTA's 128 columns of B: 16 KB (2 boxes)
+constexpr int P_STAGE_BYTES = P_A_STAGE_BYTES + P_B_STAGE_BYTES;
+constexpr int P_BM = 512;
+constexpr size_t P_SMEM_BYTES = static_cast<size_t>(P_STAGES) * P_STAGE_BYTES + EPI_WARPS * EPI_BOX_BYTES + 1024;
+
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
+                          uint32_t N, uint32_t K, int act) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[P_STAGES];    // used in the leader: bytes of BOTH CTAs land here
+  __shared__ __align__(8) uint64_t bar_empty[P_STAGES];   // in each CTA: the leader's commit arrives on both
+  __shared__ __align__(8) uint64_t bar_tmem_full;         // in each CTA
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];     // used in the leader: epilogue warps of both CTAs arrive
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const bool leader = rank == 0;
+  volatile int* abort_p = &abort_flag;
+
+  const uint32_t tiles_m = (M + P_BM - 1) / P_BM, tiles_n = (N + BN - 1) / BN;
+  const uint32_t num_tiles = tiles_m * tiles_n;
+  const uint32_t num_kb = (K + BK - 1) / BK;
+  const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < P_STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[0]), 2 * EPI_WARPS);
+    ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[1]), 2 * EPI_WARPS);
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_c);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_slot), TMEM_COLS);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  // the peer's barriers must be initialised before anything of this CTA can signal them
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs) {
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, abort_p)) { ok = false; break; }
+          const uint32_t full_leader = ptx::mapa(ptx::smem_u32(&bar_full[stage]), 0);
+          const uint32_t a_dst = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t b_dst = a_dst + P_A_STAGE_BYTES;
+          if (leader) ptx::mbar_expect_tx(ptx::smem_u32(&bar_full[stage]), 2 * P_STAGE_BYTES);
+#pragma unroll
+          for (int a = 0; a < 2; ++a)  // accumulator a covers rows [a*256, a*256+256) of the tile; mine: + rank*128
+            ptx::tma_load_2d_pair(a_dst + a * (UMMA_M * 128), &tmap_a, full_leader, static_cast<int32_t>(kb * BK),
+                                  static_cast<int32_t>(tc.m * P_BM + a * 256 + rank * UMMA_M));
+#pragma unroll
+          for (int j = 0; j < 2; ++j)  // my 128 columns of B
+            ptx::tma_load_2d_pair(b_dst + j * B_ATOM_BYTES, &tmap_b, full_leader,
+                                  static_cast<int32_t>(tc.n * BN + rank * 128 + j * 64), static_cast<int32_t>(kb * BK));
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(2 * UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      uint32_t stage = 0, phase = 0, tile_iter = 0;
+      bool ok = true;
+      for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs, ++tile_iter) {
+        for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_src = smem_base + stage * P_STAGE_BYTES;
+          const uint32_t b_src = a_src + P_A_STAGE_BYTES;
+#pragma unroll
+          for (int a = 0; a < 2; ++a) {
+            if (kb == 0) {
+              if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[a]), (tile_iter & 1u) ^ 1u, abort_p)) { ok = false; break; }
+              ptx::tc_fence_after();
+            }
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adesc = ptx::smem_desc_sw128(a_src + a * (UMMA_M * 128) + k * (UMMA_K * 2), 16, 1024);
+              const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+              ptx::mma_bf16_pair(tmem_base + a * UMMA_N, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
+            }
+          }
+          if (!ok) break;
+          ptx::mma_commit_pair(ptx::smem_u32(&bar_empty[stage]), 3);  // frees the stage in both CTAs
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::mma_commit_pair(ptx::smem_u32(&bar_tmem_full), 3);  // wakes the epilogues of both CTAs
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, each drains its own 128 rows) ----------------
+    const int e = warp - 2;
+    const uint32_t quad = static_cast<uint32_t>(warp) & 3u;
+    const uint32_t half = static_cast<uint32_t>(e) >> 2;
+    const uint32_t stage_box = smem_base + P_STAGES * P_STAGE_BYTES + e * EPI_BOX_BYTES;
+    const uint32_t my_row = stage_box + lane * 128;
+    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs, ++tile_iter) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      if (num_kb > 0) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) { ok = false; break; }
+        ptx::tc_fence_after();
+      }
+#pragma unroll 1
+      for (uint32_t a = 0; a < 2; ++a) {
+        const uint32_t row0 = tc.m * P_BM + a * 256 + rank * UMMA_M + quad * 32;
+#pragma unroll 1
+        for (uint32_t grp = 0; grp < 2; ++grp) {
+          const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
+          if (lane == 0) ptx::tma_store_wait_read();
+          __syncwarp();
+#pragma unroll
+          for (uint32_t h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            if (num_kb > 0) {
+              ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64 + h * 32, r);
+              ptx::tmem_ld_wait();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            const uint32_t col = col0 + h * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+              if (bias != nullptr && col + v * 8 < N) {
+                if (bias_vec) {
+                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8));
+                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8) + 1);
+                  f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
+                  f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] += __ldg(bias + col + v * 8 + j);
+                }
+              }
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f0 = f[2 * j], f1 = f[2 * j + 1];
+                if (act == TCAB_ACT_RELU) {
+                  f0 = fmaxf(f0, 0.0f);
+                  f1 = fmaxf(f1, 0.0f);
+                }
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+              }
+              const uint32_t chunk = (h * 4 + v) ^ (static_cast<uint32_t>(lane) & 7u);
+              ptx::st_shared_v4(my_row + chunk * 16, w[0], w[1], w[2], w[3]);
+            }
+          }
+          if (grp == 1) ptx::tc_fence_before();
+          ptx::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            // hand the accumulator back: the leader's barrier counts the epilogue warps of both CTAs
+            if (grp == 1) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[a]), 0));
+            if (row0 < M && col0 < N) {
+              ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+              ptx::tma_store_commit();
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  // neither CTA may exit (or free TMEM) while the other can still signal its barriers or read its
+  // shared memory through the tensor core
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = 2;
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not
 // link libcuda, so it still loads (and reports TCAB_ERR_CUDA) on a box without a driver.
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -332,8 +550,42 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   if (attr_err != cudaSuccess)
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(attr_err));
-  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   const Tune& tn = tune(kGemm);
+  if (tn.p1 == 2 && k > 0) {
+    // CTA pairs: A boxes of 128 rows, clusters of two CTAs
+    CUtensorMap ta2;
+    int rc = make_map(&ta2, a, m, k, UMMA_M);
+    if (rc != TCAB_OK) return rc;
+    const cudaError_t ae = cudaFuncSetAttribute(gemm_bias_act_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                static_cast<int>(P_SMEM_BYTES));
+    if (ae != cudaSuccess)
+      return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", P_SMEM_BYTES,
+                  cudaGetErrorString(ae));
+    const uint64_t ptiles = static_cast<uint64_t>((m + P_BM - 1) / P_BM) * ((n + BN - 1) / BN);
+    uint64_t pairs = (tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count())) / 2;
+    if (pairs > ptiles) pairs = ptiles;
+    if (pairs < 1) pairs = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_bias_act_pair_kernel, ta2, tb, tcm, bias, m, n, k, act);
+    count_launch();
+    if (le != cudaSuccess) {
+      cudaGetLastError();
+      return fail(TCAB_ERR_CUDA, "gemm_bias_act (pairs): launch failed: %s", cudaGetErrorString(le));
+    }
+    return TCAB_OK;
+  }
+  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   uint64_t grid = tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count());
   if (grid > tiles) grid = tiles;
   gemm_bias_act_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, tcm, bias, m, n, k, act);

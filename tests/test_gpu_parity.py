@@ -418,6 +418,26 @@ def test_gemm_bias_act(oracle, cuda, m, k, n, act):
     assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
 
 
+@pytest.mark.parametrize("m,k,n", [(512, 64, 256), (300, 200, 520), (1024, 2048, 1536), (1, 8, 8)])
+def test_gemm_cta_pair_variant(oracle, cuda, m, k, n):
+    # the cta_group::2 kernel (clusters of two CTAs, M = 256 per MMA) behind the tuning hook
+    a, b, bias = gemm_inputs(oracle, m, k, n, m + k + n)
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
+    buf, out = guarded((m, n), torch.bfloat16, cuda)
+    try:
+        T.tune("gemm", 0, 2)
+        T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu", out=out)
+        single_off = out.float().cpu().numpy()
+    finally:
+        T.tune("gemm")
+    check_guards(buf, torch.bfloat16)
+    assert T.device_status() == 0
+    assert rel_frobenius(single_off, want) <= 1e-3
+    # both kernels accumulate every output over ascending k in the tensor core: identical bits
+    ref = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
+    assert np.array_equal(single_off, ref)
+
+
 def test_gemm_without_bias_and_empty_k(oracle, cuda):
     a, b, bias = gemm_inputs(oracle, 256, 128, 256, 5)
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
