@@ -185,6 +185,27 @@ __device__ __forceinline__ float cta_allreduce(float v, float* slots) {
   }
 }
 
+// ---- thread-block clusters: distributed shared memory ---------------------------------------
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Reads a float from the shared memory of CTA `rank` of this cluster, at the address that `local`
+// has in this CTA (every CTA of a cluster lays its shared memory out identically).
+__device__ __forceinline__ float ld_dsmem(const float* local, unsigned rank) {
+  unsigned a = static_cast<unsigned>(__cvta_generic_to_shared(local)), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+// All threads of all CTAs of the cluster: writes before the barrier are visible after it.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 #endif  // __CUDACC__
 
 }  // namespace tcab

@@ -113,7 +113,116 @@ layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T
   }
 }
 
-// Rows too long for registers: one CTA per row, three streaming passes (sum,
+// A row too long for one CTA's registers, cut over a thread-block cluster (see softmax_rows.cu): every
+// CTA keeps its segment in registers; the partial sums meet through distributed shared memory.
+template <typename T, int THREADS, int VPT, int V>
+__global__ void __launch_bounds__(THREADS)
+layernorm_rows_cluster(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, float eps,
+                       T* __restrict__ y, uint32_t cols, uint32_t cs, uint32_t seg_vecs) {
+  using IO = VecIO<T, V>;
+  __shared__ float slots[2][32];
+  __shared__ float cl_sum, cl_sq;
+  const uint32_t rank = cluster_rank();
+  const uint64_t row = blockIdx.x / cs;
+  const uint32_t nvec = cols / V;
+  const uint32_t v0 = rank * seg_vecs;
+  const uint32_t v1 = (nvec - (v0 < nvec ? v0 : nvec) < seg_vecs) ? nvec : v0 + seg_vecs;
+  const float n = static_cast<float>(cols);
+  const T* xr = x + row * cols;
+  T* yr = y + row * cols;
+
+  float v[VPT][V];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (idx < v1) {
+      IO::unpack(IO::load(xr, idx), v[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) v[i][j] = 0.0f;
+    }
+  }
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) s += v[i][j];
+  s = cta_allreduce<OpSum, THREADS / 32>(s, slots[0]);
+  if (threadIdx.x == 0) cl_sum = s;
+  cluster_sync_all();
+  float gs = 0.0f;
+  for (uint32_t r = 0; r < cs; ++r) gs += ld_dsmem(&cl_sum, r);
+  const float mean = gs / n;
+
+  float q = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (idx < v1) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        v[i][j] -= mean;
+        q += v[i][j] * v[i][j];
+      }
+    }
+  }
+  q = cta_allreduce<OpSum, THREADS / 32>(q, slots[1]);
+  if (threadIdx.x == 0) cl_sq = q;
+  cluster_sync_all();
+  float gq = 0.0f;
+  for (uint32_t r = 0; r < cs; ++r) gq += ld_dsmem(&cl_sq, r);
+  const float rstd = 1.0f / sqrtf(gq / n + eps);
+
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (idx < v1) {
+      float gf[V], bf[V];
+      IO::unpack(IO::load_keep(gamma, idx), gf);
+      IO::unpack(IO::load_keep(beta, idx), bf);
+#pragma unroll
+      for (int j = 0; j < V; ++j) v[i][j] = v[i][j] * rstd * gf[j] + bf[j];
+      IO::store(yr, idx, IO::pack(v[i]));
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its partials
+}
+
+template <typename T, int THREADS, int VPT, int V>
+int launch_cluster_shape(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                         uint32_t nvec, cudaStream_t s) {
+  constexpr uint32_t kPerCta = THREADS * VPT;
+  uint32_t cs = 2;
+  while (cs < 8 && static_cast<uint64_t>(cs) * kPerCta < nvec) cs *= 2;
+  const uint32_t seg = (nvec + cs - 1) / cs;
+  auto* fn = layernorm_rows_cluster<T, THREADS, VPT, V>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * cs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, x, gamma, beta, eps, y, cols, cs, seg);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "layernorm_rows_cluster: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
+template <typename T, int V>
+int launch_cluster(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                   uint32_t nvec, cudaStream_t s) {
+  return launch_cluster_shape<T, 512, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
+}
+
+// Rows too long even for a cluster: one CTA per row, three streaming passes (sum,
 // centred squares, normalise); passes two and three re-read the row from L2.
 template <typename T, int THREADS, int V>
 __global__ void __launch_bounds__(THREADS)
@@ -201,6 +310,15 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
     vpt = tn.p1;
     fits = true;
   }
+  // Few long rows go to the cluster kernel (2-8 CTAs x 4096 vectors share a row, so a handful of rows
+  // still spreads over the GPU: 64 x 131072 bf16 runs at 1.75 TB/s instead of 1.10). With many rows the
+  // single-CTA kernels are faster (4.3 vs 2.6 TB/s at 4096 x 65536: three cluster barriers per row are
+  // not hidden), so the cluster is used only while the rows alone cannot fill the SMs. p3 == 3 forces it.
+  const bool few_rows = rows < 2ull * sm_count() && nvec > 8192;
+  if (tn.p0 <= 0 && nvec > 4096 && nvec <= 8u * 4096u && rows * 8 <= 0x7fffffffull && tn.p3 != 2 &&
+      ((few_rows && nvec <= 16384) || tn.p3 == 3))
+    return vec ? launch_cluster<T, VW>(x, gamma, beta, eps, y, rows, cols, nvec, s)
+               : launch_cluster<T, 1>(x, gamma, beta, eps, y, rows, cols, nvec, s);
   if (fits) {
 #define TCAB_CASE(TP, P)                                                                         \
   if (tpr == TP && vpt == P)                                                                     \

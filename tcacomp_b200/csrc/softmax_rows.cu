@@ -7,11 +7,14 @@
 // runner testing/runners/softmax.cu:49-61); its reducers run one shuffle tree and
 // two barriers PER ELEMENT (runtime/tca/reducer.h:109-167).
 //
-// Two kernels:
+// Three kernels:
 //   softmax_rows_reg     the row lives in registers (4 vectors of 4 fp32 per thread): x is read from HBM once and
 //                        y written once (8 bytes per element, the roofline figure);
 //                        one shuffle/shared-memory tree per reduction per ROW.
-//   softmax_rows_online  rows too long for registers: a single streaming pass
+//   softmax_rows_cluster rows of 32K..256K elements: the row is cut over a thread-block cluster of
+//                        2-8 CTAs, each keeps its segment in registers, the partial max and sum
+//                        meet through distributed shared memory: still one read and one write.
+//   softmax_rows_online  rows too long even for that: a single streaming pass
 //                        keeps a running (max, sum) pair per thread, rescaling
 //                        the sum when the max moves, then a second pass over the
 //                        row (L2-resident for any realistic row) writes y.
@@ -81,6 +84,109 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
       }
     }
   }
+}
+
+// A row too long for one CTA's registers is cut over a thread-block CLUSTER of CS CTAs: each CTA
+// keeps its segment in registers, the per-CTA max and sum meet through distributed shared memory
+// (every CTA reads the CS partials of its peers), so x is still read from HBM exactly once.
+template <int CS_MAX, int THREADS, int VPT, int V>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols, uint32_t cs,
+                     uint32_t seg_vecs) {
+  using IO = VecIO<float, V>;
+  __shared__ float slots[2][32];
+  __shared__ float cl_max, cl_sum;  // this CTA's partials, read by the whole cluster
+  const uint32_t rank = cluster_rank();
+  const uint64_t row = blockIdx.x / cs;  // clusters are consecutive CTAs: one row per cluster
+  const uint32_t nvec = cols / V;
+  const uint32_t v0 = rank * seg_vecs;
+  const uint32_t v1 = (nvec - (v0 < nvec ? v0 : nvec) < seg_vecs) ? nvec : v0 + seg_vecs;
+  const float* xr = x + row * cols;
+  float* yr = y + row * cols;
+  (void)rows;
+
+  float v[VPT][V];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (idx < v1) {
+      IO::unpack(IO::load(xr, idx), v[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;
+    }
+  }
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+  m = cta_allreduce<OpMax, THREADS / 32>(m, slots[0]);
+  if (threadIdx.x == 0) cl_max = m;
+  cluster_sync_all();
+  float gm = -INFINITY;
+  for (uint32_t r = 0; r < cs; ++r) gm = fmaxf(gm, ld_dsmem(&cl_max, r));
+
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      v[i][j] = expf(v[i][j] - gm);
+      s += v[i][j];
+    }
+  s = cta_allreduce<OpSum, THREADS / 32>(s, slots[1]);
+  if (threadIdx.x == 0) cl_sum = s;
+  cluster_sync_all();
+  float gs = 0.0f;
+  for (uint32_t r = 0; r < cs; ++r) gs += ld_dsmem(&cl_sum, r);  // ascending rank: the same total in every CTA
+  const float inv = 1.0f / gs;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (idx < v1) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) v[i][j] *= inv;
+      IO::store(yr, idx, IO::pack(v[i]));
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its partials
+}
+
+template <int THREADS, int VPT, int V>
+int launch_cluster_shape(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
+  constexpr uint32_t kPerCta = THREADS * VPT;
+  uint32_t cs = 2;
+  while (cs < 8 && static_cast<uint64_t>(cs) * kPerCta < nvec) cs *= 2;
+  const uint32_t seg = (nvec + cs - 1) / cs;
+  auto* fn = softmax_rows_cluster<8, THREADS, VPT, V>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * cs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, x, y, rows, cols, cs, seg);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "softmax_rows_cluster: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
+// Small CTAs while they cover the row (more of them fit an SM, so a CTA waiting at a cluster barrier
+// does not idle the SM); 512 threads x 16 vectors only for the longest rows.
+template <int V>
+int launch_cluster(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
+  if (nvec <= 8u * 256u * 8u) return launch_cluster_shape<256, 8, V>(x, y, rows, cols, nvec, s);
+  if (nvec <= 8u * 256u * 16u) return launch_cluster_shape<256, 16, V>(x, y, rows, cols, nvec, s);
+  return launch_cluster_shape<512, 16, V>(x, y, rows, cols, nvec, s);
 }
 
 // One CTA per row, any length. Pass 1 is the single-pass online max/sum.
@@ -165,6 +271,12 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
     vpt = tn.p1;
     fits = true;
   }
+  // Rows beyond 8192 vectors go to the cluster kernel (up to 8 CTAs x 8192 vectors), unless the tuning
+  // hook asked for a single-CTA shape; rows beyond that, or more rows than the grid can index, stream.
+  const bool long_class = nvec > 8u * 256u * 16u;  // 512-thread CTAs: they pay off only while the GPU is not full
+  if (tn.p0 <= 0 && nvec > 8192 && nvec <= 8u * 8192u && rows * 8 <= 0x7fffffffull && tn.p3 != 1 &&
+      (!long_class || rows < 2ull * sm_count() || tn.p3 == 2))
+    return vec ? launch_cluster<4>(x, y, rows, cols, nvec, s) : launch_cluster<1>(x, y, rows, cols, nvec, s);
   if (fits) {
 #define TCAB_CASE(T, P) \
   if (tpr == T && vpt == P) return vec ? launch_reg<T, P, 4>(x, y, rows, cols, tn.p2, s) \

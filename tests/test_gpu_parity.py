@@ -165,7 +165,10 @@ def assert_softmax_close(got, want, x):
 
 
 @pytest.mark.parametrize("rows,cols", [(64, 4096), (1, 1), (3, 7), (33, 517), (130, 32), (7, 1000), (5, 12288),
-                                       (3, 40000), (2, 140004), (2, 140001)])
+                                       (3, 40000), (2, 140004), (2, 140001),
+                                       # thread-block clusters of 2, 4, 8 CTAs (vector and scalar paths) and
+                                       # the first size past them
+                                       (2, 32772), (5, 60000), (3, 50001), (2, 262144), (1, 262148)])
 def test_softmax_rows(oracle, cuda, rows, cols):
     rng = np.random.default_rng(rows * 7 + cols)
     x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
@@ -237,7 +240,7 @@ def test_layernorm_rows_bf16(oracle, cuda, rows, cols):
     assert_layernorm_bf16_close(oracle, got, want, x, g, b)
 
 
-@pytest.mark.parametrize("rows,cols", [(33, 1024), (5, 77), (3, 20000)])
+@pytest.mark.parametrize("rows,cols", [(33, 1024), (5, 77), (3, 20000), (2, 131072), (2, 50001)])
 def test_layernorm_rows_f32(oracle, cuda, rows, cols):
     rng = np.random.default_rng(cols)
     x = rng.normal(0, 1, (rows, cols)).astype(np.float32)
@@ -245,7 +248,27 @@ def test_layernorm_rows_f32(oracle, cuda, rows, cols):
     b = rng.normal(0, 0.1, cols).astype(np.float32)
     want = oracle.layernorm_rows_f32(x, g, b, 1e-5)
     got = T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5).cpu().numpy()
-    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    x64 = x.astype(np.float64)
+    y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+    scale = np.abs(y64).max()
+    assert np.abs(got - y64).max() <= 1e-5 * scale
+    # against the oracle, charged with its own sequential-fold distance from the fp64 value
+    assert np.abs(got - want).max() <= 1e-5 * scale + np.abs(want - y64).max()
+
+
+@pytest.mark.parametrize("cols", [32776, 100000, 20001, 262144])
+def test_layernorm_cluster_kernel_forced(oracle, cuda, cols):
+    # the thread-block-cluster kernel is a heuristic choice; force it so that every cluster size is checked
+    rng = np.random.default_rng(cols)
+    x = oracle.f32_to_bf16(rng.normal(0, 1, (3, cols)).astype(np.float32))
+    g = oracle.f32_to_bf16(rng.normal(1, 0.1, cols).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.normal(0, 0.1, cols).astype(np.float32))
+    try:
+        T.tune("layernorm", 0, 0, 0, 3)
+        got = host_bits(T.layernorm_rows(dev_bf16(x, cuda), dev_bf16(g, cuda), dev_bf16(b, cuda)))
+    finally:
+        T.tune("layernorm")
+    assert_layernorm_bf16_close(oracle, got, oracle.layernorm_rows_bf16(x, g, b, 1e-5), x, g, b)
 
 
 @pytest.mark.parametrize("cache", [0, 1])
