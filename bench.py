@@ -42,11 +42,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each workload's kernel, from the ncu
 # captures summarised under profiles/ (mean of the two captured launches).
 NCU_TRAFFIC_BYTES = {
-    "softmax_rows_f32_16384x4096": 481820544,      # read 268.4 MB + write 213.4 MB (the rest of y still in L2)
-    "layernorm_rows_bf16_65536x8192": 2097888000,
-    "reduce_outer_f32_256x1024x1024": 1078140828,
-    "map_rowsum_f32_4096x1024": 16783488,
-    "gemm_bias_relu_bf16_8192": 1001582720,
+    "softmax_rows_f32_16384x4096": 482008320,      # read 268.4 MB + write 213.4 MB (the rest of y still in L2)
+    "layernorm_rows_bf16_65536x8192": 2097942000,
+    "reduce_outer_f32_256x1024x1024": 1078629812,
+    "map_rowsum_f32_4096x1024": 16784000,
+    "gemm_bias_relu_bf16_8192": 1000201344,
 }
 
 

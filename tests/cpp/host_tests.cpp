@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "../../tcacomp_b200/csrc/host/pkg.h"
+#include "../../tcacomp_b200/csrc/host/tca_syntax.h"
 
 #ifdef HOST_TESTS_WITH_CUDA
 #include <cuda_runtime.h>
@@ -282,6 +283,132 @@ static void test_typestate_and_classification() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// The .tca text frontend (internal/syntax/parser/parser_test.go, internal/syntax/semacheck tests and
+// internal/e2e/frontend_test.go cover the same ground in the reference): texts written for this test.
+// ---------------------------------------------------------------------------------------------
+static const char* kTcaWeightedFold = R"tca(
+// out[i][j] = bump + lift * sum_k (w0 * x + w1 * z), the trailing extent a compile-time constant
+@runtime(cxx_path="runtime/tca_runtime.h");
+@name(cxx="WeightedFold")
+kernel weighted_fold(
+  x: tensor<dtype=f32, shape=[R, C, 8u]>,
+  z: tensor<dtype=f32, shape=[R, C, 8u]>,
+  w0: f32, w1: f32, lift: f32,
+) -> tensor<dtype=f32, shape=[R, C]>
+{
+  dimvar (i, j, k);
+  let folded = map
+    on(x[i][j][k], z[i][j][k])
+    [w0, w1] (a: f32, b: f32) -> f32:
+      w0 * a + w1 * b
+  | reduce(init = 0.0f)
+    on(acc: f32, %0: f32)
+    as (i, j) -> f32:
+      acc + %0
+  | map
+    on()
+    [lift] (s: f32) -> f32:
+      0.25f + lift * s   /* literal lifted into a capture slot */
+  ;
+  return folded;
+}
+)tca";
+
+static const char* kTcaMidAxis = R"tca(
+@name(cxx="MidAxisMax")
+kernel mid_axis_max(x: tensor<dtype=f32, shape=[B, 6u, C]>) -> tensor<dtype=f32, shape=[B, C]> {
+  dimvar b, k, c;
+  let m = map on(x[b][k][c]) (v: f32): v * v - 0.5f
+        | reduce(init = -inf_f32) on(best: f32, %0) as (b, c) -> f32: fmaxf(best, %0);
+  return m;
+}
+)tca";
+
+static const char* kTcaScores = R"tca(
+@name(cxx="Scores")
+kernel scores(q: tensor<dtype=f32, shape=[H, D]>, keys: tensor<dtype=f32, shape=[N, D]>, temp: f32)
+    -> tensor<dtype=f32, shape=[H, N]> {
+  dimvar (h, n, d);
+  let s = map on(q[h][d], keys[n][d]) (l: f32, r: f32) -> f32: l * r
+        | reduce(init = 0.0f) on(acc: f32, %0: f32) as (h, n) -> f32: acc + %0
+        | map on() [temp] (v: f32) -> f32: v * temp;
+  return s;
+}
+)tca";
+
+static std::string tca_error(const std::string& text) {
+  auto r = ParseModule(text);
+  return r.ok() ? std::string("<accepted>") : r.err;
+}
+
+static void test_tca_frontend() {
+  {
+    auto r = ParseModule(kTcaWeightedFold);
+    CHECK(r.ok());
+    if (!r.ok()) std::printf("  %s\n", r.err.c_str());
+    CHECK(r.value.size() == 1);
+    if (r.ok() && r.value.size() == 1) {
+      const ParsedKernel& pk = r.value[0];
+      CHECK(pk.name == "weighted_fold" && pk.cxx_name == "WeightedFold" && pk.output == "folded");
+      CHECK(pk.graph.statements.size() == 1);
+      auto plan = Classify(pk.graph.statements[0]);
+      CHECK(plan.ok() && plan.value.kind == Plan::ChainReduce && plan.value.reduce_axis == 2);
+      CHECK(plan.value.map_expr == "((c0 * p0) + (c1 * p1))");
+      CHECK(plan.value.combine_expr == "(p0 + p1)");
+      CHECK(contains(plan.value.post_expr, "* p0") && contains(plan.value.post_expr, "0.25"));
+      CHECK(plan.value.capture_names.size() >= 3 && plan.value.capture_names[0] == "w0" && plan.value.capture_names[1] == "w1");
+    }
+  }
+  {
+    auto r = ParseModule(kTcaMidAxis);
+    CHECK(r.ok());
+    if (!r.ok()) std::printf("  %s\n", r.err.c_str());
+    if (r.ok()) {
+      auto plan = Classify(r.value[0].graph.statements[0]);
+      CHECK(plan.ok() && plan.value.kind == Plan::ChainReduce && plan.value.reduce_axis == 1);
+      CHECK(plan.value.combine_expr == "fmaxf(p0, p1)" && std::isinf(plan.value.init) && plan.value.init < 0);
+    }
+  }
+  {
+    auto r = ParseModule(std::string(kTcaScores) + kTcaMidAxis);  // two kernels in one module
+    CHECK(r.ok() && r.value.size() == 2);
+    if (!r.ok()) std::printf("  %s\n", r.err.c_str());
+    if (r.ok()) {
+      auto plan = Classify(r.value[0].graph.statements[0]);
+      CHECK(plan.ok() && plan.value.kind == Plan::ChainContract && plan.value.rhs_is_nk);
+      CHECK(plan.value.post_expr == "(p0 * c0)" && plan.value.capture_names.size() == 1 && plan.value.capture_names[0] == "temp");
+      CHECK(r.value[1].cxx_name == "MidAxisMax");
+    }
+  }
+  // diagnostics carry line:col (internal/syntax/parser/parser.go error positions)
+  CHECK(contains(tca_error("kernel k(x: tensor<dtype=f32, shape=[R, 4]>) -> f32 { }"), "1:41: a constant extent is an unsigned literal"));
+  CHECK(contains(tca_error("kernel k(x: tensor<dtype=f64, shape=[R]>) -> f32 { }"), "1:"));
+  CHECK(contains(tca_error("kernel k(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R]> {\n"
+                           "  dimvar (i, j);\n"
+                           "  let o = map on(x[i][j]) (v: f32): v > 0.0f ? v : 0.0f\n"
+                           "    | reduce(init = 0.0f) on(a: f32, %0) as (i) -> f32: a + %0;\n  return o; }"),
+                 "3:"));
+  // a store needs a reduction before it (pkg/chain.go:433-438)
+  CHECK(contains(tca_error("kernel k(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R, C]> {\n"
+                           "  dimvar (i, j);\n  let o = map on(x[i][j]) (v: f32): v + 1.0f;\n  return o; }"),
+                 "a store needs a reduction"));
+  // arity, unknown names, uncaptured scalars, rank and dimvar consistency (semacheck rules of section 7)
+  const std::string head = "kernel k(x: tensor<dtype=f32, shape=[R, C]>, y: tensor<dtype=f32, shape=[C, R]>, g: f32) -> tensor<dtype=f32, shape=[R]> {\n  dimvar (i, j);\n";
+  const std::string fold = "\n    | reduce(init = 0.0f) on(a: f32, %0) as (i) -> f32: a + %0;\n  return o; }";
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) (v: f32, w: f32): v * w" + fold), "3:11: root map: 2 lambda parameters for 1 operands"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) (v: f32): v * q" + fold), "unknown name 'q'"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) (v: f32): v * g" + fold), "used but not captured"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) [g] (v: f32): v * g" + fold), "<accepted>"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i]) (v: f32): v" + fold), "has rank 2, subscripted with 1"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j], y[i][j]) (v: f32, w: f32): v * w" + fold), "one extent per dimvar"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][t]) (v: f32): v" + fold), "'t' is not a declared dimvar"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) (v: f32): v" + fold.substr(0, fold.find("return")) + "return x; }"), "one let chain followed by"));
+  CHECK(contains(tca_error(head + "  let o = map on(x[i][j]) (v: f32): powf(v)" + fold), "powf"));
+  CHECK(contains(tca_error("@include \"other.tca\";"), "module loader"));
+  CHECK(contains(tca_error("kernel k(x: tensor<dtype=f32, shape=[R]>) -> f32 { let o = map on(x[i]) (v: f32): v /* open"), "unterminated"));
+}
+
+// ---------------------------------------------------------------------------------------------
 // GPU half: the reference's runner protocol (testing/runners/common.cuh)
 // ---------------------------------------------------------------------------------------------
 #ifdef HOST_TESTS_WITH_CUDA
@@ -546,17 +673,87 @@ static bool gpu_tests() {
   }
   return ok;
 }
+
+// The same texts the CPU half parses, launched: text -> rungs -> classifier -> C ABI (internal/e2e/frontend_test.go
+// takes a .tca through the whole pipeline the same way and compares with a host loop).
+static bool tca_gpu_tests() {
+  bool ok = true;
+  {
+    auto r = ParseModule(kTcaWeightedFold);
+    const unsigned R = 300, C = 129, K = 8;
+    std::vector<float> hx(R * C * K), hz(R * C * K), ref(R * C);
+    for (unsigned i = 0; i < hx.size(); ++i) { hx[i] = elem(i); hz[i] = elem(i + 11u); }
+    for (unsigned i = 0; i < R * C; ++i) {
+      float acc = 0.0f;
+      for (unsigned k = 0; k < K; ++k) acc += 2.0f * hx[i * K + k] + -0.5f * hz[i * K + k];
+      ref[i] = 0.25f + 0.125f * acc;
+    }
+    ok &= r.ok() && run_and_report("TcaWeightedFold", r.value[0].graph,
+                                   {{"x", view(TCAB_F32, {R, C, K})}, {"z", view(TCAB_F32, {R, C, K})}, {"folded", view(TCAB_F32, {R, C})}},
+                                   {hx.data(), hz.data(), nullptr}, {{"w0", 2.0f}, {"w1", -0.5f}, {"lift", 0.125f}}, "folded", ref, false);
+  }
+  {
+    auto r = ParseModule(kTcaMidAxis);
+    const unsigned B = 64, K = 6, C = 1000;
+    std::vector<float> hx(B * K * C), ref(B * C);
+    for (unsigned i = 0; i < hx.size(); ++i) hx[i] = elem(i);
+    for (unsigned b = 0; b < B; ++b)
+      for (unsigned c = 0; c < C; ++c) {
+        float best = -INFINITY;
+        for (unsigned k = 0; k < K; ++k) {
+          const float v = hx[(b * K + k) * C + c];
+          best = fmaxf(best, v * v - 0.5f);
+        }
+        ref[b * C + c] = best;
+      }
+    ok &= r.ok() && run_and_report("TcaMidAxisMax", r.value[0].graph, {{"x", view(TCAB_F32, {B, K, C})}, {"m", view(TCAB_F32, {B, C})}},
+                                   {hx.data(), nullptr}, {}, "m", ref, false);
+  }
+  {
+    auto r = ParseModule(kTcaScores);
+    const unsigned H = 96, N = 200, D = 64;
+    std::vector<float> hq(H * D), hk(N * D), ref(H * N);
+    for (unsigned i = 0; i < hq.size(); ++i) hq[i] = elem(i);
+    for (unsigned i = 0; i < hk.size(); ++i) hk[i] = elem(i + 5u);
+    for (unsigned h = 0; h < H; ++h)
+      for (unsigned n = 0; n < N; ++n) {
+        float acc = 0.0f;
+        for (unsigned d = 0; d < D; ++d) acc += hq[h * D + d] * hk[n * D + d];
+        ref[h * N + n] = acc * 0.125f;
+      }
+    ok &= r.ok() && run_and_report("TcaScores", r.value[0].graph,
+                                   {{"q", view(TCAB_F32, {H, D})}, {"keys", view(TCAB_F32, {N, D})}, {"s", view(TCAB_F32, {H, N})}},
+                                   {hq.data(), hk.data(), nullptr}, {{"temp", 0.125f}}, "s", ref, false);
+  }
+  {  // a constant extent is checked against the bound tensor at launch
+    auto r = ParseModule(kTcaMidAxis);
+    DeviceBuf a, o;
+    if (cudaMalloc(&a.p, 4 * 5 * 8 * 4) != cudaSuccess || cudaMalloc(&o.p, 4 * 8 * 4) != cudaSuccess) return false;
+    Bindings bind;
+    tcab_tensor tx = view(TCAB_F32, {4, 5, 8}), tm = view(TCAB_F32, {4, 8});
+    tx.data = a.p;
+    tm.data = o.p;
+    bind.tensors["x"] = tx;
+    bind.tensors["m"] = tm;
+    const int rc = r.ok() ? Launch(r.value[0].graph, bind, nullptr) : -1;
+    std::printf("TCA_CONST_EXTENT %s\n", rc == TCAB_ERR_SHAPE ? "rejected" : "accepted");
+    ok &= rc == TCAB_ERR_SHAPE;
+  }
+  return ok;
+}
 #endif  // HOST_TESTS_WITH_CUDA
 
 int main(int argc, char** argv) {
   test_matmul_scale_builds();
   test_eager_checks();
   test_typestate_and_classification();
+  test_tca_frontend();
   std::printf("%d checks, %d failures\n", g_checks, g_failures);
   bool gpu_ok = true;
   if (argc > 1 && std::strcmp(argv[1], "--gpu") == 0) {
 #ifdef HOST_TESTS_WITH_CUDA
     gpu_ok = gpu_tests();
+    gpu_ok = tca_gpu_tests() && gpu_ok;
     std::printf("GPU_TESTS %s\n", gpu_ok ? "ran" : "incomplete");
 #else
     std::printf("GPU_TESTS unavailable: built without CUDA\n");

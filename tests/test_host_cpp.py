@@ -15,7 +15,9 @@ OUT = os.path.join(ROOT, "tests", "cpp", "_build")
 
 # testing/suite.toml tolerances (max abs diff); the e2e row sum uses internal/e2e/e2e_test.go:15-21
 TOL = {"RowSum": 2e-3, "Softmax": 2e-3, "Transpose": 1e-5, "ScaleCopy": 1e-5, "Axpy3": 1e-5, "Layernorm": 1e-5,
-       "RowSumE2E": 2e-3, "MatmulScale": 2e-3, "GemmBiasRelu": 2e-2}
+       "RowSumE2E": 2e-3, "MatmulScale": 2e-3, "GemmBiasRelu": 2e-2,
+       # kernels written as .tca text in host_tests.cpp and taken through the text frontend
+       "TcaWeightedFold": 1e-5, "TcaMidAxisMax": 1e-6, "TcaScores": 2e-3}
 
 
 def build_binary(with_cuda: bool) -> str:
@@ -42,7 +44,7 @@ def test_builder_mirror_cpu():
     r = subprocess.run([build_binary(False)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout[-3000:]
     m = re.search(r"(\d+) checks, (\d+) failures", r.stdout)
-    assert m and int(m.group(1)) >= 45 and int(m.group(2)) == 0, r.stdout[-3000:]
+    assert m and int(m.group(1)) >= 80 and int(m.group(2)) == 0, r.stdout[-3000:]
 
 
 @pytest.mark.gpu
@@ -60,3 +62,4 @@ def test_suite_kernels_through_the_rungs():
         assert abs(float(f["CHECKSUM"]) - float(f["REF_CHECKSUM"])) <= 1e-4 * abs(float(f["REF_CHECKSUM"])), name
         seen[name] = float(f["MAXDIFF"])
     assert set(seen) == set(TOL), seen
+    assert "TCA_CONST_EXTENT rejected" in r.stdout
