@@ -50,6 +50,19 @@ constexpr size_t SMEM_BYTES =
 // Device status of the last contraction kernel that gave up on a wait (0 = none).
 __device__ int g_gemm_status = 0;
 
+// Developer timeline (off unless the file is compiled with -DTCAB_GEMM_TRACE): CTA 0 records SM clock
+// stamps per tile; tcab_debug_gemm_trace copies them out. slot = tile_iter * 16 + event.
+#ifdef TCAB_GEMM_TRACE
+__device__ long long g_gemm_trace[16 * 64];
+__device__ int g_gemm_debug_mode = 0;  // 1: the double-buffered kernels hand accumulators back without draining them
+#define GEMM_TRACE(tile_iter, ev)                                                        \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && (tile_iter) < 64u) g_gemm_trace[(tile_iter) * 16 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define GEMM_TRACE(tile_iter, ev) do { } while (0)
+#endif
+
 struct TileCoord {
   uint32_t m, n;
 };
@@ -61,6 +74,63 @@ __device__ __forceinline__ TileCoord tile_coord(uint32_t t, uint32_t tiles_m, ui
   const uint32_t rows = min(8u, tiles_m - first_m);
   const uint32_t r = t % band;
   return {first_m + r % rows, r / rows};
+}
+
+// The bias of a tile, held across a warp: lane l keeps the four values of columns 4l..4l+3 of the
+// warp's 128 columns. Loaded once per tile BEFORE the wait for the accumulator, so the latency of the
+// global load hides under the K loop; a load inside the drain would sit on the critical path (the asm
+// statements around it keep the compiler from hoisting it).
+struct BiasRegs {
+  float v[4];
+};
+__device__ __forceinline__ BiasRegs load_bias_regs(const float* __restrict__ bias, bool bias_vec, uint32_t col, uint32_t N) {
+  BiasRegs b = {{0.0f, 0.0f, 0.0f, 0.0f}};
+  if (bias != nullptr && col < N) {  // N % 8 == 0 and col % 4 == 0: the four columns are inside together
+    if (bias_vec) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(bias + col));
+      b.v[0] = q.x; b.v[1] = q.y; b.v[2] = q.z; b.v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b.v[j] = __ldg(bias + col + j);
+    }
+  }
+  return b;
+}
+
+// One 32-row x 64-column box of the result: TMEM -> registers -> bias / activation -> bf16 ->
+// this warp's swizzled staging box. `cbase` is the box's first column within the warp's 128 columns.
+__device__ __forceinline__ void stage_box_from_tmem(uint32_t taddr, bool have_acc, const BiasRegs& bias, uint32_t cbase,
+                                                    int act, uint32_t my_row, int lane) {
+#pragma unroll
+  for (uint32_t h = 0; h < 2; ++h) {
+    uint32_t r[32];
+    if (have_acc) {
+      ptx::tmem_ld_32x32(taddr + h * 32, r);
+      ptx::tmem_ld_wait();
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty reduction: the accumulator's init
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {  // four 16-byte chunks of 8 columns
+      const int src_lane = static_cast<int>((cbase + h * 32 + v * 8) >> 2);
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float f0 = __uint_as_float(r[v * 8 + 2 * j]) + __shfl_sync(0xffffffffu, bias.v[(2 * j) & 3], src_lane + (j >> 1));
+        float f1 = __uint_as_float(r[v * 8 + 2 * j + 1]) + __shfl_sync(0xffffffffu, bias.v[(2 * j + 1) & 3], src_lane + (j >> 1));
+        if (act == TCAB_ACT_RELU) {
+          f0 = fmaxf(f0, 0.0f);
+          f1 = fmaxf(f1, 0.0f);
+        }
+        const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+        w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+      }
+      // 128-byte swizzle: 16-byte chunk c of row r lives at chunk position c ^ (r % 8)
+      const uint32_t chunk = (h * 4 + v) ^ (static_cast<uint32_t>(lane) & 7u);
+      ptx::st_shared_v4(my_row + chunk * 16, w[0], w[1], w[2], w[3]);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -136,9 +206,11 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t stage = 0, phase = 0, tile_iter = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
+        GEMM_TRACE(tile_iter, 0);
         for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
           ptx::tc_fence_after();
+          if (kb == 0) GEMM_TRACE(tile_iter, 1);
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_STAGE_BYTES;
 #pragma unroll
@@ -146,6 +218,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (kb == 0) {  // the epilogue must have drained this accumulator (previous tile)
               if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[a]), (tile_iter & 1u) ^ 1u, abort_p)) { ok = false; break; }
               ptx::tc_fence_after();
+              GEMM_TRACE(tile_iter, 6 + a);
             }
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -161,6 +234,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) ptx::mma_commit(ptx::smem_u32(&bar_tmem_full));  // both accumulators complete
+        GEMM_TRACE(tile_iter, 2);
       }
     }
   } else {
@@ -175,10 +249,12 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     bool ok = true;
     for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const BiasRegs breg = load_bias_regs(bias, bias_vec, tc.n * BN + half * 128 + lane * 4, N);
       if (num_kb > 0) {
         if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) { ok = false; break; }
         ptx::tc_fence_after();
       }
+      if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
 #pragma unroll 1
       for (uint32_t a = 0; a < 2; ++a) {
         const uint32_t row0 = tc.m * BM + a * UMMA_M + quad * 32;
@@ -188,57 +264,21 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // the previous box must have left shared memory before it is overwritten
           if (lane == 0) ptx::tma_store_wait_read();
           __syncwarp();
-#pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            if (num_kb > 0) {
-              ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64 + h * 32, r);
-              ptx::tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = 0u;  // empty reduction: the accumulator's init
-            }
-            const uint32_t col = col0 + h * 32;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {  // four 16-byte chunks of 8 columns
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
-              if (bias != nullptr && col + v * 8 < N) {  // N % 8 == 0: 8-column groups are whole
-                if (bias_vec) {
-                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8));
-                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8) + 1);
-                  f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
-                  f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) f[j] += __ldg(bias + col + v * 8 + j);
-                }
-              }
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f0 = f[2 * j], f1 = f[2 * j + 1];
-                if (act == TCAB_ACT_RELU) {
-                  f0 = fmaxf(f0, 0.0f);
-                  f1 = fmaxf(f1, 0.0f);
-                }
-                const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                w[j] = *reinterpret_cast<const uint32_t*>(&hh);
-              }
-              // 128-byte swizzle: 16-byte chunk c of row r lives at chunk position c ^ (r % 8)
-              const uint32_t chunk = (h * 4 + v) ^ (static_cast<uint32_t>(lane) & 7u);
-              ptx::st_shared_v4(my_row + chunk * 16, w[0], w[1], w[2], w[3]);
-            }
-          }
+          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 8 + grp * 4);
+          stage_box_from_tmem(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64, num_kb > 0, breg,
+                              grp * 64, act, my_row, lane);
+          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 9 + grp * 4);
           if (grp == 1) {
             // both halves of this accumulator that this warp owns are in registers/shared memory now
             ptx::tc_fence_before();
           }
+          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 10 + grp * 4);
           ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
           __syncwarp();
+          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 11 + grp * 4);
           if (lane == 0) {
             if (grp == 1) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[a]));  // hand the accumulator back
+            if (grp == 1 && e == 0) GEMM_TRACE(tile_iter, 4 + a);
             if (row0 < M && col0 < N) {  // a box that starts inside the tensor; the hardware clips its edges
               ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
               ptx::tma_store_commit();
@@ -393,6 +433,7 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     bool ok = true;
     for (uint32_t t = pair; ok && t < num_tiles; t += num_pairs, ++tile_iter) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const BiasRegs breg = load_bias_regs(bias, bias_vec, tc.n * BN + half * 128 + lane * 4, N);
       if (num_kb > 0) {
         if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) { ok = false; break; }
         ptx::tc_fence_after();
@@ -405,48 +446,8 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
           const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
           if (lane == 0) ptx::tma_store_wait_read();
           __syncwarp();
-#pragma unroll
-          for (uint32_t h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            if (num_kb > 0) {
-              ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64 + h * 32, r);
-              ptx::tmem_ld_wait();
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) r[j] = 0u;
-            }
-            const uint32_t col = col0 + h * 32;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              float f[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
-              if (bias != nullptr && col + v * 8 < N) {
-                if (bias_vec) {
-                  const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8));
-                  const float4 b1 = __ldg(reinterpret_cast<const float4*>(bias + col + v * 8) + 1);
-                  f[0] += b0.x; f[1] += b0.y; f[2] += b0.z; f[3] += b0.w;
-                  f[4] += b1.x; f[5] += b1.y; f[6] += b1.z; f[7] += b1.w;
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) f[j] += __ldg(bias + col + v * 8 + j);
-                }
-              }
-              uint32_t w[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f0 = f[2 * j], f1 = f[2 * j + 1];
-                if (act == TCAB_ACT_RELU) {
-                  f0 = fmaxf(f0, 0.0f);
-                  f1 = fmaxf(f1, 0.0f);
-                }
-                const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                w[j] = *reinterpret_cast<const uint32_t*>(&hh);
-              }
-              const uint32_t chunk = (h * 4 + v) ^ (static_cast<uint32_t>(lane) & 7u);
-              ptx::st_shared_v4(my_row + chunk * 16, w[0], w[1], w[2], w[3]);
-            }
-          }
+          stage_box_from_tmem(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64, num_kb > 0, breg,
+                              grp * 64, act, my_row, lane);
           if (grp == 1) ptx::tc_fence_before();
           ptx::fence_proxy_async();
           __syncwarp();
@@ -475,6 +476,223 @@ gemm_bias_act_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = 2;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Double-buffered accumulators. The two kernels above give a tile all 512 TMEM columns, so the
+// tensor pipe idles while the epilogue drains a tile. Here a CTA's share of a tile is 128 rows x
+// 256 columns = 256 TMEM columns, two such accumulators alternate by tile parity, and the
+// epilogue of tile i runs under the K loop of tile i+1.
+//   PAIR = false: one CTA per 128x256 tile; a K block costs 48 KB (A 128x64 + B 64x256), 4 stages.
+//   PAIR = true : a cluster of two CTAs per 256x256 tile with cta_group::2 (M = 256): each CTA
+//                 loads its 128 rows of A and its 128 columns of B, 32 KB per K block, 6 stages;
+//                 the leader issues the MMAs and its commits arrive on both CTAs' barriers.
+// ---------------------------------------------------------------------------------------------
+template <bool PAIR>
+struct Db {
+  static constexpr int CTAS = PAIR ? 2 : 1;
+  static constexpr int TILE_M = UMMA_M * CTAS;
+  static constexpr int B_COLS = BN / CTAS;
+  static constexpr int A_BYTES = UMMA_M * 128;           // 16 KB
+  static constexpr int B_BYTES = BK * B_COLS * 2;        // 32 KB / 16 KB
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE + EPI_WARPS * EPI_BOX_BYTES + 1024;
+};
+
+template <bool PAIR>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
+                        uint32_t N, uint32_t K, int act) {
+  using C = Db<PAIR>;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[C::STAGES];   // PAIR: used in the leader, bytes of both CTAs land here
+  __shared__ __align__(8) uint64_t bar_empty[C::STAGES];  // in each CTA
+  __shared__ __align__(8) uint64_t bar_tmem_full[2];      // in each CTA, one per accumulator
+  __shared__ __align__(8) uint64_t bar_tmem_empty[2];     // PAIR: used in the leader, all epilogue warps arrive
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const bool leader = rank == 0;
+  volatile int* abort_p = &abort_flag;
+
+  const uint32_t tiles_m = (M + C::TILE_M - 1) / C::TILE_M, tiles_n = (N + BN - 1) / BN;
+  const uint32_t num_tiles = tiles_m * tiles_n;
+  const uint32_t num_kb = (K + BK - 1) / BK;
+  const uint32_t first = PAIR ? blockIdx.x >> 1 : blockIdx.x, step = PAIR ? gridDim.x >> 1 : gridDim.x;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::STAGES; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&bar_tmem_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bar_tmem_empty[a]), C::CTAS * EPI_WARPS);
+    }
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_c);
+  }
+  if (warp == 1) {
+    if (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&tmem_base_slot), TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (PAIR) {  // the peer's barriers must be initialised before anything of this CTA can signal them
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (every CTA) ----------------
+    // Lane 0 loads A, lanes 1.. load one 64-column box of B each: the boxes of a stage go out with one
+    // warp instruction instead of one instruction after the other from a single thread.
+    constexpr int B_BOXES = C::B_COLS / 64;
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (uint32_t t = first; ok && t < num_tiles; t += step) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const int32_t a_row = static_cast<int32_t>(tc.m * C::TILE_M + rank * UMMA_M);
+      const int32_t b_col = static_cast<int32_t>(tc.n * BN + rank * C::B_COLS);
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, abort_p)) { ok = false; break; }
+        const uint32_t a_dst = smem_base + stage * C::STAGE;
+        const uint32_t b_dst = a_dst + C::A_BYTES;
+        const int32_t k0 = static_cast<int32_t>(kb * BK);
+        const uint32_t full = PAIR ? ptx::mapa(ptx::smem_u32(&bar_full[stage]), 0) : ptx::smem_u32(&bar_full[stage]);
+        if (lane == 0) {
+          if (leader) ptx::mbar_expect_tx(ptx::smem_u32(&bar_full[stage]), C::CTAS * C::STAGE);
+          if (PAIR) ptx::tma_load_2d_pair(a_dst, &tmap_a, full, k0, a_row);
+          else ptx::tma_load_2d(a_dst, &tmap_a, full, k0, a_row);
+        } else if (lane <= B_BOXES) {
+          const int j = lane - 1;
+          if (PAIR) ptx::tma_load_2d_pair(b_dst + j * B_ATOM_BYTES, &tmap_b, full, b_col + j * 64, k0);
+          else ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, b_col + j * 64, k0);
+        }
+        if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (the leader CTA) ----------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(C::TILE_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      uint32_t stage = 0, phase = 0, tile_iter = 0;
+      bool ok = true;
+      for (uint32_t t = first; ok && t < num_tiles; t += step, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1u, use = (tile_iter >> 1) & 1u;
+        GEMM_TRACE(tile_iter, 0);
+        if (num_kb > 0) {  // the epilogue must have drained this accumulator (two tiles ago)
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[acc]), use ^ 1u, abort_p)) break;
+          ptx::tc_fence_after();
+        }
+        GEMM_TRACE(tile_iter, 6);
+        for (uint32_t kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+          ptx::tc_fence_after();
+          if (kb == 0) GEMM_TRACE(tile_iter, 1);
+          const uint32_t a_src = smem_base + stage * C::STAGE;
+          const uint32_t b_src = a_src + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = ptx::smem_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+            if (PAIR) ptx::mma_bf16_pair(tmem_base + acc * UMMA_N, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
+            else ptx::mma_bf16(tmem_base + acc * UMMA_N, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
+          }
+          if (PAIR) ptx::mma_commit_pair(ptx::smem_u32(&bar_empty[stage]), 3);
+          else ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok && num_kb > 0) {
+          if (PAIR) ptx::mma_commit_pair(ptx::smem_u32(&bar_tmem_full[acc]), 3);
+          else ptx::mma_commit(ptx::smem_u32(&bar_tmem_full[acc]));
+        }
+        GEMM_TRACE(tile_iter, 2);
+      }
+    }
+  } else {
+    // ---------------- epilogue (every CTA drains its own 128 rows) ----------------
+    const int e = warp - 2;
+    const uint32_t quad = static_cast<uint32_t>(warp) & 3u;
+    const uint32_t half = static_cast<uint32_t>(e) >> 2;
+    const uint32_t stage_box = smem_base + C::STAGES * C::STAGE + e * EPI_BOX_BYTES;
+    const uint32_t my_row = stage_box + lane * 128;
+    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
+    uint32_t tile_iter = 0;
+    bool ok = true;
+    for (uint32_t t = first; ok && t < num_tiles; t += step, ++tile_iter) {
+      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const uint32_t acc = tile_iter & 1u, use = (tile_iter >> 1) & 1u;
+      const BiasRegs breg = load_bias_regs(bias, bias_vec, tc.n * BN + half * 128 + lane * 4, N);
+      if (num_kb > 0) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full[acc]), use, abort_p)) { ok = false; break; }
+        ptx::tc_fence_after();
+      }
+      if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
+      const uint32_t row0 = tc.m * C::TILE_M + rank * UMMA_M + quad * 32;
+#pragma unroll 1
+      for (uint32_t grp = 0; grp < 2; ++grp) {
+        const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
+#ifdef TCAB_GEMM_TRACE
+        if (g_gemm_debug_mode == 1) {
+          if (grp == 1 && lane == 0 && num_kb > 0) {
+            if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[acc]), 0));
+            else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
+          }
+          continue;
+        }
+#endif
+        if (lane == 0) ptx::tma_store_wait_read();  // the previous box has left shared memory
+        __syncwarp();
+        stage_box_from_tmem(tmem_base + ((quad * 32u) << 16) + acc * UMMA_N + half * 128 + grp * 64, num_kb > 0, breg,
+                            grp * 64, act, my_row, lane);
+        if (grp == 1) ptx::tc_fence_before();
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          if (grp == 1 && num_kb > 0) {  // hand the accumulator back to the MMA issuer
+            if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[acc]), 0));
+            else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
+            if (e == 0) GEMM_TRACE(tile_iter, 4);
+          }
+          if (row0 < M && col0 < N) {
+            ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+            ptx::tma_store_commit();
+          }
+        }
+      }
+    }
+    if (lane == 0) ptx::tma_store_wait_all();
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (PAIR) {  // neither CTA may exit or free TMEM while the other can still signal it or read its shared memory
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    if (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = PAIR ? 4 : 3;
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not
@@ -516,6 +734,16 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 }  // namespace
 
+#ifdef TCAB_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int tcab_debug_gemm_trace(long long* out, int n) {
+  if (n > 16 * 64) n = 16 * 64;
+  return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 1;
+}
+extern "C" __attribute__((visibility("default"))) int tcab_debug_gemm_mode(int mode) {
+  return cudaMemcpyToSymbol(g_gemm_debug_mode, &mode, sizeof(int)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int gemm_device_status(int* out) {
   if (cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
@@ -551,6 +779,47 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(attr_err));
   const Tune& tn = tune(kGemm);
+  if (tn.p1 == 3 || tn.p1 == 4) {
+    // double-buffered accumulators: A boxes of 128 rows; p1 == 4 runs clusters of two CTAs
+    const bool pair = tn.p1 == 4;
+    CUtensorMap ta2;
+    int rc = k > 0 ? make_map(&ta2, a, m, k, UMMA_M) : TCAB_OK;
+    if (rc != TCAB_OK) return rc;
+    if (k == 0) ta2 = ta;
+    const size_t smem = pair ? Db<true>::SMEM : Db<false>::SMEM;
+    const void* fn = pair ? reinterpret_cast<const void*>(gemm_bias_act_db_kernel<true>)
+                          : reinterpret_cast<const void*>(gemm_bias_act_db_kernel<false>);
+    const cudaError_t ae = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (ae != cudaSuccess)
+      return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", smem,
+                  cudaGetErrorString(ae));
+    const uint32_t tile_m = pair ? Db<true>::TILE_M : Db<false>::TILE_M;
+    const uint64_t tiles = static_cast<uint64_t>((m + tile_m - 1) / tile_m) * ((n + BN - 1) / BN);
+    const uint64_t ctas_per_tile = pair ? 2 : 1;
+    uint64_t groups = (tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count())) / ctas_per_tile;
+    if (groups > tiles) groups = tiles;
+    if (groups < 1) groups = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas_per_tile * groups));
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pair ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    void* args[] = {&ta2, &tb, &tcm, &bias, &m, &n, &k, &act};
+    const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
+    count_launch();
+    if (le != cudaSuccess) {
+      cudaGetLastError();
+      return fail(TCAB_ERR_CUDA, "gemm_bias_act (double-buffered): launch failed: %s", cudaGetErrorString(le));
+    }
+    return TCAB_OK;
+  }
   if (tn.p1 == 2 && k > 0) {
     // CTA pairs: A boxes of 128 rows, clusters of two CTAs
     CUtensorMap ta2;
