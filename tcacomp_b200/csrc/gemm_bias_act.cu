@@ -133,6 +133,37 @@ __device__ __forceinline__ void stage_box_from_tmem(uint32_t taddr, bool have_ac
   }
 }
 
+// Half a box (32 rows x 32 columns) from registers: bias / activation -> bf16 -> a 2 KB staging buffer
+// with 64-byte rows and the 64-byte swizzle (16-byte chunk c of row r at chunk position c ^ ((r / 2) % 4)),
+// which keeps the 16-byte stores of a warp conflict-free. `bias32` points at the 32 bias values of these
+// columns in shared memory; every lane reads the same addresses (broadcast).
+__device__ __forceinline__ void stage_half_box(const uint32_t (&r)[32], const float* bias32, int act, uint32_t buf,
+                                               int lane) {
+  const uint32_t my_row = buf + static_cast<uint32_t>(lane) * 64u;
+  const uint32_t sw = (static_cast<uint32_t>(lane) >> 1) & 3u;
+  uint32_t w[16];
+  // all the arithmetic first, then the stores: the store statements are compiler barriers, and one per
+  // chunk in between would chain the four chunks' shared-memory loads one after the other
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {  // four 16-byte chunks of 8 columns
+    const float4 b0 = *reinterpret_cast<const float4*>(bias32 + v * 8);
+    const float4 b1 = *reinterpret_cast<const float4*>(bias32 + v * 8 + 4);
+    const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float f0 = __uint_as_float(r[v * 8 + 2 * j]) + bv[2 * j];
+      const float f1 = __uint_as_float(r[v * 8 + 2 * j + 1]) + bv[2 * j + 1];
+      __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+      // max(round(x), 0) == round(max(x, 0)): rounding keeps the sign, so the activation runs on the packed pair
+      if (act == TCAB_ACT_RELU) hh = __hmax2(hh, __floats2bfloat162_rn(0.0f, 0.0f));
+      w[v * 4 + j] = *reinterpret_cast<const uint32_t*>(&hh);
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < 4; ++v)
+    ptx::st_shared_v4(my_row + ((static_cast<uint32_t>(v) ^ sw) * 16u), w[v * 4], w[v * 4 + 1], w[v * 4 + 2], w[v * 4 + 3]);
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
@@ -142,6 +173,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   __shared__ __align__(8) uint64_t bar_empty[STAGES];
   __shared__ __align__(8) uint64_t bar_tmem_full;
   __shared__ __align__(8) uint64_t bar_tmem_empty[2];
+  __shared__ __align__(16) float bias_s[BN];  // the current tile's bias (zeros past N or without a bias)
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -207,8 +239,18 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
         GEMM_TRACE(tile_iter, 0);
+#ifdef TCAB_GEMM_TRACE
+        long long starved = 0;
+#endif
         for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
+#ifdef TCAB_GEMM_TRACE
+          const long long w0 = clock64();
+#endif
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+#ifdef TCAB_GEMM_TRACE
+          starved += clock64() - w0;
+          if (blockIdx.x == 0 && tile_iter < 64u) g_gemm_trace[tile_iter * 16 + 8] = starved;
+#endif
           ptx::tc_fence_after();
           if (kb == 0) GEMM_TRACE(tile_iter, 1);
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
@@ -243,47 +285,70 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t quad = static_cast<uint32_t>(warp) & 3u;  // TMEM lanes a warp may read: 32 * (warp % 4)
     const uint32_t half = static_cast<uint32_t>(e) >> 2;     // which 128 of the 256 columns
     const uint32_t stage_box = smem_base + STAGES * STAGE_BYTES + e * EPI_BOX_BYTES;  // 1024-byte aligned
-    const uint32_t my_row = stage_box + lane * 128;
-    const bool bias_vec = bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 15u) == 0;
     uint32_t tile_iter = 0;
     bool ok = true;
-    for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
+    // No early exit from this loop: the named barriers below need every epilogue warp, every tile. A
+    // warp that gave up on a wait keeps walking the tiles and only skips the work.
+    for (uint32_t t = blockIdx.x; t < num_tiles; t += gridDim.x, ++tile_iter) {
       const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-      const BiasRegs breg = load_bias_regs(bias, bias_vec, tc.n * BN + half * 128 + lane * 4, N);
-      if (num_kb > 0) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) { ok = false; break; }
+      // The tile's 256 bias values go to shared memory while the K loop runs; a global load inside the
+      // drain would sit on the critical path.
+      ptx::named_bar_sync(1, EPI_WARPS * 32);  // every warp has finished reading the previous tile's values
+      {
+        const uint32_t et = threadIdx.x - 64u, col = tc.n * BN + et;
+        bias_s[et] = (bias != nullptr && col < N) ? __ldg(bias + col) : 0.0f;
+      }
+      ptx::named_bar_sync(1, EPI_WARPS * 32);
+      if (ok && num_kb > 0) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), tile_iter & 1u, abort_p)) ok = false;
         ptx::tc_fence_after();
       }
+      if (!ok) continue;
       if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
-#pragma unroll 1
-      for (uint32_t a = 0; a < 2; ++a) {
+      // Eight half boxes of 32 columns per warp and tile, four per accumulator. What the next tile's K loop
+      // waits for is the accumulator, not the stores: a warp first pulls its whole share of accumulator 0
+      // into registers (128 values per thread) and hands the accumulator back, then converts and stores from
+      // registers; each register block that has been staged is refilled from accumulator 1 at once, so that
+      // accumulator 1 is handed back as soon as the last of accumulator 0's half boxes is staged.
+      const uint32_t tm_warp = tmem_base + ((quad * 32u) << 16) + half * 128;
+      uint32_t r[4][32];
+      if (num_kb > 0) {
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) ptx::tmem_ld_32x32(tm_warp + q * 32, r[q]);
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q) ptx::tmem_ld_wait_for(r[q]);
+        ptx::tc_fence_before();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[0]));
+        if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 4);
+      } else {
+#pragma unroll
+        for (uint32_t q = 0; q < 4; ++q)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[q][j] = 0u;  // empty reduction: the accumulator's init
+      }
+#pragma unroll
+      for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t a = i >> 2, q = i & 3u, cbase = q * 32;  // accumulator, register block, first column
         const uint32_t row0 = tc.m * BM + a * UMMA_M + quad * 32;
-#pragma unroll 1
-        for (uint32_t grp = 0; grp < 2; ++grp) {  // two 64-column boxes per warp and accumulator
-          const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
-          // the previous box must have left shared memory before it is overwritten
-          if (lane == 0) ptx::tma_store_wait_read();
-          __syncwarp();
-          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 8 + grp * 4);
-          stage_box_from_tmem(tmem_base + ((quad * 32u) << 16) + a * UMMA_N + half * 128 + grp * 64, num_kb > 0, breg,
-                              grp * 64, act, my_row, lane);
-          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 9 + grp * 4);
-          if (grp == 1) {
-            // both halves of this accumulator that this warp owns are in registers/shared memory now
-            ptx::tc_fence_before();
-          }
-          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 10 + grp * 4);
-          ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
-          __syncwarp();
-          if (e == 0 && lane == 0 && a == 0) GEMM_TRACE(tile_iter, 11 + grp * 4);
-          if (lane == 0) {
-            if (grp == 1) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[a]));  // hand the accumulator back
-            if (grp == 1 && e == 0) GEMM_TRACE(tile_iter, 4 + a);
-            if (row0 < M && col0 < N) {  // a box that starts inside the tensor; the hardware clips its edges
-              ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
-              ptx::tma_store_commit();
-            }
-          }
+        const uint32_t col0 = tc.n * BN + half * 128 + cbase;
+        const uint32_t buf = stage_box + (i & 1u) * (EPI_BOX_BYTES / 2);
+        if (i == 4 && num_kb > 0) {  // accumulator 1 is in registers
+#pragma unroll
+          for (uint32_t qq = 0; qq < 4; ++qq) ptx::tmem_ld_wait_for(r[qq]);
+          ptx::tc_fence_before();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[1]));
+          if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 5);
+        }
+        // two staging buffers alternate: the store issued two half boxes ago has left this one
+        if (lane == 0) ptx::tma_store_wait_read_1();
+        __syncwarp();
+        stage_half_box(r[q], bias_s + half * 128 + cbase, act, buf, lane);
+        if (i < 4 && num_kb > 0) ptx::tmem_ld_32x32(tm_warp + UMMA_N + q * 32, r[q]);  // refill from accumulator 1
+        ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
+        __syncwarp();
+        if (lane == 0 && row0 < M && col0 < N) {  // a box that starts inside the tensor; the hardware clips its edges
+          ptx::tma_store_2d(&tmap_c, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+          ptx::tma_store_commit();
         }
       }
     }
@@ -602,8 +667,18 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           ptx::tc_fence_after();
         }
         GEMM_TRACE(tile_iter, 6);
+#ifdef TCAB_GEMM_TRACE
+        long long starved = 0;
+#endif
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
+#ifdef TCAB_GEMM_TRACE
+          const long long w0 = clock64();
+#endif
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+#ifdef TCAB_GEMM_TRACE
+          starved += clock64() - w0;
+          if (blockIdx.x == 0 && tile_iter < 64u) g_gemm_trace[tile_iter * 16 + 8] = starved;
+#endif
           ptx::tc_fence_after();
           if (kb == 0) GEMM_TRACE(tile_iter, 1);
           const uint32_t a_src = smem_base + stage * C::STAGE;
@@ -716,17 +791,18 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// A 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of box_rows x 64 columns
-// (128 bytes, swizzled).
-int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// A 2-D bf16 row-major tensor [rows, cols] (cols contiguous) with a box of box_rows x box_cols columns:
+// 64 columns (128-byte rows, 128-byte swizzle) or 32 columns (64-byte rows, 64-byte swizzle).
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols = 64) {
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return fail(TCAB_ERR_CUDA, "gemm_bias_act: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(TCAB_ERR_CUDA, "gemm_bias_act: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
   return TCAB_OK;
@@ -755,9 +831,12 @@ int gemm_device_status(int* out) {
 int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias, int act,
                          __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
   if (m == 0 || n == 0) return TCAB_OK;
+  const Tune& tn = tune(kGemm);
+  const bool default_kernel = !(tn.p1 == 3 || tn.p1 == 4 || (tn.p1 == 2 && k > 0));
   CUtensorMap ta, tb, tcm;
   {
-    const int rc = make_map(&tcm, c, m, n, 32);
+    // the default kernel stores half boxes (32 x 32, 64-byte swizzle), the variants whole boxes (32 x 64)
+    const int rc = make_map(&tcm, c, m, n, 32, default_kernel ? 32 : 64);
     if (rc != TCAB_OK) return rc;
   }
   if (k > 0) {
@@ -778,7 +857,6 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   if (attr_err != cudaSuccess)
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(attr_err));
-  const Tune& tn = tune(kGemm);
   if (tn.p1 == 3 || tn.p1 == 4) {
     // double-buffered accumulators: A boxes of 128 rows; p1 == 4 runs clusters of two CTAs
     const bool pair = tn.p1 == 4;

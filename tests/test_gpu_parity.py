@@ -442,13 +442,15 @@ def test_gemm_bias_act(oracle, cuda, m, k, n, act):
 
 
 @pytest.mark.parametrize("m,k,n", [(512, 64, 256), (300, 200, 520), (1024, 2048, 1536), (1, 8, 8)])
-def test_gemm_cta_pair_variant(oracle, cuda, m, k, n):
-    # the cta_group::2 kernel (clusters of two CTAs, M = 256 per MMA) behind the tuning hook
+@pytest.mark.parametrize("variant", [2, 3, 4])
+def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
+    # the kernels behind the tuning hook: 2 = cta_group::2 (clusters of two CTAs, M = 256 per MMA, 512 x 256 tiles),
+    # 3 = double-buffered accumulators on 128 x 256 tiles, 4 = the same on CTA pairs (256 x 256 tiles)
     a, b, bias = gemm_inputs(oracle, m, k, n, m + k + n)
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
     buf, out = guarded((m, n), torch.bfloat16, cuda)
     try:
-        T.tune("gemm", 0, 2)
+        T.tune("gemm", 0, variant)
         T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu", out=out)
         single_off = out.float().cpu().numpy()
     finally:
