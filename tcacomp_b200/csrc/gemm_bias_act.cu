@@ -14,15 +14,20 @@
 //   * warp 1 (one lane) issues tcgen05.mma (M=128, N=256, K=16) into two TMEM accumulators
 //     (rows 0-127 and 128-255 of the tile, 256 fp32 columns each = all 512 TMEM columns),
 //     frees a ring stage with tcgen05.commit, and signals the epilogue per tile;
-//   * warps 2-9 are the epilogue: tcgen05.ld 32 lanes x 32 columns at a time, add bias,
-//     ReLU, round to bf16, stage a 32-row x 64-column box in shared memory (128-byte swizzle,
-//     conflict-free 16-byte stores) and hand it to a TMA store, which writes whole 128-byte
-//     row segments and clips ragged edges. Each accumulator is handed back to the MMA warp
-//     as soon as it is drained, so the next tile's first K blocks overlap the second drain.
+//   * warps 2-9 are the epilogue. The K loop runs at the tensor pipe's rate; what costs time is how long
+//     the next tile's first MMAs wait for the accumulators, so the drain hands TMEM back first: each warp
+//     pulls its 128 columns of accumulator 0 into registers (four tcgen05.ld of 32 lanes x 32 columns),
+//     arrives on the accumulator's barrier, and only then adds the bias (staged in shared memory while
+//     the K loop ran), applies the activation, rounds to bf16 and stages 32-row x 32-column half boxes in
+//     two alternating shared-memory buffers (64-byte swizzle, conflict-free 16-byte stores) for TMA
+//     stores, which write 64-byte row segments and clip ragged edges. Register blocks that have been
+//     staged are refilled from accumulator 1, which is handed back after the fourth half box.
 //
 // Per K block a CTA moves 64 KB into shared memory for 8.4 MFLOP (131 flop per byte), which
-// is what lets one CTA per SM run without cluster multicast. Every wait is bounded (see
-// sm100_ptx.cuh); a wait that gives up makes the kernel write a status word and return.
+// is what lets one CTA per SM run without cluster multicast. Every wait on another agent (TMA,
+// tensor core, another role's arrival) is bounded (see sm100_ptx.cuh); a wait that gives up makes the
+// kernel write a status word and return. The epilogue's named barrier is a rendezvous of warps that
+// all walk the same tile list and never leave it early, also after a wait has given up.
 #include <cuda.h>
 
 #include <mutex>
