@@ -1,0 +1,57 @@
+/* tcab_host.h -- C ABI over the .tca text frontend (libtcab_host.so).
+ *
+ * The reference compiles a .tca module ahead of time: `tcacomp` parses it (internal/syntax/parser),
+ * checks it (internal/syntax/semacheck), lowers it onto the pkg rungs (internal/syntax/build/build.go:27-36),
+ * emits <name>.cu (internal/cg/cxx/emit.go:85-190) and the user calls the generated
+ * <Name>Launch(tensors..., out, scalars..., stream) (internal/cg/cxx/launch.go:23-156).
+ * Here the same text is parsed at run time and each kernel is launched by name on the kernels of libtcab.so:
+ * tcab_module_parse replaces the compile step, tcab_module_launch replaces the generated launcher. Tensors
+ * and scalar parameters are passed by the names the kernel's signature gives them; the output tensor goes
+ * by the name of the returned `let`.
+ *
+ * Plain C: pointers, sizes and status codes (tcab_status of tcab.h). Handles are not thread-safe; distinct
+ * handles may be used from distinct threads. Messages are thread-local.
+ */
+#ifndef TCAB_HOST_H_
+#define TCAB_HOST_H_
+
+#include "tcab.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tcab_module tcab_module;
+
+/* Parses and lowers every kernel of `text`. On success *out owns the module (free it with
+ * tcab_module_free). On failure returns TCAB_ERR_INVALID_ARG (syntax, semantic checks: the message is
+ * "line:col: ...", like the reference's diagnostics) or TCAB_ERR_UNSUPPORTED (a construct the reference's
+ * grammar has but this path does not evaluate) and *out is NULL. Needs no GPU. */
+TCAB_API int tcab_module_parse(const char* text, tcab_module** out);
+TCAB_API void tcab_module_free(tcab_module* m);
+
+TCAB_API uint32_t tcab_module_kernel_count(const tcab_module* m);
+/* The launcher name of kernel i: @name(cxx="...") when present, else the kernel identifier
+ * (internal/cg/cxx/naming.go). NULL when i is out of range. The pointers live as long as the module. */
+TCAB_API const char* tcab_module_kernel_name(const tcab_module* m, uint32_t i);
+/* The name the output tensor is bound by: the returned `let`. */
+TCAB_API const char* tcab_module_kernel_output(const tcab_module* m, uint32_t i);
+/* Which entry point of tcab.h the kernel lowers to: "chain_reduce", "chain_contract" or "gemm_bias_act";
+ * NULL with a message when the chain has no kernel class. */
+TCAB_API const char* tcab_module_kernel_class(const tcab_module* m, uint32_t i);
+
+/* Launches kernel `kernel` (its launcher name) asynchronously on `stream` (a cudaStream_t). Every tensor
+ * parameter and the output must be bound in tensor_names/tensors, every scalar parameter in
+ * scalar_names/scalars. Shapes are checked the way the generated launcher checks them
+ * (internal/cg/cxx/launch.go:82-121): one extent per symbolic dim, constant extents exact. */
+TCAB_API int tcab_module_launch(const tcab_module* m, const char* kernel, const char* const* tensor_names,
+                                const tcab_tensor* tensors, uint32_t n_tensors, const char* const* scalar_names,
+                                const float* scalars, uint32_t n_scalars, void* stream);
+
+/* Message of the last failure of a tcab_module_* call on this thread. */
+TCAB_API const char* tcab_host_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TCAB_HOST_H_ */

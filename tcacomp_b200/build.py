@@ -111,7 +111,8 @@ def build_host(force: bool = False) -> str:
     """g++ build of csrc/host/*.cpp into libtcab_host.so, linked against libtcab.so beside it."""
     hdir = os.path.join(CSRC, "host")
     srcs = sorted(os.path.join(hdir, f) for f in os.listdir(hdir) if f.endswith(".cpp"))
-    deps = srcs + [os.path.join(hdir, "pkg.h"), os.path.join(HERE, "..", "include", "tcab.h")]
+    deps = srcs + [os.path.join(hdir, f) for f in os.listdir(hdir) if f.endswith(".h")] + \
+           [os.path.join(HERE, "..", "include", "tcab.h"), os.path.join(HERE, "..", "include", "tcab_host.h")]
     if not force and os.path.exists(HOST_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(HOST_LIB) for d in deps):
         return HOST_LIB
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-o", HOST_LIB] + srcs + \

@@ -286,7 +286,7 @@ struct Parser {
         if (n->kind == XNode::Cast && n->args.size() != 1) return fail_at(n->line, n->col, "a cast takes one argument");
         return true;
       }
-      if (id == "true" || id == "false") return fail_at(n->line, n->col, "bool expressions have no kernel class in this build");
+      if (id == "true" || id == "false") return fail_at(n->line, n->col, "bool expressions have no kernel class on this path");
       n->kind = XNode::Name;
       n->name = id;
       return true;
@@ -308,7 +308,7 @@ struct Parser {
       n->col = c;
       return true;
     }
-    if (is_punct("!") || is_punct("~")) return fail("operator '" + tok.text + "' has no kernel class in this build");
+    if (is_punct("!") || is_punct("~")) return fail("operator '" + tok.text + "' has no kernel class on this path");
     return primary(n);
   }
   bool binary(XNode* n, int level) {
@@ -337,7 +337,7 @@ struct Parser {
   bool expr(XNode* n) {
     if (!binary(n, 0)) return false;
     for (const char* o : {"?", "==", "!=", "<", "<=", ">", ">=", "&&", "||", "&", "^", "<<", ">>", "%"})
-      if (is_punct(o)) return fail(std::string("operator '") + o + "' has no kernel class in this build");
+      if (is_punct(o)) return fail(std::string("operator '") + o + "' has no kernel class on this path");
     return true;
   }
 
@@ -450,7 +450,7 @@ struct Parser {
         }
         if (!expect_punct(";")) return false;
       } else if (is_ident("let")) {
-        if (!k->let_name.empty()) return fail("this build lowers one let chain per kernel");
+        if (!k->let_name.empty()) return fail("one let chain per kernel: several chains have no kernel class on this path");
         bump();
         if (!ident(&k->let_name)) return false;
         if (is_punct(":")) {
@@ -528,7 +528,7 @@ struct Lower {
       case XNode::Lit:
         if (n.lit_type == Elem::F32) return b.Float32(static_cast<float>(n.value));
         if (n.lit_type == Elem::I32) return b.Int32(static_cast<int32_t>(n.value));
-        return bad("u32 literals have no kernel class in this build");
+        return bad("u32 literals have no kernel class on this path");
       case XNode::Pipe: {
         auto it = env.find("%0");
         return it == env.end() ? bad("%0 is not a parameter of this stage") : it->second;
@@ -650,14 +650,14 @@ struct Lower {
     size_t n_reduces = 0;
     for (size_t i = 1; i < k.stages.size() && !k.stages[i].is_map; ++i) ++n_reduces;
     if (n_reduces >= root_as_names.size())
-      return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class in this build");
+      return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class on this path");
     const std::vector<std::string> live_names(root_as_names.begin(), root_as_names.end() - static_cast<long>(n_reduces));
 
     for (const Param& p : k.params) {
       if (p.is_tensor) declare_tensor(p.name, p, nullptr);
       else scalars[p.name] = b.ScalarParam(p.name, p.elem);
     }
-    if (!k.ret.is_tensor) return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class in this build");
+    if (!k.ret.is_tensor) return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class on this path");
     if (k.ret.shape.size() != live_names.size())
       return fail(k.line, k.col, "the return type has rank " + std::to_string(k.ret.shape.size()) + " but the chain leaves " +
                                      std::to_string(live_names.size()) + " axes");

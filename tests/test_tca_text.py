@@ -1,0 +1,145 @@
+"""The .tca text frontend through its C ABI (include/tcab_host.h, tcacomp_b200/tca.py).
+
+CPU half: libtcab_host.so exports what the header declares; modules parse, classify and report errors with
+positions, the way the reference's parser and semacheck tests do (internal/syntax/parser/parser_test.go,
+internal/syntax/semacheck/*_test.go). GPU half: kernels written as text run on the device and are compared
+with the oracle, the way internal/e2e/frontend_test.go takes matmul_scale from text to numbers."""
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+AFFINE_ROWSUM = '''
+// C1-shaped: y[i] = sum_j (s * x[i][j] + t)^2
+@name(cxx="AffineSqRowsum")
+kernel affine_sq_rowsum(x: tensor<dtype=f32, shape=[R, C]>, s: f32, t: f32) -> tensor<dtype=f32, shape=[R]> {
+  dimvar (i, j);
+  let y = map on(x[i][j]) [s, t] (v: f32) -> f32: (s * v + t) * (s * v + t)
+        | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i) -> f32: acc + %0;
+  return y;
+}
+'''
+
+SCALED_MATMUL = '''
+@name(cxx="ScaledMatmul")
+kernel scaled_matmul(lhs: tensor<dtype=f32, shape=[M, N]>, rhs: tensor<dtype=f32, shape=[N, K]>, scale: f32)
+    -> tensor<dtype=f32, shape=[M, K]> {
+  dimvar (m, k, n);
+  let out = map on(lhs[m][n], rhs[n][k]) (l: f32, r: f32) -> f32: l * r
+          | reduce(init = 0.0f) on(acc: f32, %0: f32) as (m, k) -> f32: acc + %0
+          | map on() [scale] (v: f32) -> f32: v * scale;
+  return out;
+}
+'''
+
+BF16_GEMM = '''
+@name(cxx="GemmBiasRelu")
+kernel gemm_bias_relu(a: tensor<dtype=bf16, shape=[M, K]>, b: tensor<dtype=bf16, shape=[K, N]>,
+                      bias: tensor<dtype=f32, shape=[N]>) -> tensor<dtype=bf16, shape=[M, N]> {
+  dimvar (m, n, k);
+  let c = map on(a[m][k], b[k][n]) (l: bf16, r: bf16) -> f32: f32(l) * f32(r)
+        | reduce(init = 0.0f) on(acc: f32, %0: f32) as (m, n) -> f32: acc + %0
+        | map on(bias[n]) (v: f32, bb: f32) -> bf16: bf16(fmaxf(v + bb, 0.0f));
+  return c;
+}
+'''
+
+
+def test_host_library_exports_what_the_header_declares():
+    from tcacomp_b200 import tca
+    text = open(os.path.join(ROOT, "include", "tcab_host.h")).read()
+    names = sorted(set(re.findall(r"^TCAB_API[^;]*?\b(tcab_\w+)\s*\(", text, flags=re.M | re.S)))
+    lib = tca.load()
+    assert len(names) == 8
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/tcab_host.h but not exported"
+    assert sorted(s[0] for s in tca.SYMBOLS) == names
+
+
+def test_modules_parse_and_classify():
+    from tcacomp_b200 import tca
+    m = tca.Module(AFFINE_ROWSUM + SCALED_MATMUL + BF16_GEMM)
+    assert m.names() == ["AffineSqRowsum", "ScaledMatmul", "GemmBiasRelu"]
+    assert m.kernels["AffineSqRowsum"] == {"output": "y", "class": "chain_reduce"}
+    assert m.kernels["ScaledMatmul"] == {"output": "out", "class": "chain_contract"}
+    assert m.kernels["GemmBiasRelu"] == {"output": "c", "class": "gemm_bias_act"}
+
+
+@pytest.mark.parametrize("text,status,needle", [
+    ("kernel k(x: tensor<dtype=f32, shape=[R, 4]>) -> f32 { }", 1, "1:41: a constant extent is an unsigned literal"),
+    ("kernel k(x: tensor<dtype=f32, shape=[R]>) -> tensor<dtype=f32, shape=[R]> {\n  dimvar i;\n"
+     "  let o = map on(x[i]) (v: f32): v;\n  return o; }", 1, "a store needs a reduction"),
+    ('@include "other.tca";', 5, "module loader"),
+    (AFFINE_ROWSUM.replace("[s, t]", "[s]"), 1, "'t' is used but not captured"),
+    (AFFINE_ROWSUM.replace("x[i][j]", "x[i]"), 1, "has rank 2, subscripted with 1"),
+    (AFFINE_ROWSUM.replace("acc + %0", "acc < %0 ? acc : %0"), 5, "no kernel class"),
+])
+def test_diagnostics(text, status, needle):
+    from tcacomp_b200 import TcabError, tca
+    with pytest.raises(TcabError) as e:
+        tca.Module(text)
+    assert e.value.status == status, e.value.message
+    assert needle in e.value.message
+    assert re.match(r"\d+:\d+: ", e.value.message)
+
+
+def test_launch_argument_checks_need_no_gpu():
+    import ctypes as C
+
+    from tcacomp_b200 import _lib, tca
+    m = tca.Module(AFFINE_ROWSUM)
+    lib = tca.load()
+    rc = lib.tcab_module_launch(m._h, b"NoSuchKernel", None, None, 0, None, None, 0, None)
+    assert rc == _lib.ERR_INVALID_ARG and b"no kernel named" in lib.tcab_host_last_error()
+    # a missing binding is reported by name before anything touches a device
+    names = (C.c_char_p * 1)(b"x")
+    t = _lib.Tensor()
+    t.data, t.dtype, t.rank = 0x1000, _lib.F32, 2
+    t.dims[0], t.dims[1] = 8, 8
+    tensors = (_lib.Tensor * 1)(t)
+    rc = lib.tcab_module_launch(m._h, b"AffineSqRowsum", names, tensors, 1, None, None, 0, None)
+    assert rc != _lib.OK
+    assert b"y" in lib.tcab_host_last_error() or b"s" in lib.tcab_host_last_error()
+
+
+@pytest.mark.gpu
+def test_text_kernels_on_the_device(oracle, cuda):
+    import torch
+
+    from tcacomp_b200 import tca
+    m = tca.Module(AFFINE_ROWSUM + SCALED_MATMUL + BF16_GEMM)
+    rng = np.random.default_rng(11)
+
+    x = rng.uniform(-1, 1, (1000, 777)).astype(np.float32)
+    y = torch.full((1000,), -7.0, device=cuda)
+    m.launch("AffineSqRowsum", {"x": torch.from_numpy(x).to(cuda), "y": y}, {"s": 0.5, "t": 0.25})
+    from oracle import checks
+    assert checks.rowsum_close(y.cpu().numpy(), x)
+
+    lhs = rng.uniform(0, 1, (64, 128)).astype(np.float32)
+    rhs = rng.uniform(0, 1, (128, 96)).astype(np.float32)
+    out = torch.empty((64, 96), device=cuda)
+    m.launch("ScaledMatmul", {"lhs": torch.from_numpy(lhs).to(cuda), "rhs": torch.from_numpy(rhs).to(cuda), "out": out},
+             {"scale": 1.5})
+    want = oracle.matmul_scale_f32(lhs, rhs, 1.5)
+    assert np.abs(out.cpu().numpy() - want).max() <= 1e-5 * np.abs(want).max() * np.sqrt(128)
+
+    a = oracle.f32_to_bf16((rng.normal(0, 1, (300, 264)) / 16).astype(np.float32))
+    b = oracle.f32_to_bf16((rng.normal(0, 1, (264, 520)) / 16).astype(np.float32))
+    bias = rng.normal(0, 0.02, 520).astype(np.float32)
+    dev16 = lambda bits: torch.from_numpy(bits.view(np.int16)).to(cuda).view(torch.bfloat16)  # noqa: E731
+    c = torch.empty((300, 520), device=cuda, dtype=torch.bfloat16)
+    m.launch("GemmBiasRelu", {"a": dev16(a), "b": dev16(b), "bias": torch.from_numpy(bias).to(cuda), "c": c})
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
+    got = c.float().cpu().numpy()
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+
+    # shape disagreement is reported by dim name, like the generated launcher does
+    from tcacomp_b200 import TcabError
+    with pytest.raises(TcabError) as e:
+        m.launch("ScaledMatmul", {"lhs": torch.empty((64, 128), device=cuda), "rhs": torch.empty((100, 96), device=cuda),
+                                  "out": out}, {"scale": 1.0})
+    assert e.value.status == 2 and "N" in e.value.message
