@@ -70,7 +70,7 @@ const Nvrtc& nvrtc() {
 // The kernels one chain needs, in the order of JitChain::k.
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
-  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kSlots
+  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kSlots
 };
 
 struct JitChain {
@@ -80,7 +80,7 @@ struct JitChain {
 };
 
 std::mutex g_mu;
-std::map<std::string, JitChain*> g_cache;   // key: n_in | combine | map text | post text
+std::map<std::string, JitChain*> g_cache;   // key: R or C | n_in | combine | map text | post text
 std::map<std::string, std::string> g_failed;  // key -> compiler message (do not recompile a failing lambda)
 
 std::string functor(const char* name, const std::string& expr, int n_in) {
@@ -96,8 +96,11 @@ std::string functor(const char* name, const std::string& expr, int n_in) {
   return s;
 }
 
+// One program per chain and use: the reduction kernels (13 instances) or the contraction kernels (4),
+// never both -- a chain is launched through one entry point, and the unrolled contraction tiles are
+// the slowest instances to compile.
 int compile(const std::string& key, const std::string& map_text, const std::string& post_text, int combine, int n_in,
-            JitChain** out) {
+            bool contraction, JitChain** out) {
   const Nvrtc& nv = nvrtc();
   if (!nv.ok)
     return fail(TCAB_ERR_UNSUPPORTED,
@@ -110,27 +113,29 @@ int compile(const std::string& key, const std::string& map_text, const std::stri
   src += "}\n";
   const std::string n = std::to_string(n_in), c = std::to_string(combine);
   std::vector<std::string> names(kSlots);
-  const int tprs[4] = {1, 4, 32, 256};
-  for (int v = 0; v < 2; ++v)
-    for (int t = 0; t < 4; ++t)
-      names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
-                                                    std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ">";
-  names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4>";
-  names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1>";
-  names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
-  names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4>";
-  names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4>";
-  if (n_in == 2) {
-    names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0>";
-    names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1>";
+  if (!contraction) {
+    const int tprs[4] = {1, 4, 32, 256};
+    for (int v = 0; v < 2; ++v)
+      for (int t = 0; t < 4; ++t)
+        names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
+                                                      std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ">";
+    names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4>";
+    names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1>";
+    names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
+    names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4>";
+    names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4>";
   } else {
-    names.resize(kContractKN);
+    names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 4>";
+    names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 4>";
+    names[kContractKN8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 8>";
+    names[kContractNK8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 8>";
   }
 
   nvrtcProgram prog = nullptr;
   if (nv.create(&prog, src.c_str(), "tcab_chain_jit.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
     return fail(TCAB_ERR_CUDA, "chain_reduce: nvrtcCreateProgram failed");
-  for (const std::string& e : names) nv.add_name(prog, e.c_str());
+  for (const std::string& e : names)
+    if (!e.empty()) nv.add_name(prog, e.c_str());
   const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
   const nvrtcResult res = nv.compile(prog, 3, opts);
   if (res != NVRTC_SUCCESS) {
@@ -151,6 +156,7 @@ int compile(const std::string& key, const std::string& map_text, const std::stri
   jc->n_in = n_in;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
   for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
+    if (names[i].empty()) continue;
     const char* low = nullptr;
     if (nv.lowered(prog, names[i].c_str(), &low) != NVRTC_SUCCESS || low == nullptr) {
       e = cudaErrorSymbolNotFound;
@@ -185,8 +191,10 @@ int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStrea
 
 bool jit_available() { return nvrtc().ok; }
 
-int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, void** handle) {
-  const std::string key = std::to_string(n_in) + "|" + std::to_string(combine) + "|" + map_text + "|" + post_text;
+int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
+                void** handle) {
+  const std::string key = std::string(contraction ? "C|" : "R|") + std::to_string(n_in) + "|" + std::to_string(combine) + "|" +
+                          map_text + "|" + post_text;
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_cache.find(key);
   if (it != g_cache.end()) {
@@ -198,7 +206,7 @@ int jit_prepare(const std::string& map_text, const std::string& post_text, int c
     return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: run-time compilation of map '%s' failed earlier: %s",
                 map_text.c_str(), f->second.c_str());
   JitChain* jc = nullptr;
-  const int rc = compile(key, map_text, post_text, combine, n_in, &jc);
+  const int rc = compile(key, map_text, post_text, combine, n_in, contraction, &jc);
   if (rc != TCAB_OK) return rc;
   g_cache[key] = jc;
   *handle = jc;
@@ -252,13 +260,16 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
                         uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s) {
   JitChain* jc = static_cast<JitChain*>(handle);
-  if (jc->n_in != 2 || jc->k[kContractKN] == nullptr)
+  if (jc->n_in != 2 || jc->k[kContractKN] == nullptr)  // a handle prepared for reductions has no contraction kernels
     return fail(TCAB_ERR_INVALID_ARG, "chain_contract: the map lambda must take exactly two operands");
   tcabk::Caps caps;
   for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
   void* a[] = {&lhs, &rhs, &out, &m, &n, &k, &init, &caps};
-  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(jc->k[rhs_nk ? kContractNK : kContractKN]),
-                                         dim3((n + 63) / 64, (m + 63) / 64), dim3(256), a, 0, s);
+  const bool big = contract_big_tiles(m, n);
+  const uint32_t tile = big ? 128 : 64;
+  const int slot = big ? (rhs_nk ? kContractNK8 : kContractKN8) : (rhs_nk ? kContractNK : kContractKN);
+  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(jc->k[slot]),
+                                         dim3((n + tile - 1) / tile, (m + tile - 1) / tile), dim3(256), a, 0, s);
   count_launch();
   if (e != cudaSuccess) {
     cudaGetLastError();

@@ -261,70 +261,156 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 // chains: testing/kernels/llm/gemm.tca, tiling/mm_*.tca, fusion/mlp.tca, llm/qk_score.tca):
 //   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )         RHS_NK == 0, rhs is [K,N]
 //   out[m,n] = post( fold_k map(lhs[m,k], rhs[n,k]) )         RHS_NK == 1, rhs is [N,K]
-// A CTA owns a 64x64 output tile, a thread a 4x4 block of it; K advances in shared-memory tiles
-// of 16. Each output is folded over k in ascending order by one thread -- the order of the
-// reference's CPU loops (testing/runners/gemm.cu:44-56). Rows and columns past the edge are
-// computed on zero padding and never stored; k past the edge never reaches the lambda.
-template <class Map, class Post, int COMBINE, int RHS_NK>
-__global__ void __launch_bounds__(256)
+// 256 threads own a (16 TM) x (16 TM) output tile, a thread TM x TM of it as 4x4 blocks 64 rows /
+// columns apart (TM = 4: 64x64 tiles for small problems; TM = 8: 128x128 tiles). K advances in
+// shared-memory tiles of 16, double-buffered: the next tile's global loads (16-byte vectors where the
+// row pitch allows) are in registers while the current one is multiplied. Operands whose k runs fastest
+// in memory are stored transposed, so that the inner loop reads 16-byte vectors along m and n; the row
+// pitch of 16 TM + 4 floats keeps those transposing stores conflict-free.
+// Each output is folded over k in ascending order by one thread -- the order of the reference's CPU
+// loops (testing/runners/gemm.cu:44-56). Rows and columns past the edge are computed on zero padding
+// and never stored; k past the edge never reaches the lambda.
+template <int TM>
+struct ContractTile {
+  static constexpr int BM = 16 * TM, BK = 16, PITCH = BM + 4;
+  static constexpr int V = BM * BK / 4 / 256;  // 16-byte vectors per thread and operand tile (1 or 2)
+};
+
+// A [rows, K] operand (k fastest): vector v of the thread covers row r = idx / 4, k = (idx % 4) * 4 .. +3.
+template <int TM>
+__device__ __forceinline__ void contract_fetch_k_fastest(const float* __restrict__ p, u32 row0, u32 rows, u32 k0, u32 K,
+                                                         bool vec_ok, float (&reg)[ContractTile<TM>::V][4]) {
+#pragma unroll
+  for (int v = 0; v < ContractTile<TM>::V; ++v) {
+    const int idx = threadIdx.x + v * 256;
+    const u32 r = row0 + (idx >> 2), k = k0 + (idx & 3) * 4;
+    const float* src = p + static_cast<u64>(r) * K + k;
+    if (r < rows && vec_ok && k + 3 < K) {
+      const float4 q = *reinterpret_cast<const float4*>(src);
+      reg[v][0] = q.x; reg[v][1] = q.y; reg[v][2] = q.z; reg[v][3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) reg[v][j] = (r < rows && k + j < K) ? src[j] : 0.0f;
+    }
+  }
+}
+template <int TM>
+__device__ __forceinline__ void contract_stash_k_fastest(float (*tile)[ContractTile<TM>::PITCH],
+                                                         const float (&reg)[ContractTile<TM>::V][4]) {
+#pragma unroll
+  for (int v = 0; v < ContractTile<TM>::V; ++v) {
+    const int idx = threadIdx.x + v * 256;
+    const int r = idx >> 2, k = (idx & 3) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tile[k + j][r] = reg[v][j];
+  }
+}
+// B as [K, N] (n fastest): vector v covers k = idx / (BM / 4), n = (idx % (BM / 4)) * 4 .. +3.
+template <int TM>
+__device__ __forceinline__ void contract_fetch_n_fastest(const float* __restrict__ p, u32 n0, u32 N, u32 k0, u32 K,
+                                                         bool vec_ok, float (&reg)[ContractTile<TM>::V][4]) {
+  constexpr int W = ContractTile<TM>::BM / 4;
+#pragma unroll
+  for (int v = 0; v < ContractTile<TM>::V; ++v) {
+    const int idx = threadIdx.x + v * 256;
+    const u32 k = k0 + idx / W, n = n0 + (idx % W) * 4;
+    const float* src = p + static_cast<u64>(k) * N + n;
+    if (k < K && vec_ok && n + 3 < N) {
+      const float4 q = *reinterpret_cast<const float4*>(src);
+      reg[v][0] = q.x; reg[v][1] = q.y; reg[v][2] = q.z; reg[v][3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) reg[v][j] = (k < K && n + j < N) ? src[j] : 0.0f;
+    }
+  }
+}
+template <int TM>
+__device__ __forceinline__ void contract_stash_n_fastest(float (*tile)[ContractTile<TM>::PITCH],
+                                                         const float (&reg)[ContractTile<TM>::V][4]) {
+  constexpr int W = ContractTile<TM>::BM / 4;
+#pragma unroll
+  for (int v = 0; v < ContractTile<TM>::V; ++v) {
+    const int idx = threadIdx.x + v * 256;
+    *reinterpret_cast<float4*>(&tile[idx / W][(idx % W) * 4]) = make_float4(reg[v][0], reg[v][1], reg[v][2], reg[v][3]);
+  }
+}
+
+template <class Map, class Post, int COMBINE, int RHS_NK, int TM>
+__global__ void __launch_bounds__(256, 2)
 chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, float* __restrict__ out, u32 M, u32 N,
                u32 K, float init, Caps caps) {
   typedef Comb<COMBINE> C;
-  constexpr int BM = 64, BN = 64, BK = 16;
-  __shared__ float As[BK][BM + 4];
-  __shared__ float Bs[BK][BN + 4];
+  typedef ContractTile<TM> T;
+  constexpr int BM = T::BM, BK = T::BK, Q = TM / 4;
+  __shared__ __align__(16) float As[2][BK][T::PITCH];
+  __shared__ __align__(16) float Bs[2][BK][T::PITCH];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  const u32 m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[4][4];
+  const u32 m0 = blockIdx.y * BM, n0 = blockIdx.x * BM;
+  const bool a_vec = (K % 4 == 0) && (reinterpret_cast<unsigned long long>(lhs) % 16 == 0);
+  const bool b_vec = ((RHS_NK ? K : N) % 4 == 0) && (reinterpret_cast<unsigned long long>(rhs) % 16 == 0);
+  float acc[TM][TM];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = C::identity();
+    for (int j = 0; j < TM; ++j) acc[i][j] = C::identity();
 
-  for (u32 k0 = 0; k0 < K; k0 += BK) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int idx = threadIdx.x + i * 256;
-      {  // A: 64 rows x 16 k, k fastest in memory
-        const int r = idx >> 4, c = idx & 15;
-        const bool ok = (m0 + r < M) && (k0 + c < K);
-        As[c][r] = ok ? lhs[static_cast<u64>(m0 + r) * K + k0 + c] : 0.0f;
-      }
-      if (RHS_NK) {  // B as [N,K]: 64 n x 16 k, k fastest in memory
-        const int c = idx >> 4, r = idx & 15;
-        const bool ok = (n0 + c < N) && (k0 + r < K);
-        Bs[r][c] = ok ? rhs[static_cast<u64>(n0 + c) * K + k0 + r] : 0.0f;
-      } else {       // B as [K,N]: 16 k x 64 n, n fastest in memory
-        const int r = idx >> 6, c = idx & 63;
-        const bool ok = (k0 + r < K) && (n0 + c < N);
-        Bs[r][c] = ok ? rhs[static_cast<u64>(k0 + r) * N + n0 + c] : 0.0f;
-      }
+  float ra[T::V][4], rb[T::V][4];
+  if (K > 0) {
+    contract_fetch_k_fastest<TM>(lhs, m0, M, 0, K, a_vec, ra);
+    if (RHS_NK) contract_fetch_k_fastest<TM>(rhs, n0, N, 0, K, b_vec, rb);
+    else contract_fetch_n_fastest<TM>(rhs, n0, N, 0, K, b_vec, rb);
+    contract_stash_k_fastest<TM>(As[0], ra);
+    if (RHS_NK) contract_stash_k_fastest<TM>(Bs[0], rb);
+    else contract_stash_n_fastest<TM>(Bs[0], rb);
+  }
+  __syncthreads();
+
+  int cur = 0;
+  for (u32 k0 = 0; k0 < K; k0 += BK, cur ^= 1) {
+    const bool more = k0 + BK < K;
+    if (more) {  // the next tile travels while this one is multiplied
+      contract_fetch_k_fastest<TM>(lhs, m0, M, k0 + BK, K, a_vec, ra);
+      if (RHS_NK) contract_fetch_k_fastest<TM>(rhs, n0, N, k0 + BK, K, b_vec, rb);
+      else contract_fetch_n_fastest<TM>(rhs, n0, N, k0 + BK, K, b_vec, rb);
     }
-    __syncthreads();
     const int kmax = (K - k0 < static_cast<u32>(BK)) ? static_cast<int>(K - k0) : BK;
-    for (int kk = 0; kk < kmax; ++kk) {
-      float a[4], b[4];
+    auto step = [&](int kk) {
+      float a[TM], b[TM];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+      for (int q = 0; q < Q; ++q) {
+        const float4 va = *reinterpret_cast<const float4*>(&As[cur][kk][q * 64 + ty * 4]);
+        const float4 vb = *reinterpret_cast<const float4*>(&Bs[cur][kk][q * 64 + tx * 4]);
+        a[q * 4] = va.x; a[q * 4 + 1] = va.y; a[q * 4 + 2] = va.z; a[q * 4 + 3] = va.w;
+        b[q * 4] = vb.x; b[q * 4 + 1] = vb.y; b[q * 4 + 2] = vb.z; b[q * 4 + 3] = vb.w;
+      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+      for (int i = 0; i < TM; ++i)
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < TM; ++j) {
           const float p[2] = {a[i], b[j]};
           acc[i][j] = C::apply(acc[i][j], Map::apply(p, caps.c));
         }
+    };
+    if (kmax == BK) {
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) step(kk);
+    } else {
+      for (int kk = 0; kk < kmax; ++kk) step(kk);
+    }
+    if (more) {
+      contract_stash_k_fastest<TM>(As[cur ^ 1], ra);
+      if (RHS_NK) contract_stash_k_fastest<TM>(Bs[cur ^ 1], rb);
+      else contract_stash_n_fastest<TM>(Bs[cur ^ 1], rb);
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const u32 m = m0 + ty * 4 + i;
+  for (int i = 0; i < TM; ++i) {
+    const u32 m = m0 + (i / 4) * 64 + ty * 4 + (i % 4);
     if (m >= M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const u32 n = n0 + tx * 4 + j;
+    for (int j = 0; j < TM; ++j) {
+      const u32 n = n0 + (j / 4) * 64 + tx * 4 + (j % 4);
       if (n >= N) continue;
       const float r[1] = {C::apply(init, acc[i][j])};
       out[static_cast<u64>(m) * N + n] = Post::apply(r, caps.c + 8);

@@ -303,7 +303,7 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   if (outer == 0 || inner == 0) return TCAB_OK;
   if (pc.entry == kJitEntry) {
     void* h = nullptr;
-    const int rc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, &h);
+    const int rc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
     if (rc != TCAB_OK) return rc;
     uint32_t splits = 1;
     float* scratch = nullptr;
@@ -323,21 +323,40 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
 // ---------------------------------------------------------------------------
 // fp32 contraction chains
 // ---------------------------------------------------------------------------
+bool contract_big_tiles(uint32_t m, uint32_t n);
+
 namespace {
 
 template <class Map, class Post, int COMBINE>
 int launch_contract_aot(const float* lhs, const float* rhs, float* out, uint32_t m, uint32_t n, uint32_t k,
                         int rhs_nk, float init, const Caps& caps, cudaStream_t s) {
-  const dim3 grid((n + 63) / 64, (m + 63) / 64);
-  if (rhs_nk)
-    tcabk::chain_contract<Map, Post, COMBINE, 1><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
-  else
-    tcabk::chain_contract<Map, Post, COMBINE, 0><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+  if (contract_big_tiles(m, n)) {
+    const dim3 grid((n + 127) / 128, (m + 127) / 128);
+    if (rhs_nk)
+      tcabk::chain_contract<Map, Post, COMBINE, 1, 8><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+    else
+      tcabk::chain_contract<Map, Post, COMBINE, 0, 8><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+  } else {
+    const dim3 grid((n + 63) / 64, (m + 63) / 64);
+    if (rhs_nk)
+      tcabk::chain_contract<Map, Post, COMBINE, 1, 4><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+    else
+      tcabk::chain_contract<Map, Post, COMBINE, 0, 4><<<grid, 256, 0, s>>>(lhs, rhs, out, m, n, k, init, caps);
+  }
   count_launch();
   return check_launch("chain_contract");
 }
 
 }  // namespace
+
+// 128x128 tiles once they fill the GPU (two CTAs per SM are resident), 64x64 tiles below that.
+bool contract_big_tiles(uint32_t m, uint32_t n) {
+  const Tune& tn = tune(kGemm);
+  if (tn.p2 == 4) return false;
+  if (tn.p2 == 8) return true;
+  const uint64_t tiles = static_cast<uint64_t>((m + 127) / 128) * ((n + 127) / 128);
+  return tiles >= static_cast<uint64_t>(sm_count());
+}
 
 int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,
                           uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
@@ -362,7 +381,7 @@ int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float
     combine = kTable[pc.entry].combine;
   }
   void* h = nullptr;
-  const int rc = jit_prepare(map_text, post_text, combine, 2, &h);
+  const int rc = jit_prepare(map_text, post_text, combine, 2, true, &h);
   if (rc != TCAB_OK) return rc;
   return jit_launch_contract(h, lhs, rhs, rhs_nk, out, m, n, k, pc.init, pc.caps, s);
 }
@@ -431,7 +450,7 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
   if (splits < 1) splits = 1;
   if (pc.entry == kJitEntry) {
     void* h = nullptr;
-    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, &h);
+    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
     if (jrc != TCAB_OK) return jrc;
     // the split kernels always: splits may be 1, the partials still pass through the fixed array
     return jit_launch(h, ins, rows, nk, 1, pc.init, pc.caps, out, scratch, static_cast<uint32_t>(splits) | 0x80000000u, s);

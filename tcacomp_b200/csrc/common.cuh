@@ -67,7 +67,8 @@ struct PreparedChain {
 constexpr int kJitEntry = -2;
 // Run-time compilation of chains without an ahead-of-time instance (chain_jit.cu).
 bool jit_available();
-int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, void** handle);
+int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
+                void** handle);  // contraction: compile the contraction kernels instead of the reduction kernels
 int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
                const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s);
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
@@ -82,6 +83,7 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
                                 float* out, cudaStream_t s);
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
                         uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s);
+bool contract_big_tiles(uint32_t m, uint32_t n);  // tile choice of the fp32 contraction (tune "gemm" p2 = 4 / 8 forces it)
 int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,
                           uint32_t m, uint32_t n, uint32_t k, cudaStream_t s);
 int gemm_device_status(int* out);  // status word of the contraction kernel (synchronous read)

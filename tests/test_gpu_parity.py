@@ -656,6 +656,41 @@ def test_contraction_ragged_and_other_combiners(oracle, cuda):
     assert e.value.status == T._lib.ERR_SHAPE and "dim k" in e.value.message
 
 
+@pytest.mark.parametrize("tile", [4, 8])
+def test_contraction_tile_sizes(oracle, cuda, tile):
+    # both tile shapes of the fp32 contraction (64 x 64 and 128 x 128 per CTA) on the same inputs: ragged edges in
+    # m, n and k, row pitches that allow 16-byte loads and ones that do not, both layouts of rhs, a JIT lambda
+    rng = np.random.default_rng(tile)
+    try:
+        T.tune("gemm", 0, 0, tile)
+        for m, k, n in [(129, 16, 257), (300, 203, 130), (255, 64, 128), (128, 37, 131), (1, 5, 300), (260, 48, 9)]:
+            a = rng.normal(0, 1, (m, k)).astype(np.float32)
+            b = rng.normal(0, 1, (k, n)).astype(np.float32)
+            want = oracle.matmul_scale_f32(a, b, 1.0)
+            buf, out = guarded((m, n), torch.float32, cuda)
+            T.chain_contract(dev_f32(a, cuda), dev_f32(b, cuda), out=out)
+            check_guards(buf, torch.float32)
+            assert np.abs(out.cpu().numpy() - want).max() <= 1e-5 * np.sqrt(k) * max(1.0, np.abs(want).max())
+            gt = T.chain_contract(dev_f32(a, cuda), dev_f32(np.ascontiguousarray(b.T), cuda), rhs_is_nk=True).cpu().numpy()
+            assert np.abs(gt - want).max() <= 1e-5 * np.sqrt(k) * max(1.0, np.abs(want).max())
+        # a lambda outside the ahead-of-time table (run-time compiled) with a piped map, on a size that needs both
+        a = rng.uniform(0, 1, (300, 100)).astype(np.float32)
+        b = rng.uniform(0, 1, (100, 200)).astype(np.float32)
+        got = T.chain_contract(dev_f32(a, cuda), dev_f32(b, cuda), "p0 * p1 + 0.5f", post_expr="sqrtf(p0)").cpu().numpy()
+        want = np.sqrt((a[:, :, None].astype(np.float64) * b[None, :, :] + 0.5).sum(1))
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+        # operands that start 4 bytes into an allocation: the scalar load path
+        big_a = torch.zeros(128 * 64 + 1, device=cuda)
+        av = big_a[1:].view(128, 64)
+        av.copy_(torch.from_numpy(rng.normal(0, 1, (128, 64)).astype(np.float32)))
+        bb = rng.normal(0, 1, (64, 128)).astype(np.float32)
+        got = T.chain_contract(av, dev_f32(bb, cuda)).cpu().numpy()
+        want = oracle.matmul_scale_f32(av.cpu().numpy(), bb, 1.0)
+        assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+    finally:
+        T.tune("gemm")
+
+
 # ----------------------------------------------------------------------------
 # host buffers: H2D, kernel and D2H pipelined over row chunks
 # ----------------------------------------------------------------------------
