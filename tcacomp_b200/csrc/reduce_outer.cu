@@ -17,6 +17,14 @@
 // "greater value, or equal value and lower index", which makes max and argmax
 // bit-exact against a sequential ascending fold with a strict `>` update.
 // Algorithmic bytes: 4 per input element plus 12 per output column.
+//
+// Few columns and a long k (column statistics of a tall matrix) leave fewer tiles than SMs. The k axis
+// is then also split over CTAs: each writes its partial (sum, best, best_index) per column to a scratch
+// buffer and a second small kernel folds the partials in ascending split order with the same tie rule.
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "common.cuh"
 
 namespace tcab {
@@ -40,7 +48,7 @@ template <int V, int CV, int KW, int UNROLL>
 __global__ void __launch_bounds__(32 * KW)
 reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float* __restrict__ mx,
                     int32_t* __restrict__ amax, uint32_t nb, uint32_t nk, uint32_t nc,
-                    uint32_t tiles_per_b) {
+                    uint32_t tiles_per_b, uint32_t ksplit, uint32_t klen, float* __restrict__ part) {
   constexpr int TILE_C = 32 * V * CV;
   constexpr int NCOL = V * CV;  // columns owned by a thread
   extern __shared__ float smem[];
@@ -50,10 +58,12 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-  for (uint32_t tile = blockIdx.x; tile < nb * tiles_per_b; tile += gridDim.x) {
+  for (uint32_t work = blockIdx.x; work < nb * tiles_per_b * ksplit; work += gridDim.x) {
+    const uint32_t tile = work / ksplit, ks = work % ksplit;  // ks: which range of k (one range unless split)
     const uint32_t b = tile / tiles_per_b;
     const uint32_t c0 = (tile % tiles_per_b) * TILE_C;
     const float* base = t + static_cast<size_t>(b) * nk * nc;
+    const uint32_t kbeg = ks * klen, kend = min(nk, kbeg + klen);
 
     float acc[NCOL], best[NCOL];
     int32_t bidx[NCOL];
@@ -68,14 +78,14 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
 #pragma unroll
     for (int i = 0; i < CV; ++i) colok[i] = c0 + (i * 32 + lane) * V < nc;  // nc % V == 0 when V == 4
 
-    for (uint32_t k0 = warp; k0 < nk; k0 += KW * UNROLL) {
+    for (uint32_t k0 = kbeg + warp; k0 < kend; k0 += KW * UNROLL) {
       float f[UNROLL][NCOL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * KW;
 #pragma unroll
         for (int i = 0; i < CV; ++i) {
-          if (k < nk && colok[i]) {
+          if (k < kend && colok[i]) {
             ColVec<V>::load(base + static_cast<size_t>(k) * nc + c0 + (i * 32 + lane) * V, &f[u][i * V]);
           } else {
 #pragma unroll
@@ -86,7 +96,7 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * KW;
-        if (k < nk) {
+        if (k < kend) {
 #pragma unroll
           for (int j = 0; j < NCOL; ++j) {
             const float v = f[u][j];
@@ -127,18 +137,89 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
           }
         }
         const size_t o = static_cast<size_t>(b) * nc + c0 + col;
-        if (sum) sum[o] = a;
-        if (mx) mx[o] = bv;
-        if (amax) amax[o] = bi;
+        if (ksplit > 1) {  // partial state of this k range: [3][ksplit][nb * nc]
+          const size_t plane = static_cast<size_t>(ksplit) * nb * nc, po = static_cast<size_t>(ks) * nb * nc + o;
+          part[po] = a;
+          part[plane + po] = bv;
+          part[2 * plane + po] = __int_as_float(bi);
+        } else {
+          if (sum) sum[o] = a;
+          if (mx) mx[o] = bv;
+          if (amax) amax[o] = bi;
+        }
       }
     }
     __syncthreads();  // shared memory is rewritten by the next tile
   }
 }
 
+// Folds the partial states of the k ranges, ascending: the same rule as the cross-warp combine above, so
+// the lowest index among equal maxima survives whichever range it came from.
+__global__ void __launch_bounds__(256)
+reduce_outer_finish(const float* __restrict__ part, float* __restrict__ sum, float* __restrict__ mx,
+                    int32_t* __restrict__ amax, uint32_t cells, uint32_t ksplit) {
+  const uint32_t o = blockIdx.x * 256 + threadIdx.x;
+  if (o >= cells) return;
+  const size_t plane = static_cast<size_t>(ksplit) * cells;
+  float a = 0.0f, bv = -INFINITY;
+  int32_t bi = 0;
+  for (uint32_t ks = 0; ks < ksplit; ++ks) {
+    const size_t po = static_cast<size_t>(ks) * cells + o;
+    a += part[po];
+    const float v = part[plane + po];
+    const int32_t vi = __float_as_int(part[2 * plane + po]);
+    if (v > bv || (v == bv && vi < bi)) {
+      bv = v;
+      bi = vi;
+    }
+  }
+  if (sum) sum[o] = a;
+  if (mx) mx[o] = bv;
+  if (amax) amax[o] = bi;
+}
+
+// Scratch for the partial states: kMaxPartialCells cells x 3 values per (device, stream), allocated the
+// first time a stream needs the split and kept until the process exits.
+constexpr uint32_t kMaxPartialCells = 262144;  // ksplit * nb * nc at most: 3 MiB
+float* outer_scratch(cudaStream_t stream) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, float*> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = table.find({dev, stream});
+  if (it != table.end()) return it->second;
+  float* p = nullptr;
+  if (cudaMalloc(&p, static_cast<size_t>(3) * kMaxPartialCells * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;  // no split then
+  }
+  table[{dev, stream}] = p;
+  return p;
+}
+
+// How many CTAs share the k axis of one (b, column tile): none while the tiles alone fill the GPU; otherwise as
+// many as make the whole grid resident at once (`resident` = CTAs of this kernel the GPU holds: one wave, no
+// tail), each with at least 256 k, within the scratch.
+uint32_t choose_ksplit(uint64_t tiles, uint32_t nb, uint32_t nk, uint32_t nc, uint64_t resident, int forced) {
+  const uint64_t cells = static_cast<uint64_t>(nb) * nc;
+  if (cells == 0 || cells > kMaxPartialCells) return 1;
+  uint64_t want;
+  if (forced > 0) {
+    want = static_cast<uint64_t>(forced);
+  } else {
+    if (tiles >= static_cast<uint64_t>(sm_count())) return 1;
+    want = resident / tiles;
+    if (want > nk / 256) want = nk / 256;
+  }
+  if (want > kMaxPartialCells / cells) want = kMaxPartialCells / cells;
+  if (want > nk) want = nk;
+  return want < 2 ? 1 : static_cast<uint32_t>(want);
+}
+
 template <int V, int CV, int KW, int UNROLL>
 int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, uint32_t nk, uint32_t nc,
-           int ctas_per_sm, cudaStream_t s) {
+           int ctas_per_sm, int forced_ksplit, cudaStream_t s) {
   constexpr int TILE_C = 32 * V * CV;
   constexpr int THREADS = 32 * KW;
   const size_t smem = static_cast<size_t>(3) * KW * TILE_C * sizeof(float);
@@ -149,13 +230,24 @@ int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, ui
   }
   const uint32_t tiles_per_b = (nc + TILE_C - 1) / TILE_C;
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
-  // one CTA per tile unless the tuning hook caps the grid (the tile loop then takes over)
-  uint64_t grid = ctas_per_sm > 0 ? static_cast<uint64_t>(sm_count()) * ctas_per_sm : tiles;
-  if (grid > tiles) grid = tiles;
+  const int occ = occupancy(reinterpret_cast<const void*>(fn), THREADS, smem);
+  uint32_t ksplit = choose_ksplit(tiles, nb, nk, nc, static_cast<uint64_t>(occ > 0 ? occ : 1) * sm_count(), forced_ksplit);
+  float* part = ksplit > 1 ? outer_scratch(s) : nullptr;
+  if (part == nullptr) ksplit = 1;
+  const uint32_t klen = ksplit > 1 ? (nk + ksplit - 1) / ksplit : nk;
+  const uint64_t work = tiles * ksplit;
+  // one CTA per unit of work unless the tuning hook caps the grid (the loop in the kernel then takes over)
+  uint64_t grid = ctas_per_sm > 0 ? static_cast<uint64_t>(sm_count()) * ctas_per_sm : work;
+  if (grid > work) grid = work;
   if (grid > 0x7fffffffull) grid = 0x7fffffffull;
-  fn<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b);
+  fn<<<static_cast<unsigned>(grid), THREADS, smem, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, ksplit, klen, part);
   count_launch();
-  return check_launch("reduce_outer_kernel");
+  int rc = check_launch("reduce_outer_kernel");
+  if (rc != TCAB_OK || ksplit == 1) return rc;
+  const uint32_t cells = nb * nc;
+  reduce_outer_finish<<<(cells + 255) / 256, 256, 0, s>>>(part, sum, mx, amax, cells, ksplit);
+  count_launch();
+  return check_launch("reduce_outer_finish");
 }
 
 }  // namespace
@@ -167,19 +259,19 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
     return fail(TCAB_ERR_TOO_LARGE, "reduce_outer: too many column tiles");
   const bool vec = (nc % 4 == 0) && aligned16(t);
   const Tune& tn = tune(kReduceOuter);
-  // p0: vectors per lane (1|2), p1: warps splitting k (4|8|16), p2: CTAs per SM.
+  // p0: vectors per lane (1|2), p1: warps splitting k (4|8|16), p2: CTAs per SM, p3: CTAs splitting k (forced).
   const int cv = tn.p0 > 0 ? tn.p0 : 1;
   const int kw = tn.p1 > 0 ? tn.p1 : 8;
   if (vec) {
-    if (cv == 1 && kw == 8) return launch<4, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
-    if (cv == 2 && kw == 8) return launch<4, 2, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
-    if (cv == 1 && kw == 16) return launch<4, 1, 16, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
-    if (cv == 2 && kw == 16) return launch<4, 2, 16, 2>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
-    if (cv == 1 && kw == 4) return launch<4, 1, 4, 8>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
-    if (cv == 2 && kw == 4) return launch<4, 2, 4, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+    if (cv == 1 && kw == 8) return launch<4, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
+    if (cv == 2 && kw == 8) return launch<4, 2, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
+    if (cv == 1 && kw == 16) return launch<4, 1, 16, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
+    if (cv == 2 && kw == 16) return launch<4, 2, 16, 2>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
+    if (cv == 1 && kw == 4) return launch<4, 1, 4, 8>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
+    if (cv == 2 && kw == 4) return launch<4, 2, 4, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
     return fail(TCAB_ERR_UNSUPPORTED, "reduce_outer: no kernel for tuned shape %d x %d", cv, kw);
   }
-  return launch<1, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, s);
+  return launch<1, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
 }
 
 }  // namespace tcab

@@ -381,6 +381,34 @@ def test_reduce_outer_full_size_properties(oracle, cuda):
     assert (np.abs(r["sum"][:2].cpu().numpy() - s) <= 1e-5 * np.abs(sl).sum(1)).all()
 
 
+@pytest.mark.parametrize("nb,nk,nc,forced", [(1, 100000, 64, 0), (2, 5000, 100, 0), (1, 70001, 33, 0), (3, 1000, 132, 7),
+                                              (1, 300, 8, 300), (2, 4097, 260, 5)])
+def test_reduce_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc, forced):
+    # few columns, long k: the k axis is split over CTAs and the partial states are folded by a second kernel
+    rng = np.random.default_rng(nk + nc)
+    t = rng.integers(-50, 51, (nb, nk, nc)).astype(np.float32)  # integers: many equal maxima, exact sums
+    t[0, nk // 2:, 1] = 50.0                                   # a tie that spans several k ranges
+    t[0, :, 2] = -np.inf
+    t[0, 5, 3] = np.inf
+    t[nb - 1, 7, 4] = np.nan
+    s, m, a = oracle.reduce_outer(t)
+    n0 = T.launch_count()
+    try:
+        T.tune("reduce_outer", 0, 0, 0, forced)
+        r = T.reduce_outer(dev_f32(t, cuda))
+    finally:
+        T.tune("reduce_outer")
+    assert T.launch_count() - n0 == 2, "expected the split kernel plus the finishing kernel"
+    assert np.array_equal(r["argmax"].cpu().numpy(), a)
+    assert np.array_equal(r["max"].cpu().numpy(), m, equal_nan=True)
+    got = r["sum"].cpu().numpy()
+    finite = np.isfinite(s)
+    assert np.array_equal(got[finite], s[finite])
+    assert np.array_equal(np.isnan(got), np.isnan(s)) and np.array_equal(np.isinf(got), np.isinf(s))
+    only = T.reduce_outer(dev_f32(t, cuda), want=("max",))
+    assert np.array_equal(only["max"].cpu().numpy(), m, equal_nan=True)
+
+
 def test_chain_outer_generic(oracle, cuda):
     rng = np.random.default_rng(31)
     x = rng.normal(0, 2, (5, 61, 70)).astype(np.float32)
