@@ -199,11 +199,19 @@ TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, cons
 TCAB_API int tcab_device_status(int* status);
 
 /* Tuning hook, no counterpart in the reference: overrides the heuristic launch shape of one kernel
- * family ("softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm") for this process:
- * p0, p1 = the launch shape (threads per row and vectors per thread for the row kernels, vectors per lane and
- * k-splitting warps for reduce_outer), p2 = CTAs per SM, p3 = a variant switch of the family.
- * Values <= 0 restore the heuristic. Meant for benchmarking sweeps; results never depend on it
- * beyond the fold order. */
+ * family for this process. Values <= 0 restore the heuristic. Meant for benchmarking sweeps and for
+ * tests that must reach every kernel variant; results never depend on it beyond the fold order.
+ *   "softmax", "layernorm": p0 = threads per row, p1 = vectors per thread, p2 = CTAs per SM (persistent
+ *       grid), p3 = variant (softmax: 1 no cluster kernel, 2 always; layernorm: 1 gamma/beta in registers,
+ *       2 no cluster kernel, 3 always).
+ *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
+ *       split path, p2 = 2 launches without programmatic dependent launch, p3 = CTAs sharing the k axis of a
+ *       middle-axis reduction.
+ *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
+ *       p3 = CTAs sharing the k axis.
+ *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
+ *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
+ *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128). */
 TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 
 #ifdef __cplusplus

@@ -253,8 +253,20 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   uint32_t tiles_per_b = (nc + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
-  void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps};
-  return launch(jc->k[vec ? kOuterV4 : kOuterV1], tiles, 256, a, s, "chain_outer");
+  // few column tiles and a long k: the k axis is split over CTAs too (same policy as the ahead-of-time path)
+  const cudaKernel_t kern = jc->k[vec ? kOuterV4 : kOuterV1];
+  const int occ = occupancy(reinterpret_cast<const void*>(kern), 256, 0);
+  uint32_t ksplit = split_scratch_or_null == nullptr
+                        ? 1u
+                        : choose_outer_splits(tiles, static_cast<uint64_t>(nb) * nc, nk,
+                                              static_cast<uint64_t>(occ > 0 ? occ : 1) * sm_count());
+  uint32_t klen = ksplit > 1 ? (nk + ksplit - 1) / ksplit : nk;
+  void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps, &ksplit, &klen, &split_scratch_or_null};
+  int rc = launch(kern, tiles * ksplit, 256, a, s, "chain_outer");
+  if (rc != TCAB_OK || ksplit == 1) return rc;
+  uint32_t rows32 = nb * nc;
+  void* a2[] = {&split_scratch_or_null, &out, &rows32, &ksplit, &init, &caps};
+  return launch(jc->k[kFinish], (rows32 + 127) / 128, 128, a2, s, "chain_split_finish");
 }
 
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,

@@ -195,16 +195,21 @@ chain_split_finish(const float* __restrict__ partials, float* __restrict__ out, 
 
 // Reduce over a MIDDLE axis: operands are [nb, nk, nc]; a CTA owns (one b, a
 // tile of 32*V columns), lane l owns V columns, warp w owns k = w, w+KW, ...
+// With ksplit > 1 the k axis is also cut into ksplit ranges of klen, one CTA each (few columns, long k):
+// a CTA then writes the fold of its range -- without init and without the piped map -- to
+// partials[cell * ksplit + range], and chain_split_finish folds the ranges in ascending order.
 template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL>
 __global__ void __launch_bounds__(32 * KW)
 chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, float init,
-            Caps caps) {
+            Caps caps, u32 ksplit, u32 klen, float* __restrict__ partials) {
   typedef Comb<COMBINE> C;
   constexpr int TILE_C = 32 * V;
   __shared__ float s_part[KW][TILE_C];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-  for (u32 tile = blockIdx.x; tile < nb * tiles_per_b; tile += gridDim.x) {
+  for (u32 work = blockIdx.x; work < nb * tiles_per_b * ksplit; work += gridDim.x) {
+    const u32 tile = work / ksplit, ks = work % ksplit;
+    const u32 kbeg = ks * klen, kend = (nk - kbeg < klen) ? nk : kbeg + klen;
     const u32 b = tile / tiles_per_b;
     const u32 c0 = (tile % tiles_per_b) * TILE_C;
     const u32 col = c0 + lane * V;
@@ -216,12 +221,12 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
     for (int j = 0; j < V; ++j) acc[j] = C::identity();
 
     if (colok) {
-      for (u32 k0 = warp; k0 < nk; k0 += KW * UNROLL) {
+      for (u32 k0 = kbeg + warp; k0 < kend; k0 += KW * UNROLL) {
         float f[UNROLL][NIN][V];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const u32 k = k0 + u * KW;
-          if (k < nk) {
+          if (k < kend) {
 #pragma unroll
             for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a] + base + static_cast<u64>(k) * nc, 0, f[u][a]);
           }
@@ -229,7 +234,7 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const u32 k = k0 + u * KW;
-          if (k < nk) {
+          if (k < kend) {
 #pragma unroll
             for (int j = 0; j < V; ++j) {
               float p[NIN];
@@ -246,11 +251,16 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
     __syncthreads();
     for (int c = threadIdx.x; c < TILE_C; c += 32 * KW) {
       if (c0 + c < nc) {
-        float a = init;
+        float a = ksplit > 1 ? C::identity() : init;
 #pragma unroll
         for (int w = 0; w < KW; ++w) a = C::apply(a, s_part[w][c]);
-        float r[1] = {a};
-        out[static_cast<u64>(b) * nc + c0 + c] = Post::apply(r, caps.c + 8);
+        const u64 cell = static_cast<u64>(b) * nc + c0 + c;
+        if (ksplit > 1) {
+          partials[cell * ksplit + ks] = a;
+        } else {
+          float r[1] = {a};
+          out[cell] = Post::apply(r, caps.c + 8);
+        }
       }
     }
     __syncthreads();
@@ -265,8 +275,8 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 // columns apart (TM = 4: 64x64 tiles for small problems; TM = 8: 128x128 tiles). K advances in
 // shared-memory tiles of 16, double-buffered: the next tile's global loads (16-byte vectors where the
 // row pitch allows) are in registers while the current one is multiplied. Operands whose k runs fastest
-// in memory are stored transposed, so that the inner loop reads 16-byte vectors along m and n; the row
-// pitch of 16 TM + 4 floats keeps those transposing stores conflict-free.
+// in memory are stored transposed, so that the inner loop reads 16-byte vectors along m and n (the row
+// pitch of 16 TM + 4 floats keeps those vectors aligned and the transposing stores at two-way conflicts).
 // Each output is folded over k in ascending order by one thread -- the order of the reference's CPU
 // loops (testing/runners/gemm.cu:44-56). Rows and columns past the edge are computed on zero padding
 // and never stored; k past the edge never reaches the lambda.

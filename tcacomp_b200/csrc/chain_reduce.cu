@@ -47,9 +47,31 @@ TCAB_LAMBDA(PostAddTanh, 1, (p0 + (c0 * tanhf(p0))))
 TCAB_LAMBDA(PostScale, 1, (p0 * c0))
 
 // Partials of the multi-CTA split: at most this many per launch.
-constexpr uint32_t kMaxSplitPartials = 16384;
+constexpr uint32_t kMaxSplitPartials = 262144;  // 1 MiB per (device, stream)
 
 float* split_scratch(cudaStream_t stream);
+
+}  // namespace
+
+// Middle-axis reductions with fewer column tiles than SMs and a long k: how many CTAs share the k axis of a
+// tile (1 = no split) -- as many as make the grid one resident wave, at least 256 k each, within the scratch.
+uint32_t choose_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident) {
+  const Tune& tn = tune(kReduceInner);
+  if (cells == 0 || cells > kMaxSplitPartials || tiles == 0) return 1;
+  uint64_t want;
+  if (tn.p3 > 0) {
+    want = static_cast<uint64_t>(tn.p3);  // forced by the tuning hook
+  } else {
+    if (tiles >= static_cast<uint64_t>(sm_count())) return 1;
+    want = resident / tiles;
+    if (want > nk / 256) want = nk / 256;
+  }
+  if (want > kMaxSplitPartials / cells) want = kMaxSplitPartials / cells;
+  if (want > nk) want = nk;
+  return want < 2 ? 1 : static_cast<uint32_t>(want);
+}
+
+namespace {
 
 struct Args {
   const float* const* ins;
@@ -105,11 +127,24 @@ int launch_outer(const Args& a) {
   const uint32_t tiles_per_b = (nc + 32 * V - 1) / (32 * V);
   const uint64_t tiles = a.outer * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
-  const uint64_t grid = tiles > 0x7fffffffull ? 0x7fffffffull : tiles;  // one CTA per tile
+  const uint64_t cells = a.outer * nc;
+  const int occ = occupancy(reinterpret_cast<const void*>(fn), 32 * KW, 0);
+  uint32_t ksplit = choose_outer_splits(tiles, cells, a.nk, static_cast<uint64_t>(occ > 0 ? occ : 1) * sm_count());
+  float* scratch = ksplit > 1 ? split_scratch(a.stream) : nullptr;
+  if (scratch == nullptr) ksplit = 1;
+  const uint32_t klen = ksplit > 1 ? (a.nk + ksplit - 1) / ksplit : a.nk;
+  const uint64_t work = tiles * ksplit;
+  const uint64_t grid = work > 0x7fffffffull ? 0x7fffffffull : work;  // one CTA per tile (and k range)
   fn<<<static_cast<unsigned>(grid), 32 * KW, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,
-                                                          tiles_per_b, a.init, a.caps);
+                                                          tiles_per_b, a.init, a.caps, ksplit, klen, scratch);
   count_launch();
-  return check_launch("chain_outer");
+  int rc = check_launch("chain_outer");
+  if (rc != TCAB_OK || ksplit == 1) return rc;
+  const uint32_t rows = static_cast<uint32_t>(cells);
+  tcabk::chain_split_finish<Post, COMBINE>
+      <<<(rows + 127) / 128, 128, 0, a.stream>>>(scratch, a.out, rows, ksplit, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_split_finish");
 }
 
 // How many CTAs share one row: 1 = no split. A split pays off when there are fewer rows than SMs and
@@ -312,6 +347,8 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
       for (int i = 0; i < pc.n_in; ++i) al = al && aligned16(ins[i]);
       splits = choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
       if (splits > 1) scratch = split_scratch(s);
+    } else if (outer * ((inner + 127) / 128) < static_cast<uint64_t>(sm_count()) && nk >= 512) {
+      scratch = split_scratch(s);  // a middle-axis reduction that may split k over CTAs (decided at launch)
     }
     return jit_launch(h, ins, outer, nk, inner, pc.init, pc.caps, out, scratch, splits, s);
   }

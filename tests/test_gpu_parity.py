@@ -409,6 +409,31 @@ def test_reduce_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc, forced):
     assert np.array_equal(only["max"].cpu().numpy(), m, equal_nan=True)
 
 
+@pytest.mark.parametrize("nb,nk,nc", [(1, 50000, 64), (2, 7001, 100), (1, 4096, 33), (3, 600, 260)])
+def test_chain_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc):
+    # middle-axis lambda chains with few columns and a long k: k ranges over CTAs + the finishing kernel
+    rng = np.random.default_rng(nk)
+    x = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
+    z = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
+    xd, zd = dev_f32(x, cuda), dev_f32(z, cuda)
+    n0 = T.launch_count()
+    got = T.chain_reduce([xd, zd], "p0 * p1", axis=1).cpu().numpy()          # ahead-of-time lambda
+    assert T.launch_count() - n0 == 2
+    want = (x.astype(np.float64) * z).sum(1)
+    assert (np.abs(got - want) <= 1e-5 * np.abs(x.astype(np.float64) * z).sum(1)).all()
+    n0 = T.launch_count()
+    got = T.chain_reduce([xd], "expf(p0) * 0.5f", axis=1, post_expr="p0 + 1.0f").cpu().numpy()   # run-time compiled
+    assert T.launch_count() - n0 == 2
+    want = (np.exp(x.astype(np.float64)) * 0.5).sum(1) + 1.0
+    assert (np.abs(got - want) <= 2e-5 * np.abs(want)).all()
+    got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=-np.inf, axis=1).cpu().numpy()
+    assert np.array_equal(got, x.max(1))                                       # order-independent: bit-exact
+    # init enters exactly once, whatever the number of ranges
+    got = T.chain_reduce([xd, zd], "p0 * p1", axis=1, init=100.0).cpu().numpy()
+    want = (x.astype(np.float64) * z).sum(1) + 100.0
+    assert (np.abs(got - want) <= 1e-5 * (np.abs(x.astype(np.float64) * z).sum(1) + 100.0)).all()
+
+
 def test_chain_outer_generic(oracle, cuda):
     rng = np.random.default_rng(31)
     x = rng.normal(0, 2, (5, 61, 70)).astype(np.float32)
