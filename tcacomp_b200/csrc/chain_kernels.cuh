@@ -97,10 +97,23 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   const u32 nvec = nk / V;
   u32 iter = 0;
   // Programmatic dependent launch: when the launcher allowed this grid to start before the previous
-  // grid of the stream has finished, wait here (before the first global access) until it has, and let
-  // the next grid of the stream begin its own launch now. Both are no-ops for an ordinary launch.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // grid of the stream has finished, let the next grid begin its own launch now and wait here (before the
+  // first global access that returns data) until the previous grid has finished. Both are no-ops for an
+  // ordinary launch. While waiting, each row group asks the L2 to fetch its first row: a prefetch moves
+  // lines from DRAM into the L2, the point where all SMs' writes meet, and returns nothing to the SM, so
+  // it cannot observe a stale value even if the previous grid is still writing that row; it turns the
+  // DRAM latency of a short kernel's first loads into overlap with the previous kernel's tail.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if constexpr (V == 4) {
+    const u64 first = static_cast<u64>(blockIdx.x) * GROUPS + g;
+    if (t == 0 && first < rows && nk >= 4) {
+      const u32 bytes = nk * 4u < 65536u ? nk * 4u : 65536u;  // nk % 4 == 0 and 16-byte aligned rows on this path
+#pragma unroll
+      for (int a = 0; a < NIN; ++a)
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ins.p[a] + first * nk), "r"(bytes) : "memory");
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   for (u64 row0 = static_cast<u64>(blockIdx.x) * GROUPS; row0 < rows;
        row0 += static_cast<u64>(gridDim.x) * GROUPS, ++iter) {
