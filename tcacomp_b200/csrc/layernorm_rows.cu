@@ -192,8 +192,10 @@ template <typename T, int THREADS, int VPT, int V>
 int launch_cluster_shape(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
                          uint32_t nvec, cudaStream_t s) {
   constexpr uint32_t kPerCta = THREADS * VPT;
-  uint32_t cs = 2;
-  while (cs < 8 && static_cast<uint64_t>(cs) * kPerCta < nvec) cs *= 2;
+  // the smallest cluster (2..8 CTAs, any size) whose CTAs cover the row
+  uint32_t cs = (nvec + kPerCta - 1) / kPerCta;
+  if (cs < 2) cs = 2;
+  if (cs > 8) cs = 8;
   const uint32_t seg = (nvec + cs - 1) / cs;
   auto* fn = layernorm_rows_cluster<T, THREADS, VPT, V>;
   cudaLaunchConfig_t cfg = {};
@@ -219,6 +221,11 @@ int launch_cluster_shape(const T* x, const T* gamma, const T* beta, float eps, T
 template <typename T, int V>
 int launch_cluster(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
                    uint32_t nvec, cudaStream_t s) {
+  const Tune& tn = tune(kLayernorm);
+  // 256-thread CTAs while eight of them cover the row (several fit an SM, so a CTA waiting at a cluster
+  // barrier does not idle it); tune p2 = 4 / 8 / 16 picks the vectors per thread of the 256-thread shape
+  if (tn.p2 == 4 || (tn.p2 <= 0 && nvec <= 8u * 256u * 4u)) return launch_cluster_shape<T, 256, 4, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
+  if (tn.p2 == 8 || (tn.p2 <= 0 && nvec <= 8u * 256u * 8u)) return launch_cluster_shape<T, 256, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
   return launch_cluster_shape<T, 512, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
 }
 
@@ -304,7 +311,7 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   const uint32_t nvec = vec ? cols / VW : cols;
   const Tune& tn = tune(kLayernorm);
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape(nvec, 4, &tpr, &vpt);
+  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;
@@ -315,7 +322,7 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   // single-CTA kernels are faster (4.3 vs 2.6 TB/s at 4096 x 65536: three cluster barriers per row are
   // not hidden), so the cluster is used only while the rows alone cannot fill the SMs. p3 == 3 forces it.
   const bool few_rows = rows < 2ull * sm_count() && nvec > 8192;
-  if (tn.p0 <= 0 && nvec > 4096 && nvec <= 8u * 4096u && rows * 8 <= 0x7fffffffull && tn.p3 != 2 &&
+  if (tn.p0 <= 0 && nvec > (tn.p3 == 3 ? 1024u : 4096u) && nvec <= 8u * 4096u && rows * 8 <= 0x7fffffffull && tn.p3 != 2 &&
       ((few_rows && nvec <= 16384) || tn.p3 == 3))
     return vec ? launch_cluster<T, VW>(x, gamma, beta, eps, y, rows, cols, nvec, s)
                : launch_cluster<T, 1>(x, gamma, beta, eps, y, rows, cols, nvec, s);

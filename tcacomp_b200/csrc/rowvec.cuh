@@ -141,4 +141,40 @@ inline bool choose_row_shape(uint32_t nvec, int vpt_target, int* tpr, int* vpt) 
   return true;
 }
 
+// The same choice with exact fits in mind. The row kernels skip vector slots that cannot hold data (a thread
+// uses ceil(nvec / TPR) of its VPT slots), so what a shape wastes is only the idle threads of the last used
+// slot: used * TPR / nvec. Among the compiled shapes -- (TPR, 4) for every power of two, (8, 1), (8, 2),
+// (1024, 8..32) and, for 16-byte vectors, (128, 8), (256, 8), (64, 16), (32, 32) [plus (512, 8) and (64, 8)
+// where `wide8`] -- this picks the least waste, preferring fewer slots and 128..512 threads on a tie, and
+// staying at 32 row values per thread unless that wastes more than a third.
+inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values_per_vector, int* tpr, int* vpt) {
+  if (nvec == 0) nvec = 1;
+  struct Shape { int t, v; bool vec_only, wide_only; };
+  static const Shape kShapes[] = {
+      {8, 1, false, false},   {8, 2, false, false},    {8, 4, false, false},    {16, 4, false, false},
+      {32, 4, false, false},  {64, 4, false, false},   {128, 4, false, false},  {256, 4, false, false},
+      {512, 4, false, false}, {1024, 4, false, false}, {1024, 8, false, false}, {1024, 16, false, false},
+      {1024, 32, false, false}, {128, 8, true, false}, {256, 8, true, false},   {64, 16, true, false},
+      {32, 32, true, false},  {512, 8, true, true},    {64, 8, true, true}};
+  double best = 1e30;
+  bool found = false;
+  for (const Shape& sh : kShapes) {
+    if ((sh.vec_only && !vec) || (sh.wide_only && !wide8)) continue;
+    if (static_cast<uint64_t>(sh.t) * sh.v < nvec) continue;
+    const uint32_t used = (nvec + sh.t - 1) / sh.t;
+    double score = static_cast<double>(used) * sh.t / nvec;        // 1.0 = exact fit
+    score *= 1.0 + 0.01 * (sh.v > 4 ? (sh.v > 8 ? 6 : 3) : 0);     // more slots: more registers, fewer resident rows
+    if (sh.v * values_per_vector > 32) score *= 1.35;              // beyond 32 row values per thread the kernels lose occupancy
+    if (sh.t >= 1024) score *= 1.15;                               // 1024-thread CTAs move in lock step
+    else if (sh.t < 32 && nvec > 32) score *= 1.10;                // short groups: strided 16-byte loads
+    if (score < best - 1e-9) {
+      best = score;
+      *tpr = sh.t;
+      *vpt = sh.v;
+      found = true;
+    }
+  }
+  return found;
+}
+
 }  // namespace tcab

@@ -36,6 +36,7 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
   const int g = threadIdx.x / TPR;
   const int t = threadIdx.x % TPR;
   const uint32_t nvec = cols / V;
+  const int used = static_cast<int>((nvec + TPR - 1) / TPR);
 
   for (uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * GROUPS; row0 < rows;
        row0 += static_cast<uint64_t>(gridDim.x) * GROUPS) {
@@ -44,32 +45,41 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
     const float* xr = x + row * cols;
     float* yr = y + row * cols;
 
+    // `used` vector slots of each thread can hold data for this row length (the same for every thread);
+    // the slots beyond it are skipped as a whole, so a row shorter than TPR * VPT vectors costs no
+    // arithmetic for the padding
     float v[VPT][V];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const uint32_t idx = t + i * TPR;
-      if (live && idx < nvec) {
-        IO::unpack(IO::load(xr, idx), v[i]);
-      } else {
+      if (i < used) {
+        const uint32_t idx = t + i * TPR;
+        if (live && idx < nvec) {
+          IO::unpack(IO::load(xr, idx), v[i]);
+        } else {
 #pragma unroll
-        for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;  // identity of max; expf(-inf - m) = 0
+          for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;  // identity of max; expf(-inf - m) = 0
+        }
       }
     }
 
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
+      if (i < used) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+        for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+      }
     m = group_allreduce<OpMax, TPR>(m, slots[0], g);
 
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
+      if (i < used) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        v[i][j] = expf(v[i][j] - m);
-        s += v[i][j];
+        for (int j = 0; j < V; ++j) {
+          v[i][j] = expf(v[i][j] - m);
+          s += v[i][j];
+        }
       }
     s = group_allreduce<OpSum, TPR>(s, slots[1], g);
     const float inv = 1.0f / s;
@@ -77,7 +87,7 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const uint32_t idx = t + i * TPR;
-      if (live && idx < nvec) {
+      if (i < used && live && idx < nvec) {
 #pragma unroll
         for (int j = 0; j < V; ++j) v[i][j] *= inv;
         IO::store(yr, idx, IO::pack(v[i]));
@@ -105,22 +115,27 @@ softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_
   float* yr = y + row * cols;
   (void)rows;
 
+  const int used = static_cast<int>((seg_vecs + THREADS - 1) / THREADS);  // vector slots that can hold data
   float v[VPT][V];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
-    if (idx < v1) {
-      IO::unpack(IO::load(xr, idx), v[i]);
-    } else {
+    if (i < used) {
+      const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+      if (idx < v1) {
+        IO::unpack(IO::load(xr, idx), v[i]);
+      } else {
 #pragma unroll
-      for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;
+        for (int j = 0; j < V; ++j) v[i][j] = -INFINITY;
+      }
     }
   }
   float m = -INFINITY;
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
+    if (i < used) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+      for (int j = 0; j < V; ++j) m = fmaxf(m, v[i][j]);
+    }
   m = cta_allreduce<OpMax, THREADS / 32>(m, slots[0]);
   if (threadIdx.x == 0) cl_max = m;
   cluster_sync_all();
@@ -130,10 +145,12 @@ softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
+    if (i < used) {
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      v[i][j] = expf(v[i][j] - gm);
-      s += v[i][j];
+      for (int j = 0; j < V; ++j) {
+        v[i][j] = expf(v[i][j] - gm);
+        s += v[i][j];
+      }
     }
   s = cta_allreduce<OpSum, THREADS / 32>(s, slots[1]);
   if (threadIdx.x == 0) cl_sum = s;
@@ -144,7 +161,7 @@ softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const uint32_t idx = v0 + threadIdx.x + i * THREADS;
-    if (idx < v1) {
+    if (i < used && idx < v1) {
 #pragma unroll
       for (int j = 0; j < V; ++j) v[i][j] *= inv;
       IO::store(yr, idx, IO::pack(v[i]));
@@ -156,8 +173,10 @@ softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_
 template <int THREADS, int VPT, int V>
 int launch_cluster_shape(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
   constexpr uint32_t kPerCta = THREADS * VPT;
-  uint32_t cs = 2;
-  while (cs < 8 && static_cast<uint64_t>(cs) * kPerCta < nvec) cs *= 2;
+  // the smallest cluster (2..8 CTAs, any size) whose CTAs cover the row
+  uint32_t cs = (nvec + kPerCta - 1) / kPerCta;
+  if (cs < 2) cs = 2;
+  if (cs > 8) cs = 8;
   const uint32_t seg = (nvec + cs - 1) / cs;
   auto* fn = softmax_rows_cluster<8, THREADS, VPT, V>;
   cudaLaunchConfig_t cfg = {};
@@ -265,16 +284,17 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   const uint32_t nvec = vec ? cols / 4 : cols;
   const Tune& tn = tune(kSoftmax);
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape(nvec, 4, &tpr, &vpt);
+  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;
     fits = true;
   }
-  // Rows beyond 8192 vectors go to the cluster kernel (up to 8 CTAs x 8192 vectors), unless the tuning
-  // hook asked for a single-CTA shape; rows beyond that, or more rows than the grid can index, stream.
+  // Rows beyond 2048 vectors go to the cluster kernel (2..8 CTAs of 256 threads x 8 vectors while that covers
+  // the row: measured 6.1 against 4.4 TB/s for one 1024-thread CTA at 16384 columns), unless the tuning hook
+  // asked for a single-CTA shape; rows beyond 8 x 8192 vectors, or more rows than the grid can index, stream.
   const bool long_class = nvec > 8u * 256u * 16u;  // 512-thread CTAs: they pay off only while the GPU is not full
-  if (tn.p0 <= 0 && nvec > 8192 && nvec <= 8u * 8192u && rows * 8 <= 0x7fffffffull && tn.p3 != 1 &&
+  if (tn.p0 <= 0 && nvec > 2048u && nvec <= 8u * 8192u && rows * 8 <= 0x7fffffffull && tn.p3 != 1 &&
       (!long_class || rows < 2ull * sm_count() || tn.p3 == 2))
     return vec ? launch_cluster<4>(x, y, rows, cols, nvec, s) : launch_cluster<1>(x, y, rows, cols, nvec, s);
   if (fits) {
