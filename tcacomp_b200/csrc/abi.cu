@@ -184,7 +184,11 @@ uint64_t tcab_launch_count(void) { return g_launches.load(std::memory_order_rela
 int tcab_device_status(int* status) {
   if (status == nullptr) return fail(TCAB_ERR_INVALID_ARG, "device_status: null output");
   TCAB_TRY(have_device("device_status"));
-  return gemm_device_status(status);
+  int gemm = 0, rows = 0;
+  TCAB_TRY(gemm_device_status(&gemm));
+  TCAB_TRY(rows_smem_status(&rows));
+  *status = gemm != 0 ? gemm : (rows != 0 ? 16 : 0);  // 1..4: a contraction kernel, 16: a shared-memory row kernel
+  return TCAB_OK;
 }
 
 int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {

@@ -48,6 +48,14 @@ inline uint32_t pow2_ceil(uint32_t v) {
 
 // Entry points of the operator classes (one .cu each).
 int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
+// long rows held in shared memory (rows_smem.cu); the caller has checked 16-byte vectors and rows_smem_fits
+bool rows_smem_fits(uint64_t row_bytes);
+int rows_smem_status(int* out);
+int launch_softmax_rows_smem(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
+int launch_layernorm_rows_smem_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
+                                    float eps, __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s);
+int launch_layernorm_rows_smem_f32(const float* x, const float* gamma, const float* beta, float eps, float* y,
+                                   uint64_t rows, uint32_t cols, cudaStream_t s);
 int launch_layernorm_rows_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma,
                                const __nv_bfloat16* beta, float eps, __nv_bfloat16* y,
                                uint64_t rows, uint32_t cols, cudaStream_t s);

@@ -303,6 +303,15 @@ int launch_reg(const T* x, const T* gamma, const T* beta, float eps, T* y, uint6
 #define TCAB_LN_SHAPES_EXTRA(X) \
   X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(1024, 1) X(256, 8) X(512, 8) X(64, 8) X(128, 2) X(256, 2)
 
+inline int launch_smem(const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta, float eps,
+                       __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
+  return launch_layernorm_rows_smem_bf16(x, gamma, beta, eps, y, rows, cols, s);
+}
+inline int launch_smem(const float* x, const float* gamma, const float* beta, float eps, float* y, uint64_t rows,
+                       uint32_t cols, cudaStream_t s) {
+  return launch_layernorm_rows_smem_f32(x, gamma, beta, eps, y, rows, cols, s);
+}
+
 template <typename T, int VW>
 int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
              cudaStream_t s) {
@@ -317,6 +326,13 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
     vpt = tn.p1;
     fits = true;
   }
+  // Long fp32 rows with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu), measured
+  // 4.0-5.0 TB/s against 3.3-4.8 for the 1024-thread register kernels from 10240 columns on. For bf16 the three
+  // passes over shared memory unpack every element three times and lose to the register kernels, so bf16 rows
+  // stay there. p3 == 4 forces the shared-memory kernel.
+  if (vec && tn.p0 <= 0 && rows_smem_fits(static_cast<uint64_t>(cols) * sizeof(T)) &&
+      (tn.p3 == 4 || (tn.p3 <= 0 && sizeof(T) == 4 && nvec >= 2560 && rows >= static_cast<uint64_t>(sm_count()))))
+    return launch_smem(x, gamma, beta, eps, y, rows, cols, s);
   // Few long rows go to the cluster kernel (2-8 CTAs x 4096 vectors share a row, so a handful of rows
   // still spreads over the GPU: 64 x 131072 bf16 runs at 1.75 TB/s instead of 1.10). With many rows the
   // single-CTA kernels are faster (4.3 vs 2.6 TB/s at 4096 x 65536: three cluster barriers per row are

@@ -409,6 +409,42 @@ def test_reduce_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc, forced):
     assert np.array_equal(only["max"].cpu().numpy(), m, equal_nan=True)
 
 
+@pytest.mark.parametrize("rows,cols", [(3, 4096), (151, 12288), (300, 8200), (149, 45056), (5, 16), (450, 4100)])
+def test_rows_in_shared_memory(oracle, cuda, rows, cols):
+    # the shared-memory row kernels (bulk asynchronous copies into a ring of slots, three passes), forced through the
+    # tuning hook: one slot and many, a ragged last slot, fewer rows than SMs and several rows per CTA
+    rng = np.random.default_rng(rows + cols)
+    x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
+    x[0, :7] = -np.inf
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    try:
+        T.tune("softmax", 0, 0, 0, 3)
+        n0 = T.launch_count()
+        T.softmax_rows(dev_f32(x, cuda), out=out)
+        assert T.launch_count() - n0 == 1
+    finally:
+        T.tune("softmax")
+    check_guards(buf, torch.float32)
+    from oracle import checks
+    assert checks.softmax_close(out.cpu().numpy(), x)
+    g32 = rng.normal(1, 0.1, cols).astype(np.float32)
+    b32 = rng.normal(0, 0.1, cols).astype(np.float32)
+    xl = rng.normal(0.5, 2, (rows, cols)).astype(np.float32)
+    try:
+        T.tune("layernorm", 0, 0, 0, 4)
+        got32 = T.layernorm_rows(dev_f32(xl, cuda), dev_f32(g32, cuda), dev_f32(b32, cuda), 1e-5).cpu().numpy()
+        xb, gb, bb = oracle.f32_to_bf16(xl), oracle.f32_to_bf16(g32), oracle.f32_to_bf16(b32)
+        got16 = T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5)
+    finally:
+        T.tune("layernorm")
+    ref32 = T.layernorm_rows(dev_f32(xl, cuda), dev_f32(g32, cuda), dev_f32(b32, cuda), 1e-5).cpu().numpy()
+    want = oracle.layernorm_rows_f32(xl, g32, b32, 1e-5)
+    assert np.abs(got32 - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    assert np.abs(got32 - ref32).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    assert checks.layernorm_bf16_close(got16.view(torch.int16).cpu().numpy().view(np.uint16), xb, gb, bb)
+    assert T.device_status() == 0
+
+
 @pytest.mark.parametrize("nb,nk,nc", [(1, 50000, 64), (2, 7001, 100), (1, 4096, 33), (3, 600, 260)])
 def test_chain_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc):
     # middle-axis lambda chains with few columns and a long k: k ranges over CTAs + the finishing kernel
