@@ -240,7 +240,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
       void* a2[] = {&split_scratch_or_null, &out, &rows32, &sp, &init, &caps};
       return launch(jc->k[kFinish], (rows + 127) / 128, 128, a2, s, "chain_split_finish");
     }
-    const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec <= 2048 ? 2 : 3;
+    const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec < 1024 ? 2 : 3;  // the same thresholds as the ahead-of-time path
     const int tpr = t == 0 ? 1 : t == 1 ? 4 : t == 2 ? 32 : 256;
     const int threads = tpr > 128 ? tpr : 128;
     const uint64_t groups = threads / tpr;
