@@ -222,10 +222,10 @@ template <typename T, int V>
 int launch_cluster(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
                    uint32_t nvec, cudaStream_t s) {
   const Tune& tn = tune(kLayernorm);
-  // 256-thread CTAs while eight of them cover the row (several fit an SM, so a CTA waiting at a cluster
-  // barrier does not idle it); tune p2 = 4 / 8 / 16 picks the vectors per thread of the 256-thread shape
-  if (tn.p2 == 4 || (tn.p2 <= 0 && nvec <= 8u * 256u * 4u)) return launch_cluster_shape<T, 256, 4, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
-  if (tn.p2 == 8 || (tn.p2 <= 0 && nvec <= 8u * 256u * 8u)) return launch_cluster_shape<T, 256, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
+  // 512 threads x 8 vectors per CTA; the 256-thread shapes (tune p2 = 4 / 8 vectors per thread, for sweeps)
+  // measured slower for layer-norm
+  if (tn.p2 == 4 && nvec <= 8u * 256u * 4u) return launch_cluster_shape<T, 256, 4, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
+  if (tn.p2 == 8 && nvec <= 8u * 256u * 8u) return launch_cluster_shape<T, 256, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
   return launch_cluster_shape<T, 512, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
 }
 
