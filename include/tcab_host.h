@@ -40,6 +40,14 @@ TCAB_API const char* tcab_module_kernel_output(const tcab_module* m, uint32_t i)
  * NULL with a message when the chain has no kernel class. */
 TCAB_API const char* tcab_module_kernel_class(const tcab_module* m, uint32_t i);
 
+/* What the kernel lowers to, as newline-separated key=value lines (the pointer lives as long as the module):
+ * class, out, inputs (comma-separated tensor names in operand order), and for the chain classes map, combine,
+ * post (canonical lambda text over p0.. and c0..: what tcab_chain_reduce / tcab_chain_contract receive), init,
+ * captures (scalar parameter of each capture slot), axis (reduced position) or rhs_is_nk; for gemm_bias_act
+ * a, b, bias, act; always scalars (the scalar parameters in declaration order). NULL with a message when the
+ * chain has no kernel class. */
+TCAB_API const char* tcab_module_kernel_describe(const tcab_module* m, uint32_t i);
+
 /* Launches kernel `kernel` (its launcher name) asynchronously on `stream` (a cudaStream_t). Every tensor
  * parameter and the output must be bound in tensor_names/tensors, every scalar parameter in
  * scalar_names/scalars. Shapes are checked the way the generated launcher checks them

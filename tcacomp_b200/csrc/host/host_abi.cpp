@@ -1,4 +1,5 @@
 // host_abi.cpp -- the C entry points of include/tcab_host.h over ParseModule / Classify / Launch.
+#include <cstdio>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -10,6 +11,7 @@ using namespace tcab::pkg;
 
 struct tcab_module {
   std::vector<ParsedKernel> kernels;
+  mutable std::vector<std::string> described;  // one text per kernel, built on first request
 };
 
 namespace {
@@ -84,6 +86,47 @@ const char* tcab_module_kernel_class(const tcab_module* m, uint32_t i) {
     case Plan::GemmBiasAct: return "gemm_bias_act";
   }
   return nullptr;
+}
+
+const char* tcab_module_kernel_describe(const tcab_module* m, uint32_t i) {
+  const ParsedKernel* k = kernel_at(m, i);
+  if (k == nullptr) return nullptr;
+  if (k->graph.statements.empty()) {
+    g_error = "kernel has no statement";
+    return nullptr;
+  }
+  auto plan = Classify(k->graph.statements[0]);
+  if (!plan.ok()) {
+    g_error = plan.err;
+    return nullptr;
+  }
+  auto join = [](const std::vector<std::string>& v) {
+    std::string s;
+    for (size_t j = 0; j < v.size(); ++j) s += (j ? "," : "") + v[j];
+    return s;
+  };
+  const Plan& p = plan.value;
+  std::string d;
+  if (p.kind == Plan::GemmBiasAct) {
+    d = "class=gemm_bias_act\nout=" + p.out + "\ninputs=" + p.a + "," + p.b + (p.bias.empty() ? "" : "," + p.bias) +
+        "\na=" + p.a + "\nb=" + p.b + "\nbias=" + p.bias + "\nact=" + (p.act == TCAB_ACT_RELU ? "relu" : "none") + "\n";
+  } else {
+    char init[64];
+    std::snprintf(init, sizeof(init), "%.9g", static_cast<double>(p.init));
+    d = std::string("class=") + (p.kind == Plan::ChainReduce ? "chain_reduce" : "chain_contract") + "\nout=" + k->output +
+        "\ninputs=" + join(p.inputs) + "\nmap=" + p.map_expr + "\ncombine=" + p.combine_expr + "\npost=" + p.post_expr +
+        "\ninit=" + init + "\ncaptures=" + join(p.capture_names) + "\n";
+    d += p.kind == Plan::ChainReduce ? "axis=" + std::to_string(p.reduce_axis) + "\n"
+                                     : std::string("rhs_is_nk=") + (p.rhs_is_nk ? "1" : "0") + "\n";
+  }
+  {
+    std::vector<std::string> names;
+    for (const auto& sc : k->graph.scalars) names.push_back(sc.first);
+    d += "scalars=" + join(names) + "\n";  // the kernel's scalar parameters in declaration order
+  }
+  if (m->described.size() < m->kernels.size()) m->described.resize(m->kernels.size());
+  m->described[i] = d;
+  return m->described[i].c_str();
 }
 
 int tcab_module_launch(const tcab_module* m, const char* kernel, const char* const* tensor_names,

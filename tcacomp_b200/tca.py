@@ -24,6 +24,7 @@ SYMBOLS = [
     ("tcab_module_kernel_name", C.c_char_p, [C.c_void_p, C.c_uint32]),
     ("tcab_module_kernel_output", C.c_char_p, [C.c_void_p, C.c_uint32]),
     ("tcab_module_kernel_class", C.c_char_p, [C.c_void_p, C.c_uint32]),
+    ("tcab_module_kernel_describe", C.c_char_p, [C.c_void_p, C.c_uint32]),
     ("tcab_module_launch", C.c_int,
      [C.c_void_p, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(_lib.Tensor), C.c_uint32, C.POINTER(C.c_char_p),
       C.POINTER(C.c_float), C.c_uint32, C.c_void_p]),
@@ -74,6 +75,15 @@ class Module:
         if getattr(self, "_h", None) is not None and self._h.value and _host is not None:
             _host.tcab_module_free(self._h)
             self._h = C.c_void_p()
+
+    def describe(self, kernel: str) -> Dict[str, str]:
+        """What `kernel` lowers to: class, tensor names and, for the chain classes, the canonical lambda texts,
+        init, capture names and the reduced axis (tcab_module_kernel_describe)."""
+        i = list(self.kernels).index(kernel)
+        text = load().tcab_module_kernel_describe(self._h, i)
+        if text is None:
+            raise _lib.TcabError(_lib.ERR_UNSUPPORTED, load().tcab_host_last_error().decode("utf-8", "replace"))
+        return dict(line.split("=", 1) for line in text.decode().splitlines() if "=" in line)
 
     def names(self) -> List[str]:
         return list(self.kernels)

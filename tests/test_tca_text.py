@@ -53,7 +53,7 @@ def test_host_library_exports_what_the_header_declares():
     text = open(os.path.join(ROOT, "include", "tcab_host.h")).read()
     names = sorted(set(re.findall(r"^TCAB_API[^;]*?\b(tcab_\w+)\s*\(", text, flags=re.M | re.S)))
     lib = tca.load()
-    assert len(names) == 8
+    assert len(names) == 9
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/tcab_host.h but not exported"
     assert sorted(s[0] for s in tca.SYMBOLS) == names
@@ -143,3 +143,69 @@ def test_text_kernels_on_the_device(oracle, cuda):
         m.launch("ScaledMatmul", {"lhs": torch.empty((64, 128), device=cuda), "rhs": torch.empty((100, 96), device=cuda),
                                   "out": out}, {"scale": 1.0})
     assert e.value.status == 2 and "N" in e.value.message
+
+
+# ---------------------------------------------------------------------------------------------
+# The reference's own suite kernels through this frontend. tests/golden/suite_frontend.json holds what the
+# frontend made of testing/kernels/*/*.tca (derived plans, not the sources; tests/golden/make_frontend_golden.py).
+# ---------------------------------------------------------------------------------------------
+def _frontend_golden():
+    import json
+    return json.load(open(os.path.join(ROOT, "tests", "golden", "suite_frontend.json")))
+
+
+# testing/suite.toml tolerances (max abs diff); the kernels it does not list there use the matmul tolerance
+FRONTEND_TOL = {"row_sum": 2e-3, "softmax": 2e-3, "transpose": 1e-5, "scale_copy": 1e-5, "axpy3": 1e-5,
+                "layernorm": 1e-5, "dup_expr": 1e-5, "dup_const": 1e-5}
+
+
+def test_frontend_golden_covers_the_suite(oracle):
+    golden = _frontend_golden()
+    assert sorted(golden) == sorted(oracle.SUITE)
+    for name, plan in golden.items():
+        cls = oracle.SUITE[name][1]
+        assert plan["class"] == ("chain_contract" if cls in ("mm", "qk") else "chain_reduce"), name
+        if cls == "qk":
+            assert plan["rhs_is_nk"] == "1"
+        if cls == "middle":
+            assert plan["axis"] == "1"
+        if cls == "inner":
+            assert plan["axis"] == "2"
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/testing/kernels"), reason="needs the reference checkout")
+def test_frontend_golden_is_reproducible():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_frontend_golden",
+                                                  os.path.join(ROOT, "tests", "golden", "make_frontend_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert mod.derive("/root/reference") == _frontend_golden()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["axpy3", "dup_const", "dup_expr", "gemm", "layernorm", "mlp", "mm_mid", "mm_small",
+                                  "mm_splitk", "qk_score", "row_sum", "scale_copy", "softmax", "transpose"])
+def test_reference_kernel_text_to_numbers(oracle, cuda, name):
+    # reference kernel text -> (this frontend, at fixture time) -> plan -> device -> the oracle's restatement of the
+    # reference's runner for that kernel
+    import torch
+
+    import tcacomp_b200 as T
+    plan = _frontend_golden()[name]
+    x, z = oracle.suite_inputs(name)
+    want = oracle.suite(name)
+    declared = [s for s in plan["scalars"].split(",") if s]
+    values = dict(zip(declared, oracle.SUITE[name][3]))
+    caps = tuple(values[c] for c in plan["captures"].split(",") if c)
+    xd, zd = torch.from_numpy(x).to(cuda), torch.from_numpy(z).to(cuda)
+    post = plan["post"] or None
+    if plan["class"] == "chain_reduce":
+        got = T.chain_reduce([xd, zd], plan["map"], combine_expr=plan["combine"], init=float(plan["init"]),
+                             post_expr=post, captures=caps, axis=int(plan["axis"]))
+    else:
+        got = T.chain_contract(xd, zd, plan["map"], rhs_is_nk=plan["rhs_is_nk"] == "1", combine_expr=plan["combine"],
+                               init=float(plan["init"]), post_expr=post, captures=caps)
+    got = got.cpu().numpy()
+    assert got.shape == want.shape
+    assert np.abs(got.astype(np.float64) - want).max() <= FRONTEND_TOL.get(name, 2e-3)
