@@ -30,7 +30,8 @@ def derive(checkout: str) -> dict:
 
 
 if __name__ == "__main__":
-    checkout = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    from oracle.build import REF_DEFAULT
+    checkout = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TCAB_REFERENCE", REF_DEFAULT)
     golden = derive(checkout)
     with open(os.path.join(ROOT, "tests", "golden", "suite_frontend.json"), "w") as f:
         json.dump(golden, f, indent=1, sort_keys=True)

@@ -173,14 +173,20 @@ def test_frontend_golden_covers_the_suite(oracle):
             assert plan["axis"] == "2"
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/testing/kernels"), reason="needs the reference checkout")
+def _reference_checkout():
+    from oracle.build import REF_DEFAULT
+    return os.environ.get("TCAB_REFERENCE", REF_DEFAULT)
+
+
 def test_frontend_golden_is_reproducible():
+    if not os.path.isdir(os.path.join(_reference_checkout(), "testing", "kernels")):
+        pytest.skip("needs the reference checkout")
     import importlib.util
     spec = importlib.util.spec_from_file_location("make_frontend_golden",
                                                   os.path.join(ROOT, "tests", "golden", "make_frontend_golden.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    assert mod.derive("/root/reference") == _frontend_golden()
+    assert mod.derive(_reference_checkout()) == _frontend_golden()
 
 
 @pytest.mark.gpu
