@@ -455,6 +455,19 @@ def timed(fn, steps: int, warmup: int, world: int, dev) -> float:
     return max_over_ranks(e0.elapsed_time(e1), world, dev)
 
 
+def per_step_ms(fn, steps: int) -> dict:
+    """Median and minimum device time of single steps (this rank), from one event pair per step, taken in a pass
+    of its own so that the extra event records do not sit inside the region `value` is computed from."""
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    marks[0].record()
+    for i in range(steps):
+        fn()
+        marks[i + 1].record()
+    torch.cuda.synchronize()
+    t = sorted(marks[i].elapsed_time(marks[i + 1]) for i in range(steps))
+    return {"median": t[len(t) // 2], "min": t[0], "max": t[-1], "steps": steps}
+
+
 def measure(wl, steps, warmup, world, dev, peaks, peak_src):
     """Kernel-only throughput of one workload with inputs resident in HBM."""
     ms = timed(wl.step, steps, warmup, world, dev)
@@ -504,6 +517,7 @@ def run_ours(args) -> dict:
     n0 = T.launch_count()
     ms, value, roofline = measure(wl, args.steps, 0, world, dev, peaks, peak_src)
     launches = T.launch_count() - n0
+    roofline["step_ms"] = per_step_ms(wl.step, max(20, args.steps))
     if hasattr(wl, "graph"):  # launches replayed from a CUDA graph do not pass through the library's counter
         launches = args.steps * wl.launches_per_step
     clocks = sampler.stop(t_load0, time.perf_counter()) if rank == 0 else None
