@@ -96,6 +96,112 @@ softmax_rows_reg(const float* __restrict__ x, float* __restrict__ y, uint64_t ro
   }
 }
 
+// Rows whose length is not a multiple of four columns: a row then starts at any 4-byte offset, but the
+// 16-byte vectors of the flat array still line up (the base pointer is 16-byte aligned). A row is read as
+// up to three leading elements, the aligned vectors inside it (at most cols / 4, so the launch shape is the
+// one of an aligned row of that length) and up to three trailing elements; the six edge elements ride in one
+// extra value of threads 0..5 of the row's group. Same arithmetic and fold as softmax_rows_reg<TPR, VPT, 4>;
+// without this such rows fall to 4-byte loads (2.9 TB/s at 50257 columns).
+struct UnalignedRow {
+  const float* xa;   // the first aligned vector inside the row
+  float* ya;
+  const float* xrow; // the row itself
+  float* yrow;
+  uint32_t lead, nint, tail;
+  __device__ __forceinline__ UnalignedRow(const float* x, float* y, uint64_t row, uint32_t cols) {
+    const uint64_t first = row * cols;
+    lead = static_cast<uint32_t>((4 - (first & 3)) & 3);
+    if (lead > cols) lead = cols;
+    nint = (cols - lead) / 4;
+    tail = cols - lead - 4 * nint;
+    xrow = x + first;
+    yrow = y + first;
+    xa = xrow + lead;
+    ya = yrow + lead;
+  }
+  // the edge element of thread t of the row's group (threads 0..2 lead, 3..5 tail), or -1
+  __device__ __forceinline__ int edge_index(int t) const {
+    if (t < 3) return t < static_cast<int>(lead) ? t : -1;
+    if (t < 6) return t - 3 < static_cast<int>(tail) ? static_cast<int>(lead + 4 * nint) + t - 3 : -1;
+    return -1;
+  }
+};
+
+template <int TPR, int VPT>
+__global__ void __launch_bounds__(row_cta_threads(TPR), row_min_ctas(TPR, VPT * 4, 16, 1536))
+softmax_rows_reg_unaligned(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  static_assert(TPR >= 8, "six threads of a group carry the edge elements");
+  __shared__ float slots[2][32];
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const int used = static_cast<int>((cols / 4 + TPR - 1) / TPR);
+
+  for (uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * GROUPS; row0 < rows;
+       row0 += static_cast<uint64_t>(gridDim.x) * GROUPS) {
+    const uint64_t row = row0 + g;
+    const bool live = row < rows;
+    const UnalignedRow r(x, y, live ? row : 0, cols);
+    const int ei = live ? r.edge_index(t) : -1;
+    float edge = ei >= 0 ? ld_stream(r.xrow + ei) : -INFINITY;
+
+    float v[VPT][4];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      if (i < used) {
+        const uint32_t idx = t + i * TPR;
+        if (live && idx < r.nint) {
+          const float4 q = ld_stream(reinterpret_cast<const float4*>(r.xa) + idx);
+          v[i][0] = q.x; v[i][1] = q.y; v[i][2] = q.z; v[i][3] = q.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[i][j] = -INFINITY;
+        }
+      }
+    }
+    float m = edge;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (i < used) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) m = fmaxf(m, v[i][j]);
+      }
+    m = group_allreduce<OpMax, TPR>(m, slots[0], g);
+    edge = expf(edge - m);
+    float s = edge;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (i < used) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          v[i][j] = expf(v[i][j] - m);
+          s += v[i][j];
+        }
+      }
+    s = group_allreduce<OpSum, TPR>(s, slots[1], g);
+    const float inv = 1.0f / s;
+    if (ei >= 0) st_stream(r.yrow + ei, edge * inv);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (i < used && live && idx < r.nint)
+        st_stream(reinterpret_cast<float4*>(r.ya) + idx, make_float4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv));
+    }
+  }
+}
+
+template <int TPR, int VPT>
+int launch_reg_unaligned(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  uint64_t grid = (rows + GROUPS - 1) / GROUPS;
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
+  softmax_rows_reg_unaligned<TPR, VPT><<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, y, rows, cols);
+  count_launch();
+  return check_launch("softmax_rows_reg_unaligned");
+}
+
 // A row too long for one CTA's registers is cut over a thread-block CLUSTER of CS CTAs: each CTA
 // keeps its segment in registers, the per-CTA max and sum meet through distributed shared memory
 // (every CTA reads the CS partials of its peers), so x is still read from HBM exactly once.
@@ -208,6 +314,102 @@ int launch_cluster(const float* x, float* y, uint64_t rows, uint32_t cols, uint3
   return launch_cluster_shape<512, 16, V>(x, y, rows, cols, nvec, s);
 }
 
+// The cluster kernel for rows that are not a multiple of four columns (see softmax_rows_reg_unaligned): the
+// aligned vectors inside a row are cut into one segment per CTA; CTA 0 also carries the edge elements.
+template <int THREADS, int VPT>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_cluster_unaligned(const float* __restrict__ x, float* __restrict__ y, uint32_t cols, uint32_t cs,
+                               uint32_t seg_vecs) {
+  __shared__ float slots[2][32];
+  __shared__ float cl_max, cl_sum;
+  const uint32_t rank = cluster_rank();
+  const UnalignedRow r(x, y, blockIdx.x / cs, cols);
+  const uint32_t v0 = rank * seg_vecs;
+  const uint32_t v1 = (r.nint - (v0 < r.nint ? v0 : r.nint) < seg_vecs) ? r.nint : v0 + seg_vecs;
+  const int used = static_cast<int>((seg_vecs + THREADS - 1) / THREADS);
+  const int ei = rank == 0 ? r.edge_index(static_cast<int>(threadIdx.x)) : -1;
+  float edge = ei >= 0 ? ld_stream(r.xrow + ei) : -INFINITY;
+
+  float v[VPT][4];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    if (i < used) {
+      const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+      if (idx < v1) {
+        const float4 q = ld_stream(reinterpret_cast<const float4*>(r.xa) + idx);
+        v[i][0] = q.x; v[i][1] = q.y; v[i][2] = q.z; v[i][3] = q.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[i][j] = -INFINITY;
+      }
+    }
+  }
+  float m = edge;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (i < used) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) m = fmaxf(m, v[i][j]);
+    }
+  m = cta_allreduce<OpMax, THREADS / 32>(m, slots[0]);
+  if (threadIdx.x == 0) cl_max = m;
+  cluster_sync_all();
+  float gm = -INFINITY;
+  for (uint32_t k = 0; k < cs; ++k) gm = fmaxf(gm, ld_dsmem(&cl_max, k));
+  edge = expf(edge - gm);
+  float s = edge;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+    if (i < used) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[i][j] = expf(v[i][j] - gm);
+        s += v[i][j];
+      }
+    }
+  s = cta_allreduce<OpSum, THREADS / 32>(s, slots[1]);
+  if (threadIdx.x == 0) cl_sum = s;
+  cluster_sync_all();
+  float gs = 0.0f;
+  for (uint32_t k = 0; k < cs; ++k) gs += ld_dsmem(&cl_sum, k);
+  const float inv = 1.0f / gs;
+  if (ei >= 0) st_stream(r.yrow + ei, edge * inv);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const uint32_t idx = v0 + threadIdx.x + i * THREADS;
+    if (i < used && idx < v1)
+      st_stream(reinterpret_cast<float4*>(r.ya) + idx, make_float4(v[i][0] * inv, v[i][1] * inv, v[i][2] * inv, v[i][3] * inv));
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its partials
+}
+
+template <int THREADS, int VPT>
+int launch_cluster_unaligned(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t max_nv, cudaStream_t s) {
+  constexpr uint32_t kPerCta = THREADS * VPT;
+  uint32_t cs = (max_nv + kPerCta - 1) / kPerCta;
+  if (cs < 2) cs = 2;
+  if (cs > 8) cs = 8;
+  const uint32_t seg = (max_nv + cs - 1) / cs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * cs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, softmax_rows_cluster_unaligned<THREADS, VPT>, x, y, cols, cs, seg);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "softmax_rows_cluster_unaligned: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
 // One CTA per row, any length. Pass 1 is the single-pass online max/sum.
 template <int THREADS, int V>
 __global__ void __launch_bounds__(THREADS)
@@ -283,6 +485,22 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   const bool vec = (cols % 4 == 0) && aligned16(x) && aligned16(y);
   const uint32_t nvec = vec ? cols / 4 : cols;
   const Tune& tn = tune(kSoftmax);
+  // rows that are not a multiple of four columns but still fit a CTA's registers as 16-byte vectors
+  if (!vec && cols % 4 != 0 && cols >= 16 && aligned16(x) && aligned16(y) && tn.p0 <= 0 && tn.p3 != 6) {
+    const uint32_t nv = cols / 4;  // aligned vectors inside a row, at most
+    int ut = 0, uv = 0;
+    if (nv <= 2048 && choose_row_shape_fit(nv, true, false, 4, &ut, &uv)) {
+#define TCAB_CASE(T, P) \
+  if (ut == T && uv == P) return launch_reg_unaligned<T, P>(x, y, rows, cols, s);
+      TCAB_CASE(8, 1) TCAB_CASE(8, 2) TCAB_CASE(8, 4) TCAB_CASE(16, 4) TCAB_CASE(32, 4) TCAB_CASE(64, 4) TCAB_CASE(128, 4)
+      TCAB_CASE(256, 4) TCAB_CASE(512, 4) TCAB_CASE(128, 8) TCAB_CASE(256, 8)
+#undef TCAB_CASE
+    }
+    if (nv > 2048 && rows * 8 <= 0x7fffffffull) {  // clusters of 256-thread CTAs, as for aligned rows
+      if (nv <= 8u * 256u * 8u) return launch_cluster_unaligned<256, 8>(x, y, rows, cols, nv, s);
+      if (nv <= 8u * 256u * 16u) return launch_cluster_unaligned<256, 16>(x, y, rows, cols, nv, s);
+    }
+  }
   int tpr = 0, vpt = 0;
   bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {

@@ -168,7 +168,11 @@ def assert_softmax_close(got, want, x):
                                        (3, 40000), (2, 140004), (2, 140001),
                                        # thread-block clusters of 2, 4, 8 CTAs (vector and scalar paths) and
                                        # the first size past them
-                                       (2, 32772), (5, 60000), (3, 50001), (2, 262144), (1, 262148)])
+                                       (2, 32772), (5, 60000), (3, 50001), (2, 262144), (1, 262148),
+                                       # rows that are not a multiple of four columns: 16-byte vectors with
+                                       # element-wise row ends, every head offset 0..3, one CTA and clusters
+                                       (9, 17), (301, 4097), (40, 8191), (7, 8194), (6, 12289), (5, 50257), (4, 65539),
+                                       (5, 131071)])
 def test_softmax_rows(oracle, cuda, rows, cols):
     rng = np.random.default_rng(rows * 7 + cols)
     x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
