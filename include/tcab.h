@@ -212,7 +212,8 @@ TCAB_API int tcab_device_status(int* status);
  *       p3 = CTAs sharing the k axis.
  *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
  *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
- *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128). */
+ *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128),
+ *       p3 = ranges the K blocks of a tile are cut into by kernels 3 and 4 (1 = no split). */
 TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 
 #ifdef __cplusplus

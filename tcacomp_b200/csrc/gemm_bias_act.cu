@@ -30,7 +30,9 @@
 // all walk the same tile list and never leave it early, also after a wait has given up.
 #include <cuda.h>
 
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -574,7 +576,10 @@ template <bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
-                        uint32_t N, uint32_t K, int act) {
+                        uint32_t N, uint32_t K, int act, uint32_t ksplit, uint32_t kb_per_split,
+                        float* __restrict__ partial) {
+  // ksplit > 1: a unit of work is (tile, range of K blocks); its fp32 accumulator goes to
+  // partial[range][M][N] as it is, and gemm_split_finish adds the ranges, the bias and the activation.
   using C = Db<PAIR>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::STAGES];   // PAIR: used in the leader, bytes of both CTAs land here
@@ -591,8 +596,8 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   volatile int* abort_p = &abort_flag;
 
   const uint32_t tiles_m = (M + C::TILE_M - 1) / C::TILE_M, tiles_n = (N + BN - 1) / BN;
-  const uint32_t num_tiles = tiles_m * tiles_n;
-  const uint32_t num_kb = (K + BK - 1) / BK;
+  const uint32_t num_tiles = tiles_m * tiles_n * ksplit;  // units of work
+  const uint32_t all_kb = (K + BK - 1) / BK;
   const uint32_t first = PAIR ? blockIdx.x >> 1 : blockIdx.x, step = PAIR ? gridDim.x >> 1 : gridDim.x;
 
   if (threadIdx.x == 0) {
@@ -637,14 +642,16 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     uint32_t stage = 0, phase = 0;
     bool ok = true;
     for (uint32_t t = first; ok && t < num_tiles; t += step) {
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const TileCoord tc = tile_coord(t / ksplit, tiles_m, tiles_n);
+      const uint32_t kb0 = (t % ksplit) * kb_per_split;
+      const uint32_t num_kb = kb0 < all_kb ? (all_kb - kb0 < kb_per_split ? all_kb - kb0 : kb_per_split) : 0u;
       const int32_t a_row = static_cast<int32_t>(tc.m * C::TILE_M + rank * UMMA_M);
       const int32_t b_col = static_cast<int32_t>(tc.n * BN + rank * C::B_COLS);
       for (uint32_t kb = 0; kb < num_kb; ++kb) {
         if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, abort_p)) { ok = false; break; }
         const uint32_t a_dst = smem_base + stage * C::STAGE;
         const uint32_t b_dst = a_dst + C::A_BYTES;
-        const int32_t k0 = static_cast<int32_t>(kb * BK);
+        const int32_t k0 = static_cast<int32_t>((kb0 + kb) * BK);
         const uint32_t full = PAIR ? ptx::mapa(ptx::smem_u32(&bar_full[stage]), 0) : ptx::smem_u32(&bar_full[stage]);
         if (lane == 0) {
           if (leader) ptx::mbar_expect_tx(ptx::smem_u32(&bar_full[stage]), C::CTAS * C::STAGE);
@@ -666,6 +673,8 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       bool ok = true;
       for (uint32_t t = first; ok && t < num_tiles; t += step, ++tile_iter) {
         const uint32_t acc = tile_iter & 1u, use = (tile_iter >> 1) & 1u;
+        const uint32_t kb0 = (t % ksplit) * kb_per_split;
+        const uint32_t num_kb = kb0 < all_kb ? (all_kb - kb0 < kb_per_split ? all_kb - kb0 : kb_per_split) : 0u;
         GEMM_TRACE(tile_iter, 0);
         if (num_kb > 0) {  // the epilogue must have drained this accumulator (two tiles ago)
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[acc]), use ^ 1u, abort_p)) break;
@@ -717,7 +726,9 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     uint32_t tile_iter = 0;
     bool ok = true;
     for (uint32_t t = first; ok && t < num_tiles; t += step, ++tile_iter) {
-      const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+      const TileCoord tc = tile_coord(t / ksplit, tiles_m, tiles_n);
+      const uint32_t ks = t % ksplit, kb0 = ks * kb_per_split;
+      const uint32_t num_kb = kb0 < all_kb ? (all_kb - kb0 < kb_per_split ? all_kb - kb0 : kb_per_split) : 0u;
       const uint32_t acc = tile_iter & 1u, use = (tile_iter >> 1) & 1u;
       const BiasRegs breg = load_bias_regs(bias, bias_vec, tc.n * BN + half * 128 + lane * 4, N);
       if (num_kb > 0) {
@@ -726,6 +737,39 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       }
       if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
       const uint32_t row0 = tc.m * C::TILE_M + rank * UMMA_M + quad * 32;
+      if (ksplit > 1) {
+        // fp32 partial of this K range, straight from TMEM: a thread owns a row and writes 32 consecutive columns
+        // (one 128-byte line) per load
+        const uint32_t row = row0 + lane;
+        float* prow = partial + (static_cast<size_t>(ks) * M + row) * N;
+#pragma unroll 1
+        for (uint32_t q = 0; q < 4; ++q) {
+          const uint32_t col = tc.n * BN + half * 128 + q * 32;
+          uint32_t r[32];
+          if (num_kb > 0) {
+            ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + acc * UMMA_N + half * 128 + q * 32, r);
+            ptx::tmem_ld_wait_for(r);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0u;
+          }
+          if (row < M) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              if (col + v * 4 < N)  // N % 8 == 0: groups of four columns are inside or outside as a whole
+                *reinterpret_cast<uint4*>(prow + col + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+          }
+        }
+        if (num_kb > 0) {
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[acc]), 0));
+            else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (uint32_t grp = 0; grp < 2; ++grp) {
         const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
@@ -773,6 +817,66 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
   if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = PAIR ? 4 : 3;
+}
+
+// Second pass of a K-split contraction: c = act(sum over ranges of partial + bias), bf16. Eight columns per thread.
+__global__ void __launch_bounds__(256)
+gemm_split_finish(const float* __restrict__ partial, const float* __restrict__ bias, __nv_bfloat16* __restrict__ c,
+                  uint32_t M, uint32_t N, uint32_t ksplit, int act) {
+  const size_t groups = static_cast<size_t>(M) * (N / 8);
+  const size_t gidx = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (gidx >= groups) return;
+  const size_t off = gidx * 8, plane = static_cast<size_t>(M) * N;
+  const uint32_t col = static_cast<uint32_t>(off % N);
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = 0.0f;
+  for (uint32_t ks = 0; ks < ksplit; ++ks) {  // ascending ranges: ascending k, like the one-pass kernel
+    const float4 p0 = *reinterpret_cast<const float4*>(partial + ks * plane + off);
+    const float4 p1 = *reinterpret_cast<const float4*>(partial + ks * plane + off + 4);
+    f[0] += p0.x; f[1] += p0.y; f[2] += p0.z; f[3] += p0.w;
+    f[4] += p1.x; f[5] += p1.y; f[6] += p1.z; f[7] += p1.w;
+  }
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float f0 = f[2 * j], f1 = f[2 * j + 1];
+    if (bias != nullptr) {
+      f0 += __ldg(bias + col + 2 * j);
+      f1 += __ldg(bias + col + 2 * j + 1);
+    }
+    if (act == TCAB_ACT_RELU) {
+      f0 = fmaxf(f0, 0.0f);
+      f1 = fmaxf(f1, 0.0f);
+    }
+    const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+    w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+  }
+  *reinterpret_cast<uint4*>(c + off) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Workspace of the K split: one buffer per (device, stream), grown on demand up to kSplitWorkspaceBytes.
+constexpr size_t kSplitWorkspaceBytes = static_cast<size_t>(64) << 20;
+float* gemm_split_workspace(cudaStream_t stream, size_t bytes) {
+  struct Buf { float* p; size_t bytes; };
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, Buf> table;
+  if (bytes > kSplitWorkspaceBytes) return nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  Buf& b = table[{dev, stream}];
+  if (b.bytes >= bytes) return b.p;
+  if (b.p != nullptr) cudaFree(b.p);  // synchronises the device: nothing still reads the old buffer afterwards
+  b.p = nullptr;
+  b.bytes = 0;
+  if (cudaMalloc(&b.p, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    b.p = nullptr;
+    return nullptr;
+  }
+  b.bytes = bytes;
+  return b.p;
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not
@@ -837,7 +941,15 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
                          __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
   if (m == 0 || n == 0) return TCAB_OK;
   const Tune& tn = tune(kGemm);
-  const bool default_kernel = !(tn.p1 == 3 || tn.p1 == 4 || (tn.p1 == 2 && k > 0));
+  // Which kernel: the 256 x 256 single-CTA kernel while its tiles fill the GPU; below that the double-buffered
+  // kernels, whose 128-row shares give twice the CTAs (measured 2048^3: 620 -> 820 TFLOP/s), single CTAs for one
+  // 128-row band, CTA pairs otherwise. tune p1 forces a kernel.
+  int variant = tn.p1;
+  if (variant <= 0 && k > 0) {
+    const uint64_t tiles256 = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    if (2 * tiles256 <= static_cast<uint64_t>(sm_count())) variant = m <= 128 ? 3 : 4;  // 128 tiles on 148 SMs: the default is faster
+  }
+  const bool default_kernel = !(variant == 3 || variant == 4 || (variant == 2 && k > 0));
   CUtensorMap ta, tb, tcm;
   {
     // the default kernel stores half boxes (32 x 32, 64-byte swizzle), the variants whole boxes (32 x 64)
@@ -862,9 +974,9 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   if (attr_err != cudaSuccess)
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(attr_err));
-  if (tn.p1 == 3 || tn.p1 == 4) {
-    // double-buffered accumulators: A boxes of 128 rows; p1 == 4 runs clusters of two CTAs
-    const bool pair = tn.p1 == 4;
+  if (variant == 3 || variant == 4) {
+    // double-buffered accumulators: A boxes of 128 rows; variant 4 runs clusters of two CTAs
+    const bool pair = variant == 4;
     CUtensorMap ta2;
     int rc = k > 0 ? make_map(&ta2, a, m, k, UMMA_M) : TCAB_OK;
     if (rc != TCAB_OK) return rc;
@@ -880,7 +992,30 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     const uint64_t tiles = static_cast<uint64_t>((m + tile_m - 1) / tile_m) * ((n + BN - 1) / BN);
     const uint64_t ctas_per_tile = pair ? 2 : 1;
     uint64_t groups = (tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count())) / ctas_per_tile;
-    if (groups > tiles) groups = tiles;
+    // Few tiles and a long K: the K blocks of a tile are cut into ranges, one unit of work each; the fp32
+    // partials go to a workspace and gemm_split_finish adds them, the bias and the activation. tune p3 forces
+    // the number of ranges.
+    const uint32_t all_kb = (k + BK - 1) / BK;
+    uint32_t ksplit = 1, kb_per = all_kb;
+    float* partial = nullptr;
+    if (k > 0 && n % 8 == 0) {
+      uint64_t want = tn.p3 > 0 ? static_cast<uint64_t>(tn.p3) : (tiles > 0 ? groups / tiles : 1);
+      if (tn.p3 <= 0 && want > all_kb / 16) want = all_kb / 16;  // at least sixteen K blocks (1024 of K) per range
+      if (want > all_kb) want = all_kb;
+      const size_t plane = static_cast<size_t>(m) * n * sizeof(float);
+      if (want > kSplitWorkspaceBytes / plane) want = kSplitWorkspaceBytes / plane;
+      if (want >= 2) {
+        kb_per = (all_kb + static_cast<uint32_t>(want) - 1) / static_cast<uint32_t>(want);
+        ksplit = (all_kb + kb_per - 1) / kb_per;  // no empty range
+        partial = ksplit > 1 ? gemm_split_workspace(s, plane * ksplit) : nullptr;
+        if (partial == nullptr) {
+          ksplit = 1;
+          kb_per = all_kb;
+        }
+      }
+    }
+    const uint64_t units = tiles * ksplit;
+    if (groups > units) groups = units;
     if (groups < 1) groups = 1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ctas_per_tile * groups));
@@ -894,16 +1029,22 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    void* args[] = {&ta2, &tb, &tcm, &bias, &m, &n, &k, &act};
+    void* args[] = {&ta2, &tb, &tcm, &bias, &m, &n, &k, &act, &ksplit, &kb_per, &partial};
     const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
     count_launch();
     if (le != cudaSuccess) {
       cudaGetLastError();
       return fail(TCAB_ERR_CUDA, "gemm_bias_act (double-buffered): launch failed: %s", cudaGetErrorString(le));
     }
+    if (ksplit > 1) {
+      const size_t groups8 = static_cast<size_t>(m) * (n / 8);
+      gemm_split_finish<<<static_cast<unsigned>((groups8 + 255) / 256), 256, 0, s>>>(partial, bias, c, m, n, ksplit, act);
+      count_launch();
+      return check_launch("gemm_split_finish");
+    }
     return TCAB_OK;
   }
-  if (tn.p1 == 2 && k > 0) {
+  if (variant == 2 && k > 0) {
     // CTA pairs: A boxes of 128 rows, clusters of two CTAs
     CUtensorMap ta2;
     int rc = make_map(&ta2, a, m, k, UMMA_M);

@@ -543,7 +543,7 @@ def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
     buf, out = guarded((m, n), torch.bfloat16, cuda)
     try:
-        T.tune("gemm", 0, variant)
+        T.tune("gemm", 0, variant, 0, 1)  # the kernel variant alone: no K split
         T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu", out=out)
         single_off = out.float().cpu().numpy()
     finally:
@@ -551,9 +551,49 @@ def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
     check_guards(buf, torch.bfloat16)
     assert T.device_status() == 0
     assert rel_frobenius(single_off, want) <= 1e-3
-    # both kernels accumulate every output over ascending k in the tensor core: identical bits
-    ref = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
+    # both kernels accumulate every output over ascending k in the tensor core: identical bits (with the K split
+    # switched off: its partial sums round differently)
+    try:
+        T.tune("gemm", 0, 0, 0, 1)
+        ref = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
+    finally:
+        T.tune("gemm")
     assert np.array_equal(single_off, ref)
+
+
+@pytest.mark.parametrize("m,k,n,variant,ranges", [(100, 4096, 512, 0, 0), (300, 2048, 264, 0, 0), (16, 8192, 1024, 0, 0),
+                                                     (130, 200, 264, 3, 3), (260, 1032, 520, 4, 5), (128, 64, 256, 3, 4),
+                                                     (513, 4096, 776, 4, 2)])
+def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
+    # few output tiles and a long K: ranges of K blocks become units of work, fp32 partials are added by a second
+    # kernel together with bias and activation. variant / ranges = 0: the library's own choice.
+    a, b, bias = gemm_inputs(oracle, m, k, n, m + 3 * k + n)
+    want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
+    buf, out = guarded((m, n), torch.bfloat16, cuda)
+    n0 = T.launch_count()
+    try:
+        if variant:
+            T.tune("gemm", 0, variant, 0, ranges)
+        T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu", out=out)
+    finally:
+        T.tune("gemm")
+    launches = T.launch_count() - n0
+    got = out.float().cpu().numpy()
+    check_guards(buf, torch.bfloat16)
+    assert T.device_status() == 0
+    if variant == 0 or min(ranges, (k + 63) // 64) > 1:
+        assert launches == 2, "expected the contraction and the finishing kernel"
+    assert rel_frobenius(got, want) <= 1e-3
+    assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
+    # no bias, no activation through the same path
+    want2 = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
+    try:
+        if variant:
+            T.tune("gemm", 0, variant, 0, ranges)
+        got2 = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), None, "none").float().cpu().numpy()
+    finally:
+        T.tune("gemm")
+    assert rel_frobenius(got2, want2) <= 1e-3
 
 
 def test_gemm_without_bias_and_empty_k(oracle, cuda):
