@@ -839,6 +839,15 @@ def test_row_pipeline_matches_direct_call(oracle, cuda):
     torch.cuda.current_stream(cuda).synchronize()
     direct = T.softmax_rows(hx.to(cuda)).cpu()
     assert torch.equal(hy, direct)
+    # streaming: batches back to back without a join in between, different host buffers per batch, one join at the end
+    batches = [torch.from_numpy((4 * rng.normal(0, 1, (1000, 512))).astype(np.float32)).pin_memory() for _ in range(3)]
+    outs = [torch.full_like(b, CANARY).pin_memory() for b in batches]
+    for b, o in zip(batches, outs):
+        pipe.run(b, {"y": o}, lambda din, dout: T.softmax_rows(din, out=dout["y"]), join=False)
+    pipe.join()
+    torch.cuda.current_stream(cuda).synchronize()
+    for b, o in zip(batches, outs):
+        assert torch.equal(o, T.softmax_rows(b.to(cuda)).cpu())
     # several outputs per chunk (outer-axis reduce over batch chunks)
     t = rng.uniform(-100, 100, (10, 64, 96)).astype(np.float32)
     ht = torch.from_numpy(t).pin_memory()
