@@ -21,7 +21,7 @@ namespace tcab {
 namespace {
 
 template <typename T, int TPR, int VPT, int V, bool CACHE_GB>
-__global__ void __launch_bounds__(row_cta_threads(TPR), CACHE_GB ? 1 : row_min_ctas(TPR, VPT * V, sizeof(T) == 2 ? 32 : 16))
+__global__ void __launch_bounds__(row_cta_threads(TPR), CACHE_GB ? 1 : row_min_ctas(TPR, VPT * V, sizeof(T) == 2 ? 32 : 16, TPR == 512 ? 1536 : TPR == 1024 ? 2048 : 1280))
 layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
                    float eps, T* __restrict__ y, uint64_t rows, uint32_t cols) {
   constexpr int THREADS = row_cta_threads(TPR);
