@@ -206,7 +206,7 @@ int launch_reg_unaligned(const float* x, float* y, uint64_t rows, uint32_t cols,
 // keeps its segment in registers, the per-CTA max and sum meet through distributed shared memory
 // (every CTA reads the CS partials of its peers), so x is still read from HBM exactly once.
 template <int CS_MAX, int THREADS, int VPT, int V>
-__global__ void __launch_bounds__(THREADS, (THREADS == 256 && VPT * V <= 32) ? 6 : 1)
+__global__ void __launch_bounds__(THREADS)
 softmax_rows_cluster(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols, uint32_t cs,
                      uint32_t seg_vecs) {
   using IO = VecIO<float, V>;
@@ -317,7 +317,7 @@ int launch_cluster(const float* x, float* y, uint64_t rows, uint32_t cols, uint3
 // The cluster kernel for rows that are not a multiple of four columns (see softmax_rows_reg_unaligned): the
 // aligned vectors inside a row are cut into one segment per CTA; CTA 0 also carries the edge elements.
 template <int THREADS, int VPT>
-__global__ void __launch_bounds__(THREADS, (THREADS == 256 && VPT <= 8) ? 6 : 1)
+__global__ void __launch_bounds__(THREADS)
 softmax_rows_cluster_unaligned(const float* __restrict__ x, float* __restrict__ y, uint32_t cols, uint32_t cs,
                                uint32_t seg_vecs) {
   __shared__ float slots[2][32];
