@@ -326,12 +326,15 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
     vpt = tn.p1;
     fits = true;
   }
-  // Long fp32 rows with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu), measured
-  // 4.0-5.0 TB/s against 3.3-4.8 for the 1024-thread register kernels from 10240 columns on. For bf16 the three
-  // passes over shared memory unpack every element three times and lose to the register kernels, so bf16 rows
-  // stay there. p3 == 4 forces the shared-memory kernel.
-  if (vec && tn.p0 <= 0 && rows_smem_fits(static_cast<uint64_t>(cols) * sizeof(T)) &&
-      (tn.p3 == 4 || (tn.p3 <= 0 && sizeof(T) == 4 && nvec >= 2560 && rows >= static_cast<uint64_t>(sm_count()))))
+  // Long rows with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu). fp32 from 2560
+  // vectors on (10240 columns: 5.7 TB/s with three CTAs per SM, 3.8 for the 1024-thread register kernel; 4.9-5.0
+  // up to 45056 columns). bf16 unpacks every element in each of the three passes and only wins where three CTAs
+  // fit an SM and the register kernel needs 1024 threads: rows of 32..48 KiB (20480 columns 4.5 against 3.8,
+  // 24576 columns 4.8 against 4.0). p3 == 4 forces the shared-memory kernel.
+  const uint64_t row_bytes = static_cast<uint64_t>(cols) * sizeof(T);
+  const bool smem_pays = sizeof(T) == 4 ? nvec >= 2560 : (row_bytes > 32768 && row_bytes <= 49152);
+  if (vec && tn.p0 <= 0 && rows_smem_fits(row_bytes) &&
+      (tn.p3 == 4 || (tn.p3 <= 0 && smem_pays && rows >= static_cast<uint64_t>(sm_count()))))
     return launch_smem(x, gamma, beta, eps, y, rows, cols, s);
   // Few long rows go to the cluster kernel (2-8 CTAs x 4096 vectors share a row, so a handful of rows
   // still spreads over the GPU: 64 x 131072 bf16 runs at 1.75 TB/s instead of 1.10). With many rows the

@@ -26,17 +26,35 @@ namespace tcab {
 namespace {
 
 constexpr int kSlotBytes = 16384;
-constexpr int kSlots = 12;
-#ifndef TCAB_ROWS_SMEM_WARPS
-#define TCAB_ROWS_SMEM_WARPS 16
-#endif
-constexpr int kConsumerWarps = TCAB_ROWS_SMEM_WARPS;
-constexpr int kConsumers = 32 * kConsumerWarps;
-constexpr int kThreads = kConsumers + 32;  // + the producer warp
 constexpr int kSlotVecs = kSlotBytes / 16;
-constexpr size_t kRingBytes = static_cast<size_t>(kSlots) * kSlotBytes;
+
+// A configuration: ring slots per CTA and consumer warps per CTA. One CTA per SM with the whole shared memory
+// (12 slots, 16 warps) takes rows of up to 11 slots; rows of up to 5 (3) slots run two (three) CTAs per SM with
+// 6 (4) slots and 8 consumer warps each: a CTA's passes over a row are strictly one after the other (measured:
+// two barriers of 450 cycles and latency-bound chunk loops, 3,900 cycles per 32 KiB row of which the copies need
+// 800), so what fills the SM is several rows in flight, not more warps on one row.
+template <int SLOTS, int CW>
+struct Cfg {
+  static constexpr int kSlots = SLOTS;
+  static constexpr int kConsumerWarps = CW;
+  static constexpr int kConsumers = 32 * CW;
+  static constexpr int kThreads = kConsumers + 32;  // + the producer warp
+  static constexpr size_t kRingBytes = static_cast<size_t>(SLOTS) * kSlotBytes;
+};
 
 __device__ int g_rows_smem_status = 0;
+
+// Developer timeline (compiled in only with -DTCAB_ROWS_TRACE): CTA 0 stamps the SM clock per row;
+// tcab_debug_rows_trace copies the stamps out. slot = row_iter * 8 + event.
+#ifdef TCAB_ROWS_TRACE
+__device__ long long g_rows_trace[8 * 64];
+#define ROWS_TRACE(it, ev)                                                              \
+  do {                                                                                  \
+    if (blockIdx.x == 0 && (it) < 64u) g_rows_trace[(it) * 8 + (ev)] = clock64();       \
+  } while (0)
+#else
+#define ROWS_TRACE(it, ev) do { } while (0)
+#endif
 
 // global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned); completion is
 // counted on `bar` in bytes.
@@ -46,33 +64,39 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
+template <class CF>
 struct Ring {
-  uint64_t full[kSlots];   // producer: arrive.expect_tx + the copy's bytes
-  uint64_t empty[kSlots];  // one arrival per consumer warp
-  float red[2][kConsumerWarps];
+  uint64_t full[CF::kSlots];   // producer: arrive.expect_tx + the copy's bytes
+  uint64_t empty[CF::kSlots];  // one arrival per consumer warp
+  float red[2][CF::kConsumerWarps];
   int consumer_abort;      // written by consumers only, read after their barrier: a uniform decision
   int producer_abort;
 };
 
 // Sum / max over the consumer threads through shared memory; one named barrier, result in every thread.
-template <typename Op>
+template <class CF, typename Op>
 __device__ __forceinline__ float consumers_allreduce(float v, float* slots) {
   v = warp_allreduce<Op>(v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) slots[warp] = v;
-  ptx::named_bar_sync(1, kConsumers);
-  return warp_allreduce<Op>(lane < kConsumerWarps ? slots[lane] : Op::identity());
+  ptx::named_bar_sync(1, CF::kConsumers);
+  return warp_allreduce<Op>(lane < CF::kConsumerWarps ? slots[lane] : Op::identity());
 }
 
 // The producer: every row of this CTA, slot by slot, as far ahead as the ring allows.
-__device__ __forceinline__ void produce_rows(Ring& ring, uint32_t ring_base, const uint8_t* x, uint64_t rows,
+template <class CF>
+__device__ __forceinline__ void produce_rows(Ring<CF>& ring, uint32_t ring_base, const uint8_t* x, uint64_t rows,
                                              uint32_t row_bytes) {
+  constexpr int kSlots = CF::kSlots;
   uint32_t slot = 0, phase = 0;
   volatile int* abort_p = &ring.producer_abort;
-  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+  uint32_t it = 0;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
     const uint8_t* src = x + row * row_bytes;
     for (uint32_t off = 0; off < row_bytes; off += kSlotBytes) {
       if (!ptx::mbar_wait(ptx::smem_u32(&ring.empty[slot]), phase ^ 1u, abort_p)) return;
+      if (off == 0) ROWS_TRACE(it, 0);
+      if (off + kSlotBytes >= row_bytes) ROWS_TRACE(it, 1);
       const uint32_t bytes = row_bytes - off < static_cast<uint32_t>(kSlotBytes) ? row_bytes - off : kSlotBytes;
       const uint32_t bar = ptx::smem_u32(&ring.full[slot]);
       ptx::mbar_expect_tx(bar, bytes);
@@ -82,11 +106,12 @@ __device__ __forceinline__ void produce_rows(Ring& ring, uint32_t ring_base, con
   }
 }
 
-__device__ __forceinline__ void init_ring(Ring& ring) {
+template <class CF>
+__device__ __forceinline__ void init_ring(Ring<CF>& ring) {
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kSlots; ++s) {
+    for (int s = 0; s < CF::kSlots; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ring.full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&ring.empty[s]), kConsumerWarps);
+      ptx::mbar_init(ptx::smem_u32(&ring.empty[s]), CF::kConsumerWarps);
     }
     ring.consumer_abort = 0;
     ring.producer_abort = 0;
@@ -98,7 +123,8 @@ __device__ __forceinline__ void init_ring(Ring& ring) {
 
 // What a CTA does before it exits after a wait gave up: copies may still be in flight into its shared
 // memory, so it idles for a bounded time first, then records the status.
-__device__ __forceinline__ void finish_ring(Ring& ring) {
+template <class CF>
+__device__ __forceinline__ void finish_ring(Ring<CF>& ring) {
   __syncthreads();
   if (ring.consumer_abort != 0 || ring.producer_abort != 0) {
     const long long t0 = clock64();
@@ -111,14 +137,15 @@ __device__ __forceinline__ void finish_ring(Ring& ring) {
 // ---------------------------------------------------------------------------------------------
 // layer-norm
 // ---------------------------------------------------------------------------------------------
-template <typename T, int V>
-__global__ void __launch_bounds__(kThreads, 1)
+template <class CF, typename T, int V>
+__global__ void __launch_bounds__(CF::kThreads, 1)
 layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, float eps,
                     T* __restrict__ y, uint64_t rows, uint32_t cols) {
   using IO = VecIO<T, V>;
   using Raw = typename IO::Raw;
+  constexpr int kSlots = CF::kSlots, kConsumers = CF::kConsumers;
   extern __shared__ __align__(128) uint8_t ring_mem[];
-  __shared__ Ring ring;
+  __shared__ Ring<CF> ring;
   init_ring(ring);
   const uint32_t ring_base = ptx::smem_u32(ring_mem);
   const uint32_t row_bytes = cols * static_cast<uint32_t>(sizeof(T));
@@ -161,7 +188,7 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           if (++slot == kSlots) { slot = 0; phase ^= 1u; }
         }
       }
-      const float mean = consumers_allreduce<OpSum>(s, ring.red[0]) / n;
+      const float mean = consumers_allreduce<CF, OpSum>(s, ring.red[0]) / n;
       if (ring.consumer_abort != 0) break;  // uniform: written before the barrier above, by consumers only
       // pass 2: centred squares
       float q = 0.0f;
@@ -183,7 +210,7 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           if (++slot == kSlots) slot = 0;
         }
       }
-      const float rstd = 1.0f / sqrtf(consumers_allreduce<OpSum>(q, ring.red[1]) / n + eps);
+      const float rstd = 1.0f / sqrtf(consumers_allreduce<CF, OpSum>(q, ring.red[1]) / n + eps);
       // pass 3: normalise, scale, shift, store; hand each slot back once this warp has read it
       {
         uint32_t slot = slot0;
@@ -219,11 +246,13 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
 // ---------------------------------------------------------------------------------------------
 // row softmax
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1)
+template <class CF>
+__global__ void __launch_bounds__(CF::kThreads, 1)
 softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols) {
   using IO = VecIO<float, 4>;
+  constexpr int kSlots = CF::kSlots, kConsumers = CF::kConsumers;
   extern __shared__ __align__(128) uint8_t ring_mem[];
-  __shared__ Ring ring;
+  __shared__ Ring<CF> ring;
   init_ring(ring);
   const uint32_t ring_base = ptx::smem_u32(ring_mem);
   const uint32_t row_bytes = cols * 4u;
@@ -235,11 +264,12 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
   } else {
     volatile int* abort_p = &ring.consumer_abort;
     const int lane = threadIdx.x & 31;
-    uint32_t slot0 = 0, phase0 = 0;
-    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint32_t slot0 = 0, phase0 = 0, it = 0;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
       float* yr = y + row * cols;
       bool ok = true;
       float m = -INFINITY;
+      if (threadIdx.x == 0) ROWS_TRACE(it, 2);
       {
         uint32_t slot = slot0, phase = phase0;
         for (uint32_t c = 0; c < nchunks; ++c) {
@@ -262,8 +292,10 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) { slot = 0; phase ^= 1u; }
         }
       }
-      m = consumers_allreduce<OpMax>(m, ring.red[0]);
+      if (threadIdx.x == 0) ROWS_TRACE(it, 3);
+      m = consumers_allreduce<CF, OpMax>(m, ring.red[0]);
       if (ring.consumer_abort != 0) break;
+      if (threadIdx.x == 0) ROWS_TRACE(it, 4);
       // pass 2: the exponentials are kept (written back to the slot), so that pass 3 only scales them
       float s = 0.0f;
       {
@@ -284,7 +316,9 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) slot = 0;
         }
       }
-      const float inv = 1.0f / consumers_allreduce<OpSum>(s, ring.red[1]);
+      if (threadIdx.x == 0) ROWS_TRACE(it, 5);
+      const float inv = 1.0f / consumers_allreduce<CF, OpSum>(s, ring.red[1]);
+      if (threadIdx.x == 0) ROWS_TRACE(it, 6);
       {
         uint32_t slot = slot0;
         for (uint32_t c = 0; c < nchunks; ++c) {
@@ -307,6 +341,7 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) slot = 0;
         }
       }
+      if (threadIdx.x == 0) ROWS_TRACE(it, 7);
       slot0 += nchunks;
       while (slot0 >= static_cast<uint32_t>(kSlots)) { slot0 -= kSlots; phase0 ^= 1u; }
     }
@@ -314,25 +349,49 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
   finish_ring(ring);
 }
 
-template <typename Fn>
-int prepare(Fn* fn) {
-  const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingBytes));
+// The three configurations: CTAs per SM x ring slots x consumer warps.
+typedef Cfg<12, 16> Whole;   // 1 CTA per SM, rows of up to 11 slots
+typedef Cfg<6, 8> Half;      // 2 CTAs per SM, rows of up to 5 slots
+typedef Cfg<4, 8> Third;     // 3 CTAs per SM, rows of up to 3 slots
+
+template <class CF, typename Fn, typename... Args>
+int launch_cfg(Fn* fn, int ctas_per_sm, uint64_t rows, cudaStream_t s, const char* what, Args... args) {
+  const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(CF::kRingBytes));
   if (e != cudaSuccess) {
     cudaGetLastError();
-    return fail(TCAB_ERR_CUDA, "rows_smem: cannot reserve %zu bytes of shared memory: %s", kRingBytes, cudaGetErrorString(e));
+    return fail(TCAB_ERR_CUDA, "rows_smem: cannot reserve %zu bytes of shared memory: %s", CF::kRingBytes,
+                cudaGetErrorString(e));
   }
-  return TCAB_OK;
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * ctas_per_sm;
+  const unsigned grid = static_cast<unsigned>(rows < resident ? rows : resident);
+  fn<<<grid, CF::kThreads, CF::kRingBytes, s>>>(args...);
+  count_launch();
+  return check_launch(what);
 }
 
-unsigned grid_for(uint64_t rows) {
-  const uint64_t sms = static_cast<uint64_t>(sm_count());
-  return static_cast<unsigned>(rows < sms ? rows : sms);
+// 0: one CTA per SM, 1: two, 2: three -- the most CTAs whose ring still holds a row plus one free slot.
+// tune("softmax" / "layernorm", _, _, p2 = 1 | 2 | 3) forces the number of CTAs per SM where the row allows it.
+int pick_cfg(uint64_t row_bytes, int forced_ctas) {
+  const uint64_t slots = (row_bytes + kSlotBytes - 1) / kSlotBytes;
+  int best = slots <= 3 ? 2 : slots <= 5 ? 1 : 0;
+  if (forced_ctas >= 1 && forced_ctas <= 3 && forced_ctas - 1 <= best) best = forced_ctas - 1;
+  return best;
 }
 
 }  // namespace
 
-// A row fits when it leaves at least one slot of the ring free (the producer then always has room to run ahead).
-bool rows_smem_fits(uint64_t row_bytes) { return row_bytes > 0 && row_bytes <= kRingBytes - kSlotBytes && row_bytes % 16 == 0; }
+#ifdef TCAB_ROWS_TRACE
+extern "C" __attribute__((visibility("default"))) int tcab_debug_rows_trace(long long* out, int n) {
+  if (n > 8 * 64) n = 8 * 64;
+  return cudaMemcpyFromSymbol(out, g_rows_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 1;
+}
+#endif
+
+// A row fits when it leaves at least one slot of the largest ring free (the producer then always has room to
+// run ahead).
+bool rows_smem_fits(uint64_t row_bytes) {
+  return row_bytes > 0 && row_bytes <= Whole::kRingBytes - kSlotBytes && row_bytes % 16 == 0;
+}
 
 int rows_smem_status(int* out) {
   if (cudaMemcpyFromSymbol(out, g_rows_smem_status, sizeof(int)) != cudaSuccess) {
@@ -343,29 +402,30 @@ int rows_smem_status(int* out) {
 }
 
 int launch_softmax_rows_smem(const float* x, float* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
-  int rc = prepare(softmax_rows_smem);
-  if (rc != TCAB_OK) return rc;
-  softmax_rows_smem<<<grid_for(rows), kThreads, kRingBytes, s>>>(x, y, rows, cols);
-  count_launch();
-  return check_launch("softmax_rows_smem");
+  switch (pick_cfg(static_cast<uint64_t>(cols) * 4, tune(kSoftmax).p2)) {
+    case 2: return launch_cfg<Third>(softmax_rows_smem<Third>, 3, rows, s, "softmax_rows_smem", x, y, rows, cols);
+    case 1: return launch_cfg<Half>(softmax_rows_smem<Half>, 2, rows, s, "softmax_rows_smem", x, y, rows, cols);
+    default: return launch_cfg<Whole>(softmax_rows_smem<Whole>, 1, rows, s, "softmax_rows_smem", x, y, rows, cols);
+  }
 }
 
 int launch_layernorm_rows_smem_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
                                     float eps, __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
-  int rc = prepare(layernorm_rows_smem<__nv_bfloat16, 8>);
-  if (rc != TCAB_OK) return rc;
-  layernorm_rows_smem<__nv_bfloat16, 8><<<grid_for(rows), kThreads, kRingBytes, s>>>(x, gamma, beta, eps, y, rows, cols);
-  count_launch();
-  return check_launch("layernorm_rows_smem");
+  typedef __nv_bfloat16 B;
+  switch (pick_cfg(static_cast<uint64_t>(cols) * 2, tune(kLayernorm).p2)) {
+    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, B, 8>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+  }
 }
 
 int launch_layernorm_rows_smem_f32(const float* x, const float* gamma, const float* beta, float eps, float* y,
                                    uint64_t rows, uint32_t cols, cudaStream_t s) {
-  int rc = prepare(layernorm_rows_smem<float, 4>);
-  if (rc != TCAB_OK) return rc;
-  layernorm_rows_smem<float, 4><<<grid_for(rows), kThreads, kRingBytes, s>>>(x, gamma, beta, eps, y, rows, cols);
-  count_launch();
-  return check_launch("layernorm_rows_smem");
+  switch (pick_cfg(static_cast<uint64_t>(cols) * 4, tune(kLayernorm).p2)) {
+    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, float, 4>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+  }
 }
 
 }  // namespace tcab

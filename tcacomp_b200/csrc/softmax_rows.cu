@@ -508,10 +508,11 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
     vpt = tn.p1;
     fits = true;
   }
-  // Rows of 4097..11264 vectors with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu),
-  // measured 5.1-5.5 TB/s against 4.8-5.4 for the clusters at 20480..45056 columns. p3 == 3 forces it.
+  // Rows of 2049..11264 vectors with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu), two or
+  // three CTAs per SM while the row allows it. Measured 6.0-6.3 TB/s at 10240..20480 columns (clusters: 4.8-6.1)
+  // and 5.1-5.5 at 24576..45056 (clusters: 4.8-5.4). p3 == 3 forces it.
   if (vec && tn.p0 <= 0 && rows_smem_fits(static_cast<uint64_t>(cols) * 4) &&
-      (tn.p3 == 3 || (tn.p3 <= 0 && nvec > 4096 && rows >= static_cast<uint64_t>(sm_count()))))
+      (tn.p3 == 3 || (tn.p3 <= 0 && nvec > 2048 && rows >= static_cast<uint64_t>(sm_count()))))
     return launch_softmax_rows_smem(x, y, rows, cols, s);
   // Rows beyond 2048 vectors go to the cluster kernel (2..8 CTAs of 256 threads x 8 vectors while that covers
   // the row: measured 6.1 against 4.4 TB/s for one 1024-thread CTA at 16384 columns), unless the tuning hook
