@@ -45,7 +45,8 @@ def layernorm_bf16_close(got_bits, x_bits, g_bits, b_bits, eps: float = 1e-5, wa
 
     y64 is the formula in fp64 on the same bf16 inputs, r64 its bf16 rounding. fp32err is the fp32
     error (1e-5 relative) of the two terms x_hat*gamma and beta, which matters only where they cancel
-    to a value near zero.
+    to a value near zero, plus the error an fp32 mean leaves on x - mean (1e-6 of |mean| + std), which
+    matters only for elements that sit on the mean.
       * the kernel must be a rounding of a value that close to exact: |got - y64| <= ulp/2 + fp32err;
       * against the oracle: |got - want| <= ulp + fp32err + |want - r64|, and the two may round
         differently only rarely: frac(got != want) <= max_mismatch + frac(want != r64).
@@ -59,7 +60,9 @@ def layernorm_bf16_close(got_bits, x_bits, g_bits, b_bits, eps: float = 1e-5, wa
     y64 = xhat * g + b
     r64_bits = O.f32_to_bf16(y64.astype(np.float32))
     r64 = O.bf16_to_f32(r64_bits).astype(np.float64)
-    fp32err = 1e-5 * (np.abs(xhat * g) + np.abs(b))
+    # ... plus the floor any fp32 mean leaves on x - mean: a relative 1e-6 of (|mean| + std), scaled like x_hat
+    std = np.sqrt(x.var(1, keepdims=True) + eps)
+    fp32err = 1e-5 * (np.abs(xhat * g) + np.abs(b)) + 1e-6 * (np.abs(x.mean(1, keepdims=True)) / std + 1.0) * np.abs(g)
     ulp = _bf16_ulp(np.maximum(np.abs(y64), np.abs(got)))
     ok_exact = (np.abs(got - y64) <= 0.5 * ulp + fp32err + 1e-30).all()
     ok_oracle = (np.abs(got - want) <= _bf16_ulp(want) + fp32err + np.abs(want - r64)).all()

@@ -68,7 +68,7 @@ template <class CF>
 struct Ring {
   uint64_t full[CF::kSlots];   // producer: arrive.expect_tx + the copy's bytes
   uint64_t empty[CF::kSlots];  // one arrival per consumer warp
-  float red[2][CF::kConsumerWarps];
+  float red[4][CF::kConsumerWarps];  // two reductions per row, alternating pairs from row to row
   int consumer_abort;      // written by consumers only, read after their barrier: a uniform decision
   int producer_abort;
 };
@@ -81,6 +81,21 @@ __device__ __forceinline__ float consumers_allreduce(float v, float* slots) {
   if (lane == 0) slots[warp] = v;
   ptx::named_bar_sync(1, CF::kConsumers);
   return warp_allreduce<Op>(lane < CF::kConsumerWarps ? slots[lane] : Op::identity());
+}
+
+// Two sums at once behind ONE named barrier (each in its own slot array).
+template <class CF>
+__device__ __forceinline__ void consumers_allreduce2(float& a, float& b, float* slots_a, float* slots_b) {
+  a = warp_allreduce<OpSum>(a);
+  b = warp_allreduce<OpSum>(b);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    slots_a[warp] = a;
+    slots_b[warp] = b;
+  }
+  ptx::named_bar_sync(1, CF::kConsumers);
+  a = warp_allreduce<OpSum>(lane < CF::kConsumerWarps ? slots_a[lane] : 0.0f);
+  b = warp_allreduce<OpSum>(lane < CF::kConsumerWarps ? slots_b[lane] : 0.0f);
 }
 
 // The producer: every row of this CTA, slot by slot, as far ahead as the ring allows.
@@ -137,7 +152,11 @@ __device__ __forceinline__ void finish_ring(Ring<CF>& ring) {
 // ---------------------------------------------------------------------------------------------
 // layer-norm
 // ---------------------------------------------------------------------------------------------
-template <class CF, typename T, int V>
+// SHIFTED: mean and variance from ONE pass over the row, as sums of (x - K) and (x - K)^2 with K the mean of the
+// row's first 32 elements (var = E[(x-K)^2] - (E[x-K])^2 cancels only when |mean - K| is large against the spread;
+// a row for which it turns out to be makes the centred second pass after all). Used for bf16 rows, where unpacking is the cost of a pass and the result is rounded
+// to 8 bits of mantissa; fp32 rows keep the two-pass centred variance of the register kernels and the oracle.
+template <class CF, typename T, int V, bool SHIFTED>
 __global__ void __launch_bounds__(CF::kThreads, 1)
 layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, float eps,
                     T* __restrict__ y, uint64_t rows, uint32_t cols) {
@@ -159,11 +178,16 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
     volatile int* abort_p = &ring.consumer_abort;
     const int lane = threadIdx.x & 31;
     uint32_t slot0 = 0, phase0 = 0;  // ring position of the row's first slot
-    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    uint32_t it = 0;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
+      // the slot arrays of this row's reductions: the other pair than the previous row's, so that a warp that runs
+      // ahead into the next row never overwrites what a slower warp has yet to read
+      float* red_a = ring.red[2 * (it & 1u)];
+      float* red_b = ring.red[2 * (it & 1u) + 1];
       T* yr = y + row * cols;
       bool ok = true;
-      // pass 1: the sum, slot by slot as the copies land
-      float s = 0.0f;
+      // pass 1: the sum (SHIFTED: of x - K, and of its square), slot by slot as the copies land
+      float s = 0.0f, s2 = 0.0f, shift = 0.0f;
       {
         uint32_t slot = slot0, phase = phase0;
         for (uint32_t c = 0; c < nchunks; ++c) {
@@ -174,6 +198,17 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           if (ok) {
             const Raw* src = reinterpret_cast<const Raw*>(ring_mem + slot * kSlotBytes);
             const uint32_t left = nvec - c * kSlotVecs;
+            if (SHIFTED && c == 0) {  // every thread reads the row's first vectors (broadcasts): K = their mean
+              const uint32_t kv = left < 4u ? left : 4u;
+              float acc = 0.0f;
+              for (uint32_t q = 0; q < kv; ++q) {
+                float f0[V];
+                IO::unpack(src[q], f0);
+#pragma unroll
+                for (int j = 0; j < V; ++j) acc += f0[j];
+              }
+              shift = acc / static_cast<float>(kv * V);
+            }
 #pragma unroll
             for (int i = 0; i < (kSlotVecs + kConsumers - 1) / kConsumers; ++i) {
               const uint32_t idx = threadIdx.x + i * kConsumers;
@@ -181,14 +216,58 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
                 float f[V];
                 IO::unpack(src[idx], f);
 #pragma unroll
-                for (int j = 0; j < V; ++j) s += f[j];
+                for (int j = 0; j < V; ++j) {
+                  if (SHIFTED) {
+                    const float d = f[j] - shift;
+                    s += d;
+                    s2 += d * d;
+                  } else {
+                    s += f[j];
+                  }
+                }
               }
             }
           }
           if (++slot == kSlots) { slot = 0; phase ^= 1u; }
         }
       }
-      const float mean = consumers_allreduce<CF, OpSum>(s, ring.red[0]) / n;
+      float mean, rstd;
+      if (SHIFTED) {
+        float d1 = s, d2 = s2;
+        consumers_allreduce2<CF>(d1, d2, red_a, red_b);
+        if (ring.consumer_abort != 0) break;  // uniform: written before the barrier above, by consumers only
+        const float m1 = d1 / n;
+        mean = shift + m1;
+        const float var = fmaxf(d2 / n - m1 * m1, 0.0f);
+        rstd = 1.0f / sqrtf(var + eps);
+        if (m1 * m1 > var) {
+          // K was a poor guess of the mean (further from it than one standard deviation): the difference above has
+          // cancelled digits, so this row takes the centred second pass after all. The test is on reduced values:
+          // every consumer thread decides the same way.
+          float q = 0.0f;
+          uint32_t slot = slot0;
+          for (uint32_t c = 0; c < nchunks; ++c) {
+            const Raw* src = reinterpret_cast<const Raw*>(ring_mem + slot * kSlotBytes);
+            const uint32_t left = nvec - c * kSlotVecs;
+#pragma unroll
+            for (int i = 0; i < (kSlotVecs + kConsumers - 1) / kConsumers; ++i) {
+              const uint32_t idx = threadIdx.x + i * kConsumers;
+              if (idx < left && idx < static_cast<uint32_t>(kSlotVecs)) {
+                float f[V];
+                IO::unpack(src[idx], f);
+#pragma unroll
+                for (int j = 0; j < V; ++j) q += (f[j] - mean) * (f[j] - mean);
+              }
+            }
+            if (++slot == kSlots) slot = 0;
+          }
+          ptx::named_bar_sync(1, CF::kConsumers);  // every warp has read the first reduction's slots
+          float unused = 0.0f;
+          consumers_allreduce2<CF>(q, unused, red_a, red_b);
+          rstd = 1.0f / sqrtf(q / n + eps);
+        }
+      } else {
+      mean = consumers_allreduce<CF, OpSum>(s, red_a) / n;
       if (ring.consumer_abort != 0) break;  // uniform: written before the barrier above, by consumers only
       // pass 2: centred squares
       float q = 0.0f;
@@ -210,7 +289,8 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           if (++slot == kSlots) slot = 0;
         }
       }
-      const float rstd = 1.0f / sqrtf(consumers_allreduce<CF, OpSum>(q, ring.red[1]) / n + eps);
+      rstd = 1.0f / sqrtf(consumers_allreduce<CF, OpSum>(q, red_b) / n + eps);
+      }
       // pass 3: normalise, scale, shift, store; hand each slot back once this warp has read it
       {
         uint32_t slot = slot0;
@@ -413,18 +493,18 @@ int launch_layernorm_rows_smem_bf16(const __nv_bfloat16* x, const __nv_bfloat16*
                                     float eps, __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
   typedef __nv_bfloat16 B;
   switch (pick_cfg(static_cast<uint64_t>(cols) * 2, tune(kLayernorm).p2)) {
-    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, B, 8>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, B, 8, true>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8, true>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8, true>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
   }
 }
 
 int launch_layernorm_rows_smem_f32(const float* x, const float* gamma, const float* beta, float eps, float* y,
                                    uint64_t rows, uint32_t cols, cudaStream_t s) {
   switch (pick_cfg(static_cast<uint64_t>(cols) * 4, tune(kLayernorm).p2)) {
-    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, float, 4>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, float, 4, false>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4, false>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4, false>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
   }
 }
 

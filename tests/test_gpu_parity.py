@@ -434,6 +434,8 @@ def test_rows_in_shared_memory(oracle, cuda, rows, cols):
     g32 = rng.normal(1, 0.1, cols).astype(np.float32)
     b32 = rng.normal(0, 0.1, cols).astype(np.float32)
     xl = rng.normal(0.5, 2, (rows, cols)).astype(np.float32)
+    if rows > 2 and cols > 64:
+        xl[1, :32] = 40.0   # a row whose first elements say nothing about its mean (the bf16 kernel's shift estimate)
     try:
         T.tune("layernorm", 0, 0, 0, 4)
         got32 = T.layernorm_rows(dev_f32(xl, cuda), dev_f32(g32, cuda), dev_f32(b32, cuda), 1e-5).cpu().numpy()
