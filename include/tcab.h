@@ -205,7 +205,7 @@ TCAB_API int tcab_device_status(int* status);
  *       grid; for a forced layernorm cluster: vectors per thread 4, 8), p3 = variant (softmax: 1 no cluster
  *       kernel, 2 always, 3 the shared-memory kernel, 6 no 16-byte vectors for rows that are not a multiple of
  *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
- *       3 always, 4 the shared-memory kernel).
+ *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
  *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
  *       split path, p2 = 2 launches without programmatic dependent launch, p3 = CTAs sharing the k axis of a
  *       middle-axis reduction.

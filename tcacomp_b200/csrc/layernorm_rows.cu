@@ -113,6 +113,202 @@ layernorm_rows_reg(const T* __restrict__ x, const T* __restrict__ gamma, const T
   }
 }
 
+// Rows whose length is not a multiple of a 16-byte vector (E = 4 fp32 or 8 bf16 columns). The flat array's
+// vectors still line up, so a row is read as up to E-1 leading elements, the aligned vectors inside it and up
+// to E-1 trailing elements (threads 0..2E-3 of the row's group carry one edge element each). gamma and beta
+// are aligned to column 0, not to the row's first vector: the E columns under the x vector idx are the
+// columns lead + E*idx .., which straddle two of gamma's vectors; both are loaded through L1 and the wanted
+// E columns are shifted out of the eight 32-bit words in registers (a 16-bit funnel shift for an odd bf16
+// lead, then selects by the two bits of the word shift). Same statistics as layernorm_rows_reg. Without this
+// such rows fall to 4- and 2-byte accesses: 2.3-4.4 TB/s fp32 and 1.2-2.5 TB/s bf16 at 1001..50001 columns.
+template <typename T>
+struct RowEdges {
+  static constexpr int E = 16 / sizeof(T);
+  const T* xa;    // the first aligned vector inside the row
+  T* ya;
+  const T* xrow;
+  T* yrow;
+  uint32_t lead, nint, tail;
+  __device__ __forceinline__ RowEdges(const T* x, T* y, uint64_t row, uint32_t cols) {
+    const uint64_t first = row * cols;
+    lead = static_cast<uint32_t>((E - (first & (E - 1))) & (E - 1));
+    if (lead > cols) lead = cols;
+    nint = (cols - lead) / E;
+    tail = cols - lead - E * nint;
+    xrow = x + first;
+    yrow = y + first;
+    xa = xrow + lead;
+    ya = yrow + lead;
+  }
+  // the column of the edge element thread t of the group carries (0..E-2 lead, E-1..2E-3 tail), or -1
+  __device__ __forceinline__ int edge_column(int t) const {
+    if (t < E - 1) return t < static_cast<int>(lead) ? t : -1;
+    if (t < 2 * (E - 1)) return t - (E - 1) < static_cast<int>(tail) ? static_cast<int>(lead + E * nint) + t - (E - 1) : -1;
+    return -1;
+  }
+};
+
+// The aligned vector k of a parameter row of `cols` elements as four words; columns past the end read as zero.
+template <typename T>
+__device__ __forceinline__ void param_words(const T* p, uint32_t k, uint32_t cols, uint32_t* w) {
+  constexpr int E = 16 / sizeof(T);
+  if (static_cast<uint64_t>(k + 1) * E <= cols) {
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(p) + k);
+    w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = 0;
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint64_t c = static_cast<uint64_t>(k) * 4 + j;
+        if (c < cols) w[j] = __float_as_uint(__ldg(reinterpret_cast<const float*>(p) + c));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint64_t c = static_cast<uint64_t>(k) * 8 + j;
+        if (c < cols) w[j / 2] |= static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(p) + c)) << (16 * (j & 1));
+      }
+    }
+  }
+}
+
+// E parameter columns starting `lead` columns into the aligned vector idx, as floats.
+template <typename T>
+__device__ __forceinline__ void param_shifted(const T* p, uint32_t idx, uint32_t lead, uint32_t cols, float* f) {
+  uint32_t w[8];
+  param_words(p, idx, cols, w);
+  param_words(p, idx + 1, cols, w + 4);
+  uint32_t words = lead;
+  if constexpr (sizeof(T) == 2) {
+    const uint32_t half = (lead & 1) * 16;
+#pragma unroll
+    for (int k = 0; k < 7; ++k) w[k] = __funnelshift_r(w[k], w[k + 1], half);
+    words = lead >> 1;
+  }
+#pragma unroll
+  for (int k = 0; k < 5; ++k) w[k] = (words & 2) ? w[k + 2] : w[k];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) w[k] = (words & 1) ? w[k + 1] : w[k];
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) f[k] = __uint_as_float(w[k]);
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      f[2 * k] = __uint_as_float(w[k] << 16);
+      f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+  }
+}
+
+// Resident threads per SM the unaligned kernel is compiled for: the shift holds sixteen parameter words on top
+// of the row, so a thread with 16 fp32 values fits 48 registers, one with 32 values 64, one with 64 values 128.
+template <typename T>
+constexpr int unaligned_threads_per_sm(int tpr, int vpt) {
+  const int values = vpt * static_cast<int>(16 / sizeof(T));
+  const int want = values <= 16 ? 1280 : values <= 32 ? 1024 : 512;
+  return tpr > want ? tpr : want;
+}
+
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__(row_cta_threads(TPR), unaligned_threads_per_sm<T>(TPR, VPT) / row_cta_threads(TPR))
+layernorm_rows_reg_unaligned(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                             float eps, T* __restrict__ y, uint64_t rows, uint32_t cols) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  constexpr int V = 16 / sizeof(T);
+  static_assert(TPR >= 2 * (V - 1), "one thread of the group per edge element");
+  using IO = VecIO<T, V>;
+  using IO1 = VecIO<T, 1>;
+  __shared__ float slots[2][32];
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const float n = static_cast<float>(cols);
+
+  for (uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * GROUPS; row0 < rows;
+       row0 += static_cast<uint64_t>(gridDim.x) * GROUPS) {
+    const uint64_t row = row0 + g;
+    const bool live = row < rows;
+    const RowEdges<T> r(x, y, live ? row : 0, cols);
+    const int ec = live ? r.edge_column(t) : -1;
+    float edge = 0.0f;
+    if (ec >= 0) IO1::unpack(IO1::load(r.xrow, ec), &edge);
+
+    float v[VPT][V];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < r.nint) {
+        IO::unpack(IO::load(r.xa, idx), v[i]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = 0.0f;
+      }
+    }
+
+    float s = edge;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int j = 0; j < V; ++j) s += v[i][j];
+    s = group_allreduce<OpSum, TPR>(s, slots[0], g);
+    const float mean = s / n;
+
+    float q = 0.0f;
+    if (ec >= 0) {
+      edge -= mean;
+      q = edge * edge;
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (idx < r.nint) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          v[i][j] -= mean;
+          q += v[i][j] * v[i][j];
+        }
+      }
+    }
+    q = group_allreduce<OpSum, TPR>(q, slots[1], g);
+    const float rstd = 1.0f / sqrtf(q / n + eps);
+
+    if (ec >= 0) {
+      float gf, bf;
+      IO1::unpack(IO1::load_keep(gamma, ec), &gf);
+      IO1::unpack(IO1::load_keep(beta, ec), &bf);
+      edge = edge * rstd * gf + bf;
+      IO1::store(r.yrow, ec, IO1::pack(&edge));
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const uint32_t idx = t + i * TPR;
+      if (live && idx < r.nint) {
+        float gf[V], bf[V];
+        param_shifted(gamma, idx, r.lead, cols, gf);
+        param_shifted(beta, idx, r.lead, cols, bf);
+#pragma unroll
+        for (int j = 0; j < V; ++j) v[i][j] = v[i][j] * rstd * gf[j] + bf[j];
+        IO::store(r.ya, idx, IO::pack(v[i]));
+      }
+    }
+  }
+}
+
+template <typename T, int TPR, int VPT>
+int launch_reg_unaligned(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                         cudaStream_t s) {
+  constexpr int THREADS = row_cta_threads(TPR);
+  constexpr int GROUPS = THREADS / TPR;
+  uint64_t grid = (rows + GROUPS - 1) / GROUPS;
+  if (grid > 0x7fffffffull) grid = 0x7fffffffull;
+  layernorm_rows_reg_unaligned<T, TPR, VPT><<<static_cast<unsigned>(grid), THREADS, 0, s>>>(x, gamma, beta, eps, y, rows, cols);
+  count_launch();
+  return check_launch("layernorm_rows_reg_unaligned");
+}
+
 // A row too long for one CTA's registers, cut over a thread-block cluster (see softmax_rows.cu): every
 // CTA keeps its segment in registers; the partial sums meet through distributed shared memory.
 template <typename T, int THREADS, int VPT, int V>
@@ -319,6 +515,20 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   const bool vec = (cols % VW == 0) && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta);
   const uint32_t nvec = vec ? cols / VW : cols;
   const Tune& tn = tune(kLayernorm);
+  // rows that are not whole 16-byte vectors but still fit a CTA's registers as such (p3 == 6: 4- / 2-byte path)
+  if (cols % VW != 0 && cols >= 4u * VW && aligned16(x) && aligned16(y) && aligned16(gamma) && aligned16(beta) &&
+      tn.p0 <= 0 && tn.p3 != 6) {
+    int ut = 0, uv = 0;
+    if (choose_row_shape_fit(cols / VW, true, true, VW, &ut, &uv) && ut >= 2 * (VW - 1)) {
+#define TCAB_CASE(TP, P) \
+  if constexpr (TP >= 2 * (VW - 1) && (TP < 1024 || P * VW <= 32)) /* longer rows would spill */ \
+    if (ut == TP && uv == P) return launch_reg_unaligned<T, TP, P>(x, gamma, beta, eps, y, rows, cols, s);
+      TCAB_CASE(8, 1) TCAB_CASE(8, 2) TCAB_CASE(8, 4) TCAB_CASE(16, 4) TCAB_CASE(32, 4) TCAB_CASE(64, 4) TCAB_CASE(128, 4)
+      TCAB_CASE(256, 4) TCAB_CASE(512, 4) TCAB_CASE(1024, 4) TCAB_CASE(128, 8) TCAB_CASE(256, 8) TCAB_CASE(512, 8)
+      TCAB_CASE(64, 8) TCAB_CASE(1024, 8) TCAB_CASE(1024, 16)
+#undef TCAB_CASE
+    }
+  }
   int tpr = 0, vpt = 0;
   bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {

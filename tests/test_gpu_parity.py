@@ -260,6 +260,42 @@ def test_layernorm_rows_f32(oracle, cuda, rows, cols):
     assert np.abs(got - want).max() <= 1e-5 * scale + np.abs(want - y64).max()
 
 
+@pytest.mark.parametrize("rows,cols", [(19, 33), (17, 127), (21, 130), (11, 1001), (9, 4097), (10, 8191), (9, 10001),
+                                       (5, 20001), (9, 32767), (3, 32769)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_layernorm_rows_not_whole_vectors(oracle, cuda, rows, cols, dtype):
+    # rows that start at every offset inside a 16-byte vector: edge elements, shifted gamma / beta, guarded output
+    rng = np.random.default_rng(rows * 7 + cols)
+    x = rng.normal(0.3, 1, (rows, cols)).astype(np.float32)
+    g = rng.normal(1, 0.1, cols).astype(np.float32)
+    b = rng.normal(0, 0.1, cols).astype(np.float32)
+    if dtype == "f32":
+        want = oracle.layernorm_rows_f32(x, g, b, 1e-5)
+        buf, out = guarded((rows, cols), torch.float32, cuda)
+        T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5, out=out)
+        got = out.cpu().numpy()
+        check_guards(buf, torch.float32)
+        x64 = x.astype(np.float64)
+        y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+        scale = np.abs(y64).max()
+        assert np.abs(got - y64).max() <= 1e-5 * scale
+        assert np.abs(got - want).max() <= 1e-5 * scale + np.abs(want - y64).max()
+    else:
+        xb, gb, bb = oracle.f32_to_bf16(x), oracle.f32_to_bf16(g), oracle.f32_to_bf16(b)
+        buf, out = guarded((rows, cols), torch.bfloat16, cuda)
+        T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5, out=out)
+        got = host_bits(out)
+        check_guards(buf, torch.bfloat16)
+        assert_layernorm_bf16_close(oracle, got, oracle.layernorm_rows_bf16(xb, gb, bb, 1e-5), xb, gb, bb)
+        # the 2-byte path computes the same statistics; the two may differ by a rounding on few elements
+        try:
+            T.tune("layernorm", 0, 0, 0, 6)
+            plain = host_bits(T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5))
+        finally:
+            T.tune("layernorm")
+        assert (plain != got).mean() <= 0.02
+
+
 @pytest.mark.parametrize("cols", [32776, 100000, 20001, 262144])
 def test_layernorm_cluster_kernel_forced(oracle, cuda, cols):
     # the thread-block-cluster kernel is a heuristic choice; force it so that every cluster size is checked
