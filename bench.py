@@ -47,6 +47,7 @@ NCU_TRAFFIC_BYTES = {
     "reduce_outer_f32_256x1024x1024": 1078629812,
     "map_rowsum_f32_4096x1024": 16784000,
     "gemm_bias_relu_bf16_8192": 1000201344,
+    "softmax_rows_f32_8192x16384": 1015706112,
 }
 
 
@@ -355,7 +356,15 @@ class GemmBiasRelu(Workload):
         assert err <= 1e-3, f"gemm parity check failed: relative Frobenius error {err}"
 
 
+class SoftmaxLongRows(SoftmaxRows):
+    """Rows too long for a CTA's registers (the shared-memory row kernel); selectable, not part of the default line."""
+    name = "softmax_rows_f32_8192x16384"
+    rows, cols = 8192, 16384
+    shape = "x fp32 [8192, 16384] ~ 4*N(0,1) -> y fp32 [8192, 16384]"
+
+
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu)}
+SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows})
 DEFAULT = SoftmaxRows.name
 
 
@@ -504,7 +513,7 @@ def run_ours(args) -> dict:
     from oracle import binding as oracle  # checker and CPU baseline only
 
     peaks, peak_src = load_peaks()
-    wl = WORKLOADS[args.workload]()
+    wl = SELECTABLE[args.workload]()
     wl.make(dev, seed=1234 + rank)
 
     # correctness of what is about to be timed (sampled rows against the oracle)
@@ -599,10 +608,10 @@ def run_reference(args) -> dict | None:
     if rank != 0:
         return None
     from oracle import binding as oracle
-    cls = WORKLOADS[args.workload]
+    cls = SELECTABLE[args.workload]
     scale = 1e9 if cls.bound == "hbm" else 1e12
     rng = np.random.default_rng(1234)
-    if cls is SoftmaxRows:
+    if issubclass(cls, SoftmaxRows):
         rows = cls.rows
         x = (4 * rng.standard_normal((rows, cls.cols), dtype=np.float32))
         fn, work = (lambda: oracle.softmax_rows(x)), 2.0 * rows * cls.cols * 4
@@ -658,7 +667,7 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT)
+    ap.add_argument("--workload", choices=sorted(SELECTABLE), default=DEFAULT)
     ap.add_argument("--no-others", action="store_true", help="skip the kernel-only lines of the other workloads")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,
                     help="how long the CPU baseline leg repeats its sample (at least two passes)")
