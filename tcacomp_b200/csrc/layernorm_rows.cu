@@ -539,11 +539,11 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   // Long rows with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu). fp32 from 2560
   // vectors on (10240 columns: 5.7 TB/s with three CTAs per SM, 3.8 for the 1024-thread register kernel; 4.9-5.0
   // up to 45056 columns). For bf16, unpacking is the cost of a pass: its kernel takes mean and variance from one
-  // pass (shifted sums) and wins where the register kernel needs 1024 threads, rows of 32..64 KiB (20480 columns
-  // 4.9 against 3.8, 24576 columns 5.0 against 4.0, 32768 columns 4.3 against 4.2). p3 == 4 forces the
-  // shared-memory kernel.
+  // pass (shifted sums) and wins where the register kernel needs 1024 threads, rows beyond 32 KiB (20480 columns
+  // 4.9 against 3.8, 24576 columns 5.0 against 4.0, 32768 columns 4.5 against 4.2, 65536 columns 4.0 against 3.9,
+  // 90112 columns 3.9 against 2.0). p3 == 4 forces the shared-memory kernel.
   const uint64_t row_bytes = static_cast<uint64_t>(cols) * sizeof(T);
-  const bool smem_pays = sizeof(T) == 4 ? nvec >= 2560 : (row_bytes > 32768 && row_bytes <= 65536);
+  const bool smem_pays = sizeof(T) == 4 ? nvec >= 2560 : row_bytes > 32768;
   if (vec && tn.p0 <= 0 && rows_smem_fits(row_bytes) &&
       (tn.p3 == 4 || (tn.p3 <= 0 && smem_pays && rows >= static_cast<uint64_t>(sm_count()))))
     return launch_smem(x, gamma, beta, eps, y, rows, cols, s);

@@ -156,8 +156,8 @@ __device__ __forceinline__ void finish_ring(Ring<CF>& ring) {
 // row's first 32 elements (var = E[(x-K)^2] - (E[x-K])^2 cancels only when |mean - K| is large against the spread;
 // a row for which it turns out to be makes the centred second pass after all). Used for bf16 rows, where unpacking is the cost of a pass and the result is rounded
 // to 8 bits of mantissa; fp32 rows keep the two-pass centred variance of the register kernels and the oracle.
-template <class CF, typename T, int V, bool SHIFTED>
-__global__ void __launch_bounds__(CF::kThreads, 1)
+template <class CF, typename T, int V, bool SHIFTED, bool PF = false>
+__global__ void __launch_bounds__(CF::kThreads, PF ? 12 / CF::kSlots : 1)
 layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, float eps,
                     T* __restrict__ y, uint64_t rows, uint32_t cols) {
   using IO = VecIO<T, V>;
@@ -231,6 +231,25 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           if (++slot == kSlots) { slot = 0; phase ^= 1u; }
         }
       }
+      // PF: gamma and beta of a slot are loaded one slot ahead (those of the first slot here, before the
+      // reductions), so that their trip from L2 is not paid between a slot's hand-back and the next slot's work:
+      // with the ring taking most of the SM's L1 they come from L2 for every row. Measured: fp32 16384 / 20480
+      // columns 4.8 / 5.0 -> 5.6 TB/s, rows of one CTA per SM +2-6 %. The second register set does not fit three
+      // CTAs per SM (it spills there: 5.7 -> 4.0 TB/s), so that shape keeps the loads in the third pass.
+      constexpr int kIter = (kSlotVecs + kConsumers - 1) / kConsumers;
+      Raw gcur[PF ? kIter : 1] = {}, bcur[PF ? kIter : 1] = {};
+      auto load_params = [&](uint32_t c, Raw* gq, Raw* bq) {
+        const uint32_t left = nvec - c * kSlotVecs;
+#pragma unroll
+        for (int i = 0; i < kIter; ++i) {
+          const uint32_t idx = threadIdx.x + i * kConsumers;
+          if (idx < left && idx < static_cast<uint32_t>(kSlotVecs)) {
+            gq[i] = IO::load_keep(gamma, c * kSlotVecs + idx);
+            bq[i] = IO::load_keep(beta, c * kSlotVecs + idx);
+          }
+        }
+      };
+      if constexpr (PF) load_params(0, gcur, bcur);
       float mean, rstd;
       if (SHIFTED) {
         float d1 = s, d2 = s2;
@@ -297,14 +316,23 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
         for (uint32_t c = 0; c < nchunks; ++c) {
           const Raw* src = reinterpret_cast<const Raw*>(ring_mem + slot * kSlotBytes);
           const uint32_t left = nvec - c * kSlotVecs;
+          Raw gnext[PF ? kIter : 1] = {}, bnext[PF ? kIter : 1] = {};
+          if constexpr (PF) {
+            if (c + 1 < nchunks) load_params(c + 1, gnext, bnext);
+          }
 #pragma unroll
-          for (int i = 0; i < (kSlotVecs + kConsumers - 1) / kConsumers; ++i) {
+          for (int i = 0; i < kIter; ++i) {
             const uint32_t idx = threadIdx.x + i * kConsumers;
             if (idx < left && idx < static_cast<uint32_t>(kSlotVecs)) {
               float f[V], gf[V], bf[V];
               IO::unpack(src[idx], f);
-              IO::unpack(IO::load_keep(gamma, c * kSlotVecs + idx), gf);
-              IO::unpack(IO::load_keep(beta, c * kSlotVecs + idx), bf);
+              if constexpr (PF) {
+                IO::unpack(gcur[i], gf);
+                IO::unpack(bcur[i], bf);
+              } else {
+                IO::unpack(IO::load_keep(gamma, c * kSlotVecs + idx), gf);
+                IO::unpack(IO::load_keep(beta, c * kSlotVecs + idx), bf);
+              }
 #pragma unroll
               for (int j = 0; j < V; ++j) f[j] = (f[j] - mean) * rstd * gf[j] + bf[j];
               IO::store(yr, c * kSlotVecs + idx, IO::pack(f));
@@ -312,6 +340,13 @@ layernorm_rows_smem(const T* __restrict__ x, const T* __restrict__ gamma, const 
           }
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ring.empty[slot]));
+          if constexpr (PF) {
+#pragma unroll
+            for (int i = 0; i < kIter; ++i) {
+              gcur[i] = gnext[i];
+              bcur[i] = bnext[i];
+            }
+          }
           if (++slot == kSlots) slot = 0;
         }
       }
@@ -492,19 +527,29 @@ int launch_softmax_rows_smem(const float* x, float* y, uint64_t rows, uint32_t c
 int launch_layernorm_rows_smem_bf16(const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta,
                                     float eps, __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
   typedef __nv_bfloat16 B;
+  const bool pf = tune(kLayernorm).p1 != 8;  // p1 == 8: no gamma / beta prefetch (for comparisons)
   switch (pick_cfg(static_cast<uint64_t>(cols) * 2, tune(kLayernorm).p2)) {
     case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, B, 8, true>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8, true>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8, true>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1:
+      if (pf) return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8, true, true>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+      return launch_cfg<Half>(layernorm_rows_smem<Half, B, 8, true>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default:
+      if (pf) return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8, true, true>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+      return launch_cfg<Whole>(layernorm_rows_smem<Whole, B, 8, true>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
   }
 }
 
 int launch_layernorm_rows_smem_f32(const float* x, const float* gamma, const float* beta, float eps, float* y,
                                    uint64_t rows, uint32_t cols, cudaStream_t s) {
+  const bool pf = tune(kLayernorm).p1 != 8;
   switch (pick_cfg(static_cast<uint64_t>(cols) * 4, tune(kLayernorm).p2)) {
     case 2: return launch_cfg<Third>(layernorm_rows_smem<Third, float, 4, false>, 3, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    case 1: return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4, false>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
-    default: return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4, false>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    case 1:
+      if (pf) return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4, false, true>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+      return launch_cfg<Half>(layernorm_rows_smem<Half, float, 4, false>, 2, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+    default:
+      if (pf) return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4, false, true>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
+      return launch_cfg<Whole>(layernorm_rows_smem<Whole, float, 4, false>, 1, rows, s, "layernorm_rows_smem", x, gamma, beta, eps, y, rows, cols);
   }
 }
 

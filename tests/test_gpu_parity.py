@@ -449,7 +449,8 @@ def test_reduce_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc, forced):
     assert np.array_equal(only["max"].cpu().numpy(), m, equal_nan=True)
 
 
-@pytest.mark.parametrize("rows,cols", [(3, 4096), (151, 12288), (300, 8200), (149, 45056), (5, 16), (450, 4100)])
+@pytest.mark.parametrize("rows,cols", [(3, 4096), (151, 12288), (300, 8200), (149, 45056), (5, 16), (450, 4100),
+                                       (310, 18000), (150, 36000)])
 def test_rows_in_shared_memory(oracle, cuda, rows, cols):
     # the shared-memory row kernels (bulk asynchronous copies into a ring of slots, three passes), forced through the
     # tuning hook: one slot and many, a ragged last slot, fewer rows than SMs and several rows per CTA
