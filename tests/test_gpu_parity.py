@@ -488,6 +488,37 @@ def test_rows_in_shared_memory(oracle, cuda, rows, cols):
     assert T.device_status() == 0
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_row_kernels_around_dispatch_boundaries(oracle, cuda, seed):
+    # row lengths a few columns either side of every length at which the launchers change kernel or shape, with
+    # row counts below, at and above the number of SMs; softmax fp32, layer-norm fp32 and bf16 through the heuristic
+    from oracle import checks
+    rnd = np.random.default_rng(1000 + seed)
+    bounds = [16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 10240, 12288, 16384, 20480, 24576, 32768, 45056,
+              65536, 90112, 131072]
+    for _ in range(14):
+        cols = max(1, int(rnd.choice(bounds)) + int(rnd.choice([-9, -8, -4, -3, -1, 0, 0, 1, 2, 4, 7, 8, 12, 16])))
+        rows = int(rnd.choice([1, 2, 3, 7, 40, 147, 148, 149, 300]))
+        rows = max(1, min(rows, (1 << 21) // cols))
+        x = (3 * rnd.normal(0, 1, (rows, cols)) + rnd.choice([0.0, 0.5, -2.0])).astype(np.float32)
+        g = rnd.normal(1, 0.1, cols).astype(np.float32)
+        b = rnd.normal(0, 0.1, cols).astype(np.float32)
+        what = f"rows {rows} cols {cols}"
+        got = T.softmax_rows(dev_f32(x, cuda)).cpu().numpy()
+        assert checks.softmax_close(got, x), "softmax " + what
+        got = T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5).cpu().numpy()
+        want = oracle.layernorm_rows_f32(x, g, b, 1e-5)
+        x64 = x.astype(np.float64)
+        y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+        scale = np.abs(y64).max()
+        assert np.abs(got - y64).max() <= 1e-5 * scale, "layernorm f32 " + what
+        assert np.abs(got - want).max() <= 1e-5 * scale + np.abs(want - y64).max(), "layernorm f32 vs oracle " + what
+        xb, gb, bb = oracle.f32_to_bf16(x), oracle.f32_to_bf16(g), oracle.f32_to_bf16(b)
+        got16 = host_bits(T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5))
+        assert checks.layernorm_bf16_close(got16, xb, gb, bb), "layernorm bf16 " + what
+    assert T.device_status() == 0
+
+
 @pytest.mark.parametrize("nb,nk,nc", [(1, 50000, 64), (2, 7001, 100), (1, 4096, 33), (3, 600, 260)])
 def test_chain_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc):
     # middle-axis lambda chains with few columns and a long k: k ranges over CTAs + the finishing kernel
