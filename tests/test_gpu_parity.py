@@ -604,6 +604,33 @@ def test_gemm_bias_act(oracle, cuda, m, k, n, act):
     assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
 
 
+@pytest.mark.parametrize("seed", [0, 1])
+def test_gemm_shapes_around_kernel_selection(oracle, cuda, seed):
+    # M, N, K either side of what the launcher switches on: one 128-row band or more, fewer or more 256 x 256 tiles
+    # than half the SMs, K long enough for one, two or more K ranges; ragged edges in every dimension
+    rnd = np.random.default_rng(500 + seed)
+    ms = [1, 64, 128, 129, 256, 300, 512, 1100, 2304]
+    ns = [8, 120, 256, 264, 520, 1024, 2304]
+    ks = [8, 72, 1024, 2048, 2056, 4096, 8192]
+    done = 0
+    while done < 12:
+        m, n, k = int(rnd.choice(ms)), int(rnd.choice(ns)), int(rnd.choice(ks))
+        if m * n * k > 3e8:
+            continue
+        done += 1
+        act = "relu" if done % 2 else "none"
+        a, b, bias = gemm_inputs(oracle, m, k, n, m + 3 * n + 7 * k)
+        want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, act))
+        buf, out = guarded((m, n), torch.bfloat16, cuda)
+        T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), act, out=out)
+        got = out.float().cpu().numpy()
+        check_guards(buf, torch.bfloat16)
+        what = f"m {m} n {n} k {k} {act}"
+        assert rel_frobenius(got, want) <= 1e-3, what
+        assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all(), what
+    assert T.device_status() == 0
+
+
 @pytest.mark.parametrize("m,k,n", [(512, 64, 256), (300, 200, 520), (1024, 2048, 1536), (1, 8, 8)])
 @pytest.mark.parametrize("variant", [2, 3, 4])
 def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
