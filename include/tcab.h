@@ -127,8 +127,8 @@ TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, 
                       uint32_t reduce_axis, const tcab_tensor* out, void* stream);
 
 /* tcab_chain_reduce over the INNERMOST axis for callers that must not trigger a device allocation.
- * It has no counterpart in the reference. Who needs it: a host that runs under a memory budget it
- * has already handed out in full (an embedding framework with its own arena, a serving process whose
+ * It has no counterpart in the reference. Who needs it: a host whose device memory is
+ * already handed out in full (an embedding framework with its own arena, a serving process whose
  * pool was sized at start-up), code that runs while a CUDA graph is being captured, or a real-time
  * loop in which cudaMalloc's implicit device synchronisation is not acceptable. tcab_chain_reduce may
  * allocate 64 KiB per (device, stream) for the partial results of its multi-CTA split; this variant

@@ -151,8 +151,8 @@ def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.
                          captures: Sequence[float] = (), stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """chain_reduce over the innermost axis through the entry point that never allocates.
 
-    For hosts that cannot let the library call cudaMalloc (a memory budget that is already handed
-    out, a stream capture in progress, a loop that cannot afford cudaMalloc's device
+    For hosts that cannot let the library call cudaMalloc (device memory that is already handed
+    out in full, a stream capture in progress, a loop that cannot afford cudaMalloc's device
     synchronisation). The caller passes `out`; nothing is allocated here either, on the host side
     only the small ctypes argument structs are built. At most `_lib.NOALLOC_MAX_ROWS` rows; calls on
     one device share a fixed scratch array, so do not let two of them overlap on the GPU.
