@@ -203,7 +203,8 @@ TCAB_API int tcab_device_status(int* status);
  * tests that must reach every kernel variant; results never depend on it beyond the fold order.
  *   "softmax", "layernorm": p0 = threads per row, p1 = vectors per thread (layernorm, with p0 <= 0: 8 = the
  *       shared-memory kernel without its gamma / beta prefetch), p2 = CTAs per SM (persistent
- *       grid; for a forced layernorm cluster: vectors per thread 4, 8), p3 = variant (softmax: 1 no cluster
+ *       grid; for a forced layernorm cluster: vectors per thread 4, 8; softmax clusters: 8 or 16 vectors per
+ *       thread), p3 = variant (softmax: 1 no cluster
  *       kernel, 2 always, 3 the shared-memory kernel, 6 no 16-byte vectors for rows that are not a multiple of
  *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
  *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).

@@ -307,9 +307,24 @@ int launch_cluster_shape(const float* x, float* y, uint64_t rows, uint32_t cols,
 
 // Small CTAs while they cover the row (more of them fit an SM, so a CTA waiting at a cluster barrier
 // does not idle the SM); 512 threads x 16 vectors only for the longest rows.
+// 8 or 16 vectors per thread for a row of nvec vectors on 256-thread CTAs. Both shapes keep the same bytes in
+// registers per SM (four CTAs of 32 KiB or two of 64 KiB), but only while the CTAs are full: the row is cut evenly
+// over ceil(nvec / capacity) CTAs, and what a CTA leaves unused is missing from the bytes in flight. Measured
+// (2^27 elements, TB/s, 8 against 16 vectors): 24576 columns 5.4 / 5.1, 32768 5.5 / 5.7, 40960 5.2 / 4.8, 49152
+// 5.1 / 5.3, 65536 5.0 / 5.3 -- the wider shape wins whenever it fills its CTAs as well as the narrow one, and
+// always against clusters of seven or eight narrow CTAs, which fit the SMs of a GPC badly (57344 columns 4.8 / 5.1,
+// 51200 4.4 / 4.8). tune("softmax", _, _, p2 = 8 | 16) forces one.
+inline bool cluster_wide(uint32_t nvec) {
+  const int forced = tune(kSoftmax).p2;
+  if (forced == 16) return true;
+  if (forced == 8 || nvec <= 4096u) return false;
+  const uint32_t cs8 = (nvec + 2047u) / 2048u, cs16 = (nvec + 4095u) / 4096u;
+  return cs8 >= 7u || cs8 == 2u * cs16;
+}
+
 template <int V>
 int launch_cluster(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
-  if (nvec <= 8u * 256u * 8u) return launch_cluster_shape<256, 8, V>(x, y, rows, cols, nvec, s);
+  if (nvec <= 8u * 256u * 8u && !cluster_wide(nvec)) return launch_cluster_shape<256, 8, V>(x, y, rows, cols, nvec, s);
   if (nvec <= 8u * 256u * 16u) return launch_cluster_shape<256, 16, V>(x, y, rows, cols, nvec, s);
   return launch_cluster_shape<512, 16, V>(x, y, rows, cols, nvec, s);
 }
@@ -497,7 +512,7 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
 #undef TCAB_CASE
     }
     if (nv > 2048 && rows * 8 <= 0x7fffffffull) {  // clusters of 256-thread CTAs, as for aligned rows
-      if (nv <= 8u * 256u * 8u) return launch_cluster_unaligned<256, 8>(x, y, rows, cols, nv, s);
+      if (nv <= 8u * 256u * 8u && !cluster_wide(nv)) return launch_cluster_unaligned<256, 8>(x, y, rows, cols, nv, s);
       if (nv <= 8u * 256u * 16u) return launch_cluster_unaligned<256, 16>(x, y, rows, cols, nv, s);
     }
   }
@@ -511,8 +526,10 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   // Rows of 2049..11264 vectors with enough of them to fill the GPU: the shared-memory kernel (rows_smem.cu), two or
   // three CTAs per SM while the row allows it. Measured 6.0-6.3 TB/s at 10240..20480 columns (clusters: 4.8-6.1)
   // and 5.1-5.5 at 24576..45056 (clusters: 4.8-5.4). p3 == 3 forces it.
+  // (30720..32768 columns: two full 16-vector CTAs per row run at 5.6-5.7, the ring of a lone CTA at 5.4-5.5)
+  const bool two_full_ctas = nvec >= 7680 && nvec <= 8192 && rows * 8 <= 0x7fffffffull;
   if (vec && tn.p0 <= 0 && rows_smem_fits(static_cast<uint64_t>(cols) * 4) &&
-      (tn.p3 == 3 || (tn.p3 <= 0 && nvec > 2048 && rows >= static_cast<uint64_t>(sm_count()))))
+      (tn.p3 == 3 || (tn.p3 <= 0 && nvec > 2048 && rows >= static_cast<uint64_t>(sm_count()) && !two_full_ctas)))
     return launch_softmax_rows_smem(x, y, rows, cols, s);
   // Rows beyond 2048 vectors go to the cluster kernel (2..8 CTAs of 256 threads x 8 vectors while that covers
   // the row: measured 6.1 against 4.4 TB/s for one 1024-thread CTA at 16384 columns), unless the tuning hook
