@@ -312,8 +312,8 @@ int launch_cluster_shape(const float* x, float* y, uint64_t rows, uint32_t cols,
 // over ceil(nvec / capacity) CTAs, and what a CTA leaves unused is missing from the bytes in flight. Measured
 // (2^27 elements, TB/s, 8 against 16 vectors): 24576 columns 5.4 / 5.1, 32768 5.5 / 5.7, 40960 5.2 / 4.8, 49152
 // 5.1 / 5.3, 65536 5.0 / 5.3 -- the wider shape wins whenever it fills its CTAs as well as the narrow one, and
-// always against clusters of seven or eight narrow CTAs, which fit the SMs of a GPC badly (57344 columns 4.8 / 5.1,
-// 51200 4.4 / 4.8). tune("softmax", _, _, p2 = 8 | 16) forces one.
+// always against clusters of seven or eight narrow CTAs (57344 columns 4.8 / 5.1, 51200 4.4 / 4.8; rounding seven
+// CTAs up to eight measured 1-4 % slower, so the size stays the smallest that covers the row). tune("softmax", _, _, p2 = 8 | 16) forces one.
 inline bool cluster_wide(uint32_t nvec) {
   const int forced = tune(kSoftmax).p2;
   if (forced == 16) return true;
