@@ -198,27 +198,6 @@ TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, cons
  * this library never traps: it reports here. */
 TCAB_API int tcab_device_status(int* status);
 
-/* Tuning hook, no counterpart in the reference: overrides the heuristic launch shape of one kernel
- * family for this process. Values <= 0 restore the heuristic. Meant for benchmarking sweeps and for
- * tests that must reach every kernel variant; results never depend on it beyond the fold order.
- *   "softmax", "layernorm": p0 = threads per row, p1 = vectors per thread (layernorm, with p0 <= 0: 8 = the
- *       shared-memory kernel without its gamma / beta prefetch), p2 = CTAs per SM (persistent
- *       grid; for a forced layernorm cluster: vectors per thread 4, 8; softmax clusters: 8 or 16 vectors per
- *       thread), p3 = variant (softmax: 1 no cluster
- *       kernel, 2 always, 3 the shared-memory kernel, 6 no 16-byte vectors for rows that are not a multiple of
- *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
- *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
- *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
- *       split path, p2 = 2 launches without programmatic dependent launch, p3 = CTAs sharing the k axis of a
- *       middle-axis reduction.
- *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
- *       p3 = CTAs sharing the k axis.
- *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
- *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
- *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128),
- *       p3 = ranges the K blocks of a tile are cut into by kernels 3 and 4 (1 = no split). */
-TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
-
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,52 @@
+/*
+ * tcab_tuning.h -- benchmarking and test hooks of libtcab.so. NOT part of the surface a host binds:
+ * include/tcab.h does not include this file, results never depend on anything declared here beyond
+ * the order in which partial results are folded, and the hooks are process-global and not
+ * thread-safe (set them before the threads that launch are started). The reference has no
+ * counterpart: its launch geometry is fixed when a kernel is emitted
+ * (internal/cg/cxx/emit.go:203-239 deriveLaunch).
+ */
+#ifndef TCAB_TUNING_H_
+#define TCAB_TUNING_H_
+
+#include "tcab.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Overrides the heuristic launch shape of one kernel
+ * family for this process. Values <= 0 restore the heuristic. Meant for benchmarking sweeps and for
+ * tests that must reach every kernel variant; results never depend on it beyond the fold order.
+ *   "softmax", "layernorm": p0 = threads per row, p1 = vectors per thread (layernorm, with p0 <= 0: 8 = the
+ *       shared-memory kernel without its gamma / beta prefetch), p2 = CTAs per SM (persistent
+ *       grid; for a forced layernorm cluster: vectors per thread 4, 8; softmax clusters: 8 or 16 vectors per
+ *       thread), p3 = variant (softmax: 1 no cluster
+ *       kernel, 2 always, 3 the shared-memory kernel, 6 no 16-byte vectors for rows that are not a multiple of
+ *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
+ *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
+ *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
+ *       split path, p2 = 2 launches without programmatic dependent launch, p3 = CTAs sharing the k axis of a
+ *       middle-axis reduction.
+ *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
+ *       p3 = CTAs sharing the k axis.
+ *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
+ *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
+ *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128),
+ *       p3 = ranges the K blocks of a tile are cut into by kernels 3 and 4 (1 = no split). */
+TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
+
+
+/* The launcher's plan for a middle-axis chain reduction whose k axis may be cut over several CTAs
+ * (few column tiles, long k): pure arithmetic, no device needed. Inputs: the number of (batch, column tile)
+ * pairs, of output cells, the reduced extent, how many CTAs are resident on the whole GPU at once, the SM
+ * count, and a forced number of ranges (0 = the heuristic). Outputs: the number of k ranges and their
+ * length. Every range r covers [r * klen, min(nk, (r + 1) * klen)) and none is empty. */
+TCAB_API int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident_ctas, int sms,
+                                   int forced, uint32_t* ranges, uint32_t* klen);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TCAB_TUNING_H_ */

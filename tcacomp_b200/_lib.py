@@ -62,7 +62,13 @@ SYMBOLS = [
     ("tcab_gemm_bias_act", C.c_int,
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_int, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_device_status", C.c_int, [C.POINTER(C.c_int)]),
+]
+
+# include/tcab_tuning.h: benchmarking and test hooks, not part of the surface a host binds.
+TUNING_SYMBOLS = [
     ("tcab_tune", C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]),
+    ("tcab_plan_outer_split", C.c_int,
+     [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
 ]
 
 _lib = None
@@ -78,7 +84,7 @@ def load() -> C.CDLL:
             f"{LIB_PATH} is missing: build it with `python -m tcacomp_b200.build` "
             "(there is no fallback implementation)")
     lib = C.CDLL(LIB_PATH)
-    for name, restype, argtypes in SYMBOLS:
+    for name, restype, argtypes in SYMBOLS + TUNING_SYMBOLS:
         fn = getattr(lib, name)  # AttributeError if the library does not export it
         fn.restype = restype
         fn.argtypes = argtypes

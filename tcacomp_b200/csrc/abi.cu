@@ -14,6 +14,7 @@
 #include <mutex>
 #include <utility>
 
+#include "../../include/tcab_tuning.h"
 #include "common.cuh"
 
 namespace tcab {
@@ -204,6 +205,14 @@ int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {
     }
   }
   return fail(TCAB_ERR_INVALID_ARG, "tune: unknown family '%s'", family);
+}
+
+int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident_ctas, int sms, int forced,
+                          uint32_t* ranges, uint32_t* klen) {
+  if (ranges == nullptr || klen == nullptr) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_split: null output");
+  if (sms < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_split: sms must be positive");
+  plan_outer_ranges(plan_outer_splits(tiles, cells, nk, resident_ctas, sms, forced), nk, ranges, klen);
+  return TCAB_OK;
 }
 
 int tcab_softmax_rows(const tcab_tensor* x, const tcab_tensor* y, void* stream) {

@@ -260,7 +260,8 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
                         ? 1u
                         : choose_outer_splits(tiles, static_cast<uint64_t>(nb) * nc, nk,
                                               static_cast<uint64_t>(occ > 0 ? occ : 1) * sm_count());
-  uint32_t klen = ksplit > 1 ? (nk + ksplit - 1) / ksplit : nk;
+  uint32_t klen = nk;
+  plan_outer_ranges(ksplit, nk, &ksplit, &klen);  // no range starts at or past nk
   void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps, &ksplit, &klen, &split_scratch_or_null};
   int rc = launch(kern, tiles * ksplit, 256, a, s, "chain_outer");
   if (rc != TCAB_OK || ksplit == 1) return rc;

@@ -222,7 +222,8 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 
   for (u32 work = blockIdx.x; work < nb * tiles_per_b * ksplit; work += gridDim.x) {
     const u32 tile = work / ksplit, ks = work % ksplit;
-    const u32 kbeg = ks * klen, kend = (nk - kbeg < klen) ? nk : kbeg + klen;
+    // a range that would start past the end is empty (kbeg == kend) and contributes the combiner's identity
+    const u32 kbeg = ks * klen < nk ? ks * klen : nk, kend = (nk - kbeg < klen) ? nk : kbeg + klen;
     const u32 b = tile / tiles_per_b;
     const u32 c0 = (tile % tiles_per_b) * TILE_C;
     const u32 col = c0 + lane * V;

@@ -55,20 +55,37 @@ float* split_scratch(cudaStream_t stream);
 
 // Middle-axis reductions with fewer column tiles than SMs and a long k: how many CTAs share the k axis of a
 // tile (1 = no split) -- as many as make the grid one resident wave, at least 256 k each, within the scratch.
-uint32_t choose_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident) {
-  const Tune& tn = tune(kReduceInner);
+// Pure arithmetic (no device query), so that it can be swept on a host without a GPU.
+uint32_t plan_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident, int sms, int forced) {
   if (cells == 0 || cells > kMaxSplitPartials || tiles == 0) return 1;
   uint64_t want;
-  if (tn.p3 > 0) {
-    want = static_cast<uint64_t>(tn.p3);  // forced by the tuning hook
+  if (forced > 0) {
+    want = static_cast<uint64_t>(forced);  // forced by the tuning hook
   } else {
-    if (tiles >= static_cast<uint64_t>(sm_count())) return 1;
+    if (tiles >= static_cast<uint64_t>(sms)) return 1;
     want = resident / tiles;
     if (want > nk / 256) want = nk / 256;
   }
   if (want > kMaxSplitPartials / cells) want = kMaxSplitPartials / cells;
   if (want > nk) want = nk;
   return want < 2 ? 1 : static_cast<uint32_t>(want);
+}
+
+uint32_t choose_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident) {
+  return plan_outer_splits(tiles, cells, nk, resident, sm_count(), tune(kReduceInner).p3);
+}
+
+// The ranges the launchers use: klen = ceil(nk / wanted), then as many ranges as cover [0, nk). Rounding
+// klen up can leave fewer ranges than were wanted; a range beyond the last one would start past the end
+// of the axis, so the count is recomputed from klen.
+void plan_outer_ranges(uint32_t wanted, uint32_t nk, uint32_t* ranges, uint32_t* klen) {
+  if (wanted < 2 || nk == 0) {
+    *ranges = 1;
+    *klen = nk;
+    return;
+  }
+  *klen = (nk + wanted - 1) / wanted;
+  *ranges = (nk + *klen - 1) / *klen;
 }
 
 namespace {
@@ -132,7 +149,8 @@ int launch_outer(const Args& a) {
   uint32_t ksplit = choose_outer_splits(tiles, cells, a.nk, static_cast<uint64_t>(occ > 0 ? occ : 1) * sm_count());
   float* scratch = ksplit > 1 ? split_scratch(a.stream) : nullptr;
   if (scratch == nullptr) ksplit = 1;
-  const uint32_t klen = ksplit > 1 ? (a.nk + ksplit - 1) / ksplit : a.nk;
+  uint32_t klen = a.nk;
+  plan_outer_ranges(ksplit, a.nk, &ksplit, &klen);  // no range starts at or past nk
   const uint64_t work = tiles * ksplit;
   const uint64_t grid = work > 0x7fffffffull ? 0x7fffffffull : work;  // one CTA per tile (and k range)
   fn<<<static_cast<unsigned>(grid), 32 * KW, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,

@@ -92,6 +92,8 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
                         uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s);
 uint32_t choose_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident);  // chain_outer k ranges
+uint32_t plan_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident, int sms, int forced);
+void plan_outer_ranges(uint32_t wanted, uint32_t nk, uint32_t* ranges, uint32_t* klen);  // ranges that cover [0, nk), none empty
 bool contract_big_tiles(uint32_t m, uint32_t n);  // tile choice of the fp32 contraction (tune "gemm" p2 = 4 / 8 forces it)
 int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,
                           uint32_t m, uint32_t n, uint32_t k, cudaStream_t s);

@@ -14,6 +14,7 @@
 
 #include "../../tcacomp_b200/csrc/host/pkg.h"
 #include "../../tcacomp_b200/csrc/host/tca_syntax.h"
+#include "../../include/tcab_tuning.h"
 
 #ifdef HOST_TESTS_WITH_CUDA
 #include <cuda_runtime.h>
@@ -743,7 +744,40 @@ static bool tca_gpu_tests() {
 }
 #endif  // HOST_TESTS_WITH_CUDA
 
+// The k ranges of a middle-axis reduction split over CTAs (the launcher's plan, pure arithmetic): for every
+// reduced extent, tile count and occupancy the ranges must tile [0, nk) exactly -- none empty, none
+// starting at or past nk -- because a CTA folds rows kbeg..kend of its range without another bound.
+static void test_outer_split_plan_covers_k() {
+  const int sms = 148;
+  const unsigned tiles_list[] = {1, 2, 3, 5, 8, 16, 37, 64, 100, 147};
+  unsigned long long bad = 0, split_cases = 0;
+  auto one = [&](unsigned long long tiles, unsigned long long cells, unsigned nk, unsigned long long resident, int forced) {
+    uint32_t ranges = 0, klen = 0;
+    if (tcab_plan_outer_split(tiles, cells, nk, resident, sms, forced, &ranges, &klen) != TCAB_OK) { ++bad; return; }
+    if (ranges < 1) { ++bad; return; }
+    if (ranges == 1) { if (klen != nk) ++bad; return; }
+    ++split_cases;
+    const unsigned long long last_beg = static_cast<unsigned long long>(ranges - 1) * klen;
+    if (klen == 0 || last_beg >= nk || static_cast<unsigned long long>(ranges) * klen < nk) ++bad;
+    if (cells * ranges > 262144ull) ++bad;  // the partials fit the library's scratch
+  };
+  for (int occ = 1; occ <= 8; ++occ)
+    for (unsigned tiles : tiles_list) {
+      const unsigned long long resident = static_cast<unsigned long long>(occ) * sms;
+      for (unsigned nk = 1; nk <= 300000; ++nk) one(tiles, tiles * 64ull, nk, resident, 0);
+      for (unsigned nk = 300007; nk <= 2000000; nk += 997) one(tiles, tiles * 128ull, nk, resident, 0);
+    }
+  // the shape that exposed an empty trailing range: [1, 66305, 64] with 259 wanted ranges
+  one(1, 64, 66305, 259, 0);
+  for (int forced : {2, 3, 7, 64, 259, 1000})
+    for (unsigned nk = 1; nk <= 70000; ++nk) one(1, 64, nk, 8 * sms, forced);
+  CHECK(bad == 0);
+  CHECK(split_cases > 100000);
+  std::printf("outer split plan: %llu split cases swept, %llu bad\n", split_cases, bad);
+}
+
 int main(int argc, char** argv) {
+  test_outer_split_plan_covers_k();
   test_matmul_scale_builds();
   test_eager_checks();
   test_typestate_and_classification();

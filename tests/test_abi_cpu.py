@@ -11,8 +11,8 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "tcab.h")).read()
+def declared_symbols(header="tcab.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     return sorted(set(re.findall(r"^TCAB_API[^;]*?\b(tcab_\w+)\s*\(", text, flags=re.M | re.S)))
 
 
@@ -23,6 +23,11 @@ def test_every_declared_symbol_is_exported(tcab_lib):
     for n in names:
         assert hasattr(tcab_lib, n), f"{n} declared in include/tcab.h but not exported"
     assert sorted(s[0] for s in _lib.SYMBOLS) == names, "ctypes table and header disagree"
+    tuning = declared_symbols("tcab_tuning.h")
+    for n in tuning:
+        assert hasattr(tcab_lib, n), f"{n} declared in include/tcab_tuning.h but not exported"
+    assert sorted(s[0] for s in _lib.TUNING_SYMBOLS) == tuning, "ctypes table and tuning header disagree"
+    assert "tcab_tuning.h" not in open(os.path.join(ROOT, "include", "tcab.h")).read()
     assert tcab_lib.tcab_abi_version() == 1
 
 

@@ -519,7 +519,10 @@ def test_row_kernels_around_dispatch_boundaries(oracle, cuda, seed):
     assert T.device_status() == 0
 
 
-@pytest.mark.parametrize("nb,nk,nc", [(1, 50000, 64), (2, 7001, 100), (1, 4096, 33), (3, 600, 260)])
+# (1, 66305, 64) and (1, 150000, 128): reduced extents for which rounding the range length up leaves fewer
+# ranges than CTAs were wanted (the plan must not hand a CTA a range that starts past the end of k)
+@pytest.mark.parametrize("nb,nk,nc", [(1, 50000, 64), (2, 7001, 100), (1, 4096, 33), (3, 600, 260),
+                                      (1, 66305, 64), (1, 150000, 128)])
 def test_chain_outer_k_split_over_ctas(oracle, cuda, nb, nk, nc):
     # middle-axis lambda chains with few columns and a long k: k ranges over CTAs + the finishing kernel
     rng = np.random.default_rng(nk)
