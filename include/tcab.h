@@ -120,9 +120,10 @@ TCAB_API uint64_t tcab_launch_count(void);
  * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative.
  * Allocation: when there are fewer rows than SMs and the rows are long, a row is split over several
  * CTAs (the multi-CTA reduction the reference stubs as GlobalReducer, runtime/tca/reducer.h:187-213) and
- * the partial results pass through 64 KiB of scratch memory that the library allocates with cudaMalloc
- * the first time a (device, stream) pair needs it and keeps until the process exits. Make that first
- * call outside any stream capture. */
+ * the partial results pass through 1 MiB of scratch memory that the library allocates with cudaMalloc
+ * the first time a (device, stream) pair needs it and keeps until tcab_release_stream, tcab_release_all
+ * or process exit. Make that first call outside any stream capture. A chain whose lambdas have no
+ * ahead-of-time kernel is compiled on its first call (see tcab_chain_prepare). */
 TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                       uint32_t reduce_axis, const tcab_tensor* out, void* stream);
 
@@ -131,10 +132,14 @@ TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, 
  * already handed out in full (an embedding framework with its own arena, a serving process whose
  * pool was sized at start-up), code that runs while a CUDA graph is being captured, or a real-time
  * loop in which cudaMalloc's implicit device synchronisation is not acceptable. tcab_chain_reduce may
- * allocate 64 KiB per (device, stream) for the partial results of its multi-CTA split; this variant
+ * allocate 1 MiB per (device, stream) for the partial results of its multi-CTA split; this variant
  * runs the same split kernels with the partials in a fixed 16 KiB array that is part of the library's
  * device image (every GPU that loads the library holds it until the process exits), and calls neither
- * cudaMalloc nor cudaFree nor any allocating library routine.
+ * cudaMalloc nor cudaFree nor any allocating library routine -- nor the run-time compiler:
+ *   - lambdas: the chain must have an ahead-of-time kernel or must already have been compiled in this
+ *     process (by tcab_chain_prepare or by an earlier tcab_chain_reduce with the same lambdas). Compiling
+ *     loads a code image onto the device, which is a device allocation, so this entry point never
+ *     compiles: an unknown lambda is rejected with TCAB_ERR_UNSUPPORTED and a message that says so.
  *   - operands: fp32, identical shape; the reduced axis is the innermost one; the rows (the product of
  *     the other extents) may number at most TCAB_NOALLOC_MAX_ROWS, because every row needs at least one
  *     slot of the array. More rows are rejected with TCAB_ERR_TOO_LARGE; use tcab_chain_reduce then.
@@ -146,6 +151,18 @@ TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, 
  *     them on one stream or with events. */
 TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                                        const tcab_tensor* out, void* stream);
+
+/* Compiles and loads, now, the kernels that the first tcab_chain_reduce (use = TCAB_USE_REDUCE) or
+ * tcab_chain_contract (use = TCAB_USE_CONTRACT, n_ins = 2) with these lambdas would otherwise compile on its
+ * first call. The reference compiles every kernel ahead of time from its lambdas
+ * (internal/cg/cxx/emit.go:85-190 prints the translation unit, the user runs nvcc); this is the same step
+ * for a lambda that this library has no ahead-of-time kernel for. It takes hundreds of milliseconds, loads a
+ * code image onto the current device (an implicit device allocation) and must not run during a stream
+ * capture. Lambdas that have an ahead-of-time kernel return at once. Only the lambdas and the operand count
+ * matter; `init` and the capture values may differ in later calls. */
+#define TCAB_USE_REDUCE 0
+#define TCAB_USE_CONTRACT 1
+TCAB_API int tcab_chain_prepare(const tcab_chain* chain, uint32_t n_ins, int use);
 
 /* Contraction chain over fp32 operands indexed by different dim subsets:
  *   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )   rhs_is_nk == 0, rhs is [K,N]
@@ -190,6 +207,15 @@ TCAB_API int tcab_layernorm_rows(const tcab_tensor* x, const tcab_tensor* gamma,
  * Requires K % 8 == 0, N % 8 == 0 and 16-byte aligned base pointers (TMA tensor maps). */
 TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias,
                        int act, const tcab_tensor* c, void* stream);
+
+/* Scratch memory the library allocated for launches on `stream` of the current device (the multi-CTA
+ * partials of tcab_chain_reduce: 1 MiB; of tcab_reduce_outer: 3 MiB; the K-range workspace of
+ * tcab_gemm_bias_act: up to 64 MiB) is freed; tcab_release_all frees it for every device and stream. A host
+ * that creates and destroys streams calls tcab_release_stream before destroying one. cudaFree waits for the
+ * device to go idle, so neither call may run during a stream capture. No counterpart in the reference, whose
+ * launchers own no memory (internal/cg/cxx/launch.go:23-156). */
+TCAB_API int tcab_release_stream(void* stream);
+TCAB_API int tcab_release_all(void);
 
 /* Reads the device-side status word of the current device into *status (a synchronous copy):
  * 0 = no kernel of this library has given up on a bounded wait since the library was loaded,

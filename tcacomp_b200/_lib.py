@@ -19,6 +19,7 @@ NOALLOC_MAX_ROWS = 4096
 OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE = range(8)
 F32, BF16, I32 = 0, 1, 2
 ACT_NONE, ACT_RELU = 0, 1
+USE_REDUCE, USE_CONTRACT = 0, 1
 
 
 class Tensor(C.Structure):
@@ -62,6 +63,9 @@ SYMBOLS = [
     ("tcab_gemm_bias_act", C.c_int,
      [C.POINTER(Tensor), C.POINTER(Tensor), C.POINTER(Tensor), C.c_int, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_device_status", C.c_int, [C.POINTER(C.c_int)]),
+    ("tcab_chain_prepare", C.c_int, [C.POINTER(Chain), C.c_uint32, C.c_int]),
+    ("tcab_release_stream", C.c_int, [C.c_void_p]),
+    ("tcab_release_all", C.c_int, []),
 ]
 
 # include/tcab_tuning.h: benchmarking and test hooks, not part of the surface a host binds.

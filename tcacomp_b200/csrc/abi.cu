@@ -102,6 +102,49 @@ int occupancy(const void* fn, int block, size_t smem) {
 }
 
 namespace {
+struct ScratchBuf {
+  void* p = nullptr;
+  size_t bytes = 0;
+};
+std::mutex g_scratch_mu;
+std::map<std::pair<std::pair<int, cudaStream_t>, int>, ScratchBuf> g_scratch;
+}  // namespace
+
+void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow) {
+  const int dev = current_device();
+  if (dev < 0) return nullptr;
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  ScratchBuf& b = g_scratch[{{dev, stream}, kind}];
+  if (b.p != nullptr && b.bytes >= bytes) return b.p;
+  if (b.p != nullptr) {
+    if (!grow) return nullptr;
+    cudaFree(b.p);
+    b = ScratchBuf{};
+  }
+  if (cudaMalloc(&b.p, bytes) != cudaSuccess) {
+    cudaGetLastError();
+    b = ScratchBuf{};
+    return nullptr;
+  }
+  b.bytes = bytes;
+  return b.p;
+}
+
+namespace {
+
+// Frees the buffers of one (device, stream), or all of them. cudaFree waits for the device to go idle.
+void release_scratch(bool all, int dev, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  for (auto it = g_scratch.begin(); it != g_scratch.end();) {
+    if (all || (it->first.first.first == dev && it->first.first.second == stream)) {
+      if (it->second.p != nullptr) cudaFree(it->second.p);
+      it = g_scratch.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  cudaGetLastError();
+}
 
 // ---- validation helpers ----------------------------------------------------
 
@@ -190,6 +233,34 @@ int tcab_device_status(int* status) {
   TCAB_TRY(rows_smem_status(&rows));
   *status = gemm != 0 ? gemm : (rows != 0 ? 16 : 0);  // 1..4: a contraction kernel, 16: a shared-memory row kernel
   return TCAB_OK;
+}
+
+int tcab_release_stream(void* stream) {
+  TCAB_TRY(have_device("release_stream"));
+  release_scratch(false, current_device(), static_cast<cudaStream_t>(stream));
+  return TCAB_OK;
+}
+
+int tcab_release_all(void) {
+  release_scratch(true, 0, nullptr);
+  return TCAB_OK;
+}
+
+int tcab_chain_prepare(const tcab_chain* chain, uint32_t n_ins, int use) {
+  const char* op = "chain_prepare";
+  if (chain == nullptr || chain->map_expr == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: chain and map_expr are required", op);
+  if (use != TCAB_USE_REDUCE && use != TCAB_USE_CONTRACT)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: unknown use %d", op, use);
+  if (chain->combine_expr == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: combine_expr is required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  if (n_ins < 1 || n_ins > TCAB_MAX_INPUTS || (use == TCAB_USE_CONTRACT && n_ins != 2))
+    return fail(TCAB_ERR_INVALID_ARG, "%s: bad operand count %u", op, n_ins);
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
+  TCAB_TRY(have_device(op));
+  return warm_chain(pc, use == TCAB_USE_CONTRACT);
 }
 
 int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {

@@ -192,7 +192,7 @@ int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStrea
 bool jit_available() { return nvrtc().ok; }
 
 int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
-                void** handle) {
+                void** handle, bool compile_if_missing) {
   const std::string key = std::string(contraction ? "C|" : "R|") + std::to_string(n_in) + "|" + std::to_string(combine) + "|" +
                           map_text + "|" + post_text;
   std::lock_guard<std::mutex> lk(g_mu);
@@ -205,6 +205,7 @@ int jit_prepare(const std::string& map_text, const std::string& post_text, int c
   if (f != g_failed.end())
     return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: run-time compilation of map '%s' failed earlier: %s",
                 map_text.c_str(), f->second.c_str());
+  if (!compile_if_missing) return fail(TCAB_ERR_UNSUPPORTED, "chain: lambda '%s' is not compiled yet", map_text.c_str());
   JitChain* jc = nullptr;
   const int rc = compile(key, map_text, post_text, combine, n_in, contraction, &jc);
   if (rc != TCAB_OK) return rc;

@@ -5,7 +5,6 @@
 // canonicaliser prints, so that the key and the code cannot drift apart: the
 // macro stringifies the expression it compiles. A chain whose lambdas are not in
 // the table is reported as unsupported by this build.
-#include <map>
 #include <mutex>
 #include <string>
 #include <utility>
@@ -279,28 +278,9 @@ const Entry kTable[] = {
     TCAB_ENTRY(MapAxpy, PostAddTanh, 0), TCAB_ENTRY(MapMul2, PostScale, 0),
 };
 
-// Scratch for the partials of the split path: one buffer of kMaxSplitPartials floats per
-// (device, stream), allocated with cudaMalloc the first time a stream needs it and kept until the
-// process exits. Per stream, because launches on different streams may overlap on the GPU.
+// Scratch for the partials of the split path: kMaxSplitPartials floats per (device, stream).
 float* split_scratch(cudaStream_t stream) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, float*> table;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  std::lock_guard<std::mutex> lk(mu);
-  auto key = std::make_pair(dev, stream);
-  auto it = table.find(key);
-  if (it != table.end()) return it->second;
-  float* p = nullptr;
-  if (cudaMalloc(&p, kMaxSplitPartials * sizeof(float)) != cudaSuccess) {
-    cudaGetLastError();
-    p = nullptr;  // not fatal: the caller falls back to the single-CTA-per-row kernels
-  }
-  table[key] = p;
-  return p;
+  return static_cast<float*>(stream_scratch(kScratchChainSplit, stream, kMaxSplitPartials * sizeof(float), false));
 }
 
 int combine_id(const std::string& text) {
@@ -374,6 +354,27 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   Args a{ins, out, outer, nk, inner, pc.init, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
   return kTable[pc.entry].launch(a);
+}
+
+// Compiles and loads the kernels of a chain that has no ahead-of-time instance (nothing to do otherwise).
+int warm_chain(const PreparedChain& pc, bool contraction) {
+  if (contraction) {
+    if (pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text() &&
+        (std::string(kTable[pc.entry].post).empty() || std::string(kTable[pc.entry].post) == PostScale::text()))
+      return TCAB_OK;
+    std::string map_text = pc.map_text, post_text = pc.post_text;
+    int combine = pc.combine;
+    if (pc.entry >= 0) {
+      map_text = kTable[pc.entry].map;
+      post_text = kTable[pc.entry].post;
+      combine = kTable[pc.entry].combine;
+    }
+    void* h = nullptr;
+    return jit_prepare(map_text, post_text, combine, 2, true, &h);
+  }
+  if (pc.entry != kJitEntry) return TCAB_OK;
+  void* h = nullptr;
+  return jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
 }
 
 // ---------------------------------------------------------------------------
@@ -505,9 +506,14 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
   if (splits * rows > kNoAllocMaxPartials) splits = kNoAllocMaxPartials / rows;
   if (splits < 1) splits = 1;
   if (pc.entry == kJitEntry) {
+    // Never compiled here: compiling loads a code image onto the device, which allocates device memory.
     void* h = nullptr;
-    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
-    if (jrc != TCAB_OK) return jrc;
+    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h, false);
+    if (jrc != TCAB_OK)
+      return fail(TCAB_ERR_UNSUPPORTED,
+                  "chain_reduce_noalloc: the lambda '%s' has no ahead-of-time kernel and has not been compiled in this "
+                  "process yet; call tcab_chain_prepare (or tcab_chain_reduce) with it once, outside any capture",
+                  pc.map_text.c_str());
     // the split kernels always: splits may be 1, the partials still pass through the fixed array
     return jit_launch(h, ins, rows, nk, 1, pc.init, pc.caps, out, scratch, static_cast<uint32_t>(splits) | 0x80000000u, s);
   }

@@ -38,6 +38,14 @@ enum Family { kSoftmax = 0, kLayernorm = 1, kReduceInner = 2, kReduceOuter = 3, 
 // Resident CTAs per SM of a kernel at a block size / dynamic smem, cached per (function, block).
 int occupancy(const void* fn, int block, size_t smem);
 
+// Scratch memory the library owns: one buffer per (device, stream, kind), allocated with cudaMalloc the first
+// time a launch on that stream needs it and kept until tcab_release_stream / tcab_release_all or process
+// exit. Per stream, because launches on different streams may overlap on the GPU. Returns null when the
+// allocation failed (the callers then take a path that needs no scratch). With `grow`, a buffer that is
+// too small is freed (cudaFree synchronises the device, so nothing still reads it) and allocated anew.
+enum ScratchKind { kScratchChainSplit = 0, kScratchOuter = 1, kScratchGemm = 2, kScratchKinds = 3 };
+void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline uint32_t pow2_ceil(uint32_t v) {
@@ -76,7 +84,9 @@ constexpr int kJitEntry = -2;
 // Run-time compilation of chains without an ahead-of-time instance (chain_jit.cu).
 bool jit_available();
 int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
-                void** handle);  // contraction: compile the contraction kernels instead of the reduction kernels
+                void** handle, bool compile_if_missing = true);  // contraction: the contraction kernels instead of the
+                                                                 // reduction kernels; without compile_if_missing a
+                                                                 // lambda that is not cached yet is TCAB_ERR_UNSUPPORTED
 int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
                const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s);
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
@@ -87,6 +97,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
                          int act, __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k,
                          cudaStream_t s);
 
+int warm_chain(const PreparedChain& pc, bool contraction);  // compile + load now what a launch would compile later
 int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins, uint64_t rows, uint32_t nk,
                                 float* out, cudaStream_t s);
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,

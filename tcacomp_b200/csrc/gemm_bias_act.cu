@@ -858,25 +858,8 @@ gemm_split_finish(const float* __restrict__ partial, const float* __restrict__ b
 // Workspace of the K split: one buffer per (device, stream), grown on demand up to kSplitWorkspaceBytes.
 constexpr size_t kSplitWorkspaceBytes = static_cast<size_t>(64) << 20;
 float* gemm_split_workspace(cudaStream_t stream, size_t bytes) {
-  struct Buf { float* p; size_t bytes; };
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, Buf> table;
   if (bytes > kSplitWorkspaceBytes) return nullptr;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> lk(mu);
-  Buf& b = table[{dev, stream}];
-  if (b.bytes >= bytes) return b.p;
-  if (b.p != nullptr) cudaFree(b.p);  // synchronises the device: nothing still reads the old buffer afterwards
-  b.p = nullptr;
-  b.bytes = 0;
-  if (cudaMalloc(&b.p, bytes) != cudaSuccess) {
-    cudaGetLastError();
-    b.p = nullptr;
-    return nullptr;
-  }
-  b.bytes = bytes;
-  return b.p;
+  return static_cast<float*>(stream_scratch(kScratchGemm, stream, bytes, true));
 }
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not

@@ -179,23 +179,11 @@ reduce_outer_finish(const float* __restrict__ part, float* __restrict__ sum, flo
 }
 
 // Scratch for the partial states: kMaxPartialCells cells x 3 values per (device, stream), allocated the
-// first time a stream needs the split and kept until the process exits.
+// first time a stream needs the split (stream_scratch).
 constexpr uint32_t kMaxPartialCells = 262144;  // ksplit * nb * nc at most: 3 MiB
 float* outer_scratch(cudaStream_t stream) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, float*> table;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> lk(mu);
-  auto it = table.find({dev, stream});
-  if (it != table.end()) return it->second;
-  float* p = nullptr;
-  if (cudaMalloc(&p, static_cast<size_t>(3) * kMaxPartialCells * sizeof(float)) != cudaSuccess) {
-    cudaGetLastError();
-    return nullptr;  // no split then
-  }
-  table[{dev, stream}] = p;
-  return p;
+  return static_cast<float*>(
+      stream_scratch(kScratchOuter, stream, static_cast<size_t>(3) * kMaxPartialCells * sizeof(float), false));
 }
 
 // How many CTAs share the k axis of one (b, column tile): none while the tiles alone fill the GPU; otherwise as

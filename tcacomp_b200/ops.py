@@ -20,6 +20,10 @@ _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int32: _lib
 def _view(t: torch.Tensor, name: str) -> _lib.Tensor:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor")
+    # the C struct holds 32-bit extents and ctypes would truncate silently: refuse here what the library
+    # refuses with TCAB_ERR_TOO_LARGE (the reference indexes with u32)
+    if t.numel() >= 2**32 or any(d >= 2**32 for d in t.shape):
+        raise ValueError(f"{name}: 2^32 or more elements ({tuple(t.shape)}); extents and element counts are 32-bit")
     if t.device.type != "cuda":
         raise ValueError(f"{name} must live on a CUDA device (this library has no CPU path)")
     if not t.is_contiguous():
@@ -46,6 +50,29 @@ def _on_device(t: torch.Tensor):
     return torch.cuda.device(t.device)
 
 
+def _same_device(*named) -> None:
+    """Every tensor of one call lives on the first one's device (the call runs there, on its stream)."""
+    first_name, first = named[0]
+    for name, t in named[1:]:
+        if t is not None and t.device != first.device:
+            raise ValueError(f"{name} is on {t.device} but {first_name} is on {first.device}")
+
+
+def _chain(map_expr: str, combine_expr: str, post_expr: Optional[str], init: float,
+           captures: Sequence[float]) -> _lib.Chain:
+    if len(captures) > _lib.MAX_CAPTURES:
+        raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
+    chain = _lib.Chain()
+    chain.map_expr = map_expr.encode()
+    chain.combine_expr = combine_expr.encode()
+    chain.post_expr = post_expr.encode() if post_expr else None
+    chain.init = init
+    chain.n_captures = len(captures)
+    for i, c in enumerate(captures):
+        chain.captures[i] = c
+    return chain
+
+
 def launch_count() -> int:
     """Kernels launched by the library in this process."""
     return int(_lib.load().tcab_launch_count())
@@ -63,12 +90,37 @@ def tune(family: str, p0: int = 0, p1: int = 0, p2: int = 0, p3: int = 0) -> Non
     _lib.check(_lib.load().tcab_tune(family.encode(), p0, p1, p2, p3))
 
 
+def chain_prepare(map_expr: str, n_ins: int = 1, combine_expr: str = "(p0 + p1)", post_expr: Optional[str] = None,
+                  captures: Sequence[float] = (), contraction: bool = False,
+                  device: Optional[torch.device] = None) -> None:
+    """Compile and load now what the first chain_reduce / chain_contract with these lambdas would compile
+    later (nothing to do for lambdas with an ahead-of-time kernel). Not during a stream capture."""
+    chain = _chain(map_expr, combine_expr, post_expr, 0.0, captures)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _lib.check(_lib.load().tcab_chain_prepare(C.byref(chain), n_ins,
+                                                  _lib.USE_CONTRACT if contraction else _lib.USE_REDUCE))
+
+
+def release_stream(stream: Optional[torch.cuda.Stream] = None, device: Optional[torch.device] = None) -> None:
+    """Free the scratch the library allocated for launches on `stream` (default: the current stream)."""
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    s = stream if stream is not None else torch.cuda.current_stream(dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().tcab_release_stream(C.c_void_p(s.cuda_stream)))
+
+
+def release_all() -> None:
+    """Free every scratch buffer the library holds, on every device and stream."""
+    _lib.check(_lib.load().tcab_release_all())
+
+
 def softmax_rows(x: torch.Tensor, out: Optional[torch.Tensor] = None,
                  stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Row softmax over the innermost axis (fp32)."""
     if out is None:
         out = torch.empty_like(x)
     xv, yv = _view(x, "x"), _view(out, "out")
+    _same_device(("x", x), ("out", out))
     with _on_device(x):
         _lib.check(_lib.load().tcab_softmax_rows(C.byref(xv), C.byref(yv), _stream(stream, x)))
     return out
@@ -81,6 +133,7 @@ def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps
     if out is None:
         out = torch.empty_like(x)
     xv, gv, bv, yv = _view(x, "x"), _view(gamma, "gamma"), _view(beta, "beta"), _view(out, "out")
+    _same_device(("x", x), ("gamma", gamma), ("beta", beta), ("out", out))
     with _on_device(x):
         _lib.check(_lib.load().tcab_layernorm_rows(C.byref(xv), C.byref(gv), C.byref(bv),
                                                    C.c_float(eps), C.byref(yv), _stream(stream, x)))
@@ -101,6 +154,7 @@ def reduce_outer(t: torch.Tensor, want: Sequence[str] = ("sum", "max", "argmax")
                                     dtype=torch.int32 if name == "argmax" else torch.float32)
     tv = _view(t, "t")
     views = {k: _view(v, k) for k, v in res.items()}
+    _same_device(("t", t), *res.items())
 
     def ref(k):
         return C.byref(views[k]) if k in views else None
@@ -123,23 +177,15 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
     ins = list(ins)
     if not 1 <= len(ins) <= _lib.MAX_INPUTS:
         raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
-    if len(captures) > _lib.MAX_CAPTURES:
-        raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
     t0 = ins[0]
     ax = axis % t0.dim()
     if out is None:
         shape = [d for i, d in enumerate(t0.shape) if i != ax] or [1]
         out = torch.empty(shape, device=t0.device, dtype=torch.float32)
-    chain = _lib.Chain()
-    chain.map_expr = map_expr.encode()
-    chain.combine_expr = combine_expr.encode()
-    chain.post_expr = post_expr.encode() if post_expr else None
-    chain.init = init
-    chain.n_captures = len(captures)
-    for i, c in enumerate(captures):
-        chain.captures[i] = c
+    chain = _chain(map_expr, combine_expr, post_expr, init, captures)
     arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
     ov = _view(out, "out")
+    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
     with _on_device(t0):
         _lib.check(_lib.load().tcab_chain_reduce(C.byref(chain), arr, len(ins), ax, C.byref(ov),
                                                  _stream(stream, t0)))
@@ -160,18 +206,10 @@ def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.
     ins = list(ins)
     if not 1 <= len(ins) <= _lib.MAX_INPUTS:
         raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
-    if len(captures) > _lib.MAX_CAPTURES:
-        raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
-    chain = _lib.Chain()
-    chain.map_expr = map_expr.encode()
-    chain.combine_expr = combine_expr.encode()
-    chain.post_expr = post_expr.encode() if post_expr else None
-    chain.init = init
-    chain.n_captures = len(captures)
-    for i, c in enumerate(captures):
-        chain.captures[i] = c
+    chain = _chain(map_expr, combine_expr, post_expr, init, captures)
     arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
     ov = _view(out, "out")
+    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
     with _on_device(ins[0]):
         _lib.check(_lib.load().tcab_chain_reduce_noalloc(C.byref(chain), arr, len(ins), C.byref(ov),
                                                          _stream(stream, ins[0])))
@@ -186,15 +224,9 @@ def chain_contract(lhs: torch.Tensor, rhs: torch.Tensor, map_expr: str = "(p0 * 
     n = rhs.shape[0] if rhs_is_nk else rhs.shape[1]
     if out is None:
         out = torch.empty((lhs.shape[0], n), device=lhs.device, dtype=torch.float32)
-    chain = _lib.Chain()
-    chain.map_expr = map_expr.encode()
-    chain.combine_expr = combine_expr.encode()
-    chain.post_expr = post_expr.encode() if post_expr else None
-    chain.init = init
-    chain.n_captures = len(captures)
-    for i, c in enumerate(captures):
-        chain.captures[i] = c
+    chain = _chain(map_expr, combine_expr, post_expr, init, captures)
     lv, rv, ov = _view(lhs, "lhs"), _view(rhs, "rhs"), _view(out, "out")
+    _same_device(("lhs", lhs), ("rhs", rhs), ("out", out))
     with _on_device(lhs):
         _lib.check(_lib.load().tcab_chain_contract(C.byref(chain), C.byref(lv), C.byref(rv), int(bool(rhs_is_nk)),
                                                    C.byref(ov), _stream(stream, lhs)))
@@ -209,6 +241,7 @@ def gemm_bias_act(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor]
         out = torch.empty((a.shape[0], b.shape[1]), device=a.device, dtype=torch.bfloat16)
     av, bv, cv = _view(a, "a"), _view(b, "b"), _view(out, "out")
     biasv = _view(bias, "bias") if bias is not None else None
+    _same_device(("a", a), ("b", b), ("bias", bias), ("out", out))
     code = {"none": _lib.ACT_NONE, "relu": _lib.ACT_RELU}[act]
     with _on_device(a):
         _lib.check(_lib.load().tcab_gemm_bias_act(C.byref(av), C.byref(bv),

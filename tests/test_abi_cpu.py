@@ -145,3 +145,32 @@ def test_tune_rejects_unknown_family(tcab_lib):
     from tcacomp_b200 import _lib
     assert tcab_lib.tcab_tune(b"nope", 1, 1, 1, 0) == _lib.ERR_INVALID_ARG
     assert tcab_lib.tcab_tune(b"softmax", 0, 0, 0, 0) == _lib.OK
+
+
+def test_python_views_refuse_what_32_bit_extents_cannot_hold():
+    # ctypes truncates a value >= 2^32 stored into a c_uint32 field without an error; the Python view must not
+    import torch
+    from tcacomp_b200 import ops
+    with pytest.raises(ValueError, match="32-bit"):
+        ops._view(torch.empty((2**32,), device="meta"), "x")
+    with pytest.raises(ValueError, match="32-bit"):
+        ops._view(torch.empty((2**16, 2**16), device="meta"), "x")
+    with pytest.raises(ValueError, match="CUDA device"):
+        ops._view(torch.empty((4, 4)), "x")
+
+
+def test_prepare_and_release_validate_without_a_device(tcab_lib):
+    from tcacomp_b200 import _lib
+    L = tcab_lib
+    ch = _lib.Chain()
+    ch.map_expr, ch.combine_expr = b"sinf(p0) * p1", b"(p0 + p1)"
+    assert L.tcab_chain_prepare(C.byref(ch), 2, 7) == _lib.ERR_INVALID_ARG          # unknown use
+    assert L.tcab_chain_prepare(C.byref(ch), 3, _lib.USE_CONTRACT) == _lib.ERR_INVALID_ARG  # contractions take two
+    ch.map_expr = b"sinf(p0) * q1"
+    assert L.tcab_chain_prepare(C.byref(ch), 2, _lib.USE_REDUCE) == _lib.ERR_INVALID_ARG    # the lambda is validated first
+    import torch
+    if not torch.cuda.is_available():
+        ch.map_expr = b"sinf(p0) * p1"
+        assert L.tcab_chain_prepare(C.byref(ch), 2, _lib.USE_REDUCE) == _lib.ERR_CUDA      # compiling needs the device
+        assert L.tcab_release_stream(None) == _lib.ERR_CUDA
+    assert L.tcab_release_all() == _lib.OK                                               # nothing held: nothing to free

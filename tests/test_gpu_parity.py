@@ -825,8 +825,13 @@ def test_run_time_compiled_lambdas_every_kernel_shape(oracle, cuda):
     with pytest.raises(T.TcabError) as e:
         T.chain_reduce([dev_f32(a, cuda)], "p0); } __global__ void k() { (void)(0")
     assert e.value.status == T._lib.ERR_INVALID_ARG
-    # the entry point that allocates nothing runs compiled lambdas too
+    # the entry point that allocates nothing runs compiled lambdas too, but never compiles one itself
+    # (loading a code image allocates device memory): an unknown lambda is refused until it has been prepared
     out = torch.empty((17,), device=cuda)
+    with pytest.raises(T.TcabError) as e:
+        T.chain_reduce_noalloc([dev_f32(a, cuda)], "cosf(p0) * cosf(p0)", out=out)
+    assert e.value.status == T._lib.ERR_UNSUPPORTED and "tcab_chain_prepare" in e.value.message
+    T.chain_prepare("cosf(p0) * cosf(p0)", n_ins=1)
     T.chain_reduce_noalloc([dev_f32(a, cuda)], "cosf(p0) * cosf(p0)", out=out)
     assert np.allclose(out.cpu().numpy(), (np.cos(a.astype(np.float64)) ** 2).sum(1), rtol=1e-5)
 
