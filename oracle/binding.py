@@ -134,6 +134,30 @@ def layernorm_rows_bf16(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray,
     return y
 
 
+def check_layernorm_bf16(got: np.ndarray, want: np.ndarray, x: np.ndarray, gamma: np.ndarray, beta: np.ndarray,
+                         eps: float = 1e-5) -> np.ndarray:
+    """Per-row counts [rows, 5] of the bf16 layer-norm criterion (oracle/checks.py states it):
+    checked, failed, accepted only through the added terms, got != want, want != rounded fp64."""
+    rows, cols = x.shape
+    for a in (got, want, x, gamma, beta):
+        assert a.dtype == np.uint16
+    counts = np.zeros((rows, 5), np.uint64)
+    lib().orc_check_layernorm_bf16(_ptr(got), _ptr(want), _ptr(x), _ptr(gamma), _ptr(beta), C.c_uint32(rows),
+                                   C.c_uint32(cols), C.c_double(eps), _ptr(counts))
+    return counts
+
+
+def check_softmax(got: np.ndarray, want: np.ndarray, x: np.ndarray) -> np.ndarray:
+    """Per-row counts [rows, 5] of the two-sided softmax criterion: checked, failed, accepted only through
+    the oracle's own distance to the fp64 value (the last two columns are unused)."""
+    rows, cols = x.shape
+    for a in (got, want, x):
+        assert a.dtype == np.float32
+    counts = np.zeros((rows, 5), np.uint64)
+    lib().orc_check_softmax(_ptr(got), _ptr(want), _ptr(x), C.c_uint32(rows), C.c_uint32(cols), _ptr(counts))
+    return counts
+
+
 def layernorm_rows_f32(x: np.ndarray, gamma: np.ndarray, beta: np.ndarray,
                        eps: float = 1e-5) -> np.ndarray:
     rows, cols = x.shape

@@ -781,3 +781,115 @@ ORC_API int orc_suite(int kernel, const float* x, const float* z, uint32_t d0, u
       return -1;
   }
 }
+
+/* ------------------------------------------------------------------------ */
+/* Parity criteria over whole tensors (the per-element rules of oracle/checks.py, */
+/* restated in C so that half a billion elements are checked in seconds).         */
+/* counts is [rows][5] uint64: checked, failed, passed-only-through-the-added-    */
+/* terms, got != want, want != rounded fp64. Rows are independent.                */
+/* ------------------------------------------------------------------------ */
+static inline double bf16_ulp_of(double v) {
+  /* 2 ** (floor(log2 |v|) - 7): the spacing of bf16 values (8 significant bits) at |v| */
+  int e;
+  double a = fabs(v);
+  if (a < 1e-38) a = 1e-38;
+  (void)frexp(a, &e); /* a = m * 2**e, m in [0.5, 1) */
+  return ldexp(1.0, e - 8);
+}
+
+typedef struct {
+  const uint16_t* got;
+  const uint16_t* want;
+  const uint16_t* x;
+  const uint16_t* gamma;
+  const uint16_t* beta;
+  uint32_t cols;
+  double eps;
+  uint64_t* counts;
+} orc_check_ln_ctx;
+
+static void orc_check_layernorm_bf16_body(const void* p, int64_t lo, int64_t hi) {
+  const orc_check_ln_ctx* q = (const orc_check_ln_ctx*)p;
+  const uint32_t n = q->cols;
+  for (int64_t r = lo; r < hi; ++r) {
+    const uint16_t* xr = q->x + (size_t)r * n;
+    const uint16_t* gr = q->got + (size_t)r * n;
+    const uint16_t* wr = q->want + (size_t)r * n;
+    uint64_t* c = q->counts + (size_t)r * 5;
+    double s = 0.0;
+    for (uint32_t j = 0; j < n; ++j) s += (double)bf16_to_f32(xr[j]);
+    const double mean = n ? s / n : 0.0;
+    double ss = 0.0;
+    for (uint32_t j = 0; j < n; ++j) {
+      const double d = (double)bf16_to_f32(xr[j]) - mean;
+      ss += d * d;
+    }
+    const double var = n ? ss / n : 0.0;
+    const double std = sqrt(var + q->eps);
+    uint64_t failed = 0, via = 0, differ = 0, off = 0;
+    for (uint32_t j = 0; j < n; ++j) {
+      const double g = (double)bf16_to_f32(q->gamma[j]), b = (double)bf16_to_f32(q->beta[j]);
+      const double xhat = ((double)bf16_to_f32(xr[j]) - mean) / std;
+      const double y64 = xhat * g + b;
+      const uint16_t r64b = f32_to_bf16((float)y64);
+      const double r64 = (double)bf16_to_f32(r64b);
+      const double got = (double)bf16_to_f32(gr[j]), want = (double)bf16_to_f32(wr[j]);
+      const double fp32err = 1e-5 * (fabs(xhat * g) + fabs(b)) + 1e-6 * (fabs(mean) / std + 1.0) * fabs(g);
+      const double ulp = bf16_ulp_of(fabs(y64) > fabs(got) ? y64 : got);
+      const double d_o = fabs(got - want);
+      const double ulp_w = bf16_ulp_of(want);
+      const int accepted = (fabs(got - y64) <= 0.5 * ulp + fp32err + 1e-30) && (d_o <= ulp_w + fp32err + fabs(want - r64));
+      const int bare = d_o <= ulp_w;
+      failed += !accepted;
+      via += accepted && !bare;
+      differ += gr[j] != wr[j];
+      off += wr[j] != r64b;
+    }
+    c[0] = n; c[1] = failed; c[2] = via; c[3] = differ; c[4] = off;
+  }
+}
+
+ORC_API void orc_check_layernorm_bf16(const uint16_t* got, const uint16_t* want, const uint16_t* x, const uint16_t* gamma,
+                                      const uint16_t* beta, uint32_t rows, uint32_t cols, double eps, uint64_t* counts) {
+  const orc_check_ln_ctx ctx = {got, want, x, gamma, beta, cols, eps, counts};
+  parallel_rows((int64_t)rows, orc_check_layernorm_bf16_body, &ctx);
+}
+
+typedef struct {
+  const float* got;
+  const float* want;
+  const float* x;
+  uint32_t cols;
+  uint64_t* counts;
+} orc_check_sm_ctx;
+
+static void orc_check_softmax_body(const void* p, int64_t lo, int64_t hi) {
+  const orc_check_sm_ctx* q = (const orc_check_sm_ctx*)p;
+  const uint32_t n = q->cols;
+  for (int64_t r = lo; r < hi; ++r) {
+    const float* xr = q->x + (size_t)r * n;
+    const float* gr = q->got + (size_t)r * n;
+    const float* wr = q->want + (size_t)r * n;
+    uint64_t* c = q->counts + (size_t)r * 5;
+    double m = -INFINITY, s = 0.0;
+    for (uint32_t j = 0; j < n; ++j) m = (double)xr[j] > m ? (double)xr[j] : m;
+    for (uint32_t j = 0; j < n; ++j) s += exp((double)xr[j] - m);
+    uint64_t failed = 0, via = 0;
+    for (uint32_t j = 0; j < n; ++j) {
+      const double f64 = exp((double)xr[j] - m) / s;
+      const double got = (double)gr[j], want = (double)wr[j];
+      const double d_o = fabs(got - want);
+      const int bare = d_o <= 1e-5 * fabs(want) + 1e-37;
+      const int accepted = (fabs(got - f64) <= 1e-5 * fabs(f64) + 1e-37) && (d_o <= 1e-5 * fabs(want) + fabs(want - f64) + 1e-37);
+      failed += !accepted;
+      via += accepted && !bare;
+    }
+    c[0] = n; c[1] = failed; c[2] = via; c[3] = 0; c[4] = 0;
+  }
+}
+
+ORC_API void orc_check_softmax(const float* got, const float* want, const float* x, uint32_t rows, uint32_t cols,
+                               uint64_t* counts) {
+  const orc_check_sm_ctx ctx = {got, want, x, cols, counts};
+  parallel_rows((int64_t)rows, orc_check_softmax_body, &ctx);
+}

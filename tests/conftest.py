@@ -35,3 +35,22 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.fail("a test marked gpu ran without a CUDA device")
     return torch.device("cuda:0")
+
+
+# Parity counts of the full-size configuration checks: how many elements were compared with the oracle and how
+# many of them were accepted only through the oracle's own distance to the fp64 value (oracle/checks.py).
+# Printed after the run so that the effect of the two-sided criterion is visible in every log.
+PARITY_COUNTS = {}
+
+
+@pytest.fixture(scope="session")
+def parity_counts():
+    return PARITY_COUNTS
+
+
+def pytest_terminal_summary(terminalreporter):
+    if PARITY_COUNTS:
+        terminalreporter.write_line("parity counts (elements compared with the oracle / accepted only through the "
+                                    "oracle-to-fp64 term):")
+        for name, rep in PARITY_COUNTS.items():
+            terminalreporter.write_line(f"  {name}: {rep}")
