@@ -44,6 +44,7 @@ extern "C" {
 #define TCAB_MAX_RANK 4
 #define TCAB_MAX_INPUTS 4
 #define TCAB_MAX_CAPTURES 8
+#define TCAB_PIPELINE_MAX_OUTPUTS 3
 #define TCAB_NOALLOC_MAX_ROWS 4096 /* rows tcab_chain_reduce_noalloc accepts (its fixed scratch array) */
 
 /* Status codes. 0 is success; everything else leaves a message for tcab_last_error(). */
@@ -62,7 +63,8 @@ typedef enum tcab_status {
 typedef enum tcab_dtype {
   TCAB_F32 = 0,
   TCAB_BF16 = 1,
-  TCAB_I32 = 2
+  TCAB_I32 = 2,
+  TCAB_U32 = 3
 } tcab_dtype;
 
 /* Non-owning tensor view: the C spelling of tca::Tensor<T,R> (runtime/tca/tensor.h:16-40).
@@ -76,14 +78,23 @@ typedef struct tcab_tensor {
 
 /* A map | reduce | map chain, as the builder's rungs describe it
  * (pkg/chain.go:360-559: Iter -> Map -> As -> Reduce -> [Map -> As] -> Store).
- * Lambdas travel as fully parenthesised C expressions in the reference's own
- * operator and builtin vocabulary (internal/cg/cxx/naming.go:126-198):
- *   map_expr      over p0..p{n-1}, the operand values at the current point,
- *                 and c0..c{m-1}, the scalar captures;            e.g. "(p0 * p1)"
+ * Lambdas travel as C expressions in the reference's own operator and builtin vocabulary
+ * (internal/cg/cxx/naming.go:126-198), typed the way the reference's builder types them
+ * (pkg/expr.go:137-176, 185-203, 271):
+ *   map_expr      over p0..p{n-1}, the operand values at the current point, each with its tensor's element
+ *                 type, and c0..c{m-1}, the f32 scalar captures;   e.g. "(p0 * p1)"
  *   combine_expr  over p0 = accumulator, p1 = mapped value;        "(p0 + p1)", "fmaxf(p0, p1)", "fminf(p0, p1)"
  *   post_expr     piped map over p0 = the reduced value and c*; NULL when the chain stores the reduction as it is
- * `init` is the reduction's initial value (an empty reduction returns it,
- * design/tca.md:299). All arithmetic is fp32 (design/syntax-design.md:601-607). */
+ * Vocabulary: + - * / and unary - + on one arithmetic type (f32, i32, u32); % & | ^ << >> ~ on one integer
+ * type; == != < <= > >= on one type, giving bool; && || ! on bool; cond ? a : b with two branches of one type;
+ * static_cast<T>(x) with T one of float, __nv_bfloat16, int32_t, uint32_t (also spelled f32(x), bf16(x), i32(x),
+ * u32(x)) between arithmetic types -- conversions are never implicit (internal/ir/types.go:60-62); the f32
+ * builtins expf logf sqrtf rsqrtf fabsf tanhf sinf cosf fminf fmaxf fmaf and the u32 pair umin umax
+ * (internal/ir/builtins.go:25-39). Literals: 1.5f / 1.5 / 2e-3 are f32, 3 is i32, 3u is u32, true / false bool.
+ * bf16 is a storage type (design/syntax-design.md:601-607): a bf16 operand is converted before any arithmetic.
+ * Converting a floating value that the integer type cannot hold is undefined, as in C++.
+ * `init` is the reduction's initial value (an empty reduction returns it, design/tca.md:299). Reductions fold
+ * f32 values: the map lambda of a reduce or contract chain must yield f32. */
 typedef struct tcab_chain {
   const char* map_expr;
   const char* combine_expr;
@@ -114,8 +125,9 @@ TCAB_API uint64_t tcab_launch_count(void);
  * (internal/cg/cxx/testdata/reduce_warp.cu:12-73), split-K warp reduce
  * (testdata/reduce_splitk.cu:13-91), amortised brackets (testdata/bracket_amort.cu:7-90),
  * i.e. SeqReducer / WarpReducer brackets (runtime/tca/reducer.h:36-181).
- * All operands: fp32, same rank (1..4) and extents. `out` is fp32 with the operands' extents
- * minus the reduced axis (a rank-1 operand gives a rank-1 output of extent 1).
+ * All operands: same rank (1..4) and extents, each f32, bf16, i32 or u32 (the map lambda sees each with its
+ * own type and must yield f32). `out` is fp32 with the operands' extents minus the reduced axis (a rank-1
+ * operand gives a rank-1 output of extent 1).
  * reduce_axis == rank-1 selects the innermost-axis kernel, any other axis the outer-axis kernel.
  * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative.
  * Allocation: when there are fewer rows than SMs and the rows are long, a row is split over several
@@ -152,9 +164,10 @@ TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, 
 TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                                        const tcab_tensor* out, void* stream);
 
-/* Compiles and loads, now, the kernels that the first tcab_chain_reduce (use = TCAB_USE_REDUCE) or
- * tcab_chain_contract (use = TCAB_USE_CONTRACT, n_ins = 2) with these lambdas would otherwise compile on its
- * first call. The reference compiles every kernel ahead of time from its lambdas
+/* Compiles and loads, now, the kernels that the first tcab_chain_reduce (use = TCAB_USE_REDUCE),
+ * tcab_chain_contract (use = TCAB_USE_CONTRACT, n_ins = 2) or tcab_map (use = TCAB_USE_MAP) with these lambdas
+ * and operand element types (in_dtypes: n_ins tcab_dtype values, NULL = all f32; out_dtype: the stored type of
+ * a map, ignored otherwise) would otherwise compile on its first call. The reference compiles every kernel ahead of time from its lambdas
  * (internal/cg/cxx/emit.go:85-190 prints the translation unit, the user runs nvcc); this is the same step
  * for a lambda that this library has no ahead-of-time kernel for. It takes hundreds of milliseconds, loads a
  * code image onto the current device (an implicit device allocation) and must not run during a stream
@@ -162,17 +175,33 @@ TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tenso
  * matter; `init` and the capture values may differ in later calls. */
 #define TCAB_USE_REDUCE 0
 #define TCAB_USE_CONTRACT 1
-TCAB_API int tcab_chain_prepare(const tcab_chain* chain, uint32_t n_ins, int use);
+#define TCAB_USE_MAP 2
+TCAB_API int tcab_chain_prepare(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use,
+                                int out_dtype);
 
-/* Contraction chain over fp32 operands indexed by different dim subsets:
+/* Map-only chain with a rank-preserving store: out[i...] = map_expr(ins[0][i...], ins[1][i...], ...).
+ * The fused elementwise map of the path. The reference's rungs cannot store a map that no reduction
+ * follows (pkg/chain.go:433-438 admits Store only after a Reduce), so, like the softmax and layer-norm
+ * chains, it is offered as an entry point of its own; what it replaces in the emitted code is the per-element
+ * TensorView::Get / Set pair (runtime/tca/view.h:104-112) of a map statement.
+ * ins: 1..TCAB_MAX_INPUTS tensors of the shape of `out`, each f32, bf16, i32 or u32; the lambda sees every
+ * operand with its own element type and must yield exactly the element type of `out` (no implicit conversion).
+ * Only chain->map_expr, n_captures and captures are read. Every element is computed once, in IEEE fp32
+ * arithmetic per operation with CUDA's math functions (expf ... fmaf: at most 2 ulp from the exact value). */
+TCAB_API int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, const tcab_tensor* out,
+                      void* stream);
+
+/* Contraction chain over operands indexed by different dim subsets:
  *   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )   rhs_is_nk == 0, rhs is [K,N]
  *   out[m,n] = post( fold_k map(lhs[m,k], rhs[n,k]) )   rhs_is_nk != 0, rhs is [N,K]
  * with the lambdas of tcab_chain (map over p0 = the lhs value, p1 = the rhs value). Replaces the emitted
  * matmul-shaped kernels of the reference's suite (testing/kernels/llm/gemm.tca, llm/qk_score.tca,
  * tiling/mm_small.tca, mm_mid.tca, mm_splitk.tca, fusion/mlp.tca; launcher form
  * internal/cg/cxx/launch.go:23-156). Each output is folded over k in ascending order, the order of the
- * reference's CPU loops (testing/runners/gemm.cu:44-56). SIMT fp32: the tensor-core path is
- * tcab_gemm_bias_act, which takes bf16 operands. */
+ * reference's CPU loops (testing/runners/gemm.cu:44-56). lhs and rhs are f32, bf16, i32 or u32 (a bf16
+ * operand is widened at the load; the lambda converts it explicitly, e.g. "f32(p0) * f32(p1)", the spelling of
+ * testing/kernels/llm/qk_score.tca with bf16 storage); out is f32. SIMT fp32 arithmetic, any lambda: the
+ * tensor-core path for the plain bf16 product is tcab_gemm_bias_act. */
 TCAB_API int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs,
                                  int rhs_is_nk, const tcab_tensor* out, void* stream);
 
@@ -207,6 +236,91 @@ TCAB_API int tcab_layernorm_rows(const tcab_tensor* x, const tcab_tensor* gamma,
  * Requires K % 8 == 0, N % 8 == 0 and 16-byte aligned base pointers (TMA tensor maps). */
 TCAB_API int tcab_gemm_bias_act(const tcab_tensor* a, const tcab_tensor* b, const tcab_tensor* bias,
                        int act, const tcab_tensor* c, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Host buffers: upload, kernel and download pipelined over chunks of the independent axis.
+ *
+ * The entry points above take device tensors and leave the copies to the caller, like the reference's
+ * launchers; the reference's own runners copy whole tensors around the launch
+ * (testing/runners/common.cuh:72-90: cudaMemcpy in, launch, synchronise, cudaMemcpy out), which serialises the
+ * two PCIe directions around the kernel. Every operator class here has an axis along which outputs are
+ * independent -- rows (softmax, layer-norm, chain_reduce over the innermost axis, map), the batch of
+ * reduce_outer, the rows of a in the contraction -- so a problem in host memory is cut into chunks of that
+ * axis: chunk i+1 uploads while chunk i computes and chunk i-1 downloads, on three streams that the pipeline
+ * owns. A "unit" is one index of the independent axis; the streamed operands hold `units` of them.
+ *
+ * A pipeline owns: three non-blocking streams, `depth` staging slots in device memory (each chunk_units units
+ * of every streamed operand and every output), three events per slot. tcab_pipeline_create allocates them
+ * (cudaMalloc), tcab_pipeline_destroy frees them after waiting for the pipeline's work. Host buffers should be
+ * page-locked (tcab_host_alloc, cudaHostAlloc / cudaHostRegister, or torch's pin_memory): with pageable memory
+ * the copies are staged by the driver and do not overlap. A pipeline may be used from one host thread at a
+ * time. There is no CPU fallback: without a device tcab_pipeline_create returns TCAB_ERR_CUDA.
+ * --------------------------------------------------------------------------------------------------- */
+typedef enum tcab_op {
+  TCAB_OP_SOFTMAX_ROWS = 0,   /* unit: a row [cols] f32                -> y row, resident: none             */
+  TCAB_OP_LAYERNORM_ROWS = 1, /* unit: a row [cols] f32 / bf16         -> y row, resident: gamma, beta; eps */
+  TCAB_OP_REDUCE_OUTER = 2,   /* unit: one batch [k, c] f32            -> sum, max, argmax [c] (by `outputs`) */
+  TCAB_OP_CHAIN_REDUCE = 3,   /* unit: a row [cols] f32 of each of n_streamed operands -> one f32; chain     */
+  TCAB_OP_GEMM_BIAS_ACT = 4,  /* unit: a row of a [K] bf16             -> row of c [N] bf16, resident: b [K,N], bias [N] or none; act */
+  TCAB_OP_MAP = 5             /* unit: any shape, n_streamed operands of in_dtype -> same shape, out_dtype; chain */
+} tcab_op;
+
+typedef struct tcab_pipeline_desc {
+  int32_t op;            /* tcab_op */
+  int32_t device;        /* CUDA ordinal the pipeline runs on; -1 = the device current at create */
+  uint32_t chunk_units;  /* units per chunk (the last chunk of a run may be shorter) */
+  uint32_t depth;        /* staging slots, 2..8; 0 = 4 */
+  int32_t in_dtype;      /* tcab_dtype of the streamed operand(s) */
+  uint32_t n_streamed;   /* streamed operands: 1, or 1..TCAB_MAX_INPUTS for CHAIN_REDUCE and MAP */
+  uint32_t unit_rank;    /* rank of one unit, 1..TCAB_MAX_RANK-1 */
+  uint32_t unit_dims[TCAB_MAX_RANK - 1];
+  uint32_t outputs;      /* REDUCE_OUTER: bit 0 sum, bit 1 max, bit 2 argmax; host_outs lists the chosen ones in that order */
+  int32_t out_dtype;     /* MAP: tcab_dtype of the result */
+  int32_t act;           /* GEMM_BIAS_ACT: tcab_act */
+  float eps;             /* LAYERNORM_ROWS */
+  const tcab_chain* chain; /* CHAIN_REDUCE, MAP: the lambdas (copied at create) */
+  tcab_tensor resident[2]; /* operands that stay in device memory (on `device`): gamma, beta | b, bias (data NULL = none) */
+} tcab_pipeline_desc;
+
+typedef struct tcab_pipeline tcab_pipeline;
+
+TCAB_API int tcab_pipeline_create(const tcab_pipeline_desc* desc, tcab_pipeline** out);
+/* Number of host output buffers a run takes (1, or the number of bits set in `outputs`). */
+TCAB_API uint32_t tcab_pipeline_outputs(const tcab_pipeline* p);
+/* Queues `units` units: host_ins[i] holds units * (unit elements) of streamed operand i, host_outs[j] receives the
+ * j-th output. Returns once everything is queued (with page-locked buffers nothing waits on the host); runs may
+ * follow each other without a join in between -- the first uploads of the next run then overlap the last
+ * downloads of this one. The buffers must stay valid until tcab_pipeline_sync or a stream joined after the run
+ * has passed. */
+TCAB_API int tcab_pipeline_run(tcab_pipeline* p, const void* const* host_ins, uint64_t units, void* const* host_outs);
+/* Work queued on the pipeline after this call starts only once everything queued on `stream` so far is done. */
+TCAB_API int tcab_pipeline_order_after(tcab_pipeline* p, void* stream);
+/* `stream` waits (on the device, not the host) for everything queued on the pipeline so far. */
+TCAB_API int tcab_pipeline_join(tcab_pipeline* p, void* stream);
+/* The calling host thread waits for everything queued on the pipeline so far. */
+TCAB_API int tcab_pipeline_sync(tcab_pipeline* p);
+TCAB_API int tcab_pipeline_destroy(tcab_pipeline* p);
+
+/* One problem in host memory cut over several devices of this process: device r of n takes the contiguous
+ * block tcab_shard_block(units, n, r) of the independent axis through a pipeline of its own (descs[r], whose
+ * `device` fields must name distinct devices and whose resident operands live on that device: gamma / beta or
+ * b / bias are replicated by the caller beforehand). No device exchanges anything with another: the path has no
+ * data-path collective. The reference has no multi-device support (internal/cg/cxx/loops.go:11-22 spreads loop
+ * dims over CTAs and warps of one GPU only). Chunks are queued round-robin over the devices. */
+typedef struct tcab_multi tcab_multi;
+TCAB_API int tcab_multi_create(const tcab_pipeline_desc* descs, uint32_t n_devices, tcab_multi** out);
+TCAB_API int tcab_multi_run(tcab_multi* m, const void* const* host_ins, uint64_t units, void* const* host_outs);
+TCAB_API int tcab_multi_sync(tcab_multi* m);
+TCAB_API int tcab_multi_destroy(tcab_multi* m);
+
+/* The partition rule: [*lo, *hi) is the contiguous block rank `rank` of `world` owns out of n units. Blocks
+ * differ by at most one unit, the first n % world ranks get the larger ones, every unit belongs to one rank. */
+TCAB_API int tcab_shard_block(uint64_t n, uint32_t world, uint32_t rank, uint64_t* lo, uint64_t* hi);
+
+/* Page-locked host memory usable from every device (cudaHostAlloc with the portable flag), for hosts that
+ * cannot call the CUDA runtime themselves (a cgo host). */
+TCAB_API int tcab_host_alloc(uint64_t bytes, void** out);
+TCAB_API int tcab_host_free(void* p);
 
 /* Scratch memory the library allocated for launches on `stream` of the current device (the multi-CTA
  * partials of tcab_chain_reduce: 1 MiB; of tcab_reduce_outer: 3 MiB; the K-range workspace of

@@ -45,6 +45,12 @@ TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 TCAB_API int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident_ctas, int sms,
                                    int forced, uint32_t* ranges, uint32_t* klen);
 
+/* Validates a chain exactly as tcab_chain_prepare does and runs the run-time compiler on it for sm_100a, but
+ * loads nothing: works on a host without a GPU (needs libnvrtc). A chain that has an ahead-of-time kernel is
+ * compiled all the same. Arguments as tcab_chain_prepare. */
+TCAB_API int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use,
+                                int out_dtype);
+
 #ifdef __cplusplus
 }
 #endif

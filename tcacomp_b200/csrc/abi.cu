@@ -187,6 +187,13 @@ int need_elem_align(const char* op, const char* name, const tcab_tensor* t, unsi
   return TCAB_OK;
 }
 
+// Element types a lambda operand may have (the chain and map classes): 4-byte f32 / i32 / u32, 2-byte bf16.
+int need_operand_dtype(const char* op, const char* name, const tcab_tensor* t) {
+  if (t->dtype != TCAB_F32 && t->dtype != TCAB_BF16 && t->dtype != TCAB_I32 && t->dtype != TCAB_U32)
+    return fail(TCAB_ERR_DTYPE, "%s: tensor '%s' must be f32, bf16, i32 or u32", op, name);
+  return need_elem_align(op, name, t, t->dtype == TCAB_BF16 ? 2 : 4);
+}
+
 int have_device(const char* op) {
   if (current_device() < 0) return fail(TCAB_ERR_CUDA, "%s: no CUDA device (this library has no CPU path)", op);
   return TCAB_OK;
@@ -246,22 +253,49 @@ int tcab_release_all(void) {
   return TCAB_OK;
 }
 
-int tcab_chain_prepare(const tcab_chain* chain, uint32_t n_ins, int use) {
+namespace {
+int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype,
+                   PreparedChain* pc);
+}
+
+int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype) {
+  PreparedChain pc;
+  TCAB_TRY(prepare_common("compile_check", chain, in_dtypes, n_ins, use, out_dtype, &pc));
+  JitSpec sp = pc.spec;
+  return jit_compile_check(sp);
+}
+
+int tcab_chain_prepare(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype) {
   const char* op = "chain_prepare";
+  PreparedChain pc;
+  TCAB_TRY(prepare_common(op, chain, in_dtypes, n_ins, use, out_dtype, &pc));
+  TCAB_TRY(have_device(op));
+  return warm_chain(pc);
+}
+
+namespace {
+int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype,
+                   PreparedChain* pcp) {
+  PreparedChain& pc = *pcp;
   if (chain == nullptr || chain->map_expr == nullptr)
     return fail(TCAB_ERR_INVALID_ARG, "%s: chain and map_expr are required", op);
-  if (use != TCAB_USE_REDUCE && use != TCAB_USE_CONTRACT)
+  if (use != TCAB_USE_REDUCE && use != TCAB_USE_CONTRACT && use != TCAB_USE_MAP)
     return fail(TCAB_ERR_INVALID_ARG, "%s: unknown use %d", op, use);
-  if (chain->combine_expr == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: combine_expr is required", op);
+  if (use != TCAB_USE_MAP && chain->combine_expr == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: combine_expr is required", op);
   if (chain->n_captures > TCAB_MAX_CAPTURES)
     return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
   if (n_ins < 1 || n_ins > TCAB_MAX_INPUTS || (use == TCAB_USE_CONTRACT && n_ins != 2))
     return fail(TCAB_ERR_INVALID_ARG, "%s: bad operand count %u", op, n_ins);
-  PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
-  TCAB_TRY(have_device(op));
-  return warm_chain(pc, use == TCAB_USE_CONTRACT);
+  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  for (uint32_t i = 0; i < n_ins && in_dtypes != nullptr; ++i) {
+    if (in_dtypes[i] < TCAB_F32 || in_dtypes[i] > TCAB_U32) return fail(TCAB_ERR_DTYPE, "%s: in_dtypes[%u] is not a tcab_dtype", op, i);
+    types[i] = in_dtypes[i];
+  }
+  if (use == TCAB_USE_MAP && (out_dtype < TCAB_F32 || out_dtype > TCAB_U32)) return fail(TCAB_ERR_DTYPE, "%s: out_dtype is not a tcab_dtype", op);
+  return prepare_chain(chain, n_ins, &pc, use == TCAB_USE_MAP ? 'M' : use == TCAB_USE_CONTRACT ? 'C' : 'R', types,
+                       use == TCAB_USE_MAP ? out_dtype : TCAB_F32);
 }
+}  // namespace
 
 int tcab_tune(const char* family, int p0, int p1, int p2, int p3) {
   static const char* names[kFamilies] = {"softmax", "layernorm", "reduce_inner", "reduce_outer", "gemm"};
@@ -371,15 +405,16 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
     return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
   const float* ptrs[TCAB_MAX_INPUTS] = {};
+  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];
     std::snprintf(name, sizeof(name), "ins[%u]", i);
     TCAB_TRY(check_tensor(op, name, &ins[i]));
-    TCAB_TRY(need_dtype(op, name, &ins[i], TCAB_F32, "f32"));
-    TCAB_TRY(need_elem_align(op, name, &ins[i], 4));
+    TCAB_TRY(need_operand_dtype(op, name, &ins[i]));
     if (i > 0 && !same_shape(&ins[0], &ins[i]))
       return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0]", op, name);
     ptrs[i] = static_cast<const float*>(ins[i].data);
+    types[i] = ins[i].dtype;
   }
   const tcab_tensor* t = &ins[0];
   if (reduce_axis >= t->rank) return fail(TCAB_ERR_INVALID_ARG, "%s: reduce_axis %u out of range", op, reduce_axis);
@@ -395,7 +430,7 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   for (uint32_t i = 0; ok && i < wr; ++i) ok = out->dims[i] == want[i];
   if (!ok) return fail(TCAB_ERR_SHAPE, "%s: out must have the operands' extents without axis %u", op, reduce_axis);
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types));
   TCAB_TRY(have_device(op));
   return launch_chain_reduce(pc, ptrs, count(t, 0, reduce_axis), t->dims[reduce_axis],
                              count(t, reduce_axis + 1, t->rank), static_cast<float*>(out->data),
@@ -412,15 +447,16 @@ int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, u
   if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
     return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
   const float* ptrs[TCAB_MAX_INPUTS] = {};
+  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];
     std::snprintf(name, sizeof(name), "ins[%u]", i);
     TCAB_TRY(check_tensor(op, name, &ins[i]));
-    TCAB_TRY(need_dtype(op, name, &ins[i], TCAB_F32, "f32"));
-    TCAB_TRY(need_elem_align(op, name, &ins[i], 4));
+    TCAB_TRY(need_operand_dtype(op, name, &ins[i]));
     if (i > 0 && !same_shape(&ins[0], &ins[i]))
       return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0]", op, name);
     ptrs[i] = static_cast<const float*>(ins[i].data);
+    types[i] = ins[i].dtype;
   }
   const tcab_tensor* t = &ins[0];
   TCAB_TRY(check_tensor(op, "out", out));
@@ -435,10 +471,36 @@ int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, u
                 "%s: %llu rows exceed TCAB_NOALLOC_MAX_ROWS = %d (the fixed scratch array); use tcab_chain_reduce",
                 op, static_cast<unsigned long long>(rows), TCAB_NOALLOC_MAX_ROWS);
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc));
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types));
   TCAB_TRY(have_device(op));
   return launch_chain_reduce_noalloc(pc, ptrs, rows, t->dims[t->rank - 1], static_cast<float*>(out->data),
                                      static_cast<cudaStream_t>(stream));
+}
+
+int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, const tcab_tensor* out, void* stream) {
+  const char* op = "map";
+  if (chain == nullptr || chain->map_expr == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: chain and map_expr are required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
+  TCAB_TRY(check_tensor(op, "out", out));
+  TCAB_TRY(need_operand_dtype(op, "out", out));
+  const void* ptrs[TCAB_MAX_INPUTS] = {};
+  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  for (uint32_t i = 0; i < n_ins; ++i) {
+    char name[16];
+    std::snprintf(name, sizeof(name), "ins[%u]", i);
+    TCAB_TRY(check_tensor(op, name, &ins[i]));
+    TCAB_TRY(need_operand_dtype(op, name, &ins[i]));
+    if (!same_shape(out, &ins[i])) return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of out", op, name);
+    ptrs[i] = ins[i].data;
+    types[i] = ins[i].dtype;
+  }
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'M', types, out->dtype));
+  TCAB_TRY(have_device(op));
+  return launch_chain_map(pc, ptrs, out->data, count(out, 0, out->rank), static_cast<cudaStream_t>(stream));
 }
 
 int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs, int rhs_is_nk,
@@ -451,8 +513,8 @@ int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const t
   TCAB_TRY(check_tensor(op, "lhs", lhs));
   TCAB_TRY(check_tensor(op, "rhs", rhs));
   TCAB_TRY(check_tensor(op, "out", out));
-  TCAB_TRY(need_dtype(op, "lhs", lhs, TCAB_F32, "f32"));
-  TCAB_TRY(need_dtype(op, "rhs", rhs, TCAB_F32, "f32"));
+  TCAB_TRY(need_operand_dtype(op, "lhs", lhs));
+  TCAB_TRY(need_operand_dtype(op, "rhs", rhs));
   TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
   if (lhs->rank != 2 || rhs->rank != 2 || out->rank != 2)
     return fail(TCAB_ERR_SHAPE, "%s: lhs, rhs and out must be rank 2", op);
@@ -460,11 +522,10 @@ int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const t
   const uint32_t rk = rhs_is_nk ? rhs->dims[1] : rhs->dims[0], n = rhs_is_nk ? rhs->dims[0] : rhs->dims[1];
   if (rk != k) return fail(TCAB_ERR_SHAPE, "%s: rhs.Dim(%d) must equal lhs.Dim(1) (dim k)", op, rhs_is_nk ? 1 : 0);
   if (out->dims[0] != m || out->dims[1] != n) return fail(TCAB_ERR_SHAPE, "%s: out must be [%u, %u]", op, m, n);
-  TCAB_TRY(need_elem_align(op, "lhs", lhs, 4));
-  TCAB_TRY(need_elem_align(op, "rhs", rhs, 4));
   TCAB_TRY(need_elem_align(op, "out", out, 4));
+  const int types[2] = {lhs->dtype, rhs->dtype};
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, 2, &pc));
+  TCAB_TRY(prepare_chain(chain, 2, &pc, 'C', types));
   TCAB_TRY(have_device(op));
   return launch_chain_contract(pc, static_cast<const float*>(lhs->data), static_cast<const float*>(rhs->data),
                                rhs_is_nk ? 1 : 0, static_cast<float*>(out->data), m, n, k,

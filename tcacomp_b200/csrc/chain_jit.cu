@@ -70,65 +70,88 @@ const Nvrtc& nvrtc() {
 // The kernels one chain needs, in the order of JitChain::k.
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
-  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kSlots
+  kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
+  kSlots
 };
 
 struct JitChain {
   cudaLibrary_t lib = nullptr;
   cudaKernel_t k[kSlots] = {};
   int n_in = 0;
+  char kind = 'R';
 };
 
 std::mutex g_mu;
 std::map<std::string, JitChain*> g_cache;   // key: R or C | n_in | combine | map text | post text
 std::map<std::string, std::string> g_failed;  // key -> compiler message (do not recompile a failing lambda)
 
-std::string functor(const char* name, const std::string& expr, int n_in) {
+// A lambda as a functor over the kernels' 32-bit operand registers (see chain_kernels.cuh): the prologue gives
+// every operand its declared type back, the body is the canonical text, and the value returns as an f32
+// register again (an integer as its bit pattern, a bf16 widened exactly).
+std::string functor(const char* name, const std::string& expr, int n_in, const int* in_types, int result_type) {
   std::string s = "struct ";
   s += name;
   s += " {\n  static __device__ __forceinline__ float apply(const float* p, const float* c) {\n";
-  for (int i = 0; i < 4; ++i)
-    s += "    const float p" + std::to_string(i) + " = p[" + std::to_string(i < n_in ? i : 0) + "];\n";
+  for (int i = 0; i < n_in; ++i) {
+    const std::string pi = "p" + std::to_string(i), src = "p[" + std::to_string(i) + "]";
+    switch (in_types ? in_types[i] : TCAB_F32) {
+      case TCAB_BF16: s += "    const __nv_bfloat16 " + pi + " = __nv_bfloat16(" + src + ");\n"; break;
+      case TCAB_I32: s += "    const int32_t " + pi + " = __float_as_int(" + src + ");\n"; break;
+      case TCAB_U32: s += "    const uint32_t " + pi + " = __float_as_uint(" + src + ");\n"; break;
+      default: s += "    const float " + pi + " = " + src + ";\n"; break;
+    }
+    s += "    (void)" + pi + ";\n";
+  }
   for (int i = 0; i < 8; ++i) s += "    const float c" + std::to_string(i) + " = c[" + std::to_string(i) + "];\n";
-  s += "    (void)p0; (void)p1; (void)p2; (void)p3;\n";
   s += "    (void)c0; (void)c1; (void)c2; (void)c3; (void)c4; (void)c5; (void)c6; (void)c7;\n";
-  s += "    return " + expr + ";\n  }\n};\n";
+  switch (result_type) {
+    case TCAB_BF16: s += "    return static_cast<float>(" + expr + ");\n"; break;
+    case TCAB_I32: s += "    return __int_as_float(" + expr + ");\n"; break;
+    case TCAB_U32: s += "    return __uint_as_float(" + expr + ");\n"; break;
+    default: s += "    return " + expr + ";\n"; break;
+  }
+  s += "  }\n};\n";
   return s;
 }
 
-// One program per chain and use: the reduction kernels (13 instances) or the contraction kernels (4),
-// never both -- a chain is launched through one entry point, and the unrolled contraction tiles are
-// the slowest instances to compile.
-int compile(const std::string& key, const std::string& map_text, const std::string& post_text, int combine, int n_in,
-            bool contraction, JitChain** out) {
+// One program per chain and use: the reduction kernels (13 instances), the contraction kernels (4) or the
+// map-only kernels (2), never more than one group -- a chain is launched through one entry point, and the
+// unrolled contraction tiles are the slowest instances to compile.
+int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load = true) {
+  const std::string &map_text = sp.map_text, &post_text = sp.post_text;
   const Nvrtc& nv = nvrtc();
   if (!nv.ok)
     return fail(TCAB_ERR_UNSUPPORTED,
-                "chain_reduce: no kernel in this build for map '%s' post '%s', and libnvrtc is not available to "
+                "chain: no kernel in this build for map '%s' post '%s', and libnvrtc is not available to "
                 "compile one", map_text.c_str(), post_text.c_str());
   std::string src = kKernelText;
-  src += "\nnamespace tcabj {\n";
-  src += functor("Map", map_text, n_in);
-  src += post_text.empty() ? "typedef tcabk::PostNone Post;\n" : functor("Post", post_text, 1);
+  // the element types' C++ spellings as the reference emits them (internal/cg/cxx/naming.go:21-46)
+  src += "\nnamespace tcabj {\ntypedef tcabk::bf16 __nv_bfloat16;\ntypedef int int32_t;\ntypedef unsigned int uint32_t;\n";
+  src += functor("Map", map_text, sp.n_in, sp.in_types, sp.kind == 'M' ? sp.out_type : TCAB_F32);
+  src += post_text.empty() ? "typedef tcabk::PostNone Post;\n" : functor("Post", post_text, 1, nullptr, TCAB_F32);
   src += "}\n";
-  const std::string n = std::to_string(n_in), c = std::to_string(combine);
+  const std::string n = std::to_string(sp.n_in), c = std::to_string(sp.combine), bf = std::to_string(sp.bf_mask());
   std::vector<std::string> names(kSlots);
-  if (!contraction) {
+  if (sp.kind == 'R') {
     const int tprs[4] = {1, 4, 32, 256};
     for (int v = 0; v < 2; ++v)
       for (int t = 0; t < 4; ++t)
         names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
-                                                      std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ">";
-    names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4>";
-    names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1>";
+                                                      std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ">";
+    names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4, " + bf + ">";
+    names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1, " + bf + ">";
     names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
-    names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4>";
-    names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4>";
+    names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
+    names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + ">";
+  } else if (sp.kind == 'C') {
+    names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 4, " + bf + ">";
+    names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 4, " + bf + ">";
+    names[kContractKN8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 8, " + bf + ">";
+    names[kContractNK8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 8, " + bf + ">";
   } else {
-    names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 4>";
-    names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 4>";
-    names[kContractKN8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 8>";
-    names[kContractNK8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 8>";
+    const std::string ob = sp.out_type == TCAB_BF16 ? "true" : "false";
+    names[kMap8] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 8>";
+    names[kMap1] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 1>";
   }
 
   nvrtcProgram prog = nullptr;
@@ -144,16 +167,21 @@ int compile(const std::string& key, const std::string& map_text, const std::stri
     std::string log(ls, '\0');
     if (ls) nv.log(prog, &log[0]);
     nv.destroy(&prog);
-    g_failed[key] = log.substr(0, 300);
+    if (load) g_failed[key] = log.substr(0, 300);
     return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: run-time compilation of map '%s' post '%s' failed: %s",
                 map_text.c_str(), post_text.c_str(), log.substr(0, 300).c_str());
+  }
+  if (!load) {  // a compile check on a host without a device: the image is not loaded
+    nv.destroy(&prog);
+    return TCAB_OK;
   }
   size_t cs = 0;
   nv.cubin_size(prog, &cs);
   std::vector<char> cubin(cs);
   nv.cubin(prog, cubin.data());
   auto* jc = new JitChain();
-  jc->n_in = n_in;
+  jc->n_in = sp.n_in;
+  jc->kind = sp.kind;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
   for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
     if (names[i].empty()) continue;
@@ -191,10 +219,12 @@ int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStrea
 
 bool jit_available() { return nvrtc().ok; }
 
-int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
-                void** handle, bool compile_if_missing) {
-  const std::string key = std::string(contraction ? "C|" : "R|") + std::to_string(n_in) + "|" + std::to_string(combine) + "|" +
-                          map_text + "|" + post_text;
+int jit_prepare(const JitSpec& sp, void** handle, bool compile_if_missing) {
+  const std::string& map_text = sp.map_text;
+  std::string key(1, sp.kind);
+  key += "|" + std::to_string(sp.n_in) + "|" + std::to_string(sp.combine) + "|";
+  for (int i = 0; i < sp.n_in; ++i) key += std::to_string(sp.in_types[i]);
+  key += ">" + std::to_string(sp.kind == 'M' ? sp.out_type : TCAB_F32) + "|" + sp.map_text + "|" + sp.post_text;
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_cache.find(key);
   if (it != g_cache.end()) {
@@ -207,11 +237,17 @@ int jit_prepare(const std::string& map_text, const std::string& post_text, int c
                 map_text.c_str(), f->second.c_str());
   if (!compile_if_missing) return fail(TCAB_ERR_UNSUPPORTED, "chain: lambda '%s' is not compiled yet", map_text.c_str());
   JitChain* jc = nullptr;
-  const int rc = compile(key, map_text, post_text, combine, n_in, contraction, &jc);
+  const int rc = compile(key, sp, &jc);
   if (rc != TCAB_OK) return rc;
   g_cache[key] = jc;
   *handle = jc;
   return TCAB_OK;
+}
+
+int jit_compile_check(const JitSpec& sp) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  JitChain* none = nullptr;
+  return compile("check", sp, &none, false);
 }
 
 // Mirrors the ahead-of-time dispatch of chain_reduce.cu (launch_chain / launch_split / launch_outer).
@@ -271,10 +307,23 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   return launch(jc->k[kFinish], (rows32 + 127) / 128, 128, a2, s, "chain_split_finish");
 }
 
+int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, const float* caps16, cudaStream_t s) {
+  JitChain* jc = static_cast<JitChain*>(handle);
+  if (jc->kind != 'M') return fail(TCAB_ERR_INVALID_ARG, "map: the chain was prepared for another use");
+  tcabk::Caps caps;
+  for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
+  const void* ptrs[4] = {ins[0], jc->n_in > 1 ? ins[1] : ins[0], jc->n_in > 2 ? ins[2] : ins[0], jc->n_in > 3 ? ins[3] : ins[0]};
+  bool al = aligned16(out);
+  for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
+  void* a[] = {ptrs, &out, &n, &caps};
+  if (al) return launch(jc->k[kMap8], (n / 8 + 1 + 255) / 256, 256, a, s, "chain_map");
+  return launch(jc->k[kMap1], (n + 255) / 256, 256, a, s, "chain_map");
+}
+
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
                         uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s) {
   JitChain* jc = static_cast<JitChain*>(handle);
-  if (jc->n_in != 2 || jc->k[kContractKN] == nullptr)  // a handle prepared for reductions has no contraction kernels
+  if (jc->n_in != 2 || jc->kind != 'C')  // a handle prepared for reductions has no contraction kernels
     return fail(TCAB_ERR_INVALID_ARG, "chain_contract: the map lambda must take exactly two operands");
   tcabk::Caps caps;
   for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];

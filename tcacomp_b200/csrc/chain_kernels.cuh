@@ -17,6 +17,11 @@
 //   struct Map  { static __device__ float apply(const float* p, const float* c); }  p[i] = operand i
 //   struct Post { static __device__ float apply(const float* p, const float* c); }  p[0] = reduced value
 // COMBINE: 0 = p0 + p1, 1 = fmaxf(p0, p1), 2 = fminf(p0, p1).
+// Operands travel to the functor as 32-bit registers: an f32 operand as its value, an i32 / u32 operand as
+// its bit pattern, a bf16 operand widened to f32 at the load (exact). The functor's prologue gives each p#
+// its declared type back (the run-time compiler prints that prologue from the operands' element types), and
+// a map-only functor returns its result the same way. BF is the bit mask of the operands that are bf16 in
+// memory: those are read with 8-byte (four elements) or 2-byte loads.
 #pragma once
 
 namespace tcabk {
@@ -72,6 +77,65 @@ struct Ld<1> {
   }
 };
 
+// bf16 in memory: the top half of an f32 (widening is exact). Kept free of cuda_bf16.h so that this text also
+// compiles at run time without any include path.
+__device__ __forceinline__ float bf16_bits_to_float(unsigned int h) { return __uint_as_float(h << 16); }
+__device__ __forceinline__ unsigned int float_to_bf16_bits(float f) {  // round to nearest even, quiet NaN kept
+  const unsigned int u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x0040u;
+  return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+struct bf16 {  // the value type a bf16 operand has inside a lambda: convertible, not arithmetic
+  unsigned short bits;
+  __device__ __forceinline__ bf16() : bits(0) {}
+  __device__ __forceinline__ explicit bf16(float f) : bits(static_cast<unsigned short>(float_to_bf16_bits(f))) {}
+  __device__ __forceinline__ explicit operator float() const { return bf16_bits_to_float(bits); }
+  __device__ __forceinline__ explicit operator int() const { return static_cast<int>(bf16_bits_to_float(bits)); }
+  __device__ __forceinline__ explicit operator unsigned int() const { return static_cast<unsigned int>(bf16_bits_to_float(bits)); }
+};
+
+// Operand `a` of a kernel: element size by the BF mask. `index` counts vectors of V elements.
+template <int V, bool IS_BF16>
+struct LdT;
+template <>
+struct LdT<4, false> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) { Ld<4>::load(base, index, f); }
+};
+template <>
+struct LdT<1, false> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) { Ld<1>::load(base, index, f); }
+};
+template <>
+struct LdT<4, true> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) {
+    const uint2 q = __ldcs(reinterpret_cast<const uint2*>(base) + index);
+    f[0] = bf16_bits_to_float(q.x & 0xffffu); f[1] = bf16_bits_to_float(q.x >> 16);
+    f[2] = bf16_bits_to_float(q.y & 0xffffu); f[3] = bf16_bits_to_float(q.y >> 16);
+  }
+};
+template <>
+struct LdT<1, true> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) {
+    f[0] = bf16_bits_to_float(__ldcs(reinterpret_cast<const unsigned short*>(base) + index));
+  }
+};
+template <int V, int BF, int A>
+__device__ __forceinline__ void load_operand(const float* base, u64 index, float* f) {
+  LdT<V, ((BF >> A) & 1) != 0>::load(base, index, f);
+}
+// The NIN operands at one vector index (compile-time operand numbers select the element size).
+template <int V, int BF, int NIN, int A = 0>
+struct LoadAll {
+  static __device__ __forceinline__ void at(const float* const* p, u64 index, float (*f)[V]) {
+    load_operand<V, BF, A>(p[A], index, f[A]);
+    LoadAll<V, BF, NIN, A + 1>::at(p, index, f);
+  }
+};
+template <int V, int BF, int NIN>
+struct LoadAll<V, BF, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, float (*)[V]) {}
+};
+
 template <class C, int WIDTH>
 __device__ __forceinline__ float lanes_allreduce(float v) {
 #pragma unroll
@@ -84,7 +148,7 @@ __host__ __device__ constexpr int inner_cta_threads(int tpr) { return tpr > 128 
 // Reduce over the INNERMOST axis: operands are [rows, nk]; a group of TPR
 // threads folds one row. TPR == 1 is a plain sequential ascending fold per
 // thread (bit-identical to the reference's SeqReducer order).
-template <class Map, class Post, int COMBINE, int NIN, int TPR, int V>
+template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0>
 __global__ void __launch_bounds__(inner_cta_threads(TPR))
 chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
   typedef Comb<COMBINE> C;
@@ -110,7 +174,8 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
       const u32 bytes = nk * 4u < 65536u ? nk * 4u : 65536u;  // nk % 4 == 0 and 16-byte aligned rows on this path
 #pragma unroll
       for (int a = 0; a < NIN; ++a)
-        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ins.p[a] + first * nk), "r"(bytes) : "memory");
+        if (!((BF >> a) & 1))  // f32 / i32 / u32 rows; a bf16 row (8-byte granules) is left to the loads
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ins.p[a] + first * nk), "r"(bytes) : "memory");
     }
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -125,8 +190,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
 #pragma unroll 8
       for (u32 idx = t; idx < nvec; idx += TPR) {
         float f[NIN][V];
-#pragma unroll
-        for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a], vbase + idx, f[a]);
+        LoadAll<V, BF, NIN>::at(ins.p, vbase + idx, f);
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           float p[NIN];
@@ -158,7 +222,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
 // [s*vec_per_split, (s+1)*vec_per_split) of its row and writes ONE partial to
 // partials[row*splits + s] (global scratch memory). Pass 2 (chain_split_finish) folds the
 // partials of a row in ascending order, applies init and the piped map.
-template <class Map, int COMBINE, int NIN, int V>
+template <class Map, int COMBINE, int NIN, int V, int BF = 0>
 __global__ void __launch_bounds__(256)
 chain_inner_split(Ptrs<NIN> ins, float* __restrict__ partials, u32 nk, u32 splits, u32 vec_per_split, Caps caps) {
   typedef Comb<COMBINE> C;
@@ -173,8 +237,7 @@ chain_inner_split(Ptrs<NIN> ins, float* __restrict__ partials, u32 nk, u32 split
 #pragma unroll 4
     for (u32 idx = v0 + threadIdx.x; idx < v1; idx += 256) {
       float f[NIN][V];
-#pragma unroll
-      for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a], vbase + idx, f[a]);
+      LoadAll<V, BF, NIN>::at(ins.p, vbase + idx, f);
 #pragma unroll
       for (int j = 0; j < V; ++j) {
         float p[NIN];
@@ -211,7 +274,7 @@ chain_split_finish(const float* __restrict__ partials, float* __restrict__ out, 
 // With ksplit > 1 the k axis is also cut into ksplit ranges of klen, one CTA each (few columns, long k):
 // a CTA then writes the fold of its range -- without init and without the piped map -- to
 // partials[cell * ksplit + range], and chain_split_finish folds the ranges in ascending order.
-template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL>
+template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL, int BF = 0>
 __global__ void __launch_bounds__(32 * KW)
 chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, float init,
             Caps caps, u32 ksplit, u32 klen, float* __restrict__ partials) {
@@ -240,10 +303,8 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const u32 k = k0 + u * KW;
-          if (k < kend) {
-#pragma unroll
-            for (int a = 0; a < NIN; ++a) Ld<V>::load(ins.p[a] + base + static_cast<u64>(k) * nc, 0, f[u][a]);
-          }
+          if (k < kend)  // base and k * nc are multiples of V on the vector path
+            LoadAll<V, BF, NIN>::at(ins.p, (base + static_cast<u64>(k) * nc) / V, f[u]);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
@@ -301,21 +362,41 @@ struct ContractTile {
 };
 
 // A [rows, K] operand (k fastest): vector v of the thread covers row r = idx / 4, k = (idx % 4) * 4 .. +3.
-template <int TM>
+// Four consecutive elements at element offset `e` of an operand (fp32, or bf16 widened): one 16-byte
+// (8-byte) load when the caller has checked alignment and bounds, else up to `valid` single elements.
+template <bool IS_BF16>
+__device__ __forceinline__ void contract_load4(const float* __restrict__ p, u64 e, bool vec, int valid, float (&r)[4]) {
+  if constexpr (IS_BF16) {
+    const unsigned short* h = reinterpret_cast<const unsigned short*>(p) + e;
+    if (vec) {
+      const uint2 q = *reinterpret_cast<const uint2*>(h);
+      r[0] = bf16_bits_to_float(q.x & 0xffffu); r[1] = bf16_bits_to_float(q.x >> 16);
+      r[2] = bf16_bits_to_float(q.y & 0xffffu); r[3] = bf16_bits_to_float(q.y >> 16);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = j < valid ? bf16_bits_to_float(h[j]) : 0.0f;
+    }
+  } else {
+    const float* src = p + e;
+    if (vec) {
+      const float4 q = *reinterpret_cast<const float4*>(src);
+      r[0] = q.x; r[1] = q.y; r[2] = q.z; r[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = j < valid ? src[j] : 0.0f;
+    }
+  }
+}
+
+template <int TM, bool IS_BF16>
 __device__ __forceinline__ void contract_fetch_k_fastest(const float* __restrict__ p, u32 row0, u32 rows, u32 k0, u32 K,
                                                          bool vec_ok, float (&reg)[ContractTile<TM>::V][4]) {
 #pragma unroll
   for (int v = 0; v < ContractTile<TM>::V; ++v) {
     const int idx = threadIdx.x + v * 256;
     const u32 r = row0 + (idx >> 2), k = k0 + (idx & 3) * 4;
-    const float* src = p + static_cast<u64>(r) * K + k;
-    if (r < rows && vec_ok && k + 3 < K) {
-      const float4 q = *reinterpret_cast<const float4*>(src);
-      reg[v][0] = q.x; reg[v][1] = q.y; reg[v][2] = q.z; reg[v][3] = q.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) reg[v][j] = (r < rows && k + j < K) ? src[j] : 0.0f;
-    }
+    const int valid = r < rows && k < K ? static_cast<int>(K - k < 4u ? K - k : 4u) : 0;
+    contract_load4<IS_BF16>(p, static_cast<u64>(r) * K + k, vec_ok && valid == 4, valid, reg[v]);
   }
 }
 template <int TM>
@@ -330,7 +411,7 @@ __device__ __forceinline__ void contract_stash_k_fastest(float (*tile)[ContractT
   }
 }
 // B as [K, N] (n fastest): vector v covers k = idx / (BM / 4), n = (idx % (BM / 4)) * 4 .. +3.
-template <int TM>
+template <int TM, bool IS_BF16>
 __device__ __forceinline__ void contract_fetch_n_fastest(const float* __restrict__ p, u32 n0, u32 N, u32 k0, u32 K,
                                                          bool vec_ok, float (&reg)[ContractTile<TM>::V][4]) {
   constexpr int W = ContractTile<TM>::BM / 4;
@@ -338,14 +419,8 @@ __device__ __forceinline__ void contract_fetch_n_fastest(const float* __restrict
   for (int v = 0; v < ContractTile<TM>::V; ++v) {
     const int idx = threadIdx.x + v * 256;
     const u32 k = k0 + idx / W, n = n0 + (idx % W) * 4;
-    const float* src = p + static_cast<u64>(k) * N + n;
-    if (k < K && vec_ok && n + 3 < N) {
-      const float4 q = *reinterpret_cast<const float4*>(src);
-      reg[v][0] = q.x; reg[v][1] = q.y; reg[v][2] = q.z; reg[v][3] = q.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) reg[v][j] = (k < K && n + j < N) ? src[j] : 0.0f;
-    }
+    const int valid = k < K && n < N ? static_cast<int>(N - n < 4u ? N - n : 4u) : 0;
+    contract_load4<IS_BF16>(p, static_cast<u64>(k) * N + n, vec_ok && valid == 4, valid, reg[v]);
   }
 }
 template <int TM>
@@ -359,7 +434,7 @@ __device__ __forceinline__ void contract_stash_n_fastest(float (*tile)[ContractT
   }
 }
 
-template <class Map, class Post, int COMBINE, int RHS_NK, int TM>
+template <class Map, class Post, int COMBINE, int RHS_NK, int TM, int BF = 0>
 __global__ void __launch_bounds__(256, 2)
 chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, float* __restrict__ out, u32 M, u32 N,
                u32 K, float init, Caps caps) {
@@ -378,11 +453,12 @@ chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, flo
 #pragma unroll
     for (int j = 0; j < TM; ++j) acc[i][j] = C::identity();
 
+  constexpr bool ABF = (BF & 1) != 0, BBF = (BF & 2) != 0;  // bf16 operands are widened to f32 at the load
   float ra[T::V][4], rb[T::V][4];
   if (K > 0) {
-    contract_fetch_k_fastest<TM>(lhs, m0, M, 0, K, a_vec, ra);
-    if (RHS_NK) contract_fetch_k_fastest<TM>(rhs, n0, N, 0, K, b_vec, rb);
-    else contract_fetch_n_fastest<TM>(rhs, n0, N, 0, K, b_vec, rb);
+    contract_fetch_k_fastest<TM, ABF>(lhs, m0, M, 0, K, a_vec, ra);
+    if (RHS_NK) contract_fetch_k_fastest<TM, BBF>(rhs, n0, N, 0, K, b_vec, rb);
+    else contract_fetch_n_fastest<TM, BBF>(rhs, n0, N, 0, K, b_vec, rb);
     contract_stash_k_fastest<TM>(As[0], ra);
     if (RHS_NK) contract_stash_k_fastest<TM>(Bs[0], rb);
     else contract_stash_n_fastest<TM>(Bs[0], rb);
@@ -393,9 +469,9 @@ chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, flo
   for (u32 k0 = 0; k0 < K; k0 += BK, cur ^= 1) {
     const bool more = k0 + BK < K;
     if (more) {  // the next tile travels while this one is multiplied
-      contract_fetch_k_fastest<TM>(lhs, m0, M, k0 + BK, K, a_vec, ra);
-      if (RHS_NK) contract_fetch_k_fastest<TM>(rhs, n0, N, k0 + BK, K, b_vec, rb);
-      else contract_fetch_n_fastest<TM>(rhs, n0, N, k0 + BK, K, b_vec, rb);
+      contract_fetch_k_fastest<TM, ABF>(lhs, m0, M, k0 + BK, K, a_vec, ra);
+      if (RHS_NK) contract_fetch_k_fastest<TM, BBF>(rhs, n0, N, k0 + BK, K, b_vec, rb);
+      else contract_fetch_n_fastest<TM, BBF>(rhs, n0, N, k0 + BK, K, b_vec, rb);
     }
     const int kmax = (K - k0 < static_cast<u32>(BK)) ? static_cast<int>(K - k0) : BK;
     auto step = [&](int kk) {
@@ -438,6 +514,107 @@ chain_contract(const float* __restrict__ lhs, const float* __restrict__ rhs, flo
       if (n >= N) continue;
       const float r[1] = {C::apply(init, acc[i][j])};
       out[static_cast<u64>(m) * N + n] = Post::apply(r, caps.c + 8);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Map-only chain with a rank-preserving store: out[i] = map(ins[0][i], ins[1][i], ...) over n elements of
+// identically shaped operands. The reference's rungs cannot store a map without a reduction
+// (pkg/chain.go:433-438); its emitted code for a map statement is one predicated TensorView::Get per operand
+// and one Set per element (runtime/tca/view.h:104-112). Here a thread owns EPT = 8 consecutive elements: per
+// operand two 16-byte loads (f32 / i32 / u32) or one (bf16), all issued before the first lambda, and the same
+// on the store side. The last n % 8 elements are done one by one by the thread after the last full group.
+// EPT = 1 is the same kernel with single-element accesses, for pointers that are not 16-byte aligned.
+// OUT_BF16: the result is rounded to bf16 (the functor returns the bf16 value widened to f32, exactly).
+template <int EPT, bool IS_BF16>
+struct MapLd;
+template <>
+struct MapLd<8, false> {
+  static __device__ __forceinline__ void load(const float* base, u64 group, float* f) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(base) + 2 * group);
+    const float4 b = __ldcs(reinterpret_cast<const float4*>(base) + 2 * group + 1);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+template <>
+struct MapLd<8, true> {
+  static __device__ __forceinline__ void load(const float* base, u64 group, float* f) {
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(base) + group);
+    const unsigned int w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = bf16_bits_to_float(w[i] & 0xffffu);
+      f[2 * i + 1] = bf16_bits_to_float(w[i] >> 16);
+    }
+  }
+};
+template <>
+struct MapLd<1, false> {
+  static __device__ __forceinline__ void load(const float* base, u64 i, float* f) { f[0] = __ldcs(base + i); }
+};
+template <>
+struct MapLd<1, true> {
+  static __device__ __forceinline__ void load(const float* base, u64 i, float* f) {
+    f[0] = bf16_bits_to_float(__ldcs(reinterpret_cast<const unsigned short*>(base) + i));
+  }
+};
+template <int EPT, int BF, int NIN, int A = 0>
+struct MapLoadAll {
+  static __device__ __forceinline__ void at(const float* const* p, u64 index, float (*f)[EPT]) {
+    MapLd<EPT, ((BF >> A) & 1) != 0>::load(p[A], index, f[A]);
+    MapLoadAll<EPT, BF, NIN, A + 1>::at(p, index, f);
+  }
+};
+template <int EPT, int BF, int NIN>
+struct MapLoadAll<EPT, BF, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, float (*)[EPT]) {}
+};
+
+template <int NIN, int BF, bool OUT_BF16, class Map>
+__device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i, const float* caps) {
+  float f[NIN][1];
+  MapLoadAll<1, BF, NIN>::at(p, i, f);
+  float v[NIN];
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) v[a] = f[a][0];
+  const float r = Map::apply(v, caps);
+  if constexpr (OUT_BF16) static_cast<unsigned short*>(out)[i] = static_cast<unsigned short>(float_to_bf16_bits(r));
+  else __stcs(static_cast<float*>(out) + i, r);
+}
+
+template <class Map, int NIN, int BF, bool OUT_BF16, int EPT>
+__global__ void __launch_bounds__(256)
+chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps) {
+  const u64 tid = static_cast<u64>(blockIdx.x) * 256 + threadIdx.x;
+  if constexpr (EPT == 1) {
+    if (tid < n) map_one<NIN, BF, OUT_BF16, Map>(ins.p, out, tid, caps.c);
+  } else {
+    const u64 groups = n / 8;
+    if (tid < groups) {
+      float f[NIN][8];
+      MapLoadAll<8, BF, NIN>::at(ins.p, tid, f);
+      float r[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float v[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) v[a] = f[a][j];
+        r[j] = Map::apply(v, caps.c);
+      }
+      if constexpr (OUT_BF16) {
+        uint4 q;
+        q.x = float_to_bf16_bits(r[0]) | (float_to_bf16_bits(r[1]) << 16);
+        q.y = float_to_bf16_bits(r[2]) | (float_to_bf16_bits(r[3]) << 16);
+        q.z = float_to_bf16_bits(r[4]) | (float_to_bf16_bits(r[5]) << 16);
+        q.w = float_to_bf16_bits(r[6]) | (float_to_bf16_bits(r[7]) << 16);
+        __stcs(static_cast<uint4*>(out) + tid, q);
+      } else {
+        __stcs(static_cast<float4*>(out) + 2 * tid, make_float4(r[0], r[1], r[2], r[3]));
+        __stcs(static_cast<float4*>(out) + 2 * tid + 1, make_float4(r[4], r[5], r[6], r[7]));
+      }
+    } else if (tid == groups) {  // the ragged end, fewer than eight elements
+      for (u64 i = groups * 8; i < n; ++i) map_one<NIN, BF, OUT_BF16, Map>(ins.p, out, i, caps.c);
     }
   }
 }

@@ -45,10 +45,20 @@ TCAB_LAMBDA(PostSelfRsqrt, 1, (p0 * rsqrtf(((p0 * c0) + c1))))
 TCAB_LAMBDA(PostAddTanh, 1, (p0 + (c0 * tanhf(p0))))
 TCAB_LAMBDA(PostScale, 1, (p0 * c0))
 
+// map-only lambdas with an ahead-of-time kernel
+TCAB_LAMBDA(MapScale, 1, (p0 * c0))
+TCAB_LAMBDA(MapAffine, 1, ((p0 * c0) + c1))
+TCAB_LAMBDA(MapAffineL, 1, ((c0 * p0) + c1))
+TCAB_LAMBDA(MapRelu, 1, fmaxf(p0, c0))
+TCAB_LAMBDA(MapExp, 1, expf(p0))
+TCAB_LAMBDA(MapTanh, 1, tanhf(p0))
+TCAB_LAMBDA(MapAdd2, 2, (p0 + p1))
+
 // Partials of the multi-CTA split: at most this many per launch.
 constexpr uint32_t kMaxSplitPartials = 262144;  // 1 MiB per (device, stream)
 
 float* split_scratch(cudaStream_t stream);
+int find_map_entry(const std::string& text, int n_in);
 
 }  // namespace
 
@@ -283,6 +293,54 @@ float* split_scratch(cudaStream_t stream) {
   return static_cast<float*>(stream_scratch(kScratchChainSplit, stream, kMaxSplitPartials * sizeof(float), false));
 }
 
+// ---- map-only chains ----------------------------------------------------------------------------------
+struct MapArgs {
+  const void* const* ins;
+  void* out;
+  uint64_t n;
+  Caps caps;
+  cudaStream_t stream;
+};
+
+template <class Map>
+int launch_map_aot(const MapArgs& a) {
+  constexpr int NIN = Map::kIn;
+  Ptrs<NIN> ptrs;
+  bool al = aligned16(a.out);
+  for (int i = 0; i < NIN; ++i) {
+    ptrs.p[i] = static_cast<const float*>(a.ins[i]);
+    al = al && aligned16(a.ins[i]);
+  }
+  if (al) {
+    const uint64_t threads = a.n / 8 + 1;  // one thread per group of eight, one more for the ragged end
+    tcabk::chain_map<Map, NIN, 0, false, 8>
+        <<<static_cast<unsigned>((threads + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps);
+  } else {
+    tcabk::chain_map<Map, NIN, 0, false, 1>
+        <<<static_cast<unsigned>((a.n + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps);
+  }
+  count_launch();
+  return check_launch("chain_map");
+}
+
+struct MapEntry {
+  const char* map;
+  int n_in;
+  int (*launch)(const MapArgs&);
+};
+#define TCAB_MAP_ENTRY(MAP) { MAP::text(), MAP::kIn, &launch_map_aot<MAP> }
+const MapEntry kMapTable[] = {
+    TCAB_MAP_ENTRY(MapIdent),  TCAB_MAP_ENTRY(MapAffineSq), TCAB_MAP_ENTRY(MapScale), TCAB_MAP_ENTRY(MapAffine),
+    TCAB_MAP_ENTRY(MapAffineL), TCAB_MAP_ENTRY(MapRelu),    TCAB_MAP_ENTRY(MapExp),   TCAB_MAP_ENTRY(MapTanh),
+    TCAB_MAP_ENTRY(MapAdd2),   TCAB_MAP_ENTRY(MapMul2),
+};
+
+int find_map_entry(const std::string& text, int n_in) {
+  for (size_t i = 0; i < sizeof(kMapTable) / sizeof(kMapTable[0]); ++i)
+    if (kMapTable[i].n_in == n_in && text == kMapTable[i].map) return static_cast<int>(i);
+  return -1;
+}
+
 int combine_id(const std::string& text) {
   if (text == "(p0 + p1)" || text == "(p1 + p0)") return 0;
   if (text == "fmaxf(p0, p1)" || text == "fmaxf(p1, p0)") return 1;
@@ -292,43 +350,71 @@ int combine_id(const std::string& text) {
 
 }  // namespace
 
-int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc) {
+int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind, const int* in_types, int out_type) {
+  const char* op = kind == 'M' ? "map" : kind == 'C' ? "chain_contract" : "chain_reduce";
   std::vector<float> user(chain->captures, chain->captures + chain->n_captures);
   CanonExpr map, comb, post;
   std::string err;
-  if (!canonicalize(chain->map_expr, static_cast<int>(n_ins), user, &map, &err))
-    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: map_expr: %s", err.c_str());
-  if (!canonicalize(chain->combine_expr, 2, {}, &comb, &err))
-    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: combine_expr: %s", err.c_str());
-  const bool has_post = chain->post_expr != nullptr && chain->post_expr[0] != '\0';
-  if (has_post && !canonicalize(chain->post_expr, 1, user, &post, &err))
-    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: post_expr: %s", err.c_str());
+  ElemT types[TCAB_MAX_INPUTS] = {kF32, kF32, kF32, kF32};
+  bool all_f32 = true;
+  for (uint32_t i = 0; i < n_ins && in_types != nullptr; ++i) {
+    types[i] = static_cast<ElemT>(in_types[i]);
+    all_f32 = all_f32 && in_types[i] == TCAB_F32;
+  }
+  if (!canonicalize(chain->map_expr, static_cast<int>(n_ins), types, user, &map, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "%s: map_expr: %s", op, err.c_str());
   if (map.n_operands != static_cast<int>(n_ins))
-    return fail(TCAB_ERR_INVALID_ARG, "chain_reduce: map_expr uses %d operands, %u given", map.n_operands, n_ins);
-  const int cid = combine_id(comb.text);
-  if (cid < 0)
-    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: combiner '%s' is not sum/fmaxf/fminf", comb.text.c_str());
-  if (map.captures.size() > 8 || post.captures.size() > 8)
-    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: more than 8 distinct constants in one lambda");
+    return fail(TCAB_ERR_INVALID_ARG, "%s: map_expr uses %d operands, %u given", op, map.n_operands, n_ins);
+  if (map.captures.size() > 8) return fail(TCAB_ERR_UNSUPPORTED, "%s: more than 8 distinct constants in one lambda", op);
   for (int i = 0; i < 16; ++i) pc->caps[i] = 0.0f;
   for (size_t i = 0; i < map.captures.size(); ++i) pc->caps[i] = map.captures[i];
-  for (size_t i = 0; i < post.captures.size(); ++i) pc->caps[8 + i] = post.captures[i];
   pc->init = chain->init;
   pc->entry = -1;
-  const std::string post_text = has_post ? post.text : std::string();
-  for (size_t i = 0; i < sizeof(kTable) / sizeof(kTable[0]); ++i) {
-    const Entry& e = kTable[i];
-    if (e.combine == cid && e.n_in == static_cast<int>(n_ins) && map.text == e.map && post_text == e.post) {
-      pc->entry = static_cast<int>(i);
-      return TCAB_OK;
+  JitSpec& sp = pc->spec;
+  sp = JitSpec();
+  sp.kind = kind;
+  sp.n_in = static_cast<int>(n_ins);
+  for (uint32_t i = 0; i < n_ins; ++i) sp.in_types[i] = static_cast<int>(types[i]);
+  sp.out_type = out_type;
+  sp.map_text = map.text;
+  if (kind == 'M') {
+    // a map-only chain stores the lambda's value as it is: its type is the output's element type, no conversion
+    // is implied (casts are always explicit, internal/ir/types.go:60-62)
+    if (static_cast<int>(map.type) != out_type)
+      return fail(TCAB_ERR_DTYPE, "map: the lambda yields %s but out holds %s; convert explicitly (static_cast)",
+                  elem_name(map.type), elem_name(static_cast<ElemT>(out_type)));
+    if (all_f32 && out_type == TCAB_F32) pc->entry = find_map_entry(map.text, static_cast<int>(n_ins));
+    if (pc->entry < 0) pc->entry = kJitEntry;
+    return TCAB_OK;
+  }
+  // reductions and contractions fold f32 values (homogeneous reducers: pkg/chain.go:229-264)
+  if (map.type != kF32)
+    return fail(TCAB_ERR_DTYPE, "%s: the map lambda yields %s; this class folds f32 values, convert explicitly", op,
+                elem_name(map.type));
+  if (!canonicalize(chain->combine_expr, 2, nullptr, {}, &comb, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "%s: combine_expr: %s", op, err.c_str());
+  const bool has_post = chain->post_expr != nullptr && chain->post_expr[0] != '\0';
+  if (has_post && !canonicalize(chain->post_expr, 1, nullptr, user, &post, &err))
+    return fail(TCAB_ERR_INVALID_ARG, "%s: post_expr: %s", op, err.c_str());
+  if (has_post && post.type != kF32)
+    return fail(TCAB_ERR_DTYPE, "%s: the piped map yields %s; out holds f32", op, elem_name(post.type));
+  const int cid = combine_id(comb.text);
+  if (cid < 0) return fail(TCAB_ERR_UNSUPPORTED, "%s: combiner '%s' is not sum/fmaxf/fminf", op, comb.text.c_str());
+  if (post.captures.size() > 8) return fail(TCAB_ERR_UNSUPPORTED, "%s: more than 8 distinct constants in one lambda", op);
+  for (size_t i = 0; i < post.captures.size(); ++i) pc->caps[8 + i] = post.captures[i];
+  sp.combine = cid;
+  sp.post_text = has_post ? post.text : std::string();
+  if (all_f32) {
+    for (size_t i = 0; i < sizeof(kTable) / sizeof(kTable[0]); ++i) {
+      const Entry& e = kTable[i];
+      if (e.combine == cid && e.n_in == static_cast<int>(n_ins) && map.text == e.map && sp.post_text == e.post) {
+        pc->entry = static_cast<int>(i);
+        return TCAB_OK;
+      }
     }
   }
   // no ahead-of-time instance: compiled at run time on the first launch (chain_jit.cu)
   pc->entry = kJitEntry;
-  pc->combine = cid;
-  pc->n_in = static_cast<int>(n_ins);
-  pc->map_text = map.text;
-  pc->post_text = post_text;
   return TCAB_OK;
 }
 
@@ -337,13 +423,13 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   if (outer == 0 || inner == 0) return TCAB_OK;
   if (pc.entry == kJitEntry) {
     void* h = nullptr;
-    const int rc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
+    const int rc = jit_prepare(pc.spec, &h);
     if (rc != TCAB_OK) return rc;
     uint32_t splits = 1;
     float* scratch = nullptr;
     if (inner == 1) {
       bool al = true;
-      for (int i = 0; i < pc.n_in; ++i) al = al && aligned16(ins[i]);
+      for (int i = 0; i < pc.spec.n_in; ++i) al = al && aligned16(ins[i]);
       splits = choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
       if (splits > 1) scratch = split_scratch(s);
     } else if (outer * ((inner + 127) / 128) < static_cast<uint64_t>(sm_count()) && nk >= 512) {
@@ -356,25 +442,40 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   return kTable[pc.entry].launch(a);
 }
 
-// Compiles and loads the kernels of a chain that has no ahead-of-time instance (nothing to do otherwise).
-int warm_chain(const PreparedChain& pc, bool contraction) {
-  if (contraction) {
-    if (pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text() &&
-        (std::string(kTable[pc.entry].post).empty() || std::string(kTable[pc.entry].post) == PostScale::text()))
-      return TCAB_OK;
-    std::string map_text = pc.map_text, post_text = pc.post_text;
-    int combine = pc.combine;
-    if (pc.entry >= 0) {
-      map_text = kTable[pc.entry].map;
-      post_text = kTable[pc.entry].post;
-      combine = kTable[pc.entry].combine;
-    }
+int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, cudaStream_t s) {
+  if (n == 0) return TCAB_OK;
+  if (n / 8 / 256 >= 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "map: too many elements for one launch");
+  if (pc.entry == kJitEntry) {
     void* h = nullptr;
-    return jit_prepare(map_text, post_text, combine, 2, true, &h);
+    const int rc = jit_prepare(pc.spec, &h);
+    if (rc != TCAB_OK) return rc;
+    return jit_launch_map(h, ins, out, n, pc.caps, s);
   }
-  if (pc.entry != kJitEntry) return TCAB_OK;
+  MapArgs a{ins, out, n, {}, s};
+  for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
+  return kMapTable[pc.entry].launch(a);
+}
+
+// The chain as the run-time compiler sees it when it is launched as a contraction: a chain found in the
+// reduce table carries that table's lambdas.
+JitSpec contract_spec(const PreparedChain& pc) {
+  JitSpec sp = pc.spec;
+  sp.kind = 'C';
+  sp.n_in = 2;
+  return sp;
+}
+
+bool contract_is_aot(const PreparedChain& pc) {
+  return pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text() &&
+         (std::string(kTable[pc.entry].post).empty() || std::string(kTable[pc.entry].post) == PostScale::text());
+}
+
+// Compiles and loads the kernels of a chain that has no ahead-of-time instance (nothing to do otherwise).
+int warm_chain(const PreparedChain& pc) {
   void* h = nullptr;
-  return jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h);
+  if (pc.spec.kind == 'C') return contract_is_aot(pc) ? TCAB_OK : jit_prepare(contract_spec(pc), &h);
+  if (pc.entry != kJitEntry) return TCAB_OK;
+  return jit_prepare(pc.spec, &h);
 }
 
 // ---------------------------------------------------------------------------
@@ -430,15 +531,8 @@ int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float
     if (post == PostScale::text())
       return launch_contract_aot<MapMul2, PostScale, 0>(lhs, rhs, out, m, n, k, rhs_nk, pc.init, caps, s);
   }
-  std::string map_text = pc.map_text, post_text = pc.post_text;
-  int combine = pc.combine;
-  if (pc.entry >= 0) {  // in the reduce table but without a contraction instance: compile it
-    map_text = kTable[pc.entry].map;
-    post_text = kTable[pc.entry].post;
-    combine = kTable[pc.entry].combine;
-  }
   void* h = nullptr;
-  const int rc = jit_prepare(map_text, post_text, combine, 2, true, &h);
+  const int rc = jit_prepare(contract_spec(pc), &h);
   if (rc != TCAB_OK) return rc;
   return jit_launch_contract(h, lhs, rhs, rhs_nk, out, m, n, k, pc.init, pc.caps, s);
 }
@@ -508,12 +602,12 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
   if (pc.entry == kJitEntry) {
     // Never compiled here: compiling loads a code image onto the device, which allocates device memory.
     void* h = nullptr;
-    const int jrc = jit_prepare(pc.map_text, pc.post_text, pc.combine, pc.n_in, false, &h, false);
+    const int jrc = jit_prepare(pc.spec, &h, false);
     if (jrc != TCAB_OK)
       return fail(TCAB_ERR_UNSUPPORTED,
                   "chain_reduce_noalloc: the lambda '%s' has no ahead-of-time kernel and has not been compiled in this "
                   "process yet; call tcab_chain_prepare (or tcab_chain_reduce) with it once, outside any capture",
-                  pc.map_text.c_str());
+                  pc.spec.map_text.c_str());
     // the split kernels always: splits may be 1, the partials still pass through the fixed array
     return jit_launch(h, ins, rows, nk, 1, pc.init, pc.caps, out, scratch, static_cast<uint32_t>(splits) | 0x80000000u, s);
   }

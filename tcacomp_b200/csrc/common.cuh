@@ -71,33 +71,48 @@ int launch_layernorm_rows_f32(const float* x, const float* gamma, const float* b
                               float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
 int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb,
                         uint32_t nk, uint32_t nc, cudaStream_t s);
+// What the run-time compiler needs to know about a chain: which kernels ('R' the reduction kernels, 'C' the
+// contraction kernels, 'M' the map-only kernels), the canonical lambdas and the element types.
+struct JitSpec {
+  char kind = 'R';
+  int n_in = 0, combine = 0;
+  int in_types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};  // tcab_dtype of each operand
+  int out_type = TCAB_F32;                                                   // map-only: the stored element type
+  std::string map_text, post_text;
+  int bf_mask() const {
+    int m = 0;
+    for (int i = 0; i < n_in; ++i) m |= (in_types[i] == TCAB_BF16) << i;
+    return m;
+  }
+};
 // A chain whose lambdas were validated, canonicalised and matched to a compiled kernel.
 struct PreparedChain {
   int entry = -1;   // index into the table of ahead-of-time chains, or kJitEntry
   float init = 0.0f;
   float caps[16];   // map captures in [0,8), piped-map captures in [8,16)
-  // for a chain that has to be compiled at run time: its canonical lambdas
-  int combine = 0, n_in = 0;
-  std::string map_text, post_text;
+  JitSpec spec;     // canonical lambdas and types (always filled in)
 };
 constexpr int kJitEntry = -2;
 // Run-time compilation of chains without an ahead-of-time instance (chain_jit.cu).
 bool jit_available();
-int jit_prepare(const std::string& map_text, const std::string& post_text, int combine, int n_in, bool contraction,
-                void** handle, bool compile_if_missing = true);  // contraction: the contraction kernels instead of the
-                                                                 // reduction kernels; without compile_if_missing a
-                                                                 // lambda that is not cached yet is TCAB_ERR_UNSUPPORTED
+// Without compile_if_missing a chain that is not cached yet is TCAB_ERR_UNSUPPORTED.
+int jit_prepare(const JitSpec& spec, void** handle, bool compile_if_missing = true);
+int jit_compile_check(const JitSpec& spec);  // NVRTC only, nothing is loaded: works without a device
 int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
                const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s);
+int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, const float* caps16, cudaStream_t s);
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
-int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc);
+// kind: 'R' / 'C' / 'M' as in JitSpec; in_types: n_ins tcab_dtype values (null = all f32); out_type: map-only.
+int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind = 'R', const int* in_types = nullptr,
+                  int out_type = TCAB_F32);
+int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, cudaStream_t s);
 int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
                         uint64_t inner, float* out, cudaStream_t s);
 int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias,
                          int act, __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k,
                          cudaStream_t s);
 
-int warm_chain(const PreparedChain& pc, bool contraction);  // compile + load now what a launch would compile later
+int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
 int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins, uint64_t rows, uint32_t nk,
                                 float* out, cudaStream_t s);
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,

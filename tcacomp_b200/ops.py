@@ -14,7 +14,7 @@ import torch
 
 from . import _lib
 
-_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int32: _lib.I32}
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int32: _lib.I32, torch.uint32: _lib.U32}
 
 
 def _view(t: torch.Tensor, name: str) -> _lib.Tensor:
@@ -91,14 +91,20 @@ def tune(family: str, p0: int = 0, p1: int = 0, p2: int = 0, p3: int = 0) -> Non
 
 
 def chain_prepare(map_expr: str, n_ins: int = 1, combine_expr: str = "(p0 + p1)", post_expr: Optional[str] = None,
-                  captures: Sequence[float] = (), contraction: bool = False,
-                  device: Optional[torch.device] = None) -> None:
-    """Compile and load now what the first chain_reduce / chain_contract with these lambdas would compile
-    later (nothing to do for lambdas with an ahead-of-time kernel). Not during a stream capture."""
+                  captures: Sequence[float] = (), use: str = "reduce", in_dtypes: Optional[Sequence[torch.dtype]] = None,
+                  out_dtype: torch.dtype = torch.float32, device: Optional[torch.device] = None) -> None:
+    """Compile and load now what the first chain_reduce / chain_contract / map (use = "reduce", "contract",
+    "map") with these lambdas and operand types would compile later (nothing to do for lambdas with an
+    ahead-of-time kernel). Not during a stream capture."""
     chain = _chain(map_expr, combine_expr, post_expr, 0.0, captures)
+    code = {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP}[use]
+    types = None
+    if in_dtypes is not None:
+        if len(in_dtypes) != n_ins:
+            raise ValueError("in_dtypes must name one dtype per operand")
+        types = (C.c_int32 * n_ins)(*[_DTYPES[d] for d in in_dtypes])
     with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
-        _lib.check(_lib.load().tcab_chain_prepare(C.byref(chain), n_ins,
-                                                  _lib.USE_CONTRACT if contraction else _lib.USE_REDUCE))
+        _lib.check(_lib.load().tcab_chain_prepare(C.byref(chain), types, n_ins, code, _DTYPES[out_dtype]))
 
 
 def release_stream(stream: Optional[torch.cuda.Stream] = None, device: Optional[torch.device] = None) -> None:
@@ -189,6 +195,27 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
     with _on_device(t0):
         _lib.check(_lib.load().tcab_chain_reduce(C.byref(chain), arr, len(ins), ax, C.byref(ov),
                                                  _stream(stream, t0)))
+    return out
+
+
+def map(ins: Sequence[torch.Tensor], map_expr: str, captures: Sequence[float] = (),  # noqa: A001 (the operator's name)
+        out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
+        stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Map-only chain with a rank-preserving store: out[...] = map_expr(ins[0][...], ins[1][...], ...).
+
+    Operands share one shape and may be f32, bf16, i32 or u32; the lambda sees each with its own type and must
+    yield exactly the output's element type (out.dtype, or out_dtype, default: that of ins[0])."""
+    ins = list(ins)
+    if not 1 <= len(ins) <= _lib.MAX_INPUTS:
+        raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
+    if out is None:
+        out = torch.empty(ins[0].shape, device=ins[0].device, dtype=out_dtype or ins[0].dtype)
+    chain = _chain(map_expr, "(p0 + p1)", None, 0.0, captures)
+    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    ov = _view(out, "out")
+    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
+    with _on_device(ins[0]):
+        _lib.check(_lib.load().tcab_map(C.byref(chain), arr, len(ins), C.byref(ov), _stream(stream, ins[0])))
     return out
 
 

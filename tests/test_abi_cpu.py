@@ -159,18 +159,116 @@ def test_python_views_refuse_what_32_bit_extents_cannot_hold():
         ops._view(torch.empty((4, 4)), "x")
 
 
+def _bchain(map_expr, combine=b"(p0 + p1)", post=None):
+    from tcacomp_b200 import _lib
+    ch = _lib.Chain()
+    ch.map_expr, ch.combine_expr, ch.post_expr = map_expr, combine, post
+    return ch
+
+
 def test_prepare_and_release_validate_without_a_device(tcab_lib):
     from tcacomp_b200 import _lib
     L = tcab_lib
-    ch = _lib.Chain()
-    ch.map_expr, ch.combine_expr = b"sinf(p0) * p1", b"(p0 + p1)"
-    assert L.tcab_chain_prepare(C.byref(ch), 2, 7) == _lib.ERR_INVALID_ARG          # unknown use
-    assert L.tcab_chain_prepare(C.byref(ch), 3, _lib.USE_CONTRACT) == _lib.ERR_INVALID_ARG  # contractions take two
-    ch.map_expr = b"sinf(p0) * q1"
-    assert L.tcab_chain_prepare(C.byref(ch), 2, _lib.USE_REDUCE) == _lib.ERR_INVALID_ARG    # the lambda is validated first
+    ch = _bchain(b"sinf(p0) * p1")
+    assert L.tcab_chain_prepare(C.byref(ch), None, 2, 7, 0) == _lib.ERR_INVALID_ARG          # unknown use
+    assert L.tcab_chain_prepare(C.byref(ch), None, 3, _lib.USE_CONTRACT, 0) == _lib.ERR_INVALID_ARG  # contractions take two
+    bad = _bchain(b"sinf(p0) * q1")
+    assert L.tcab_chain_prepare(C.byref(bad), None, 2, _lib.USE_REDUCE, 0) == _lib.ERR_INVALID_ARG   # the lambda is validated first
     import torch
     if not torch.cuda.is_available():
-        ch.map_expr = b"sinf(p0) * p1"
-        assert L.tcab_chain_prepare(C.byref(ch), 2, _lib.USE_REDUCE) == _lib.ERR_CUDA      # compiling needs the device
+        assert L.tcab_chain_prepare(C.byref(ch), None, 2, _lib.USE_REDUCE, 0) == _lib.ERR_CUDA      # compiling needs the device
         assert L.tcab_release_stream(None) == _lib.ERR_CUDA
     assert L.tcab_release_all() == _lib.OK                                               # nothing held: nothing to free
+
+
+F, B, I, U = 0, 1, 2, 3
+
+# (lambda, operand types, use, output type): the reference's typed vocabulary (pkg/expr.go:137-176, 185-203, 271;
+# operator spellings internal/cg/cxx/naming.go:126-183), every form once. Each is validated, printed as a typed
+# functor and compiled for sm_100a by the run-time compiler -- no GPU needed for that.
+TYPED_OK = [
+    (b"p0 > 0.0f ? p0 : 0.0f", [F], "map", F),                                  # Select(Gt(v, 0), v, 0): relu
+    (b"(p0 >= p1 && p0 != 1.0f) || !(p1 <= 2.0f) ? p0 - p1 : -p0 / p1", [F, F], "map", F),
+    (b"p0 == p1 ? 1 : 0", [F, F], "map", I),
+    (b"bf16(fmaxf(f32(p0) * f32(p1) + 1.0f, 0.0f))", [B, B], "map", B),         # Cast bf16 -> f32 -> bf16
+    (b"static_cast<float>(p0)", [B], "map", F),
+    (b"(p0 & 255) << 3 | p1 >> 1 ^ ~p0 % 7", [I, I], "map", I),                # Mod BitAnd BitOr BitXor Shl Shr BitsNot
+    (b"umin(p0, 7u) + umax(p1, p0) * 3u - (p0 >> 1u)", [U, U], "map", U),
+    (b"i32(p0) + i32(f32(p1))", [F, B], "map", I),
+    (b"u32(p0) < 5u ? f32(p0) : fabsf(f32(p0))", [I], "map", F),
+    (b"f32(p0) * p1", [B, F], "reduce", F),                                     # bf16 operand widened inside a reduction
+    (b"(p0 % 3 == 0 ? 2.0f : 0.5f) * p1", [I, F], "reduce", F),
+]
+TYPED_BAD = [
+    (b"p0 * 2", [F], "map", F, b"operand types differ"),                         # no implicit promotion
+    (b"p0 + p1", [F, I], "map", F, b"operand types differ"),
+    (b"p0 * p1", [B, B], "map", B, b"convert bf16 to f32 first"),                # bf16 is a storage type
+    (b"p0 % p1", [F, F], "map", F, b"same integer type"),
+    (b"p0 && p1", [F, F], "map", F, b"must be bool"),
+    (b"p0 ? p1 : p0", [F, F], "map", F, b"condition must be bool"),
+    (b"p0 < p1 ? 1 : 2u", [F, F], "map", I, b"identical types"),
+    (b"f32(p0)", [F], "map", F, b"redundant cast"),
+    (b"f32(p0 < p1)", [F, F], "map", F, b"bool cannot be converted"),
+    (b"~p0", [F], "map", F, b"integer type"),
+    (b"p0", [F], "map", B, b"convert explicitly"),                               # the store never converts
+    (b"i32(p0)", [F], "reduce", F, b"folds f32 values"),
+    (b"expf(p0)", [I], "map", F, b"must be f32"),
+    (b"umin(p0, p1)", [I, I], "map", I, b"must be u32"),
+    (b"4294967296u", [F], "map", U, b"out of range"),
+]
+
+
+def _use(name):
+    from tcacomp_b200 import _lib
+    return {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP}[name]
+
+
+@pytest.mark.parametrize("expr,types,use,out", TYPED_OK)
+def test_typed_lambdas_compile_for_sm100(tcab_lib, expr, types, use, out):
+    from tcacomp_b200 import _lib
+    ch = _bchain(expr)
+    arr = (C.c_int32 * len(types))(*types)
+    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out)
+    assert rc == _lib.OK, _err(tcab_lib)
+
+
+@pytest.mark.parametrize("expr,types,use,out,why", TYPED_BAD)
+def test_ill_typed_lambdas_are_refused_before_any_compiler(tcab_lib, expr, types, use, out, why):
+    from tcacomp_b200 import _lib
+    ch = _bchain(expr)
+    arr = (C.c_int32 * len(types))(*types)
+    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out)
+    assert rc in (_lib.ERR_INVALID_ARG, _lib.ERR_DTYPE), (rc, _err(tcab_lib))
+    assert why in tcab_lib.tcab_last_error(), _err(tcab_lib)
+
+
+def test_partition_rule_and_pipeline_validation_without_a_device(tcab_lib):
+    from tcacomp_b200 import _lib, shard
+    L = tcab_lib
+    lo, hi = C.c_uint64(), C.c_uint64()
+    for n in (0, 1, 7, 1003, 65536):
+        for world in (1, 2, 3, 8):
+            covered = 0
+            for r in range(world):
+                assert L.tcab_shard_block(n, world, r, C.byref(lo), C.byref(hi)) == _lib.OK
+                assert (lo.value, hi.value) == shard.block(n, world, r) and lo.value == covered
+                covered = hi.value
+            assert covered == n
+    assert L.tcab_shard_block(10, 2, 2, C.byref(lo), C.byref(hi)) == _lib.ERR_INVALID_ARG
+    d = _lib.PipelineDesc()
+    d.op, d.device, d.chunk_units, d.in_dtype, d.n_streamed, d.unit_rank = _lib.OP_SOFTMAX_ROWS, -1, 16, _lib.F32, 1, 1
+    d.unit_dims[0] = 512
+    h = C.c_void_p()
+    d.chunk_units = 0
+    assert L.tcab_pipeline_create(C.byref(d), C.byref(h)) == _lib.ERR_INVALID_ARG and not h.value
+    d.chunk_units, d.depth = 16, 9
+    assert L.tcab_pipeline_create(C.byref(d), C.byref(h)) == _lib.ERR_INVALID_ARG
+    d.depth, d.in_dtype = 0, _lib.BF16
+    assert L.tcab_pipeline_create(C.byref(d), C.byref(h)) == _lib.ERR_DTYPE          # softmax rows are f32
+    d.in_dtype, d.op = _lib.F32, _lib.OP_LAYERNORM_ROWS
+    assert L.tcab_pipeline_create(C.byref(d), C.byref(h)) == _lib.ERR_INVALID_ARG    # gamma / beta missing
+    import torch
+    if not torch.cuda.is_available():
+        d.op = _lib.OP_SOFTMAX_ROWS
+        assert L.tcab_pipeline_create(C.byref(d), C.byref(h)) == _lib.ERR_CUDA and not h.value   # no CPU path
+    assert L.tcab_pipeline_destroy(None) == _lib.OK and L.tcab_multi_destroy(None) == _lib.OK

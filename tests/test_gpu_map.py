@@ -1,0 +1,249 @@
+"""The map-only operator (tcab_map) and the typed lambda vocabulary on a B200, through the C ABI.
+
+Oracle: the caller's expression text compiled by the host C++ compiler and run element by element
+(oracle/lambda_eval.py) -- what the reference does with a lambda, on the CPU
+(internal/cg/cxx/expr.go:14-101 prints it, the C++ compiler gives it its meaning).
+Tolerances, as stated for this path: integer, index and bool-selected outputs bit-exact; fp32 maps
+within 2 ulp. For the math builtins the 2 ulp are measured against the correctly rounded fp64 value
+(the way CUDA states its own bounds); for plain arithmetic against the host evaluation, where the
+only admissible difference is one FMA contraction per operation (design/syntax-design.md:601-607).
+"""
+import numpy as np
+import pytest
+import torch
+
+import tcacomp_b200 as T
+
+pytestmark = pytest.mark.gpu
+
+NP2T = {np.dtype(np.float32): torch.float32, np.dtype(np.int32): torch.int32, np.dtype(np.uint32): torch.uint32}
+
+
+def to_dev(a, dev):
+    """numpy -> device; uint16 arrays are bf16 bit patterns."""
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.uint16:
+        return torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)
+    if a.dtype == np.uint32:
+        return torch.from_numpy(a.view(np.int32)).to(dev).view(torch.uint32)
+    return torch.from_numpy(a).to(dev)
+
+
+def to_host(t):
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    if t.dtype == torch.uint32:
+        return t.view(torch.int32).cpu().numpy().view(np.uint32)
+    return t.cpu().numpy()
+
+
+def torch_dtype(np_dtype):
+    return torch.bfloat16 if np.dtype(np_dtype) == np.uint16 else NP2T[np.dtype(np_dtype)]
+
+
+def ulp_distance(a, b):
+    """Distance in units in the last place between two float32 arrays (monotone integer images of the floats)."""
+    def key(x):
+        i = x.astype(np.float32).view(np.int32).astype(np.int64)
+        return np.where(i < 0, -(i & 0x7fffffff), i)
+    return np.abs(key(a) - key(b))
+
+
+def run_map(expr, arrays, dev, out_np_dtype, captures=()):
+    from oracle import lambda_eval
+    want = lambda_eval.evaluate(expr, arrays, captures, out_np_dtype)
+    got = to_host(T.map([to_dev(a, dev) for a in arrays], expr, captures=captures, out_dtype=torch_dtype(out_np_dtype)))
+    return got, want
+
+
+def inputs(rng, n, kind):
+    if kind == "f":
+        return rng.uniform(-4, 4, n).astype(np.float32)
+    if kind == "i":
+        return rng.integers(-1000, 1000, n).astype(np.int32)
+    if kind == "u":
+        return rng.integers(0, 1 << 20, n).astype(np.uint32)
+    from oracle import binding as O
+    return O.f32_to_bf16(rng.uniform(-4, 4, n).astype(np.float32))
+
+
+# One case per operator of the reference's vocabulary (pkg/expr.go:185-203, 271; internal/cg/cxx/naming.go:126-183).
+# (expression, operand kinds, output dtype): every one of these is exact arithmetic or a selection, so bit-exact.
+EXACT = [
+    ("p0 > p1 ? p0 : p1", "ff", np.float32), ("p0 >= 0.0f ? p0 : 0.0f", "f", np.float32),
+    ("p0 < p1 ? 1 : 0", "ff", np.int32), ("p0 <= p1 ? 1 : 0", "ii", np.int32),
+    ("p0 == p1 ? 7u : 9u", "uu", np.uint32), ("p0 != 3 ? p0 : -p0", "i", np.int32),
+    ("(p0 > 0.0f && p1 > 0.0f) ? 1 : 0", "ff", np.int32), ("(p0 > 0.0f || p1 > 0.0f) ? 1 : 0", "ff", np.int32),
+    ("!(p0 > p1) ? p0 : p1", "ff", np.float32),
+    ("p0 % 7", "i", np.int32), ("p0 % 7u", "u", np.uint32), ("p0 / 3", "i", np.int32),
+    ("p0 & p1", "ii", np.int32), ("p0 | p1", "uu", np.uint32), ("p0 ^ p1", "ii", np.int32), ("~p0", "u", np.uint32),
+    ("p0 << 3", "i", np.int32), ("p0 >> 2", "i", np.int32), ("p0 >> 5u", "u", np.uint32),
+    ("p0 + p1", "ii", np.int32), ("p0 - p1", "uu", np.uint32), ("p0 * p1", "ii", np.int32), ("-p0", "f", np.float32),
+    ("umin(p0, p1) + umax(p0, 77u)", "uu", np.uint32),
+    ("f32(p0)", "i", np.float32), ("f32(p0)", "u", np.float32), ("f32(p0)", "b", np.float32),
+    ("i32(p0)", "f", np.int32), ("u32(fabsf(p0))", "f", np.uint32), ("bf16(p0)", "f", np.uint16),
+    ("i32(p0)", "b", np.int32), ("bf16(p0)", "i", np.uint16), ("u32(p0)", "i", np.uint32),
+    ("static_cast<int32_t>(p0) + static_cast<int32_t>(static_cast<float>(p1))", "fb", np.int32),
+    ("p0 + p1", "ff", np.float32), ("p0 * p1", "ff", np.float32), ("p0 / p1", "ff", np.float32), ("p0 - 1.5f", "f", np.float32),
+    ("fminf(p0, p1)", "ff", np.float32), ("fmaxf(p0, 0.0f)", "f", np.float32), ("fabsf(p0)", "f", np.float32),
+    ("sqrtf(fabsf(p0))", "f", np.float32), ("fmaf(p0, p1, p2)", "fff", np.float32),
+    ("f32(p0) > 0.0f ? p0 : p1", "bb", np.uint16),                     # a bf16 value can be selected as it is
+    ("bf16(fmaxf(f32(p0) + f32(p1), 0.0f))", "bb", np.uint16),
+]
+
+
+@pytest.mark.parametrize("expr,kinds,out_dtype", EXACT)
+def test_operator_is_bit_exact(cuda, expr, kinds, out_dtype):
+    rng = np.random.default_rng(len(expr) * 7 + len(kinds))
+    arrays = [inputs(rng, 5003, k) for k in kinds]    # 5003: full groups of eight and a ragged end
+    got, want = run_map(expr, arrays, cuda, out_dtype)
+    assert np.array_equal(got, want), expr
+
+
+def test_arithmetic_within_one_contraction_of_the_host(cuda):
+    # a product feeding a sum may be contracted into one fused multiply-add on the device (permitted per
+    # operation); the host evaluates with two roundings. 2 ulp of the result bounds the difference when
+    # the sum does not cancel (all terms positive here).
+    rng = np.random.default_rng(3)
+    x, y = rng.uniform(0.5, 4, 100003).astype(np.float32), rng.uniform(0.5, 4, 100003).astype(np.float32)
+    got, want = run_map("(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f) + p1 * p1", [x, y], cuda, np.float32)
+    assert ulp_distance(got, want).max() <= 2
+    got, want = run_map("c0 * p0 + c1 * p1", [x, y], cuda, np.float32, captures=(1.25, 0.75))
+    assert ulp_distance(got, want).max() <= 2
+
+
+BUILTINS = {
+    # name: (device expression, fp64 formula, operand ranges)
+    "expf": ("expf(p0)", lambda a: np.exp(a), [(-87.0, 88.0)]),
+    "logf": ("logf(p0)", lambda a: np.log(a), [(1e-30, 1e30)]),
+    "sqrtf": ("sqrtf(p0)", lambda a: np.sqrt(a), [(1e-30, 1e30)]),
+    "rsqrtf": ("rsqrtf(p0)", lambda a: 1.0 / np.sqrt(a), [(1e-30, 1e30)]),
+    "fabsf": ("fabsf(p0)", lambda a: np.abs(a), [(-1e30, 1e30)]),
+    "tanhf": ("tanhf(p0)", lambda a: np.tanh(a), [(-12.0, 12.0)]),
+    "sinf": ("sinf(p0)", lambda a: np.sin(a), [(-100.0, 100.0)]),
+    "cosf": ("cosf(p0)", lambda a: np.cos(a), [(-100.0, 100.0)]),
+    "fminf": ("fminf(p0, p1)", lambda a, b: np.minimum(a, b), [(-5.0, 5.0), (-5.0, 5.0)]),
+    "fmaxf": ("fmaxf(p0, p1)", lambda a, b: np.maximum(a, b), [(-5.0, 5.0), (-5.0, 5.0)]),
+    "fmaf": ("fmaf(p0, p1, p2)", lambda a, b, c: a * b + c, [(-5.0, 5.0), (-5.0, 5.0), (-5.0, 5.0)]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(BUILTINS))
+def test_fp32_map_within_2_ulp_of_fp64(cuda, name):
+    """fp32 maps: within 2 ulp -- every builtin of the vocabulary (internal/ir/builtins.go:25-39) through the
+    map-only path, against the fp64 value of the same formula rounded to fp32."""
+    expr, f64, ranges = BUILTINS[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    n = 1 << 20
+    arrays = []
+    for lo, hi in ranges:
+        if lo > 0 and hi / lo > 1e6:   # wide positive ranges: uniform in the exponent
+            arrays.append(np.exp(rng.uniform(np.log(lo), np.log(hi), n)).astype(np.float32))
+        else:
+            arrays.append(rng.uniform(lo, hi, n).astype(np.float32))
+    got = to_host(T.map([to_dev(a, cuda) for a in arrays], expr))
+    want = f64(*[a.astype(np.float64) for a in arrays]).astype(np.float32)
+    d = ulp_distance(got, want)
+    assert d.max() <= 2, (name, int(d.max()), arrays[0][int(d.argmax())])
+
+
+@pytest.mark.parametrize("shape", [(0,), (1,), (7,), (8,), (9,), (3, 5), (2, 3, 5, 7), (1025, 33), (64, 4096)])
+def test_shapes_ragged_ends_and_guard_bands(cuda, shape):
+    rng = np.random.default_rng(int(np.prod(shape)) + len(shape))
+    n = int(np.prod(shape))
+    x = rng.uniform(-3, 3, shape).astype(np.float32)
+    guard, canary = 64, -12345.0
+    buf = torch.full((n + 2 * guard,), canary, device=cuda)
+    out = buf[guard:guard + n].view(*shape)
+    T.map([to_dev(x, cuda)], "p0 * 2.0f - 1.0f", out=out)
+    b = buf.cpu().numpy()
+    assert (b[:guard] == canary).all() and (b[guard + n:] == canary).all(), "the kernel wrote outside its output"
+    want = x * np.float32(2.0) - np.float32(1.0)   # exact in fp32 with or without contraction (scaling by 2)
+    assert np.array_equal(b[guard:guard + n].reshape(shape), want)
+
+
+def test_pointers_aligned_to_their_element_only(cuda):
+    # operands that start 4 (2) bytes into a 16-byte vector take the single-element kernel
+    rng = np.random.default_rng(5)
+    n = 4099
+    x = rng.uniform(-3, 3, n).astype(np.float32)
+    base = torch.zeros(n + 1, device=cuda)
+    xd = base[1:]
+    xd.copy_(to_dev(x, cuda))
+    assert xd.data_ptr() % 16 == 4
+    got = T.map([xd], "fmaxf(p0, 0.0f)").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x, 0))
+    from oracle import binding as O
+    hb = O.f32_to_bf16(x)
+    bb = torch.zeros(n + 1, device=cuda, dtype=torch.bfloat16)
+    bd = bb[1:]
+    bd.copy_(to_dev(hb, cuda))
+    assert bd.data_ptr() % 16 == 2
+    got = T.map([bd], "f32(p0) * 0.5f", out_dtype=torch.float32).cpu().numpy()
+    assert np.array_equal(got, O.bf16_to_f32(hb) * np.float32(0.5))
+
+
+def test_ahead_of_time_and_compiled_lambdas_agree(cuda):
+    # "(p0 * c0) + c1" has an ahead-of-time kernel; the same arithmetic spelled with an extra exact step does not
+    rng = np.random.default_rng(6)
+    x = rng.uniform(-3, 3, (257, 129)).astype(np.float32)
+    xd = to_dev(x, cuda)
+    n0 = T.launch_count()
+    a = T.map([xd], "p0 * 3.0f + 0.5f").cpu().numpy()
+    b = T.map([xd], "(p0 * 3.0f + 0.5f) * 1.0f").cpu().numpy()
+    assert T.launch_count() - n0 == 2
+    assert ulp_distance(a, b).max() <= 1
+
+
+def test_type_errors_reach_the_caller(cuda):
+    x = torch.zeros((4, 4), device=cuda)
+    with pytest.raises(T.TcabError) as e:
+        T.map([x], "p0", out_dtype=torch.bfloat16)          # the store never converts
+    assert e.value.status == T._lib.ERR_DTYPE and "convert explicitly" in e.value.message
+    with pytest.raises(T.TcabError) as e:
+        T.map([x], "p0 * 2")                                 # f32 * i32
+    assert e.value.status == T._lib.ERR_INVALID_ARG and "operand types differ" in e.value.message
+    with pytest.raises(T.TcabError) as e:
+        T.map([x, torch.zeros((4, 5), device=cuda)], "p0 + p1")
+    assert e.value.status == T._lib.ERR_SHAPE
+
+
+# ----------------------------------------------------------------------------
+# typed operands inside reductions and contractions
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("shape,axis", [((37, 1000), 1), ((5, 300, 132), 1), ((3, 64), 1), ((2, 70000), 1), ((6, 50, 7), 1)])
+def test_reduction_over_bf16_and_integer_operands(cuda, shape, axis):
+    from oracle import binding as O
+    rng = np.random.default_rng(shape[-1])
+    xb = O.f32_to_bf16(rng.uniform(-1, 1, shape).astype(np.float32))
+    w = rng.uniform(-1, 1, shape).astype(np.float32)
+    k = rng.integers(0, 9, shape).astype(np.int32)
+    ax = axis if len(shape) == 3 else len(shape) - 1
+    got = T.chain_reduce([to_dev(xb, cuda), to_dev(w, cuda), to_dev(k, cuda)],
+                         "f32(p0) * p1 * (p2 % 3 == 0 ? 2.0f : 0.5f)", axis=ax).cpu().numpy()
+    terms = O.bf16_to_f32(xb).astype(np.float64) * w * np.where(k % 3 == 0, 2.0, 0.5)
+    assert (np.abs(got - terms.sum(ax)) <= 1e-5 * np.abs(terms).sum(ax) + 1e-30).all()
+    # max over a bf16 operand: order-independent, bit-exact
+    got = T.chain_reduce([to_dev(xb, cuda)], "f32(p0)", combine_expr="fmaxf(p0, p1)", init=-np.inf, axis=ax).cpu().numpy()
+    assert np.array_equal(got, O.bf16_to_f32(xb).max(ax))
+
+
+@pytest.mark.parametrize("m,k,n,nk", [(128, 64, 192, True), (70, 100, 36, False), (256, 512, 256, False), (33, 7, 5, True)])
+def test_contraction_over_bf16_operands(cuda, m, k, n, nk):
+    # testing/kernels/llm/qk_score.tca with bf16 storage: scores[m,n] = scale * sum_k q[m,k] * key[n,k], f32 accumulate
+    from oracle import binding as O
+    rng = np.random.default_rng(m + k + n)
+    q = O.f32_to_bf16(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    key = O.f32_to_bf16(rng.uniform(-1, 1, (n, k) if nk else (k, n)).astype(np.float32))
+    got = T.chain_contract(to_dev(q, cuda), to_dev(key, cuda), "f32(p0) * f32(p1)", rhs_is_nk=nk,
+                           post_expr="p0 * c0", captures=(0.125,)).cpu().numpy()
+    qf, kf = O.bf16_to_f32(q).astype(np.float64), O.bf16_to_f32(key).astype(np.float64)
+    want = 0.125 * (qf @ (kf.T if nk else kf))
+    mag = 0.125 * (np.abs(qf) @ np.abs(kf.T if nk else kf))
+    assert (np.abs(got - want) <= 1e-5 * mag + 1e-30).all()
+    # mixed: bf16 lhs, f32 rhs
+    kf32 = rng.uniform(-1, 1, (n, k) if nk else (k, n)).astype(np.float32)
+    got = T.chain_contract(to_dev(q, cuda), to_dev(kf32, cuda), "f32(p0) * p1", rhs_is_nk=nk).cpu().numpy()
+    want = qf @ (kf32.astype(np.float64).T if nk else kf32.astype(np.float64))
+    mag = np.abs(qf) @ np.abs(kf32.astype(np.float64).T if nk else kf32.astype(np.float64))
+    assert (np.abs(got - want) <= 1e-5 * mag + 1e-30).all()

@@ -952,40 +952,3 @@ def test_contraction_tile_sizes(oracle, cuda, tile):
         assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
     finally:
         T.tune("gemm")
-
-
-# ----------------------------------------------------------------------------
-# host buffers: H2D, kernel and D2H pipelined over row chunks
-# ----------------------------------------------------------------------------
-def test_row_pipeline_matches_direct_call(oracle, cuda):
-    from tcacomp_b200.pipeline import RowPipeline
-    rng = np.random.default_rng(8)
-    x = (4 * rng.normal(0, 1, (1000, 512))).astype(np.float32)   # 1000 rows in chunks of 96: a ragged last chunk
-    hx = torch.from_numpy(x).pin_memory()
-    hy = torch.full_like(hx, CANARY).pin_memory()
-    pipe = RowPipeline(cuda, 96, (512,), torch.float32, {"y": ((512,), torch.float32)}, depth=3)
-    for _ in range(2):  # twice: the staging slots are reused
-        pipe.run(hx, {"y": hy}, lambda din, dout: T.softmax_rows(din, out=dout["y"]))
-    torch.cuda.current_stream(cuda).synchronize()
-    direct = T.softmax_rows(hx.to(cuda)).cpu()
-    assert torch.equal(hy, direct)
-    # streaming: batches back to back without a join in between, different host buffers per batch, one join at the end
-    batches = [torch.from_numpy((4 * rng.normal(0, 1, (1000, 512))).astype(np.float32)).pin_memory() for _ in range(3)]
-    outs = [torch.full_like(b, CANARY).pin_memory() for b in batches]
-    for b, o in zip(batches, outs):
-        pipe.run(b, {"y": o}, lambda din, dout: T.softmax_rows(din, out=dout["y"]), join=False)
-    pipe.join()
-    torch.cuda.current_stream(cuda).synchronize()
-    for b, o in zip(batches, outs):
-        assert torch.equal(o, T.softmax_rows(b.to(cuda)).cpu())
-    # several outputs per chunk (outer-axis reduce over batch chunks)
-    t = rng.uniform(-100, 100, (10, 64, 96)).astype(np.float32)
-    ht = torch.from_numpy(t).pin_memory()
-    ho = {"sum": torch.empty((10, 96)).pin_memory(), "max": torch.empty((10, 96)).pin_memory(),
-          "argmax": torch.empty((10, 96), dtype=torch.int32).pin_memory()}
-    p2 = RowPipeline(cuda, 3, (64, 96), torch.float32, {"sum": ((96,), torch.float32), "max": ((96,), torch.float32),
-                                                      "argmax": ((96,), torch.int32)})
-    p2.run(ht, ho, lambda din, dout: T.reduce_outer(din, out=dout))
-    torch.cuda.current_stream(cuda).synchronize()
-    s, m, a = oracle.reduce_outer(t)
-    assert np.array_equal(ho["argmax"].numpy(), a) and np.array_equal(ho["max"].numpy(), m)
