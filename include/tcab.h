@@ -44,6 +44,7 @@ extern "C" {
 #define TCAB_MAX_RANK 4
 #define TCAB_MAX_INPUTS 4
 #define TCAB_MAX_CAPTURES 8
+#define TCAB_MAX_BATCH 32 /* problems tcab_chain_reduce_batched takes per call */
 #define TCAB_PIPELINE_MAX_OUTPUTS 3
 #define TCAB_NOALLOC_MAX_ROWS 4096 /* rows tcab_chain_reduce_noalloc accepts (its fixed scratch array) */
 
@@ -139,6 +140,20 @@ TCAB_API uint64_t tcab_launch_count(void);
 TCAB_API int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
                       uint32_t reduce_axis, const tcab_tensor* out, void* stream);
 
+/* tcab_chain_reduce over the INNERMOST axis for n_problems independent problems of ONE shape in one launch:
+ *   outs[b][...] = post( fold_k map(ins[b * n_ins + 0][..k], ins[b * n_ins + 1][..k], ...) ),  b = 0..n_problems-1.
+ * A lone small reduction is bounded by what a launch costs and by the wait for its predecessor on the stream,
+ * not by memory: a [4096, 1024] fp32 input is 2.6 us of HBM time on a B200, and a dependent launch adds more
+ * than a microsecond to it. A host that has several such problems (the rows of several layers, several
+ * requests) hands them over together; the rows of all problems are one pool of work for the grid. The
+ * reference's generated launcher takes one problem per call (internal/cg/cxx/launch.go:23-156).
+ * ins: n_problems * n_ins tensors, problem-major, all of the shape and (per operand position) element type of
+ * the first problem's; outs: n_problems f32 tensors with the operands' extents minus the innermost axis;
+ * n_problems <= TCAB_MAX_BATCH. Pointers travel as kernel arguments: nothing is allocated, and rows are not
+ * split over CTAs (long rows of few problems belong to tcab_chain_reduce). */
+TCAB_API int tcab_chain_reduce_batched(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,
+                                       uint32_t n_problems, const tcab_tensor* outs, void* stream);
+
 /* tcab_chain_reduce over the INNERMOST axis for callers that must not trigger a device allocation.
  * It has no counterpart in the reference. Who needs it: a host whose device memory is
  * already handed out in full (an embedding framework with its own arena, a serving process whose
@@ -165,7 +180,8 @@ TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tenso
                                        const tcab_tensor* out, void* stream);
 
 /* Compiles and loads, now, the kernels that the first tcab_chain_reduce (use = TCAB_USE_REDUCE),
- * tcab_chain_contract (use = TCAB_USE_CONTRACT, n_ins = 2) or tcab_map (use = TCAB_USE_MAP) with these lambdas
+ * tcab_chain_contract (use = TCAB_USE_CONTRACT, n_ins = 2), tcab_map (use = TCAB_USE_MAP) or
+ * tcab_chain_reduce_batched (use = TCAB_USE_REDUCE_BATCHED) with these lambdas
  * and operand element types (in_dtypes: n_ins tcab_dtype values, NULL = all f32; out_dtype: the stored type of
  * a map, ignored otherwise) would otherwise compile on its first call. The reference compiles every kernel ahead of time from its lambdas
  * (internal/cg/cxx/emit.go:85-190 prints the translation unit, the user runs nvcc); this is the same step
@@ -176,6 +192,7 @@ TCAB_API int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tenso
 #define TCAB_USE_REDUCE 0
 #define TCAB_USE_CONTRACT 1
 #define TCAB_USE_MAP 2
+#define TCAB_USE_REDUCE_BATCHED 3
 TCAB_API int tcab_chain_prepare(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use,
                                 int out_dtype);
 

@@ -15,11 +15,12 @@ MAX_RANK = 4
 MAX_INPUTS = 4
 MAX_CAPTURES = 8
 NOALLOC_MAX_ROWS = 4096
+MAX_BATCH = 32
 
 OK, ERR_INVALID_ARG, ERR_SHAPE, ERR_DTYPE, ERR_ALIGNMENT, ERR_UNSUPPORTED, ERR_CUDA, ERR_TOO_LARGE = range(8)
 F32, BF16, I32, U32 = 0, 1, 2, 3
 ACT_NONE, ACT_RELU = 0, 1
-USE_REDUCE, USE_CONTRACT, USE_MAP = 0, 1, 2
+USE_REDUCE, USE_CONTRACT, USE_MAP, USE_REDUCE_BATCHED = 0, 1, 2, 3
 
 
 class Tensor(C.Structure):
@@ -61,6 +62,8 @@ SYMBOLS = [
     ("tcab_abi_version", C.c_int, []),
     ("tcab_launch_count", C.c_uint64, []),
     ("tcab_chain_reduce", C.c_int,
+     [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
+    ("tcab_chain_reduce_batched", C.c_int,
      [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.c_uint32, C.POINTER(Tensor), C.c_void_p]),
     ("tcab_chain_reduce_noalloc", C.c_int,
      [C.POINTER(Chain), C.POINTER(Tensor), C.c_uint32, C.POINTER(Tensor), C.c_void_p]),

@@ -279,7 +279,7 @@ int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dt
   PreparedChain& pc = *pcp;
   if (chain == nullptr || chain->map_expr == nullptr)
     return fail(TCAB_ERR_INVALID_ARG, "%s: chain and map_expr are required", op);
-  if (use != TCAB_USE_REDUCE && use != TCAB_USE_CONTRACT && use != TCAB_USE_MAP)
+  if (use != TCAB_USE_REDUCE && use != TCAB_USE_CONTRACT && use != TCAB_USE_MAP && use != TCAB_USE_REDUCE_BATCHED)
     return fail(TCAB_ERR_INVALID_ARG, "%s: unknown use %d", op, use);
   if (use != TCAB_USE_MAP && chain->combine_expr == nullptr) return fail(TCAB_ERR_INVALID_ARG, "%s: combine_expr is required", op);
   if (chain->n_captures > TCAB_MAX_CAPTURES)
@@ -292,8 +292,10 @@ int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dt
     types[i] = in_dtypes[i];
   }
   if (use == TCAB_USE_MAP && (out_dtype < TCAB_F32 || out_dtype > TCAB_U32)) return fail(TCAB_ERR_DTYPE, "%s: out_dtype is not a tcab_dtype", op);
-  return prepare_chain(chain, n_ins, &pc, use == TCAB_USE_MAP ? 'M' : use == TCAB_USE_CONTRACT ? 'C' : 'R', types,
-                       use == TCAB_USE_MAP ? out_dtype : TCAB_F32);
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, use == TCAB_USE_MAP ? 'M' : use == TCAB_USE_CONTRACT ? 'C' : 'R', types,
+                         use == TCAB_USE_MAP ? out_dtype : TCAB_F32));
+  if (use == TCAB_USE_REDUCE_BATCHED) pc.spec.kind = 'B';
+  return TCAB_OK;
 }
 }  // namespace
 
@@ -435,6 +437,51 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   return launch_chain_reduce(pc, ptrs, count(t, 0, reduce_axis), t->dims[reduce_axis],
                              count(t, reduce_axis + 1, t->rank), static_cast<float*>(out->data),
                              static_cast<cudaStream_t>(stream));
+}
+
+int tcab_chain_reduce_batched(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, uint32_t n_problems,
+                              const tcab_tensor* outs, void* stream) {
+  const char* op = "chain_reduce_batched";
+  if (chain == nullptr || chain->map_expr == nullptr || chain->combine_expr == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: chain, map_expr and combine_expr are required", op);
+  if (chain->n_captures > TCAB_MAX_CAPTURES)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
+  if (ins == nullptr || outs == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
+    return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands per problem are required", op, TCAB_MAX_INPUTS);
+  if (n_problems < 1 || n_problems > TCAB_MAX_BATCH)
+    return fail(TCAB_ERR_TOO_LARGE, "%s: %u problems (between 1 and %d per call)", op, n_problems, TCAB_MAX_BATCH);
+  const float* ptrs[TCAB_MAX_BATCH * TCAB_MAX_INPUTS] = {};
+  float* optrs[TCAB_MAX_BATCH] = {};
+  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  const tcab_tensor* t0 = &ins[0];
+  for (uint32_t b = 0; b < n_problems; ++b) {
+    for (uint32_t i = 0; i < n_ins; ++i) {
+      const tcab_tensor* t = &ins[b * n_ins + i];
+      char name[32];
+      std::snprintf(name, sizeof(name), "ins[%u][%u]", b, i);
+      TCAB_TRY(check_tensor(op, name, t));
+      TCAB_TRY(need_operand_dtype(op, name, t));
+      if (!same_shape(t0, t)) return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0][0]", op, name);
+      if (b == 0) types[i] = t->dtype;
+      else if (t->dtype != types[i]) return fail(TCAB_ERR_DTYPE, "%s: %s must have the element type of ins[0][%u]", op, name, i);
+      ptrs[b * n_ins + i] = static_cast<const float*>(t->data);
+    }
+    const tcab_tensor* o = &outs[b];
+    char name[32];
+    std::snprintf(name, sizeof(name), "outs[%u]", b);
+    TCAB_TRY(check_tensor(op, name, o));
+    TCAB_TRY(need_dtype(op, name, o, TCAB_F32, "f32"));
+    TCAB_TRY(need_elem_align(op, name, o, 4));
+    bool ok = t0->rank == 1 ? (o->rank == 1 && o->dims[0] == 1) : o->rank == t0->rank - 1;
+    for (uint32_t i = 0; ok && t0->rank > 1 && i + 1 < t0->rank; ++i) ok = o->dims[i] == t0->dims[i];
+    if (!ok) return fail(TCAB_ERR_SHAPE, "%s: %s must have the operands' extents without the innermost axis", op, name);
+    optrs[b] = static_cast<float*>(o->data);
+  }
+  PreparedChain pc;
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types));
+  TCAB_TRY(have_device(op));
+  return launch_chain_reduce_batched(pc, ptrs, optrs, n_problems, static_cast<uint32_t>(count(t0, 0, t0->rank - 1)),
+                                     t0->dims[t0->rank - 1], static_cast<cudaStream_t>(stream));
 }
 
 int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins,

@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kSlots
 };
 
 struct JitChain {
@@ -138,11 +138,16 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
       for (int t = 0; t < 4; ++t)
         names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
                                                       std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ">";
+    names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024>";
     names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4, " + bf + ">";
     names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1, " + bf + ">";
     names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
     names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
     names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + ">";
+  } else if (sp.kind == 'B') {
+    const char* shapes[4] = {"32, 4", "256, 4", "32, 1", "256, 1"};
+    for (int i = 0; i < 4; ++i)
+      names[kBatch32V4 + i] = "tcabk::chain_inner_batched<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + shapes[i] + ", " + bf + ">";
   } else if (sp.kind == 'C') {
     names[kContractKN] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 0, 4, " + bf + ">";
     names[kContractNK] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 4, " + bf + ">";
@@ -279,10 +284,12 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
     }
     const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec < 1024 ? 2 : 3;  // the same thresholds as the ahead-of-time path
     const int tpr = t == 0 ? 1 : t == 1 ? 4 : t == 2 ? 32 : 256;
-    const int threads = tpr > 128 ? tpr : 128;
+    const bool big = vec && t == 2 && inner_wants_big_ctas(outer);        // small problems: 1024-thread CTAs
+    const int threads = big ? 1024 : tpr > 128 ? tpr : 128;
     const uint64_t groups = threads / tpr;
     void* a[] = {ptrs, &out, &outer, &nk, &init, &caps};
-    return launch(jc->k[(vec ? kInner1V4 : kInner1V1) + t], (outer + groups - 1) / groups, threads, a, s, "chain_inner");
+    return launch(big ? jc->k[kInner32V4Big] : jc->k[(vec ? kInner1V4 : kInner1V1) + t], (outer + groups - 1) / groups, threads, a,
+                  s, "chain_inner");
   }
   if (inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
   const bool vec = al && (inner % 4 == 0);
@@ -305,6 +312,30 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   uint32_t rows32 = nb * nc;
   void* a2[] = {&split_scratch_or_null, &out, &rows32, &ksplit, &init, &caps};
   return launch(jc->k[kFinish], (rows32 + 127) / 128, 128, a2, s, "chain_split_finish");
+}
+
+int jit_launch_batched(void* handle, const float* const* ins, float* const* outs, uint32_t nprob, uint32_t rows, uint32_t nk,
+                       float init, const float* caps16, cudaStream_t s) {
+  JitChain* jc = static_cast<JitChain*>(handle);
+  if (jc->kind != 'B') return fail(TCAB_ERR_INVALID_ARG, "chain_reduce_batched: the chain was prepared for another use");
+  tcabk::Caps caps;
+  for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
+  // BatchPtrs<NIN>: kMaxBatch rows of NIN input pointers, then kMaxBatch output pointers
+  const void* flat[tcabk::kMaxBatch * TCAB_MAX_INPUTS + tcabk::kMaxBatch] = {};
+  bool al = true;
+  for (uint32_t b = 0; b < nprob; ++b)
+    for (int i = 0; i < jc->n_in; ++i) {
+      flat[b * jc->n_in + i] = ins[b * jc->n_in + i];
+      al = al && aligned16(ins[b * jc->n_in + i]);
+    }
+  for (uint32_t b = 0; b < nprob; ++b) flat[tcabk::kMaxBatch * jc->n_in + b] = outs[b];
+  const bool vec = al && (nk % 4 == 0);
+  const uint32_t nvec = vec ? nk / 4 : nk;
+  const bool cta_per_row = nvec >= 1024;
+  const uint64_t total = static_cast<uint64_t>(nprob) * rows;
+  void* a[] = {flat, &nprob, &rows, &nk, &init, &caps};
+  return launch(jc->k[(vec ? kBatch32V4 : kBatch32V1) + (cta_per_row ? 1 : 0)], cta_per_row ? total : (total + 7) / 8, 256, a, s,
+                "chain_inner_batched");
 }
 
 int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, const float* caps16, cudaStream_t s) {

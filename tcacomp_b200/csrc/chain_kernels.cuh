@@ -145,14 +145,51 @@ __device__ __forceinline__ float lanes_allreduce(float v) {
 
 __host__ __device__ constexpr int inner_cta_threads(int tpr) { return tpr > 128 ? tpr : 128; }
 
+// One thread's share of a row: vectors t, t + TPR, ... of the nvec vectors that start at vector index vbase.
+template <class Map, class C, int NIN, int TPR, int V, int BF>
+__device__ __forceinline__ float fold_row_share(const float* const* p, u64 vbase, u32 nvec, int t, const float* caps) {
+  float acc = C::identity();
+#pragma unroll 8
+  for (u32 idx = t; idx < nvec; idx += TPR) {
+    float f[NIN][V];
+    LoadAll<V, BF, NIN>::at(p, vbase + idx, f);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      float v[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) v[a] = f[a][j];
+      acc = C::apply(acc, Map::apply(v, caps));
+    }
+  }
+  return acc;
+}
+
+// The partials of the TPR threads of a row group meet: every thread returns the row's fold. `slots` is
+// 2 x 32 floats of shared memory, alternated by `iter` so that a slot is rewritten only after everyone read it.
+template <class C, int TPR>
+__device__ __forceinline__ float fold_row_group(float acc, float (*slots)[32], u32 iter) {
+  if constexpr (TPR > 1 && TPR <= 32) {
+    acc = lanes_allreduce<C, TPR>(acc);
+  } else if constexpr (TPR > 32) {
+    constexpr int NW = TPR / 32;
+    float* sl = slots[iter & 1];
+    acc = lanes_allreduce<C, 32>(acc);
+    if ((threadIdx.x & 31) == 0) sl[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    acc = lanes_allreduce<C, NW>(sl[threadIdx.x & (NW - 1)]);
+  }
+  return acc;
+}
+
 // Reduce over the INNERMOST axis: operands are [rows, nk]; a group of TPR
 // threads folds one row. TPR == 1 is a plain sequential ascending fold per
-// thread (bit-identical to the reference's SeqReducer order).
-template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0>
-__global__ void __launch_bounds__(inner_cta_threads(TPR))
+// thread (bit-identical to the reference's SeqReducer order). THREADS is the CTA size: 128 (256 for a CTA
+// per row) by default; small problems take 1024-thread CTAs, because a launch costs by the CTA (measured in a
+// graph of dependent launches: an empty grid of 1024 x 128 threads 1.7 us, of 148 x 1024 threads 0.8 us).
+template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0, int THREADS = inner_cta_threads(TPR)>
+__global__ void __launch_bounds__(THREADS)
 chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
   typedef Comb<COMBINE> C;
-  constexpr int THREADS = inner_cta_threads(TPR);
   constexpr int GROUPS = THREADS / TPR;
   __shared__ float slots[2][32];
 
@@ -184,35 +221,53 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
        row0 += static_cast<u64>(gridDim.x) * GROUPS, ++iter) {
     const u64 row = row0 + g;
     const bool live = row < rows;
-    const u64 vbase = row * nvec;  // first vector of the row (nk % V == 0)
     float acc = C::identity();
-    if (live) {
-#pragma unroll 8
-      for (u32 idx = t; idx < nvec; idx += TPR) {
-        float f[NIN][V];
-        LoadAll<V, BF, NIN>::at(ins.p, vbase + idx, f);
-#pragma unroll
-        for (int j = 0; j < V; ++j) {
-          float p[NIN];
-#pragma unroll
-          for (int a = 0; a < NIN; ++a) p[a] = f[a][j];
-          acc = C::apply(acc, Map::apply(p, caps.c));
-        }
-      }
-    }
-    if constexpr (TPR > 1 && TPR <= 32) {
-      acc = lanes_allreduce<C, TPR>(acc);
-    } else if constexpr (TPR > 32) {
-      constexpr int NW = TPR / 32;
-      float* sl = slots[iter & 1];  // alternate: a slot is rewritten only after everyone read it
-      acc = lanes_allreduce<C, 32>(acc);
-      if ((threadIdx.x & 31) == 0) sl[threadIdx.x >> 5] = acc;
-      __syncthreads();
-      acc = lanes_allreduce<C, NW>(sl[threadIdx.x & (NW - 1)]);
-    }
+    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF>(ins.p, row * nvec, nvec, t, caps.c);  // nk % V == 0
+    acc = fold_row_group<C, TPR>(acc, slots, iter);
     if (live && t == 0) {
       float r[1] = {C::apply(init, acc)};
       out[row] = Post::apply(r, caps.c + 8);
+    }
+  }
+}
+
+// Several problems of ONE shape in one launch: problem b has operands ins.in[b][*] of [rows, nk] and output
+// ins.out[b] of [rows]. A lone small reduction is bounded by what a launch costs and by the wait for its
+// predecessor on the stream, not by memory (a [4096, 1024] fp32 input is 2.6 us of HBM time; a dependent launch
+// adds more than a microsecond to it); a host that has many of them hands them over together, and the rows
+// of all problems are one pool of work for the grid. The reference's launcher takes one problem per call
+// (internal/cg/cxx/launch.go:23-156).
+constexpr int kMaxBatch = 32;
+template <int NIN>
+struct BatchPtrs {
+  const float* in[kMaxBatch][NIN];
+  float* out[kMaxBatch];
+};
+
+template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0>
+__global__ void __launch_bounds__(256)
+chain_inner_batched(BatchPtrs<NIN> ins, u32 nprob, u32 rows, u32 nk, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  constexpr int GROUPS = 256 / TPR;
+  __shared__ float slots[2][32];
+  const int g = threadIdx.x / TPR;
+  const int t = threadIdx.x % TPR;
+  const u32 nvec = nk / V;
+  const u64 total = static_cast<u64>(nprob) * rows;
+  u32 iter = 0;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (u64 row0 = static_cast<u64>(blockIdx.x) * GROUPS; row0 < total; row0 += static_cast<u64>(gridDim.x) * GROUPS, ++iter) {
+    const u64 gr = row0 + g;
+    const bool live = gr < total;
+    const u32 b = live ? static_cast<u32>(gr / rows) : 0u;
+    const u64 row = live ? gr % rows : 0;
+    float acc = C::identity();
+    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF>(ins.in[b], row * nvec, nvec, t, caps.c);
+    acc = fold_row_group<C, TPR>(acc, slots, iter);
+    if (live && t == 0) {
+      float r[1] = {C::apply(init, acc)};
+      ins.out[b][row] = Post::apply(r, caps.c + 8);
     }
   }
 }

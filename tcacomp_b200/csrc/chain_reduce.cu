@@ -97,6 +97,11 @@ void plan_outer_ranges(uint32_t wanted, uint32_t nk, uint32_t* ranges, uint32_t*
   *ranges = (nk + *klen - 1) / *klen;
 }
 
+// Rows folded by a warp each on a problem so small that all its CTAs are resident at once: 1024-thread CTAs.
+// A launch costs by the CTA, and a small launch is bounded by exactly that cost (a [4096, 1024] input: 3.65 us
+// per launch with 1024 CTAs of 128 threads, 3.33 us with 128 CTAs of 1024).
+bool inner_wants_big_ctas(uint64_t rows) { return rows >= 64 && rows <= static_cast<uint64_t>(sm_count()) * 64; }
+
 namespace {
 
 struct Args {
@@ -110,12 +115,11 @@ struct Args {
   cudaStream_t stream;
 };
 
-template <class Map, class Post, int COMBINE, int TPR, int V>
+template <class Map, class Post, int COMBINE, int TPR, int V, int THREADS = tcabk::inner_cta_threads(TPR)>
 int launch_inner(const Args& a) {
   constexpr int NIN = Map::kIn;
-  constexpr int THREADS = tcabk::inner_cta_threads(TPR);
   constexpr int GROUPS = THREADS / TPR;
-  auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V>;
+  auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V, 0, THREADS>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
   // one CTA per group of rows; the kernel's row loop only matters beyond 2^31 - 1 CTAs
@@ -235,7 +239,9 @@ int launch_chain(const Args& a) {
       switch (tpr) {
         case 1: return launch_inner<Map, Post, COMBINE, 1, 4>(a);
         case 4: return launch_inner<Map, Post, COMBINE, 4, 4>(a);
-        case 32: return launch_inner<Map, Post, COMBINE, 32, 4>(a);
+        case 32:
+          if (inner_wants_big_ctas(a.outer) && tn.p2 != 3) return launch_inner<Map, Post, COMBINE, 32, 4, 1024>(a);
+          return launch_inner<Map, Post, COMBINE, 32, 4>(a);
         default: return launch_inner<Map, Post, COMBINE, 256, 4>(a);
       }
     }
@@ -249,6 +255,59 @@ int launch_chain(const Args& a) {
   if (a.inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
   const bool vec = al && (a.inner % 4 == 0);
   return vec ? launch_outer<Map, Post, COMBINE, 4>(a) : launch_outer<Map, Post, COMBINE, 1>(a);
+}
+
+// Several problems of one shape in one launch (chain_inner_batched): a warp per row below 1024 vectors, a CTA per
+// row from there.
+struct BatchArgs {
+  const float* const* ins;   // [nprob][n_in]
+  float* const* outs;        // [nprob]
+  uint32_t nprob;
+  uint32_t rows, nk;
+  float init;
+  Caps caps;
+  cudaStream_t stream;
+};
+
+template <class Map, class Post, int COMBINE>
+int launch_batched(const BatchArgs& a) {
+  constexpr int NIN = Map::kIn;
+  tcabk::BatchPtrs<NIN> ptrs = {};
+  bool al = true;
+  for (uint32_t b = 0; b < a.nprob; ++b) {
+    for (int i = 0; i < NIN; ++i) {
+      ptrs.in[b][i] = a.ins[b * NIN + i];
+      al = al && aligned16(ptrs.in[b][i]);
+    }
+    ptrs.out[b] = a.outs[b];
+  }
+  const bool vec = al && (a.nk % 4 == 0);
+  const uint32_t nvec = vec ? a.nk / 4 : a.nk;
+  const bool cta_per_row = nvec >= 1024;
+  const uint64_t total = static_cast<uint64_t>(a.nprob) * a.rows;
+  const uint64_t need = cta_per_row ? total : (total + 7) / 8;
+  const unsigned grid = static_cast<unsigned>(need > 0x7fffffffull ? 0x7fffffffull : need);
+  void (*fn)(tcabk::BatchPtrs<NIN>, uint32_t, uint32_t, uint32_t, float, Caps) =
+      vec ? (cta_per_row ? tcabk::chain_inner_batched<Map, Post, COMBINE, NIN, 256, 4>
+                         : tcabk::chain_inner_batched<Map, Post, COMBINE, NIN, 32, 4>)
+          : (cta_per_row ? tcabk::chain_inner_batched<Map, Post, COMBINE, NIN, 256, 1>
+                         : tcabk::chain_inner_batched<Map, Post, COMBINE, NIN, 32, 1>);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(256);
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tune(kReduceInner).p2 == 2 ? 0 : 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, ptrs, a.nprob, a.rows, a.nk, a.init, a.caps);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "chain_inner_batched: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
 }
 
 // The split path on a scratch buffer the caller of this function provides (used by the entry point
@@ -272,14 +331,15 @@ struct Entry {
   int n_in;
   int (*launch)(const Args&);
   int (*launch_noalloc)(const Args&, float* scratch, uint32_t splits);  // split path on caller-free scratch
+  int (*launch_batched)(const BatchArgs&);                              // several problems of one shape in one launch
 };
 
 #define TCAB_ENTRY(MAP, POST, COMBINE)                                            \
   { MAP::text(), POST::text(), COMBINE, MAP::kIn, &launch_chain<MAP, POST, COMBINE>, \
-    &launch_split_on<MAP, POST, COMBINE> }
+    &launch_split_on<MAP, POST, COMBINE>, &launch_batched<MAP, POST, COMBINE> }
 #define TCAB_ENTRY_NOPOST(MAP, COMBINE)                                                  \
   { MAP::text(), "", COMBINE, MAP::kIn, &launch_chain<MAP, tcabk::PostNone, COMBINE>,    \
-    &launch_split_on<MAP, tcabk::PostNone, COMBINE> }
+    &launch_split_on<MAP, tcabk::PostNone, COMBINE>, &launch_batched<MAP, tcabk::PostNone, COMBINE> }
 
 const Entry kTable[] = {
     TCAB_ENTRY_NOPOST(MapIdent, 0),    TCAB_ENTRY_NOPOST(MapIdent, 1),    TCAB_ENTRY_NOPOST(MapIdent, 2),
@@ -440,6 +500,22 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
   Args a{ins, out, outer, nk, inner, pc.init, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
   return kTable[pc.entry].launch(a);
+}
+
+int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,
+                                uint32_t rows, uint32_t nk, cudaStream_t s) {
+  if (nprob == 0 || rows == 0) return TCAB_OK;
+  if (pc.entry == kJitEntry) {
+    JitSpec sp = pc.spec;
+    sp.kind = 'B';
+    void* h = nullptr;
+    const int rc = jit_prepare(sp, &h);
+    if (rc != TCAB_OK) return rc;
+    return jit_launch_batched(h, ins, outs, nprob, rows, nk, pc.init, pc.caps, s);
+  }
+  BatchArgs a{ins, outs, nprob, rows, nk, pc.init, {}, s};
+  for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
+  return kTable[pc.entry].launch_batched(a);
 }
 
 int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, cudaStream_t s) {

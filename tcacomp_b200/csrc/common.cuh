@@ -71,8 +71,8 @@ int launch_layernorm_rows_f32(const float* x, const float* gamma, const float* b
                               float* y, uint64_t rows, uint32_t cols, cudaStream_t s);
 int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb,
                         uint32_t nk, uint32_t nc, cudaStream_t s);
-// What the run-time compiler needs to know about a chain: which kernels ('R' the reduction kernels, 'C' the
-// contraction kernels, 'M' the map-only kernels), the canonical lambdas and the element types.
+// What the run-time compiler needs to know about a chain: which kernels ('R' the reduction kernels, 'B' the
+// batched reduction kernels, 'C' the contraction kernels, 'M' the map-only kernels), the canonical lambdas and the element types.
 struct JitSpec {
   char kind = 'R';
   int n_in = 0, combine = 0;
@@ -113,12 +113,17 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
                          cudaStream_t s);
 
 int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
+int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,
+                                uint32_t rows, uint32_t nk, cudaStream_t s);  // ins: [nprob][n_in]
+int jit_launch_batched(void* handle, const float* const* ins, float* const* outs, uint32_t nprob, uint32_t rows, uint32_t nk,
+                       float init, const float* caps16, cudaStream_t s);
 int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins, uint64_t rows, uint32_t nk,
                                 float* out, cudaStream_t s);
 int jit_launch_contract(void* handle, const float* lhs, const float* rhs, int rhs_nk, float* out, uint32_t m,
                         uint32_t n, uint32_t k, float init, const float* caps16, cudaStream_t s);
 uint32_t choose_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident);  // chain_outer k ranges
 uint32_t plan_outer_splits(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident, int sms, int forced);
+bool inner_wants_big_ctas(uint64_t rows);  // chain_inner: 1024-thread CTAs for problems whose CTAs are all resident at once
 void plan_outer_ranges(uint32_t wanted, uint32_t nk, uint32_t* ranges, uint32_t* klen);  // ranges that cover [0, nk), none empty
 bool contract_big_tiles(uint32_t m, uint32_t n);  // tile choice of the fp32 contraction (tune "gemm" p2 = 4 / 8 forces it)
 int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float* rhs, int rhs_nk, float* out,

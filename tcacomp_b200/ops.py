@@ -97,7 +97,8 @@ def chain_prepare(map_expr: str, n_ins: int = 1, combine_expr: str = "(p0 + p1)"
     "map") with these lambdas and operand types would compile later (nothing to do for lambdas with an
     ahead-of-time kernel). Not during a stream capture."""
     chain = _chain(map_expr, combine_expr, post_expr, 0.0, captures)
-    code = {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP}[use]
+    code = {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP,
+            "reduce_batched": _lib.USE_REDUCE_BATCHED}[use]
     types = None
     if in_dtypes is not None:
         if len(in_dtypes) != n_ins:
@@ -217,6 +218,34 @@ def map(ins: Sequence[torch.Tensor], map_expr: str, captures: Sequence[float] = 
     with _on_device(ins[0]):
         _lib.check(_lib.load().tcab_map(C.byref(chain), arr, len(ins), C.byref(ov), _stream(stream, ins[0])))
     return out
+
+
+def chain_reduce_batched(problems: Sequence[Sequence[torch.Tensor]], map_expr: str, outs: Optional[Sequence[torch.Tensor]] = None,
+                         combine_expr: str = "(p0 + p1)", init: float = 0.0, post_expr: Optional[str] = None,
+                         captures: Sequence[float] = (), stream: Optional[torch.cuda.Stream] = None) -> list:
+    """chain_reduce over the innermost axis for several independent problems of one shape in ONE launch.
+
+    problems[b] lists the operands of problem b; outs[b] receives its result. At most `_lib.MAX_BATCH`
+    problems per call. For many small reductions, whose cost is the launch and not the memory."""
+    problems = [list(p) for p in problems]
+    n_ins = len(problems[0])
+    if not 1 <= n_ins <= _lib.MAX_INPUTS or any(len(p) != n_ins for p in problems):
+        raise ValueError(f"every problem takes the same 1..{_lib.MAX_INPUTS} operands")
+    if not 1 <= len(problems) <= _lib.MAX_BATCH:
+        raise ValueError(f"between 1 and {_lib.MAX_BATCH} problems per call")
+    t0 = problems[0][0]
+    if outs is None:
+        outs = [torch.empty(list(t0.shape[:-1]) or [1], device=t0.device, dtype=torch.float32) for _ in problems]
+    outs = list(outs)
+    chain = _chain(map_expr, combine_expr, post_expr, init, captures)
+    flat = [t for p in problems for t in p]
+    arr = (_lib.Tensor * len(flat))(*[_view(t, f"ins[{i // n_ins}][{i % n_ins}]") for i, t in enumerate(flat)])
+    oarr = (_lib.Tensor * len(outs))(*[_view(t, f"outs[{i}]") for i, t in enumerate(outs)])
+    _same_device(*[(f"operand {i}", t) for i, t in enumerate(flat)], *[(f"outs[{i}]", t) for i, t in enumerate(outs)])
+    with _on_device(t0):
+        _lib.check(_lib.load().tcab_chain_reduce_batched(C.byref(chain), arr, n_ins, len(problems), oarr,
+                                                         _stream(stream, t0)))
+    return outs
 
 
 def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.Tensor,

@@ -198,6 +198,8 @@ TYPED_OK = [
     (b"u32(p0) < 5u ? f32(p0) : fabsf(f32(p0))", [I], "map", F),
     (b"f32(p0) * p1", [B, F], "reduce", F),                                     # bf16 operand widened inside a reduction
     (b"(p0 % 3 == 0 ? 2.0f : 0.5f) * p1", [I, F], "reduce", F),
+    (b"sinf(p0) * f32(p1)", [F, B], "reduce_batched", F),                       # several problems in one launch
+    (b"f32(p0) * f32(p1)", [B, B], "contract", F),                              # bf16 operands of a contraction
 ]
 TYPED_BAD = [
     (b"p0 * 2", [F], "map", F, b"operand types differ"),                         # no implicit promotion
@@ -220,7 +222,8 @@ TYPED_BAD = [
 
 def _use(name):
     from tcacomp_b200 import _lib
-    return {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP}[name]
+    return {"reduce": _lib.USE_REDUCE, "contract": _lib.USE_CONTRACT, "map": _lib.USE_MAP,
+            "reduce_batched": _lib.USE_REDUCE_BATCHED}[name]
 
 
 @pytest.mark.parametrize("expr,types,use,out", TYPED_OK)

@@ -952,3 +952,65 @@ def test_contraction_tile_sizes(oracle, cuda, tile):
         assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
     finally:
         T.tune("gemm")
+
+
+# ----------------------------------------------------------------------------
+# several problems of one shape in one launch
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("nprob,rows,cols", [(16, 4096, 1024), (1, 5, 7), (3, 33, 130), (32, 17, 64), (2, 3, 9000), (5, 2, 4096)])
+def test_batched_row_reductions_match_single_launches(oracle, cuda, nprob, rows, cols):
+    from oracle import checks
+    rng = np.random.default_rng(nprob * 7 + rows + cols)
+    xs = [rng.uniform(-1, 1, (rows, cols)).astype(np.float32) for _ in range(nprob)]
+    xd = [dev_f32(x, cuda) for x in xs]
+    bufs = [guarded((rows,), torch.float32, cuda) for _ in range(nprob)]
+    n0 = T.launch_count()
+    T.chain_reduce_batched([[x] for x in xd], "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)", outs=[o for _, o in bufs])
+    assert T.launch_count() - n0 == 1
+    for x, (buf, out) in zip(xs, bufs):
+        check_guards(buf, torch.float32)
+        assert checks.rowsum_close(out.cpu().numpy(), x)
+    # two operands, a compiled lambda, max combiner with init, piped map
+    zs = [rng.uniform(-1, 1, (rows, cols)).astype(np.float32) for _ in range(nprob)]
+    zd = [dev_f32(z, cuda) for z in zs]
+    got = T.chain_reduce_batched([[x, z] for x, z in zip(xd, zd)], "sinf(p0) * p1", post_expr="p0 * 0.5f + 1.0f")
+    for x, z, g in zip(xs, zs, got):
+        want = 0.5 * (np.sin(x.astype(np.float64)) * z).sum(1) + 1.0
+        assert (np.abs(g.cpu().numpy() - want) <= 1e-5 * (0.5 * np.abs(np.sin(x.astype(np.float64)) * z).sum(1) + 1.0)).all()
+    got = T.chain_reduce_batched([[x] for x in xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.25)
+    for x, g in zip(xs, got):
+        assert np.array_equal(g.cpu().numpy(), np.maximum(x.max(1), np.float32(0.25)))
+    # bit-identical to the single-problem entry on the same shapes (same kernels' fold order per row)
+    single = T.chain_reduce([xd[0]], "p0").cpu().numpy()
+    batched = T.chain_reduce_batched([[xd[0]]], "p0")[0].cpu().numpy()
+    assert (np.abs(single - batched) <= 1e-5 * np.abs(xs[0]).sum(1)).all()
+
+
+def test_batched_arguments_are_validated(cuda):
+    x = torch.zeros((4, 8), device=cuda)
+    with pytest.raises(ValueError):
+        T.chain_reduce_batched([[x]] * 33, "p0")
+    with pytest.raises(T.TcabError) as e:
+        T.chain_reduce_batched([[x], [torch.zeros((4, 9), device=cuda)]], "p0")
+    assert e.value.status == T._lib.ERR_SHAPE
+    with pytest.raises(T.TcabError) as e:
+        T.chain_reduce_batched([[x]], "p0", outs=[torch.zeros((5,), device=cuda)])
+    assert e.value.status == T._lib.ERR_SHAPE
+
+
+def test_small_problems_take_big_ctas_and_agree(oracle, cuda):
+    # rows that fit the GPU at once are folded by 1024-thread CTAs (32 rows each); the tuning hook p2 = 3 keeps the
+    # 128-thread shape: both must give the same sums (same warp-per-row fold)
+    rng = np.random.default_rng(21)
+    for rows, cols in [(4096, 1024), (64, 512), (9000, 260), (100, 4000)]:
+        x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+        xd = dev_f32(x, cuda)
+        a = T.chain_reduce([xd], "p0 * p0").cpu().numpy()
+        try:
+            T.tune("reduce_inner", 0, 0, 3, 0)
+            b = T.chain_reduce([xd], "p0 * p0").cpu().numpy()
+        finally:
+            T.tune("reduce_inner")
+        assert np.array_equal(a, b)
+        assert (np.abs(a - (x.astype(np.float64) ** 2).sum(1)) <= 1e-5 * (x.astype(np.float64) ** 2).sum(1)).all()
+
