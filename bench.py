@@ -321,7 +321,7 @@ class MapRowsum(Workload):
              "and the wait for its predecessor, and L2-resident when repeated; see roofline.one_launch_each and "
              "roofline.as_specified)")
     EXPR = "(0.5f*p0 + 0.25f) * (0.5f*p0 + 0.25f)"
-    profile = "chain_inner_map_rowsum_f32_4096x1024.md"
+    profile = "chain_inner_batched_map_rowsum_f32_4096x1024.md"
 
     def work(self):
         return self.copies * (self.units * self.cols * 4.0 + self.units * 4)
