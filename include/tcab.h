@@ -129,6 +129,11 @@ TCAB_API uint64_t tcab_launch_count(void);
  * All operands: same rank (1..4) and extents, each f32, bf16, i32 or u32 (the map lambda sees each with its
  * own type and must yield f32). `out` is fp32 with the operands' extents minus the reduced axis (a rank-1
  * operand gives a rank-1 output of extent 1).
+ * Operands that bind a subset of the iteration axes (the reference's structural indexing admits x[i] inside an
+ * (i, j) iteration, pkg/chain.go checkOperand -- this is how a later statement reads a Local such as a row
+ * maximum, pkg/local_test.go:17-68): when the reduced axis is the innermost one, an operand may have extent 1
+ * along the innermost axis (one value per row) or extent 1 along every other axis (one row shared by all
+ * rows: a bias, gamma, beta). Such chains are compiled at run time; their rows are never split over CTAs.
  * reduce_axis == rank-1 selects the innermost-axis kernel, any other axis the outer-axis kernel.
  * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative.
  * Allocation: when there are fewer rows than SMs and the rows are long, a row is split over several
@@ -203,6 +208,9 @@ TCAB_API int tcab_chain_prepare(const tcab_chain* chain, const int32_t* in_dtype
  * TensorView::Get / Set pair (runtime/tca/view.h:104-112) of a map statement.
  * ins: 1..TCAB_MAX_INPUTS tensors of the shape of `out`, each f32, bf16, i32 or u32; the lambda sees every
  * operand with its own element type and must yield exactly the element type of `out` (no implicit conversion).
+ * An operand may also have the rank of `out` with extent 1 along the innermost axis (one value per row: the
+ * row maximum of a softmax) or extent 1 along every other axis (one row shared by all rows: a bias), the two
+ * subsets of the iteration axes an operand of the reference may bind (pkg/chain.go checkOperand).
  * Only chain->map_expr, n_captures and captures are read. Every element is computed once, in IEEE fp32
  * arithmetic per operation with CUDA's math functions (expf ... fmaf: at most 2 ulp from the exact value). */
 TCAB_API int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, const tcab_tensor* out,

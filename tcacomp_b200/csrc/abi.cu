@@ -194,6 +194,24 @@ int need_operand_dtype(const char* op, const char* name, const tcab_tensor* t) {
   return need_elem_align(op, name, t, t->dtype == TCAB_BF16 ? 2 : 4);
 }
 
+// How an operand of the iteration shape `full` (rank r) is indexed: 0 = by every axis (same shape), 1 = one value
+// per row (full's extents with the innermost one = 1), 2 = one row shared by all rows (every extent 1 but the
+// innermost), -1 = none of these. The reference lets an operand bind a subset of the live axes
+// (pkg/chain.go checkOperand); these are the two subsets the innermost-axis kernels take.
+int operand_indexing(const uint32_t* full, uint32_t rank, const tcab_tensor* t) {
+  if (t->rank != rank) return -1;
+  bool same = true, row = t->dims[rank - 1] == 1, col = t->dims[rank - 1] == full[rank - 1];
+  for (uint32_t i = 0; i < rank; ++i) same = same && t->dims[i] == full[i];
+  for (uint32_t i = 0; i + 1 < rank; ++i) {
+    row = row && t->dims[i] == full[i];
+    col = col && t->dims[i] == 1;
+  }
+  if (same) return 0;
+  if (row) return 1;
+  if (col && rank > 1) return 2;
+  return -1;
+}
+
 int have_device(const char* op) {
   if (current_device() < 0) return fail(TCAB_ERR_CUDA, "%s: no CUDA device (this library has no CPU path)", op);
   return TCAB_OK;
@@ -258,10 +276,13 @@ int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dt
                    PreparedChain* pc);
 }
 
-int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype) {
+int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype,
+                       int row_value_mask, int shared_row_mask) {
   PreparedChain pc;
   TCAB_TRY(prepare_common("compile_check", chain, in_dtypes, n_ins, use, out_dtype, &pc));
   JitSpec sp = pc.spec;
+  sp.rb_mask = row_value_mask;
+  sp.cb_mask = shared_row_mask;
   return jit_compile_check(sp);
 }
 
@@ -413,13 +434,29 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
     std::snprintf(name, sizeof(name), "ins[%u]", i);
     TCAB_TRY(check_tensor(op, name, &ins[i]));
     TCAB_TRY(need_operand_dtype(op, name, &ins[i]));
-    if (i > 0 && !same_shape(&ins[0], &ins[i]))
-      return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of ins[0]", op, name);
+    if (ins[i].rank != ins[0].rank) return fail(TCAB_ERR_SHAPE, "%s: %s must have the rank of ins[0]", op, name);
     ptrs[i] = static_cast<const float*>(ins[i].data);
     types[i] = ins[i].dtype;
   }
-  const tcab_tensor* t = &ins[0];
+  // the iteration shape: per axis the largest extent among the operands; an operand may have extent 1 along the
+  // innermost axis (one value per row) or along every other axis (one row shared by all rows)
+  tcab_tensor full = ins[0];
+  for (uint32_t i = 1; i < n_ins; ++i)
+    for (uint32_t d = 0; d < full.rank; ++d)
+      if (ins[i].dims[d] > full.dims[d]) full.dims[d] = ins[i].dims[d];
+  int rb = 0, cb = 0;
+  for (uint32_t i = 0; i < n_ins; ++i) {
+    const int how = operand_indexing(full.dims, full.rank, &ins[i]);
+    if (how < 0)
+      return fail(TCAB_ERR_SHAPE, "%s: ins[%u] must have the operands' common shape, or extent 1 along the innermost axis, "
+                  "or extent 1 along every other axis", op, i);
+    rb |= (how == 1) << i;
+    cb |= (how == 2) << i;
+  }
+  const tcab_tensor* t = &full;
   if (reduce_axis >= t->rank) return fail(TCAB_ERR_INVALID_ARG, "%s: reduce_axis %u out of range", op, reduce_axis);
+  if ((rb | cb) != 0 && reduce_axis != t->rank - 1)
+    return fail(TCAB_ERR_UNSUPPORTED, "%s: operands with broadcast extents are taken by innermost-axis reductions only", op);
   TCAB_TRY(check_tensor(op, "out", out));
   TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
   TCAB_TRY(need_elem_align(op, "out", out, 4));
@@ -432,7 +469,7 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   for (uint32_t i = 0; ok && i < wr; ++i) ok = out->dims[i] == want[i];
   if (!ok) return fail(TCAB_ERR_SHAPE, "%s: out must have the operands' extents without axis %u", op, reduce_axis);
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types));
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types, TCAB_F32, rb, cb));
   TCAB_TRY(have_device(op));
   return launch_chain_reduce(pc, ptrs, count(t, 0, reduce_axis), t->dims[reduce_axis],
                              count(t, reduce_axis + 1, t->rank), static_cast<float*>(out->data),
@@ -535,19 +572,26 @@ int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, co
   TCAB_TRY(need_operand_dtype(op, "out", out));
   const void* ptrs[TCAB_MAX_INPUTS] = {};
   int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int rb = 0, cb = 0;
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];
     std::snprintf(name, sizeof(name), "ins[%u]", i);
     TCAB_TRY(check_tensor(op, name, &ins[i]));
     TCAB_TRY(need_operand_dtype(op, name, &ins[i]));
-    if (!same_shape(out, &ins[i])) return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of out", op, name);
+    const int how = operand_indexing(out->dims, out->rank, &ins[i]);
+    if (how < 0)
+      return fail(TCAB_ERR_SHAPE, "%s: %s must have the shape of out, or extent 1 along the innermost axis (one value per "
+                  "row), or extent 1 along every other axis (one row shared by all rows)", op, name);
+    rb |= (how == 1) << i;
+    cb |= (how == 2) << i;
     ptrs[i] = ins[i].data;
     types[i] = ins[i].dtype;
   }
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'M', types, out->dtype));
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'M', types, out->dtype, rb, cb));
   TCAB_TRY(have_device(op));
-  return launch_chain_map(pc, ptrs, out->data, count(out, 0, out->rank), static_cast<cudaStream_t>(stream));
+  return launch_chain_map(pc, ptrs, out->data, count(out, 0, out->rank), out->dims[out->rank - 1],
+                          static_cast<cudaStream_t>(stream));
 }
 
 int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs, int rhs_is_nk,

@@ -79,6 +79,7 @@ struct JitChain {
   cudaKernel_t k[kSlots] = {};
   int n_in = 0;
   char kind = 'R';
+  bool broadcast = false;  // an operand is not indexed by every axis: innermost-axis kernels only
 };
 
 std::mutex g_mu;
@@ -131,19 +132,31 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
   src += post_text.empty() ? "typedef tcabk::PostNone Post;\n" : functor("Post", post_text, 1, nullptr, TCAB_F32);
   src += "}\n";
   const std::string n = std::to_string(sp.n_in), c = std::to_string(sp.combine), bf = std::to_string(sp.bf_mask());
+  const std::string bc = ", " + std::to_string(sp.rb_mask) + ", " + std::to_string(sp.cb_mask);  // broadcast masks
   std::vector<std::string> names(kSlots);
   if (sp.kind == 'R') {
     const int tprs[4] = {1, 4, 32, 256};
     for (int v = 0; v < 2; ++v)
       for (int t = 0; t < 4; ++t)
         names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
-                                                      std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ">";
-    names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024>";
+                                                      std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ", " +
+                                                      std::to_string(tprs[t] > 128 ? tprs[t] : 128) + bc + ">";
+    names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024" + bc + ">";
+    if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
+      names.assign(kSlots, std::string());
+      for (int v = 0; v < 2; ++v)
+        for (int t = 0; t < 4; ++t)
+          names[(v == 0 ? kInner1V4 : kInner1V1) + t] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " +
+                                                        std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ", " +
+                                                        std::to_string(tprs[t] > 128 ? tprs[t] : 128) + bc + ">";
+      names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024" + bc + ">";
+    } else {
     names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4, " + bf + ">";
     names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1, " + bf + ">";
     names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
     names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
     names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + ">";
+    }
   } else if (sp.kind == 'B') {
     const char* shapes[4] = {"32, 4", "256, 4", "32, 1", "256, 1"};
     for (int i = 0; i < 4; ++i)
@@ -155,8 +168,8 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kContractNK8] = "tcabk::chain_contract<tcabj::Map, tcabj::Post, " + c + ", 1, 8, " + bf + ">";
   } else {
     const std::string ob = sp.out_type == TCAB_BF16 ? "true" : "false";
-    names[kMap8] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 8>";
-    names[kMap1] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 1>";
+    names[kMap8] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 8" + bc + ">";
+    names[kMap1] = "tcabk::chain_map<tcabj::Map, " + n + ", " + bf + ", " + ob + ", 1" + bc + ">";
   }
 
   nvrtcProgram prog = nullptr;
@@ -187,6 +200,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
   auto* jc = new JitChain();
   jc->n_in = sp.n_in;
   jc->kind = sp.kind;
+  jc->broadcast = (sp.rb_mask | sp.cb_mask) != 0;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
   for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
     if (names[i].empty()) continue;
@@ -229,7 +243,8 @@ int jit_prepare(const JitSpec& sp, void** handle, bool compile_if_missing) {
   std::string key(1, sp.kind);
   key += "|" + std::to_string(sp.n_in) + "|" + std::to_string(sp.combine) + "|";
   for (int i = 0; i < sp.n_in; ++i) key += std::to_string(sp.in_types[i]);
-  key += ">" + std::to_string(sp.kind == 'M' ? sp.out_type : TCAB_F32) + "|" + sp.map_text + "|" + sp.post_text;
+  key += ">" + std::to_string(sp.kind == 'M' ? sp.out_type : TCAB_F32) + "|" + std::to_string(sp.rb_mask) + "," +
+         std::to_string(sp.cb_mask) + "|" + sp.map_text + "|" + sp.post_text;
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_cache.find(key);
   if (it != g_cache.end()) {
@@ -292,6 +307,8 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
                   s, "chain_inner");
   }
   if (inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
+  if (jc->broadcast)
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: operands with broadcast extents are taken by innermost-axis reductions only");
   const bool vec = al && (inner % 4 == 0);
   uint32_t nb = static_cast<uint32_t>(outer), nc = static_cast<uint32_t>(inner);
   uint32_t tiles_per_b = (nc + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
@@ -338,7 +355,8 @@ int jit_launch_batched(void* handle, const float* const* ins, float* const* outs
                 "chain_inner_batched");
 }
 
-int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, const float* caps16, cudaStream_t s) {
+int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, uint32_t cols, const float* caps16,
+                   cudaStream_t s) {
   JitChain* jc = static_cast<JitChain*>(handle);
   if (jc->kind != 'M') return fail(TCAB_ERR_INVALID_ARG, "map: the chain was prepared for another use");
   tcabk::Caps caps;
@@ -346,7 +364,8 @@ int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, 
   const void* ptrs[4] = {ins[0], jc->n_in > 1 ? ins[1] : ins[0], jc->n_in > 2 ? ins[2] : ins[0], jc->n_in > 3 ? ins[3] : ins[0]};
   bool al = aligned16(out);
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
-  void* a[] = {ptrs, &out, &n, &caps};
+  if (jc->broadcast && cols % 8 != 0) al = false;  // a group of eight must not straddle two rows
+  void* a[] = {ptrs, &out, &n, &caps, &cols};
   if (al) return launch(jc->k[kMap8], (n / 8 + 1 + 255) / 256, 256, a, s, "chain_map");
   return launch(jc->k[kMap1], (n + 255) / 256, 256, a, s, "chain_map");
 }

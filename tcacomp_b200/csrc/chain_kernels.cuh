@@ -145,14 +145,46 @@ __device__ __forceinline__ float lanes_allreduce(float v) {
 
 __host__ __device__ constexpr int inner_cta_threads(int tpr) { return tpr > 128 ? tpr : 128; }
 
-// One thread's share of a row: vectors t, t + TPR, ... of the nvec vectors that start at vector index vbase.
-template <class Map, class C, int NIN, int TPR, int V, int BF>
-__device__ __forceinline__ float fold_row_share(const float* const* p, u64 vbase, u32 nvec, int t, const float* caps) {
+// Operands that are not indexed by every iteration axis (the reference's structural indexing lets an operand
+// bind a subset of the live axes, pkg/chain.go checkOperand: x[i] inside an (i, j) iteration): RB is the bit
+// mask of operands with ONE value per row (shape [rows, 1]: a max or a sum from an earlier statement), CB of
+// operands with one row shared by all rows (shape [1, cols]: a bias, gamma, beta). A row value is loaded
+// once per row and thread, a shared row with the same vector index in every row (it stays in L1 / L2).
+template <int V, int BF, int RB, int CB, int NIN, int A = 0>
+struct LoadRowAll {
+  static __device__ __forceinline__ void at(const float* const* p, u64 row, u32 nvec, u32 idx, const float* rowval,
+                                            float (*f)[V]) {
+    if constexpr (((RB >> A) & 1) != 0) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[A][j] = rowval[A];
+    } else if constexpr (((CB >> A) & 1) != 0) {
+      load_operand<V, BF, A>(p[A], idx, f[A]);
+    } else {
+      load_operand<V, BF, A>(p[A], row * nvec + idx, f[A]);
+    }
+    LoadRowAll<V, BF, RB, CB, NIN, A + 1>::at(p, row, nvec, idx, rowval, f);
+  }
+  static __device__ __forceinline__ void row_values(const float* const* p, u64 row, float* rowval) {
+    if constexpr (((RB >> A) & 1) != 0) LdT<1, ((BF >> A) & 1) != 0>::load(p[A], row, &rowval[A]);
+    LoadRowAll<V, BF, RB, CB, NIN, A + 1>::row_values(p, row, rowval);
+  }
+};
+template <int V, int BF, int RB, int CB, int NIN>
+struct LoadRowAll<V, BF, RB, CB, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, u32, u32, const float*, float (*)[V]) {}
+  static __device__ __forceinline__ void row_values(const float* const*, u64, float*) {}
+};
+
+// One thread's share of a row: vectors t, t + TPR, ... of the row's nvec vectors.
+template <class Map, class C, int NIN, int TPR, int V, int BF, int RB = 0, int CB = 0>
+__device__ __forceinline__ float fold_row_share(const float* const* p, u64 row, u32 nvec, int t, const float* caps) {
   float acc = C::identity();
+  float rowval[NIN];
+  LoadRowAll<V, BF, RB, CB, NIN>::row_values(p, row, rowval);
 #pragma unroll 8
   for (u32 idx = t; idx < nvec; idx += TPR) {
     float f[NIN][V];
-    LoadAll<V, BF, NIN>::at(p, vbase + idx, f);
+    LoadRowAll<V, BF, RB, CB, NIN>::at(p, row, nvec, idx, rowval, f);
 #pragma unroll
     for (int j = 0; j < V; ++j) {
       float v[NIN];
@@ -186,7 +218,8 @@ __device__ __forceinline__ float fold_row_group(float acc, float (*slots)[32], u
 // thread (bit-identical to the reference's SeqReducer order). THREADS is the CTA size: 128 (256 for a CTA
 // per row) by default; small problems take 1024-thread CTAs, because a launch costs by the CTA (measured in a
 // graph of dependent launches: an empty grid of 1024 x 128 threads 1.7 us, of 148 x 1024 threads 0.8 us).
-template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0, int THREADS = inner_cta_threads(TPR)>
+template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0, int THREADS = inner_cta_threads(TPR),
+          int RB = 0, int CB = 0>
 __global__ void __launch_bounds__(THREADS)
 chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
   typedef Comb<COMBINE> C;
@@ -211,7 +244,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
       const u32 bytes = nk * 4u < 65536u ? nk * 4u : 65536u;  // nk % 4 == 0 and 16-byte aligned rows on this path
 #pragma unroll
       for (int a = 0; a < NIN; ++a)
-        if (!((BF >> a) & 1))  // f32 / i32 / u32 rows; a bf16 row (8-byte granules) is left to the loads
+        if (!(((BF | RB | CB) >> a) & 1))  // full f32 / i32 / u32 rows; bf16 rows (8-byte granules) are left to the loads
           asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ins.p[a] + first * nk), "r"(bytes) : "memory");
     }
   }
@@ -222,7 +255,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
     const u64 row = row0 + g;
     const bool live = row < rows;
     float acc = C::identity();
-    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF>(ins.p, row * nvec, nvec, t, caps.c);  // nk % V == 0
+    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF, RB, CB>(ins.p, row, nvec, t, caps.c);  // nk % V == 0
     acc = fold_row_group<C, TPR>(acc, slots, iter);
     if (live && t == 0) {
       float r[1] = {C::apply(init, acc)};
@@ -263,7 +296,7 @@ chain_inner_batched(BatchPtrs<NIN> ins, u32 nprob, u32 rows, u32 nk, float init,
     const u32 b = live ? static_cast<u32>(gr / rows) : 0u;
     const u64 row = live ? gr % rows : 0;
     float acc = C::identity();
-    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF>(ins.in[b], row * nvec, nvec, t, caps.c);
+    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF>(ins.in[b], row, nvec, t, caps.c);
     acc = fold_row_group<C, TPR>(acc, slots, iter);
     if (live && t == 0) {
       float r[1] = {C::apply(init, acc)};
@@ -614,22 +647,34 @@ struct MapLd<1, true> {
     f[0] = bf16_bits_to_float(__ldcs(reinterpret_cast<const unsigned short*>(base) + i));
   }
 };
-template <int EPT, int BF, int NIN, int A = 0>
+// index: the group (EPT = 8) or element (EPT = 1) in the flat output; row / col_index: the same position as a
+// row and a group or element within the row, for operands with one value per row (RB) or one shared row (CB).
+template <int EPT, int BF, int RB, int CB, int NIN, int A = 0>
 struct MapLoadAll {
-  static __device__ __forceinline__ void at(const float* const* p, u64 index, float (*f)[EPT]) {
-    MapLd<EPT, ((BF >> A) & 1) != 0>::load(p[A], index, f[A]);
-    MapLoadAll<EPT, BF, NIN, A + 1>::at(p, index, f);
+  static __device__ __forceinline__ void at(const float* const* p, u64 index, u64 row, u64 col_index, float (*f)[EPT]) {
+    constexpr bool bf = ((BF >> A) & 1) != 0;
+    if constexpr (((RB >> A) & 1) != 0) {
+      float v;
+      MapLd<1, bf>::load(p[A], row, &v);
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) f[A][j] = v;
+    } else if constexpr (((CB >> A) & 1) != 0) {
+      MapLd<EPT, bf>::load(p[A], col_index, f[A]);
+    } else {
+      MapLd<EPT, bf>::load(p[A], index, f[A]);
+    }
+    MapLoadAll<EPT, BF, RB, CB, NIN, A + 1>::at(p, index, row, col_index, f);
   }
 };
-template <int EPT, int BF, int NIN>
-struct MapLoadAll<EPT, BF, NIN, NIN> {
-  static __device__ __forceinline__ void at(const float* const*, u64, float (*)[EPT]) {}
+template <int EPT, int BF, int RB, int CB, int NIN>
+struct MapLoadAll<EPT, BF, RB, CB, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, u64, u64, float (*)[EPT]) {}
 };
 
-template <int NIN, int BF, bool OUT_BF16, class Map>
-__device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i, const float* caps) {
+template <int NIN, int BF, int RB, int CB, bool OUT_BF16, class Map>
+__device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i, u32 cols, const float* caps) {
   float f[NIN][1];
-  MapLoadAll<1, BF, NIN>::at(p, i, f);
+  MapLoadAll<1, BF, RB, CB, NIN>::at(p, i, (RB | CB) ? i / cols : 0, (RB | CB) ? i % cols : 0, f);
   float v[NIN];
 #pragma unroll
   for (int a = 0; a < NIN; ++a) v[a] = f[a][0];
@@ -638,17 +683,20 @@ __device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i,
   else __stcs(static_cast<float*>(out) + i, r);
 }
 
-template <class Map, int NIN, int BF, bool OUT_BF16, int EPT>
+// cols: the innermost extent; only read when an operand is broadcast (RB | CB != 0), and then the EPT = 8
+// path requires cols % 8 == 0 (a group of eight never straddles two rows).
+template <class Map, int NIN, int BF, bool OUT_BF16, int EPT, int RB = 0, int CB = 0>
 __global__ void __launch_bounds__(256)
-chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps) {
+chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
   const u64 tid = static_cast<u64>(blockIdx.x) * 256 + threadIdx.x;
   if constexpr (EPT == 1) {
-    if (tid < n) map_one<NIN, BF, OUT_BF16, Map>(ins.p, out, tid, caps.c);
+    if (tid < n) map_one<NIN, BF, RB, CB, OUT_BF16, Map>(ins.p, out, tid, cols, caps.c);
   } else {
     const u64 groups = n / 8;
     if (tid < groups) {
       float f[NIN][8];
-      MapLoadAll<8, BF, NIN>::at(ins.p, tid, f);
+      const u64 gpr = (RB | CB) ? cols / 8 : 1;   // groups per row
+      MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, (RB | CB) ? tid / gpr : 0, (RB | CB) ? tid % gpr : 0, f);
       float r[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -669,7 +717,7 @@ chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps) {
         __stcs(static_cast<float4*>(out) + 2 * tid + 1, make_float4(r[4], r[5], r[6], r[7]));
       }
     } else if (tid == groups) {  // the ragged end, fewer than eight elements
-      for (u64 i = groups * 8; i < n; ++i) map_one<NIN, BF, OUT_BF16, Map>(ins.p, out, i, caps.c);
+      for (u64 i = groups * 8; i < n; ++i) map_one<NIN, BF, RB, CB, OUT_BF16, Map>(ins.p, out, i, cols, caps.c);
     }
   }
 }

@@ -374,10 +374,10 @@ int launch_map_aot(const MapArgs& a) {
   if (al) {
     const uint64_t threads = a.n / 8 + 1;  // one thread per group of eight, one more for the ragged end
     tcabk::chain_map<Map, NIN, 0, false, 8>
-        <<<static_cast<unsigned>((threads + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps);
+        <<<static_cast<unsigned>((threads + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps, 0u);
   } else {
     tcabk::chain_map<Map, NIN, 0, false, 1>
-        <<<static_cast<unsigned>((a.n + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps);
+        <<<static_cast<unsigned>((a.n + 255) / 256), 256, 0, a.stream>>>(ptrs, a.out, a.n, a.caps, 0u);
   }
   count_launch();
   return check_launch("chain_map");
@@ -410,7 +410,8 @@ int combine_id(const std::string& text) {
 
 }  // namespace
 
-int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind, const int* in_types, int out_type) {
+int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind, const int* in_types, int out_type,
+                  int rb_mask, int cb_mask) {
   const char* op = kind == 'M' ? "map" : kind == 'C' ? "chain_contract" : "chain_reduce";
   std::vector<float> user(chain->captures, chain->captures + chain->n_captures);
   CanonExpr map, comb, post;
@@ -436,6 +437,9 @@ int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, ch
   sp.n_in = static_cast<int>(n_ins);
   for (uint32_t i = 0; i < n_ins; ++i) sp.in_types[i] = static_cast<int>(types[i]);
   sp.out_type = out_type;
+  sp.rb_mask = rb_mask;
+  sp.cb_mask = cb_mask;
+  if ((rb_mask | cb_mask) != 0) all_f32 = false;  // broadcast operands: compiled at run time only
   sp.map_text = map.text;
   if (kind == 'M') {
     // a map-only chain stores the lambda's value as it is: its type is the output's element type, no conversion
@@ -490,7 +494,7 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
     if (inner == 1) {
       bool al = true;
       for (int i = 0; i < pc.spec.n_in; ++i) al = al && aligned16(ins[i]);
-      splits = choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
+      splits = (pc.spec.rb_mask | pc.spec.cb_mask) ? 1 : choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
       if (splits > 1) scratch = split_scratch(s);
     } else if (outer * ((inner + 127) / 128) < static_cast<uint64_t>(sm_count()) && nk >= 512) {
       scratch = split_scratch(s);  // a middle-axis reduction that may split k over CTAs (decided at launch)
@@ -518,14 +522,14 @@ int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins
   return kTable[pc.entry].launch_batched(a);
 }
 
-int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, cudaStream_t s) {
+int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, uint32_t cols, cudaStream_t s) {
   if (n == 0) return TCAB_OK;
   if (n / 8 / 256 >= 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "map: too many elements for one launch");
   if (pc.entry == kJitEntry) {
     void* h = nullptr;
     const int rc = jit_prepare(pc.spec, &h);
     if (rc != TCAB_OK) return rc;
-    return jit_launch_map(h, ins, out, n, pc.caps, s);
+    return jit_launch_map(h, ins, out, n, cols, pc.caps, s);
   }
   MapArgs a{ins, out, n, {}, s};
   for (int i = 0; i < 16; ++i) a.caps.c[i] = pc.caps[i];
@@ -663,6 +667,8 @@ int launch_chain_reduce_noalloc(const PreparedChain& pc, const float* const* ins
                 "(one per row at least); use tcab_chain_reduce for larger problems",
                 static_cast<unsigned long long>(rows), kNoAllocMaxPartials);
   if (rows == 0) return TCAB_OK;
+  if ((pc.spec.rb_mask | pc.spec.cb_mask) != 0)
+    return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce_noalloc: operands with broadcast extents are not taken by the split kernels");
   float* scratch = nullptr;
   const int rc = noalloc_scratch(&scratch);
   if (rc != TCAB_OK) return rc;

@@ -78,6 +78,7 @@ struct JitSpec {
   int n_in = 0, combine = 0;
   int in_types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};  // tcab_dtype of each operand
   int out_type = TCAB_F32;                                                   // map-only: the stored element type
+  int rb_mask = 0, cb_mask = 0;  // operands with one value per row / one row shared by all rows (innermost-axis kernels)
   std::string map_text, post_text;
   int bf_mask() const {
     int m = 0;
@@ -100,12 +101,13 @@ int jit_prepare(const JitSpec& spec, void** handle, bool compile_if_missing = tr
 int jit_compile_check(const JitSpec& spec);  // NVRTC only, nothing is loaded: works without a device
 int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
                const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s);
-int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, const float* caps16, cudaStream_t s);
+int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, uint32_t cols, const float* caps16,
+                   cudaStream_t s);
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
 // kind: 'R' / 'C' / 'M' as in JitSpec; in_types: n_ins tcab_dtype values (null = all f32); out_type: map-only.
 int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind = 'R', const int* in_types = nullptr,
-                  int out_type = TCAB_F32);
-int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, cudaStream_t s);
+                  int out_type = TCAB_F32, int rb_mask = 0, int cb_mask = 0);
+int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, uint32_t cols, cudaStream_t s);
 int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
                         uint64_t inner, float* out, cudaStream_t s);
 int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias,

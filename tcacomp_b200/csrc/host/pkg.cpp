@@ -135,38 +135,107 @@ Expr Builder::bad(const std::string& e) {
   return x;
 }
 
-Expr Builder::binop(const char* op, Expr x, Expr y) {
+// The shared bottom of every binary operator (pkg/expr.go:137-176 typedBinOp): operand errors propagate,
+// operands belong to this builder and share one type, the type satisfies the operator's class, comparisons
+// yield bool.
+Expr Builder::binop(const char* op, Expr x, Expr y, const char* cls) {
   if (!x.ok()) return bad(x.err);
   if (!y.ok()) return bad(y.err);
   if (x.b != this || y.b != this) return bad(std::string(op) + ": operands come from a different builder");
   if (x.typ != y.typ)
     return bad(std::string(op) + ": operand types differ (" + ElemName(x.typ) + " vs " + ElemName(y.typ) +
                "); implicit promotions are not supported (syntax-design.md §4.6 rule 17)");
-  if (!is_arith(x.typ))
-    return bad(std::string(op) + ": operands must have the same arithmetic type, got " + ElemName(x.typ));
+  Elem result = x.typ;
+  const std::string c = cls;
+  if (c == "arithmetic") {
+    if (!is_arith(x.typ))
+      return bad(std::string(op) + ": operands must have the same arithmetic type, got " + ElemName(x.typ));
+  } else if (c == "integer") {
+    if (!is_int(x.typ)) return bad(std::string(op) + ": operands must have the same integer type, got " + ElemName(x.typ));
+  } else if (c == "bool") {
+    if (x.typ != Elem::Bool) return bad(std::string(op) + ": operands must be bool, got " + ElemName(x.typ));
+  } else {  // comparable: every supported scalar type, result bool
+    result = Elem::Bool;
+  }
   auto n = std::make_shared<Node>();
   n->kind = Node::Binary;
-  n->typ = x.typ;
+  n->typ = result;
   n->name = op;
   n->args = {x.node, y.node};
-  return Expr{this, n, x.typ, ""};
+  return Expr{this, n, result, ""};
 }
 
 Expr Builder::Add(Expr x, Expr y) { return binop("+", x, y); }
 Expr Builder::Sub(Expr x, Expr y) { return binop("-", x, y); }
 Expr Builder::Mul(Expr x, Expr y) { return binop("*", x, y); }
 Expr Builder::Div(Expr x, Expr y) { return binop("/", x, y); }
+Expr Builder::Mod(Expr x, Expr y) { return binop("%", x, y, "integer"); }
+Expr Builder::Eq(Expr x, Expr y) { return binop("==", x, y, "comparable"); }
+Expr Builder::Ne(Expr x, Expr y) { return binop("!=", x, y, "comparable"); }
+Expr Builder::Lt(Expr x, Expr y) { return binop("<", x, y, "comparable"); }
+Expr Builder::Le(Expr x, Expr y) { return binop("<=", x, y, "comparable"); }
+Expr Builder::Gt(Expr x, Expr y) { return binop(">", x, y, "comparable"); }
+Expr Builder::Ge(Expr x, Expr y) { return binop(">=", x, y, "comparable"); }
+Expr Builder::And(Expr x, Expr y) { return binop("&&", x, y, "bool"); }
+Expr Builder::Or(Expr x, Expr y) { return binop("||", x, y, "bool"); }
+Expr Builder::BitAnd(Expr x, Expr y) { return binop("&", x, y, "integer"); }
+Expr Builder::BitOr(Expr x, Expr y) { return binop("|", x, y, "integer"); }
+Expr Builder::BitXor(Expr x, Expr y) { return binop("^", x, y, "integer"); }
+Expr Builder::Shl(Expr x, Expr y) { return binop("<<", x, y, "integer"); }
+Expr Builder::Shr(Expr x, Expr y) { return binop(">>", x, y, "integer"); }
 
-Expr Builder::Neg(Expr x) {
+// pkg/expr.go typedUnary: Neg / Pos arithmetic, Not bool, BitsNot integer.
+Expr Builder::unop(const char* op, Expr x, const char* cls) {
   if (!x.ok()) return bad(x.err);
-  if (x.b != this) return bad("-: operand comes from a different builder");
-  if (!is_arith(x.typ)) return bad(std::string("-: operand must have an arithmetic type, got ") + ElemName(x.typ));
+  if (x.b != this) return bad(std::string(op) + ": operand comes from a different builder");
+  const std::string c = cls;
+  if (c == "arithmetic" && !is_arith(x.typ))
+    return bad(std::string(op) + ": operand must have an arithmetic type, got " + ElemName(x.typ));
+  if (c == "integer" && !is_int(x.typ))
+    return bad(std::string(op) + ": operand must have an integer type, got " + ElemName(x.typ));
+  if (c == "bool" && x.typ != Elem::Bool) return bad(std::string(op) + ": operand must be bool, got " + ElemName(x.typ));
   auto n = std::make_shared<Node>();
   n->kind = Node::Unary;
   n->typ = x.typ;
-  n->name = "-";
+  n->name = op;
   n->args = {x.node};
   return Expr{this, n, x.typ, ""};
+}
+
+Expr Builder::Neg(Expr x) { return unop("-", x, "arithmetic"); }
+Expr Builder::Pos(Expr x) { return unop("+", x, "arithmetic"); }
+Expr Builder::Not(Expr x) { return unop("!", x, "bool"); }
+Expr Builder::BitsNot(Expr x) { return unop("~", x, "integer"); }
+
+Expr Builder::UInt32(uint32_t v) {
+  auto n = std::make_shared<Node>();
+  n->kind = Node::Const;
+  n->typ = Elem::U32;
+  n->value = v;
+  return Expr{this, n, Elem::U32, ""};
+}
+
+Expr Builder::Bool(bool v) {
+  auto n = std::make_shared<Node>();
+  n->kind = Node::Const;
+  n->typ = Elem::Bool;
+  n->value = v ? 1 : 0;
+  return Expr{this, n, Elem::Bool, ""};
+}
+
+// pkg/expr.go:271 Select: the condition must be bool and the branches identically typed.
+Expr Builder::Select(Expr cond, Expr a, Expr b) {
+  for (const Expr* e : {&cond, &a, &b})
+    if (!e->ok()) return bad(e->err);
+  if (cond.b != this || a.b != this || b.b != this) return bad("select: operands come from different builders");
+  if (cond.typ != Elem::Bool) return bad(std::string("select: condition must be bool, got ") + ElemName(cond.typ));
+  if (a.typ != b.typ)
+    return bad(std::string("select: branches must have identical types, got ") + ElemName(a.typ) + " vs " + ElemName(b.typ));
+  auto n = std::make_shared<Node>();
+  n->kind = Node::Select;
+  n->typ = a.typ;
+  n->args = {cond.node, a.node, b.node};
+  return Expr{this, n, a.typ, ""};
 }
 
 Expr Builder::Float32(float v) {
@@ -189,8 +258,10 @@ Expr Builder::Int32(int32_t v) {
 Expr Builder::Cast(Expr x, Elem to) {
   if (!x.ok()) return bad(x.err);
   if (x.b != this) return bad("cast: operand comes from a different builder");
+  if (x.typ == to) return bad(std::string("cast: redundant cast to ") + ElemName(to));
   if (!is_arith(x.typ) || !is_arith(to))
-    return bad(std::string("cast: only arithmetic types convert, got ") + ElemName(x.typ) + " -> " + ElemName(to));
+    return bad(std::string("cast: pair ") + ElemName(x.typ) + " -> " + ElemName(to) +
+               " is not in the v0 cast registry (arithmetic-to-arithmetic only)");
   auto n = std::make_shared<Node>();
   n->kind = Node::Cast;
   n->typ = to;

@@ -73,7 +73,7 @@ Operand At(const Tensor& t, D... axes) {
 
 // Scalar expression tree node.
 struct Node {
-  enum Kind { Const, Param, Scalar, Unary, Binary, Call, Cast } kind = Const;
+  enum Kind { Const, Param, Scalar, Unary, Binary, Call, Cast, Select } kind = Const;
   Elem typ = Elem::F32;
   double value = 0;           // Const
   int index = 0;              // Param: lambda parameter position
@@ -161,14 +161,36 @@ class Builder {
   StmtIter Stmt();
   Result<Graph> Build();  // pkg/builder.go:340-370
 
-  // Typed scalar expression DSL (pkg/expr.go:179-341): the subset this path evaluates.
+  // Typed scalar expression DSL (pkg/expr.go:179-341), operand classes as pkg/expr.go:137-176:
+  // arithmetic operators take one arithmetic type, % and the bit operators one integer type, comparisons any
+  // one type and yield bool, And / Or / Not take bool; nothing is promoted implicitly.
   Expr Add(Expr x, Expr y);
   Expr Sub(Expr x, Expr y);
   Expr Mul(Expr x, Expr y);
   Expr Div(Expr x, Expr y);
+  Expr Mod(Expr x, Expr y);
+  Expr Eq(Expr x, Expr y);
+  Expr Ne(Expr x, Expr y);
+  Expr Lt(Expr x, Expr y);
+  Expr Le(Expr x, Expr y);
+  Expr Gt(Expr x, Expr y);
+  Expr Ge(Expr x, Expr y);
+  Expr And(Expr x, Expr y);
+  Expr Or(Expr x, Expr y);
+  Expr BitAnd(Expr x, Expr y);
+  Expr BitOr(Expr x, Expr y);
+  Expr BitXor(Expr x, Expr y);
+  Expr Shl(Expr x, Expr y);
+  Expr Shr(Expr x, Expr y);
   Expr Neg(Expr x);
+  Expr Pos(Expr x);
+  Expr Not(Expr x);
+  Expr BitsNot(Expr x);
   Expr Float32(float v);
   Expr Int32(int32_t v);
+  Expr UInt32(uint32_t v);
+  Expr Bool(bool v);
+  Expr Select(Expr cond, Expr a, Expr b);  // pkg/expr.go:271: the lazy conditional cond ? a : b
   Expr Cast(Expr x, Elem to);
   Expr Call(const std::string& builtin, const std::vector<Expr>& args);  // internal/ir/builtins.go:25-39
 
@@ -185,7 +207,8 @@ class Builder {
   void noteDeclErr(const std::string& e);
   std::string checkDim(const pkg::Dim& d, const std::string& what) const;
   Expr bad(const std::string& e);
-  Expr binop(const char* op, Expr x, Expr y);
+  Expr binop(const char* op, Expr x, Expr y, const char* cls = "arithmetic");
+  Expr unop(const char* op, Expr x, const char* cls);
 
   Graph g_;
   std::map<std::string, pkg::Dim> dims_;

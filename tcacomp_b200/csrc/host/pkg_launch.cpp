@@ -33,6 +33,15 @@ std::string print_node(const Node& n, std::vector<std::string>* captures, std::s
         if (s.find_first_of(".e") == std::string::npos) s += ".0";
         return s + "f";
       }
+      if (n.typ == Elem::Bool) return n.value != 0 ? "true" : "false";
+      if (n.typ == Elem::U32) {
+        std::snprintf(buf, sizeof(buf), "%lluu", static_cast<unsigned long long>(n.value));
+        return buf;
+      }
+      if (n.value < 0) {  // a literal carries no sign (pkg/expr.go: unary minus is a separate operator)
+        std::snprintf(buf, sizeof(buf), "(-%lld)", -static_cast<long long>(n.value));
+        return buf;
+      }
       std::snprintf(buf, sizeof(buf), "%lld", static_cast<long long>(n.value));
       return buf;
     }
@@ -60,11 +69,21 @@ std::string print_node(const Node& n, std::vector<std::string>* captures, std::s
       }
       return s + ")";
     }
-    case Node::Cast:
-      if (n.typ == n.args[0]->typ) return print_node(*n.args[0], captures, err);
-      *err = std::string("a cast ") + ElemName(n.args[0]->typ) + " -> " + ElemName(n.typ) +
-             " inside a lambda is outside the fp32 chain class";
-      return "";
+    case Node::Cast: {  // internal/cg/cxx/expr.go:57-66: static_cast<T>(x), T spelled as internal/cg/cxx/naming.go:21-46
+      const char* ts = n.typ == Elem::F32 ? "float" : n.typ == Elem::BF16 ? "__nv_bfloat16" : n.typ == Elem::I32 ? "int32_t"
+                       : n.typ == Elem::U32 ? "uint32_t" : nullptr;
+      if (ts == nullptr) {
+        *err = std::string("a cast to ") + ElemName(n.typ) + " has no kernel in this library (f32, bf16, i32, u32)";
+        return "";
+      }
+      return std::string("static_cast<") + ts + ">(" + print_node(*n.args[0], captures, err) + ")";
+    }
+    case Node::Select: {  // internal/cg/cxx/expr.go:38-56
+      const std::string c = print_node(*n.args[0], captures, err);
+      const std::string a = print_node(*n.args[1], captures, err);
+      const std::string b = print_node(*n.args[2], captures, err);
+      return "(" + c + " ? " + a + " : " + b + ")";
+    }
   }
   return "";
 }

@@ -187,7 +187,10 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
     t0 = ins[0]
     ax = axis % t0.dim()
     if out is None:
-        shape = [d for i, d in enumerate(t0.shape) if i != ax] or [1]
+        # the iteration shape: per axis the largest extent among the operands (an operand may have extent 1 along
+        # the innermost axis, or along every other axis)
+        full = [max(t.shape[i] for t in ins if t.dim() == t0.dim()) for i in range(t0.dim())]
+        shape = [d for i, d in enumerate(full) if i != ax] or [1]
         out = torch.empty(shape, device=t0.device, dtype=torch.float32)
     chain = _chain(map_expr, combine_expr, post_expr, init, captures)
     arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
@@ -204,13 +207,16 @@ def map(ins: Sequence[torch.Tensor], map_expr: str, captures: Sequence[float] = 
         stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Map-only chain with a rank-preserving store: out[...] = map_expr(ins[0][...], ins[1][...], ...).
 
-    Operands share one shape and may be f32, bf16, i32 or u32; the lambda sees each with its own type and must
-    yield exactly the output's element type (out.dtype, or out_dtype, default: that of ins[0])."""
+    Operands may be f32, bf16, i32 or u32; the lambda sees each with its own type and must yield exactly the
+    output's element type (out.dtype, or out_dtype, default: that of ins[0]). They share the output's shape; an
+    operand may instead have extent 1 along the innermost axis (one value per row, shape [..., 1]) or along every
+    other axis (one row shared by all rows, shape [1, ..., C])."""
     ins = list(ins)
     if not 1 <= len(ins) <= _lib.MAX_INPUTS:
         raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
     if out is None:
-        out = torch.empty(ins[0].shape, device=ins[0].device, dtype=out_dtype or ins[0].dtype)
+        full = [max(t.shape[i] for t in ins if t.dim() == ins[0].dim()) for i in range(ins[0].dim())]
+        out = torch.empty(full, device=ins[0].device, dtype=out_dtype or ins[0].dtype)
     chain = _chain(map_expr, "(p0 + p1)", None, 0.0, captures)
     arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
     ov = _view(out, "out")

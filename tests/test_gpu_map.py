@@ -247,3 +247,74 @@ def test_contraction_over_bf16_operands(cuda, m, k, n, nk):
     want = qf @ (kf32.astype(np.float64).T if nk else kf32.astype(np.float64))
     mag = np.abs(qf) @ np.abs(kf32.astype(np.float64).T if nk else kf32.astype(np.float64))
     assert (np.abs(got - want) <= 1e-5 * mag + 1e-30).all()
+
+
+# ----------------------------------------------------------------------------
+# operands that bind a subset of the iteration axes: one value per row, one row shared by all rows
+# ----------------------------------------------------------------------------
+def bcast(a, shape):
+    return np.ascontiguousarray(np.broadcast_to(a, shape))
+
+
+@pytest.mark.parametrize("rows,cols", [(37, 1000), (5, 8), (300, 4096), (3, 13), (64, 20000)])
+def test_softmax_statement_by_statement_reads_row_values(oracle, cuda, rows, cols):
+    """The softmax chain as the reference would have to spell it (pkg/local_test.go:17-68: a reduction stores into
+    a rank-1 Local, the next statement reads it as x[i] inside the (i, j) iteration): m = max_j x; s = sum_j
+    exp(x - m[i]); y = exp(x - m[i]) / s[i]. Three launches; against the one-launch operator and the oracle."""
+    from oracle import checks, lambda_eval
+    rng = np.random.default_rng(rows + cols)
+    x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
+    xd = to_dev(x, cuda)
+    m = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=-np.inf)            # [rows]
+    s = T.chain_reduce([xd, m.view(rows, 1)], "expf(p0 - p1)")                            # reads m[i]
+    y = T.map([xd, m.view(rows, 1), s.view(rows, 1)], "expf(p0 - p1) / p2")
+    assert np.array_equal(m.cpu().numpy(), x.max(1))
+    mh = x.max(1, keepdims=True)
+    want_s = np.exp(x.astype(np.float64) - mh).sum(1)
+    assert (np.abs(s.cpu().numpy() - want_s) <= 1e-5 * want_s).all()
+    assert checks.softmax_close(y.cpu().numpy(), x)
+    # the map alone, bit for bit against the host evaluation of the same expression on materialised operands
+    sh = s.cpu().numpy().reshape(rows, 1)
+    want = lambda_eval.evaluate("expf(p0 - p1) / p2", [x, bcast(mh, x.shape), bcast(sh, x.shape)])
+    assert ulp_distance(y.cpu().numpy(), want).max() <= 2
+
+
+@pytest.mark.parametrize("rows,cols", [(33, 1024), (7, 10), (128, 8192)])
+def test_shared_rows_bias_and_layernorm_tail(oracle, cuda, rows, cols):
+    from oracle import binding as O, lambda_eval
+    rng = np.random.default_rng(rows * cols)
+    x = rng.normal(0, 1, (rows, cols)).astype(np.float32)
+    bias = rng.normal(0, 1, (1, cols)).astype(np.float32)
+    got = T.map([to_dev(x, cuda), to_dev(bias, cuda)], "fmaxf(p0 + p1, 0.0f)").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x + bias, 0))
+    # layer-norm's last map on bf16 rows: y = bf16((f32(x) - mean[i]) * rstd[i] * f32(gamma[j]) + f32(beta[j]))
+    xb = O.f32_to_bf16(x)
+    g = O.f32_to_bf16(rng.normal(1, 0.1, (1, cols)).astype(np.float32))
+    b = O.f32_to_bf16(rng.normal(0, 0.1, (1, cols)).astype(np.float32))
+    xf = O.bf16_to_f32(xb)
+    mean = xf.mean(1, keepdims=True).astype(np.float32)
+    rstd = (1.0 / np.sqrt(xf.var(1, keepdims=True) + 1e-5)).astype(np.float32)
+    expr = "bf16((f32(p0) - p1) * p2 * f32(p3) + f32(p4))"
+    with pytest.raises(ValueError):
+        T.map([to_dev(xb, cuda)] * 5, expr)                    # at most four operands per lambda
+    expr4 = "bf16((f32(p0) - p1) * p2 * f32(p3))"
+    got = to_host(T.map([to_dev(xb, cuda), to_dev(mean, cuda), to_dev(rstd, cuda), to_dev(g, cuda)], expr4,
+                        out_dtype=torch.bfloat16))
+    want = lambda_eval.evaluate(expr4, [xb, bcast(mean, x.shape), bcast(rstd, x.shape), bcast(g, x.shape)], out_dtype=np.uint16)
+    # one fused multiply-add may differ from the host's two roundings before the bf16 rounding: one bf16 ulp at most
+    assert (np.abs(got.astype(np.int32) - want.astype(np.int32)) <= 1).all()
+    assert (got != want).mean() < 0.01
+    # a reduction over a row weighted by a shared row: sum_j x[i][j] * w[j]
+    got = T.chain_reduce([to_dev(x, cuda), to_dev(bias, cuda)], "p0 * p1").cpu().numpy()
+    want = (x.astype(np.float64) * bias).sum(1)
+    assert (np.abs(got - want) <= 1e-5 * np.abs(x.astype(np.float64) * bias).sum(1)).all()
+
+
+def test_broadcast_shapes_are_checked(cuda):
+    x = torch.zeros((6, 16), device=cuda)
+    with pytest.raises(T.TcabError) as e:
+        T.map([x, torch.zeros((6, 2), device=cuda)], "p0 + p1")
+    assert e.value.status == T._lib.ERR_SHAPE
+    with pytest.raises(T.TcabError) as e:     # a value per row needs the innermost axis to be the reduced one
+        T.chain_reduce([torch.zeros((4, 6, 16), device=cuda), torch.zeros((4, 6, 1), device=cuda)], "p0 * p1", axis=1)
+    assert e.value.status == T._lib.ERR_UNSUPPORTED
