@@ -28,6 +28,13 @@ typedef struct tcab_module tcab_module;
  * "line:col: ...", like the reference's diagnostics) or TCAB_ERR_UNSUPPORTED (a construct the reference's
  * grammar has but this path does not evaluate) and *out is NULL. Needs no GPU. */
 TCAB_API int tcab_module_parse(const char* text, tcab_module** out);
+/* The same for a module spread over several files: paths[i] / texts[i] are the files, `root` names the entry file.
+ * The reference's loader reads the include graph from disk (internal/syntax/module.go:3-31); this library does
+ * no file I/O, the host hands the texts over. @include paths are relative to the including file, may not be
+ * absolute nor leave its directory; a file reached twice merges once; a cycle is an error; an included file's
+ * kernels follow the including file's own. */
+TCAB_API int tcab_module_parse_files(const char* const* paths, const char* const* texts, uint32_t n_files,
+                                     const char* root, tcab_module** out);
 TCAB_API void tcab_module_free(tcab_module* m);
 
 TCAB_API uint32_t tcab_module_kernel_count(const tcab_module* m);
@@ -36,20 +43,30 @@ TCAB_API uint32_t tcab_module_kernel_count(const tcab_module* m);
 TCAB_API const char* tcab_module_kernel_name(const tcab_module* m, uint32_t i);
 /* The name the output tensor is bound by: the returned `let`. */
 TCAB_API const char* tcab_module_kernel_output(const tcab_module* m, uint32_t i);
-/* Which entry point of tcab.h the kernel lowers to: "chain_reduce", "chain_contract" or "gemm_bias_act";
- * NULL with a message when the chain has no kernel class. */
+/* Which entry point of tcab.h the kernel lowers to: "chain_reduce", "chain_contract", "gemm_bias_act", "map",
+ * "softmax_rows" or "layernorm_rows"; a kernel of several let chains lists its launches joined by '+' (statement
+ * groups that spell a whole row softmax or layer-norm count as the one launch that replaces them). NULL with a
+ * message when a chain has no kernel class. */
 TCAB_API const char* tcab_module_kernel_class(const tcab_module* m, uint32_t i);
 
 /* What the kernel lowers to, as newline-separated key=value lines (the pointer lives as long as the module):
  * class, out, inputs (comma-separated tensor names in operand order), and for the chain classes map, combine,
  * post (canonical lambda text over p0.. and c0..: what tcab_chain_reduce / tcab_chain_contract receive), init,
  * captures (scalar parameter of each capture slot), axis (reduced position) or rhs_is_nk; for gemm_bias_act
- * a, b, bias, act; always scalars (the scalar parameters in declaration order). NULL with a message when the
- * chain has no kernel class. */
+ * a, b, bias, act; always scalars (the scalar parameters in declaration order). A kernel of several launches has
+ * class, out, launches (their number) and the keys of every launch prefixed "launch<i>."; locals lists the
+ * intermediates that need device memory from the caller (bound by name like every tensor), local.<name> gives
+ * each one's element type and dims. NULL with a message when a chain has no kernel class. */
 TCAB_API const char* tcab_module_kernel_describe(const tcab_module* m, uint32_t i);
 
+/* The kernel's tensors and scalar parameters, one per line: "<name>=<elem>[<dim>,...]" (a symbolic dim by its name,
+ * a constant one by its extent; " local" follows an intermediate between statements) and "<name>=<elem>" for a
+ * scalar. With it a host sizes the locals from the extents of the tensors it binds. */
+TCAB_API const char* tcab_module_kernel_signature(const tcab_module* m, uint32_t i);
+
 /* Launches kernel `kernel` (its launcher name) asynchronously on `stream` (a cudaStream_t). Every tensor
- * parameter and the output must be bound in tensor_names/tensors, every scalar parameter in
+ * parameter, the output and every local that tcab_module_kernel_describe lists must be bound in
+ * tensor_names/tensors (the caller owns all device memory, intermediates included), every scalar parameter in
  * scalar_names/scalars. Shapes are checked the way the generated launcher checks them
  * (internal/cg/cxx/launch.go:82-121): one extent per symbolic dim, constant extents exact. */
 TCAB_API int tcab_module_launch(const tcab_module* m, const char* kernel, const char* const* tensor_names,

@@ -1,6 +1,6 @@
 // pkg.cpp -- the builder rungs and the expression DSL (see pkg.h). The classification and launch
 // half lives in pkg_launch.cpp.
-#include "pkg.h"
+#include "pkg_ext.h"
 
 #include <cmath>
 #include <set>
@@ -85,6 +85,29 @@ pkg::Tensor Builder::Tensor(const std::string& name, Elem elem, const std::vecto
   t.name = name;
   t.dims = dims;
   t.elem = elem;
+  tensors_[name] = t;
+  g_.tensors.push_back(t);
+  return t;
+}
+
+pkg::Tensor Builder::Local(const std::string& name, Elem elem, const std::vector<pkg::Dim>& dims) {
+  if (final_) noteDeclErr("local " + name + ": builder already finalized by Build");
+  if (tensors_.count(name)) noteDeclErr("local " + name + ": already declared");
+  if (dims.empty()) noteDeclErr("local " + name + ": must be a tensor type");
+  bool dynamic = false;
+  for (const pkg::Dim& d : dims) {
+    noteDeclErr(checkDim(d, "local " + name));
+    dynamic = dynamic || d.extent == 0;
+  }
+  if (dims.size() > 1 && dynamic)
+    noteDeclErr("local " + name + ": rank " + std::to_string(dims.size()) +
+                " with dynamic extents is not v0 (a multiplicative GMEM size is not constructed)");
+  pkg::Tensor t;
+  t.b = this;
+  t.name = name;
+  t.dims = dims;
+  t.elem = elem;
+  t.local = true;
   tensors_[name] = t;
   g_.tensors.push_back(t);
   return t;
@@ -547,6 +570,24 @@ static Result<Stored> store(std::shared_ptr<Builder::Chain> cp, Builder* b, std:
   c.stored = true;
   g.statements.push_back(c.st);
   return r;
+}
+
+// EXTENSION (pkg_ext.h): the store of a map that no reduction follows.
+Result<Stored> ext::StoreMap(MidChain mid, const Tensor& t, const std::vector<Dim>& axes) {
+  auto cp = mid.c_;
+  Builder* b = cp->b;
+  if (cp->pending().empty()) {
+    if (axes.size() != cp->live.size()) {
+      cp->deferErr("store of a map: the stored axes must be all " + std::to_string(cp->live.size()) + " live axes, got " +
+                   std::to_string(axes.size()) + " (a map cannot drop an axis)");
+    } else {
+      for (size_t i = 0; i < axes.size(); ++i)
+        if (axes[i].name != cp->live[i].name)
+          cp->deferErr("store of a map: axis " + std::to_string(i) + " binds @" + axes[i].name + ", the live order requires @" +
+                       cp->live[i].name);
+    }
+  }
+  return store(cp, b, b->tensors_, b->g_, t, axes, [&](const Dim& d, const std::string& w) { return b->checkDim(d, w); });
 }
 
 Result<Stored> AfterReduce::StoreV(const Tensor& t, const std::vector<Dim>& axes) {

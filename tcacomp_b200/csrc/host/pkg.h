@@ -56,6 +56,7 @@ struct Tensor {
   std::string name;
   std::vector<Dim> dims;
   Elem elem = Elem::F32;
+  bool local = false;  // declared with Builder::Local: an intermediate between two statements, not a parameter
   const std::string& Name() const { return name; }
   Elem ElemType() const { return elem; }
   int Rank() const { return static_cast<int>(dims.size()); }
@@ -123,6 +124,9 @@ class AfterReduce;
 class AfterMap;
 class Tail;
 struct Stored {};
+namespace ext {
+Result<Stored> StoreMap(MidChain mid, const Tensor& t, const std::vector<Dim>& axes);  // the one added rung: pkg_ext.h
+}
 
 // A map lambda: a callable of 1-4 Expr parameters (its arity is checked against the operand count,
 // pkg/chain.go coerceMapFn) or of one std::vector<Expr> (variadic, any arity).
@@ -157,6 +161,10 @@ class Builder {
   pkg::Tensor Tensor(const std::string& name, Elem elem, pkg::Dim d0, D... rest) {
     return Tensor(name, elem, std::vector<pkg::Dim>{d0, rest...});
   }
+  // pkg/builder.go:224 Local: a tensor handle that one statement stores into and a later one reads as an
+  // operand (the lowering of a `let` that is not the returned one). A rank-1 local may have a dynamic extent; a
+  // local of rank >= 2 must be fully static ("a multiplicative GMEM size is not constructed").
+  pkg::Tensor Local(const std::string& name, Elem elem, const std::vector<pkg::Dim>& dims);
   Expr ScalarParam(const std::string& name, Elem elem);
   StmtIter Stmt();
   Result<Graph> Build();  // pkg/builder.go:340-370
@@ -204,6 +212,7 @@ class Builder {
   friend class AfterReduce;
   friend class AfterMap;
   friend class Tail;
+  friend Result<Stored> ext::StoreMap(MidChain mid, const pkg::Tensor& t, const std::vector<pkg::Dim>& axes);
   void noteDeclErr(const std::string& e);
   std::string checkDim(const pkg::Dim& d, const std::string& what) const;
   Expr bad(const std::string& e);
@@ -266,6 +275,7 @@ class MidChain {
 
  private:
   friend class RootAs;
+  friend Result<Stored> ext::StoreMap(MidChain mid, const Tensor& t, const std::vector<Dim>& axes);
   std::shared_ptr<Builder::Chain> c_;
 };
 class Tail {
@@ -311,7 +321,7 @@ Tail AfterMap::As(D... dims) { return AsV(std::vector<Dim>{dims...}); }
 std::string PrintLambda(const Expr& body, std::vector<std::string>* captures);
 
 struct Plan {
-  enum Kind { ChainReduce, ChainContract, GemmBiasAct } kind = ChainReduce;
+  enum Kind { ChainReduce, ChainContract, GemmBiasAct, Map, SoftmaxRows, LayernormRows } kind = ChainReduce;
   // ChainReduce
   std::string map_expr, combine_expr, post_expr;
   float init = 0.0f;
@@ -319,14 +329,26 @@ struct Plan {
   std::vector<std::string> inputs;         // tensor names, in operand order
   uint32_t reduce_axis = 0;                // position of the reduced dim in the operands
   bool rhs_is_nk = false;                  // ChainContract: the second operand is [n,k] rather than [k,n]
+  // ChainReduce / Map: how operand i is indexed -- 0 by every axis, 1 one value per row (it lacks the innermost
+  // axis), 2 one row shared by all rows (it has the innermost axis only)
+  std::vector<int> indexing;
   // GemmBiasAct
   std::string a, b, bias;                  // bias empty = none
   int act = TCAB_ACT_NONE;
+  // SoftmaxRows: inputs = {x}; LayernormRows: inputs = {x, gamma, beta}, eps_scalar names the scalar parameter
+  std::string eps_scalar;
   std::string out;
+  std::vector<std::string> fused_locals;   // locals of the statements this plan replaces: they need no memory
 };
 
 // Matches a statement to an operator class of the kernel library; err explains a chain no class covers.
 Result<Plan> Classify(const Statement& st);
+
+// The launches a graph lowers to, in order: every statement classified, after the statement groups that spell
+// a whole row chain -- max into a local, sum of exp(x - max) into a local, the normalising map (row softmax);
+// mean and variance into locals, the scale-and-shift map (layer-norm) -- have been replaced by the one-launch
+// operators tcab_softmax_rows / tcab_layernorm_rows. err names the first statement no class covers.
+Result<std::vector<Plan>> PlanGraph(const Graph& g);
 
 // Device bindings for a launch: the C spelling of the tca::Tensor arguments of the generated
 // launcher (internal/cg/cxx/launch.go:23-156), by tensor name; scalars by parameter name.

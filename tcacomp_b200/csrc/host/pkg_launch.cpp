@@ -2,6 +2,7 @@
 // statement to an operator class of the kernel library, check the bound tensors the way the
 // reference's generated launcher does (internal/cg/cxx/launch.go:23-156: every dim is derived from
 // its first tensor occurrence and every other occurrence must agree), call the C ABI.
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 
@@ -163,9 +164,11 @@ Result<Plan> Classify(const Statement& st) {
   if (match_gemm(st, &r.value)) return r;
 
   Plan& p = r.value;
-  // fp32 contraction: lhs[m,k] with rhs[k,n] or rhs[n,k], as (m, n, k), out[m,n], piped map without operands
+  // contraction with f32 arithmetic: lhs[m,k] with rhs[k,n] or rhs[n,k], as (m, n, k), out[m,n], piped map without
+  // operands; the operands may be f32, bf16, i32 or u32 (the lambda converts explicitly)
+  auto movable = [](Elem e) { return e == Elem::F32 || e == Elem::BF16 || e == Elem::I32 || e == Elem::U32; };
   if (st.operands.size() == 2 && st.reduces.size() == 1 && st.as.size() == 3 && st.iters.size() == 3 &&
-      st.operands[0].t.elem == Elem::F32 && st.operands[1].t.elem == Elem::F32 && st.operands[0].axes.size() == 2 &&
+      movable(st.operands[0].t.elem) && movable(st.operands[1].t.elem) && st.operands[0].axes.size() == 2 &&
       st.operands[1].axes.size() == 2 && st.out.elem == Elem::F32 && st.elem == Elem::F32 &&
       (!st.has_post || st.post_operands.empty())) {
     const std::string m = st.as[0].name, n = st.as[1].name, k = st.as[2].name;
@@ -193,9 +196,11 @@ Result<Plan> Classify(const Statement& st) {
     }
   }
 
-  // fp32 map | reduce | [map] over identically indexed operands
-  p.kind = Plan::ChainReduce;
-  if (st.reduces.size() != 1) {
+  // map | reduce | [map], or a map alone (the added rung of pkg_ext.h), over operands that are indexed by every
+  // iteration axis, by all but the innermost (one value per row) or by the innermost only (one shared row)
+  const bool map_only = st.reduces.empty();
+  p.kind = map_only ? Plan::Map : Plan::ChainReduce;
+  if (st.reduces.size() > 1) {
     r.err = "classify: " + std::to_string(st.reduces.size()) +
             " reductions in one chain; the kernel library reduces one axis per launch";
     return r;
@@ -204,22 +209,56 @@ Result<Plan> Classify(const Statement& st) {
     r.err = "classify: a map without tensor operands has no kernel class";
     return r;
   }
-  const std::vector<Dim>& axes = st.operands[0].axes;
-  for (const Operand& op : st.operands) {
-    if (op.t.elem != Elem::F32) {
-      r.err = "classify: operand " + op.t.name + " is " + ElemName(op.t.elem) +
-              "; the chain class is fp32 (bf16 operands are covered by the contraction and layer-norm classes)";
-      return r;
-    }
-    if (!same_axes(op.axes, axes)) {
-      r.err = "classify: operand " + op.t.name + " is not indexed like " + st.operands[0].t.name +
-              "; operands with different index sets (contractions, broadcasts) need the contraction class, "
-              "which this chain does not match";
-      return r;
-    }
+  // the operand with every iteration axis fixes the order of the axes in memory
+  const Operand* full = nullptr;
+  for (const Operand& op : st.operands)
+    if (op.axes.size() == st.iters.size() && full == nullptr) full = &op;
+  if (full == nullptr) {
+    r.err = "classify: no operand carries every iteration axis; a chain needs one operand that fixes the layout";
+    return r;
   }
-  if (axes.size() != st.iters.size()) {
-    r.err = "classify: the operands do not carry every iteration axis";
+  const std::vector<Dim>& axes = full->axes;
+  std::vector<Dim> row_axes(axes.begin(), axes.end() - 1);       // all but the innermost
+  std::vector<Dim> col_axes(axes.end() - 1, axes.end());          // the innermost only
+  for (const Operand& op : st.operands) {
+    if (op.t.elem != Elem::F32 && op.t.elem != Elem::BF16 && op.t.elem != Elem::I32 && op.t.elem != Elem::U32) {
+      r.err = "classify: operand " + op.t.name + " is " + ElemName(op.t.elem) + "; the kernels move f32, bf16, i32 and u32";
+      return r;
+    }
+    int how = -1;
+    if (same_axes(op.axes, axes)) how = 0;
+    else if (axes.size() > 1 && same_axes(op.axes, row_axes)) how = 1;
+    else if (axes.size() > 1 && same_axes(op.axes, col_axes)) how = 2;
+    if (how < 0) {
+      r.err = "classify: operand " + op.t.name + " is not indexed like " + full->t.name +
+              ", nor by all but its innermost axis, nor by its innermost axis alone; operands with other index sets "
+              "(contractions, transposes) need the contraction class, which this chain does not match";
+      return r;
+    }
+    p.indexing.push_back(how);
+  }
+  if (st.has_post && !st.post_operands.empty()) {
+    r.err = "classify: a piped map with tensor operands is only covered by the contraction class";
+    return r;
+  }
+  std::string err;
+  if (map_only) {
+    if (!same_axes(st.as, axes) || !same_axes(st.out_axes, axes)) {
+      r.err = "classify: a stored map keeps the operands' axis order (a transposing store has no kernel class)";
+      return r;
+    }
+    if (st.out.elem != st.elem) {
+      r.err = std::string("classify: the map yields ") + ElemName(st.elem) + " but " + st.out.name + " holds " +
+              ElemName(st.out.elem) + "; convert explicitly";
+      return r;
+    }
+    p.map_expr = print_node(*st.map_body.node, &p.capture_names, &err);
+    if (!err.empty()) {
+      r.err = "classify: " + err;
+      return r;
+    }
+    for (const Operand& op : st.operands) p.inputs.push_back(op.t.name);
+    p.out = st.out.name;
     return r;
   }
   const std::string red = st.as.back().name;
@@ -235,12 +274,13 @@ Result<Plan> Classify(const Statement& st) {
             " (a transposing store has no kernel class)";
     return r;
   }
+  for (int how : p.indexing)
+    if (how != 0 && pos != static_cast<int>(axes.size()) - 1) {
+      r.err = "classify: an operand that lacks an axis is only taken when the reduced axis is the innermost one";
+      return r;
+    }
   if (st.out.elem != Elem::F32 || st.elem != Elem::F32) {
-    r.err = "classify: the chain class stores fp32";
-    return r;
-  }
-  if (st.has_post && !st.post_operands.empty()) {
-    r.err = "classify: a piped map with tensor operands is only covered by the contraction class";
+    r.err = "classify: the chain class folds and stores fp32 (convert the mapped value with an explicit cast)";
     return r;
   }
   const auto& rd = st.reduces[0];
@@ -250,7 +290,6 @@ Result<Plan> Classify(const Statement& st) {
   }
   p.init = static_cast<float>(rd.init.node->value);
   p.reduce_axis = static_cast<uint32_t>(pos);
-  std::string err;
   p.map_expr = print_node(*st.map_body.node, &p.capture_names, &err);
   std::vector<std::string> none;
   if (err.empty()) p.combine_expr = print_node(*rd.body.node, &none, &err);
@@ -265,6 +304,137 @@ Result<Plan> Classify(const Statement& st) {
   return r;
 }
 
+// ---- statement groups that spell a whole row chain ----------------------------------------------------------
+namespace {
+
+std::string printed(const Expr& e, std::vector<std::string>* caps) {
+  std::string err;
+  if (!e.node) return "";
+  const std::string s = print_node(*e.node, caps, &err);
+  return err.empty() ? s : "";
+}
+
+// a reduction over the innermost axis of `x` (operand 0, indexed by every axis) into a local with the other axes
+bool is_row_reduction(const Statement& st, size_t n_operands, std::string* map, std::string* comb, std::string* post,
+                      std::vector<std::string>* caps) {
+  if (st.reduces.size() != 1 || st.operands.size() != n_operands || st.operands[0].axes.size() != st.iters.size() ||
+      st.iters.size() < 2 || !st.out.local)
+    return false;
+  const auto& axes = st.operands[0].axes;
+  if (st.as.empty() || st.as.back().name != axes.back().name) return false;
+  for (size_t i = 1; i < st.operands.size(); ++i) {   // the others: one value per row
+    if (st.operands[i].axes.size() + 1 != axes.size()) return false;
+    for (size_t d = 0; d < st.operands[i].axes.size(); ++d)
+      if (st.operands[i].axes[d].name != axes[d].name) return false;
+  }
+  if (!st.reduces[0].init.node || st.reduces[0].init.node->kind != Node::Const) return false;
+  std::vector<std::string> none;
+  *map = printed(st.map_body, caps);
+  *comb = printed(st.reduces[0].body, &none);
+  *post = st.has_post ? printed(st.post_body, caps) : "";
+  return !map->empty() && !comb->empty() && none.empty() && (!st.has_post || (st.post_operands.empty() && !post->empty()));
+}
+
+bool used_elsewhere(const Graph& g, const std::string& tensor, size_t from, size_t to) {
+  for (size_t i = 0; i < g.statements.size(); ++i) {
+    if (i >= from && i < to) continue;
+    for (const Operand& op : g.statements[i].operands)
+      if (op.t.name == tensor) return true;
+    for (const Operand& op : g.statements[i].post_operands)
+      if (op.t.name == tensor) return true;
+  }
+  return false;
+}
+
+bool is_sum(const std::string& c) { return c == "(p0 + p1)" || c == "(p1 + p0)"; }
+bool is_max(const std::string& c) { return c == "fmaxf(p0, p1)" || c == "fmaxf(p1, p0)"; }
+
+// m = max_j x;  s = sum_j expf(x - m);  y = expf(x - m) / s      (x, y f32, same shape; m, s locals used nowhere else)
+bool match_softmax(const Graph& g, size_t at, Plan* p) {
+  if (at + 3 > g.statements.size()) return false;
+  const Statement &s1 = g.statements[at], &s2 = g.statements[at + 1], &s3 = g.statements[at + 2];
+  std::string map, comb, post;
+  std::vector<std::string> caps;
+  if (!is_row_reduction(s1, 1, &map, &comb, &post, &caps) || map != "p0" || !is_max(comb) || !post.empty()) return false;
+  if (!(s1.reduces[0].init.node->value == -__builtin_inf())) return false;
+  const Tensor x = s1.operands[0].t, m = s1.out;
+  if (x.elem != Elem::F32) return false;
+  if (!is_row_reduction(s2, 2, &map, &comb, &post, &caps) || map != "expf((p0 - p1))" || !is_sum(comb) || !post.empty() ||
+      s2.reduces[0].init.node->value != 0.0 || s2.operands[0].t.name != x.name || s2.operands[1].t.name != m.name)
+    return false;
+  const Tensor s = s2.out;
+  if (!s3.reduces.empty() || s3.operands.size() != 3 || s3.operands[0].t.name != x.name || s3.operands[1].t.name != m.name ||
+      s3.operands[2].t.name != s.name || s3.out.elem != Elem::F32 || s3.out.dims.size() != x.dims.size())
+    return false;
+  if (printed(s3.map_body, &caps) != "(expf((p0 - p1)) / p2)" || !caps.empty()) return false;
+  if (used_elsewhere(g, m.name, at, at + 3) || used_elsewhere(g, s.name, at, at + 3)) return false;
+  p->kind = Plan::SoftmaxRows;
+  p->inputs = {x.name};
+  p->out = s3.out.name;
+  p->fused_locals = {m.name, s.name};
+  return true;
+}
+
+// mean = (sum_j X) * inv_n;  var = (sum_j (X - mean)^2) * inv_n;  y = (X - mean) * rsqrtf(var + eps) * G + B
+// with X = x (f32 rows) or f32(x) (bf16 rows), G, B likewise gamma[j], beta[j], y converted back for bf16 rows;
+// inv_n and eps are captured scalar parameters. The statistics are f32 locals used nowhere else.
+bool match_layernorm(const Graph& g, size_t at, Plan* p) {
+  if (at + 3 > g.statements.size()) return false;
+  const Statement &s1 = g.statements[at], &s2 = g.statements[at + 1], &s3 = g.statements[at + 2];
+  std::string map, comb, post;
+  std::vector<std::string> c1, c2, c3;
+  if (!is_row_reduction(s1, 1, &map, &comb, &post, &c1)) return false;
+  const Tensor x = s1.operands[0].t, mean = s1.out;
+  const bool bf = x.elem == Elem::BF16;
+  if (x.elem != Elem::F32 && !bf) return false;
+  const std::string X = bf ? "static_cast<float>(p0)" : "p0";
+  if (map != X || !is_sum(comb) || post != "(p0 * c0)" || c1.size() != 1 || s1.reduces[0].init.node->value != 0.0) return false;
+  if (!is_row_reduction(s2, 2, &map, &comb, &post, &c2) || s2.operands[0].t.name != x.name || s2.operands[1].t.name != mean.name ||
+      map != "((" + X + " - p1) * (" + X + " - p1))" || !is_sum(comb) || post != "(p0 * c0)" || c2 != c1 ||
+      s2.reduces[0].init.node->value != 0.0)
+    return false;
+  const Tensor var = s2.out;
+  if (!s3.reduces.empty() || s3.operands.size() != 5 || s3.operands[0].t.name != x.name || s3.operands[1].t.name != mean.name ||
+      s3.operands[2].t.name != var.name || s3.out.elem != x.elem || s3.out.dims.size() != x.dims.size())
+    return false;
+  const Tensor gamma = s3.operands[3].t, beta = s3.operands[4].t;
+  if (gamma.elem != x.elem || beta.elem != x.elem || gamma.dims.size() != 1 || beta.dims.size() != 1) return false;
+  const std::string G = bf ? "static_cast<float>(p3)" : "p3", B = bf ? "static_cast<float>(p4)" : "p4";
+  const std::string body = "((((" + X + " - p1) * rsqrtf((p2 + c0))) * " + G + ") + " + B + ")";
+  if (printed(s3.map_body, &c3) != (bf ? "static_cast<__nv_bfloat16>(" + body + ")" : body) || c3.size() != 1) return false;
+  if (used_elsewhere(g, mean.name, at, at + 3) || used_elsewhere(g, var.name, at, at + 3)) return false;
+  p->kind = Plan::LayernormRows;
+  p->inputs = {x.name, gamma.name, beta.name};
+  p->out = s3.out.name;
+  p->eps_scalar = c3[0];
+  p->capture_names = c1;   // inv_n: checked against the row length at launch
+  p->fused_locals = {mean.name, var.name};
+  return true;
+}
+
+}  // namespace
+
+Result<std::vector<Plan>> PlanGraph(const Graph& g) {
+  Result<std::vector<Plan>> r;
+  for (size_t i = 0; i < g.statements.size();) {
+    Plan fused;
+    if (match_softmax(g, i, &fused) || match_layernorm(g, i, &fused)) {
+      r.value.push_back(fused);
+      i += 3;
+      continue;
+    }
+    const Result<Plan> one = Classify(g.statements[i]);
+    if (!one.ok()) {
+      r.err = "statement " + std::to_string(i) + " (" + g.statements[i].out.name + "): " + one.err;
+      r.value.clear();
+      return r;
+    }
+    r.value.push_back(one.value);
+    ++i;
+  }
+  return r;
+}
+
 const std::string& LastError() { return g_last_error; }
 
 namespace {
@@ -274,6 +444,7 @@ int elem_dtype(Elem e) {
     case Elem::F32: return TCAB_F32;
     case Elem::BF16: return TCAB_BF16;
     case Elem::I32: return TCAB_I32;
+    case Elem::U32: return TCAB_U32;
     default: return -1;
   }
 }
@@ -311,40 +482,91 @@ const Tensor* find_tensor(const Graph& g, const std::string& name) {
   return nullptr;
 }
 
+// An operand that lacks axes of the iteration is handed to the kernel library with the iteration's rank and
+// extent 1 where it has no axis: [rows..., 1] for a value per row, [1..., cols] for a shared row.
+tcab_tensor with_unit_axes(const tcab_tensor& t, int how, uint32_t rank) {
+  if (how == 0) return t;
+  tcab_tensor v = t;
+  v.rank = rank;
+  for (uint32_t i = 0; i < rank; ++i) v.dims[i] = 1;
+  if (how == 1) for (uint32_t i = 0; i < t.rank && i + 1 < rank; ++i) v.dims[i] = t.dims[i];
+  if (how == 2) v.dims[rank - 1] = t.dims[t.rank - 1];
+  return v;
+}
+
 }  // namespace
 
 int Launch(const Graph& g, const Bindings& bind, void* stream) {
   g_last_error.clear();
   std::map<std::string, uint32_t> extents;  // dim name -> extent from its first tensor occurrence
-  for (const Statement& st : g.statements) {
-    const Result<Plan> plan = Classify(st);
-    if (!plan.ok()) return fail(TCAB_ERR_UNSUPPORTED, plan.err);
-    const Plan& p = plan.value;
+  const Result<std::vector<Plan>> plans = PlanGraph(g);
+  if (!plans.ok()) return fail(TCAB_ERR_UNSUPPORTED, plans.err);
+  auto bound = [&](const std::string& name, tcab_tensor* out) {
+    const Tensor* t = find_tensor(g, name);
+    if (t == nullptr) return fail(TCAB_ERR_INVALID_ARG, "launch: tensor " + name + " is not declared");
+    if (t->local && bind.tensors.find(name) == bind.tensors.end())
+      return fail(TCAB_ERR_INVALID_ARG, "launch: local " + name + " is not bound: an intermediate between two statements "
+                                        "needs device memory of its shape from the caller, like every other tensor");
+    return bind_tensor(*t, bind, &extents, out);
+  };
+  for (const Plan& p : plans.value) {
     if (p.kind == Plan::GemmBiasAct) {
       tcab_tensor a, b, c, bias;
-      int rc = bind_tensor(*find_tensor(g, p.a), bind, &extents, &a);
-      if (rc == TCAB_OK) rc = bind_tensor(*find_tensor(g, p.b), bind, &extents, &b);
-      if (rc == TCAB_OK && !p.bias.empty()) rc = bind_tensor(*find_tensor(g, p.bias), bind, &extents, &bias);
-      if (rc == TCAB_OK) rc = bind_tensor(*find_tensor(g, p.out), bind, &extents, &c);
+      int rc = bound(p.a, &a);
+      if (rc == TCAB_OK) rc = bound(p.b, &b);
+      if (rc == TCAB_OK && !p.bias.empty()) rc = bound(p.bias, &bias);
+      if (rc == TCAB_OK) rc = bound(p.out, &c);
       if (rc != TCAB_OK) return rc;
       rc = tcab_gemm_bias_act(&a, &b, p.bias.empty() ? nullptr : &bias, p.act, &c, stream);
+      if (rc != TCAB_OK) return fail(rc, tcab_last_error());
+      continue;
+    }
+    if (p.kind == Plan::SoftmaxRows) {
+      tcab_tensor x, y;
+      int rc = bound(p.inputs[0], &x);
+      if (rc == TCAB_OK) rc = bound(p.out, &y);
+      if (rc != TCAB_OK) return rc;
+      rc = tcab_softmax_rows(&x, &y, stream);
+      if (rc != TCAB_OK) return fail(rc, tcab_last_error());
+      continue;
+    }
+    if (p.kind == Plan::LayernormRows) {
+      tcab_tensor x, gm, bt, y;
+      int rc = bound(p.inputs[0], &x);
+      if (rc == TCAB_OK) rc = bound(p.inputs[1], &gm);
+      if (rc == TCAB_OK) rc = bound(p.inputs[2], &bt);
+      if (rc == TCAB_OK) rc = bound(p.out, &y);
+      if (rc != TCAB_OK) return rc;
+      auto eps = bind.scalars.find(p.eps_scalar);
+      auto inv = bind.scalars.find(p.capture_names[0]);
+      if (eps == bind.scalars.end()) return fail(TCAB_ERR_INVALID_ARG, "launch: scalar " + p.eps_scalar + " is not bound");
+      if (inv == bind.scalars.end()) return fail(TCAB_ERR_INVALID_ARG, "launch: scalar " + p.capture_names[0] + " is not bound");
+      // the one-launch operator divides by the row length itself: the captured factor must be its reciprocal
+      const float want = 1.0f / static_cast<float>(x.dims[x.rank - 1]);
+      if (!(std::fabs(inv->second - want) <= 1e-6f * want))
+        return fail(TCAB_ERR_INVALID_ARG, "launch: scalar " + p.capture_names[0] + " must be 1 / (row length) for the mean and "
+                                          "variance statements to be a layer-norm");
+      rc = tcab_layernorm_rows(&x, &gm, &bt, eps->second, &y, stream);
       if (rc != TCAB_OK) return fail(rc, tcab_last_error());
       continue;
     }
     tcab_tensor ins[TCAB_MAX_INPUTS];
     if (p.inputs.size() > TCAB_MAX_INPUTS)
       return fail(TCAB_ERR_UNSUPPORTED, "launch: more than " + std::to_string(TCAB_MAX_INPUTS) + " operands");
+    uint32_t rank = 0;
     for (size_t i = 0; i < p.inputs.size(); ++i) {
-      const int rc = bind_tensor(*find_tensor(g, p.inputs[i]), bind, &extents, &ins[i]);
+      const int rc = bound(p.inputs[i], &ins[i]);
       if (rc != TCAB_OK) return rc;
+      if (i < p.indexing.size() && p.indexing[i] == 0 && rank == 0) rank = ins[i].rank;
     }
+    for (size_t i = 0; i < p.inputs.size() && i < p.indexing.size(); ++i) ins[i] = with_unit_axes(ins[i], p.indexing[i], rank);
     tcab_tensor out;
-    int rc = bind_tensor(*find_tensor(g, p.out), bind, &extents, &out);
+    int rc = bound(p.out, &out);
     if (rc != TCAB_OK) return rc;
     tcab_chain ch;
     std::memset(&ch, 0, sizeof(ch));
     ch.map_expr = p.map_expr.c_str();
-    ch.combine_expr = p.combine_expr.c_str();
+    ch.combine_expr = p.combine_expr.empty() ? nullptr : p.combine_expr.c_str();
     ch.post_expr = p.post_expr.empty() ? nullptr : p.post_expr.c_str();
     ch.init = p.init;
     if (p.capture_names.size() > TCAB_MAX_CAPTURES)
@@ -358,6 +580,8 @@ int Launch(const Graph& g, const Bindings& bind, void* stream) {
     }
     if (p.kind == Plan::ChainContract)
       rc = tcab_chain_contract(&ch, &ins[0], &ins[1], p.rhs_is_nk ? 1 : 0, &out, stream);
+    else if (p.kind == Plan::Map)
+      rc = tcab_map(&ch, ins, static_cast<uint32_t>(p.inputs.size()), &out, stream);
     else
       rc = tcab_chain_reduce(&ch, ins, static_cast<uint32_t>(p.inputs.size()), p.reduce_axis, &out, stream);
     if (rc != TCAB_OK) return fail(rc, tcab_last_error());

@@ -1,8 +1,11 @@
 // tca_syntax.cpp -- lexer, recursive-descent parser and lowering onto the builder rungs (see tca_syntax.h).
 #include "tca_syntax.h"
 
+#include "pkg_ext.h"
+
 #include <cctype>
 #include <cstdlib>
+#include <cstring>
 #include <map>
 #include <set>
 
@@ -113,7 +116,7 @@ struct Lexer {
 
 // ---- AST (design/syntax-design.md section 3, the subset) ---------------------------------------
 struct XNode {  // scalar expression
-  enum Kind { Lit, Name, Pipe, Unary, Binary, Call, Cast } kind = Lit;
+  enum Kind { Lit, Name, Pipe, Unary, Binary, Call, Cast, Select } kind = Lit;
   Elem lit_type = Elem::F32;
   double value = 0;
   std::string name;  // Name / operator / builtin / cast target
@@ -139,8 +142,15 @@ struct Kernel {
   std::vector<Param> params;
   Param ret;
   std::vector<std::string> dimvars;
-  std::string let_name, return_name;
-  std::vector<Stage> stages;
+  struct Let {
+    std::string name;
+    bool annotated = false;
+    Param annotation;          // the written `: tensor<...>` when present
+    std::vector<Stage> stages;
+    int line = 0, col = 0;
+  };
+  std::vector<Let> lets;       // in source order; a later let may bind an earlier one as an operand
+  std::string return_name;
   int line = 0, col = 0;
 };
 
@@ -246,7 +256,8 @@ struct Parser {
     return expect_punct(")");
   }
 
-  // ---- expressions: + - * / with C precedence; everything else in the grammar is recognised and refused
+  // ---- expressions: the operators of design/syntax-design.md section 2.7 with C precedence and associativity:
+  //   ?:  ||  &&  |  ^  &  == !=  < <= > >=  << >>  + -  * / %  unary - + ! ~
   bool primary(XNode* n) {
     n->line = tok.line;
     n->col = tok.col;
@@ -286,7 +297,12 @@ struct Parser {
         if (n->kind == XNode::Cast && n->args.size() != 1) return fail_at(n->line, n->col, "a cast takes one argument");
         return true;
       }
-      if (id == "true" || id == "false") return fail_at(n->line, n->col, "bool expressions have no kernel class on this path");
+      if (id == "true" || id == "false") {
+        n->kind = XNode::Lit;
+        n->lit_type = Elem::Bool;
+        n->value = id == "true" ? 1 : 0;
+        return true;
+      }
       n->kind = XNode::Name;
       n->name = id;
       return true;
@@ -294,32 +310,39 @@ struct Parser {
     return fail("expected an expression, found '" + tok.text + "'");
   }
   bool unary(XNode* n) {
-    if (is_punct("-") || is_punct("+")) {
-      const bool neg = is_punct("-");
+    for (const char* o : {"-", "+", "!", "~"}) {
+      if (!is_punct(o)) continue;
       const int l = tok.line, c = tok.col;
       bump();
       XNode x;
       if (!unary(&x)) return false;
-      if (!neg) { *n = x; return true; }
       n->kind = XNode::Unary;
-      n->name = "-";
+      n->name = o;
       n->args = {x};
       n->line = l;
       n->col = c;
       return true;
     }
-    if (is_punct("!") || is_punct("~")) return fail("operator '" + tok.text + "' has no kernel class on this path");
     return primary(n);
   }
+  // `|` also separates the stages of a chain: inside a lambda body it is the bit operator unless the next stage
+  // keyword follows it
+  bool pipe_follows() const {
+    Lexer probe = lx;
+    const Tok t = probe.next();
+    return t.kind == Tok::Ident && (t.text == "map" || t.text == "reduce");
+  }
   bool binary(XNode* n, int level) {
-    static const char* ops[2][2] = {{"+", "-"}, {"*", "/"}};
-    if (level == 2) return unary(n);
+    static const std::vector<std::vector<const char*>> ops = {{"||"}, {"&&"}, {"|"}, {"^"}, {"&"}, {"==", "!="},
+                                                              {"<=", ">=", "<", ">"}, {"<<", ">>"}, {"+", "-"}, {"*", "/", "%"}};
+    if (level == static_cast<int>(ops.size())) return unary(n);
     if (!binary(n, level + 1)) return false;
     for (;;) {
       const char* hit = nullptr;
       for (const char* o : ops[level])
         if (is_punct(o)) hit = o;
       if (!hit) break;
+      if (std::strcmp(hit, "|") == 0 && pipe_follows()) break;
       const int l = tok.line, c = tok.col;
       bump();
       XNode r;
@@ -336,8 +359,17 @@ struct Parser {
   }
   bool expr(XNode* n) {
     if (!binary(n, 0)) return false;
-    for (const char* o : {"?", "==", "!=", "<", "<=", ">", ">=", "&&", "||", "&", "^", "<<", ">>", "%"})
-      if (is_punct(o)) return fail(std::string("operator '") + o + "' has no kernel class on this path");
+    if (!is_punct("?")) return true;
+    const int l = tok.line, c = tok.col;
+    bump();
+    XNode a, b;
+    if (!expr(&a) || !expect_punct(":") || !expr(&b)) return false;   // right-associative
+    XNode sel;
+    sel.kind = XNode::Select;
+    sel.args = {*n, a, b};
+    sel.line = l;
+    sel.col = c;
+    *n = sel;
     return true;
   }
 
@@ -450,22 +482,27 @@ struct Parser {
         }
         if (!expect_punct(";")) return false;
       } else if (is_ident("let")) {
-        if (!k->let_name.empty()) return fail("one let chain per kernel: several chains have no kernel class on this path");
+        Kernel::Let let;
+        let.line = tok.line;
+        let.col = tok.col;
         bump();
-        if (!ident(&k->let_name)) return false;
+        if (!ident(&let.name)) return false;
+        for (const Kernel::Let& prev : k->lets)
+          if (prev.name == let.name) return fail_at(let.line, let.col, "let '" + let.name + "' is already bound (names are immutable)");
         if (is_punct(":")) {
           bump();
-          Param ignored;
-          if (!type(&ignored)) return false;
+          let.annotated = true;
+          if (!type(&let.annotation)) return false;
         }
         if (!expect_punct("=")) return false;
         for (;;) {
           Stage st;
           if (!stage(&st)) return false;
-          k->stages.push_back(st);
+          let.stages.push_back(st);
           if (is_punct("|")) bump(); else break;
         }
         if (!expect_punct(";")) return false;
+        k->lets.push_back(let);
       } else if (is_ident("return")) {
         bump();
         if (!ident(&k->return_name) || !expect_punct(";")) return false;
@@ -528,7 +565,8 @@ struct Lower {
       case XNode::Lit:
         if (n.lit_type == Elem::F32) return b.Float32(static_cast<float>(n.value));
         if (n.lit_type == Elem::I32) return b.Int32(static_cast<int32_t>(n.value));
-        return bad("u32 literals have no kernel class on this path");
+        if (n.lit_type == Elem::Bool) return b.Bool(n.value != 0);
+        return b.UInt32(static_cast<uint32_t>(n.value));
       case XNode::Pipe: {
         auto it = env.find("%0");
         return it == env.end() ? bad("%0 is not a parameter of this stage") : it->second;
@@ -546,10 +584,16 @@ struct Lower {
       }
       case XNode::Unary: {
         const XNode& a = n.args[0];  // a negated literal stays a literal (a reduction's init must be one)
-        if (a.kind == XNode::Lit && a.lit_type == Elem::F32) return b.Float32(-static_cast<float>(a.value));
-        if (a.kind == XNode::Lit && a.lit_type == Elem::I32) return b.Int32(-static_cast<int32_t>(a.value));
-        if (a.kind == XNode::Name && a.name == "inf_f32" && !env.count(a.name)) return b.Float32(-__builtin_inff());
-        return b.Neg(lower_expr(a, env, captures));
+        if (n.name == "-" && a.kind == XNode::Lit && a.lit_type == Elem::F32) return b.Float32(-static_cast<float>(a.value));
+        if (n.name == "-" && a.kind == XNode::Lit && a.lit_type == Elem::I32) return b.Int32(-static_cast<int32_t>(a.value));
+        if (n.name == "-" && a.kind == XNode::Name && a.name == "inf_f32" && !env.count(a.name)) return b.Float32(-__builtin_inff());
+        if (n.name == "-" && a.kind == XNode::Lit && a.lit_type != Elem::F32 && a.lit_type != Elem::I32)
+          return b.Neg(lower_expr(a, env, captures));
+        const Expr x = lower_expr(a, env, captures);
+        if (n.name == "-") return b.Neg(x);
+        if (n.name == "+") return b.Pos(x);
+        if (n.name == "!") return b.Not(x);
+        return b.BitsNot(x);
       }
       case XNode::Binary: {
         const Expr l = lower_expr(n.args[0], env, captures);
@@ -557,7 +601,27 @@ struct Lower {
         if (n.name == "+") return b.Add(l, r);
         if (n.name == "-") return b.Sub(l, r);
         if (n.name == "*") return b.Mul(l, r);
-        return b.Div(l, r);
+        if (n.name == "/") return b.Div(l, r);
+        if (n.name == "%") return b.Mod(l, r);
+        if (n.name == "==") return b.Eq(l, r);
+        if (n.name == "!=") return b.Ne(l, r);
+        if (n.name == "<") return b.Lt(l, r);
+        if (n.name == "<=") return b.Le(l, r);
+        if (n.name == ">") return b.Gt(l, r);
+        if (n.name == ">=") return b.Ge(l, r);
+        if (n.name == "&&") return b.And(l, r);
+        if (n.name == "||") return b.Or(l, r);
+        if (n.name == "&") return b.BitAnd(l, r);
+        if (n.name == "|") return b.BitOr(l, r);
+        if (n.name == "^") return b.BitXor(l, r);
+        if (n.name == "<<") return b.Shl(l, r);
+        return b.Shr(l, r);
+      }
+      case XNode::Select: {
+        const Expr c = lower_expr(n.args[0], env, captures);
+        const Expr x = lower_expr(n.args[1], env, captures);
+        const Expr y = lower_expr(n.args[2], env, captures);
+        return b.Select(c, x, y);
       }
       case XNode::Call: {
         std::vector<Expr> args;
@@ -610,66 +674,57 @@ struct Lower {
     return true;
   }
 
-  bool run(ParsedKernel* out) {
-    if (k.let_name.empty() || k.return_name != k.let_name)
-      return fail(k.line, k.col, "a kernel is one let chain followed by 'return <that let>'");
-    if (k.stages.size() < 2 || !k.stages[0].is_map || k.stages[1].is_map)
-      return fail(k.line, k.col, "a chain is map | reduce [| reduce]* [| map]: a store needs a reduction before it");
-    const Stage& root = k.stages[0];
-    const Stage& red0 = k.stages[1];
-    for (const Stage& st : k.stages)
-      for (const Binding& bd : st.bindings) {
-        const Param* decl = nullptr;
-        for (const Param& p : k.params)
-          if (p.is_tensor && p.name == bd.tensor) decl = &p;
-        if (decl == nullptr) return fail(bd.line, bd.col, "unknown tensor '" + bd.tensor + "'");
-        if (bd.dims.size() != decl->shape.size())
-          return fail(bd.line, bd.col, "tensor '" + bd.tensor + "' has rank " + std::to_string(decl->shape.size()) +
-                                           ", subscripted with " + std::to_string(bd.dims.size()) + " dimvars");
-        for (size_t i = 0; i < bd.dims.size(); ++i) {
-          bool declared = false;
-          for (const std::string& d : k.dimvars) declared = declared || d == bd.dims[i];
-          if (!declared) return fail(bd.line, bd.col, "'" + bd.dims[i] + "' is not a declared dimvar");
-          where[{bd.tensor, i}] = bd.dims[i];
-        }
-      }
-    // the root `as`: explicit, or the first reduce's as-list followed by the axis it removes (section 7.4)
-    std::vector<std::string> root_as_names = root.has_as ? root.as : red0.as;
+  // One let chain: map | reduce [| reduce]* [| map], or (the added rung of pkg_ext.h) a map alone. The returned let
+  // stores into the kernel's output, every other let into a Local whose type is the chain's output type
+  // (design/syntax-design.md 5.1 step 5; lowering table: `let` local tensor -> b.Local + Store).
+  bool lower_let(const Kernel::Let& let, bool returned) {
+    if (let.stages.empty() || !let.stages[0].is_map)
+      return fail(let.line, let.col, "a let chain begins with a root map");
+    const Stage& root = let.stages[0];
+    const bool map_only = let.stages.size() == 1;
+    if (!map_only && let.stages[1].is_map)
+      return fail(let.stages[1].line, let.stages[1].col, "a chain is map | reduce [| reduce]* [| map]: a second map needs a reduction before it");
+    // the root `as`: explicit; else the first reduce's as-list followed by the axis it removes (section 7.4); else,
+    // for a map alone, the bound dimvars in order of first appearance (section 5.1 step 2)
+    std::vector<std::string> root_as_names = root.as;
     if (!root.has_as) {
-      if (!red0.has_as) return fail(red0.line, red0.col, "either the root map or the reduce must carry an as-list");
-      int added = 0;
-      for (const std::string& dv : k.dimvars) {
-        bool used = false, kept = false;
-        for (const Binding& bd : root.bindings)
-          for (const std::string& d : bd.dims) used = used || d == dv;
-        for (const std::string& a : red0.as) kept = kept || a == dv;
-        if (used && !kept) { root_as_names.push_back(dv); ++added; }
+      std::vector<std::string> appear;
+      for (const Binding& bd : root.bindings)
+        for (const std::string& d : bd.dims) {
+          bool seen = false;
+          for (const std::string& a : appear) seen = seen || a == d;
+          if (!seen) appear.push_back(d);
+        }
+      if (map_only || !let.stages[1].has_as) {
+        root_as_names = appear;
+      } else {
+        const Stage& red0 = let.stages[1];
+        root_as_names = red0.as;
+        int added = 0;
+        for (const std::string& dv : k.dimvars) {
+          bool used = false, kept = false;
+          for (const std::string& d : appear) used = used || d == dv;
+          for (const std::string& a : red0.as) kept = kept || a == dv;
+          if (used && !kept) { root_as_names.push_back(dv); ++added; }
+        }
+        if (added != 1) return fail(red0.line, red0.col, "the reduce's as-list must drop exactly one axis");
       }
-      if (added != 1) return fail(red0.line, red0.col, "the reduce's as-list must drop exactly one axis");
     }
     size_t n_reduces = 0;
-    for (size_t i = 1; i < k.stages.size() && !k.stages[i].is_map; ++i) ++n_reduces;
+    for (size_t i = 1; i < let.stages.size() && !let.stages[i].is_map; ++i) ++n_reduces;
     if (n_reduces >= root_as_names.size())
-      return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class on this path");
+      return fail(let.line, let.col, "a fully reduced (scalar) result has no kernel class on this path");
     const std::vector<std::string> live_names(root_as_names.begin(), root_as_names.end() - static_cast<long>(n_reduces));
-
-    for (const Param& p : k.params) {
-      if (p.is_tensor) declare_tensor(p.name, p, nullptr);
-      else scalars[p.name] = b.ScalarParam(p.name, p.elem);
-    }
-    if (!k.ret.is_tensor) return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class on this path");
-    if (k.ret.shape.size() != live_names.size())
-      return fail(k.line, k.col, "the return type has rank " + std::to_string(k.ret.shape.size()) + " but the chain leaves " +
-                                     std::to_string(live_names.size()) + " axes");
-    const Tensor result = declare_tensor(k.let_name, k.ret, &live_names);
 
     // root map
     std::vector<Operand> ops;
     if (!bind_dimvars(root, &ops)) return false;
     std::vector<Dim> iters;
     for (const std::string& dv : k.dimvars) {
+      bool in_chain = false;
+      for (const std::string& a : root_as_names) in_chain = in_chain || a == dv;
       auto it = dimvar.find(dv);
-      if (it != dimvar.end()) iters.push_back(it->second);
+      if (in_chain && it != dimvar.end()) iters.push_back(it->second);
     }
     if (root.params.size() != root.bindings.size())
       return fail(root.line, root.col, "root map: " + std::to_string(root.params.size()) + " lambda parameters for " +
@@ -677,23 +732,26 @@ struct Lower {
     const std::set<std::string> caps(root.captures.begin(), root.captures.end());
     for (const std::string& c : root.captures)
       if (!scalars.count(c)) return fail(root.line, root.col, "capture '" + c + "' is not a scalar parameter of the kernel");
+    Elem elem = Elem::F32;   // element type flowing out of the chain so far
     Lambda fn([&](const std::vector<Expr>& a) {
       std::map<std::string, Expr> env;
       for (size_t i = 0; i < root.params.size(); ++i) env[root.params[i].name] = a[i];
-      return lower_expr(root.body, env, caps);
+      const Expr e = lower_expr(root.body, env, caps);
+      elem = e.typ;
+      return e;
     });
     auto ra = b.Stmt().IterV(iters).Map(ops, fn);
     if (!ra.ok()) return fail(root.line, root.col, err.empty() ? ra.err : err.substr(err.find(": ") + 2));
 
     std::vector<Dim> root_as;
-    if (!axes_of(root_as_names, root.has_as ? root.line : red0.line, root.has_as ? root.col : red0.col, &root_as)) return false;
+    if (!axes_of(root_as_names, root.line, root.col, &root_as)) return false;
     MidChain mid = ra.value.AsV(root_as);
 
     // reduces
     size_t si = 1;
     Result<AfterReduce> ar;
-    for (; si < k.stages.size() && !k.stages[si].is_map; ++si) {
-      const Stage& rs = k.stages[si];
+    for (; si < let.stages.size() && !let.stages[si].is_map; ++si) {
+      const Stage& rs = let.stages[si];
       const Expr init = lower_expr(rs.init, {}, {});
       Combiner comb = [&](Expr acc, Expr v) {
         std::map<std::string, Expr> env;
@@ -705,40 +763,107 @@ struct Lower {
       if (!ar.ok()) return fail(rs.line, rs.col, ar.err);
       if (!err.empty()) return false;
     }
-    // live axes now: root_as minus one per reduce
-    std::vector<Dim> live(root_as.begin(), root_as.end() - static_cast<long>(si - 1));
+    std::vector<Dim> live(root_as.begin(), root_as.end() - static_cast<long>(n_reduces));
 
-    Result<Stored> st;
-    if (si < k.stages.size()) {
-      const Stage& pm = k.stages[si];
-      if (si + 1 != k.stages.size()) return fail(pm.line, pm.col, "nothing may follow the piped map");
+    // a piped map, lowered before the result is declared: a Local takes the chain's final element type
+    Result<AfterMap> am;
+    const bool piped = si < let.stages.size();
+    std::vector<Dim> pas = live;
+    if (piped) {
+      const Stage& pm = let.stages[si];
+      if (si + 1 != let.stages.size()) return fail(pm.line, pm.col, "nothing may follow the piped map");
       std::vector<Operand> pops;
       if (!bind_dimvars(pm, &pops)) return false;
       if (pm.params.size() != pm.bindings.size() + 1)
         return fail(pm.line, pm.col, "piped map: the lambda takes the piped value plus one parameter per operand (arity)");
       const std::set<std::string> pcaps(pm.captures.begin(), pm.captures.end());
+      for (const std::string& c : pm.captures)
+        if (!scalars.count(c)) return fail(pm.line, pm.col, "capture '" + c + "' is not a scalar parameter of the kernel");
       Lambda pfn([&](const std::vector<Expr>& a) {
         std::map<std::string, Expr> env;
         for (size_t i = 0; i < pm.params.size(); ++i) env[pm.params[i].name] = a[i];
-        return lower_expr(pm.body, env, pcaps);
+        const Expr e = lower_expr(pm.body, env, pcaps);
+        elem = e.typ;
+        return e;
       });
-      auto am = ar.value.Map(pops, pfn);
+      am = ar.value.Map(pops, pfn);
       if (!am.ok()) return fail(pm.line, pm.col, err.empty() ? am.err : err.substr(err.find(": ") + 2));
-      std::vector<Dim> pas = live;
       if (pm.has_as) {
         pas.clear();
         if (!axes_of(pm.as, pm.line, pm.col, &pas)) return false;
       }
-      st = am.value.AsV(pas).StoreV(result, live);
-    } else {
-      st = ar.value.StoreV(result, live);
     }
-    if (!st.ok()) return fail(k.line, k.col, st.err);
+
+    // where the chain stores: the kernel's output for the returned let, a Local otherwise
+    Tensor result;
+    if (returned) {
+      if (!k.ret.is_tensor) return fail(k.line, k.col, "a fully reduced (scalar) return has no kernel class on this path");
+      if (k.ret.shape.size() != live_names.size())
+        return fail(k.line, k.col, "the return type has rank " + std::to_string(k.ret.shape.size()) + " but the chain leaves " +
+                                       std::to_string(live_names.size()) + " axes");
+      result = declare_tensor(let.name, k.ret, &live_names);
+    } else {
+      if (let.annotated) {  // rule 24: the annotation equals the inferred type
+        if (!let.annotation.is_tensor || let.annotation.shape.size() != live.size())
+          return fail(let.line, let.col, "let '" + let.name + "': the annotation has rank " +
+                                             std::to_string(let.annotation.shape.size()) + " but the chain leaves " +
+                                             std::to_string(live.size()) + " axes");
+        if (let.annotation.elem != elem)
+          return fail(let.line, let.col, std::string("let '") + let.name + "': the annotation says " + ElemName(let.annotation.elem) +
+                                             " but the chain yields " + ElemName(elem));
+      }
+      result = b.Local(let.name, elem, live);
+      tensors[let.name] = result;
+    }
+    Result<Stored> st;
+    if (piped) st = am.value.AsV(pas).StoreV(result, live);
+    else if (map_only) st = ext::StoreMap(mid, result, live);
+    else st = ar.value.StoreV(result, live);
+    if (!st.ok()) return fail(let.line, let.col, st.err);
+    return true;
+  }
+
+  bool run(ParsedKernel* out) {
+    if (k.lets.empty()) return fail(k.line, k.col, "a kernel binds at least one let chain and returns one of them");
+    const Kernel::Let* returned = nullptr;
+    for (const Kernel::Let& l : k.lets)
+      if (l.name == k.return_name) returned = &l;
+    if (returned == nullptr) return fail(k.line, k.col, "'return' must name a let-bound tensor of this kernel");
+    // constant extents of parameters get one dim per dimvar that subscripts them: collect the subscripts first
+    std::set<std::string> bound_lets;
+    for (const Kernel::Let& l : k.lets) {
+      for (const Stage& st : l.stages)
+        for (const Binding& bd : st.bindings) {
+          const Param* decl = nullptr;
+          for (const Param& p : k.params)
+            if (p.is_tensor && p.name == bd.tensor) decl = &p;
+          if (decl == nullptr) {
+            if (bound_lets.count(bd.tensor)) continue;   // an earlier let: checked when it is bound
+            return fail(bd.line, bd.col, "unknown tensor '" + bd.tensor + "'");
+          }
+          if (bd.dims.size() != decl->shape.size())
+            return fail(bd.line, bd.col, "tensor '" + bd.tensor + "' has rank " + std::to_string(decl->shape.size()) +
+                                             ", subscripted with " + std::to_string(bd.dims.size()) + " dimvars");
+          for (size_t i = 0; i < bd.dims.size(); ++i) {
+            bool declared = false;
+            for (const std::string& d : k.dimvars) declared = declared || d == bd.dims[i];
+            if (!declared) return fail(bd.line, bd.col, "'" + bd.dims[i] + "' is not a declared dimvar");
+            where[{bd.tensor, i}] = bd.dims[i];
+          }
+        }
+      bound_lets.insert(l.name);
+    }
+    for (const Param& p : k.params) {
+      if (p.is_tensor) declare_tensor(p.name, p, nullptr);
+      else scalars[p.name] = b.ScalarParam(p.name, p.elem);
+    }
+    for (const Kernel::Let& l : k.lets)
+      if (!lower_let(l, &l == returned)) return false;
     auto g = b.Build();
     if (!g.ok()) return fail(k.line, k.col, g.err);
     out->name = k.name;
     out->cxx_name = k.cxx_name;
-    out->output = k.let_name;
+    out->output = k.return_name;
     out->graph = g.value;
     return true;
   }
@@ -746,25 +871,62 @@ struct Lower {
 
 }  // namespace
 
-Result<std::vector<ParsedKernel>> ParseModule(const std::string& text) {
-  Result<std::vector<ParsedKernel>> r;
-  Parser p(text);
+namespace {
+
+// filepath.Clean / Dir for the virtual file set ('/'-separated)
+std::string clean_path(const std::string& p) {
+  std::vector<std::string> parts;
+  const bool abs = !p.empty() && p[0] == '/';
+  size_t i = 0;
+  while (i <= p.size()) {
+    const size_t j = p.find('/', i);
+    const std::string part = p.substr(i, j == std::string::npos ? std::string::npos : j - i);
+    if (part == "..") {
+      if (!parts.empty() && parts.back() != "..") parts.pop_back();
+      else if (!abs) parts.push_back("..");
+    } else if (!part.empty() && part != ".") {
+      parts.push_back(part);
+    }
+    if (j == std::string::npos) break;
+    i = j + 1;
+  }
+  std::string out = abs ? "/" : "";
+  for (size_t k = 0; k < parts.size(); ++k) out += (k ? "/" : "") + parts[k];
+  return out.empty() ? "." : out;
+}
+std::string dir_of(const std::string& p) {
+  const size_t j = p.rfind('/');
+  return j == std::string::npos ? "." : (j == 0 ? "/" : p.substr(0, j));
+}
+
+struct ParsedFile {
   std::vector<Kernel> kernels;
+  struct Include { std::string path; int line, col; };
+  std::vector<Include> includes;
+};
+
+// One file: its kernels and its include requests (unresolved).
+bool parse_file(const std::string& text, const std::string& name, ParsedFile* out, std::string* err) {
+  Parser p(text);
   std::string pending_cxx;
   while (p.tok.kind != Tok::End && p.err.empty()) {
     if (p.is_punct("@")) {
       p.bump();
-      std::string name;
-      if (!p.ident(&name)) break;
-      if (name == "include") {
-        p.fail("@include needs a module loader; pass the included text in the same module instead");
-        break;
+      std::string ann;
+      if (!p.ident(&ann)) break;
+      if (ann == "include") {   // '@include' stringLit ';' (design/syntax-design.md: includeDecl)
+        const int l = p.tok.line, c = p.tok.col;
+        if (p.tok.kind != Tok::String) { p.fail("@include takes a string literal"); break; }
+        out->includes.push_back({p.tok.text, l, c});
+        p.bump();
+        if (!p.expect_punct(";")) break;
+        continue;
       }
       std::string cxx;
-      if (!p.keyed(name == "name" ? &cxx : nullptr)) break;
-      if (name == "runtime") {
+      if (!p.keyed(ann == "name" ? &cxx : nullptr)) break;
+      if (ann == "runtime") {
         if (!p.expect_punct(";")) break;
-      } else if (name == "name") {
+      } else if (ann == "name") {
         pending_cxx = cxx;
       }
       continue;
@@ -772,13 +934,66 @@ Result<std::vector<ParsedKernel>> ParseModule(const std::string& text) {
     Kernel k;
     if (!p.kernel(&k, pending_cxx)) break;
     pending_cxx.clear();
-    kernels.push_back(k);
+    out->kernels.push_back(k);
   }
   if (!p.err.empty()) {
-    r.err = p.err;
-    return r;
+    *err = name.empty() ? p.err : name + ":" + p.err;
+    return false;
   }
+  return true;
+}
+
+// internal/syntax/module.go:86-124 resolveIncludes: depth-first, an included file's kernels land after the
+// including file's own, a file reached twice merges once (include guard), a file that includes one of its
+// includers is a cycle; paths are relative to the including file and may not leave its directory.
+struct Loader {
+  const std::vector<SourceFile>& files;
+  std::set<std::string> processed;
+  std::string err;
+  bool prefix = true;   // diagnostics carry the file's path (not for a module given as one text)
+
+  const SourceFile* find(const std::string& path) const {
+    for (const SourceFile& f : files)
+      if (clean_path(f.path) == path) return &f;
+    return nullptr;
+  }
+  bool resolve(ParsedFile* m, const std::string& path, std::set<std::string> stack) {
+    for (const ParsedFile::Include& inc : m->includes) {
+      auto bad = [&](const std::string& msg) {
+        err = (prefix ? path + ":" : std::string()) + std::to_string(inc.line) + ":" + std::to_string(inc.col) + ": " + msg;
+        return false;
+      };
+      if (!inc.path.empty() && inc.path[0] == '/')
+        return bad("@include path \"" + inc.path + "\" must be relative to the including file");
+      const std::string dir = dir_of(path);
+      const std::string resolved = clean_path(dir + "/" + inc.path);
+      const bool within = dir == "." ? (resolved.rfind("..", 0) != 0) : (resolved == dir || resolved.rfind(dir + "/", 0) == 0);
+      if (!within) return bad("@include path \"" + inc.path + "\" escapes the including file's directory");
+      const SourceFile* f = find(resolved);
+      if (f == nullptr) return bad("missing include file \"" + inc.path + "\"");
+      if (stack.count(resolved)) return bad("@include cycle: " + resolved + " is already being loaded");
+      if (processed.count(resolved)) continue;
+      ParsedFile sub;
+      if (!parse_file(f->text, resolved, &sub, &err)) return false;
+      processed.insert(resolved);
+      std::set<std::string> inner = stack;
+      inner.insert(resolved);
+      if (!resolve(&sub, resolved, inner)) return false;
+      m->kernels.insert(m->kernels.end(), sub.kernels.begin(), sub.kernels.end());
+    }
+    return true;
+  }
+};
+
+Result<std::vector<ParsedKernel>> lower_all(const std::vector<Kernel>& kernels) {
+  Result<std::vector<ParsedKernel>> r;
+  std::set<std::string> names;
   for (const Kernel& k : kernels) {
+    if (!names.insert(k.name).second) {   // module rule: kernel names are unique across the merged module
+      r.err = std::to_string(k.line) + ":" + std::to_string(k.col) + ": kernel '" + k.name + "' is defined twice in the module";
+      r.value.clear();
+      return r;
+    }
     Lower lw(k);
     ParsedKernel pk;
     if (!lw.run(&pk)) {
@@ -789,6 +1004,31 @@ Result<std::vector<ParsedKernel>> ParseModule(const std::string& text) {
     r.value.push_back(pk);
   }
   return r;
+}
+
+}  // namespace
+
+Result<std::vector<ParsedKernel>> ParseModuleFiles(const std::vector<SourceFile>& files, const std::string& root) {
+  Result<std::vector<ParsedKernel>> r;
+  Loader ld{files, {}, "", files.size() > 1};
+  const std::string root_path = clean_path(root);
+  const SourceFile* f = ld.find(root_path);
+  if (f == nullptr) {
+    r.err = "cannot read source file: " + root;
+    return r;
+  }
+  ParsedFile m;
+  if (!parse_file(f->text, files.size() > 1 ? root_path : "", &m, &r.err)) return r;
+  ld.processed.insert(root_path);
+  if (!ld.resolve(&m, root_path, {root_path})) {
+    r.err = ld.err;
+    return r;
+  }
+  return lower_all(m.kernels);
+}
+
+Result<std::vector<ParsedKernel>> ParseModule(const std::string& text) {
+  return ParseModuleFiles({SourceFile{"module.tca", text}}, "module.tca");
 }
 
 }  // namespace pkg

@@ -12,11 +12,16 @@
 //   map stage   ::= 'map' 'on' '(' bindings ')' [ 'as' '(' idents ')' ] [ '[' captures ']' ] '(' params ')' [ '->' elem ] ':' expr
 //   reduce      ::= 'reduce' '(' 'init' '=' expr ')' 'on' '(' acc ':' elem ',' ( '%0' | ident ) [ ':' elem ] ')'
 //                   [ 'as' '(' idents ')' ] '->' elem ':' expr
-//   expr        ::= + - * / , unary -, calls of the fp32 builtins, casts elem '(' expr ')', literals
-//                   (1.5f, 3, 8u, inf_f32), names (lambda parameters, captured scalar parameters)
+//   expr        ::= cond '?' expr ':' expr | the binary operators || && | ^ & == != < <= > >= << >> + - * / % with C
+//                   precedence | unary - + ! ~ | calls of the builtins | casts elem '(' expr ')' | literals
+//                   (1.5f, 3, 8u, true, false, inf_f32) | names (lambda parameters, captured scalar parameters)
 //
-// Comparisons, ?:, bit operators and bool are parsed by the reference but have no kernel class here;
-// they are reported as unsupported. One kernel = one let chain ending in `return <that let>`.
+// A kernel may bind several lets (design/syntax-design.md 5.1, lowering table: a `let` that is not the returned
+// one becomes a Local that its chain stores into and later chains bind as an operand, pkg/builder.go:224). An
+// operand may bind a subset of the iteration's dimvars (m[i] inside an (i, j) iteration). One construct goes
+// beyond the reference's v0: a let whose chain is a map alone (the reference requires a reduction before a
+// store, pkg/chain.go:433-438) is lowered through the added rung of pkg_ext.h, because the kernel library has
+// the map-only operator; it is what the last statement of a softmax or a layer-norm needs.
 // Trailing commas are accepted in every list; // and /* */ comments are skipped.
 #pragma once
 
@@ -38,6 +43,16 @@ struct ParsedKernel {
 // Parses a module and lowers every kernel through the builder rungs. On failure err carries
 // "line:col: message" like the reference's diagnostics.
 Result<std::vector<ParsedKernel>> ParseModule(const std::string& text);
+
+// A module spread over several files (the reference's loader reads them from disk, internal/syntax/module.go:
+// 3-31; here the host hands over the texts, this library does no file I/O): `root` names the entry file among
+// `files`; @include paths are resolved relative to the including file, may not be absolute nor leave its
+// directory, a file reached twice merges once, a cycle is an error; an included file's kernels land after the
+// including file's own. Diagnostics of included files are prefixed with their path.
+struct SourceFile {
+  std::string path, text;
+};
+Result<std::vector<ParsedKernel>> ParseModuleFiles(const std::vector<SourceFile>& files, const std::string& root);
 
 }  // namespace pkg
 }  // namespace tcab

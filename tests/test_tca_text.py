@@ -53,7 +53,7 @@ def test_host_library_exports_what_the_header_declares():
     text = open(os.path.join(ROOT, "include", "tcab_host.h")).read()
     names = sorted(set(re.findall(r"^TCAB_API[^;]*?\b(tcab_\w+)\s*\(", text, flags=re.M | re.S)))
     lib = tca.load()
-    assert len(names) == 9
+    assert len(names) >= 11
     for n in names:
         assert hasattr(lib, n), f"{n} declared in include/tcab_host.h but not exported"
     assert sorted(s[0] for s in tca.SYMBOLS) == names
@@ -71,11 +71,17 @@ def test_modules_parse_and_classify():
 @pytest.mark.parametrize("text,status,needle", [
     ("kernel k(x: tensor<dtype=f32, shape=[R, 4]>) -> f32 { }", 1, "1:41: a constant extent is an unsigned literal"),
     ("kernel k(x: tensor<dtype=f32, shape=[R]>) -> tensor<dtype=f32, shape=[R]> {\n  dimvar i;\n"
-     "  let o = map on(x[i]) (v: f32): v;\n  return o; }", 1, "a store needs a reduction"),
-    ('@include "other.tca";', 5, "module loader"),
+     "  let o = map on(x[i]) (v: f32): v | map on() (w: f32): w;\n  return o; }", 1, "a second map needs a reduction before it"),
+    ('@include "other.tca";', 1, 'missing include file "other.tca"'),
+    ('@include "/etc/other.tca";', 1, "must be relative to the including file"),
+    ('@include "../other.tca";', 1, "escapes the including file's directory"),
     (AFFINE_ROWSUM.replace("[s, t]", "[s]"), 1, "'t' is used but not captured"),
     (AFFINE_ROWSUM.replace("x[i][j]", "x[i]"), 1, "has rank 2, subscripted with 1"),
-    (AFFINE_ROWSUM.replace("acc + %0", "acc < %0 ? acc : %0"), 5, "no kernel class"),
+    (AFFINE_ROWSUM.replace("acc + %0", "acc < %0 ? acc : 1"), 1, "select: branches must have identical types"),
+    (AFFINE_ROWSUM.replace("(s * v + t) * (s * v + t)", "v * 2"), 1, "operand types differ (f32 vs i32)"),
+    (AFFINE_ROWSUM.replace("(s * v + t) * (s * v + t)", "v > 0.0f"), 1, "homogeneous reducer"),
+    (AFFINE_ROWSUM.replace("return y;", "return z;"), 1, "'return' must name a let-bound tensor"),
+    (AFFINE_ROWSUM.replace("return y;", "let y = map on(x[i][j]) (v: f32): v; return y;"), 1, "already bound"),
 ])
 def test_diagnostics(text, status, needle):
     from tcacomp_b200 import TcabError, tca
@@ -84,6 +90,119 @@ def test_diagnostics(text, status, needle):
     assert e.value.status == status, e.value.message
     assert needle in e.value.message
     assert re.match(r"\d+:\d+: ", e.value.message)
+
+
+SOFTMAX_BY_STATEMENTS = '''
+// Row softmax written statement by statement: the two reductions store into locals (pkg/builder.go:224,
+// pkg/local_test.go:17-68), the last statement is the rank-preserving map.
+@name(cxx="SoftmaxRows")
+kernel softmax_rows(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R, C]> {
+  dimvar (i, j);
+  let m = map on(x[i][j]) (v: f32) -> f32: v
+        | reduce(init = -inf_f32) on(acc: f32, %0: f32) as (i) -> f32: fmaxf(acc, %0);
+  let s = map on(x[i][j], m[i]) (v: f32, mx: f32) -> f32: expf(v - mx)
+        | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i) -> f32: acc + %0;
+  let y = map on(x[i][j], m[i], s[i]) (v: f32, mx: f32, sum: f32) -> f32: expf(v - mx) / sum;
+  return y;
+}
+'''
+
+LAYERNORM_BY_STATEMENTS = '''
+@name(cxx="LayernormRows")
+kernel layernorm_rows(x: tensor<dtype=bf16, shape=[R, C]>, gamma: tensor<dtype=bf16, shape=[C]>,
+                      beta: tensor<dtype=bf16, shape=[C]>, inv_n: f32, eps: f32) -> tensor<dtype=bf16, shape=[R, C]> {
+  dimvar (i, j);
+  let mean = map on(x[i][j]) (v: bf16) -> f32: f32(v)
+           | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i) -> f32: acc + %0
+           | map on() [inv_n] (t: f32) -> f32: t * inv_n;
+  let var = map on(x[i][j], mean[i]) (v: bf16, mu: f32) -> f32: (f32(v) - mu) * (f32(v) - mu)
+          | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i) -> f32: acc + %0
+          | map on() [inv_n] (t: f32) -> f32: t * inv_n;
+  let y = map on(x[i][j], mean[i], var[i], gamma[j], beta[j]) [eps]
+            (v: bf16, mu: f32, s2: f32, g: bf16, b: bf16) -> bf16:
+              bf16((f32(v) - mu) * rsqrtf(s2 + eps) * f32(g) + f32(b));
+  return y;
+}
+'''
+
+TYPED_KERNELS = '''
+@name(cxx="ReluSelect")
+kernel relu_select(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R, C]> {
+  dimvar (i, j);
+  let y = map on(x[i][j]) (v: f32) -> f32: v > 0.0f ? v : 0.0f;     // Select(Gt(v, 0), v, 0)
+  return y;
+}
+@name(cxx="CountMultiples")
+kernel count_multiples(k: tensor<dtype=i32, shape=[R, C]>, w: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R]> {
+  dimvar (i, j);
+  let n = map on(k[i][j], w[i][j]) (a: i32, b: f32) -> f32: ((a % 3 == 0 && a != 9) || (a & 1) == 1 ? 1.0f : 0.0f) * b
+        | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i) -> f32: acc + %0;
+  return n;
+}
+@name(cxx="BiasRelu")
+kernel bias_relu(x: tensor<dtype=f32, shape=[R, C]>, bias: tensor<dtype=f32, shape=[C]>) -> tensor<dtype=bf16, shape=[R, C]> {
+  dimvar (i, j);
+  let y = map on(x[i][j], bias[j]) (v: f32, b: f32) -> bf16: bf16(fmaxf(v + b, 0.0f));
+  return y;
+}
+'''
+
+
+def test_several_let_chains_lower_to_locals_and_whole_row_chains_are_recognised():
+    from tcacomp_b200 import tca
+    m = tca.Module(SOFTMAX_BY_STATEMENTS + LAYERNORM_BY_STATEMENTS + TYPED_KERNELS)
+    # max | sum of exp | normalise over one x with locals used nowhere else: the one-launch operator replaces them
+    assert m.kernels["SoftmaxRows"]["class"] == "softmax_rows"
+    d = m.describe("SoftmaxRows")
+    assert d["inputs"] == "x" and d["out"] == "y" and d["fused_locals"] == "m,s" and d.get("locals", "") == ""
+    assert m.kernels["LayernormRows"]["class"] == "layernorm_rows"
+    d = m.describe("LayernormRows")
+    assert d["inputs"] == "x,gamma,beta" and d["eps"] == "eps" and d["inv_n"] == "inv_n" and d["fused_locals"] == "mean,var"
+    # the typed vocabulary, printed the way the reference's emitter prints it (internal/cg/cxx/naming.go:126-183)
+    assert m.describe("ReluSelect") == {"class": "map", "out": "y", "inputs": "x", "map": "((p0 > 0.0f) ? p0 : 0.0f)",
+                                        "captures": "", "scalars": ""}
+    d = m.describe("CountMultiples")
+    assert d["class"] == "chain_reduce" and d["axis"] == "1"
+    assert d["map"] == "((((((p0 % 3) == 0) && (p0 != 9)) || ((p0 & 1) == 1)) ? 1.0f : 0.0f) * p1)"
+    d = m.describe("BiasRelu")
+    assert d["class"] == "map" and d["indexing"] == "0,2" and d["map"] == "static_cast<__nv_bfloat16>(fmaxf((p0 + p1), 0.0f))"
+    # a local that something else reads keeps the statements apart: three launches, two locals to bind
+    spread = SOFTMAX_BY_STATEMENTS.replace("expf(v - mx) / sum;", "expf(v - mx) / sum * 2.0f;")
+    m2 = tca.Module(spread)
+    assert m2.kernels["SoftmaxRows"]["class"] == "chain_reduce+chain_reduce+map"
+    d = m2.describe("SoftmaxRows")
+    assert d["launches"] == "3" and d["locals"] == "m,s" and d["local.m"] == "f32[R]" and d["launch1.indexing"] == "0,1"
+    assert d["launch2.map"] == "((expf((p0 - p1)) / p2) * 2.0f)"
+
+
+def test_include_graph_over_a_file_set():
+    from tcacomp_b200 import TcabError, tca
+    common = '@name(cxx="Common") kernel common(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R]> {\n' \
+             '  dimvar (i, j);\n  let y = map on(x[i][j]) (v: f32): v | reduce(init = 0.0f) on(a: f32, %0: f32) as (i) -> f32: a + %0;\n' \
+             '  return y; }\n'
+    files = {
+        "k/main.tca": '@include "lib/a.tca";\n@include "lib/b.tca";\n' + AFFINE_ROWSUM,
+        "k/lib/a.tca": '@include "common.tca";\n' + SCALED_MATMUL,
+        "k/lib/b.tca": '@include "common.tca";\n' + BF16_GEMM,          # a diamond: common merges once
+        "k/lib/common.tca": common,
+    }
+    m = tca.Module(files=files, root="k/main.tca")
+    # the root's own kernels first, then each include's, depth-first (internal/syntax/module.go:86-124)
+    assert m.names() == ["AffineSqRowsum", "ScaledMatmul", "Common", "GemmBiasRelu"]
+    cyc = dict(files)
+    cyc["k/lib/common.tca"] = '@include "../main.tca";\n' + common
+    with pytest.raises(TcabError) as e:
+        tca.Module(files=cyc, root="k/main.tca")
+    assert "escapes the including file's directory" in e.value.message
+    cyc["k/lib/common.tca"] = '@include "a.tca";\n' + common
+    with pytest.raises(TcabError) as e:
+        tca.Module(files=cyc, root="k/main.tca")
+    assert "@include cycle" in e.value.message and "k/lib/common.tca:1:" in e.value.message
+    bad = dict(files)
+    bad["k/lib/b.tca"] = "kernel oops(\n"
+    with pytest.raises(TcabError) as e:
+        tca.Module(files=bad, root="k/main.tca")
+    assert e.value.message.startswith("k/lib/b.tca:")      # diagnostics of an included file carry its path
 
 
 def test_launch_argument_checks_need_no_gpu():
@@ -143,6 +262,68 @@ def test_text_kernels_on_the_device(oracle, cuda):
         m.launch("ScaledMatmul", {"lhs": torch.empty((64, 128), device=cuda), "rhs": torch.empty((100, 96), device=cuda),
                                   "out": out}, {"scale": 1.0})
     assert e.value.status == 2 and "N" in e.value.message
+
+
+@pytest.mark.gpu
+def test_statement_by_statement_kernels_on_the_device(oracle, cuda):
+    import torch
+
+    import tcacomp_b200 as T
+    from oracle import checks
+    from tcacomp_b200 import tca
+    rng = np.random.default_rng(12)
+    m = tca.Module(SOFTMAX_BY_STATEMENTS + LAYERNORM_BY_STATEMENTS + TYPED_KERNELS)
+    x = (4 * rng.normal(0, 1, (300, 1000))).astype(np.float32)
+    xd = torch.from_numpy(x).to(cuda)
+    # recognised as a whole: ONE launch, no local bound
+    y = torch.empty_like(xd)
+    n0 = T.launch_count()
+    m.launch("SoftmaxRows", {"x": xd, "y": y})
+    assert T.launch_count() - n0 == 1
+    assert checks.softmax_close(y.cpu().numpy(), x)
+    # kept apart (the last map differs): three launches through locals that the Python host allocates
+    m2 = tca.Module(SOFTMAX_BY_STATEMENTS.replace("expf(v - mx) / sum;", "expf(v - mx) / sum * 2.0f;"))
+    y2 = torch.empty_like(xd)
+    n0 = T.launch_count()
+    m2.launch("SoftmaxRows", {"x": xd, "y": y2})
+    assert T.launch_count() - n0 == 3
+    assert checks.softmax_close(y2.cpu().numpy() * np.float32(0.5), x)
+    # locals bound by the caller are used as they are
+    mloc, sloc = torch.empty((300,), device=cuda), torch.empty((300,), device=cuda)
+    m2.launch("SoftmaxRows", {"x": xd, "y": y2, "m": mloc, "s": sloc})
+    assert np.array_equal(mloc.cpu().numpy(), x.max(1))
+
+    # layer-norm by statements on bf16 rows: one launch of the row operator, against the oracle
+    xb = oracle.f32_to_bf16(rng.normal(0, 1, (200, 1024)).astype(np.float32))
+    g = oracle.f32_to_bf16(rng.normal(1, .1, 1024).astype(np.float32))
+    b = oracle.f32_to_bf16(rng.normal(0, .1, 1024).astype(np.float32))
+    dev16 = lambda bits: torch.from_numpy(bits.view(np.int16)).to(cuda).view(torch.bfloat16)  # noqa: E731
+    yb = torch.empty((200, 1024), device=cuda, dtype=torch.bfloat16)
+    n0 = T.launch_count()
+    m.launch("LayernormRows", {"x": dev16(xb), "gamma": dev16(g), "beta": dev16(b), "y": yb}, {"inv_n": 1.0 / 1024, "eps": 1e-5})
+    assert T.launch_count() - n0 == 1
+    assert checks.layernorm_bf16_close(yb.view(torch.int16).cpu().numpy().view(np.uint16), xb, g, b)
+    from tcacomp_b200 import TcabError
+    with pytest.raises(TcabError) as e:    # the captured factor must be the reciprocal of the row length
+        m.launch("LayernormRows", {"x": dev16(xb), "gamma": dev16(g), "beta": dev16(b), "y": yb}, {"inv_n": 0.5, "eps": 1e-5})
+    assert "1 / (row length)" in e.value.message
+
+    # typed lambdas from text
+    yr = torch.empty_like(xd)
+    m.launch("ReluSelect", {"x": xd, "y": yr})
+    assert np.array_equal(yr.cpu().numpy(), np.maximum(x, 0))
+    k = rng.integers(0, 20, (300, 1000)).astype(np.int32)
+    w = rng.uniform(0, 1, (300, 1000)).astype(np.float32)
+    n = torch.empty((300,), device=cuda)
+    m.launch("CountMultiples", {"k": torch.from_numpy(k).to(cuda), "w": torch.from_numpy(w).to(cuda), "n": n})
+    sel = ((k % 3 == 0) & (k != 9)) | ((k & 1) == 1)
+    want = (np.where(sel, 1.0, 0.0) * w.astype(np.float64)).sum(1)
+    assert (np.abs(n.cpu().numpy() - want) <= 1e-5 * want).all()
+    bias = rng.normal(0, 1, 1000).astype(np.float32)
+    yb2 = torch.empty((300, 1000), device=cuda, dtype=torch.bfloat16)
+    m.launch("BiasRelu", {"x": xd, "bias": torch.from_numpy(bias).to(cuda), "y": yb2})
+    want = oracle.f32_to_bf16(np.maximum(x + bias, 0))
+    assert np.array_equal(yb2.view(torch.int16).cpu().numpy().view(np.uint16), want)
 
 
 # ---------------------------------------------------------------------------------------------
