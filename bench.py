@@ -690,8 +690,10 @@ def measure_cpu(wl, oracle, seconds: float) -> dict:
 
 
 def copy_ceiling(world: int, dev, mib: int = 256, reps: int = 6) -> dict:
-    """Bare bidirectional copies between pinned host memory and the device on every rank at once: one
-    cudaMemcpyAsync per direction and repetition, two streams. The host-buffer path cannot beat this."""
+    """Bare copies between pinned host memory and the device on every rank at once: one cudaMemcpyAsync per
+    direction and repetition, a stream per direction. `value` is both directions together (what a workload
+    with as much output as input can reach at most), `h2d_only` the upload direction alone (the ceiling of a
+    reduction, whose output is small). The host-buffer path cannot beat these."""
     n = mib << 20
     h_up = torch.empty(n, dtype=torch.uint8).pin_memory()
     h_dn = torch.empty(n, dtype=torch.uint8).pin_memory()
@@ -699,36 +701,47 @@ def copy_ceiling(world: int, dev, mib: int = 256, reps: int = 6) -> dict:
     d_dn = torch.empty(n, dtype=torch.uint8, device=dev)
     s_up, s_dn = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
 
-    def both():
-        with torch.cuda.stream(s_up):
-            d_up.copy_(h_up, non_blocking=True)
-        with torch.cuda.stream(s_dn):
-            h_dn.copy_(d_dn, non_blocking=True)
+    def run(down: bool) -> float:
+        def once():
+            with torch.cuda.stream(s_up):
+                d_up.copy_(h_up, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_dn):
+                    h_dn.copy_(d_dn, non_blocking=True)
 
-    def join():
-        cur = torch.cuda.current_stream(dev)
-        cur.wait_stream(s_up)
-        cur.wait_stream(s_dn)
+        def join():
+            cur = torch.cuda.current_stream(dev)
+            cur.wait_stream(s_up)
+            cur.wait_stream(s_dn)
 
-    def start():
+        once()
+        join()
+        barrier(world)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         cur = torch.cuda.current_stream(dev)
         s_up.wait_stream(cur)
         s_dn.wait_stream(cur)
+        for _ in range(reps):
+            once()
+        join()
+        e1.record()
+        barrier(world)
+        return max_over_ranks(e0.elapsed_time(e1), world, dev)
 
-    both()
-    join()
-    barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    start()
-    for _ in range(reps):
-        both()
-    join()
-    e1.record()
-    barrier(world)
-    ms = max_over_ranks(e0.elapsed_time(e1), world, dev)
-    return {"value": 2.0 * n * reps * world / (ms * 1e-3) / 1e9, "unit": "GB/s (both directions, all ranks)",
-            "mib_per_direction": mib, "reps": reps}
+    both, up = run(True), run(False)
+    return {"value": 2.0 * n * reps * world / (both * 1e-3) / 1e9, "unit": "GB/s (both directions, all ranks)",
+            "h2d_only": 1.0 * n * reps * world / (up * 1e-3) / 1e9, "mib_per_direction": mib, "reps": reps}
+
+
+def frac_of_ceiling(e2e: dict, ceiling: dict):
+    """An end-to-end rate against the copy ceiling that applies to it: both directions when the step downloads at
+    least a quarter of what it uploads, the upload direction alone otherwise."""
+    up, dn = e2e["h2d_bytes_per_step"], e2e["d2h_bytes_per_step"]
+    key = "value" if dn * 4 >= up else "h2d_only"
+    c = ceiling.get(key)
+    return {"frac_of_copy_ceiling": e2e["copy_gbs"] / c if c else None,
+            "copy_ceiling_used": "both directions" if key == "value" else "upload only"}
 
 
 def sharded_axis_check(rank: int, world: int, dev, oracle) -> str:
@@ -881,11 +894,10 @@ def run_ours(args) -> dict:
     extra = {}
     if not args.no_others:
         extra["copy_ceiling"] = copy_ceiling(world, dev)
-        c = extra["copy_ceiling"]["value"]
-        head["e2e"]["frac_of_copy_ceiling"] = head["e2e"]["copy_gbs"] / c if c else None
+        head["e2e"].update(frac_of_ceiling(head["e2e"], extra["copy_ceiling"]))
         for o in others:
             if "e2e" in o:
-                o["e2e"]["frac_of_copy_ceiling"] = o["e2e"]["copy_gbs"] / c if c else None
+                o["e2e"].update(frac_of_ceiling(o["e2e"], extra["copy_ceiling"]))
     if world > 1:
         extra["sharded_axis_check"] = sharded_axis_check(rank, world, dev, oracle)
         strong = []
