@@ -110,7 +110,7 @@ std::mutex g_scratch_mu;
 std::map<std::pair<std::pair<int, cudaStream_t>, int>, ScratchBuf> g_scratch;
 }  // namespace
 
-void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow) {
+void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow, bool zero) {
   const int dev = current_device();
   if (dev < 0) return nullptr;
   std::lock_guard<std::mutex> lk(g_scratch_mu);
@@ -121,8 +121,9 @@ void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow) {
     cudaFree(b.p);
     b = ScratchBuf{};
   }
-  if (cudaMalloc(&b.p, bytes) != cudaSuccess) {
+  if (cudaMalloc(&b.p, bytes) != cudaSuccess || (zero && cudaMemset(b.p, 0, bytes) != cudaSuccess)) {
     cudaGetLastError();
+    if (b.p != nullptr) cudaFree(b.p);
     b = ScratchBuf{};
     return nullptr;
   }

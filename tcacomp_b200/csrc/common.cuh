@@ -43,8 +43,9 @@ int occupancy(const void* fn, int block, size_t smem);
 // exit. Per stream, because launches on different streams may overlap on the GPU. Returns null when the
 // allocation failed (the callers then take a path that needs no scratch). With `grow`, a buffer that is
 // too small is freed (cudaFree synchronises the device, so nothing still reads it) and allocated anew.
-enum ScratchKind { kScratchChainSplit = 0, kScratchOuter = 1, kScratchGemm = 2, kScratchKinds = 3 };
-void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow);
+// `zero`: the buffer is cleared when it is allocated (arrival counters that their users leave at zero).
+enum ScratchKind { kScratchChainSplit = 0, kScratchOuter = 1, kScratchGemm = 2, kScratchGemmCounters = 3, kScratchKinds = 4 };
+void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow, bool zero = false);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -577,9 +577,13 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
                         uint32_t N, uint32_t K, int act, uint32_t ksplit, uint32_t kb_per_split,
-                        float* __restrict__ partial) {
+                        float* __restrict__ partial, uint32_t* __restrict__ counters, __nv_bfloat16* __restrict__ c_raw) {
   // ksplit > 1: a unit of work is (tile, range of K blocks); its fp32 accumulator goes to
-  // partial[range][M][N] as it is, and gemm_split_finish adds the ranges, the bias and the activation.
+  // partial[range][M][N] as it is. With `counters` (one per tile, CTA of the pair and epilogue warp, all zero
+  // between launches) the epilogue warp that arrives LAST at its 32 x 128 block of the tile adds the ranges in
+  // ascending order, the bias and the activation and stores c; every other warp only publishes its partial.
+  // Nobody waits for anybody: the last arriver is whoever finds the counter at ksplit - 1. Without `counters`
+  // gemm_split_finish does the adding in a second launch.
   using C = Db<PAIR>;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[C::STAGES];   // PAIR: used in the leader, bytes of both CTAs land here
@@ -768,6 +772,60 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
           }
         }
+        if (counters != nullptr) {
+          __threadfence();  // this lane's partial stores are visible device-wide before the count below
+          __syncwarp();
+          uint32_t* ctr = counters + ((t / ksplit) * C::CTAS + rank) * EPI_WARPS + e;
+          uint32_t last = 0;
+          if (lane == 0) {
+            last = atomicAdd(ctr, 1u) == ksplit - 1 ? 1u : 0u;
+            if (last) *ctr = 0u;  // every range of this block has arrived: ready for the next launch
+          }
+          last = __shfl_sync(0xffffffffu, last, 0);
+          if (last) {
+            __threadfence();  // the other ranges' partials, published before their counts, are visible now
+            if (row < M) {
+              __nv_bfloat16* crow = c_raw + static_cast<size_t>(row) * N;
+#pragma unroll 1
+              for (uint32_t q = 0; q < 4; ++q) {
+                const uint32_t col = tc.n * BN + half * 128 + q * 32;
+                if (col >= N) break;
+                float f[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) f[j] = 0.0f;
+                for (uint32_t r2 = 0; r2 < ksplit; ++r2) {  // ascending ranges: ascending k, like the one-pass kernel
+                  const float* src = partial + (static_cast<size_t>(r2) * M + row) * N + col;
+#pragma unroll
+                  for (int v = 0; v < 8; ++v)
+                    if (col + v * 4 < N) {  // read around L1: these lines were written by other SMs
+                      const float4 pv = __ldcg(reinterpret_cast<const float4*>(src + v * 4));
+                      f[v * 4] += pv.x; f[v * 4 + 1] += pv.y; f[v * 4 + 2] += pv.z; f[v * 4 + 3] += pv.w;
+                    }
+                }
+#pragma unroll
+                for (int g8 = 0; g8 < 4; ++g8) {  // eight columns = one 16-byte store
+                  if (col + g8 * 8 >= N) break;
+                  uint32_t w[4];
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float f0 = f[g8 * 8 + 2 * j], f1 = f[g8 * 8 + 2 * j + 1];
+                    if (bias != nullptr) {
+                      f0 += __ldg(bias + col + g8 * 8 + 2 * j);
+                      f1 += __ldg(bias + col + g8 * 8 + 2 * j + 1);
+                    }
+                    if (act == TCAB_ACT_RELU) {
+                      f0 = fmaxf(f0, 0.0f);
+                      f1 = fmaxf(f1, 0.0f);
+                    }
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
+                    w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                  }
+                  *reinterpret_cast<uint4*>(crow + col + g8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              }
+            }
+          }
+        }
         continue;
       }
 #pragma unroll 1
@@ -857,6 +915,7 @@ gemm_split_finish(const float* __restrict__ partial, const float* __restrict__ b
 
 // Workspace of the K split: one buffer per (device, stream), grown on demand up to kSplitWorkspaceBytes.
 constexpr size_t kSplitWorkspaceBytes = static_cast<size_t>(64) << 20;
+constexpr size_t kSplitCounters = 16384;  // arrival counters of the fused fold: 64 KiB per (device, stream), zero between launches
 float* gemm_split_workspace(cudaStream_t stream, size_t bytes) {
   if (bytes > kSplitWorkspaceBytes) return nullptr;
   return static_cast<float*>(stream_scratch(kScratchGemm, stream, bytes, true));
@@ -981,6 +1040,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     const uint32_t all_kb = (k + BK - 1) / BK;
     uint32_t ksplit = 1, kb_per = all_kb;
     float* partial = nullptr;
+    uint32_t* counters = nullptr;
     if (k > 0 && n % 8 == 0) {
       uint64_t want = tn.p3 > 0 ? static_cast<uint64_t>(tn.p3) : (tiles > 0 ? groups / tiles : 1);
       if (tn.p3 <= 0 && want > all_kb / 16) want = all_kb / 16;  // at least sixteen K blocks (1024 of K) per range
@@ -995,6 +1055,10 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
           ksplit = 1;
           kb_per = all_kb;
         }
+        // one counter per (tile, CTA of the pair, epilogue warp): the last arriver folds. tune p2 == 16 keeps the
+        // second launch instead (for comparison)
+        if (ksplit > 1 && tn.p2 != 16 && tiles * ctas_per_tile * EPI_WARPS <= kSplitCounters)
+          counters = static_cast<uint32_t*>(stream_scratch(kScratchGemmCounters, s, kSplitCounters * sizeof(uint32_t), false, true));
       }
     }
     const uint64_t units = tiles * ksplit;
@@ -1012,14 +1076,14 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    void* args[] = {&ta2, &tb, &tcm, &bias, &m, &n, &k, &act, &ksplit, &kb_per, &partial};
+    void* args[] = {&ta2, &tb, &tcm, &bias, &m, &n, &k, &act, &ksplit, &kb_per, &partial, &counters, &c};
     const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
     count_launch();
     if (le != cudaSuccess) {
       cudaGetLastError();
       return fail(TCAB_ERR_CUDA, "gemm_bias_act (double-buffered): launch failed: %s", cudaGetErrorString(le));
     }
-    if (ksplit > 1) {
+    if (ksplit > 1 && counters == nullptr) {
       const size_t groups8 = static_cast<size_t>(m) * (n / 8);
       gemm_split_finish<<<static_cast<unsigned>((groups8 + 255) / 256), 256, 0, s>>>(partial, bias, c, m, n, ksplit, act);
       count_launch();

@@ -679,8 +679,10 @@ def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
                                                      (130, 200, 264, 3, 3), (260, 1032, 520, 4, 5), (128, 64, 256, 3, 4),
                                                      (513, 4096, 776, 4, 2)])
 def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
-    # few output tiles and a long K: ranges of K blocks become units of work, fp32 partials are added by a second
-    # kernel together with bias and activation. variant / ranges = 0: the library's own choice.
+    # few output tiles and a long K: ranges of K blocks become units of work whose fp32 partials go to a workspace;
+    # the epilogue warp that arrives last at a block of the tile adds the ranges, the bias and the activation (one
+    # launch), or -- with the tuning value gemm p2 = 16 -- a second kernel does. variant / ranges = 0: the library's
+    # own choice. Both forms add the ranges in ascending order: identical bits.
     a, b, bias = gemm_inputs(oracle, m, k, n, m + 3 * k + n)
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
     buf, out = guarded((m, n), torch.bfloat16, cuda)
@@ -695,9 +697,21 @@ def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
     got = out.float().cpu().numpy()
     check_guards(buf, torch.bfloat16)
     assert T.device_status() == 0
-    if variant == 0 or min(ranges, (k + 63) // 64) > 1:
-        assert launches == 2, "expected the contraction and the finishing kernel"
+    split = variant == 0 or min(ranges, (k + 63) // 64) > 1
+    assert launches == 1, "the last-arriving warps fold the ranges inside the contraction's launch"
     assert rel_frobenius(got, want) <= 1e-3
+    for _ in range(2):   # again, twice: the arrival counters must be back at zero after every launch
+        again = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu") if not variant else None
+        if again is not None:
+            assert np.array_equal(again.float().cpu().numpy(), got)
+    try:                 # the two-launch form of the same split
+        T.tune("gemm", 0, variant, 16, ranges)
+        n0 = T.launch_count()
+        two = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
+        assert T.launch_count() - n0 == (2 if split else 1)
+    finally:
+        T.tune("gemm")
+    assert np.array_equal(two, got)
     assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
     # no bias, no activation through the same path
     want2 = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
