@@ -26,13 +26,14 @@ extern "C" {
  *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
  *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
  *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
- *       split path, p2 = 2 launches without programmatic dependent launch, p3 = CTAs sharing the k axis of a
+ *       split path, p2 = 2 launches without programmatic dependent launch, 3 no 1024-thread CTAs for small problems, p3 = CTAs sharing the k axis of a
  *       middle-axis reduction.
  *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
  *       p3 = CTAs sharing the k axis.
  *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
  *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
- *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128),
+ *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128; 16: the K ranges
+ *       of tcab_gemm_bias_act are added by the last-arriving epilogue warps instead of a second launch),
  *       p3 = ranges the K blocks of a tile are cut into by kernels 3 and 4 (1 = no split). */
 TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 

@@ -784,44 +784,39 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           last = __shfl_sync(0xffffffffu, last, 0);
           if (last) {
             __threadfence();  // the other ranges' partials, published before their counts, are visible now
-            if (row < M) {
-              __nv_bfloat16* crow = c_raw + static_cast<size_t>(row) * N;
+            // the warp's 32 x 128 block, four rows at a time: a lane owns four columns, so a row of a range is one
+            // coalesced 512-byte load and the loads of all ranges and rows of a step are in flight together
+            const uint32_t colbase = tc.n * BN + half * 128 + lane * 4;
+            const bool col_ok = colbase < N;  // N % 8 == 0: groups of four columns are inside or outside as a whole
+            float4 bv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (bias != nullptr && col_ok) bv = make_float4(__ldg(bias + colbase), __ldg(bias + colbase + 1), __ldg(bias + colbase + 2), __ldg(bias + colbase + 3));
 #pragma unroll 1
-              for (uint32_t q = 0; q < 4; ++q) {
-                const uint32_t col = tc.n * BN + half * 128 + q * 32;
-                if (col >= N) break;
-                float f[32];
+            for (uint32_t r0 = 0; r0 < 32; r0 += 4) {
+              float4 sum[4];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) f[j] = 0.0f;
-                for (uint32_t r2 = 0; r2 < ksplit; ++r2) {  // ascending ranges: ascending k, like the one-pass kernel
-                  const float* src = partial + (static_cast<size_t>(r2) * M + row) * N + col;
+              for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+              for (uint32_t r2 = 0; r2 < ksplit; ++r2) {  // ascending ranges: ascending k, like the one-pass kernel
 #pragma unroll
-                  for (int v = 0; v < 8; ++v)
-                    if (col + v * 4 < N) {  // read around L1: these lines were written by other SMs
-                      const float4 pv = __ldcg(reinterpret_cast<const float4*>(src + v * 4));
-                      f[v * 4] += pv.x; f[v * 4 + 1] += pv.y; f[v * 4 + 2] += pv.z; f[v * 4 + 3] += pv.w;
-                    }
-                }
-#pragma unroll
-                for (int g8 = 0; g8 < 4; ++g8) {  // eight columns = one 16-byte store
-                  if (col + g8 * 8 >= N) break;
-                  uint32_t w[4];
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float f0 = f[g8 * 8 + 2 * j], f1 = f[g8 * 8 + 2 * j + 1];
-                    if (bias != nullptr) {
-                      f0 += __ldg(bias + col + g8 * 8 + 2 * j);
-                      f1 += __ldg(bias + col + g8 * 8 + 2 * j + 1);
-                    }
-                    if (act == TCAB_ACT_RELU) {
-                      f0 = fmaxf(f0, 0.0f);
-                      f1 = fmaxf(f1, 0.0f);
-                    }
-                    const __nv_bfloat162 hh = __floats2bfloat162_rn(f0, f1);
-                    w[j] = *reinterpret_cast<const uint32_t*>(&hh);
+                for (int i = 0; i < 4; ++i) {
+                  const uint32_t ri = row0 + r0 + i;
+                  if (ri < M && col_ok) {  // read around L1: these lines were written by other SMs
+                    const float4 pv = __ldcg(reinterpret_cast<const float4*>(partial + (static_cast<size_t>(r2) * M + ri) * N + colbase));
+                    sum[i].x += pv.x; sum[i].y += pv.y; sum[i].z += pv.z; sum[i].w += pv.w;
                   }
-                  *reinterpret_cast<uint4*>(crow + col + g8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const uint32_t ri = row0 + r0 + i;
+                if (ri >= M || !col_ok) continue;
+                float f0 = sum[i].x + bv.x, f1 = sum[i].y + bv.y, f2 = sum[i].z + bv.z, f3 = sum[i].w + bv.w;
+                if (act == TCAB_ACT_RELU) {
+                  f0 = fmaxf(f0, 0.0f); f1 = fmaxf(f1, 0.0f); f2 = fmaxf(f2, 0.0f); f3 = fmaxf(f3, 0.0f);
+                }
+                const __nv_bfloat162 h0 = __floats2bfloat162_rn(f0, f1), h1 = __floats2bfloat162_rn(f2, f3);
+                *reinterpret_cast<uint2*>(c_raw + static_cast<size_t>(ri) * N + colbase) =
+                    make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
               }
             }
           }
@@ -1055,9 +1050,11 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
           ksplit = 1;
           kb_per = all_kb;
         }
-        // one counter per (tile, CTA of the pair, epilogue warp): the last arriver folds. tune p2 == 16 keeps the
-        // second launch instead (for comparison)
-        if (ksplit > 1 && tn.p2 != 16 && tiles * ctas_per_tile * EPI_WARPS <= kSplitCounters)
+        // The ranges are added by a second launch (gemm_split_finish). The one-launch form -- one counter per (tile,
+        // CTA of the pair, epilogue warp), the last arriver folds -- is kept behind tune p2 == 16: it was measured
+        // slower (128 x 8192 x 8192: 46 us against 39 us, 256 x 8192 x 4096: 37 against 31; equal from 64 tiles up),
+        // because the few warps that arrive last do at the tail what the second launch spreads over every SM.
+        if (ksplit > 1 && tn.p2 == 16 && tiles * ctas_per_tile * EPI_WARPS <= kSplitCounters)
           counters = static_cast<uint32_t*>(stream_scratch(kScratchGemmCounters, s, kSplitCounters * sizeof(uint32_t), false, true));
       }
     }

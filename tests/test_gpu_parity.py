@@ -680,9 +680,10 @@ def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
                                                      (513, 4096, 776, 4, 2)])
 def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
     # few output tiles and a long K: ranges of K blocks become units of work whose fp32 partials go to a workspace;
-    # the epilogue warp that arrives last at a block of the tile adds the ranges, the bias and the activation (one
-    # launch), or -- with the tuning value gemm p2 = 16 -- a second kernel does. variant / ranges = 0: the library's
-    # own choice. Both forms add the ranges in ascending order: identical bits.
+    # a second kernel adds the ranges, the bias and the activation, or -- with the tuning value gemm p2 = 16 -- the
+    # epilogue warp that arrives last at a block of the tile does, inside the one launch (measured slower, kept for
+    # comparison). variant / ranges = 0: the library's own choice. Both forms add the ranges in ascending order:
+    # identical bits.
     a, b, bias = gemm_inputs(oracle, m, k, n, m + 3 * k + n)
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
     buf, out = guarded((m, n), torch.bfloat16, cuda)
@@ -698,20 +699,18 @@ def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
     check_guards(buf, torch.bfloat16)
     assert T.device_status() == 0
     split = variant == 0 or min(ranges, (k + 63) // 64) > 1
-    assert launches == 1, "the last-arriving warps fold the ranges inside the contraction's launch"
+    if split:
+        assert launches == 2, "expected the contraction and the finishing kernel"
     assert rel_frobenius(got, want) <= 1e-3
-    for _ in range(2):   # again, twice: the arrival counters must be back at zero after every launch
-        again = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu") if not variant else None
-        if again is not None:
-            assert np.array_equal(again.float().cpu().numpy(), got)
-    try:                 # the two-launch form of the same split
+    try:                 # the one-launch form of the same split, three times: its arrival counters return to zero
         T.tune("gemm", 0, variant, 16, ranges)
-        n0 = T.launch_count()
-        two = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
-        assert T.launch_count() - n0 == (2 if split else 1)
+        for _ in range(3):
+            n0 = T.launch_count()
+            one = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
+            assert T.launch_count() - n0 == 1
+            assert np.array_equal(one, got)
     finally:
         T.tune("gemm")
-    assert np.array_equal(two, got)
     assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
     # no bias, no activation through the same path
     want2 = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
