@@ -42,7 +42,7 @@ extern "C" {
 
 #define TCAB_ABI_VERSION 1
 #define TCAB_MAX_RANK 4
-#define TCAB_MAX_INPUTS 4
+#define TCAB_MAX_INPUTS 6
 #define TCAB_MAX_CAPTURES 8
 #define TCAB_MAX_BATCH 32 /* problems tcab_chain_reduce_batched takes per call */
 #define TCAB_PIPELINE_MAX_OUTPUTS 3

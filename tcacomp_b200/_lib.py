@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libtcab.so")
 
 MAX_RANK = 4
-MAX_INPUTS = 4
+MAX_INPUTS = 6
 MAX_CAPTURES = 8
 NOALLOC_MAX_ROWS = 4096
 MAX_BATCH = 32

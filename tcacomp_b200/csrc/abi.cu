@@ -308,7 +308,7 @@ int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dt
     return fail(TCAB_ERR_INVALID_ARG, "%s: %u captures (at most %d)", op, chain->n_captures, TCAB_MAX_CAPTURES);
   if (n_ins < 1 || n_ins > TCAB_MAX_INPUTS || (use == TCAB_USE_CONTRACT && n_ins != 2))
     return fail(TCAB_ERR_INVALID_ARG, "%s: bad operand count %u", op, n_ins);
-  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int types[TCAB_MAX_INPUTS] = {};  // TCAB_F32 == 0
   for (uint32_t i = 0; i < n_ins && in_dtypes != nullptr; ++i) {
     if (in_dtypes[i] < TCAB_F32 || in_dtypes[i] > TCAB_U32) return fail(TCAB_ERR_DTYPE, "%s: in_dtypes[%u] is not a tcab_dtype", op, i);
     types[i] = in_dtypes[i];
@@ -429,7 +429,7 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
     return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
   const float* ptrs[TCAB_MAX_INPUTS] = {};
-  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int types[TCAB_MAX_INPUTS] = {};  // TCAB_F32 == 0
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];
     std::snprintf(name, sizeof(name), "ins[%u]", i);
@@ -490,7 +490,7 @@ int tcab_chain_reduce_batched(const tcab_chain* chain, const tcab_tensor* ins, u
     return fail(TCAB_ERR_TOO_LARGE, "%s: %u problems (between 1 and %d per call)", op, n_problems, TCAB_MAX_BATCH);
   const float* ptrs[TCAB_MAX_BATCH * TCAB_MAX_INPUTS] = {};
   float* optrs[TCAB_MAX_BATCH] = {};
-  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int types[TCAB_MAX_INPUTS] = {};  // TCAB_F32 == 0
   const tcab_tensor* t0 = &ins[0];
   for (uint32_t b = 0; b < n_problems; ++b) {
     for (uint32_t i = 0; i < n_ins; ++i) {
@@ -532,7 +532,7 @@ int tcab_chain_reduce_noalloc(const tcab_chain* chain, const tcab_tensor* ins, u
   if (ins == nullptr || n_ins < 1 || n_ins > TCAB_MAX_INPUTS)
     return fail(TCAB_ERR_INVALID_ARG, "%s: between 1 and %d operands are required", op, TCAB_MAX_INPUTS);
   const float* ptrs[TCAB_MAX_INPUTS] = {};
-  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int types[TCAB_MAX_INPUTS] = {};  // TCAB_F32 == 0
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];
     std::snprintf(name, sizeof(name), "ins[%u]", i);
@@ -572,7 +572,7 @@ int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t n_ins, co
   TCAB_TRY(check_tensor(op, "out", out));
   TCAB_TRY(need_operand_dtype(op, "out", out));
   const void* ptrs[TCAB_MAX_INPUTS] = {};
-  int types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};
+  int types[TCAB_MAX_INPUTS] = {};  // TCAB_F32 == 0
   int rb = 0, cb = 0;
   for (uint32_t i = 0; i < n_ins; ++i) {
     char name[16];

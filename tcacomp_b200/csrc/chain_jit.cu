@@ -277,8 +277,8 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   JitChain* jc = static_cast<JitChain*>(handle);
   tcabk::Caps caps;
   for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
-  const float* ptrs[4] = {ins[0], jc->n_in > 1 ? ins[1] : ins[0], jc->n_in > 2 ? ins[2] : ins[0],
-                          jc->n_in > 3 ? ins[3] : ins[0]};  // Ptrs<NIN> is NIN pointers: a prefix of this array
+  const float* ptrs[TCAB_MAX_INPUTS];  // Ptrs<NIN> is NIN pointers: a prefix of this array
+  for (int i = 0; i < TCAB_MAX_INPUTS; ++i) ptrs[i] = ins[i < jc->n_in ? i : 0];
   bool al = true;
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
   if (inner == 1) {
@@ -361,7 +361,8 @@ int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, 
   if (jc->kind != 'M') return fail(TCAB_ERR_INVALID_ARG, "map: the chain was prepared for another use");
   tcabk::Caps caps;
   for (int i = 0; i < 16; ++i) caps.c[i] = caps16[i];
-  const void* ptrs[4] = {ins[0], jc->n_in > 1 ? ins[1] : ins[0], jc->n_in > 2 ? ins[2] : ins[0], jc->n_in > 3 ? ins[3] : ins[0]};
+  const void* ptrs[TCAB_MAX_INPUTS];
+  for (int i = 0; i < TCAB_MAX_INPUTS; ++i) ptrs[i] = ins[i < jc->n_in ? i : 0];
   bool al = aligned16(out);
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
   if (jc->broadcast && cols % 8 != 0) al = false;  // a group of eight must not straddle two rows

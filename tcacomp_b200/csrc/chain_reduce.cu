@@ -416,7 +416,7 @@ int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, ch
   std::vector<float> user(chain->captures, chain->captures + chain->n_captures);
   CanonExpr map, comb, post;
   std::string err;
-  ElemT types[TCAB_MAX_INPUTS] = {kF32, kF32, kF32, kF32};
+  ElemT types[TCAB_MAX_INPUTS] = {};  // kF32 == 0
   bool all_f32 = true;
   for (uint32_t i = 0; i < n_ins && in_types != nullptr; ++i) {
     types[i] = static_cast<ElemT>(in_types[i]);

@@ -77,7 +77,7 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
 struct JitSpec {
   char kind = 'R';
   int n_in = 0, combine = 0;
-  int in_types[TCAB_MAX_INPUTS] = {TCAB_F32, TCAB_F32, TCAB_F32, TCAB_F32};  // tcab_dtype of each operand
+  int in_types[TCAB_MAX_INPUTS] = {};  // tcab_dtype of each operand (TCAB_F32 == 0)
   int out_type = TCAB_F32;                                                   // map-only: the stored element type
   int rb_mask = 0, cb_mask = 0;  // operands with one value per row / one row shared by all rows (innermost-axis kernels)
   std::string map_text, post_text;

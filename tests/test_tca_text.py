@@ -166,6 +166,11 @@ def test_several_let_chains_lower_to_locals_and_whole_row_chains_are_recognised(
     assert d["map"] == "((((((p0 % 3) == 0) && (p0 != 9)) || ((p0 & 1) == 1)) ? 1.0f : 0.0f) * p1)"
     d = m.describe("BiasRelu")
     assert d["class"] == "map" and d["indexing"] == "0,2" and d["map"] == "static_cast<__nv_bfloat16>(fmaxf((p0 + p1), 0.0f))"
+    # the same statements with another epsilon placement are not the recognised group: three launches, the last one a
+    # map over five operands
+    m3 = tca.Module(LAYERNORM_BY_STATEMENTS.replace("rsqrtf(s2 + eps)", "rsqrtf(eps + s2)"))
+    assert m3.kernels["LayernormRows"]["class"] == "chain_reduce+chain_reduce+map"
+    assert m3.describe("LayernormRows")["launch2.indexing"] == "0,1,1,2,2"
     # a local that something else reads keeps the statements apart: three launches, two locals to bind
     spread = SOFTMAX_BY_STATEMENTS.replace("expf(v - mx) / sum;", "expf(v - mx) / sum * 2.0f;")
     m2 = tca.Module(spread)
