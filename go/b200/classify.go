@@ -25,7 +25,7 @@ type Plan struct {
 	Init                     float32
 	Captures                 []string // scalar parameter of capture slot i
 	Inputs                   []string // tensor names, in operand order
-	Indexing                 []int    // per operand: 0 every axis, 1 one value per row, 2 one row shared by all rows
+	Indexing                 []int    // per operand: 0 every axis, 1 one value per row, 2 one row shared by all rows, 3 one value per output cell (middle-axis reductions)
 	ReduceAxis               uint32
 	RhsIsNK                  bool
 	A, B, Bias               string
@@ -201,10 +201,23 @@ func Classify(store ir.Node) (Plan, error) {
 		return p, fmt.Errorf("b200: no operand carries every iteration axis; a chain needs one operand that fixes the layout")
 	}
 	axes := full.axes
+	// under a reduction of an axis that is not the innermost: all axes but the reduced one (one value per output cell)
+	var cellAxes []string
+	if reduce != nil && len(as) > 0 && len(axes) > 1 && axes[len(axes)-1] != as[len(as)-1] {
+		for _, a := range axes {
+			if a != as[len(as)-1] {
+				cellAxes = append(cellAxes, a)
+			}
+		}
+	}
 	for _, o := range ops {
 		switch {
 		case same(o.axes, axes):
 			p.Indexing = append(p.Indexing, 0)
+		case cellAxes != nil && same(o.axes, cellAxes):
+			p.Indexing = append(p.Indexing, 3)
+		case cellAxes != nil:
+			return p, fmt.Errorf("b200: operand %s: under a reduction of a middle axis an operand carries every axis or all but the reduced one", o.name)
 		case len(axes) > 1 && same(o.axes, axes[:len(axes)-1]):
 			p.Indexing = append(p.Indexing, 1)
 		case len(axes) > 1 && same(o.axes, axes[len(axes)-1:]):
@@ -232,11 +245,6 @@ func Classify(store ir.Node) (Plan, error) {
 	}
 	if pos < 0 || !same(rest, as[:len(as)-1]) || !same(outAxes, rest) {
 		return p, fmt.Errorf("b200: the output must keep the operands' axis order minus the reduced axis @%s", red)
-	}
-	for _, h := range p.Indexing {
-		if h != 0 && pos != len(axes)-1 {
-			return p, fmt.Errorf("b200: an operand that lacks an axis is only taken when the reduced axis is the innermost one")
-		}
 	}
 	p.Kind, p.ReduceAxis = ChainReduce, uint32(pos)
 	return p, nil

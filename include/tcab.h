@@ -133,7 +133,9 @@ TCAB_API uint64_t tcab_launch_count(void);
  * (i, j) iteration, pkg/chain.go checkOperand -- this is how a later statement reads a Local such as a row
  * maximum, pkg/local_test.go:17-68): when the reduced axis is the innermost one, an operand may have extent 1
  * along the innermost axis (one value per row) or extent 1 along every other axis (one row shared by all
- * rows: a bias, gamma, beta). Such chains are compiled at run time; their rows are never split over CTAs.
+ * rows: a bias, gamma, beta); when another axis is reduced, an operand may have extent 1 along the REDUCED axis
+ * (one value per output cell: the column maxima of a middle-axis softmax). Such chains are compiled at run time;
+ * rows with such operands are never split over CTAs.
  * reduce_axis == rank-1 selects the innermost-axis kernel, any other axis the outer-axis kernel.
  * The fold order is unspecified (design/tca.md:80-81,92); combine must be associative and commutative.
  * Allocation: when there are fewer rows than SMs and the rows are long, a row is split over several

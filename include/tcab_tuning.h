@@ -49,9 +49,10 @@ TCAB_API int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, 
 /* Validates a chain exactly as tcab_chain_prepare does and runs the run-time compiler on it for sm_100a, but
  * loads nothing: works on a host without a GPU (needs libnvrtc). A chain that has an ahead-of-time kernel is
  * compiled all the same. Arguments as tcab_chain_prepare, plus the bit masks of the operands that have one
- * value per row / one row shared by all rows (what the entry points derive from the operands' shapes). */
+ * value per row / one row shared by all rows / (middle-axis reductions) one value per output cell -- what the
+ * entry points derive from the operands' shapes. */
 TCAB_API int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use,
-                                int out_dtype, int row_value_mask, int shared_row_mask);
+                                int out_dtype, int row_value_mask, int shared_row_mask, int cell_value_mask);
 
 #ifdef __cplusplus
 }

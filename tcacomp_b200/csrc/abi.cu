@@ -278,12 +278,13 @@ int prepare_common(const char* op, const tcab_chain* chain, const int32_t* in_dt
 }
 
 int tcab_compile_check(const tcab_chain* chain, const int32_t* in_dtypes, uint32_t n_ins, int use, int out_dtype,
-                       int row_value_mask, int shared_row_mask) {
+                       int row_value_mask, int shared_row_mask, int cell_value_mask) {
   PreparedChain pc;
   TCAB_TRY(prepare_common("compile_check", chain, in_dtypes, n_ins, use, out_dtype, &pc));
   JitSpec sp = pc.spec;
   sp.rb_mask = row_value_mask;
   sp.cb_mask = shared_row_mask;
+  sp.cell_mask = cell_value_mask;
   return jit_compile_check(sp);
 }
 
@@ -445,9 +446,20 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   for (uint32_t i = 1; i < n_ins; ++i)
     for (uint32_t d = 0; d < full.rank; ++d)
       if (ins[i].dims[d] > full.dims[d]) full.dims[d] = ins[i].dims[d];
-  int rb = 0, cb = 0;
+  if (reduce_axis >= full.rank) return fail(TCAB_ERR_INVALID_ARG, "%s: reduce_axis %u out of range", op, reduce_axis);
+  int rb = 0, cb = 0, cells = 0;
   for (uint32_t i = 0; i < n_ins; ++i) {
-    const int how = operand_indexing(full.dims, full.rank, &ins[i]);
+    int how = operand_indexing(full.dims, full.rank, &ins[i]);
+    if (how != 0 && reduce_axis != full.rank - 1) {
+      // a middle-axis reduction: an operand may lack the REDUCED axis (extent 1 there, the common extents elsewhere):
+      // one value per output cell
+      bool cell = ins[i].dims[reduce_axis] == 1;
+      for (uint32_t d = 0; cell && d < full.rank; ++d) cell = d == reduce_axis || ins[i].dims[d] == full.dims[d];
+      if (!cell)
+        return fail(TCAB_ERR_SHAPE, "%s: ins[%u] must have the operands' common shape, or extent 1 along the reduced axis", op, i);
+      cells |= 1 << i;
+      continue;
+    }
     if (how < 0)
       return fail(TCAB_ERR_SHAPE, "%s: ins[%u] must have the operands' common shape, or extent 1 along the innermost axis, "
                   "or extent 1 along every other axis", op, i);
@@ -455,9 +467,6 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
     cb |= (how == 2) << i;
   }
   const tcab_tensor* t = &full;
-  if (reduce_axis >= t->rank) return fail(TCAB_ERR_INVALID_ARG, "%s: reduce_axis %u out of range", op, reduce_axis);
-  if ((rb | cb) != 0 && reduce_axis != t->rank - 1)
-    return fail(TCAB_ERR_UNSUPPORTED, "%s: operands with broadcast extents are taken by innermost-axis reductions only", op);
   TCAB_TRY(check_tensor(op, "out", out));
   TCAB_TRY(need_dtype(op, "out", out, TCAB_F32, "f32"));
   TCAB_TRY(need_elem_align(op, "out", out, 4));
@@ -470,7 +479,7 @@ int tcab_chain_reduce(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
   for (uint32_t i = 0; ok && i < wr; ++i) ok = out->dims[i] == want[i];
   if (!ok) return fail(TCAB_ERR_SHAPE, "%s: out must have the operands' extents without axis %u", op, reduce_axis);
   PreparedChain pc;
-  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types, TCAB_F32, rb, cb));
+  TCAB_TRY(prepare_chain(chain, n_ins, &pc, 'R', types, TCAB_F32, rb, cb, cells));
   TCAB_TRY(have_device(op));
   return launch_chain_reduce(pc, ptrs, count(t, 0, reduce_axis), t->dims[reduce_axis],
                              count(t, reduce_axis + 1, t->rank), static_cast<float*>(out->data),

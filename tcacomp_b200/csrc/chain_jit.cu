@@ -80,6 +80,7 @@ struct JitChain {
   int n_in = 0;
   char kind = 'R';
   bool broadcast = false;  // an operand is not indexed by every axis: innermost-axis kernels only
+  bool cells = false;      // an operand lacks the reduced middle axis: middle-axis kernels only
 };
 
 std::mutex g_mu;
@@ -142,7 +143,13 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
                                                       std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ", " +
                                                       std::to_string(tprs[t] > 128 ? tprs[t] : 128) + bc + ">";
     names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024" + bc + ">";
-    if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
+    if (sp.cell_mask != 0) {  // operands without the reduced middle axis: the middle-axis kernels only
+      names.assign(kSlots, std::string());
+      const std::string cm = ", " + std::to_string(sp.cell_mask);
+      names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
+      names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + cm + ">";
+      names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + cm + ">";
+    } else if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
       names.assign(kSlots, std::string());
       for (int v = 0; v < 2; ++v)
         for (int t = 0; t < 4; ++t)
@@ -201,6 +208,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
   jc->n_in = sp.n_in;
   jc->kind = sp.kind;
   jc->broadcast = (sp.rb_mask | sp.cb_mask) != 0;
+  jc->cells = sp.cell_mask != 0;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
   for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
     if (names[i].empty()) continue;
@@ -244,7 +252,7 @@ int jit_prepare(const JitSpec& sp, void** handle, bool compile_if_missing) {
   key += "|" + std::to_string(sp.n_in) + "|" + std::to_string(sp.combine) + "|";
   for (int i = 0; i < sp.n_in; ++i) key += std::to_string(sp.in_types[i]);
   key += ">" + std::to_string(sp.kind == 'M' ? sp.out_type : TCAB_F32) + "|" + std::to_string(sp.rb_mask) + "," +
-         std::to_string(sp.cb_mask) + "|" + sp.map_text + "|" + sp.post_text;
+         std::to_string(sp.cb_mask) + "," + std::to_string(sp.cell_mask) + "|" + sp.map_text + "|" + sp.post_text;
   std::lock_guard<std::mutex> lk(g_mu);
   auto it = g_cache.find(key);
   if (it != g_cache.end()) {
@@ -282,6 +290,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   bool al = true;
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
   if (inner == 1) {
+    if (jc->cells) return fail(TCAB_ERR_UNSUPPORTED, "chain_reduce: the chain was prepared for a middle-axis reduction");
     const bool vec = al && (nk % 4 == 0);
     const uint32_t nvec = vec ? nk / 4 : nk;
     const bool force_split = (splits & 0x80000000u) != 0;  // the entry point that allocates nothing

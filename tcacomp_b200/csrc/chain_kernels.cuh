@@ -136,6 +136,31 @@ struct LoadAll<V, BF, NIN, NIN> {
   static __device__ __forceinline__ void at(const float* const*, u64, float (*)[V]) {}
 };
 
+// Middle-axis reductions: operands at vector index `index` of the [nb, nk, nc] tensors, except those of the
+// mask CELL, which have ONE value per output cell (shape [nb, 1, nc]: they lack the reduced axis) and were
+// loaded once, before the k loop, into cellval.
+template <int V, int BF, int CELL, int NIN, int A = 0>
+struct LoadOuterAll {
+  static __device__ __forceinline__ void at(const float* const* p, u64 index, const float (*cellval)[V], float (*f)[V]) {
+    if constexpr (((CELL >> A) & 1) != 0) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) f[A][j] = cellval[A][j];
+    } else {
+      load_operand<V, BF, A>(p[A], index, f[A]);
+    }
+    LoadOuterAll<V, BF, CELL, NIN, A + 1>::at(p, index, cellval, f);
+  }
+  static __device__ __forceinline__ void cells(const float* const* p, u64 cell_index, float (*cellval)[V]) {
+    if constexpr (((CELL >> A) & 1) != 0) load_operand<V, BF, A>(p[A], cell_index, cellval[A]);
+    LoadOuterAll<V, BF, CELL, NIN, A + 1>::cells(p, cell_index, cellval);
+  }
+};
+template <int V, int BF, int CELL, int NIN>
+struct LoadOuterAll<V, BF, CELL, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, const float (*)[V], float (*)[V]) {}
+  static __device__ __forceinline__ void cells(const float* const*, u64, float (*)[V]) {}
+};
+
 template <class C, int WIDTH>
 __device__ __forceinline__ float lanes_allreduce(float v) {
 #pragma unroll
@@ -362,7 +387,7 @@ chain_split_finish(const float* __restrict__ partials, float* __restrict__ out, 
 // With ksplit > 1 the k axis is also cut into ksplit ranges of klen, one CTA each (few columns, long k):
 // a CTA then writes the fold of its range -- without init and without the piped map -- to
 // partials[cell * ksplit + range], and chain_split_finish folds the ranges in ascending order.
-template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL, int BF = 0>
+template <class Map, class Post, int COMBINE, int NIN, int V, int KW, int UNROLL, int BF = 0, int CELL = 0>
 __global__ void __launch_bounds__(32 * KW)
 chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, float init,
             Caps caps, u32 ksplit, u32 klen, float* __restrict__ partials) {
@@ -386,13 +411,15 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
     for (int j = 0; j < V; ++j) acc[j] = C::identity();
 
     if (colok) {
+      float cellval[NIN][V];  // operands that lack the reduced axis: one value per output cell, loaded once
+      LoadOuterAll<V, BF, CELL, NIN>::cells(ins.p, (static_cast<u64>(b) * nc + col) / V, cellval);
       for (u32 k0 = kbeg + warp; k0 < kend; k0 += KW * UNROLL) {
         float f[UNROLL][NIN][V];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const u32 k = k0 + u * KW;
           if (k < kend)  // base and k * nc are multiples of V on the vector path
-            LoadAll<V, BF, NIN>::at(ins.p, (base + static_cast<u64>(k) * nc) / V, f[u]);
+            LoadOuterAll<V, BF, CELL, NIN>::at(ins.p, (base + static_cast<u64>(k) * nc) / V, cellval, f[u]);
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {

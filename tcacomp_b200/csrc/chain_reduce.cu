@@ -411,7 +411,7 @@ int combine_id(const std::string& text) {
 }  // namespace
 
 int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind, const int* in_types, int out_type,
-                  int rb_mask, int cb_mask) {
+                  int rb_mask, int cb_mask, int cell_mask) {
   const char* op = kind == 'M' ? "map" : kind == 'C' ? "chain_contract" : "chain_reduce";
   std::vector<float> user(chain->captures, chain->captures + chain->n_captures);
   CanonExpr map, comb, post;
@@ -439,7 +439,8 @@ int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, ch
   sp.out_type = out_type;
   sp.rb_mask = rb_mask;
   sp.cb_mask = cb_mask;
-  if ((rb_mask | cb_mask) != 0) all_f32 = false;  // broadcast operands: compiled at run time only
+  sp.cell_mask = cell_mask;
+  if ((rb_mask | cb_mask | cell_mask) != 0) all_f32 = false;  // broadcast operands: compiled at run time only
   sp.map_text = map.text;
   if (kind == 'M') {
     // a map-only chain stores the lambda's value as it is: its type is the output's element type, no conversion

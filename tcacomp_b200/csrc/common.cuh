@@ -80,6 +80,7 @@ struct JitSpec {
   int in_types[TCAB_MAX_INPUTS] = {};  // tcab_dtype of each operand (TCAB_F32 == 0)
   int out_type = TCAB_F32;                                                   // map-only: the stored element type
   int rb_mask = 0, cb_mask = 0;  // operands with one value per row / one row shared by all rows (innermost-axis kernels)
+  int cell_mask = 0;             // middle-axis reductions: operands with one value per output cell (no reduced axis)
   std::string map_text, post_text;
   int bf_mask() const {
     int m = 0;
@@ -107,7 +108,7 @@ int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, 
 // Host-only step (no device needed): parse, canonicalise and look the chain up.
 // kind: 'R' / 'C' / 'M' as in JitSpec; in_types: n_ins tcab_dtype values (null = all f32); out_type: map-only.
 int prepare_chain(const tcab_chain* chain, uint32_t n_ins, PreparedChain* pc, char kind = 'R', const int* in_types = nullptr,
-                  int out_type = TCAB_F32, int rb_mask = 0, int cb_mask = 0);
+                  int out_type = TCAB_F32, int rb_mask = 0, int cb_mask = 0, int cell_mask = 0);
 int launch_chain_map(const PreparedChain& pc, const void* const* ins, void* out, uint64_t n, uint32_t cols, cudaStream_t s);
 int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64_t outer, uint32_t nk,
                         uint64_t inner, float* out, cudaStream_t s);

@@ -330,7 +330,8 @@ struct Plan {
   uint32_t reduce_axis = 0;                // position of the reduced dim in the operands
   bool rhs_is_nk = false;                  // ChainContract: the second operand is [n,k] rather than [k,n]
   // ChainReduce / Map: how operand i is indexed -- 0 by every axis, 1 one value per row (it lacks the innermost
-  // axis), 2 one row shared by all rows (it has the innermost axis only)
+  // axis), 2 one row shared by all rows (it has the innermost axis only), 3 one value per output cell (it lacks
+  // the reduced axis, which is not the innermost)
   std::vector<int> indexing;
   // GemmBiasAct
   std::string a, b, bias;                  // bias empty = none

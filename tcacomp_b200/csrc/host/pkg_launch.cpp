@@ -197,7 +197,8 @@ Result<Plan> Classify(const Statement& st) {
   }
 
   // map | reduce | [map], or a map alone (the added rung of pkg_ext.h), over operands that are indexed by every
-  // iteration axis, by all but the innermost (one value per row) or by the innermost only (one shared row)
+  // iteration axis, by all but the innermost (one value per row), by the innermost only (one shared row) or, when
+  // an axis other than the innermost is reduced, by all but the reduced one (one value per output cell)
   const bool map_only = st.reduces.empty();
   p.kind = map_only ? Plan::Map : Plan::ChainReduce;
   if (st.reduces.size() > 1) {
@@ -220,6 +221,12 @@ Result<Plan> Classify(const Statement& st) {
   const std::vector<Dim>& axes = full->axes;
   std::vector<Dim> row_axes(axes.begin(), axes.end() - 1);       // all but the innermost
   std::vector<Dim> col_axes(axes.end() - 1, axes.end());          // the innermost only
+  std::vector<Dim> cell_axes;                                     // all but a reduced axis that is not the innermost
+  if (!map_only && !st.as.empty()) {
+    for (const Dim& d : axes)
+      if (d.name != st.as.back().name) cell_axes.push_back(d);
+    if (cell_axes.size() == axes.size() || axes.back().name == st.as.back().name) cell_axes.clear();
+  }
   for (const Operand& op : st.operands) {
     if (op.t.elem != Elem::F32 && op.t.elem != Elem::BF16 && op.t.elem != Elem::I32 && op.t.elem != Elem::U32) {
       r.err = "classify: operand " + op.t.name + " is " + ElemName(op.t.elem) + "; the kernels move f32, bf16, i32 and u32";
@@ -229,9 +236,11 @@ Result<Plan> Classify(const Statement& st) {
     if (same_axes(op.axes, axes)) how = 0;
     else if (axes.size() > 1 && same_axes(op.axes, row_axes)) how = 1;
     else if (axes.size() > 1 && same_axes(op.axes, col_axes)) how = 2;
+    if (!cell_axes.empty()) how = same_axes(op.axes, axes) ? 0 : same_axes(op.axes, cell_axes) ? 3 : -1;
     if (how < 0) {
       r.err = "classify: operand " + op.t.name + " is not indexed like " + full->t.name +
-              ", nor by all but its innermost axis, nor by its innermost axis alone; operands with other index sets "
+              ", nor by all but its innermost axis, nor by its innermost axis alone, nor (under a reduction of another "
+              "axis) by all but the reduced axis; operands with other index sets "
               "(contractions, transposes) need the contraction class, which this chain does not match";
       return r;
     }
@@ -274,11 +283,7 @@ Result<Plan> Classify(const Statement& st) {
             " (a transposing store has no kernel class)";
     return r;
   }
-  for (int how : p.indexing)
-    if (how != 0 && pos != static_cast<int>(axes.size()) - 1) {
-      r.err = "classify: an operand that lacks an axis is only taken when the reduced axis is the innermost one";
-      return r;
-    }
+  p.reduce_axis = static_cast<uint32_t>(pos);
   if (st.out.elem != Elem::F32 || st.elem != Elem::F32) {
     r.err = "classify: the chain class folds and stores fp32 (convert the mapped value with an explicit cast)";
     return r;
@@ -289,7 +294,6 @@ Result<Plan> Classify(const Statement& st) {
     return r;
   }
   p.init = static_cast<float>(rd.init.node->value);
-  p.reduce_axis = static_cast<uint32_t>(pos);
   p.map_expr = print_node(*st.map_body.node, &p.capture_names, &err);
   std::vector<std::string> none;
   if (err.empty()) p.combine_expr = print_node(*rd.body.node, &none, &err);
@@ -484,13 +488,16 @@ const Tensor* find_tensor(const Graph& g, const std::string& name) {
 
 // An operand that lacks axes of the iteration is handed to the kernel library with the iteration's rank and
 // extent 1 where it has no axis: [rows..., 1] for a value per row, [1..., cols] for a shared row.
-tcab_tensor with_unit_axes(const tcab_tensor& t, int how, uint32_t rank) {
+tcab_tensor with_unit_axes(const tcab_tensor& t, int how, uint32_t rank, uint32_t reduce_axis) {
   if (how == 0) return t;
   tcab_tensor v = t;
   v.rank = rank;
   for (uint32_t i = 0; i < rank; ++i) v.dims[i] = 1;
   if (how == 1) for (uint32_t i = 0; i < t.rank && i + 1 < rank; ++i) v.dims[i] = t.dims[i];
   if (how == 2) v.dims[rank - 1] = t.dims[t.rank - 1];
+  if (how == 3)
+    for (uint32_t i = 0, j = 0; i < rank; ++i)
+      if (i != reduce_axis && j < t.rank) v.dims[i] = t.dims[j++];
   return v;
 }
 
@@ -559,7 +566,7 @@ int Launch(const Graph& g, const Bindings& bind, void* stream) {
       if (rc != TCAB_OK) return rc;
       if (i < p.indexing.size() && p.indexing[i] == 0 && rank == 0) rank = ins[i].rank;
     }
-    for (size_t i = 0; i < p.inputs.size() && i < p.indexing.size(); ++i) ins[i] = with_unit_axes(ins[i], p.indexing[i], rank);
+    for (size_t i = 0; i < p.inputs.size() && i < p.indexing.size(); ++i) ins[i] = with_unit_axes(ins[i], p.indexing[i], rank, p.reduce_axis);
     tcab_tensor out;
     int rc = bound(p.out, &out);
     if (rc != TCAB_OK) return rc;

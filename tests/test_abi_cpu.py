@@ -231,7 +231,7 @@ def test_typed_lambdas_compile_for_sm100(tcab_lib, expr, types, use, out):
     from tcacomp_b200 import _lib
     ch = _bchain(expr)
     arr = (C.c_int32 * len(types))(*types)
-    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, 0, 0)
+    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, 0, 0, 0)
     assert rc == _lib.OK, _err(tcab_lib)
 
 
@@ -240,7 +240,7 @@ def test_ill_typed_lambdas_are_refused_before_any_compiler(tcab_lib, expr, types
     from tcacomp_b200 import _lib
     ch = _bchain(expr)
     arr = (C.c_int32 * len(types))(*types)
-    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, 0, 0)
+    rc = tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, 0, 0, 0)
     assert rc in (_lib.ERR_INVALID_ARG, _lib.ERR_DTYPE), (rc, _err(tcab_lib))
     assert why in tcab_lib.tcab_last_error(), _err(tcab_lib)
 
@@ -277,14 +277,15 @@ def test_partition_rule_and_pipeline_validation_without_a_device(tcab_lib):
     assert L.tcab_pipeline_destroy(None) == _lib.OK and L.tcab_multi_destroy(None) == _lib.OK
 
 
-@pytest.mark.parametrize("expr,types,use,out,rb,cb", [
-    (b"expf(p0 - p1)", [F, F], "reduce", F, 0b10, 0),                 # sum_j exp(x[i][j] - m[i]): reads a row maximum
-    (b"expf(p0 - p1) / p2", [F, F, F], "map", F, 0b110, 0),          # the normalising map of a softmax
-    (b"bf16((f32(p0) - p1) * p2 * f32(p3))", [B, F, F, B], "map", B, 0b0110, 0b1000),   # layer-norm's last map
-    (b"fmaxf(p0 + p1, 0.0f)", [F, F], "map", F, 0, 0b10),            # bias[n] and ReLU
+@pytest.mark.parametrize("expr,types,use,out,rb,cb,cells", [
+    (b"expf(p0 - p1)", [F, F], "reduce", F, 0b10, 0, 0),              # sum_j exp(x[i][j] - m[i]): reads a row maximum
+    (b"expf(p0 - p1) / p2", [F, F, F], "map", F, 0b110, 0, 0),       # the normalising map of a softmax
+    (b"bf16((f32(p0) - p1) * p2 * f32(p3) + f32(p4))", [B, F, F, B, B], "map", B, 0b00110, 0b11000, 0),   # layer-norm's last map
+    (b"fmaxf(p0 + p1, 0.0f)", [F, F], "map", F, 0, 0b10, 0),         # bias[n] and ReLU
+    (b"expf(p0 - p1) * f32(p2)", [F, F, B], "reduce", F, 0, 0, 0b010),   # middle-axis: sum_k exp(x[i][k][j] - m[i][j]) * z
 ])
-def test_lambdas_over_operands_that_bind_a_subset_of_the_axes_compile(tcab_lib, expr, types, use, out, rb, cb):
+def test_lambdas_over_operands_that_bind_a_subset_of_the_axes_compile(tcab_lib, expr, types, use, out, rb, cb, cells):
     from tcacomp_b200 import _lib
     ch = _bchain(expr)
     arr = (C.c_int32 * len(types))(*types)
-    assert tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, rb, cb) == _lib.OK, _err(tcab_lib)
+    assert tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, rb, cb, cells) == _lib.OK, _err(tcab_lib)

@@ -323,4 +323,23 @@ def test_broadcast_shapes_are_checked(cuda):
     assert e.value.status == T._lib.ERR_SHAPE
     with pytest.raises(T.TcabError) as e:     # a value per row needs the innermost axis to be the reduced one
         T.chain_reduce([torch.zeros((4, 6, 16), device=cuda), torch.zeros((4, 6, 1), device=cuda)], "p0 * p1", axis=1)
-    assert e.value.status == T._lib.ERR_UNSUPPORTED
+    assert e.value.status == T._lib.ERR_SHAPE
+
+
+@pytest.mark.parametrize("nb,nk,nc", [(5, 300, 132), (2, 9, 7), (1, 5000, 64), (16, 8, 256)])
+def test_middle_axis_reduction_reads_a_value_per_output_cell(cuda, nb, nk, nc):
+    """The reference's softmax suite kernel reduces over the MIDDLE axis (testing/kernels/fusion/softmax.tca). Written
+    statement by statement its second reduction reads the first one's result m[i][j] inside the (i, k, j) iteration:
+    an operand that lacks the reduced axis, one value per output cell."""
+    rng = np.random.default_rng(nb + nk + nc)
+    x = (3 * rng.normal(0, 1, (nb, nk, nc))).astype(np.float32)
+    z = rng.uniform(0, 1, (nb, nk, nc)).astype(np.float32)
+    xd, zd = to_dev(x, cuda), to_dev(z, cuda)
+    m = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=-np.inf, axis=1)                # [nb, nc]
+    s = T.chain_reduce([xd, m.view(nb, 1, nc), zd], "expf(p0 - p1) * p2", axis=1).cpu().numpy()
+    assert np.array_equal(m.cpu().numpy(), x.max(1))
+    want = (np.exp(x.astype(np.float64) - x.max(1, keepdims=True)) * z).sum(1)
+    assert (np.abs(s - want) <= 1e-5 * want + 1e-30).all()
+    with pytest.raises(T.TcabError) as e:       # the value per row of the innermost-axis kernels is not a value per cell
+        T.chain_reduce([xd, torch.zeros((nb, nk, 1), device=cuda)], "p0 * p1", axis=1)
+    assert e.value.status == T._lib.ERR_SHAPE

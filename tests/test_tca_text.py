@@ -125,6 +125,23 @@ kernel layernorm_rows(x: tensor<dtype=bf16, shape=[R, C]>, gamma: tensor<dtype=b
 }
 '''
 
+MASKED_NORMALISER_MIDDLE_AXIS = '''
+// The reference's suite softmax reduces over the MIDDLE axis with a mask operand and without the row maximum
+// (testing/kernels/fusion/softmax.tca:1-21 records why). With locals the stable form is two statements; the second
+// reads the first one's result by the two axes that remain: one value per output cell. (A local of rank 2 needs
+// static extents, as in the reference's builder.)
+@name(cxx="MaskedNormaliser")
+kernel masked_normaliser(x: tensor<dtype=f32, shape=[7u, 50u, 132u]>, z: tensor<dtype=f32, shape=[7u, 50u, 132u]>)
+    -> tensor<dtype=f32, shape=[7u, 132u]> {
+  dimvar (i, k, j);
+  let m = map on(x[i][k][j]) (v: f32) -> f32: v
+        | reduce(init = -inf_f32) on(acc: f32, %0: f32) as (i, j) -> f32: fmaxf(acc, %0);
+  let out = map on(x[i][k][j], m[i][j], z[i][k][j]) (v: f32, mx: f32, w: f32) -> f32: expf(v - mx) * w
+          | reduce(init = 0.0f) on(acc: f32, %0: f32) as (i, j) -> f32: acc + %0;
+  return out;
+}
+'''
+
 TYPED_KERNELS = '''
 @name(cxx="ReluSelect")
 kernel relu_select(x: tensor<dtype=f32, shape=[R, C]>) -> tensor<dtype=f32, shape=[R, C]> {
@@ -178,6 +195,16 @@ def test_several_let_chains_lower_to_locals_and_whole_row_chains_are_recognised(
     d = m2.describe("SoftmaxRows")
     assert d["launches"] == "3" and d["locals"] == "m,s" and d["local.m"] == "f32[R]" and d["launch1.indexing"] == "0,1"
     assert d["launch2.map"] == "((expf((p0 - p1)) / p2) * 2.0f)"
+    # a reduction over the middle axis whose map reads the previous reduction's result per output cell
+    d = tca.Module(MASKED_NORMALISER_MIDDLE_AXIS).describe("MaskedNormaliser")
+    assert d["class"] == "chain_reduce+chain_reduce" and d["locals"] == "m" and d["local.m"] == "f32[7,132]"
+    assert d["launch1.axis"] == "1" and d["launch1.indexing"] == "0,3,0" and d["launch1.map"] == "(expf((p0 - p1)) * p2)"
+    from tcacomp_b200 import TcabError
+    with pytest.raises(TcabError) as e:      # ... but not one that lacks another axis than the reduced one
+        tca.Module(MASKED_NORMALISER_MIDDLE_AXIS.replace(
+            "on(x[i][k][j], m[i][j], z[i][k][j])", "on(x[i][k][j], m[i][j], z[i][k])").replace(
+            "z: tensor<dtype=f32, shape=[7u, 50u, 132u]>", "z: tensor<dtype=f32, shape=[7u, 50u]>")).describe("MaskedNormaliser")
+    assert "all but the reduced axis" in e.value.message
 
 
 def test_include_graph_over_a_file_set():
@@ -312,6 +339,17 @@ def test_statement_by_statement_kernels_on_the_device(oracle, cuda):
     with pytest.raises(TcabError) as e:    # the captured factor must be the reciprocal of the row length
         m.launch("LayernormRows", {"x": dev16(xb), "gamma": dev16(g), "beta": dev16(b), "y": yb}, {"inv_n": 0.5, "eps": 1e-5})
     assert "1 / (row length)" in e.value.message
+
+    # middle-axis reduction reading a value per output cell (the local m[i][j]); the Python host allocates m
+    mm = tca.Module(MASKED_NORMALISER_MIDDLE_AXIS)
+    x3 = (3 * rng.normal(0, 1, (7, 50, 132))).astype(np.float32)
+    z3 = rng.uniform(0, 1, (7, 50, 132)).astype(np.float32)
+    o3 = torch.empty((7, 132), device=cuda)
+    n0 = T.launch_count()
+    mm.launch("MaskedNormaliser", {"x": torch.from_numpy(x3).to(cuda), "z": torch.from_numpy(z3).to(cuda), "out": o3})
+    assert T.launch_count() - n0 == 2
+    want = (np.exp(x3.astype(np.float64) - x3.max(1, keepdims=True)) * z3).sum(1)
+    assert (np.abs(o3.cpu().numpy() - want) <= 1e-5 * want).all()
 
     # typed lambdas from text
     yr = torch.empty_like(xd)
