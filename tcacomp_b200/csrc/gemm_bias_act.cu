@@ -872,6 +872,252 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
   if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = PAIR ? 4 : 3;
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// Few output tiles and a long K: the K ranges of one 128 x 256 tile run on the CTAs of ONE thread-block cluster
+// (KS = 2..8 CTAs, one unit of work each). Every CTA accumulates its range in TMEM and copies the fp32 accumulator
+// into its own shared memory (over the drained operand ring). The tile's rows are dealt out to the CTAs of the
+// cluster: a CTA writes the rows it does not own to a workspace (they stay in L2), the cluster synchronises, and
+// each CTA adds, for its own rows, the ranges in ascending order -- its own from shared memory, the others' from
+// the workspace -- then the bias and the activation, and stores bf16. One launch; every SM of the cluster takes an
+// equal share of the adding. (Reading the peers' accumulators through distributed shared memory instead was
+// measured at 8 us for a 128 x 256 tile in four ranges: the SM-to-SM path is slower than L2.) The sum is taken in
+// the same order as gemm_split_finish takes it: the forms give the same bits.
+// ------------------------------------------------------------------------------------------------------------
+struct Ck {
+  static constexpr int A_BYTES = UMMA_M * 128;            // 16 KB: 128 rows x 64 bf16
+  static constexpr int B_BYTES = BK * BN * 2;             // 32 KB
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 4;
+  static constexpr int PLANE_BYTES = UMMA_M * BN * 4;     // the fp32 accumulator: 128 rows x 1 KB
+  static constexpr size_t SMEM = static_cast<size_t>(STAGES) * STAGE + 1024;
+  static_assert(PLANE_BYTES <= STAGES * STAGE, "the accumulator plane lies over the operand ring");
+};
+
+__device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+template <int KS>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const float* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, int act,
+                      uint32_t kb_per_split, float* __restrict__ ws, __nv_bfloat16* __restrict__ c_raw) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[Ck::STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[Ck::STAGES];
+  __shared__ __align__(8) uint64_t bar_tmem_full;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // the K range; clusters are KS x 1 x 1 over a 1-D grid
+  volatile int* abort_p = &abort_flag;
+
+  const uint32_t tiles_m = (M + UMMA_M - 1) / UMMA_M, tiles_n = (N + BN - 1) / BN;
+  const uint32_t tile = blockIdx.x / KS;
+  const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+  const uint32_t all_kb = (K + BK - 1) / BK;
+  const uint32_t kb0 = rank * kb_per_split;
+  const uint32_t num_kb = kb0 < all_kb ? (all_kb - kb0 < kb_per_split ? all_kb - kb0 : kb_per_split) : 0u;
+  constexpr uint32_t ROWS_PER = (UMMA_M + KS - 1) / KS;  // rows of the tile a CTA adds and stores
+  const uint32_t rows_here = min(static_cast<uint32_t>(UMMA_M), M - tc.m * UMMA_M);  // rows of the tile inside c
+
+  // Warp 0 initialises the barriers and has the first copies under way before the rest of the CTA is set up
+  // (the TMEM allocation, the CTA-wide barrier): the first bytes from HBM are what the kernel waits for longest.
+  const int32_t a_row = static_cast<int32_t>(tc.m * UMMA_M), b_col = static_cast<int32_t>(tc.n * BN);
+  auto load_stage = [&](uint32_t kb, uint32_t stage) {
+    const uint32_t a_dst = smem_base + stage * Ck::STAGE, b_dst = a_dst + Ck::A_BYTES;
+    const int32_t k0 = static_cast<int32_t>((kb0 + kb) * BK);
+    const uint32_t full = ptx::smem_u32(&bar_full[stage]);
+    if (lane == 0) {
+      ptx::mbar_expect_tx(full, Ck::STAGE);
+      ptx::tma_load_2d(a_dst, &tmap_a, full, k0, a_row);
+    } else if (lane <= BN / 64) {
+      const int j = lane - 1;
+      ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, b_col + j * 64, k0);
+    }
+  };
+  const uint32_t early = num_kb < static_cast<uint32_t>(Ck::STAGES) ? num_kb : static_cast<uint32_t>(Ck::STAGES);
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_b);
+      abort_flag = 0;
+      for (int s = 0; s < Ck::STAGES; ++s) {
+        ptx::mbar_init(ptx::smem_u32(&bar_full[s]), 1);
+        ptx::mbar_init(ptx::smem_u32(&bar_empty[s]), 1);
+      }
+      ptx::mbar_init(ptx::smem_u32(&bar_tmem_full), 1);
+      ptx::fence_barrier_init();
+      ptx::fence_proxy_async();
+    }
+    __syncwarp();
+    for (uint32_t kb = 0; kb < early; ++kb) load_stage(kb, kb);  // the ring is empty: nothing to wait for
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tmem_base_slot), UMMA_N);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  float bv[2][4];  // epilogue warps: the bias of the lane's two groups of four columns
+  if (warp == 0) {
+    // ---------------- TMA producer: lane 0 loads A, lanes 1..4 one 64-column box of B each ----------------
+    uint32_t stage = early == static_cast<uint32_t>(Ck::STAGES) ? 0u : early, phase = early == static_cast<uint32_t>(Ck::STAGES) ? 1u : 0u;
+    for (uint32_t kb = early; kb < num_kb; ++kb) {
+      if (!ptx::mbar_wait(ptx::smem_u32(&bar_empty[stage]), phase ^ 1u, abort_p)) break;
+      load_stage(kb, stage);
+      if (++stage == Ck::STAGES) { stage = 0; phase ^= 1u; }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (uint32_t kb = 0; kb < num_kb; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
+        ptx::tc_fence_after();
+        const uint32_t a_src = smem_base + stage * Ck::STAGE, b_src = a_src + Ck::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t adesc = ptx::smem_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024);
+          const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+          ptx::mma_bf16(tmem_base, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
+        }
+        ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
+        if (++stage == Ck::STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (ok && num_kb > 0) ptx::mma_commit(ptx::smem_u32(&bar_tmem_full));
+    }
+  } else {
+    // ---------------- the accumulator of this range: TMEM -> this CTA's shared memory ----------------
+    // Row r lies at r * 1 KB; its 16-byte chunk c at position c ^ (r & 7), so that the eight lanes of a store
+    // wavefront (eight rows, the same c) fall into eight different bank groups. The ring below is drained: every
+    // copy has landed and every MMA that read it has completed once bar_tmem_full has fired.
+    const uint32_t e = static_cast<uint32_t>(warp) - 2u, quad = static_cast<uint32_t>(warp) & 3u, half = e >> 2;
+    {  // the bias is fetched before the wait: its latency hides under the K loop
+      const uint32_t gcol0 = tc.n * BN + static_cast<uint32_t>(lane) * 4u;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          bv[h][j] = (bias != nullptr && gcol0 + 128u * h < N) ? __ldg(bias + gcol0 + 128u * h + j) : 0.0f;
+    }
+    bool ok = true;
+    if (num_kb > 0) {
+      ok = ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full), 0u, abort_p);
+      ptx::tc_fence_after();
+    }
+    {
+      const uint32_t row = quad * 32u + static_cast<uint32_t>(lane);
+      const uint32_t prow = smem_base + row * 1024u;
+#pragma unroll 1
+      for (uint32_t q = 0; q < 4; ++q) {
+        uint32_t r[32];
+        if (num_kb > 0 && ok) {
+          ptx::tmem_ld_32x32(tmem_base + ((quad * 32u) << 16) + half * 128 + q * 32, r);
+          ptx::tmem_ld_wait_for(r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+#pragma unroll
+        for (uint32_t v = 0; v < 8; ++v) {
+          const uint32_t chunk = half * 32u + q * 8u + v;
+          ptx::st_shared_v4(prow + ((chunk ^ (row & 7u)) << 4), r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        }
+      }
+    }
+    ptx::named_bar_sync(1, EPI_WARPS * 32);  // the whole plane is in shared memory
+    // The rows other CTAs own go to the workspace: a warp per row, 512 contiguous bytes per store instruction.
+    float* mine = ws + static_cast<size_t>(blockIdx.x) * (UMMA_M * BN);
+    for (uint32_t row = e; row < rows_here; row += EPI_WARPS) {
+      if (row / ROWS_PER == rank) continue;
+#pragma unroll
+      for (uint32_t h = 0; h < 2; ++h) {
+        const uint32_t chunk = static_cast<uint32_t>(lane) + 32u * h;
+        const float4 v = ld_shared_v4(smem_base + row * 1024u + ((chunk ^ (row & 7u)) << 4));
+        __stcg(reinterpret_cast<float4*>(mine + row * BN + chunk * 4u), v);
+      }
+    }
+  }
+
+  // every range of the tile is in its CTA's shared memory or, for the rows other CTAs own, in the workspace: the
+  // cluster barrier orders those writes before the peers' reads
+  ptx::tc_fence_before();
+  __syncthreads();  // the warps' roles have diverged: converge before the aligned cluster barrier
+  ptx::cluster_arrive();
+  ptx::cluster_wait();
+
+  if (warp >= 2) {
+    // ---------------- this CTA's rows of the tile: ranges in ascending order, bias, activation ----------------
+    // A lane owns the 16-byte chunks `lane` and `lane + 32` of a row; R rows are in flight together.
+    constexpr int R = KS <= 4 ? 4 : 2;
+    const uint32_t e = static_cast<uint32_t>(warp) - 2u;
+    const uint32_t r_lo = rank * ROWS_PER, r_hi = min(rows_here, r_lo + ROWS_PER);
+    const uint32_t gcol0 = tc.n * BN + static_cast<uint32_t>(lane) * 4u;
+    bool col_ok[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) col_ok[h] = gcol0 + 128u * h < N;  // N % 8 == 0: a group of four columns is inside or outside as a whole
+    const float* peers = ws + static_cast<size_t>(tile) * KS * (UMMA_M * BN);
+#pragma unroll 1
+    for (uint32_t row0 = r_lo + e; row0 < r_hi; row0 += EPI_WARPS * R) {
+      float4 p[R][KS][2];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const uint32_t row = row0 + EPI_WARPS * i;
+#pragma unroll
+        for (int r2 = 0; r2 < KS; ++r2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t chunk = static_cast<uint32_t>(lane) + 32u * h;
+            if (row >= r_hi || !col_ok[h]) p[i][r2][h] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            else if (static_cast<uint32_t>(r2) == rank) p[i][r2][h] = ld_shared_v4(smem_base + row * 1024u + ((chunk ^ (row & 7u)) << 4));
+            else p[i][r2][h] = __ldcg(reinterpret_cast<const float4*>(peers + (static_cast<size_t>(r2) * UMMA_M + row) * BN + chunk * 4u));
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        const uint32_t row = row0 + EPI_WARPS * i;
+        if (row >= r_hi) continue;
+        const size_t grow = static_cast<size_t>(tc.m) * UMMA_M + row;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (!col_ok[h]) continue;
+          float f0 = 0.0f, f1 = 0.0f, f2 = 0.0f, f3 = 0.0f;
+#pragma unroll
+          for (int r2 = 0; r2 < KS; ++r2) {  // ascending ranges: ascending k, like the one-pass kernel
+            f0 += p[i][r2][h].x; f1 += p[i][r2][h].y; f2 += p[i][r2][h].z; f3 += p[i][r2][h].w;
+          }
+          f0 += bv[h][0]; f1 += bv[h][1]; f2 += bv[h][2]; f3 += bv[h][3];  // a sum is never -0: a zero bias keeps its bits
+          if (act == TCAB_ACT_RELU) {
+            f0 = fmaxf(f0, 0.0f); f1 = fmaxf(f1, 0.0f); f2 = fmaxf(f2, 0.0f); f3 = fmaxf(f3, 0.0f);
+          }
+          const __nv_bfloat162 h0 = __floats2bfloat162_rn(f0, f1), h1 = __floats2bfloat162_rn(f2, f3);
+          *reinterpret_cast<uint2*>(c_raw + grow * N + gcol0 + 128u * h) =
+              make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, UMMA_N);
+  }
+  if (threadIdx.x == 0 && abort_flag != 0) g_gemm_status = 5;
+}
+
 // Second pass of a K-split contraction: c = act(sum over ranges of partial + bias), bf16. Eight columns per thread.
 __global__ void __launch_bounds__(256)
 gemm_split_finish(const float* __restrict__ partial, const float* __restrict__ bias, __nv_bfloat16* __restrict__ c,
@@ -974,6 +1220,52 @@ int gemm_device_status(int* out) {
   return TCAB_OK;
 }
 
+// The cluster K-split kernel for a cluster of ks CTAs (2..8).
+const void* cluster_k_fn(int ks) {
+  switch (ks) {
+    case 2: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<2>);
+    case 3: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<3>);
+    case 4: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<4>);
+    case 5: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<5>);
+    case 6: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<6>);
+    case 7: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<7>);
+    default: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<8>);
+  }
+}
+
+// How many clusters of ks CTAs of that kernel the current device holds at once (0 when it cannot say); asked once
+// per device and size. The shared-memory attribute of the device's copy of the function is set on the way.
+int cluster_k_resident(int ks) {
+  constexpr int kMaxDev = 64;
+  static std::mutex mu;
+  static int cache[kMaxDev][9];  // 0 = not asked yet, -1 = none, else the count
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev || ks < 2 || ks > 8) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache[dev][ks] == 0) {
+    const void* fn = cluster_k_fn(ks);
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ks) * 64);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = Ck::SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(ks);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Ck::SMEM)) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, fn, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cache[dev][ks] = n > 0 ? n : -1;
+  }
+  return cache[dev][ks] > 0 ? cache[dev][ks] : 0;
+}
+
 int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const float* bias, int act,
                          __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k, cudaStream_t s) {
   if (m == 0 || n == 0) return TCAB_OK;
@@ -982,6 +1274,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   // kernels, whose 128-row shares give twice the CTAs (measured 2048^3: 620 -> 820 TFLOP/s), single CTAs for one
   // 128-row band, CTA pairs otherwise. tune p1 forces a kernel.
   int variant = tn.p1;
+  if (variant == 5) variant = m <= 128 ? 3 : 4;  // the cluster K split where it applies, else what these shapes get
   if (variant <= 0 && k > 0) {
     const uint64_t tiles256 = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     if (2 * tiles256 <= static_cast<uint64_t>(sm_count())) variant = m <= 128 ? 3 : 4;  // 128 tiles on 148 SMs: the default is faster
@@ -1011,6 +1304,49 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   if (attr_err != cudaSuccess)
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
                 cudaGetErrorString(attr_err));
+  // Few tiles and a long K: one cluster per 128 x 256 tile, one K range per CTA (gemm_cluster_k_kernel), as long as
+  // every cluster is resident at once. tune p1 == 5 asks for it whatever the shape, p3 then gives the cluster size;
+  // p2 == 32 keeps the two-launch workspace form below (p2 == 16 its one-launch variant).
+  if (k > 0 && n % 8 == 0 && tn.p2 != 32 && tn.p2 != 16 && ((tn.p1 <= 0 && (variant == 3 || variant == 4) && tn.p3 <= 0) || tn.p1 == 5)) {
+    const uint32_t all_kb = (k + BK - 1) / BK;
+    const uint64_t tiles = static_cast<uint64_t>((m + UMMA_M - 1) / UMMA_M) * ((n + BN - 1) / BN);
+    uint64_t ks = tn.p3 > 0 ? static_cast<uint64_t>(tn.p3) : static_cast<uint64_t>(sm_count()) / (tiles > 0 ? tiles : 1);
+    if (tn.p3 <= 0 && ks > all_kb / 16) ks = all_kb / 16;  // at least sixteen K blocks (1024 of K) per range
+    if (ks > 8) ks = 8;                                     // the portable cluster size
+    if (ks > all_kb) ks = all_kb;
+    if (tn.p3 <= 0)
+      while (ks >= 2 && static_cast<uint64_t>(cluster_k_resident(static_cast<int>(ks))) < tiles) --ks;  // one wave
+    else if (ks >= 2 && cluster_k_resident(static_cast<int>(ks)) == 0)  // (the query also reserves the shared memory)
+      ks = 0;
+    float* ws = ks >= 2 ? gemm_split_workspace(s, static_cast<size_t>(tiles) * ks * Ck::PLANE_BYTES) : nullptr;
+    if (ks >= 2 && ws != nullptr) {
+      CUtensorMap ta2;
+      const int rc = make_map(&ta2, a, m, k, UMMA_M);
+      if (rc != TCAB_OK) return rc;
+      const void* fn = cluster_k_fn(static_cast<int>(ks));
+      uint32_t kb_per = (all_kb + static_cast<uint32_t>(ks) - 1) / static_cast<uint32_t>(ks);
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(tiles * ks));
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = Ck::SMEM;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(ks);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      void* args[] = {&ta2, &tb, &bias, &m, &n, &k, &act, &kb_per, &ws, &c};
+      const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
+      count_launch();
+      if (le != cudaSuccess) {
+        cudaGetLastError();
+        return fail(TCAB_ERR_CUDA, "gemm_bias_act (cluster K split): launch failed: %s", cudaGetErrorString(le));
+      }
+      return TCAB_OK;
+    }
+  }
   if (variant == 3 || variant == 4) {
     // double-buffered accumulators: A boxes of 128 rows; variant 4 runs clusters of two CTAs
     const bool pair = variant == 4;

@@ -679,11 +679,13 @@ def test_gemm_cta_pair_variant(oracle, cuda, m, k, n, variant):
                                                      (130, 200, 264, 3, 3), (260, 1032, 520, 4, 5), (128, 64, 256, 3, 4),
                                                      (513, 4096, 776, 4, 2)])
 def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
-    # few output tiles and a long K: ranges of K blocks become units of work whose fp32 partials go to a workspace;
-    # a second kernel adds the ranges, the bias and the activation, or -- with the tuning value gemm p2 = 16 -- the
-    # epilogue warp that arrives last at a block of the tile does, inside the one launch (measured slower, kept for
-    # comparison). variant / ranges = 0: the library's own choice. Both forms add the ranges in ascending order:
-    # identical bits.
+    # few output tiles and a long K: ranges of K blocks become units of work. Three forms add the ranges, the bias and
+    # the activation, all in ascending order and so with identical bits: (a) the CTAs of a cluster hold one range of a
+    # 128-row tile each, exchange the rows they do not own through an L2-resident workspace and add their own rows
+    # after a cluster barrier, one launch (the library's choice while every cluster is resident at once, or tuning
+    # value p1 = 5); (b) p2 = 32: every fp32 partial goes to the workspace and a second kernel adds them; (c) p2 = 16:
+    # the epilogue warp that arrives last at a block of the tile adds them inside the one launch (measured slower,
+    # kept for comparison). variant / ranges = 0: the library's own choice.
     a, b, bias = gemm_inputs(oracle, m, k, n, m + 3 * k + n)
     want = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, bias, "relu"))
     buf, out = guarded((m, n), torch.bfloat16, cuda)
@@ -700,17 +702,21 @@ def test_gemm_k_split(oracle, cuda, m, k, n, variant, ranges):
     assert T.device_status() == 0
     split = variant == 0 or min(ranges, (k + 63) // 64) > 1
     if split:
-        assert launches == 2, "expected the contraction and the finishing kernel"
+        assert launches == (1 if variant == 0 else 2), "a cluster per tile, or the contraction and the finishing kernel"
     assert rel_frobenius(got, want) <= 1e-3
-    try:                 # the one-launch form of the same split, three times: its arrival counters return to zero
-        T.tune("gemm", 0, variant, 16, ranges)
-        for _ in range(3):
-            n0 = T.launch_count()
-            one = T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu").float().cpu().numpy()
-            assert T.launch_count() - n0 == 1
-            assert np.array_equal(one, got)
-    finally:
-        T.tune("gemm")
+    for p1, p2, expect in [(variant, 16, 1), (variant, 32, 2 if split else 1), (5, 0, 1)]:
+        try:             # each form three times: the arrival counters of (c) return to zero
+            T.tune("gemm", 0, p1, p2, ranges)
+            for _ in range(3):
+                buf, out = guarded((m, n), torch.bfloat16, cuda)
+                n0 = T.launch_count()
+                T.gemm_bias_act(dev_bf16(a, cuda), dev_bf16(b, cuda), dev_f32(bias, cuda), "relu", out=out)
+                assert T.launch_count() - n0 == expect, (p1, p2)
+                check_guards(buf, torch.bfloat16)
+                assert np.array_equal(out.float().cpu().numpy(), got), (p1, p2)
+        finally:
+            T.tune("gemm")
+    assert T.device_status() == 0
     assert (np.abs(got - want) <= 2.0 ** -7 * np.abs(want) + 1e-5 * np.sqrt(k)).all()
     # no bias, no activation through the same path
     want2 = oracle.bf16_to_f32(oracle.gemm_bias_act_bf16(a, b, None, "none"))
