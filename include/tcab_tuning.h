@@ -31,10 +31,12 @@ extern "C" {
  *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
  *       p3 = CTAs sharing the k axis.
  *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
- *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs),
- *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128; 16: the K ranges
- *       of tcab_gemm_bias_act are added by the last-arriving epilogue warps instead of a second launch),
- *       p3 = ranges the K blocks of a tile are cut into by kernels 3 and 4 (1 = no split). */
+ *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs, 5 one
+ *       cluster per 128 x 256 tile with a K range per CTA, whatever the shape),
+ *       p2 = outputs per thread and side of tcab_chain_contract's tile (4: 64 x 64 tiles, 8: 128 x 128; for
+ *       tcab_gemm_bias_act 32: the K ranges go to a workspace and a second launch adds them, never the cluster
+ *       form; 16: the same with the last-arriving epilogue warps adding them instead of the second launch),
+ *       p3 = ranges the K blocks of a tile are cut into by kernels 3, 4 and 5 (1 = no split; 2..8 for 5). */
 TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 
 

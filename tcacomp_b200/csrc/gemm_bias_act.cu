@@ -1311,7 +1311,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     const uint32_t all_kb = (k + BK - 1) / BK;
     const uint64_t tiles = static_cast<uint64_t>((m + UMMA_M - 1) / UMMA_M) * ((n + BN - 1) / BN);
     uint64_t ks = tn.p3 > 0 ? static_cast<uint64_t>(tn.p3) : static_cast<uint64_t>(sm_count()) / (tiles > 0 ? tiles : 1);
-    if (tn.p3 <= 0 && ks > all_kb / 16) ks = all_kb / 16;  // at least sixteen K blocks (1024 of K) per range
+    if (tn.p3 <= 0 && ks > all_kb / 8) ks = all_kb / 8;    // at least eight K blocks (512 of K) per range
     if (ks > 8) ks = 8;                                     // the portable cluster size
     if (ks > all_kb) ks = all_kb;
     if (tn.p3 <= 0)
