@@ -57,19 +57,6 @@ constexpr size_t SMEM_BYTES =
 // Device status of the last contraction kernel that gave up on a wait (0 = none).
 __device__ int g_gemm_status = 0;
 
-// Developer timeline (off unless the file is compiled with -DTCAB_GEMM_TRACE): CTA 0 records SM clock
-// stamps per tile; tcab_debug_gemm_trace copies them out. slot = tile_iter * 16 + event.
-#ifdef TCAB_GEMM_TRACE
-__device__ long long g_gemm_trace[16 * 64];
-__device__ int g_gemm_debug_mode = 0;  // 1: the double-buffered kernels hand accumulators back without draining them
-#define GEMM_TRACE(tile_iter, ev)                                                        \
-  do {                                                                                   \
-    if (blockIdx.x == 0 && (tile_iter) < 64u) g_gemm_trace[(tile_iter) * 16 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define GEMM_TRACE(tile_iter, ev) do { } while (0)
-#endif
-
 struct TileCoord {
   uint32_t m, n;
 };
@@ -245,21 +232,9 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t stage = 0, phase = 0, tile_iter = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
-        GEMM_TRACE(tile_iter, 0);
-#ifdef TCAB_GEMM_TRACE
-        long long starved = 0;
-#endif
         for (uint32_t kb = 0; ok && kb < num_kb; ++kb) {
-#ifdef TCAB_GEMM_TRACE
-          const long long w0 = clock64();
-#endif
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
-#ifdef TCAB_GEMM_TRACE
-          starved += clock64() - w0;
-          if (blockIdx.x == 0 && tile_iter < 64u) g_gemm_trace[tile_iter * 16 + 8] = starved;
-#endif
           ptx::tc_fence_after();
-          if (kb == 0) GEMM_TRACE(tile_iter, 1);
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
           const uint32_t b_src = a_src + A_STAGE_BYTES;
 #pragma unroll
@@ -267,7 +242,6 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             if (kb == 0) {  // the epilogue must have drained this accumulator (previous tile)
               if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[a]), (tile_iter & 1u) ^ 1u, abort_p)) { ok = false; break; }
               ptx::tc_fence_after();
-              GEMM_TRACE(tile_iter, 6 + a);
             }
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -283,7 +257,6 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (ok) ptx::mma_commit(ptx::smem_u32(&bar_tmem_full));  // both accumulators complete
-        GEMM_TRACE(tile_iter, 2);
       }
     }
   } else {
@@ -311,7 +284,6 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ptx::tc_fence_after();
       }
       if (!ok) continue;
-      if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
       // Eight half boxes of 32 columns per warp and tile, four per accumulator. What the next tile's K loop
       // waits for is the accumulator, not the stores: a warp first pulls its whole share of accumulator 0
       // into registers (128 values per thread) and hands the accumulator back, then converts and stores from
@@ -326,7 +298,6 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         for (uint32_t q = 0; q < 4; ++q) ptx::tmem_ld_wait_for(r[q]);
         ptx::tc_fence_before();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[0]));
-        if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 4);
       } else {
 #pragma unroll
         for (uint32_t q = 0; q < 4; ++q)
@@ -344,7 +315,6 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           for (uint32_t qq = 0; qq < 4; ++qq) ptx::tmem_ld_wait_for(r[qq]);
           ptx::tc_fence_before();
           if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[1]));
-          if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 5);
         }
         // two staging buffers alternate: the store issued two half boxes ago has left this one
         if (lane == 0) ptx::tma_store_wait_read_1();
@@ -679,26 +649,13 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t acc = tile_iter & 1u, use = (tile_iter >> 1) & 1u;
         const uint32_t kb0 = (t % ksplit) * kb_per_split;
         const uint32_t num_kb = kb0 < all_kb ? (all_kb - kb0 < kb_per_split ? all_kb - kb0 : kb_per_split) : 0u;
-        GEMM_TRACE(tile_iter, 0);
         if (num_kb > 0) {  // the epilogue must have drained this accumulator (two tiles ago)
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_empty[acc]), use ^ 1u, abort_p)) break;
           ptx::tc_fence_after();
         }
-        GEMM_TRACE(tile_iter, 6);
-#ifdef TCAB_GEMM_TRACE
-        long long starved = 0;
-#endif
         for (uint32_t kb = 0; kb < num_kb; ++kb) {
-#ifdef TCAB_GEMM_TRACE
-          const long long w0 = clock64();
-#endif
           if (!ptx::mbar_wait(ptx::smem_u32(&bar_full[stage]), phase, abort_p)) { ok = false; break; }
-#ifdef TCAB_GEMM_TRACE
-          starved += clock64() - w0;
-          if (blockIdx.x == 0 && tile_iter < 64u) g_gemm_trace[tile_iter * 16 + 8] = starved;
-#endif
           ptx::tc_fence_after();
-          if (kb == 0) GEMM_TRACE(tile_iter, 1);
           const uint32_t a_src = smem_base + stage * C::STAGE;
           const uint32_t b_src = a_src + C::A_BYTES;
 #pragma unroll
@@ -716,7 +673,6 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           if (PAIR) ptx::mma_commit_pair(ptx::smem_u32(&bar_tmem_full[acc]), 3);
           else ptx::mma_commit(ptx::smem_u32(&bar_tmem_full[acc]));
         }
-        GEMM_TRACE(tile_iter, 2);
       }
     }
   } else {
@@ -739,7 +695,6 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (!ptx::mbar_wait(ptx::smem_u32(&bar_tmem_full[acc]), use, abort_p)) { ok = false; break; }
         ptx::tc_fence_after();
       }
-      if (e == 0 && lane == 0) GEMM_TRACE(tile_iter, 3);
       const uint32_t row0 = tc.m * C::TILE_M + rank * UMMA_M + quad * 32;
       if (ksplit > 1) {
         // fp32 partial of this K range, straight from TMEM: a thread owns a row and writes 32 consecutive columns
@@ -826,15 +781,6 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll 1
       for (uint32_t grp = 0; grp < 2; ++grp) {
         const uint32_t col0 = tc.n * BN + half * 128 + grp * 64;
-#ifdef TCAB_GEMM_TRACE
-        if (g_gemm_debug_mode == 1) {
-          if (grp == 1 && lane == 0 && num_kb > 0) {
-            if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[acc]), 0));
-            else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
-          }
-          continue;
-        }
-#endif
         if (lane == 0) ptx::tma_store_wait_read();  // the previous box has left shared memory
         __syncwarp();
         stage_box_from_tmem(tmem_base + ((quad * 32u) << 16) + acc * UMMA_N + half * 128 + grp * 64, num_kb > 0, breg,
@@ -846,7 +792,6 @@ gemm_bias_act_db_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
           if (grp == 1 && num_kb > 0) {  // hand the accumulator back to the MMA issuer
             if (PAIR) ptx::mbar_arrive_cluster(ptx::mapa(ptx::smem_u32(&bar_tmem_empty[acc]), 0));
             else ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[acc]));
-            if (e == 0) GEMM_TRACE(tile_iter, 4);
           }
           if (row0 < M && col0 < N) {
             ptx::tma_store_2d(&tmap_c, stage_box, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
@@ -1202,15 +1147,6 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 }  // namespace
 
-#ifdef TCAB_GEMM_TRACE
-extern "C" __attribute__((visibility("default"))) int tcab_debug_gemm_trace(long long* out, int n) {
-  if (n > 16 * 64) n = 16 * 64;
-  return cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 1;
-}
-extern "C" __attribute__((visibility("default"))) int tcab_debug_gemm_mode(int mode) {
-  return cudaMemcpyToSymbol(g_gemm_debug_mode, &mode, sizeof(int)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int gemm_device_status(int* out) {
   if (cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(int)) != cudaSuccess) {

@@ -44,18 +44,6 @@ struct Cfg {
 
 __device__ int g_rows_smem_status = 0;
 
-// Developer timeline (compiled in only with -DTCAB_ROWS_TRACE): CTA 0 stamps the SM clock per row;
-// tcab_debug_rows_trace copies the stamps out. slot = row_iter * 8 + event.
-#ifdef TCAB_ROWS_TRACE
-__device__ long long g_rows_trace[8 * 64];
-#define ROWS_TRACE(it, ev)                                                              \
-  do {                                                                                  \
-    if (blockIdx.x == 0 && (it) < 64u) g_rows_trace[(it) * 8 + (ev)] = clock64();       \
-  } while (0)
-#else
-#define ROWS_TRACE(it, ev) do { } while (0)
-#endif
-
 // global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned); completion is
 // counted on `bar` in bytes.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -110,8 +98,6 @@ __device__ __forceinline__ void produce_rows(Ring<CF>& ring, uint32_t ring_base,
     const uint8_t* src = x + row * row_bytes;
     for (uint32_t off = 0; off < row_bytes; off += kSlotBytes) {
       if (!ptx::mbar_wait(ptx::smem_u32(&ring.empty[slot]), phase ^ 1u, abort_p)) return;
-      if (off == 0) ROWS_TRACE(it, 0);
-      if (off + kSlotBytes >= row_bytes) ROWS_TRACE(it, 1);
       const uint32_t bytes = row_bytes - off < static_cast<uint32_t>(kSlotBytes) ? row_bytes - off : kSlotBytes;
       const uint32_t bar = ptx::smem_u32(&ring.full[slot]);
       ptx::mbar_expect_tx(bar, bytes);
@@ -384,7 +370,6 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
       float* yr = y + row * cols;
       bool ok = true;
       float m = -INFINITY;
-      if (threadIdx.x == 0) ROWS_TRACE(it, 2);
       {
         uint32_t slot = slot0, phase = phase0;
         for (uint32_t c = 0; c < nchunks; ++c) {
@@ -407,10 +392,8 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) { slot = 0; phase ^= 1u; }
         }
       }
-      if (threadIdx.x == 0) ROWS_TRACE(it, 3);
       m = consumers_allreduce<CF, OpMax>(m, ring.red[0]);
       if (ring.consumer_abort != 0) break;
-      if (threadIdx.x == 0) ROWS_TRACE(it, 4);
       // pass 2: the exponentials are kept (written back to the slot), so that pass 3 only scales them
       float s = 0.0f;
       {
@@ -431,9 +414,7 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) slot = 0;
         }
       }
-      if (threadIdx.x == 0) ROWS_TRACE(it, 5);
       const float inv = 1.0f / consumers_allreduce<CF, OpSum>(s, ring.red[1]);
-      if (threadIdx.x == 0) ROWS_TRACE(it, 6);
       {
         uint32_t slot = slot0;
         for (uint32_t c = 0; c < nchunks; ++c) {
@@ -456,7 +437,6 @@ softmax_rows_smem(const float* __restrict__ x, float* __restrict__ y, uint64_t r
           if (++slot == kSlots) slot = 0;
         }
       }
-      if (threadIdx.x == 0) ROWS_TRACE(it, 7);
       slot0 += nchunks;
       while (slot0 >= static_cast<uint32_t>(kSlots)) { slot0 -= kSlots; phase0 ^= 1u; }
     }
@@ -494,13 +474,6 @@ int pick_cfg(uint64_t row_bytes, int forced_ctas) {
 }
 
 }  // namespace
-
-#ifdef TCAB_ROWS_TRACE
-extern "C" __attribute__((visibility("default"))) int tcab_debug_rows_trace(long long* out, int n) {
-  if (n > 8 * 64) n = 8 * 64;
-  return cudaMemcpyFromSymbol(out, g_rows_trace, sizeof(long long) * static_cast<size_t>(n)) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 // A row fits when it leaves at least one slot of the largest ring free (the producer then always has room to
 // run ahead).

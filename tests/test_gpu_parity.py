@@ -25,6 +25,7 @@ import pytest
 import torch
 
 import tcacomp_b200 as T
+from guards import guarded_input
 
 pytestmark = pytest.mark.gpu
 
@@ -48,11 +49,11 @@ def check_guards(buf, dtype):
 
 
 def dev_f32(a, dev):
-    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    return guarded_input(a, dev)       # NaN bands around every operand: a read outside it cannot pass by luck
 
 
 def dev_bf16(bits, dev):
-    return torch.from_numpy(bits.view(np.int16)).to(dev).view(torch.bfloat16)
+    return guarded_input(bits, dev)    # uint16 bit patterns -> a bf16 tensor inside NaN bands
 
 
 def host_bits(t):
