@@ -425,6 +425,165 @@ int launch_cluster(const T* x, const T* gamma, const T* beta, float eps, T* y, u
   return launch_cluster_shape<T, 512, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, s);
 }
 
+// Long rows streamed by a cluster (the scheme of softmax_rows_cluster_stream): one segment per CTA, nothing kept
+// on chip. Pass 1 takes the sums of d = x - K and of d * d with K the row's first element; the CTAs' pairs meet
+// through distributed shared memory: mean = K + S1 / n, variance = S2 / n - (S1 / n)^2. When K turns out further
+// than one standard deviation from the mean that difference has cancelled digits, and one more pass over the
+// (L2-resident) segment takes the centred squares instead. The last pass reads the segment again from L2,
+// normalises, scales, shifts and stores. HBM sees each element once in and once out.
+template <typename T, int THREADS, int U, int V>
+__global__ void __launch_bounds__(THREADS)
+layernorm_rows_cluster_stream(const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta,
+                              float eps, T* __restrict__ y, uint32_t cols, uint32_t cs, uint32_t seg_vecs) {
+  using IO = VecIO<T, V>;
+  __shared__ float slots[2][32];
+  __shared__ float cl_a[2], cl_b;  // this CTA's partials, read by the whole cluster
+  const uint32_t rank = cluster_rank();
+  const uint64_t row = blockIdx.x / cs;
+  const uint32_t nvec = cols / V;
+  const uint32_t v0 = rank * seg_vecs < nvec ? rank * seg_vecs : nvec;
+  const uint32_t v1 = nvec - v0 < seg_vecs ? nvec : v0 + seg_vecs;
+  const float n = static_cast<float>(cols);
+  const T* xr = x + row * cols;
+  T* yr = y + row * cols;
+  float k0[V];
+  IO::unpack(IO::load_keep(xr, 0), k0);
+  const float K = k0[0];
+
+  float s1 = 0.0f, s2 = 0.0f;
+  for (uint32_t base = v0 + threadIdx.x; base < v1; base += THREADS * U) {
+    float f[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) {
+        IO::unpack(IO::load_keep(xr, idx), f[u]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) f[u][j] = K;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float d = f[u][j] - K;
+        s1 += d;
+        s2 += d * d;
+      }
+  }
+  s1 = cta_allreduce<OpSum, THREADS / 32>(s1, slots[0]);
+  s2 = cta_allreduce<OpSum, THREADS / 32>(s2, slots[1]);
+  if (threadIdx.x == 0) {
+    cl_a[0] = s1;
+    cl_a[1] = s2;
+  }
+  cluster_sync_all();
+  float g1 = 0.0f, g2 = 0.0f;
+  for (uint32_t r = 0; r < cs; ++r) {  // ascending rank: the same totals in every CTA
+    g1 += ld_dsmem(&cl_a[0], r);
+    g2 += ld_dsmem(&cl_a[1], r);
+  }
+  const float delta = g1 / n;
+  const float mean = K + delta;
+  float var = g2 / n - delta * delta;
+  if (!(delta * delta <= var)) {  // K is far from the mean (or something is not finite): centred squares, one more pass
+    float q = 0.0f;
+    for (uint32_t base = v0 + threadIdx.x; base < v1; base += THREADS * U) {
+      float f[U][V];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t idx = base + u * THREADS;
+        if (idx < v1) {
+          IO::unpack(IO::load_keep(xr, idx), f[u]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) f[u][j] = mean;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < V; ++j) q += (f[u][j] - mean) * (f[u][j] - mean);
+    }
+    q = cta_allreduce<OpSum, THREADS / 32>(q, slots[0]);  // every thread has read slots[0] before the cluster barrier above
+    if (threadIdx.x == 0) cl_b = q;
+    cluster_sync_all();
+    float gq = 0.0f;
+    for (uint32_t r = 0; r < cs; ++r) gq += ld_dsmem(&cl_b, r);
+    var = gq / n;
+  }
+  const float rstd = 1.0f / sqrtf(var + eps);
+  for (uint32_t base = v0 + threadIdx.x; base < v1; base += THREADS * U) {
+    float f[U][V];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) IO::unpack(IO::load(xr, idx), f[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) {
+        float gf[V], bf[V];
+        IO::unpack(IO::load_keep(gamma, idx), gf);
+        IO::unpack(IO::load_keep(beta, idx), bf);
+#pragma unroll
+        for (int j = 0; j < V; ++j) f[u][j] = (f[u][j] - mean) * rstd * gf[j] + bf[j];
+        IO::store(yr, idx, IO::pack(f[u]));
+      }
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its partials
+}
+
+template <typename T, int THREADS, int U, int V>
+int launch_cluster_stream_shape(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                                uint32_t nvec, uint32_t cs, cudaStream_t s) {
+  const uint32_t seg = (nvec + cs - 1) / cs;
+  auto* fn = layernorm_rows_cluster_stream<T, THREADS, U, V>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * cs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, x, gamma, beta, eps, y, cols, cs, seg);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "layernorm_rows_cluster_stream: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
+// tune("layernorm", _, p1 = CTAs per row, p2 = shape 1..5, p3 = 7) forces a shape of the streaming clusters.
+template <typename T, int V>
+int launch_cluster_stream(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_t rows, uint32_t cols,
+                          uint32_t nvec, cudaStream_t s) {
+  const Tune& tn = tune(kLayernorm);
+  uint32_t cs = 0;
+  int shape = 0;
+  if (tn.p3 == 7) {
+    cs = tn.p1 >= 1 && tn.p1 <= 8 ? static_cast<uint32_t>(tn.p1) : 0u;
+    shape = tn.p2;
+  }
+  if (shape <= 0) shape = nvec <= 8u * 1024u * 4u ? 1 : nvec <= 8u * 2048u * 4u ? 2 : 5;
+  if (cs == 0) cs = stream_cluster_size(nvec, shape == 1 ? 1024u : shape == 5 ? 4096u : 2048u, sizeof(T) == 4);
+  switch (shape) {
+    case 1: return launch_cluster_stream_shape<T, 256, 4, V>(x, gamma, beta, eps, y, rows, cols, nvec, cs, s);
+    case 2: return launch_cluster_stream_shape<T, 512, 4, V>(x, gamma, beta, eps, y, rows, cols, nvec, cs, s);
+    case 3: return launch_cluster_stream_shape<T, 256, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, cs, s);
+    case 4: return launch_cluster_stream_shape<T, 256, 2, V>(x, gamma, beta, eps, y, rows, cols, nvec, cs, s);
+    default: return launch_cluster_stream_shape<T, 512, 8, V>(x, gamma, beta, eps, y, rows, cols, nvec, cs, s);
+  }
+}
+
 // Rows too long even for a cluster: one CTA per row, three streaming passes (sum,
 // centred squares, normalise); passes two and three re-read the row from L2.
 template <typename T, int THREADS, int V>
@@ -542,6 +701,18 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   // pass (shifted sums) and wins where the register kernel needs 1024 threads, rows beyond 32 KiB (20480 columns
   // 4.9 against 3.8, 24576 columns 5.0 against 4.0, 32768 columns 4.5 against 4.2, 65536 columns 4.0 against 3.9,
   // 90112 columns 3.9 against 2.0). p3 == 4 forces the shared-memory kernel.
+  // Long rows, enough of them to fill the GPU with small CTAs: streaming clusters. fp32 from 24576 columns
+  // (measured, 2^27 elements, TB/s against the shared-memory rows / register kernels: 24576 columns 5.5 against
+  // 4.9, 32768 5.2 against 5.0, 45056 5.3 against 4.6, 65536 4.9 against 3.7, 131072 4.9 against 3.0); bf16 rows
+  // only beyond what the shared-memory kernel takes (131072 columns 4.2 against 2.4; at 49152-65536 the two are
+  // within 5 %). p3 == 7 forces them.
+  {
+    const uint64_t rb = static_cast<uint64_t>(cols) * sizeof(T);
+    const bool pays = sizeof(T) == 4 ? nvec >= 6144u : !rows_smem_fits(rb);
+    if (vec && tn.p0 <= 0 && rows * 8 <= 0x7fffffffull &&
+        (tn.p3 == 7 || (tn.p3 <= 0 && pays && rows * 2 >= static_cast<uint64_t>(sm_count()))))
+      return launch_cluster_stream<T, VW>(x, gamma, beta, eps, y, rows, cols, nvec, s);
+  }
   const uint64_t row_bytes = static_cast<uint64_t>(cols) * sizeof(T);
   const bool smem_pays = sizeof(T) == 4 ? nvec >= 2560 : row_bytes > 32768;
   if (vec && tn.p0 <= 0 && rows_smem_fits(row_bytes) &&

@@ -468,6 +468,162 @@ softmax_rows_online(const float* __restrict__ x, float* __restrict__ y, uint64_t
   }
 }
 
+// Long rows streamed by a cluster: the row is cut into one segment per CTA. Pass 1 streams the segment once with
+// U vectors in flight per thread and keeps a running (max, sum) per thread, rescaling the sum when the max moves;
+// the CTAs' (max, sum) pairs meet through distributed shared memory. Pass 2 reads the segment again -- from L2,
+// where pass 1 left it: the segments in flight on the whole GPU are far smaller than L2 -- and writes y. HBM
+// still sees each element once in and once out; nothing has to fit in registers, so the CTAs are small and many
+// of them share an SM, each in another phase. (Requesting the next step's vectors before using the current ones
+// was measured 3-6 % slower: the registers cost resident CTAs.)
+template <int THREADS, int U>
+__global__ void __launch_bounds__(THREADS)
+softmax_rows_cluster_stream(const float* __restrict__ x, float* __restrict__ y, uint64_t rows, uint32_t cols, uint32_t cs,
+                            uint32_t seg_vecs) {
+  using IO = VecIO<float, 4>;
+  __shared__ float slots[2][32];
+  __shared__ float cl_max, cl_sum;  // this CTA's partials, read by the whole cluster
+  const uint32_t rank = cluster_rank();
+  const uint64_t row = blockIdx.x / cs;  // clusters are consecutive CTAs: one row per cluster
+  // x and y are 16-byte aligned as arrays; a row whose length is not a multiple of four starts anywhere inside a
+  // vector. Its first `head` and last `tail` elements (at most three each) ride with thread 0 of CTA 0, the
+  // aligned vectors between them are cut into the CTAs' segments.
+  const uint64_t start = row * cols;
+  const uint32_t head = min(cols, (4u - static_cast<uint32_t>(start & 3u)) & 3u);
+  const uint32_t nvec = (cols - head) / 4;
+  const uint32_t tail = cols - head - 4 * nvec;
+  const uint32_t v0 = rank * seg_vecs < nvec ? rank * seg_vecs : nvec;
+  const uint32_t v1 = nvec - v0 < seg_vecs ? nvec : v0 + seg_vecs;
+  const float* xe = x + start;            // the row, element-wise
+  float* ye = y + start;
+  const float* xr = xe + head;            // its aligned vectors
+  float* yr = ye + head;
+  const bool edges = rank == 0 && threadIdx.x == 0 && head + tail > 0;
+  (void)rows;
+
+  float m = -INFINITY, s = 0.0f;
+  if (edges) {
+    for (uint32_t j = 0; j < head + tail; ++j) m = fmaxf(m, __ldg(xe + (j < head ? j : cols - tail + (j - head))));
+    if (m != -INFINITY)
+      for (uint32_t j = 0; j < head + tail; ++j) s += expf(__ldg(xe + (j < head ? j : cols - tail + (j - head))) - m);
+  }
+  for (uint32_t base = v0 + threadIdx.x; base < v1; base += THREADS * U) {
+    float f[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) {
+        IO::unpack(IO::load_keep(xr, idx), f[u]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[u][j] = -INFINITY;
+      }
+    }
+    float lm = f[0][0];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) lm = fmaxf(lm, f[u][j]);
+    if (lm > m) {  // the running max moves: rescale what was summed so far
+      s *= expf(m - lm);
+      m = lm;
+    }
+    if (m != -INFINITY) {  // nothing finite seen yet: -inf entries add 0, as in the plain formula
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s += expf(f[u][j] - m);
+    }
+  }
+  const float cm = cta_allreduce<OpMax, THREADS / 32>(m, slots[0]);
+  // A thread that saw nothing has m = -inf and s = 0; expf(-inf - cm) = 0 keeps it neutral unless cm is -inf too
+  s = (m == -INFINITY && cm != -INFINITY) ? 0.0f : s * expf(m - cm);
+  const float csum = cta_allreduce<OpSum, THREADS / 32>(s, slots[1]);
+  if (threadIdx.x == 0) {
+    cl_max = cm;
+    cl_sum = csum;
+  }
+  cluster_sync_all();
+  float gm = -INFINITY;
+  for (uint32_t r = 0; r < cs; ++r) gm = fmaxf(gm, ld_dsmem(&cl_max, r));
+  float gs = 0.0f;
+  for (uint32_t r = 0; r < cs; ++r) {  // ascending rank: the same total in every CTA
+    const float pm = ld_dsmem(&cl_max, r), ps = ld_dsmem(&cl_sum, r);
+    gs += (pm == -INFINITY && gm != -INFINITY) ? 0.0f : ps * expf(pm - gm);  // an all -inf row: NaN, like the plain formula
+  }
+  const float inv = 1.0f / gs;
+  if (edges)
+    for (uint32_t j = 0; j < head + tail; ++j) {
+      const uint32_t c = j < head ? j : cols - tail + (j - head);
+      ye[c] = expf(__ldg(xe + c) - gm) * inv;
+    }
+  for (uint32_t base = v0 + threadIdx.x; base < v1; base += THREADS * U) {
+    float f[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) IO::unpack(IO::load(xr, idx), f[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t idx = base + u * THREADS;
+      if (idx < v1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) f[u][j] = expf(f[u][j] - gm) * inv;
+        IO::store(yr, idx, IO::pack(f[u]));
+      }
+    }
+  }
+  cluster_sync_all();  // no CTA leaves while a peer may still read its partials
+}
+
+template <int THREADS, int U>
+int launch_cluster_stream_shape(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, uint32_t cs, cudaStream_t s) {
+  const uint32_t seg = (nvec + cs - 1) / cs;
+  auto* fn = softmax_rows_cluster_stream<THREADS, U>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows * cs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, fn, x, y, rows, cols, cs, seg);
+  count_launch();
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "softmax_rows_cluster_stream: launch failed: %s", cudaGetErrorString(e));
+  }
+  return TCAB_OK;
+}
+
+// Shape of the streaming clusters: 256 threads x 4 vectors per step while eight CTAs cover the row in four steps
+// that way, then 512 x 4, then 512 x 8. Measured (2^27 elements, TB/s, against the register clusters
+// and the shared-memory rows): 24576 columns 6.1 (5.5), 32768 5.8 (5.6), 49152 6.0 (5.1), 65536 5.5 (5.2), 98304
+// 5.7 (4.9), 131072 5.3 (4.4), 262144 5.1 (4.0), 524288 4.8 (3.2), 1048576 4.3 (2.0). tune("softmax", _, p1 =
+// CTAs per row, p2 = shape 1..5, p3 = 7) forces one.
+int launch_cluster_stream(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
+  const Tune& tn = tune(kSoftmax);
+  uint32_t cs = 0;
+  int shape = 0;
+  if (tn.p3 == 7) {
+    cs = tn.p1 >= 1 && tn.p1 <= 8 ? static_cast<uint32_t>(tn.p1) : 0u;
+    shape = tn.p2;
+  }
+  if (shape <= 0) shape = nvec <= 8u * 1024u * 4u ? 1 : nvec <= 8u * 2048u * 4u ? 2 : 5;
+  if (cs == 0) cs = stream_cluster_size(nvec, shape == 1 ? 1024u : shape == 5 ? 4096u : 2048u, true);
+  switch (shape) {
+    case 1: return launch_cluster_stream_shape<256, 4>(x, y, rows, cols, nvec, cs, s);
+    case 2: return launch_cluster_stream_shape<512, 4>(x, y, rows, cols, nvec, cs, s);
+    case 3: return launch_cluster_stream_shape<256, 8>(x, y, rows, cols, nvec, cs, s);
+    case 4: return launch_cluster_stream_shape<1024, 4>(x, y, rows, cols, nvec, cs, s);
+    default: return launch_cluster_stream_shape<512, 8>(x, y, rows, cols, nvec, cs, s);
+  }
+}
+
 template <int TPR, int VPT, int V>
 int launch_reg(const float* x, float* y, uint64_t rows, uint32_t cols, int ctas_per_sm, cudaStream_t s) {
   constexpr int THREADS = row_cta_threads(TPR);
@@ -500,6 +656,11 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   const bool vec = (cols % 4 == 0) && aligned16(x) && aligned16(y);
   const uint32_t nvec = vec ? cols / 4 : cols;
   const Tune& tn = tune(kSoftmax);
+  // Rows from 6144 vectors (24576 columns) up, enough of them to fill the GPU with small CTAs: streaming clusters
+  // (any row length: the row ends that do not fill a vector are handled element by element).
+  if (aligned16(x) && aligned16(y) && rows * 8 <= 0x7fffffffull && tn.p0 <= 0 &&
+      (tn.p3 == 7 || (tn.p3 <= 0 && cols / 4 >= 6144u && rows * 2 >= static_cast<uint64_t>(sm_count()))))
+    return launch_cluster_stream(x, y, rows, cols, cols / 4, s);
   // rows that are not a multiple of four columns but still fit a CTA's registers as 16-byte vectors
   if (!vec && cols % 4 != 0 && cols >= 16 && aligned16(x) && aligned16(y) && tn.p0 <= 0 && tn.p3 != 6) {
     const uint32_t nv = cols / 4;  // aligned vectors inside a row, at most

@@ -190,6 +190,43 @@ def test_softmax_rows(oracle, cuda, rows, cols):
     assert np.abs(got.astype(np.float64).sum(1) - 1.0).max() <= 1e-5
 
 
+@pytest.mark.parametrize("rows,cols,cs,shape", [(80, 24576, 0, 0), (75, 49152, 0, 0), (74, 98308, 0, 0),   # the library's own choice
+                                                 (76, 50257, 0, 0), (77, 32003, 0, 0), (5, 4099, 2, 1), (6, 1001, 4, 1),
+                                                 (3, 70001, 8, 3), (4, 14, 2, 1), (9, 9, 8, 1),
+                                                 (3, 4096, 2, 1), (2, 12292, 3, 1), (5, 1028, 8, 1), (2, 65536, 4, 2),
+                                                 (3, 40000, 5, 3), (1, 300000, 8, 4), (2, 262148, 8, 5), (1, 1048576, 8, 5),
+                                                 (7, 20, 8, 1)])
+def test_softmax_streaming_clusters(oracle, cuda, rows, cols, cs, shape):
+    # long rows: a cluster streams the row twice (the second time from L2) with an online max / sum in the first
+    # pass; forced shapes include clusters with CTAs that get no element at all
+    rng = np.random.default_rng(rows + cols + cs)
+    x = (4 * rng.normal(0, 1, (rows, cols))).astype(np.float32)
+    x[0, :: max(2, cols // 7)] = -np.inf            # -inf entries add nothing
+    x[rows - 1, cols // 3:] -= 40.0                 # the maximum sits early in the row: later segments rescale
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    n0 = T.launch_count()
+    try:
+        if cs:
+            T.tune("softmax", 0, cs, shape, 7)
+        T.softmax_rows(dev_f32(x, cuda), out=out)
+    finally:
+        T.tune("softmax")
+    assert T.launch_count() - n0 == 1
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert_softmax_close(got, oracle.softmax_rows(x), x)
+    assert np.abs(got.astype(np.float64).sum(1) - 1.0).max() <= 1e-5
+    # an all -inf row is NaN, like the plain formula; one finite entry takes everything
+    xx = np.full((2, cols), -np.inf, np.float32)
+    xx[1, cols // 2] = 5.0
+    try:
+        T.tune("softmax", 0, cs or 2, shape or 1, 7)
+        g = T.softmax_rows(dev_f32(xx, cuda)).cpu().numpy()
+    finally:
+        T.tune("softmax")
+    assert np.isnan(g[0]).all() and g[1, cols // 2] == 1.0 and g[1].sum() == 1.0
+
+
 def test_softmax_unaligned_view(oracle, cuda):
     rng = np.random.default_rng(12)
     x = (4 * rng.normal(0, 1, (9, 256))).astype(np.float32)
@@ -316,6 +353,50 @@ def test_layernorm_cluster_kernel_forced(oracle, cuda, cols):
     finally:
         T.tune("layernorm")
     assert_layernorm_bf16_close(oracle, got, oracle.layernorm_rows_bf16(x, g, b, 1e-5), x, g, b)
+
+
+@pytest.mark.parametrize("dtype,rows,cols,cs,shape", [("f32", 80, 24576, 0, 0), ("f32", 75, 45056, 0, 0), ("bf16", 74, 131072, 0, 0),
+                                                       ("f32", 3, 4096, 2, 1), ("f32", 2, 12292, 3, 4), ("f32", 5, 1028, 8, 1),
+                                                       ("f32", 2, 65536, 4, 2), ("f32", 1, 300000, 8, 5), ("f32", 7, 20, 8, 1),
+                                                       ("bf16", 3, 8192, 2, 1), ("bf16", 2, 65544, 5, 3), ("bf16", 1, 300008, 8, 5),
+                                                       ("bf16", 6, 40, 8, 4)])
+def test_layernorm_streaming_clusters(oracle, cuda, dtype, rows, cols, cs, shape):
+    # long rows: a cluster streams the row (statistics from shifted sums in one pass; a centred pass when the shift
+    # turns out far from the mean), then once more from L2 to normalise. Row 0 has a mean far from its first
+    # element (the centred pass runs), the other rows do not; forced shapes include CTAs without any element.
+    rng = np.random.default_rng(rows + cols + cs)
+    x = rng.normal(0.2, 1, (rows, cols)).astype(np.float32)
+    x[0] += 7.0
+    x[0, 0] = 0.0
+    g = rng.normal(1, 0.1, cols).astype(np.float32)
+    b = rng.normal(0, 0.1, cols).astype(np.float32)
+    n0 = T.launch_count()
+    try:
+        if cs:
+            T.tune("layernorm", 0, cs, shape, 7)
+        if dtype == "f32":
+            buf, out = guarded((rows, cols), torch.float32, cuda)
+            T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5, out=out)
+        else:
+            xb, gb, bb = oracle.f32_to_bf16(x), oracle.f32_to_bf16(g), oracle.f32_to_bf16(b)
+            buf, out = guarded((rows, cols), torch.bfloat16, cuda)
+            T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5, out=out)
+    finally:
+        T.tune("layernorm")
+    assert T.launch_count() - n0 == 1
+    if dtype == "f32":
+        got = out.cpu().numpy()
+        check_guards(buf, torch.float32)
+        want = oracle.layernorm_rows_f32(x, g, b, 1e-5)
+        x64 = x.astype(np.float64)
+        y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+        scale = np.abs(y64).max()
+        assert np.abs(got - y64).max() <= 1e-5 * scale
+        assert np.abs(got - want).max() <= 1e-5 * scale + np.abs(want - y64).max()
+    else:
+        got = host_bits(out)
+        check_guards(buf, torch.bfloat16)
+        assert_layernorm_bf16_close(oracle, got, oracle.layernorm_rows_bf16(xb, gb, bb, 1e-5), xb, gb, bb)
 
 
 @pytest.mark.parametrize("cache", [0, 1])

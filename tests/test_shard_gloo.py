@@ -108,3 +108,35 @@ def test_reduction_along_the_sharded_axis_two_ranks():
         p.join(60)
         assert p.exitcode == 0
     assert res == (True, True, True)
+
+
+def test_run_block_queues_exactly_this_ranks_slices():
+    """multi.run_block: every rank queues its own contiguous block of the GLOBAL host buffers through its pipeline,
+    a rank whose block is empty queues nothing, and the blocks of all ranks tile the problem (fake pipeline: the
+    host logic needs no device)."""
+    from tcacomp_b200 import multi
+
+    class FakePipeline:
+        def __init__(self):
+            self.calls = []
+
+        def run(self, ins, outs, n):
+            self.calls.append((ins, outs, n))
+            for i, o in zip(ins, outs):
+                o.copy_(i * 2)
+
+    for units in (0, 1, 3, 16, 17):
+        for world in (1, 2, 3, 4):
+            x = torch.arange(units * 5, dtype=torch.float32).view(units, 5)
+            y = torch.full_like(x, -1.0)
+            total = 0
+            for rank in range(world):
+                pipe = FakePipeline()
+                n = multi.run_block(pipe, [x], [y], units, world, rank)
+                views, m = multi.block_views([x], units, world, rank)
+                assert m == n == views[0].shape[0]
+                assert len(pipe.calls) == (1 if n > 0 else 0)
+                if n:
+                    assert pipe.calls[0][0][0].data_ptr() == views[0].data_ptr()   # a view of the global buffer, no copy
+                total += n
+            assert total == units and torch.equal(y, x * 2)
