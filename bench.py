@@ -208,6 +208,14 @@ class SoftmaxLongRows(SoftmaxRows):
     profile = "softmax_rows_smem_softmax_rows_f32_8192x16384.md"
 
 
+class SoftmaxVocabRows(SoftmaxRows):
+    """Rows as long as a vocabulary (the streaming clusters: two passes, the second from L2); selectable only."""
+    name = "softmax_rows_f32_2048x65536"
+    full_units, cols = 2048, 65536
+    shape = "x fp32 [2048, 65536] ~ 4*N(0,1) -> y fp32 [2048, 65536]"
+    profile = "softmax_rows_cluster_stream_softmax_rows_f32_2048x65536.md"
+
+
 class LayernormRows(Workload):
     name = "layernorm_rows_bf16_65536x8192"
     dtype = "bf16"
@@ -492,7 +500,7 @@ class MapOnly(Workload):
 
 
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
-SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows})
+SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows})
 DEFAULT = SoftmaxRows.name
 
 
