@@ -227,8 +227,12 @@ TCAB_API int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
  * internal/cg/cxx/launch.go:23-156). Each output is folded over k in ascending order, the order of the
  * reference's CPU loops (testing/runners/gemm.cu:44-56). lhs and rhs are f32, bf16, i32 or u32 (a bf16
  * operand is widened at the load; the lambda converts it explicitly, e.g. "f32(p0) * f32(p1)", the spelling of
- * testing/kernels/llm/qk_score.tca with bf16 storage); out is f32. SIMT fp32 arithmetic, any lambda: the
- * tensor-core path for the plain bf16 product is tcab_gemm_bias_act. */
+ * testing/kernels/llm/qk_score.tca with bf16 storage); out is f32. Any lambda runs in fp32 arithmetic on the
+ * scalar pipes. One chain runs on the tensor cores instead (fp32 accumulation, fp32 store, the same launch
+ * count): both operands bf16, map the plain product "f32(p0) * f32(p1)", a sum reducer with init 0, no piped map
+ * or a scaling by one constant ("p0 * c0", "0.5f * p0"), K a multiple of 8, N a multiple of 4 (of 8 when rhs is
+ * [K,N]) and 16-byte aligned pointers. Products of bf16 values are exact in fp32, so only the order in which an
+ * output's k terms are added differs from the scalar kernel. */
 TCAB_API int tcab_chain_contract(const tcab_chain* chain, const tcab_tensor* lhs, const tcab_tensor* rhs,
                                  int rhs_is_nk, const tcab_tensor* out, void* stream);
 

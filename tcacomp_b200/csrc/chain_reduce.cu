@@ -604,6 +604,19 @@ int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float
     return fail(TCAB_ERR_TOO_LARGE, "chain_contract: more than 65535 row tiles");
   Caps caps;
   for (int i = 0; i < 16; ++i) caps.c[i] = pc.caps[i];
+  // bf16 x bf16 with the plain product, a sum reducer and init 0, stored as it is or scaled: that is a tensor-core
+  // contraction with fp32 accumulation (products of bf16 values are exact in fp32, so only the order of the sum
+  // differs from the scalar kernel). Needs 16-byte rows and pointers; tune("gemm", _, _, 64) keeps the scalar kernel.
+  if (pc.spec.in_types[0] == TCAB_BF16 && pc.spec.in_types[1] == TCAB_BF16 && pc.spec.combine == 0 &&
+      pc.init == 0.0f && pc.spec.map_text == "(static_cast<float>(p0) * static_cast<float>(p1))" &&
+      (pc.spec.post_text.empty() || pc.spec.post_text == "(p0 * c0)" || pc.spec.post_text == "(c0 * p0)") &&
+      k % 8 == 0 && n % 4 == 0 && (rhs_nk || n % 8 == 0) && ((reinterpret_cast<uintptr_t>(lhs) | reinterpret_cast<uintptr_t>(rhs) |
+                                                              reinterpret_cast<uintptr_t>(out)) & 15u) == 0 &&
+      tune(kGemm).p2 != 64) {
+    const float alpha = pc.spec.post_text.empty() ? 1.0f : pc.caps[8];  // the piped map's first constant
+    return launch_contract_bf16_tc(reinterpret_cast<const __nv_bfloat16*>(lhs), reinterpret_cast<const __nv_bfloat16*>(rhs), rhs_nk,
+                                   alpha, out, m, n, k, s);
+  }
   // ahead-of-time: the plain product with a sum reducer, stored as it is or scaled
   if (pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text()) {
     const std::string post = kTable[pc.entry].post;

@@ -116,6 +116,9 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
                          int act, __nv_bfloat16* c, uint32_t m, uint32_t n, uint32_t k,
                          cudaStream_t s);
 
+int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int b_is_nk, float alpha, float* c, uint32_t m,
+                            uint32_t n, uint32_t k, cudaStream_t s);  // tensor cores, fp32 out (gemm_bias_act.cu)
+
 int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
 int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,
                                 uint32_t rows, uint32_t nk, cudaStream_t s);  // ins: [nprob][n_in]

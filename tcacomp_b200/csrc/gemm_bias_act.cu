@@ -158,10 +158,26 @@ __device__ __forceinline__ void stage_half_box(const uint32_t (&r)[32], const fl
     ptx::st_shared_v4(my_row + ((static_cast<uint32_t>(v) ^ sw) * 16u), w[v * 4], w[v * 4 + 1], w[v * 4 + 2], w[v * 4 + 3]);
 }
 
+// The same half box as fp32 for the contraction chains that store what they accumulate: 32 rows x 32 columns,
+// scaled, to a 4 KB staging buffer with 128-byte rows and the 128-byte swizzle (chunk c of row r at c ^ (r % 8)).
+__device__ __forceinline__ void stage_half_box_f32(const uint32_t (&r)[32], float alpha, uint32_t buf, int lane) {
+  const uint32_t my_row = buf + static_cast<uint32_t>(lane) * 128u;
+  const uint32_t sw = static_cast<uint32_t>(lane) & 7u;
+#pragma unroll
+  for (uint32_t v = 0; v < 8; ++v)
+    ptx::st_shared_v4(my_row + ((v ^ sw) * 16u), __float_as_uint(__uint_as_float(r[v * 4]) * alpha),
+                      __float_as_uint(__uint_as_float(r[v * 4 + 1]) * alpha), __float_as_uint(__uint_as_float(r[v * 4 + 2]) * alpha),
+                      __float_as_uint(__uint_as_float(r[v * 4 + 3]) * alpha));
+}
+
+// OUT_F32: c is fp32 and receives alpha * accumulator (no bias, no activation): the tensor-core form of a
+// contraction chain over bf16 operands whose map is the plain product. B_NK: b is [N, K] (K contiguous) instead of
+// [K, N]; its tile is then K-major in shared memory like a's.
+template <bool OUT_F32, bool B_NK>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_c, const float* __restrict__ bias, uint32_t M,
-                     uint32_t N, uint32_t K, int act) {
+                     uint32_t N, uint32_t K, int act, float alpha) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
   __shared__ __align__(8) uint64_t bar_empty[STAGES];
@@ -217,10 +233,14 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
           ptx::mbar_expect_tx(full, STAGE_BYTES);
           ptx::tma_load_2d(a_dst, &tmap_a, full, static_cast<int32_t>(kb * BK), static_cast<int32_t>(tc.m * BM));
+          if (B_NK) {  // one box: 256 rows of n, 64 of k
+            ptx::tma_load_2d(b_dst, &tmap_b, full, static_cast<int32_t>(kb * BK), static_cast<int32_t>(tc.n * BN));
+          } else {
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, static_cast<int32_t>(tc.n * BN + j * 64),
-                             static_cast<int32_t>(kb * BK));
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, static_cast<int32_t>(tc.n * BN + j * 64),
+                               static_cast<int32_t>(kb * BK));
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -228,7 +248,7 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/B_NK ? 0 : 1);
       uint32_t stage = 0, phase = 0, tile_iter = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++tile_iter) {
@@ -248,7 +268,9 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               // A: K-major, 8-row groups 1024 B apart; one UMMA_K step is 32 B inside the 128-B swizzle row.
               const uint64_t adesc = ptx::smem_desc_sw128(a_src + a * (UMMA_M * 128) + k * (UMMA_K * 2), 16, 1024);
               // B: N-major, 64-wide n atoms B_ATOM_BYTES apart, 8-k-row groups 1024 B apart; one step is 16 k-rows.
-              const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+              // ([N, K] operand: K-major like A, 256 rows of n in 8-row groups 1024 B apart)
+              const uint64_t bdesc = B_NK ? ptx::smem_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024)
+                                          : ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
               ptx::mma_bf16(tmem_base + a * UMMA_N, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
             }
           }
@@ -309,17 +331,22 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         const uint32_t a = i >> 2, q = i & 3u, cbase = q * 32;  // accumulator, register block, first column
         const uint32_t row0 = tc.m * BM + a * UMMA_M + quad * 32;
         const uint32_t col0 = tc.n * BN + half * 128 + cbase;
-        const uint32_t buf = stage_box + (i & 1u) * (EPI_BOX_BYTES / 2);
+        const uint32_t buf = OUT_F32 ? stage_box : stage_box + (i & 1u) * (EPI_BOX_BYTES / 2);
         if (i == 4 && num_kb > 0) {  // accumulator 1 is in registers
 #pragma unroll
           for (uint32_t qq = 0; qq < 4; ++qq) ptx::tmem_ld_wait_for(r[qq]);
           ptx::tc_fence_before();
           if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bar_tmem_empty[1]));
         }
-        // two staging buffers alternate: the store issued two half boxes ago has left this one
-        if (lane == 0) ptx::tma_store_wait_read_1();
+        // two staging buffers alternate: the store issued two half boxes ago has left this one (an fp32 half box
+        // fills the warp's whole staging space: the previous store must have left it)
+        if (lane == 0) {
+          if (OUT_F32) ptx::tma_store_wait_read();
+          else ptx::tma_store_wait_read_1();
+        }
         __syncwarp();
-        stage_half_box(r[q], bias_s + half * 128 + cbase, act, buf, lane);
+        if (OUT_F32) stage_half_box_f32(r[q], alpha, buf, lane);
+        else stage_half_box(r[q], bias_s + half * 128 + cbase, act, buf, lane);
         if (i < 4 && num_kb > 0) ptx::tmem_ld_32x32(tm_warp + UMMA_N + q * 32, r[q]);  // refill from accumulator 1
         ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
         __syncwarp();
@@ -1145,6 +1172,21 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
   return TCAB_OK;
 }
 
+// A 2-D fp32 row-major tensor with a box of box_rows x 32 columns (128-byte rows, 128-byte swizzle).
+int make_map_f32(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  EncodeFn enc = encode_fn();
+  if (enc == nullptr) return fail(TCAB_ERR_CUDA, "chain_contract: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TCAB_ERR_CUDA, "chain_contract: cuTensorMapEncodeTiled failed (%d)", static_cast<int>(r));
+  return TCAB_OK;
+}
+
 }  // namespace
 
 
@@ -1235,7 +1277,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   }
   // per launch, like the reference's launcher does above 48 KB (internal/cg/cxx/launch.go:145-155):
   // the attribute belongs to the current device's copy of the function
-  const cudaError_t attr_err = cudaFuncSetAttribute(gemm_bias_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  const cudaError_t attr_err = cudaFuncSetAttribute(gemm_bias_act_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                     static_cast<int>(SMEM_BYTES));
   if (attr_err != cudaSuccess)
     return fail(TCAB_ERR_CUDA, "gemm_bias_act: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES,
@@ -1397,9 +1439,45 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   uint64_t grid = tn.p0 > 0 ? static_cast<uint64_t>(tn.p0) : static_cast<uint64_t>(sm_count());
   if (grid > tiles) grid = tiles;
-  gemm_bias_act_kernel<<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, tcm, bias, m, n, k, act);
+  gemm_bias_act_kernel<false, false><<<static_cast<unsigned>(grid), THREADS, SMEM_BYTES, s>>>(ta, tb, tcm, bias, m, n, k, act, 1.0f);
   count_launch();
   return check_launch("gemm_bias_act_kernel");
+}
+
+// c[m, n] (fp32) = alpha * sum_k a[m, k] * b[k, n] (or b[n, k]) over bf16 operands, fp32 accumulation in the tensor
+// cores: what a contraction chain with the plain product as its map, a sum reducer and init 0 asks for. The caller
+// has checked the alignment rules (K % 8 == 0, N % 8 == 0 for [K, N] operands, N % 4 == 0, 16-byte aligned
+// pointers).
+int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int b_is_nk, float alpha, float* c, uint32_t m,
+                            uint32_t n, uint32_t k, cudaStream_t s) {
+  if (m == 0 || n == 0) return TCAB_OK;
+  if (k == 0) {  // an empty reduction: init = 0 everywhere
+    const cudaError_t e = cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * sizeof(float), s);
+    return e == cudaSuccess ? TCAB_OK : fail(TCAB_ERR_CUDA, "chain_contract: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+  }
+  CUtensorMap ta, tb, tcm;
+  int rc = make_map(&ta, a, m, k, BM);
+  if (rc == TCAB_OK) rc = b_is_nk ? make_map(&tb, b, n, k, BN) : make_map(&tb, b, k, n, BK);
+  if (rc == TCAB_OK) rc = make_map_f32(&tcm, c, m, n, 32, 32);
+  if (rc != TCAB_OK) return rc;
+  const void* fn = b_is_nk ? reinterpret_cast<const void*>(gemm_bias_act_kernel<true, true>)
+                           : reinterpret_cast<const void*>(gemm_bias_act_kernel<true, false>);
+  const cudaError_t ae = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMEM_BYTES));
+  if (ae != cudaSuccess)
+    return fail(TCAB_ERR_CUDA, "chain_contract: cannot reserve %zu bytes of shared memory: %s", SMEM_BYTES, cudaGetErrorString(ae));
+  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  uint64_t grid = static_cast<uint64_t>(sm_count());
+  if (grid > tiles) grid = tiles;
+  const float* bias = nullptr;
+  int act = TCAB_ACT_NONE;
+  void* args[] = {&ta, &tb, &tcm, &bias, &m, &n, &k, &act, &alpha};
+  const cudaError_t le = cudaLaunchKernel(fn, dim3(static_cast<unsigned>(grid)), dim3(THREADS), args, SMEM_BYTES, s);
+  count_launch();
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(TCAB_ERR_CUDA, "chain_contract (tensor cores): launch failed: %s", cudaGetErrorString(le));
+  }
+  return TCAB_OK;
 }
 
 }  // namespace tcab

@@ -245,6 +245,40 @@ def test_contraction_over_bf16_operands(cuda, m, k, n, nk):
     assert (np.abs(got - want) <= 1e-5 * mag + 1e-30).all()
 
 
+@pytest.mark.parametrize("m,k,n,nk", [(300, 264, 520, False), (300, 264, 516, True), (1, 8, 8, False), (129, 4096, 264, True),
+                                      (513, 72, 1032, False), (2048, 2048, 2048, False), (700, 1024, 260, True)])
+def test_bf16_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
+    # map = the plain product of two bf16 operands, sum reducer, init 0, stored as it is or scaled: the library takes
+    # the tcgen05 kernel with fp32 accumulation and an fp32 store (one launch). Products of bf16 values are exact in
+    # fp32, so only the order of the sum differs from the scalar kernel (tuning value gemm p2 = 64 keeps that one).
+    from oracle import binding as O
+    rng = np.random.default_rng(m + k + n)
+    a = O.f32_to_bf16(rng.uniform(-1, 1, (m, k)).astype(np.float32))
+    b = O.f32_to_bf16(rng.uniform(-1, 1, (n, k) if nk else (k, n)).astype(np.float32))
+    af, bf = O.bf16_to_f32(a).astype(np.float64), O.bf16_to_f32(b).astype(np.float64)
+    bm = bf.T if nk else bf
+    want, mag = af @ bm, np.abs(af) @ np.abs(bm)
+    for post, caps, scale in ((None, (), 1.0), ("p0 * c0", (0.125,), 0.125), ("0.5f * p0", (), 0.5)):
+        out = torch.full((m + 2, n), -7.0, device=cuda)             # canary rows around the output
+        n0 = T.launch_count()
+        T.chain_contract(to_dev(a, cuda), to_dev(b, cuda), "f32(p0) * f32(p1)", rhs_is_nk=nk, post_expr=post, captures=caps,
+                         out=out[1:m + 1])
+        assert T.launch_count() - n0 == 1
+        got = out.cpu().numpy()
+        assert (got[0] == -7.0).all() and (got[-1] == -7.0).all()
+        assert (np.abs(got[1:-1] - scale * want) <= 1e-5 * scale * mag + 1e-30).all()
+    try:    # the scalar kernel on the same operands: the same sums in another order
+        T.tune("gemm", 0, 0, 64)
+        ref = T.chain_contract(to_dev(a, cuda), to_dev(b, cuda), "f32(p0) * f32(p1)", rhs_is_nk=nk).cpu().numpy()
+    finally:
+        T.tune("gemm")
+    tc = T.chain_contract(to_dev(a, cuda), to_dev(b, cuda), "f32(p0) * f32(p1)", rhs_is_nk=nk).cpu().numpy()
+    assert (np.abs(tc - ref) <= 2e-5 * mag + 1e-30).all()
+    # anything else keeps the scalar kernel: another map, another reducer, rows that are not 16-byte multiples
+    got = T.chain_contract(to_dev(a, cuda), to_dev(b, cuda), "f32(p0) * f32(p1) + 1.0f", rhs_is_nk=nk).cpu().numpy()
+    assert (np.abs(got - (want + k)) <= 1e-5 * (mag + k) + 1e-30).all()
+
+
 # ----------------------------------------------------------------------------
 # operands that bind a subset of the iteration axes: one value per row, one row shared by all rows
 # ----------------------------------------------------------------------------
