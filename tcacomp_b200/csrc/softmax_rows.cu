@@ -616,13 +616,17 @@ int launch_cluster_stream_shape(const float* x, float* y, uint64_t rows, uint32_
 // and the shared-memory rows): 24576 columns 6.1 (5.5), 32768 5.8 (5.6), 49152 6.0 (5.1), 65536 5.5 (5.2), 98304
 // 5.7 (4.9), 131072 5.3 (4.4), 262144 5.1 (4.0), 524288 4.8 (3.2), 1048576 4.3 (2.0). tune("softmax", _, p1 =
 // CTAs per row, p2 = shape 1..5, p3 = 7) forces one.
-int launch_cluster_stream(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, cudaStream_t s) {
+int launch_cluster_stream(const float* x, float* y, uint64_t rows, uint32_t cols, uint32_t nvec, bool few_rows, cudaStream_t s) {
   const Tune& tn = tune(kSoftmax);
   uint32_t cs = 0;
   int shape = 0;
   if (tn.p3 == 7) {
     cs = tn.p1 >= 1 && tn.p1 <= 8 ? static_cast<uint32_t>(tn.p1) : 0u;
     shape = tn.p2;
+  }
+  if (shape <= 0 && few_rows) {  // few rows: large steps, four CTAs per row while a CTA then has at most four steps
+    shape = 5;
+    if (cs == 0) cs = nvec <= 65536u ? 4u : 8u;
   }
   if (shape <= 0) shape = nvec <= 8u * 1024u * 4u ? 1 : nvec <= 8u * 2048u * 4u ? 2 : 5;
   if (cs == 0) cs = stream_cluster_size(nvec, shape == 1 ? 1024u : shape == 5 ? 4096u : 2048u, true);
@@ -669,9 +673,13 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
   const Tune& tn = tune(kSoftmax);
   // Rows from 6144 vectors (24576 columns) up, enough of them to fill the GPU with small CTAs: streaming clusters
   // (any row length: the row ends that do not fill a vector are handled element by element).
+  // With fewer rows the register clusters keep rows of up to 65536 vectors unless there are at least 32 rows of at
+  // least 32768 vectors (64 x 262144: 4.1 against 2.4 TB/s; 16 x 1048576: 2.9 against 0.4 for the one-CTA kernel).
+  const bool many = rows * 2 >= static_cast<uint64_t>(sm_count());
+  const bool few_long = !many && (cols / 4 > 65536u || (rows >= 32 && cols / 4 >= 32768u));
   if (aligned16(x) && aligned16(y) && rows * 8 <= 0x7fffffffull && tn.p0 <= 0 &&
-      (tn.p3 == 7 || (tn.p3 <= 0 && cols / 4 >= 6144u && rows * 2 >= static_cast<uint64_t>(sm_count()))))
-    return launch_cluster_stream(x, y, rows, cols, cols / 4, s);
+      (tn.p3 == 7 || (tn.p3 <= 0 && cols / 4 >= 6144u && (many || few_long))))
+    return launch_cluster_stream(x, y, rows, cols, cols / 4, few_long, s);
   // rows that are not a multiple of four columns but still fit a CTA's registers as 16-byte vectors
   if (!vec && cols % 4 != 0 && cols >= 16 && aligned16(x) && aligned16(y) && tn.p0 <= 0 && tn.p3 != 6) {
     const uint32_t nv = cols / 4;  // aligned vectors inside a row, at most

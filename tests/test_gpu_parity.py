@@ -191,7 +191,7 @@ def test_softmax_rows(oracle, cuda, rows, cols):
 
 
 @pytest.mark.parametrize("rows,cols,cs,shape", [(80, 24576, 0, 0), (75, 49152, 0, 0), (74, 98308, 0, 0),   # the library's own choice
-                                                 (76, 50257, 0, 0), (77, 32003, 0, 0), (5, 4099, 2, 1), (6, 1001, 4, 1),
+                                                 (76, 50257, 0, 0), (77, 32003, 0, 0), (33, 131076, 0, 0), (2, 300004, 0, 0), (5, 4099, 2, 1), (6, 1001, 4, 1),
                                                  (3, 70001, 8, 3), (4, 14, 2, 1), (9, 9, 8, 1),
                                                  (3, 4096, 2, 1), (2, 12292, 3, 1), (5, 1028, 8, 1), (2, 65536, 4, 2),
                                                  (3, 40000, 5, 3), (1, 300000, 8, 4), (2, 262148, 8, 5), (1, 1048576, 8, 5),
@@ -356,6 +356,7 @@ def test_layernorm_cluster_kernel_forced(oracle, cuda, cols):
 
 
 @pytest.mark.parametrize("dtype,rows,cols,cs,shape", [("f32", 80, 24576, 0, 0), ("f32", 75, 45056, 0, 0), ("bf16", 74, 131072, 0, 0),
+                                                       ("f32", 3, 65540, 0, 0), ("bf16", 2, 262152, 0, 0),
                                                        ("f32", 3, 4096, 2, 1), ("f32", 2, 12292, 3, 4), ("f32", 5, 1028, 8, 1),
                                                        ("f32", 2, 65536, 4, 2), ("f32", 1, 300000, 8, 5), ("f32", 7, 20, 8, 1),
                                                        ("bf16", 3, 8192, 2, 1), ("bf16", 2, 65544, 5, 3), ("bf16", 1, 300008, 8, 5),
@@ -367,7 +368,7 @@ def test_layernorm_streaming_clusters(oracle, cuda, dtype, rows, cols, cs, shape
     rng = np.random.default_rng(rows + cols + cs)
     x = rng.normal(0.2, 1, (rows, cols)).astype(np.float32)
     x[0] += 7.0
-    x[0, 0] = 0.0
+    x[0, 0] = 4.0          # the shift K: three standard deviations below the row's mean
     g = rng.normal(1, 0.1, cols).astype(np.float32)
     b = rng.normal(0, 0.1, cols).astype(np.float32)
     n0 = T.launch_count()
