@@ -27,9 +27,10 @@ extern "C" {
  *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
  *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
  *       split path, p2 = 2 launches without programmatic dependent launch, 3 no 1024-thread CTAs for small problems, p3 = CTAs sharing the k axis of a
- *       middle-axis reduction.
+ *       middle-axis reduction (any value, 1 included, also keeps the kernel with a CTA per column tile where the
+ *       library would take a warp per tile).
  *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
- *       p3 = CTAs sharing the k axis.
+ *       p3 = CTAs sharing the k axis (any of p0, p1, p3 keeps the kernel with a CTA per column tile).
  *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
  *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs, 5 one
  *       cluster per 128 x 256 tile with a K range per CTA, whatever the shape),

@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kSlots
 };
 
 struct JitChain {
@@ -163,6 +163,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
     names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
     names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + ">";
+    names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     }
   } else if (sp.kind == 'B') {
     const char* shapes[4] = {"32, 4", "256, 4", "32, 1", "256, 1"};
@@ -323,6 +324,16 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   uint32_t tiles_per_b = (nc + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
+  // narrow rows and short reduced axes: a warp per (b, column tile) (same policy as the ahead-of-time path)
+  if (vec && !jc->cells && jc->k[kOuterFlat] != nullptr && tune(kReduceInner).p3 <= 0) {
+    const uint32_t g = outer_flat_groups(nb, nk, nc, sm_count());
+    if (g != 0) {
+      uint32_t tpb = (nc + 127) / 128;
+      const uint64_t work = static_cast<uint64_t>(nb) * tpb;
+      void* af[] = {ptrs, &out, &nb, &nk, &nc, &tpb, const_cast<uint32_t*>(&g), &init, &caps};
+      return launch(jc->k[kOuterFlat], (work + 7) / 8, 256, af, s, "chain_outer_flat");
+    }
+  }
   // few column tiles and a long k: the k axis is split over CTAs too (same policy as the ahead-of-time path)
   const cudaKernel_t kern = jc->k[vec ? kOuterV4 : kOuterV1];
   const int occ = occupancy(reinterpret_cast<const void*>(kern), 256, 0);

@@ -457,6 +457,69 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
   }
 }
 
+// Reduce over a MIDDLE axis with a WARP per (b, column tile), for the shapes on which chain_outer idles: narrow
+// rows (nc = 4, 8, ... 64: most lanes of a 128-column tile would have no column) and short reduced axes (a CTA per
+// tile would do a few hundred bytes of work between two barriers). The warp's 32 lanes cover g = tile columns / 4
+// column groups of four and 32 / g consecutive k rows per step; when the tile is the whole row (nc = 4 g < 128) the
+// 32 vectors of a step are contiguous in memory. Every lane folds the k rows it sees (ascending), lanes with the
+// same column group then meet by shuffles, and lanes 0..g-1 store. No shared memory, no barrier; eight independent
+// warps per CTA. 16-byte vectors only (nc % 4 == 0, aligned operands).
+template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0>
+__global__ void __launch_bounds__(256)
+chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, u32 g, float init,
+                 Caps caps) {
+  typedef Comb<COMBINE> C;
+  const u32 lane = threadIdx.x & 31;
+  const u64 work = static_cast<u64>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (work >= static_cast<u64>(nb) * tiles_per_b) return;  // the whole warp leaves
+  const u32 b = static_cast<u32>(work / tiles_per_b), tile = static_cast<u32>(work % tiles_per_b);
+  const u32 rows_per_step = 32 / g;
+  const u32 cg = lane % g, kr = lane / g;  // this lane's column group, and its row inside a step
+  const u32 col = tile * 128 + cg * 4;     // g < 32 only when one tile is the whole row
+  const bool colok = col < nc;
+  const u64 rowvecs = nc / 4;
+  const u64 base = static_cast<u64>(b) * nk * rowvecs + col / 4;
+
+  float acc[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) acc[j] = C::identity();
+  if (colok) {
+    for (u32 k0 = kr; k0 < nk; k0 += rows_per_step * UNROLL) {
+      float f[UNROLL][NIN][4];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const u32 k = k0 + u * rows_per_step;
+        if (k < nk) LoadAll<4, BF, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, f[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const u32 k = k0 + u * rows_per_step;
+        if (k < nk) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float p[NIN];
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
+            acc[j] = C::apply(acc[j], Map::apply(p, caps.c));
+          }
+        }
+      }
+    }
+  }
+  for (u32 off = 16; off >= g; off >>= 1) {  // lanes that differ in the row bits hold the same column group
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = C::apply(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+  }
+  if (lane < g && colok) {
+    const u64 cell = static_cast<u64>(b) * nc + col;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float r[1] = {C::apply(init, acc[j])};
+      out[cell + j] = Post::apply(r, caps.c + 8);
+    }
+  }
+}
+
 // Contraction of two fp32 operands indexed by different dim subsets (the reference's matmul-shaped
 // chains: testing/kernels/llm/gemm.tca, tiling/mm_*.tca, fusion/mlp.tca, llm/qk_score.tca):
 //   out[m,n] = post( fold_k map(lhs[m,k], rhs[k,n]) )         RHS_NK == 0, rhs is [K,N]

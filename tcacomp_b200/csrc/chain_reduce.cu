@@ -146,6 +146,22 @@ int launch_inner(const Args& a) {
   return TCAB_OK;
 }
 
+template <class Map, class Post, int COMBINE>
+int launch_outer_flat(const Args& a, uint32_t g) {
+  constexpr int NIN = Map::kIn;
+  auto* fn = tcabk::chain_outer_flat<Map, Post, COMBINE, NIN, 4>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  const uint32_t nc = static_cast<uint32_t>(a.inner);
+  const uint32_t tiles_per_b = (nc + 127) / 128;
+  const uint64_t work = a.outer * tiles_per_b;
+  if (work > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
+  fn<<<static_cast<unsigned>((work + 7) / 8), 256, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,
+                                                                  tiles_per_b, g, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_outer_flat");
+}
+
 template <class Map, class Post, int COMBINE, int V>
 int launch_outer(const Args& a) {
   constexpr int NIN = Map::kIn;
@@ -254,6 +270,12 @@ int launch_chain(const Args& a) {
   }
   if (a.inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
   const bool vec = al && (a.inner % 4 == 0);
+  // narrow rows and short reduced axes: a warp per (b, column tile) (outer_flat_groups has the rule and the
+  // measurements). tune("reduce_inner", _, _, _, p3 = 1) keeps chain_outer.
+  if (vec && tune(kReduceInner).p3 <= 0) {
+    const uint32_t g = outer_flat_groups(a.outer, a.nk, static_cast<uint32_t>(a.inner), sm_count());
+    if (g != 0) return launch_outer_flat<Map, Post, COMBINE>(a, g);
+  }
   return vec ? launch_outer<Map, Post, COMBINE, 4>(a) : launch_outer<Map, Post, COMBINE, 1>(a);
 }
 

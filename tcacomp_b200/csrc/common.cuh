@@ -119,6 +119,27 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
 int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int b_is_nk, float alpha, float* c, uint32_t m,
                             uint32_t n, uint32_t k, cudaStream_t s);  // tensor cores, fp32 out (gemm_bias_act.cu)
 
+// chain_outer_flat (a warp per (b, column tile)) instead of chain_outer (a CTA per tile) for a middle-axis
+// reduction over [nb, nk, nc] with 16-byte vectors: rows of at most 32 columns, rows of 64 columns when there are
+// many of them, or a reduced axis shorter than 64 with rows of 4 * 2^i <= 64 or of at least 128 columns. Returns
+// the column groups per tile (1..32), or 0 for a CTA per tile. Measured (fp32 sum over 2^28 elements, TB/s, a CTA
+// per tile -> a warp per tile): [262144, 256, 4] 0.58 -> 7.1, [131072, 256, 8] 1.2 -> 6.9, [65536, 256, 16] 2.3 ->
+// 6.9, [32768, 256, 32] 4.4 -> 6.9, [65536, 4, 1024] 1.6 -> 5.5, [131072, 8, 256] 2.6 -> 5.9, [262144, 16, 64]
+// 2.6 -> 6.4; the fused sum / max / argmax kernel 0.36 -> 5.6, 0.73 -> 6.3, 1.4 -> 6.6, 2.7 -> 6.6 on the first four.
+inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm) {
+  if (nc == 0 || nc % 4 != 0 || nk == 0) return 0;
+  const uint32_t g = nc >= 128 ? 32u : nc / 4;
+  if (nc < 128 && (g & (g - 1)) != 0) return 0;       // 4, 8, 16, 32, 64 columns: the whole row is one tile
+  if (nc > 64 && nc < 128) return 0;
+  const uint64_t work = nb * ((nc + 127) / 128);  // warps
+  if (work < 4ull * static_cast<uint64_t>(sm) && nk > 4096) return 0;  // few long columns: chain_outer cuts k over CTAs
+  if (nc <= 32) return g;
+  // 64 columns use half the lanes of a CTA's tile: the warps win only when there are enough of them to keep an
+  // SM's memory pipeline full (measured [1024, 4096, 64]: 6.6 TB/s with a CTA per tile, 3.4 with 1024 warps)
+  if (nc == 64 && work >= 32ull * static_cast<uint64_t>(sm)) return g;
+  return nk < 64 ? g : 0;
+}
+
 int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
 int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,
                                 uint32_t rows, uint32_t nk, cudaStream_t s);  // ins: [nprob][n_in]

@@ -153,6 +153,82 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
   }
 }
 
+// The same reduction with a WARP per (b, column tile), for narrow rows (nc = 4 ... 64: most lanes of a 128-column
+// tile would own no column) and short reduced axes (a CTA per tile would do a few hundred bytes of work between two
+// barriers). The 32 lanes cover g column groups of four and 32 / g consecutive k rows per step (contiguous in memory
+// when the tile is the whole row); a lane folds the rows it sees in ascending order, lanes with the same column
+// group then meet by shuffles under the same rule -- greater value, or equal value and lower index -- and lanes
+// 0..g-1 store. No shared memory, no barrier.
+template <int UNROLL>
+__global__ void __launch_bounds__(256)
+reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* __restrict__ mx, int32_t* __restrict__ amax,
+                  uint32_t nb, uint32_t nk, uint32_t nc, uint32_t tiles_per_b, uint32_t g) {
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t work = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (work >= static_cast<uint64_t>(nb) * tiles_per_b) return;  // the whole warp leaves
+  const uint32_t b = static_cast<uint32_t>(work / tiles_per_b), tile = static_cast<uint32_t>(work % tiles_per_b);
+  const uint32_t rows_per_step = 32 / g;
+  const uint32_t cg = lane % g, kr = lane / g;
+  const uint32_t col = tile * 128 + cg * 4;  // g < 32 only when one tile is the whole row
+  const bool colok = col < nc;
+  const float* base = t + static_cast<size_t>(b) * nk * nc + col;
+
+  float acc[4], best[4];
+  int32_t bidx[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    acc[j] = 0.0f;
+    best[j] = -INFINITY;
+    bidx[j] = 0;
+  }
+  if (colok) {
+    for (uint32_t k0 = kr; k0 < nk; k0 += rows_per_step * UNROLL) {
+      float f[UNROLL][4];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const uint32_t k = k0 + u * rows_per_step;
+        if (k < nk) ColVec<4>::load(base + static_cast<size_t>(k) * nc, f[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const uint32_t k = k0 + u * rows_per_step;
+        if (k < nk) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float v = f[u][j];
+            acc[j] += v;
+            if (v > best[j]) {  // strict: the lowest index among equals survives
+              best[j] = v;
+              bidx[j] = static_cast<int32_t>(k);
+            }
+          }
+        }
+      }
+    }
+  }
+  for (uint32_t off = 16; off >= g; off >>= 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+      const float v = __shfl_xor_sync(0xffffffffu, best[j], off);
+      const int32_t vi = __shfl_xor_sync(0xffffffffu, bidx[j], off);
+      if (v > best[j] || (v == best[j] && vi < bidx[j])) {  // a lane that saw no row holds (-inf, 0): the initial state
+        best[j] = v;
+        bidx[j] = vi;
+      }
+    }
+  }
+  if (lane < g && colok) {
+    const size_t o = static_cast<size_t>(b) * nc + col;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (sum) sum[o + j] = acc[j];
+      if (mx) mx[o + j] = best[j];
+      if (amax) amax[o + j] = bidx[j];
+    }
+  }
+}
+
 // Folds the partial states of the k ranges, ascending: the same rule as the cross-warp combine above, so
 // the lowest index among equal maxima survives whichever range it came from.
 __global__ void __launch_bounds__(256)
@@ -250,6 +326,16 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
   // p0: vectors per lane (1|2), p1: warps splitting k (4|8|16), p2: CTAs per SM, p3: CTAs splitting k (forced).
   const int cv = tn.p0 > 0 ? tn.p0 : 1;
   const int kw = tn.p1 > 0 ? tn.p1 : 8;
+  if (vec && tn.p0 <= 0 && tn.p1 <= 0 && tn.p3 <= 0) {  // narrow rows, short reduced axes: a warp per (b, column tile)
+    const uint32_t g = outer_flat_groups(nb, nk, nc, sm_count());
+    if (g != 0) {
+      const uint32_t tiles_per_b = (nc + 127) / 128;
+      const uint64_t work = static_cast<uint64_t>(nb) * tiles_per_b;
+      reduce_outer_flat<4><<<static_cast<unsigned>((work + 7) / 8), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g);
+      count_launch();
+      return check_launch("reduce_outer_flat");
+    }
+  }
   if (vec) {
     if (cv == 1 && kw == 8) return launch<4, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
     if (cv == 2 && kw == 8) return launch<4, 2, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);

@@ -1066,6 +1066,61 @@ def test_contraction_tile_sizes(oracle, cuda, tile):
 
 
 # ----------------------------------------------------------------------------
+# middle-axis chains on narrow rows and short reduced axes: a warp per (b, column tile)
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("nb,nk,nc", [(3000, 256, 4), (2500, 300, 8), (1300, 77, 16), (700, 1000, 32), (4000, 4, 1024),
+                                      (2000, 8, 256), (900, 33, 64), (5000, 1, 4), (1200, 63, 132), (600, 5, 2052),
+                                      (1, 7, 8), (3, 2, 4)])
+def test_middle_axis_chains_warp_per_tile(oracle, cuda, nb, nk, nc):
+    rng = np.random.default_rng(nb + nk + nc)
+    x = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
+    z = rng.uniform(0, 1, (nb, nk, nc)).astype(np.float32)
+    xd, zd = dev_f32(x, cuda), dev_f32(z, cuda)
+    x64 = x.astype(np.float64)
+    # a table lambda (compiled ahead of time) with a sum; the kernel that a CTA per tile runs gives the same sums
+    buf, out = guarded((nb, nc), torch.float32, cuda)
+    n0 = T.launch_count()
+    T.chain_reduce([xd], "p0", axis=1, out=out)
+    assert T.launch_count() - n0 == 1
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    mag = np.abs(x64).sum(1)
+    assert (np.abs(got - x64.sum(1)) <= 1e-5 * mag + 1e-30).all()
+    try:
+        T.tune("reduce_inner", 0, 0, 0, 1)
+        old = T.chain_reduce([xd], "p0", axis=1).cpu().numpy()
+    finally:
+        T.tune("reduce_inner")
+    assert (np.abs(got - old) <= 2e-5 * mag + 1e-30).all()
+    # max: order-independent, bit-exact; with init and a piped map
+    got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=-0.5, axis=1, post_expr="p0 * 2.0f").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x.max(1), np.float32(-0.5)) * np.float32(2))
+    # a run-time compiled lambda over two operands, one of them bf16 (the suite's softmax core: sum_k exp(x) * z)
+    zb = oracle.f32_to_bf16(z)
+    got = T.chain_reduce([xd, dev_bf16(zb, cuda)], "expf(p0) * f32(p1)", axis=1).cpu().numpy()
+    want = (np.exp(x64) * oracle.bf16_to_f32(zb)).sum(1)
+    assert (np.abs(got - want) <= 1e-5 * want + 1e-30).all()
+    got = T.chain_reduce([xd, zd], "p0 * p1 + 0.25f", init=1.0, axis=1).cpu().numpy()
+    want = (x64 * z + 0.25).sum(1) + 1.0
+    assert (np.abs(got - want) <= 1e-5 * (np.abs(x64 * z) + 0.25).sum(1) + 1e-5).all()
+    # sum, max and argmax in one pass: max and argmax bit-exact (ties on purpose: the lowest index wins), as with a
+    # CTA per tile
+    xt = np.round(x * 4).astype(np.float32) / 4
+    got = T.reduce_outer(dev_f32(xt, cuda))
+    assert np.array_equal(got["max"].cpu().numpy(), xt.max(1))
+    assert np.array_equal(got["argmax"].cpu().numpy(), xt.argmax(1).astype(np.int32))
+    assert (np.abs(got["sum"].cpu().numpy() - xt.astype(np.float64).sum(1)) <= 1e-5 * np.abs(xt).sum(1) + 1e-30).all()
+    try:
+        T.tune("reduce_outer", 0, 0, 0, 1)
+        old = T.reduce_outer(dev_f32(xt, cuda))
+    finally:
+        T.tune("reduce_outer")
+    assert torch.equal(old["max"], got["max"]) and torch.equal(old["argmax"], got["argmax"])
+    only = T.reduce_outer(dev_f32(xt, cuda), want=("argmax",))
+    assert torch.equal(only["argmax"], got["argmax"])
+
+
+# ----------------------------------------------------------------------------
 # several problems of one shape in one launch
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nprob,rows,cols", [(16, 4096, 1024), (1, 5, 7), (3, 33, 130), (32, 17, 64), (2, 3, 9000), (5, 2, 4096)])
