@@ -289,6 +289,52 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   }
 }
 
+// Reduce over the INNERMOST axis of SHORT rows (at most 32 vectors of four): g = 1, 2, 4 ... 32 lanes per row
+// (the power of two that covers the row), one 16-byte vector per lane, 32 / g rows per warp and step, UNROLL steps
+// in flight. The lanes of a warp read consecutive vectors of consecutive rows, a lane folds the four values of its
+// vector, the g lanes of a row meet by xor shuffles, and the first lane of a row stores. chain_inner gives a whole
+// row to one thread (up to 16 vectors: every load instruction of a warp touches 32 different rows) or to four, or
+// a warp to a row of 17 ... 32 vectors and lets the CTA end after four rows; both cost more than the bytes.
+template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0>
+__global__ void __launch_bounds__(256)
+chain_inner_flat(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nvec, u32 g, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  const u32 lane = threadIdx.x & 31;
+  const u32 rows_per_step = 32 / g;
+  const u32 i = lane % g, r = lane / g;  // this lane's vector inside its row, and its row inside a step
+  const u64 warp_id = static_cast<u64>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const u64 row0 = warp_id * (rows_per_step * UNROLL) + r;
+  if (warp_id * (rows_per_step * UNROLL) >= rows) return;  // the whole warp leaves
+
+  float f[UNROLL][NIN][4];
+  bool live[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const u64 row = row0 + static_cast<u64>(u) * rows_per_step;
+    live[u] = row < rows && i < nvec;
+    if (live[u]) LoadAll<4, BF, NIN>::at(ins.p, row * nvec + i, f[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    float acc = C::identity();
+    if (live[u]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float p[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
+        acc = C::apply(acc, Map::apply(p, caps.c));
+      }
+    }
+    for (u32 off = g >> 1; off > 0; off >>= 1) acc = C::apply(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+    const u64 row = row0 + static_cast<u64>(u) * rows_per_step;
+    if (i == 0 && row < rows) {
+      float res[1] = {C::apply(init, acc)};
+      out[row] = Post::apply(res, caps.c + 8);
+    }
+  }
+}
+
 // Several problems of ONE shape in one launch: problem b has operands ins.in[b][*] of [rows, nk] and output
 // ins.out[b] of [rows]. A lone small reduction is bounded by what a launch costs and by the wait for its
 // predecessor on the stream, not by memory (a [4096, 1024] fp32 input is 2.6 us of HBM time; a dependent launch

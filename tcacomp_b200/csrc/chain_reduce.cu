@@ -146,6 +146,24 @@ int launch_inner(const Args& a) {
   return TCAB_OK;
 }
 
+// Short rows (at most 32 vectors): g lanes per row, see chain_inner_flat.
+template <class Map, class Post, int COMBINE>
+int launch_inner_flat(const Args& a, uint32_t nvec) {
+  constexpr int NIN = Map::kIn;
+  constexpr int UNROLL = 4;
+  auto* fn = tcabk::chain_inner_flat<Map, Post, COMBINE, NIN, UNROLL>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  uint32_t g = 1;
+  while (g < nvec) g <<= 1;
+  const uint64_t rows_per_cta = static_cast<uint64_t>(8) * UNROLL * (32 / g);
+  const uint64_t grid = (a.outer + rows_per_cta - 1) / rows_per_cta;
+  if (grid > 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many rows");
+  fn<<<static_cast<unsigned>(grid), 256, 0, a.stream>>>(ptrs, a.out, a.outer, nvec, g, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_inner_flat");
+}
+
 template <class Map, class Post, int COMBINE>
 int launch_outer_flat(const Args& a, uint32_t g) {
   constexpr int NIN = Map::kIn;
@@ -246,6 +264,9 @@ int launch_chain(const Args& a) {
         return vec ? launch_split<Map, Post, COMBINE, 4>(a, scratch, nvec, splits)
                    : launch_split<Map, Post, COMBINE, 1>(a, scratch, nvec, splits);
     }
+    // short rows with enough of them: lanes along the row, consecutive rows in a warp (tune p0 keeps chain_inner)
+    if (vec && nvec >= 1 && nvec <= 32 && a.outer >= 1024 && tune(kReduceInner).p0 <= 0)
+      return launch_inner_flat<Map, Post, COMBINE>(a, nvec);
     // short rows: one thread folds a row sequentially, which is the reference's SeqReducer order exactly
     // measured: a warp per row up to 1023 vectors, a CTA per row from 1024 (8192 columns: 4.6 -> 7.1 TB/s)
     int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec < 1024 ? 32 : 256;

@@ -657,7 +657,7 @@ int launch_reg(const T* x, const T* gamma, const T* beta, float eps, T* y, uint6
 }
 
 #define TCAB_LN_SHAPES_BASE(X) \
-  X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
+  X(1, 1) X(2, 1) X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
   X(1024, 8) X(1024, 16)
 #define TCAB_LN_SHAPES_EXTRA(X) \
   X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(1024, 1) X(256, 8) X(512, 8) X(64, 8) X(128, 2) X(256, 2)
@@ -693,7 +693,7 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
     }
   }
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt);
+  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt, /*small=*/true);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;

@@ -147,9 +147,17 @@ inline bool choose_row_shape(uint32_t nvec, int vpt_target, int* tpr, int* vpt) 
 // (1024, 8..32) and, for 16-byte vectors, (128, 8), (256, 8), (64, 16), (32, 32) [plus (512, 8) and (64, 8)
 // where `wide8`] -- this picks the least waste, preferring fewer slots and 128..512 threads on a tie, and
 // staying at 32 row values per thread unless that wastes more than a third.
-inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values_per_vector, int* tpr, int* vpt) {
+inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values_per_vector, int* tpr, int* vpt,
+                                 bool small = false) {
   if (nvec == 0) nvec = 1;
   struct Shape { int t, v; bool vec_only, wide_only; };
+  // rows of one to four vectors: one, two or four threads per row (`small`: the aligned register kernels have
+  // these shapes; with eight threads per row a 4-column softmax ran at 0.95 TB/s, seven of eight threads idle)
+  if (small && nvec <= 4) {
+    *tpr = nvec <= 1 ? 1 : nvec <= 2 ? 2 : 4;
+    *vpt = 1;
+    return true;
+  }
   static const Shape kShapes[] = {
       {8, 1, false, false},   {8, 2, false, false},    {8, 4, false, false},    {16, 4, false, false},
       {32, 4, false, false},  {64, 4, false, false},   {128, 4, false, false},  {256, 4, false, false},

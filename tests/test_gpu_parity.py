@@ -1066,6 +1066,58 @@ def test_contraction_tile_sizes(oracle, cuda, tile):
 
 
 # ----------------------------------------------------------------------------
+# innermost-axis chains and row kernels on short rows (1 to 32 vectors)
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(5000, 4), (3001, 8), (2049, 12), (1500, 16), (1024, 20), (4000, 32), (1111, 36),
+                                       (2000, 64), (1300, 100), (1025, 128), (1024, 124)])
+def test_short_rows(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    z = rng.uniform(0, 1, (rows, cols)).astype(np.float32)
+    xd, zd = dev_f32(x, cuda), dev_f32(z, cuda)
+    x64 = x.astype(np.float64)
+    # the benchmark's chain (a table lambda), every row against the oracle and fp64
+    buf, out = guarded((rows,), torch.float32, cuda)
+    T.chain_reduce([xd], "(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f)", axis=1, out=out)
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    from oracle import checks
+    assert checks.rowsum_close(got, x)
+    try:        # the kernels that give a row to one thread, to four or to a warp: the same sums in another order
+        T.tune("reduce_inner", 32)
+        old = T.chain_reduce([xd], "(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f)", axis=1).cpu().numpy()
+    finally:
+        T.tune("reduce_inner")
+    assert (np.abs(got - old) <= 2e-5 * np.abs(old) + 1e-30).all()
+    # max with init and a piped map: bit-exact
+    got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.25, axis=1, post_expr="p0 + 1.0f").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x.max(1), np.float32(0.25)) + np.float32(1))
+    # run-time compiled, two operands, one of them bf16
+    zb = oracle.f32_to_bf16(z)
+    got = T.chain_reduce([xd, dev_bf16(zb, cuda)], "expf(p0) * f32(p1)", axis=1).cpu().numpy()
+    want = (np.exp(x64) * oracle.bf16_to_f32(zb)).sum(1)
+    assert (np.abs(got - want) <= 1e-5 * want + 1e-30).all()
+    # softmax and layer-norm of the same rows (one, two or four threads per row up to four vectors)
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    T.softmax_rows(dev_f32(4 * x, cuda), out=out)
+    check_guards(buf, torch.float32)
+    assert_softmax_close(out.cpu().numpy(), oracle.softmax_rows(4 * x), 4 * x)
+    g = rng.normal(1, 0.1, cols).astype(np.float32)
+    b = rng.normal(0, 0.1, cols).astype(np.float32)
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    T.layernorm_rows(xd, dev_f32(g, cuda), dev_f32(b, cuda), 1e-5, out=out)
+    check_guards(buf, torch.float32)
+    y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+    assert np.abs(out.cpu().numpy() - y64).max() <= 1e-5 * np.abs(y64).max()
+    if cols % 8 == 0:
+        xb, gb, bb = oracle.f32_to_bf16(x), oracle.f32_to_bf16(g), oracle.f32_to_bf16(b)
+        buf, outb = guarded((rows, cols), torch.bfloat16, cuda)
+        T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5, out=outb)
+        check_guards(buf, torch.bfloat16)
+        assert_layernorm_bf16_close(oracle, host_bits(outb), oracle.layernorm_rows_bf16(xb, gb, bb, 1e-5), xb, gb, bb)
+
+
+# ----------------------------------------------------------------------------
 # middle-axis chains on narrow rows and short reduced axes: a warp per (b, column tile)
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nb,nk,nc", [(3000, 256, 4), (2500, 300, 8), (1300, 77, 16), (700, 1000, 32), (4000, 4, 1024),
