@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kInnerFlat, kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
 };
 
 struct JitChain {
@@ -165,6 +165,8 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 4, " + bf + ">";
     names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
+    names[kInnerFlat2] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ", 2>";
+    names[kInnerRows32] = "tcabk::chain_inner_rows32<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
     }
   } else if (sp.kind == 'B') {
     const char* shapes[4] = {"32, 4", "256, 4", "32, 1", "256, 1"};
@@ -232,10 +234,10 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
   return TCAB_OK;
 }
 
-int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStream_t s, const char* what) {
+int launch(cudaKernel_t k, uint64_t grid, unsigned block, void** args, cudaStream_t s, const char* what, size_t smem = 0) {
   if (grid > 0x7fffffffull) grid = 0x7fffffffull;
   const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k), dim3(static_cast<unsigned>(grid)),
-                                         dim3(block), args, 0, s);
+                                         dim3(block), args, smem, s);
   count_launch();
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -308,12 +310,22 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
       void* a2[] = {&split_scratch_or_null, &out, &rows32, &sp, &init, &caps};
       return launch(jc->k[kFinish], (rows + 127) / 128, 128, a2, s, "chain_split_finish");
     }
-    if (vec && nvec >= 1 && nvec <= 32 && outer >= 1024 && jc->k[kInnerFlat] != nullptr && tune(kReduceInner).p0 <= 0) {
+    if (vec && nvec >= 2 && nvec <= 16 && outer >= 1024 && jc->k[kInnerRows32] != nullptr && tune(kReduceInner).p0 <= 0 &&
+        rows32_warps(nvec, jc->n_in) >= 2) {  // a thread per row over a coalesced copy (same policy as ahead of time)
+      const uint32_t warps = rows32_warps(nvec, jc->n_in);
+      uint32_t nv = nvec;
+      void* af[] = {ptrs, &out, &outer, &nv, &init, &caps};
+      return launch(jc->k[kInnerRows32], (outer + warps * 32ull - 1) / (warps * 32ull), 32 * warps, af, s, "chain_inner_rows32",
+                    static_cast<size_t>(warps) * jc->n_in * 32 * (nvec + 1) * 16);
+    }
+    if (vec && nvec >= 1 && (nvec <= 32 || (nvec > 48 && nvec <= 64)) && outer >= 1024 && jc->k[kInnerFlat] != nullptr &&
+        tune(kReduceInner).p0 <= 0) {
       uint32_t g = 1, nv = nvec;  // short rows: lanes along the row (same policy as the ahead-of-time path)
-      while (g < nvec) g <<= 1;
+      while (g < nvec && g < 32) g <<= 1;
       const uint64_t rows_per_cta = static_cast<uint64_t>(8) * 4 * (32 / g);
       void* af[] = {ptrs, &out, &outer, &nv, &g, &init, &caps};
-      return launch(jc->k[kInnerFlat], (outer + rows_per_cta - 1) / rows_per_cta, 256, af, s, "chain_inner_flat");
+      return launch(jc->k[nvec <= 32 ? kInnerFlat : kInnerFlat2], (outer + rows_per_cta - 1) / rows_per_cta,
+                    256, af, s, "chain_inner_flat");
     }
     const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec < 1024 ? 2 : 3;  // the same thresholds as the ahead-of-time path
     const int tpr = t == 0 ? 1 : t == 1 ? 4 : t == 2 ? 32 : 256;

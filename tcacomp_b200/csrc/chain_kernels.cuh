@@ -289,15 +289,16 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   }
 }
 
-// Reduce over the INNERMOST axis of SHORT rows (at most 32 vectors of four): g = 1, 2, 4 ... 32 lanes per row
+// Reduce over the INNERMOST axis of SHORT rows (at most 128 vectors of four): g = 1, 2, 4 ... 32 lanes per row
 // (the power of two that covers the row), one 16-byte vector per lane, 32 / g rows per warp and step, UNROLL steps
 // in flight. The lanes of a warp read consecutive vectors of consecutive rows, a lane folds the four values of its
 // vector, the g lanes of a row meet by xor shuffles, and the first lane of a row stores. chain_inner gives a whole
 // row to one thread (up to 16 vectors: every load instruction of a warp touches 32 different rows) or to four, or
 // a warp to a row of 17 ... 32 vectors and lets the CTA end after four rows; both cost more than the bytes.
-template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0>
+template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0, int VPL = 1>
 __global__ void __launch_bounds__(256)
 chain_inner_flat(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nvec, u32 g, float init, Caps caps) {
+  // VPL > 1: rows of up to 32 * VPL vectors, a warp per row (g == 32), VPL vectors per lane
   typedef Comb<COMBINE> C;
   const u32 lane = threadIdx.x & 31;
   const u32 rows_per_step = 32 / g;
@@ -306,32 +307,100 @@ chain_inner_flat(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nvec, u32
   const u64 row0 = warp_id * (rows_per_step * UNROLL) + r;
   if (warp_id * (rows_per_step * UNROLL) >= rows) return;  // the whole warp leaves
 
-  float f[UNROLL][NIN][4];
-  bool live[UNROLL];
+  float f[UNROLL][VPL][NIN][4];
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
     const u64 row = row0 + static_cast<u64>(u) * rows_per_step;
-    live[u] = row < rows && i < nvec;
-    if (live[u]) LoadAll<4, BF, NIN>::at(ins.p, row * nvec + i, f[u]);
+#pragma unroll
+    for (int v = 0; v < VPL; ++v)
+      if (row < rows && i + v * 32 < nvec) LoadAll<4, BF, NIN>::at(ins.p, row * nvec + i + v * 32, f[u][v]);
   }
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
+    const u64 row = row0 + static_cast<u64>(u) * rows_per_step;
     float acc = C::identity();
-    if (live[u]) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float p[NIN];
+    for (int v = 0; v < VPL; ++v) {
+      if (row < rows && i + v * 32 < nvec) {
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
-        acc = C::apply(acc, Map::apply(p, caps.c));
+        for (int j = 0; j < 4; ++j) {
+          float p[NIN];
+#pragma unroll
+          for (int a = 0; a < NIN; ++a) p[a] = f[u][v][a][j];
+          acc = C::apply(acc, Map::apply(p, caps.c));
+        }
       }
     }
     for (u32 off = g >> 1; off > 0; off >>= 1) acc = C::apply(acc, __shfl_xor_sync(0xffffffffu, acc, off));
-    const u64 row = row0 + static_cast<u64>(u) * rows_per_step;
     if (i == 0 && row < rows) {
       float res[1] = {C::apply(init, acc)};
       out[row] = Post::apply(res, caps.c + 8);
     }
+  }
+}
+
+// Reduce over the INNERMOST axis of rows of at most 16 vectors with ONE THREAD PER ROW folding it in ascending
+// order -- the order of the reference's SeqReducer (runtime/tca/reducer.h:45-51), which the reference's own suite
+// tolerances (1e-5 absolute on sums of magnitude 32) in effect demand -- but with coalesced loads: a warp owns 32
+// consecutive rows, which are one contiguous piece of memory; its lanes copy that piece vector by vector into
+// shared memory (cp.async, 16 bytes per fp32 vector, 8 per bf16 vector, rows padded by one slot so that the 32
+// lanes later read 32 different banks groups), and lane r then folds row r from there. chain_inner with a thread
+// per row reads the same bytes with every load instruction touching 32 different rows.
+// Dynamic shared memory: warps * NIN * 32 * (nvec + 1) * 16 bytes; blockDim.x = 32 * warps.
+template <class Map, class Post, int COMBINE, int NIN, int BF = 0>
+__global__ void __launch_bounds__(256)
+chain_inner_rows32(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nvec, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  extern __shared__ __align__(16) unsigned char rows32_smem[];
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const u64 row_base = (static_cast<u64>(blockIdx.x) * warps + warp) * 32;
+  if (row_base >= rows) return;  // the whole warp leaves
+  const u32 nrows = rows - row_base < 32 ? static_cast<u32>(rows - row_base) : 32u;
+  const u32 pitch = nvec + 1;
+  unsigned char* area = rows32_smem + static_cast<size_t>(warp) * NIN * 32 * pitch * 16;
+  const u32 total = nrows * nvec;
+  for (u32 v = lane; v < total; v += 32) {
+    const u32 r = v / nvec, j = v - r * nvec;
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(area + (static_cast<size_t>(a * 32 + r) * pitch + j) * 16));
+      if ((BF >> a) & 1) {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(ins.p[a]) + (row_base * nvec + v) * 8;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+      } else {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(ins.p[a]) + (row_base * nvec + v) * 16;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncwarp();
+  if (lane < nrows) {
+    float acc = C::identity();
+    for (u32 j = 0; j < nvec; ++j) {
+      float f[NIN][4];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        const unsigned char* slot = area + (static_cast<size_t>(a * 32 + lane) * pitch + j) * 16;
+        if ((BF >> a) & 1) {
+          const uint2 q = *reinterpret_cast<const uint2*>(slot);
+          f[a][0] = bf16_bits_to_float(q.x & 0xffffu); f[a][1] = bf16_bits_to_float(q.x >> 16);
+          f[a][2] = bf16_bits_to_float(q.y & 0xffffu); f[a][3] = bf16_bits_to_float(q.y >> 16);
+        } else {
+          const float4 q = *reinterpret_cast<const float4*>(slot);
+          f[a][0] = q.x; f[a][1] = q.y; f[a][2] = q.z; f[a][3] = q.w;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float p[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) p[a] = f[a][e];
+        acc = C::apply(acc, Map::apply(p, caps.c));
+      }
+    }
+    float res[1] = {C::apply(init, acc)};
+    out[row_base + lane] = Post::apply(res, caps.c + 8);
   }
 }
 

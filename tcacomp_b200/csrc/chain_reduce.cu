@@ -146,22 +146,43 @@ int launch_inner(const Args& a) {
   return TCAB_OK;
 }
 
-// Short rows (at most 32 vectors): g lanes per row, see chain_inner_flat.
+// Rows of at most 16 vectors, a thread per row over a coalesced copy in shared memory: see chain_inner_rows32.
 template <class Map, class Post, int COMBINE>
-int launch_inner_flat(const Args& a, uint32_t nvec) {
+int launch_inner_rows32(const Args& a, uint32_t nvec, uint32_t warps) {
+  constexpr int NIN = Map::kIn;
+  auto* fn = tcabk::chain_inner_rows32<Map, Post, COMBINE, NIN>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  const uint64_t rows_per_cta = static_cast<uint64_t>(warps) * 32;
+  const uint64_t grid = (a.outer + rows_per_cta - 1) / rows_per_cta;
+  if (grid > 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many rows");
+  const size_t smem = static_cast<size_t>(warps) * NIN * 32 * (nvec + 1) * 16;
+  fn<<<static_cast<unsigned>(grid), 32 * warps, smem, a.stream>>>(ptrs, a.out, a.outer, nvec, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_inner_rows32");
+}
+
+// Short rows (at most 128 vectors): g lanes per row, VPL vectors per lane beyond 32, see chain_inner_flat.
+template <class Map, class Post, int COMBINE, int VPL>
+int launch_inner_flat_vpl(const Args& a, uint32_t nvec) {
   constexpr int NIN = Map::kIn;
   constexpr int UNROLL = 4;
-  auto* fn = tcabk::chain_inner_flat<Map, Post, COMBINE, NIN, UNROLL>;
+  auto* fn = tcabk::chain_inner_flat<Map, Post, COMBINE, NIN, UNROLL, 0, VPL>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
   uint32_t g = 1;
-  while (g < nvec) g <<= 1;
+  while (g < nvec && g < 32) g <<= 1;
   const uint64_t rows_per_cta = static_cast<uint64_t>(8) * UNROLL * (32 / g);
   const uint64_t grid = (a.outer + rows_per_cta - 1) / rows_per_cta;
   if (grid > 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many rows");
   fn<<<static_cast<unsigned>(grid), 256, 0, a.stream>>>(ptrs, a.out, a.outer, nvec, g, a.init, a.caps);
   count_launch();
   return check_launch("chain_inner_flat");
+}
+template <class Map, class Post, int COMBINE>
+int launch_inner_flat(const Args& a, uint32_t nvec) {
+  if (nvec <= 32) return launch_inner_flat_vpl<Map, Post, COMBINE, 1>(a, nvec);
+  return launch_inner_flat_vpl<Map, Post, COMBINE, 2>(a, nvec);
 }
 
 template <class Map, class Post, int COMBINE>
@@ -265,7 +286,12 @@ int launch_chain(const Args& a) {
                    : launch_split<Map, Post, COMBINE, 1>(a, scratch, nvec, splits);
     }
     // short rows with enough of them: lanes along the row, consecutive rows in a warp (tune p0 keeps chain_inner)
-    if (vec && nvec >= 1 && nvec <= 32 && a.outer >= 1024 && tune(kReduceInner).p0 <= 0)
+    // up to 16 vectors a thread still folds its row in the reference's ascending order, over a coalesced copy
+    // (a row of one vector needs no copy: a lane folds its own vector in order)
+    if (vec && nvec >= 2 && nvec <= 16 && a.outer >= 1024 && tune(kReduceInner).p0 <= 0 && rows32_warps(nvec, NIN) >= 2)
+      return launch_inner_rows32<Map, Post, COMBINE>(a, nvec, rows32_warps(nvec, NIN));
+    // (measured: up to 32 vectors, and 49 ... 64 with two vectors per lane; other lengths up to 128 were no faster)
+    if (vec && nvec >= 1 && (nvec <= 32 || (nvec > 48 && nvec <= 64)) && a.outer >= 1024 && tune(kReduceInner).p0 <= 0)
       return launch_inner_flat<Map, Post, COMBINE>(a, nvec);
     // short rows: one thread folds a row sequentially, which is the reference's SeqReducer order exactly
     // measured: a warp per row up to 1023 vectors, a CTA per row from 1024 (8192 columns: 4.6 -> 7.1 TB/s)

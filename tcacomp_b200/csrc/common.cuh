@@ -140,6 +140,14 @@ inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm)
   return nk < 64 ? g : 0;
 }
 
+// chain_inner_rows32: warps per CTA for rows of nvec vectors and n_in operands such that the CTA's shared memory
+// stays within the 48 KiB that need no opt-in; 0 when not even one warp fits.
+inline uint32_t rows32_warps(uint32_t nvec, int n_in) {
+  const uint64_t per_warp = static_cast<uint64_t>(n_in) * 32 * (nvec + 1) * 16;
+  const uint64_t w = per_warp ? (48 * 1024) / per_warp : 0;
+  return w >= 8 ? 8u : static_cast<uint32_t>(w);
+}
+
 int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
 int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,
                                 uint32_t rows, uint32_t nk, cudaStream_t s);  // ins: [nprob][n_in]

@@ -1069,7 +1069,8 @@ def test_contraction_tile_sizes(oracle, cuda, tile):
 # innermost-axis chains and row kernels on short rows (1 to 32 vectors)
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("rows,cols", [(5000, 4), (3001, 8), (2049, 12), (1500, 16), (1024, 20), (4000, 32), (1111, 36),
-                                       (2000, 64), (1300, 100), (1025, 128), (1024, 124)])
+                                       (2000, 64), (1300, 100), (1025, 128), (1024, 124), (1100, 132), (1500, 256),
+                                       (1027, 300), (1200, 512), (1030, 508)])
 def test_short_rows(oracle, cuda, rows, cols):
     rng = np.random.default_rng(rows + cols)
     x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
@@ -1083,12 +1084,19 @@ def test_short_rows(oracle, cuda, rows, cols):
     check_guards(buf, torch.float32)
     from oracle import checks
     assert checks.rowsum_close(got, x)
-    try:        # the kernels that give a row to one thread, to four or to a warp: the same sums in another order
+    try:        # a warp per row: the same sums in another order
         T.tune("reduce_inner", 32)
         old = T.chain_reduce([xd], "(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f)", axis=1).cpu().numpy()
     finally:
         T.tune("reduce_inner")
     assert (np.abs(got - old) <= 2e-5 * np.abs(old) + 1e-30).all()
+    if cols <= 64:   # up to 16 vectors a thread folds its row in ascending order, the reference's: the same BITS as the
+        try:         # kernel that gives a thread a row without the coalesced copy, and as the sequential oracle
+            T.tune("reduce_inner", 1)
+            seq = T.chain_reduce([xd], "(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f)", axis=1).cpu().numpy()
+        finally:
+            T.tune("reduce_inner")
+        assert np.array_equal(got, seq)
     # max with init and a piped map: bit-exact
     got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.25, axis=1, post_expr="p0 + 1.0f").cpu().numpy()
     assert np.array_equal(got, np.maximum(x.max(1), np.float32(0.25)) + np.float32(1))
