@@ -405,7 +405,6 @@ int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, 
   for (int i = 0; i < TCAB_MAX_INPUTS; ++i) ptrs[i] = ins[i < jc->n_in ? i : 0];
   bool al = aligned16(out);
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
-  if (jc->broadcast && cols % 8 != 0) al = false;  // a group of eight must not straddle two rows
   void* a[] = {ptrs, &out, &n, &caps, &cols};
   if (al) return launch(jc->k[kMap8], (n / 8 + 1 + 255) / 256, 256, a, s, "chain_map");
   return launch(jc->k[kMap1], (n + 255) / 256, 256, a, s, "chain_map");

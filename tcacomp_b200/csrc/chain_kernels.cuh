@@ -876,6 +876,36 @@ struct MapLoadAll<EPT, BF, RB, CB, NIN, NIN> {
   static __device__ __forceinline__ void at(const float* const*, u64, u64, u64, float (*)[EPT]) {}
 };
 
+// The same for a group of eight that may straddle rows (cols % 8 != 0): operands of the full shape still load
+// their 32 (16) aligned bytes; an operand with one value per row or one shared row is read element by element, the
+// (row, column) of the group's first element advanced without further divisions.
+template <int BF, int RB, int CB, int NIN, int A = 0>
+struct MapLoadRagged {
+  static __device__ __forceinline__ void at(const float* const* p, u64 group, u64 row0, u32 col0, u32 cols, float (*f)[8]) {
+    constexpr bool bf = ((BF >> A) & 1) != 0;
+    if constexpr ((((RB | CB) >> A) & 1) != 0) {
+      u64 row = row0;
+      u32 col = col0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (col >= cols) {  // cols >= 1: at most one row ends per element
+          col = 0;
+          ++row;
+        }
+        MapLd<1, bf>::load(p[A], ((RB >> A) & 1) ? row : static_cast<u64>(col), &f[A][j]);
+        ++col;
+      }
+    } else {
+      MapLd<8, bf>::load(p[A], group, f[A]);
+    }
+    MapLoadRagged<BF, RB, CB, NIN, A + 1>::at(p, group, row0, col0, cols, f);
+  }
+};
+template <int BF, int RB, int CB, int NIN>
+struct MapLoadRagged<BF, RB, CB, NIN, NIN> {
+  static __device__ __forceinline__ void at(const float* const*, u64, u64, u32, u32, float (*)[8]) {}
+};
+
 template <int NIN, int BF, int RB, int CB, bool OUT_BF16, class Map>
 __device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i, u32 cols, const float* caps) {
   float f[NIN][1];
@@ -888,8 +918,8 @@ __device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i,
   else __stcs(static_cast<float*>(out) + i, r);
 }
 
-// cols: the innermost extent; only read when an operand is broadcast (RB | CB != 0), and then the EPT = 8
-// path requires cols % 8 == 0 (a group of eight never straddles two rows).
+// cols: the innermost extent; only read when an operand is broadcast (RB | CB != 0). A group of eight that
+// straddles rows (cols % 8 != 0) reads its broadcast operands element by element.
 template <class Map, int NIN, int BF, bool OUT_BF16, int EPT, int RB = 0, int CB = 0>
 __global__ void __launch_bounds__(256)
 chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
@@ -900,8 +930,13 @@ chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
     const u64 groups = n / 8;
     if (tid < groups) {
       float f[NIN][8];
-      const u64 gpr = (RB | CB) ? cols / 8 : 1;   // groups per row
-      MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, (RB | CB) ? tid / gpr : 0, (RB | CB) ? tid % gpr : 0, f);
+      if ((RB | CB) != 0 && cols % 8 != 0) {        // a group may straddle rows
+        const u64 first = tid * 8, row0 = first / cols;
+        MapLoadRagged<BF, RB, CB, NIN>::at(ins.p, tid, row0, static_cast<u32>(first - row0 * cols), cols, f);
+      } else {
+        const u64 gpr = (RB | CB) ? cols / 8 : 1;   // groups per row
+        MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, (RB | CB) ? tid / gpr : 0, (RB | CB) ? tid % gpr : 0, f);
+      }
       float r[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {

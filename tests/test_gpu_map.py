@@ -286,7 +286,7 @@ def bcast(a, shape):
     return np.ascontiguousarray(np.broadcast_to(a, shape))
 
 
-@pytest.mark.parametrize("rows,cols", [(37, 1000), (5, 8), (300, 4096), (3, 13), (64, 20000)])
+@pytest.mark.parametrize("rows,cols", [(37, 1000), (5, 8), (300, 4096), (3, 13), (64, 20000), (41, 1001), (90, 3), (77, 1)])
 def test_softmax_statement_by_statement_reads_row_values(oracle, cuda, rows, cols):
     """The softmax chain as the reference would have to spell it (pkg/local_test.go:17-68: a reduction stores into
     a rank-1 Local, the next statement reads it as x[i] inside the (i, j) iteration): m = max_j x; s = sum_j
@@ -313,7 +313,7 @@ def test_softmax_statement_by_statement_reads_row_values(oracle, cuda, rows, col
     assert ulp_distance(y.cpu().numpy(), host).max() <= 4 and (y.cpu().numpy() == host).mean() > 0.5
 
 
-@pytest.mark.parametrize("rows,cols", [(33, 1024), (7, 10), (128, 8192)])
+@pytest.mark.parametrize("rows,cols", [(33, 1024), (7, 10), (128, 8192), (19, 1003), (110, 5)])
 def test_shared_rows_bias_and_layernorm_tail(oracle, cuda, rows, cols):
     from oracle import binding as O, lambda_eval
     rng = np.random.default_rng(rows * cols)
