@@ -204,7 +204,8 @@ int launch_outer_flat(const Args& a, uint32_t g) {
 template <class Map, class Post, int COMBINE, int V>
 int launch_outer(const Args& a) {
   constexpr int NIN = Map::kIn;
-  constexpr int KW = 8, UNROLL = 4;
+  // 4-byte loads (rows that are not 16-byte multiples) need more of them in flight for the same bytes
+  constexpr int KW = 8, UNROLL = V == 1 ? 16 : 4;
   auto* fn = tcabk::chain_outer<Map, Post, COMBINE, NIN, V, KW, UNROLL>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
