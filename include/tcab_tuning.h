@@ -50,6 +50,16 @@ TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 TCAB_API int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t resident_ctas, int sms,
                                    int forced, uint32_t* ranges, uint32_t* klen);
 
+/* The launchers' shape rules that are pure arithmetic, for tests without a device:
+ *   outer_flat_g   - middle-axis reduction over [rows_or_batches, nk, nc]: column groups per tile when a warp takes a
+ *                    (b, column tile) instead of a CTA (0 = a CTA per tile);
+ *   stream_cluster - CTAs per row of a streaming cluster for a row of nvec vectors at per_step vectors per CTA and step;
+ *   rows32         - warps per CTA of the thread-per-row kernel for rows of nvec vectors and n_in operands (its shared
+ *                    memory stays within 48 KiB; fewer than 2: not used). */
+TCAB_API int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32_t nc, int sms, uint32_t nvec,
+                                   uint32_t per_step, int prefer_three, int n_in, uint32_t* outer_flat_g,
+                                   uint32_t* stream_cluster, uint32_t* rows32);
+
 /* Validates a chain exactly as tcab_chain_prepare does and runs the run-time compiler on it for sm_100a, but
  * loads nothing: works on a host without a GPU (needs libnvrtc). A chain that has an ahead-of-time kernel is
  * compiled all the same. Arguments as tcab_chain_prepare, plus the bit masks of the operands that have one

@@ -102,6 +102,9 @@ TUNING_SYMBOLS = [
     ("tcab_tune", C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int]),
     ("tcab_compile_check", C.c_int,
      [C.POINTER(Chain), C.POINTER(C.c_int32), C.c_uint32, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    ("tcab_plan_row_kernels", C.c_int,
+     [C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_uint32),
+      C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     ("tcab_plan_outer_split", C.c_int,
      [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
 ]

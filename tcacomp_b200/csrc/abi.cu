@@ -16,6 +16,7 @@
 
 #include "../../include/tcab_tuning.h"
 #include "common.cuh"
+#include "rowvec.cuh"
 
 namespace tcab {
 namespace {
@@ -342,6 +343,17 @@ int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, uint64_t 
   if (ranges == nullptr || klen == nullptr) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_split: null output");
   if (sms < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_split: sms must be positive");
   plan_outer_ranges(plan_outer_splits(tiles, cells, nk, resident_ctas, sms, forced), nk, ranges, klen);
+  return TCAB_OK;
+}
+
+int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32_t nc, int sms, uint32_t nvec, uint32_t per_step,
+                          int prefer_three, int n_in, uint32_t* outer_flat_g, uint32_t* stream_cluster, uint32_t* rows32) {
+  if (outer_flat_g == nullptr || stream_cluster == nullptr || rows32 == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "plan_row_kernels: null output");
+  if (sms < 1 || per_step < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_row_kernels: sms and per_step must be positive");
+  *outer_flat_g = outer_flat_groups(rows_or_batches, nk, nc, sms);
+  *stream_cluster = stream_cluster_size(nvec, per_step, prefer_three != 0);
+  *rows32 = rows32_warps(nvec, n_in);
   return TCAB_OK;
 }
 

@@ -289,3 +289,27 @@ def test_lambdas_over_operands_that_bind_a_subset_of_the_axes_compile(tcab_lib, 
     ch = _bchain(expr)
     arr = (C.c_int32 * len(types))(*types)
     assert tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, rb, cb, cells) == _lib.OK, _err(tcab_lib)
+
+
+def test_row_kernel_shape_rules(tcab_lib):
+    """The launchers' choices that are pure arithmetic: which middle-axis shapes a warp per (b, column tile) takes, how
+    many CTAs stream a long row, how many warps the thread-per-row kernel gets."""
+    def plan(rows=0, nk=1, nc=4, sms=148, nvec=1, per_step=1024, three=1, n_in=1):
+        g, cs, w = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        assert tcab_lib.tcab_plan_row_kernels(rows, nk, nc, sms, nvec, per_step, three, n_in, C.byref(g), C.byref(cs), C.byref(w)) == 0
+        return g.value, cs.value, w.value
+    # narrow rows: the whole row is one tile of nc / 4 column groups
+    assert [plan(rows=100000, nk=256, nc=c)[0] for c in (4, 8, 16, 32)] == [1, 2, 4, 8]
+    assert plan(rows=100000, nk=256, nc=64)[0] == 16 and plan(rows=1000, nk=256, nc=64)[0] == 0   # 64 columns: only with many warps
+    assert plan(rows=100000, nk=256, nc=12)[0] == 0 and plan(rows=100000, nk=256, nc=96)[0] == 0  # not 4 * 2^i / between 64 and 128
+    assert plan(rows=100000, nk=256, nc=6)[0] == 0                                                # not whole vectors
+    # short reduced axes with wide rows: 32 groups of a 128-column tile; long axes keep a CTA per tile
+    assert plan(rows=65536, nk=4, nc=1024)[0] == 32 and plan(rows=65536, nk=64, nc=1024)[0] == 0
+    # a handful of long columns needs the k split over CTAs instead
+    assert plan(rows=8, nk=1 << 20, nc=8)[0] == 0 and plan(rows=8, nk=4096, nc=8)[0] == 2
+    # streaming clusters: four steps with the smallest cluster, three full steps where a larger one gives them
+    assert plan(nvec=6144)[1] == 2 and plan(nvec=8192)[1] == 4 and plan(nvec=12564)[1] == 4 and plan(nvec=32768)[1] == 8
+    assert plan(nvec=8192, three=0)[1] == 2 and plan(nvec=100)[1] == 2 and plan(nvec=10**6, per_step=4096)[1] == 8
+    # thread-per-row kernel: 8 warps while 48 KiB hold them, fewer with more operands, none when one warp does not fit
+    assert plan(nvec=16, n_in=1)[2] == 5 and plan(nvec=4, n_in=1)[2] == 8 and plan(nvec=16, n_in=6)[2] == 0
+    assert plan(nvec=16, n_in=2)[2] == 2 and plan(nvec=16, n_in=3)[2] == 1
