@@ -148,7 +148,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
       const std::string cm = ", " + std::to_string(sp.cell_mask);
       names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
       names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + cm + ">";
-      names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 16, " + bf + cm + ">";
+      names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 8, " + bf + cm + ">";
     } else if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
       names.assign(kSlots, std::string());
       for (int v = 0; v < 2; ++v)
@@ -162,7 +162,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1, " + bf + ">";
     names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
     names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
-    names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 16, " + bf + ">";
+    names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 8, " + bf + ">";
     names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat2] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ", 2>";

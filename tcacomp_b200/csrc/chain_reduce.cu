@@ -205,7 +205,7 @@ template <class Map, class Post, int COMBINE, int V>
 int launch_outer(const Args& a) {
   constexpr int NIN = Map::kIn;
   // 4-byte loads (rows that are not 16-byte multiples) need more of them in flight for the same bytes
-  constexpr int KW = 8, UNROLL = V == 1 ? 16 : 4;
+  constexpr int KW = 8, UNROLL = V == 1 ? 8 : 4;
   auto* fn = tcabk::chain_outer<Map, Post, COMBINE, NIN, V, KW, UNROLL>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];

@@ -345,7 +345,7 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
     if (cv == 2 && kw == 4) return launch<4, 2, 4, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
     return fail(TCAB_ERR_UNSUPPORTED, "reduce_outer: no kernel for tuned shape %d x %d", cv, kw);
   }
-  return launch<1, 1, 8, 16>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);  // 4-byte loads: more of them in flight
+  return launch<1, 1, 8, 4>(t, sum, mx, amax, nb, nk, nc, tn.p2, tn.p3, s);
 }
 
 }  // namespace tcab
