@@ -216,6 +216,51 @@ class SoftmaxVocabRows(SoftmaxRows):
     profile = "softmax_rows_cluster_stream_softmax_rows_f32_2048x65536.md"
 
 
+class LayernormHeadRows(Workload):
+    """Rows of one attention head (the per-head normalisation of queries and keys); selectable only."""
+    name = "layernorm_rows_bf16_1048576x128"
+    dtype = "bf16"
+    full_units, cols = 1048576, 128
+    shape = "x bf16 [1048576, 128] ~ N(0,1), gamma/beta bf16 [128] -> y bf16 [1048576, 128]"
+    profile = "layernorm_rows_reg_layernorm_rows_bf16_1048576x128.md"
+
+    def work(self):
+        return 2.0 * self.units * self.cols * 2 + 2 * self.cols * 2
+
+    def make(self, dev, seed):
+        import tcacomp_b200 as T
+        self.T = T
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.x = torch.randn((self.units, self.cols), generator=g, device=dev).to(torch.bfloat16)
+        self.gamma = (1 + 0.1 * torch.randn((self.cols,), generator=g, device=dev)).to(torch.bfloat16)
+        self.beta = (0.1 * torch.randn((self.cols,), generator=g, device=dev)).to(torch.bfloat16)
+        self.y = torch.empty_like(self.x)
+
+    def step(self):
+        self.T.layernorm_rows(self.x, self.gamma, self.beta, 1e-5, out=self.y)
+
+    def pipeline_spec(self, chunk_units):
+        from tcacomp_b200.pipeline import PipelineSpec
+        return PipelineSpec("layernorm_rows", self.x.device, chunk_units, (self.cols,), torch.bfloat16, eps=1e-5,
+                            resident=(self.gamma, self.beta))
+
+    def host_buffers(self):
+        hx = self.x.cpu().pin_memory()
+        return [hx], [torch.empty_like(hx).pin_memory()]
+
+    def cpu_sample(self, oracle):
+        rows = min(65536, self.units)
+        x, g, b = bits16(self.x[:rows]), bits16(self.gamma), bits16(self.beta)
+        return (lambda: oracle.layernorm_rows_bf16(x, g, b, 1e-5)), 2.0 * rows * self.cols * 2, f"first {rows} of {self.units} rows per pass"
+
+    def check(self, oracle, full):
+        from oracle import checks
+        idx = torch.arange(0, self.units, max(1, self.units // (65536 if full else 256)), device=self.x.device)
+        rep = checks.layernorm_bf16_report_fast(bits16(self.y[idx]), bits16(self.x[idx]), bits16(self.gamma), bits16(self.beta), 1e-5)
+        assert rep.ok, f"layer-norm parity check failed: {rep}"
+        return rep.as_dict()
+
+
 class LayernormRows(Workload):
     name = "layernorm_rows_bf16_65536x8192"
     dtype = "bf16"
@@ -500,7 +545,8 @@ class MapOnly(Workload):
 
 
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
-SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows})
+SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows,
+                                LayernormHeadRows.name: LayernormHeadRows})
 DEFAULT = SoftmaxRows.name
 
 
