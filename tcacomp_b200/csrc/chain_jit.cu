@@ -149,6 +149,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
       names[kFinish] = "tcabk::chain_split_finish<tcabj::Post, " + c + ">";
       names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + cm + ">";
       names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 8, " + bf + cm + ">";
+      names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + cm + ">";
     } else if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
       names.assign(kSlots, std::string());
       for (int v = 0; v < 2; ++v)
@@ -345,7 +346,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
   // narrow rows and short reduced axes: a warp per (b, column tile) (same policy as the ahead-of-time path)
-  if (vec && !jc->cells && jc->k[kOuterFlat] != nullptr && tune(kReduceInner).p3 <= 0) {
+  if (vec && jc->k[kOuterFlat] != nullptr && tune(kReduceInner).p3 <= 0) {
     const uint32_t g = outer_flat_groups(nb, nk, nc, sm_count());
     if (g != 0) {
       uint32_t tpb = (nc + 127) / 128;

@@ -579,7 +579,7 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 // 32 vectors of a step are contiguous in memory. Every lane folds the k rows it sees (ascending), lanes with the
 // same column group then meet by shuffles, and lanes 0..g-1 store. No shared memory, no barrier; eight independent
 // warps per CTA. 16-byte vectors only (nc % 4 == 0, aligned operands).
-template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0>
+template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0, int CELL = 0>
 __global__ void __launch_bounds__(256)
 chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, u32 g, float init,
                  Caps caps) {
@@ -599,12 +599,14 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
 #pragma unroll
   for (int j = 0; j < 4; ++j) acc[j] = C::identity();
   if (colok) {
+    float cellval[NIN][4];  // operands that lack the reduced axis: one value per output cell, loaded once
+    LoadOuterAll<4, BF, CELL, NIN>::cells(ins.p, (static_cast<u64>(b) * nc + col) / 4, cellval);
     for (u32 k0 = kr; k0 < nk; k0 += rows_per_step * UNROLL) {
       float f[UNROLL][NIN][4];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const u32 k = k0 + u * rows_per_step;
-        if (k < nk) LoadAll<4, BF, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, f[u]);
+        if (k < nk) LoadOuterAll<4, BF, CELL, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, cellval, f[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {

@@ -356,7 +356,8 @@ def test_broadcast_shapes_are_checked(cuda):
     assert e.value.status == T._lib.ERR_SHAPE
 
 
-@pytest.mark.parametrize("nb,nk,nc", [(5, 300, 132), (2, 9, 7), (1, 5000, 64), (16, 8, 256)])
+@pytest.mark.parametrize("nb,nk,nc", [(5, 300, 132), (2, 9, 7), (1, 5000, 64), (16, 8, 256), (3000, 40, 8), (700, 6, 512),
+                                      (5000, 3, 4)])
 def test_middle_axis_reduction_reads_a_value_per_output_cell(cuda, nb, nk, nc):
     """The reference's softmax suite kernel reduces over the MIDDLE axis (testing/kernels/fusion/softmax.tca). Written
     statement by statement its second reduction reads the first one's result m[i][j] inside the (i, k, j) iteration:
