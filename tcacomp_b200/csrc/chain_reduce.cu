@@ -690,6 +690,12 @@ int launch_chain_contract(const PreparedChain& pc, const float* lhs, const float
   // ahead-of-time: the plain product with a sum reducer, stored as it is or scaled
   if (pc.entry >= 0 && kTable[pc.entry].combine == 0 && std::string(kTable[pc.entry].map) == MapMul2::text()) {
     const std::string post = kTable[pc.entry].post;
+    // large fp32 problems: three bf16 pieces per operand on the tensor cores (tune("gemm", _, _, 64) keeps the scalar
+    // kernel; so do small problems, whose outputs then keep the reference's ascending order over k)
+    if (pc.init == 0.0f && (post.empty() || post == PostScale::text()) && tune(kGemm).p2 != 64) {
+      const int rc = launch_contract_f32_split3(lhs, rhs, rhs_nk, post.empty() ? 1.0f : pc.caps[8], out, m, n, k, s);
+      if (rc != TCAB_ERR_UNSUPPORTED) return rc;
+    }
     if (post.empty())
       return launch_contract_aot<MapMul2, tcabk::PostNone, 0>(lhs, rhs, out, m, n, k, rhs_nk, pc.init, caps, s);
     if (post == PostScale::text())

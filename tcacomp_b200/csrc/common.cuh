@@ -44,7 +44,7 @@ int occupancy(const void* fn, int block, size_t smem);
 // allocation failed (the callers then take a path that needs no scratch). With `grow`, a buffer that is
 // too small is freed (cudaFree synchronises the device, so nothing still reads it) and allocated anew.
 // `zero`: the buffer is cleared when it is allocated (arrival counters that their users leave at zero).
-enum ScratchKind { kScratchChainSplit = 0, kScratchOuter = 1, kScratchGemm = 2, kScratchGemmCounters = 3, kScratchKinds = 4 };
+enum ScratchKind { kScratchChainSplit = 0, kScratchOuter = 1, kScratchGemm = 2, kScratchGemmCounters = 3, kScratchSplit3 = 4, kScratchKinds = 5 };
 void* stream_scratch(int kind, cudaStream_t stream, size_t bytes, bool grow, bool zero = false);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -147,6 +147,12 @@ inline uint32_t rows32_warps(uint32_t nvec, int n_in) {
   const uint64_t w = per_warp ? (48 * 1024) / per_warp : 0;
   return w >= 8 ? 8u : static_cast<uint32_t>(w);
 }
+
+// fp32 operands, plain product: each operand is cut into three bf16 pieces and the six significant piece products
+// run as ONE bf16 tensor-core contraction over 6 K. Returns TCAB_ERR_UNSUPPORTED (without a message) when the shape
+// does not qualify or the workspace would exceed its cap: the caller keeps the scalar kernel.
+int launch_contract_f32_split3(const float* a, const float* b, int b_is_nk, float alpha, float* c, uint32_t m, uint32_t n,
+                               uint32_t k, cudaStream_t s);
 
 int warm_chain(const PreparedChain& pc);  // compile + load now what a launch would compile later
 int launch_chain_reduce_batched(const PreparedChain& pc, const float* const* ins, float* const* outs, uint32_t nprob,

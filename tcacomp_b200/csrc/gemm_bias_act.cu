@@ -1480,4 +1480,90 @@ int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int 
   return TCAB_OK;
 }
 
+// ------------------------------------------------------------------------------------------------------------
+// fp32 contraction chains with the plain product on the tensor cores. x = x0 + x1 + x2 with three bf16 pieces
+// (x0 = bf16(x), x1 = bf16(x - x0), x2 = bf16(x - x0 - x1): 24 significant bits, the remainder is below
+// 2^-24 |x|). a * b = sum of nine piece products, of which the six with weight of at least 2^-16 are kept:
+// a2 b0, a1 b1, a0 b2, a1 b0, a0 b1, a0 b0 (what is dropped is below 3 * 2^-24 |a b|). Written side by side
+// along K -- A' = [a2 | a1 | a0 | a1 | a0 | a0] ([M, 6 K]) against B' = [b0; b1; b2; b0; b1; b0] ([6 K, N]) --
+// they are ONE bf16 contraction with fp32 accumulation, which the kernel above already is; the smallest terms
+// come first in K. Products of bf16 values are exact in fp32, so the error of an output is 2e-7 of sum |a||b|
+// plus the accumulation's, against 6e-8 per operation for the scalar kernel.
+// ------------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kSplit3WorkspaceBytes = static_cast<size_t>(512) << 20;
+
+__device__ __forceinline__ void split3(float x, unsigned short* p) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(x);
+  float r = x - __bfloat162float(h0);
+  if (!(fabsf(x) <= 3.0e38f)) r = 0.0f;  // inf and NaN stay in the first piece alone
+  const __nv_bfloat16 h1 = __float2bfloat16_rn(r);
+  r -= __bfloat162float(h1);
+  const __nv_bfloat16 h2 = __float2bfloat16_rn(r);
+  p[0] = __bfloat16_as_ushort(h0);
+  p[1] = __bfloat16_as_ushort(h1);
+  p[2] = __bfloat16_as_ushort(h2);
+}
+
+// src [rows, cols] fp32 (cols % 4 == 0) -> dst bf16: six blocks of pieces order[0..5], side by side ([rows, 6 cols],
+// STACK = false) or below each other ([6 rows, cols], STACK = true). A thread takes four consecutive elements.
+template <bool STACK>
+__global__ void __launch_bounds__(256)
+split3_kernel(const float* __restrict__ src, unsigned short* __restrict__ dst, uint64_t rows, uint32_t cols, uint32_t order) {
+  const uint64_t q = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;  // group of four
+  const uint64_t per_row = cols / 4;
+  if (q >= rows * per_row) return;
+  const uint64_t r = q / per_row;
+  const uint32_t c = static_cast<uint32_t>(q - r * per_row) * 4;
+  const float4 v = __ldcs(reinterpret_cast<const float4*>(src) + q);
+  unsigned short pc[4][3];
+  split3(v.x, pc[0]);
+  split3(v.y, pc[1]);
+  split3(v.z, pc[2]);
+  split3(v.w, pc[3]);
+#pragma unroll
+  for (uint32_t j = 0; j < 6; ++j) {
+    const uint32_t w = (order >> (4 * j)) & 3u;
+    const uint64_t at = STACK ? (static_cast<uint64_t>(j) * rows + r) * cols + c : (r * 6 + j) * static_cast<uint64_t>(cols) + c;
+    const uint2 out = make_uint2(static_cast<uint32_t>(pc[0][w]) | (static_cast<uint32_t>(pc[1][w]) << 16),
+                                 static_cast<uint32_t>(pc[2][w]) | (static_cast<uint32_t>(pc[3][w]) << 16));
+    *reinterpret_cast<uint2*>(dst + at) = out;
+  }
+}
+
+}  // namespace
+
+int launch_contract_f32_split3(const float* a, const float* b, int b_is_nk, float alpha, float* c, uint32_t m, uint32_t n,
+                               uint32_t k, cudaStream_t s) {
+  // enough 256 x 256 tiles to fill the tensor-core kernel's persistent grid, a K worth three launches, 16-byte rows
+  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  if (tiles < 64 || k < 256 || k % 4 != 0 || n % 4 != 0 || (!b_is_nk && n % 8 != 0)) return TCAB_ERR_UNSUPPORTED;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c) || static_cast<uint64_t>(k) * 6 > 0xffffffffull) return TCAB_ERR_UNSUPPORTED;
+  const size_t bytes_a = ((static_cast<size_t>(m) * k * 12) + 255) & ~static_cast<size_t>(255);
+  const size_t bytes_b = static_cast<size_t>(n) * k * 12;
+  if (bytes_a + bytes_b > kSplit3WorkspaceBytes) return TCAB_ERR_UNSUPPORTED;
+  unsigned char* ws = static_cast<unsigned char*>(stream_scratch(kScratchSplit3, s, bytes_a + bytes_b, true));
+  if (ws == nullptr) return TCAB_ERR_UNSUPPORTED;
+  unsigned short* a3 = reinterpret_cast<unsigned short*>(ws);
+  unsigned short* b3 = reinterpret_cast<unsigned short*>(ws + bytes_a);
+  constexpr uint32_t kOrderA = 2u | (1u << 4) | (0u << 8) | (1u << 12) | (0u << 16) | (0u << 20);  // a2 a1 a0 a1 a0 a0
+  constexpr uint32_t kOrderB = 0u | (1u << 4) | (2u << 8) | (0u << 12) | (1u << 16) | (0u << 20);  // b0 b1 b2 b0 b1 b0
+  const uint64_t qa = static_cast<uint64_t>(m) * (k / 4);
+  split3_kernel<false><<<static_cast<unsigned>((qa + 255) / 256), 256, 0, s>>>(a, a3, m, k, kOrderA);
+  count_launch();
+  if (b_is_nk) {  // [N, K]: blocks side by side, like a's
+    const uint64_t qb = static_cast<uint64_t>(n) * (k / 4);
+    split3_kernel<false><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b, b3, n, k, kOrderB);
+  } else {        // [K, N]: blocks below each other
+    const uint64_t qb = static_cast<uint64_t>(k) * (n / 4);
+    split3_kernel<true><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b, b3, k, n, kOrderB);
+  }
+  count_launch();
+  const int rc = check_launch("split3_kernel");
+  if (rc != TCAB_OK) return rc;
+  return launch_contract_bf16_tc(reinterpret_cast<const __nv_bfloat16*>(a3), reinterpret_cast<const __nv_bfloat16*>(b3), b_is_nk,
+                                 alpha, c, m, n, 6 * k, s);
+}
+
 }  // namespace tcab

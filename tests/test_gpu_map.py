@@ -279,6 +279,43 @@ def test_bf16_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     assert (np.abs(got - (want + k)) <= 1e-5 * (mag + k) + 1e-30).all()
 
 
+@pytest.mark.parametrize("m,k,n,nk", [(2048, 512, 2048, False), (2048, 260, 2056, True), (4100, 256, 1032, False)])
+def test_large_f32_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
+    # fp32 operands, the plain product, a sum from 0: from 64 output tiles of 256 x 256 on, each operand is cut into
+    # three bf16 pieces and the six significant piece products run as one bf16 contraction over 6 K (three launches).
+    # What is dropped is below 3 * 2^-24 of |a b| per product; small problems keep the scalar kernel and with it the
+    # reference's ascending order over k (tuning value gemm p2 = 64 keeps it for every size).
+    rng = np.random.default_rng(m + k + n)
+    a = rng.normal(0, 1, (m, k)).astype(np.float32)
+    b = rng.normal(0, 1, (n, k) if nk else (k, n)).astype(np.float32)
+    a[0, :8] = [1e-30, -1e30, 3.0, 1e-38, 0.0, -0.0, 65504.0, 1.0000001]      # tiny, huge and exact values
+    ad, bd = to_dev(a, cuda), to_dev(b, cuda)
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    bm = b64.T if nk else b64
+    want, mag = a64 @ bm, np.abs(a64) @ np.abs(bm)
+    out = torch.full((m + 2, n), -7.0, device=cuda)
+    n0 = T.launch_count()
+    T.chain_contract(ad, bd, rhs_is_nk=nk, post_expr="p0 * c0", captures=(0.5,), out=out[1:m + 1])
+    assert T.launch_count() - n0 == 3
+    got = out.cpu().numpy()
+    assert (got[0] == -7.0).all() and (got[-1] == -7.0).all()
+    err = np.abs(got[1:-1] - 0.5 * want) / (0.5 * mag)
+    assert err.max() <= 2e-6, err.max()                 # the scalar kernel's bound on the same data is 1e-5
+    try:
+        T.tune("gemm", 0, 0, 64)
+        n0 = T.launch_count()
+        ref = T.chain_contract(ad, bd, rhs_is_nk=nk).cpu().numpy()
+        assert T.launch_count() - n0 == 1
+    finally:
+        T.tune("gemm")
+    tc = T.chain_contract(ad, bd, rhs_is_nk=nk).cpu().numpy()
+    assert (np.abs(tc - ref) <= 4e-6 * mag).all()
+    # a reducer other than the sum, or an init other than 0, keeps the scalar kernel
+    n0 = T.launch_count()
+    T.chain_contract(ad, bd, rhs_is_nk=nk, init=1.0)
+    assert T.launch_count() - n0 == 1
+
+
 # ----------------------------------------------------------------------------
 # operands that bind a subset of the iteration axes: one value per row, one row shared by all rows
 # ----------------------------------------------------------------------------
