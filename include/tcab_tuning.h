@@ -38,7 +38,7 @@ extern "C" {
  *       tcab_gemm_bias_act 32: the K ranges go to a workspace and a second launch adds them, never the cluster
  *       form; 16: the same with the last-arriving epilogue warps adding them instead of the second launch;
  *       64: tcab_chain_contract keeps product chains (bf16, or large f32) on the scalar kernel instead of the
- *       tensor cores),
+ *       tensor cores; 128: p3 = workspace cap in MiB of the three-piece f32 contraction, which then runs in blocks),
  *       p3 = ranges the K blocks of a tile are cut into by kernels 3, 4 and 5 (1 = no split; 2..8 for 5). */
 TCAB_API int tcab_tune(const char* family, int p0, int p1, int p2, int p3);
 

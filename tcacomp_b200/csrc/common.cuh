@@ -117,7 +117,7 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
                          cudaStream_t s);
 
 int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int b_is_nk, float alpha, float* c, uint32_t m,
-                            uint32_t n, uint32_t k, cudaStream_t s);  // tensor cores, fp32 out (gemm_bias_act.cu)
+                            uint32_t n, uint32_t k, cudaStream_t s, uint64_t c_pitch = 0);  // tensor cores, fp32 out (gemm_bias_act.cu)
 
 // chain_outer_flat (a warp per (b, column tile)) instead of chain_outer (a CTA per tile) for a middle-axis
 // reduction over [nb, nk, nc] with 16-byte vectors: rows of at most 32 columns, rows of 64 columns when there are

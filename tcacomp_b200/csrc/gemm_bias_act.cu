@@ -1173,11 +1173,12 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 }
 
 // A 2-D fp32 row-major tensor with a box of box_rows x 32 columns (128-byte rows, 128-byte swizzle).
-int make_map_f32(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+int make_map_f32(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols,
+                 uint64_t pitch = 0) {  // pitch: elements between rows (0 = cols)
   EncodeFn enc = encode_fn();
   if (enc == nullptr) return fail(TCAB_ERR_CUDA, "chain_contract: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint64_t strides[1] = {(pitch ? pitch : cols) * 4};
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
@@ -1449,16 +1450,19 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
 // has checked the alignment rules (K % 8 == 0, N % 8 == 0 for [K, N] operands, N % 4 == 0, 16-byte aligned
 // pointers).
 int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int b_is_nk, float alpha, float* c, uint32_t m,
-                            uint32_t n, uint32_t k, cudaStream_t s) {
+                            uint32_t n, uint32_t k, cudaStream_t s, uint64_t c_pitch) {
+  // c_pitch: elements between the rows of c (0 = n): c may be a block of columns of a wider matrix
   if (m == 0 || n == 0) return TCAB_OK;
   if (k == 0) {  // an empty reduction: init = 0 everywhere
-    const cudaError_t e = cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * sizeof(float), s);
+    const cudaError_t e = (c_pitch == 0 || c_pitch == n)
+                              ? cudaMemsetAsync(c, 0, static_cast<size_t>(m) * n * sizeof(float), s)
+                              : cudaMemset2DAsync(c, c_pitch * sizeof(float), 0, static_cast<size_t>(n) * sizeof(float), m, s);
     return e == cudaSuccess ? TCAB_OK : fail(TCAB_ERR_CUDA, "chain_contract: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
   }
   CUtensorMap ta, tb, tcm;
   int rc = make_map(&ta, a, m, k, BM);
   if (rc == TCAB_OK) rc = b_is_nk ? make_map(&tb, b, n, k, BN) : make_map(&tb, b, k, n, BK);
-  if (rc == TCAB_OK) rc = make_map_f32(&tcm, c, m, n, 32, 32);
+  if (rc == TCAB_OK) rc = make_map_f32(&tcm, c, m, n, 32, 32, c_pitch);
   if (rc != TCAB_OK) return rc;
   const void* fn = b_is_nk ? reinterpret_cast<const void*>(gemm_bias_act_kernel<true, true>)
                            : reinterpret_cast<const void*>(gemm_bias_act_kernel<true, false>);
@@ -1506,17 +1510,19 @@ __device__ __forceinline__ void split3(float x, unsigned short* p) {
   p[2] = __bfloat16_as_ushort(h2);
 }
 
-// src [rows, cols] fp32 (cols % 4 == 0) -> dst bf16: six blocks of pieces order[0..5], side by side ([rows, 6 cols],
-// STACK = false) or below each other ([6 rows, cols], STACK = true). A thread takes four consecutive elements.
+// src [rows, cols] fp32 (cols % 4 == 0; `pitch` elements between its rows: it may be a block of columns of a wider
+// matrix) -> dst bf16, contiguous: six blocks of pieces order[0..5], side by side ([rows, 6 cols], STACK = false) or
+// below each other ([6 rows, cols], STACK = true). A thread takes four consecutive elements.
 template <bool STACK>
 __global__ void __launch_bounds__(256)
-split3_kernel(const float* __restrict__ src, unsigned short* __restrict__ dst, uint64_t rows, uint32_t cols, uint32_t order) {
+split3_kernel(const float* __restrict__ src, uint64_t pitch, unsigned short* __restrict__ dst, uint64_t rows, uint32_t cols,
+              uint32_t order) {
   const uint64_t q = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;  // group of four
   const uint64_t per_row = cols / 4;
   if (q >= rows * per_row) return;
   const uint64_t r = q / per_row;
   const uint32_t c = static_cast<uint32_t>(q - r * per_row) * 4;
-  const float4 v = __ldcs(reinterpret_cast<const float4*>(src) + q);
+  const float4 v = __ldcs(reinterpret_cast<const float4*>(src + r * pitch + c));
   unsigned short pc[4][3];
   split3(v.x, pc[0]);
   split3(v.y, pc[1]);
@@ -1540,30 +1546,54 @@ int launch_contract_f32_split3(const float* a, const float* b, int b_is_nk, floa
   const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
   if (tiles < 64 || k < 256 || k % 4 != 0 || n % 4 != 0 || (!b_is_nk && n % 8 != 0)) return TCAB_ERR_UNSUPPORTED;
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || static_cast<uint64_t>(k) * 6 > 0xffffffffull) return TCAB_ERR_UNSUPPORTED;
-  const size_t bytes_a = ((static_cast<size_t>(m) * k * 12) + 255) & ~static_cast<size_t>(255);
-  const size_t bytes_b = static_cast<size_t>(n) * k * 12;
-  if (bytes_a + bytes_b > kSplit3WorkspaceBytes) return TCAB_ERR_UNSUPPORTED;
+  // The pieces of a block of mc rows of a and of a block of nc columns (rows, for [N, K]) of b fit the workspace at a
+  // time: 12 k bytes per row or column. The whole problem when that is enough; otherwise blocks of multiples of
+  // 256 (at least 1024 each way, so that a block product still has 16 tiles or more), b's block outermost.
+  const uint64_t per_line = static_cast<uint64_t>(k) * 12;
+  const Tune& tn = tune(kGemm);  // p2 == 128: p3 = the workspace cap in MiB (tests of the blocked form)
+  const uint64_t cap = tn.p2 == 128 && tn.p3 > 0 ? static_cast<uint64_t>(tn.p3) << 20 : kSplit3WorkspaceBytes;
+  const uint64_t lines = cap / per_line;  // rows of a plus columns of b that fit
+  uint32_t mc = m, nc = n;
+  if (static_cast<uint64_t>(m) + n + 64 > lines) {
+    if (lines < 2048 + 64) return TCAB_ERR_UNSUPPORTED;  // K so long that not even 1024 x 1024 blocks fit
+    const uint64_t half = ((lines - 64) / 2) & ~static_cast<uint64_t>(255);
+    nc = n <= half ? n : static_cast<uint32_t>(half);
+    const uint64_t left = (lines - 64 - nc) & ~static_cast<uint64_t>(255);
+    mc = m <= left ? m : static_cast<uint32_t>(left);
+  }
+  const size_t bytes_a = ((static_cast<size_t>(mc) * per_line) + 255) & ~static_cast<size_t>(255);
+  const size_t bytes_b = static_cast<size_t>(nc) * per_line;
   unsigned char* ws = static_cast<unsigned char*>(stream_scratch(kScratchSplit3, s, bytes_a + bytes_b, true));
   if (ws == nullptr) return TCAB_ERR_UNSUPPORTED;
   unsigned short* a3 = reinterpret_cast<unsigned short*>(ws);
   unsigned short* b3 = reinterpret_cast<unsigned short*>(ws + bytes_a);
   constexpr uint32_t kOrderA = 2u | (1u << 4) | (0u << 8) | (1u << 12) | (0u << 16) | (0u << 20);  // a2 a1 a0 a1 a0 a0
   constexpr uint32_t kOrderB = 0u | (1u << 4) | (2u << 8) | (0u << 12) | (1u << 16) | (0u << 20);  // b0 b1 b2 b0 b1 b0
-  const uint64_t qa = static_cast<uint64_t>(m) * (k / 4);
-  split3_kernel<false><<<static_cast<unsigned>((qa + 255) / 256), 256, 0, s>>>(a, a3, m, k, kOrderA);
-  count_launch();
-  if (b_is_nk) {  // [N, K]: blocks side by side, like a's
-    const uint64_t qb = static_cast<uint64_t>(n) * (k / 4);
-    split3_kernel<false><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b, b3, n, k, kOrderB);
-  } else {        // [K, N]: blocks below each other
-    const uint64_t qb = static_cast<uint64_t>(k) * (n / 4);
-    split3_kernel<true><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b, b3, k, n, kOrderB);
+  for (uint32_t n0 = 0; n0 < n; n0 += nc) {
+    const uint32_t nn = n - n0 < nc ? n - n0 : nc;  // a multiple of 8 (of 4 for [N, K]): n, n0 and nc are
+    if (b_is_nk) {  // [N, K]: rows n0 .. n0 + nn, blocks side by side, like a's
+      const uint64_t qb = static_cast<uint64_t>(nn) * (k / 4);
+      split3_kernel<false><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b + static_cast<size_t>(n0) * k, k, b3, nn, k, kOrderB);
+    } else {        // [K, N]: columns n0 .. n0 + nn of every row, blocks below each other
+      const uint64_t qb = static_cast<uint64_t>(k) * (nn / 4);
+      split3_kernel<true><<<static_cast<unsigned>((qb + 255) / 256), 256, 0, s>>>(b + n0, n, b3, k, nn, kOrderB);
+    }
+    count_launch();
+    for (uint32_t m0 = 0; m0 < m; m0 += mc) {
+      const uint32_t mm = m - m0 < mc ? m - m0 : mc;
+      if (n0 == 0 || mc < m) {  // a's pieces are still there when one block holds all of a
+        const uint64_t qa = static_cast<uint64_t>(mm) * (k / 4);
+        split3_kernel<false><<<static_cast<unsigned>((qa + 255) / 256), 256, 0, s>>>(a + static_cast<size_t>(m0) * k, k, a3, mm, k, kOrderA);
+        count_launch();
+      }
+      int rc = check_launch("split3_kernel");
+      if (rc == TCAB_OK)
+        rc = launch_contract_bf16_tc(reinterpret_cast<const __nv_bfloat16*>(a3), reinterpret_cast<const __nv_bfloat16*>(b3), b_is_nk,
+                                     alpha, c + static_cast<size_t>(m0) * n + n0, mm, nn, 6 * k, s, n);
+      if (rc != TCAB_OK) return rc;
+    }
   }
-  count_launch();
-  const int rc = check_launch("split3_kernel");
-  if (rc != TCAB_OK) return rc;
-  return launch_contract_bf16_tc(reinterpret_cast<const __nv_bfloat16*>(a3), reinterpret_cast<const __nv_bfloat16*>(b3), b_is_nk,
-                                 alpha, c, m, n, 6 * k, s);
+  return TCAB_OK;
 }
 
 }  // namespace tcab

@@ -314,6 +314,18 @@ def test_large_f32_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     n0 = T.launch_count()
     T.chain_contract(ad, bd, rhs_is_nk=nk, init=1.0)
     assert T.launch_count() - n0 == 1
+    # a workspace too small for all pieces at once: blocks of rows of a against blocks of columns of b, the same bits
+    try:
+        T.tune("gemm", 0, 0, 128, max(8, (2304 * k * 12 >> 20) + 1))     # room for 1024 + 1024 (+ 256) lines
+        out = torch.full((m + 2, n), -7.0, device=cuda)
+        n0 = T.launch_count()
+        T.chain_contract(ad, bd, rhs_is_nk=nk, out=out[1:m + 1])
+        assert T.launch_count() - n0 > 3
+    finally:
+        T.tune("gemm")
+    got = out.cpu().numpy()
+    assert (got[0] == -7.0).all() and (got[-1] == -7.0).all()
+    assert np.array_equal(got[1:-1], tc)
 
 
 # ----------------------------------------------------------------------------
