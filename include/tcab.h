@@ -233,7 +233,7 @@ TCAB_API int tcab_map(const tcab_chain* chain, const tcab_tensor* ins, uint32_t 
  * or a scaling by one constant ("p0 * c0", "0.5f * p0"), K a multiple of 8, N a multiple of 4 (of 8 when rhs is
  * [K,N]) and 16-byte aligned pointers. Products of bf16 values are exact in fp32, so only the order in which an
  * output's k terms are added differs from the scalar kernel. The same chain over two f32 operands ("p0 * p1")
- * takes the tensor cores from 64 output tiles of 256 x 256 on (K >= 256, K a multiple of 4): each operand is cut
+ * takes the tensor cores from m * n * k = 2^29 on (K >= 256, K a multiple of 4): each operand is cut
  * into three bf16 pieces (24 significant bits) in a workspace of 12 bytes per operand element (per device and
  * stream, at most 512 MiB; larger problems run in blocks), and the six significant piece products are one bf16
  * contraction over 6 K; what is dropped is below 3 * 2^-24 of |a b| per product (measured: 3e-7 .. 8e-7 of

@@ -872,11 +872,14 @@ __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
-template <int KS>
+// OUT_F32: c is fp32 (c_f32, rows c_pitch elements apart) and receives alpha * sum, no bias, no activation: the
+// product chains of tcab_chain_contract; B_NK: b is [N, K] (one K-major box of 256 rows per stage).
+template <int KS, bool OUT_F32 = false, bool B_NK = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const float* __restrict__ bias, uint32_t M, uint32_t N, uint32_t K, int act,
-                      uint32_t kb_per_split, float* __restrict__ ws, __nv_bfloat16* __restrict__ c_raw) {
+                      uint32_t kb_per_split, float* __restrict__ ws, __nv_bfloat16* __restrict__ c_raw,
+                      float* __restrict__ c_f32, uint64_t c_pitch, float alpha) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[Ck::STAGES];
   __shared__ __align__(8) uint64_t bar_empty[Ck::STAGES];
@@ -908,7 +911,8 @@ gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (lane == 0) {
       ptx::mbar_expect_tx(full, Ck::STAGE);
       ptx::tma_load_2d(a_dst, &tmap_a, full, k0, a_row);
-    } else if (lane <= BN / 64) {
+      if (B_NK) ptx::tma_load_2d(b_dst, &tmap_b, full, k0, b_col);  // one box: 256 rows of n, 64 of k
+    } else if (!B_NK && lane <= BN / 64) {
       const int j = lane - 1;
       ptx::tma_load_2d(b_dst + j * B_ATOM_BYTES, &tmap_b, full, b_col + j * 64, k0);
     }
@@ -951,7 +955,7 @@ gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/1);
+      constexpr uint32_t idesc = ptx::idesc_bf16_f32(UMMA_M, UMMA_N, /*a_mn=*/0, /*b_mn=*/B_NK ? 0 : 1);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (uint32_t kb = 0; kb < num_kb; ++kb) {
@@ -961,7 +965,8 @@ gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint64_t adesc = ptx::smem_desc_sw128(a_src + k * (UMMA_K * 2), 16, 1024);
-          const uint64_t bdesc = ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
+          const uint64_t bdesc = B_NK ? ptx::smem_desc_sw128(b_src + k * (UMMA_K * 2), 16, 1024)
+                                      : ptx::smem_desc_sw128(b_src + k * (UMMA_K * 128), B_ATOM_BYTES, 1024);
           ptx::mma_bf16(tmem_base, adesc, bdesc, idesc, (kb | static_cast<uint32_t>(k)) != 0u);
         }
         ptx::mma_commit(ptx::smem_u32(&bar_empty[stage]));
@@ -1070,13 +1075,18 @@ gemm_cluster_k_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           for (int r2 = 0; r2 < KS; ++r2) {  // ascending ranges: ascending k, like the one-pass kernel
             f0 += p[i][r2][h].x; f1 += p[i][r2][h].y; f2 += p[i][r2][h].z; f3 += p[i][r2][h].w;
           }
-          f0 += bv[h][0]; f1 += bv[h][1]; f2 += bv[h][2]; f3 += bv[h][3];  // a sum is never -0: a zero bias keeps its bits
-          if (act == TCAB_ACT_RELU) {
-            f0 = fmaxf(f0, 0.0f); f1 = fmaxf(f1, 0.0f); f2 = fmaxf(f2, 0.0f); f3 = fmaxf(f3, 0.0f);
+          if constexpr (OUT_F32) {
+            *reinterpret_cast<float4*>(c_f32 + grow * c_pitch + gcol0 + 128u * h) =
+                make_float4(f0 * alpha, f1 * alpha, f2 * alpha, f3 * alpha);
+          } else {
+            f0 += bv[h][0]; f1 += bv[h][1]; f2 += bv[h][2]; f3 += bv[h][3];  // a sum is never -0: a zero bias keeps its bits
+            if (act == TCAB_ACT_RELU) {
+              f0 = fmaxf(f0, 0.0f); f1 = fmaxf(f1, 0.0f); f2 = fmaxf(f2, 0.0f); f3 = fmaxf(f3, 0.0f);
+            }
+            const __nv_bfloat162 h0 = __floats2bfloat162_rn(f0, f1), h1 = __floats2bfloat162_rn(f2, f3);
+            *reinterpret_cast<uint2*>(c_raw + grow * N + gcol0 + 128u * h) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
           }
-          const __nv_bfloat162 h0 = __floats2bfloat162_rn(f0, f1), h1 = __floats2bfloat162_rn(f2, f3);
-          *reinterpret_cast<uint2*>(c_raw + grow * N + gcol0 + 128u * h) =
-              make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
         }
       }
     }
@@ -1199,8 +1209,24 @@ int gemm_device_status(int* out) {
   return TCAB_OK;
 }
 
-// The cluster K-split kernel for a cluster of ks CTAs (2..8).
-const void* cluster_k_fn(int ks) {
+// The cluster K-split kernel for a cluster of ks CTAs (2..8); the fp32-out forms exist for 2, 4 and 8.
+const void* cluster_k_fn(int ks, int form = 0) {  // form: 0 bf16 out, 1 fp32 out with b [K, N], 2 fp32 out with b [N, K]
+  if (form == 1) {
+    switch (ks) {
+      case 2: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<2, true, false>);
+      case 4: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<4, true, false>);
+      case 8: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<8, true, false>);
+      default: return nullptr;
+    }
+  }
+  if (form == 2) {
+    switch (ks) {
+      case 2: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<2, true, true>);
+      case 4: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<4, true, true>);
+      case 8: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<8, true, true>);
+      default: return nullptr;
+    }
+  }
   switch (ks) {
     case 2: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<2>);
     case 3: return reinterpret_cast<const void*>(gemm_cluster_k_kernel<3>);
@@ -1214,15 +1240,17 @@ const void* cluster_k_fn(int ks) {
 
 // How many clusters of ks CTAs of that kernel the current device holds at once (0 when it cannot say); asked once
 // per device and size. The shared-memory attribute of the device's copy of the function is set on the way.
-int cluster_k_resident(int ks) {
+int cluster_k_resident(int ks, int form = 0) {
   constexpr int kMaxDev = 64;
   static std::mutex mu;
-  static int cache[kMaxDev][9];  // 0 = not asked yet, -1 = none, else the count
+  static int cache_all[3][kMaxDev][9];  // 0 = not asked yet, -1 = none, else the count
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev || ks < 2 || ks > 8) return 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev || ks < 2 || ks > 8 || form < 0 || form > 2) return 0;
+  if (cluster_k_fn(ks, form) == nullptr) return 0;
   std::lock_guard<std::mutex> lock(mu);
+  int (*cache)[9] = cache_all[form];
   if (cache[dev][ks] == 0) {
-    const void* fn = cluster_k_fn(ks);
+    const void* fn = cluster_k_fn(ks, form);
     int n = 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(ks) * 64);
@@ -1316,7 +1344,10 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
       attr[0].val.clusterDim.z = 1;
       cfg.attrs = attr;
       cfg.numAttrs = 1;
-      void* args[] = {&ta2, &tb, &bias, &m, &n, &k, &act, &kb_per, &ws, &c};
+      float* c_f32 = nullptr;
+      uint64_t c_pitch = 0;
+      float alpha = 1.0f;
+      void* args[] = {&ta2, &tb, &bias, &m, &n, &k, &act, &kb_per, &ws, &c, &c_f32, &c_pitch, &alpha};
       const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
       count_launch();
       if (le != cudaSuccess) {
@@ -1459,6 +1490,52 @@ int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int 
                               : cudaMemset2DAsync(c, c_pitch * sizeof(float), 0, static_cast<size_t>(n) * sizeof(float), m, s);
     return e == cudaSuccess ? TCAB_OK : fail(TCAB_ERR_CUDA, "chain_contract: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
   }
+  // Few 256 x 256 tiles and a long K: one cluster per 128 x 256 tile, a K range per CTA (see gemm_cluster_k_kernel)
+  {
+    const uint64_t tiles256 = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const uint64_t tiles128 = static_cast<uint64_t>((m + UMMA_M - 1) / UMMA_M) * ((n + BN - 1) / BN);
+    const uint32_t all_kb = (k + BK - 1) / BK;
+    const int form = b_is_nk ? 2 : 1;
+    if (2 * tiles256 <= static_cast<uint64_t>(sm_count()) && all_kb >= 16 && tune(kGemm).p2 != 32) {
+      uint64_t ks = static_cast<uint64_t>(sm_count()) / tiles128;
+      if (ks > all_kb / 8) ks = all_kb / 8;
+      ks = ks >= 8 ? 8 : ks >= 4 ? 4 : ks >= 2 ? 2 : 0;
+      while (ks >= 2 && static_cast<uint64_t>(cluster_k_resident(static_cast<int>(ks), form)) < tiles128) ks >>= 1;
+      float* ws = ks >= 2 ? gemm_split_workspace(s, static_cast<size_t>(tiles128) * ks * Ck::PLANE_BYTES) : nullptr;
+      if (ks >= 2 && ws != nullptr) {
+        CUtensorMap ta2, tb2;
+        int rc = make_map(&ta2, a, m, k, UMMA_M);
+        if (rc == TCAB_OK) rc = b_is_nk ? make_map(&tb2, b, n, k, BN) : make_map(&tb2, b, k, n, BK);
+        if (rc != TCAB_OK) return rc;
+        const void* fn = cluster_k_fn(static_cast<int>(ks), form);
+        uint32_t kb_per = (all_kb + static_cast<uint32_t>(ks) - 1) / static_cast<uint32_t>(ks);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(tiles128 * ks));
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = Ck::SMEM;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = static_cast<unsigned>(ks);
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        const float* bias = nullptr;
+        int act = TCAB_ACT_NONE;
+        __nv_bfloat16* c_raw = nullptr;
+        uint64_t pitch = c_pitch ? c_pitch : n;
+        void* args[] = {&ta2, &tb2, &bias, &m, &n, &k, &act, &kb_per, &ws, &c_raw, &c, &pitch, &alpha};
+        const cudaError_t le = cudaLaunchKernelExC(&cfg, fn, args);
+        count_launch();
+        if (le != cudaSuccess) {
+          cudaGetLastError();
+          return fail(TCAB_ERR_CUDA, "chain_contract (cluster K split): launch failed: %s", cudaGetErrorString(le));
+        }
+        return TCAB_OK;
+      }
+    }
+  }
   CUtensorMap ta, tb, tcm;
   int rc = make_map(&ta, a, m, k, BM);
   if (rc == TCAB_OK) rc = b_is_nk ? make_map(&tb, b, n, k, BN) : make_map(&tb, b, k, n, BK);
@@ -1542,9 +1619,11 @@ split3_kernel(const float* __restrict__ src, uint64_t pitch, unsigned short* __r
 
 int launch_contract_f32_split3(const float* a, const float* b, int b_is_nk, float alpha, float* c, uint32_t m, uint32_t n,
                                uint32_t k, cudaStream_t s) {
-  // enough 256 x 256 tiles to fill the tensor-core kernel's persistent grid, a K worth three launches, 16-byte rows
-  const uint64_t tiles = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-  if (tiles < 64 || k < 256 || k % 4 != 0 || n % 4 != 0 || (!b_is_nk && n % 8 != 0)) return TCAB_ERR_UNSUPPORTED;
+  // a problem worth three launches (few output tiles then share their K over the CTAs of a cluster), 16-byte rows
+  const Tune& tn0 = tune(kGemm);  // p2 == 256: p3 = log2 of the smallest m * n * k that takes this path (sweeps)
+  const uint64_t min_work = 1ull << (tn0.p2 == 256 && tn0.p3 > 0 ? tn0.p3 : 29);
+  if (static_cast<uint64_t>(m) * n * k < min_work || k < 256 || k % 4 != 0 || n % 4 != 0 || (!b_is_nk && n % 8 != 0))
+    return TCAB_ERR_UNSUPPORTED;
   if (!aligned16(a) || !aligned16(b) || !aligned16(c) || static_cast<uint64_t>(k) * 6 > 0xffffffffull) return TCAB_ERR_UNSUPPORTED;
   // The pieces of a block of mc rows of a and of a block of nc columns (rows, for [N, K]) of b fit the workspace at a
   // time: 12 k bytes per row or column. The whole problem when that is enough; otherwise blocks of multiples of

@@ -246,7 +246,8 @@ def test_contraction_over_bf16_operands(cuda, m, k, n, nk):
 
 
 @pytest.mark.parametrize("m,k,n,nk", [(300, 264, 520, False), (300, 264, 516, True), (1, 8, 8, False), (129, 4096, 264, True),
-                                      (513, 72, 1032, False), (2048, 2048, 2048, False), (700, 1024, 260, True)])
+                                      (513, 72, 1032, False), (2048, 2048, 2048, False), (700, 1024, 260, True),
+                                      (100, 8192, 520, False), (260, 2048, 1028, True), (128, 1024, 256, False)])
 def test_bf16_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     # map = the plain product of two bf16 operands, sum reducer, init 0, stored as it is or scaled: the library takes
     # the tcgen05 kernel with fp32 accumulation and an fp32 store (one launch). Products of bf16 values are exact in
@@ -279,7 +280,8 @@ def test_bf16_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     assert (np.abs(got - (want + k)) <= 1e-5 * (mag + k) + 1e-30).all()
 
 
-@pytest.mark.parametrize("m,k,n,nk", [(2048, 512, 2048, False), (2048, 260, 2056, True), (4100, 256, 1032, False)])
+@pytest.mark.parametrize("m,k,n,nk", [(2048, 512, 2048, False), (2048, 260, 2056, True), (4100, 256, 1032, False),
+                                      (1024, 1024, 1024, False), (520, 2048, 1028, True)])
 def test_large_f32_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     # fp32 operands, the plain product, a sum from 0: from 64 output tiles of 256 x 256 on, each operand is cut into
     # three bf16 pieces and the six significant piece products run as one bf16 contraction over 6 K (three launches).
@@ -314,18 +316,19 @@ def test_large_f32_product_chains_run_on_the_tensor_cores(cuda, m, k, n, nk):
     n0 = T.launch_count()
     T.chain_contract(ad, bd, rhs_is_nk=nk, init=1.0)
     assert T.launch_count() - n0 == 1
-    # a workspace too small for all pieces at once: blocks of rows of a against blocks of columns of b, the same bits
+    # a workspace too small for all pieces at once: blocks of rows of a against blocks of columns of b (the K ranges
+    # of a block product may be cut differently over CTAs: the same sums in another order)
     try:
         T.tune("gemm", 0, 0, 128, max(8, (2304 * k * 12 >> 20) + 1))     # room for 1024 + 1024 (+ 256) lines
         out = torch.full((m + 2, n), -7.0, device=cuda)
         n0 = T.launch_count()
         T.chain_contract(ad, bd, rhs_is_nk=nk, out=out[1:m + 1])
-        assert T.launch_count() - n0 > 3
+        assert T.launch_count() - n0 > 3 or m + n <= 2304
     finally:
         T.tune("gemm")
     got = out.cpu().numpy()
     assert (got[0] == -7.0).all() and (got[-1] == -7.0).all()
-    assert np.array_equal(got[1:-1], tc)
+    assert (np.abs(got[1:-1] - tc) <= 1e-6 * mag).all()
 
 
 # ----------------------------------------------------------------------------
