@@ -362,6 +362,14 @@ class ReduceOuter(Workload):
         return d
 
 
+class ReduceOuterNarrow(ReduceOuter):
+    """Narrow rows (16 columns): a warp per (b, column tile) instead of a CTA; selectable only."""
+    name = "reduce_outer_f32_65536x256x16"
+    full_units, nk, nc = 65536, 256, 16
+    shape = "t fp32 [65536, 256, 16] ~ U(-100,100) -> sum f32, max f32, argmax i32 [65536, 16] in one pass"
+    profile = "reduce_outer_flat_reduce_outer_f32_65536x256x16.md"
+
+
 class MapRowsum(Workload):
     name = "map_rowsum_f32_4096x1024"
     dtype = "f32"
@@ -546,7 +554,7 @@ class MapOnly(Workload):
 
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
 SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows,
-                                LayernormHeadRows.name: LayernormHeadRows})
+                                LayernormHeadRows.name: LayernormHeadRows, ReduceOuterNarrow.name: ReduceOuterNarrow})
 DEFAULT = SoftmaxRows.name
 
 
