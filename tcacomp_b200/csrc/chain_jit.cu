@@ -328,7 +328,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
       return launch(jc->k[nvec <= 32 ? kInnerFlat : kInnerFlat2], (outer + rows_per_cta - 1) / rows_per_cta,
                     256, af, s, "chain_inner_flat");
     }
-    const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec < 1024 ? 2 : 3;  // the same thresholds as the ahead-of-time path
+    const int t = nvec <= 16 ? 0 : nvec <= 64 ? 1 : nvec < (vec ? inner_cta_per_row_from(jc->n_in) : 1024u) ? 2 : 3;  // the same thresholds as the ahead-of-time path
     const int tpr = t == 0 ? 1 : t == 1 ? 4 : t == 2 ? 32 : 256;
     const bool big = vec && t == 2 && inner_wants_big_ctas(outer);        // small problems: 1024-thread CTAs
     const int threads = big ? 1024 : tpr > 128 ? tpr : 128;

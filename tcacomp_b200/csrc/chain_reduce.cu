@@ -295,8 +295,10 @@ int launch_chain(const Args& a) {
     if (vec && nvec >= 1 && (nvec <= 32 || (nvec > 48 && nvec <= 64)) && a.outer >= 1024 && tune(kReduceInner).p0 <= 0)
       return launch_inner_flat<Map, Post, COMBINE>(a, nvec);
     // short rows: one thread folds a row sequentially, which is the reference's SeqReducer order exactly
-    // measured: a warp per row up to 1023 vectors, a CTA per row from 1024 (8192 columns: 4.6 -> 7.1 TB/s)
-    int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec < 1024 ? 32 : 256;
+    // measured: a warp per row for mid-length rows, a CTA per row for long ones (8192 columns: 4.6 -> 7.1 TB/s)
+    // (a CTA per row from 640 vectors, from 384 with two or more operands: 3072 columns 6.4 -> 7.1 TB/s, 4092 5.1 -> 6.8,
+    //  two operands at 1536 columns 6.9 -> 7.4)
+    int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec < (vec ? inner_cta_per_row_from(NIN) : 1024u) ? 32 : 256;
     const Tune& tn = tune(kReduceInner);
     if (tn.p0 == 1 || tn.p0 == 4 || tn.p0 == 32 || tn.p0 == 256) tpr = tn.p0;
     if (vec) {

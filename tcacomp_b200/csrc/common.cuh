@@ -140,6 +140,9 @@ inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm)
   return nk < 64 ? g : 0;
 }
 
+// Innermost-axis chains: the row length (in vectors) from which a CTA of 256 threads takes a row instead of a warp.
+inline uint32_t inner_cta_per_row_from(int n_in) { return n_in >= 2 ? 384u : 640u; }
+
 // chain_inner_rows32: warps per CTA for rows of nvec vectors and n_in operands such that the CTA's shared memory
 // stays within the 48 KiB that need no opt-in; 0 when not even one warp fits.
 inline uint32_t rows32_warps(uint32_t nvec, int n_in) {
