@@ -17,37 +17,66 @@ from . import _lib
 _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int32: _lib.I32, torch.uint32: _lib.U32}
 
 
-def _view(t: torch.Tensor, name: str) -> _lib.Tensor:
+_TWO32 = 2 ** 32
+
+
+def _name(name) -> str:
+    return name if isinstance(name, str) else f"ins[{name}]"
+
+
+def _view(t: torch.Tensor, name) -> _lib.Tensor:
+    """The C view of a tensor. `name` is used in error messages only: a string, or the operand's index."""
     if not isinstance(t, torch.Tensor):
-        raise TypeError(f"{name} must be a torch.Tensor")
+        raise TypeError(f"{_name(name)} must be a torch.Tensor")
+    shape = t.shape
+    rank = len(shape)
     # the C struct holds 32-bit extents and ctypes would truncate silently: refuse here what the library
-    # refuses with TCAB_ERR_TOO_LARGE (the reference indexes with u32)
-    if t.numel() >= 2**32 or any(d >= 2**32 for d in t.shape):
-        raise ValueError(f"{name}: 2^32 or more elements ({tuple(t.shape)}); extents and element counts are 32-bit")
-    if t.device.type != "cuda":
-        raise ValueError(f"{name} must live on a CUDA device (this library has no CPU path)")
+    # refuses with TCAB_ERR_TOO_LARGE (the reference indexes with u32); an element count below 2^32 bounds
+    # every extent of a non-empty tensor
+    if t.numel() >= _TWO32 or (rank and max(shape) >= _TWO32):
+        raise ValueError(f"{_name(name)}: 2^32 or more elements ({tuple(shape)}); extents and element counts are 32-bit")
+    if not t.is_cuda:
+        raise ValueError(f"{_name(name)} must live on a CUDA device (this library has no CPU path)")
     if not t.is_contiguous():
-        raise ValueError(f"{name} must be contiguous (row-major), as the reference's tensors are")
-    if t.dtype not in _DTYPES:
-        raise TypeError(f"{name}: unsupported dtype {t.dtype}")
-    if t.dim() < 1 or t.dim() > _lib.MAX_RANK:
-        raise ValueError(f"{name}: rank {t.dim()} outside 1..{_lib.MAX_RANK}")
+        raise ValueError(f"{_name(name)} must be contiguous (row-major), as the reference's tensors are")
+    code = _DTYPES.get(t.dtype)
+    if code is None:
+        raise TypeError(f"{_name(name)}: unsupported dtype {t.dtype}")
+    if rank < 1 or rank > _lib.MAX_RANK:
+        raise ValueError(f"{_name(name)}: rank {rank} outside 1..{_lib.MAX_RANK}")
     v = _lib.Tensor()
     v.data = t.data_ptr()
-    v.dtype = _DTYPES[t.dtype]
-    v.rank = t.dim()
-    for i, d in enumerate(t.shape):
-        v.dims[i] = d
+    v.dtype = code
+    v.rank = rank
+    v.dims[:rank] = shape
     return v
 
 
 def _stream(stream: Optional[torch.cuda.Stream], ref: torch.Tensor) -> C.c_void_p:
-    s = stream if stream is not None else torch.cuda.current_stream(ref.device)
-    return C.c_void_p(s.cuda_stream)
+    if stream is not None:
+        return C.c_void_p(stream.cuda_stream)
+    # the raw handle of torch's current stream on the operand's device (what torch.cuda.current_stream wraps)
+    return C.c_void_p(torch._C._cuda_getCurrentRawStream(ref.device.index))
+
+
+class _AlreadyCurrent:
+    """Stands in for torch.cuda.device when the operand's device is the current one already (the usual case)."""
+
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_ALREADY_CURRENT = _AlreadyCurrent()
 
 
 def _on_device(t: torch.Tensor):
-    return torch.cuda.device(t.device)
+    dev = t.device
+    if dev.index == torch.cuda.current_device():
+        return _ALREADY_CURRENT
+    return torch.cuda.device(dev)
 
 
 def _same_device(*named) -> None:
@@ -58,14 +87,35 @@ def _same_device(*named) -> None:
             raise ValueError(f"{name} is on {t.device} but {first_name} is on {first.device}")
 
 
+def _operands_on_one_device(ins, out) -> None:
+    """_same_device for a list of operands and an output, without building names unless something is wrong."""
+    dev = ins[0].device
+    if out.device == dev and all(t.device == dev for t in ins):
+        return
+    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
+
+
+_ENCODED: dict = {}
+
+
+def _encoded(text: str) -> bytes:
+    """The lambda text as bytes; a program uses a handful of lambdas, many times each."""
+    b = _ENCODED.get(text)
+    if b is None:
+        if len(_ENCODED) > 4096:
+            _ENCODED.clear()
+        b = _ENCODED[text] = text.encode()
+    return b
+
+
 def _chain(map_expr: str, combine_expr: str, post_expr: Optional[str], init: float,
            captures: Sequence[float]) -> _lib.Chain:
     if len(captures) > _lib.MAX_CAPTURES:
         raise ValueError(f"at most {_lib.MAX_CAPTURES} captures")
     chain = _lib.Chain()
-    chain.map_expr = map_expr.encode()
-    chain.combine_expr = combine_expr.encode()
-    chain.post_expr = post_expr.encode() if post_expr else None
+    chain.map_expr = _encoded(map_expr)
+    chain.combine_expr = _encoded(combine_expr)
+    chain.post_expr = _encoded(post_expr) if post_expr else None
     chain.init = init
     chain.n_captures = len(captures)
     for i, c in enumerate(captures):
@@ -193,9 +243,9 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
         shape = [d for i, d in enumerate(full) if i != ax] or [1]
         out = torch.empty(shape, device=t0.device, dtype=torch.float32)
     chain = _chain(map_expr, combine_expr, post_expr, init, captures)
-    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    arr = (_lib.Tensor * len(ins))(*[_view(t, i) for i, t in enumerate(ins)])
     ov = _view(out, "out")
-    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
+    _operands_on_one_device(ins, out)
     with _on_device(t0):
         _lib.check(_lib.load().tcab_chain_reduce(C.byref(chain), arr, len(ins), ax, C.byref(ov),
                                                  _stream(stream, t0)))
@@ -218,9 +268,9 @@ def map(ins: Sequence[torch.Tensor], map_expr: str, captures: Sequence[float] = 
         full = [max(t.shape[i] for t in ins if t.dim() == ins[0].dim()) for i in range(ins[0].dim())]
         out = torch.empty(full, device=ins[0].device, dtype=out_dtype or ins[0].dtype)
     chain = _chain(map_expr, "(p0 + p1)", None, 0.0, captures)
-    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    arr = (_lib.Tensor * len(ins))(*[_view(t, i) for i, t in enumerate(ins)])
     ov = _view(out, "out")
-    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
+    _operands_on_one_device(ins, out)
     with _on_device(ins[0]):
         _lib.check(_lib.load().tcab_map(C.byref(chain), arr, len(ins), C.byref(ov), _stream(stream, ins[0])))
     return out
@@ -269,9 +319,9 @@ def chain_reduce_noalloc(ins: Sequence[torch.Tensor], map_expr: str, out: torch.
     if not 1 <= len(ins) <= _lib.MAX_INPUTS:
         raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
     chain = _chain(map_expr, combine_expr, post_expr, init, captures)
-    arr = (_lib.Tensor * len(ins))(*[_view(t, f"ins[{i}]") for i, t in enumerate(ins)])
+    arr = (_lib.Tensor * len(ins))(*[_view(t, i) for i, t in enumerate(ins)])
     ov = _view(out, "out")
-    _same_device(*[(f"ins[{i}]", t) for i, t in enumerate(ins)], ("out", out))
+    _operands_on_one_device(ins, out)
     with _on_device(ins[0]):
         _lib.check(_lib.load().tcab_chain_reduce_noalloc(C.byref(chain), arr, len(ins), C.byref(ov),
                                                          _stream(stream, ins[0])))
