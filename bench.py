@@ -552,9 +552,52 @@ class MapOnly(Workload):
         return {"checked": int(got.size), "failed": 0, "max_ulp": int(d.max()), "via_fp64_term": 0}
 
 
+class ShortRowsum(Workload):
+    """Rows of 64 columns (16 vectors): a thread per row in ascending order over a coalesced copy; selectable only."""
+    name = "map_rowsum_f32_4194304x64"
+    dtype = "f32"
+    full_units, cols = 4194304, 64
+    shape = "x fp32 [4194304, 64] ~ U(-1,1) -> y[i] = sum_j (0.5*x+0.25)^2 fp32 [4194304]"
+    EXPR = MapRowsum.EXPR
+    profile = "chain_inner_rows32_map_rowsum_f32_4194304x64.md"
+
+    def work(self):
+        return self.units * self.cols * 4.0 + self.units * 4
+
+    def make(self, dev, seed):
+        import tcacomp_b200 as T
+        self.T = T
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.x = torch.rand((self.units, self.cols), generator=g, device=dev) * 2 - 1
+        self.y = torch.empty((self.units,), device=dev)
+
+    def step(self):
+        self.T.chain_reduce([self.x], self.EXPR, axis=1, out=self.y)
+
+    def pipeline_spec(self, chunk_units):
+        from tcacomp_b200.pipeline import PipelineSpec
+        return PipelineSpec("chain_reduce", self.x.device, chunk_units, (self.cols,), torch.float32, map_expr=self.EXPR)
+
+    def host_buffers(self):
+        hx = self.x.cpu().pin_memory()
+        return [hx], [torch.empty((self.units,), dtype=torch.float32).pin_memory()]
+
+    def cpu_sample(self, oracle):
+        x = self.x[:min(1 << 20, self.units)].cpu().numpy()
+        return (lambda: oracle.map_rowsum_affine_sq(x, 0.5, 0.25)), x.size * 4.0 + x.shape[0] * 4, f"first {x.shape[0]} of {self.units} rows per pass"
+
+    def check(self, oracle, full):
+        from oracle import checks
+        rows = self.units if full else min(self.units, 65536)
+        rep = checks.rowsum_report(self.y[:rows].cpu().numpy(), self.x[:rows].cpu().numpy())
+        assert rep.ok, f"row-sum parity check failed: {rep}"
+        return rep.as_dict()
+
+
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
 SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows,
-                                LayernormHeadRows.name: LayernormHeadRows, ReduceOuterNarrow.name: ReduceOuterNarrow})
+                                LayernormHeadRows.name: LayernormHeadRows, ReduceOuterNarrow.name: ReduceOuterNarrow,
+                                ShortRowsum.name: ShortRowsum})
 DEFAULT = SoftmaxRows.name
 
 
