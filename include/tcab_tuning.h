@@ -61,6 +61,14 @@ TCAB_API int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32
                                    uint32_t per_step, int prefer_three, int n_in, uint32_t* outer_flat_g,
                                    uint32_t* stream_cluster, uint32_t* rows32);
 
+/* The warp-per-(b, column tile) kernels of a middle-axis reduction over [batches, nk, nc] (pure arithmetic): the column
+ * groups per tile (0 = those kernels are not used), and into how many ranges of klen rows the k axis is cut when
+ * there are few narrow tiles and a long reduced axis (column statistics of a tall matrix). A CTA of eight warps takes
+ * a range and leaves one partial result per output cell. Range r covers [r * klen, min(nk, (r + 1) * klen)), none
+ * is empty, and batches * nc * ranges stays within max_partials. */
+TCAB_API int tcab_plan_outer_flat_ranges(uint64_t batches, uint32_t nk, uint32_t nc, int sms, uint64_t max_partials,
+                                         uint32_t* groups, uint32_t* ranges, uint32_t* klen);
+
 /* Validates a chain exactly as tcab_chain_prepare does and runs the run-time compiler on it for sm_100a, but
  * loads nothing: works on a host without a GPU (needs libnvrtc). A chain that has an ahead-of-time kernel is
  * compiled all the same. Arguments as tcab_chain_prepare, plus the bit masks of the operands that have one

@@ -357,6 +357,18 @@ int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32_t nc, in
   return TCAB_OK;
 }
 
+int tcab_plan_outer_flat_ranges(uint64_t batches, uint32_t nk, uint32_t nc, int sms, uint64_t max_partials,
+                                uint32_t* groups, uint32_t* ranges, uint32_t* klen) {
+  if (groups == nullptr || ranges == nullptr || klen == nullptr)
+    return fail(TCAB_ERR_INVALID_ARG, "plan_outer_flat_ranges: null output");
+  if (sms < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_flat_ranges: sms must be positive");
+  *groups = outer_flat_groups(batches, nk, nc, sms);
+  *ranges = 1;
+  *klen = nk;
+  if (*groups != 0) *ranges = outer_flat_ranges(batches, nk, nc, *groups, sms, max_partials, klen);
+  return TCAB_OK;
+}
+
 int tcab_softmax_rows(const tcab_tensor* x, const tcab_tensor* y, void* stream) {
   const char* op = "softmax_rows";
   TCAB_TRY(check_tensor(op, "x", x));

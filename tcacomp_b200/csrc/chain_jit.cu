@@ -284,6 +284,14 @@ int jit_compile_check(const JitSpec& sp) {
 }
 
 // Mirrors the ahead-of-time dispatch of chain_reduce.cu (launch_chain / launch_split / launch_outer).
+// The second launch of a split reduction (several threads per output when it has many partials: finish_lanes).
+static int launch_jit_finish(JitChain* jc, float* scratch, float* out, uint32_t rows, uint32_t splits, float init,
+                             tcabk::Caps caps, cudaStream_t s) {
+  uint32_t lanes = finish_lanes(splits);
+  void* a2[] = {&scratch, &out, &rows, &splits, &init, &caps, &lanes};
+  return launch(jc->k[kFinish], (static_cast<uint64_t>(rows) * lanes + 127) / 128, 128, a2, s, "chain_split_finish");
+}
+
 int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t nk, uint64_t inner, float init,
                const float* caps16, float* out, float* split_scratch_or_null, uint32_t splits, cudaStream_t s) {
   // splits: CTAs per row for the split path (1 = none); top bit set = take the split path even with 1
@@ -307,9 +315,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
       void* a1[] = {ptrs, &split_scratch_or_null, &nk, &sp, &vec_per_split, &caps};
       int rc = launch(jc->k[vec ? kSplitV4 : kSplitV1], static_cast<uint64_t>(rows) * sp, 256, a1, s, "chain_inner_split");
       if (rc != TCAB_OK) return rc;
-      uint32_t rows32 = rows;
-      void* a2[] = {&split_scratch_or_null, &out, &rows32, &sp, &init, &caps};
-      return launch(jc->k[kFinish], (rows + 127) / 128, 128, a2, s, "chain_split_finish");
+      return launch_jit_finish(jc, split_scratch_or_null, out, rows, sp, init, caps, s);
     }
     if (vec && nvec >= 2 && nvec <= 16 && outer >= 1024 && jc->k[kInnerRows32] != nullptr && tune(kReduceInner).p0 <= 0 &&
         rows32_warps(nvec, jc->n_in) >= 2) {  // a thread per row over a coalesced copy (same policy as ahead of time)
@@ -351,8 +357,14 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
     if (g != 0) {
       uint32_t tpb = (nc + 127) / 128;
       const uint64_t work = static_cast<uint64_t>(nb) * tpb;
-      void* af[] = {ptrs, &out, &nb, &nk, &nc, &tpb, const_cast<uint32_t*>(&g), &init, &caps};
-      return launch(jc->k[kOuterFlat], (work + 7) / 8, 256, af, s, "chain_outer_flat");
+      uint32_t klen = nk;
+      uint32_t ksplit = split_scratch_or_null == nullptr ? 1u : outer_flat_ranges(nb, nk, nc, g, sm_count(), 262144, &klen);
+      if (ksplit == 1) klen = nk;
+      void* af[] = {ptrs, &out, &nb, &nk, &nc, &tpb, const_cast<uint32_t*>(&g), &init, &caps, &ksplit, &klen, &split_scratch_or_null};
+      // a CTA per range, or eight tiles per CTA
+      int rc = launch(jc->k[kOuterFlat], ksplit > 1 ? work * ksplit : (work + 7) / 8, 256, af, s, "chain_outer_flat");
+      if (rc != TCAB_OK || ksplit == 1) return rc;
+      return launch_jit_finish(jc, split_scratch_or_null, out, nb * nc, ksplit, init, caps, s);
     }
   }
   // few column tiles and a long k: the k axis is split over CTAs too (same policy as the ahead-of-time path)
@@ -367,9 +379,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   void* a[] = {ptrs, &out, &nb, &nk, &nc, &tiles_per_b, &init, &caps, &ksplit, &klen, &split_scratch_or_null};
   int rc = launch(kern, tiles * ksplit, 256, a, s, "chain_outer");
   if (rc != TCAB_OK || ksplit == 1) return rc;
-  uint32_t rows32 = nb * nc;
-  void* a2[] = {&split_scratch_or_null, &out, &rows32, &ksplit, &init, &caps};
-  return launch(jc->k[kFinish], (rows32 + 127) / 128, 128, a2, s, "chain_split_finish");
+  return launch_jit_finish(jc, split_scratch_or_null, out, nb * nc, ksplit, init, caps, s);
 }
 
 int jit_launch_batched(void* handle, const float* const* ins, float* const* outs, uint32_t nprob, uint32_t rows, uint32_t nk,

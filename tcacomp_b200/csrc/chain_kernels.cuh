@@ -484,17 +484,29 @@ chain_inner_split(Ptrs<NIN> ins, float* __restrict__ partials, u32 nk, u32 split
   }
 }
 
+// `lanes` (a power of two up to 32) threads share a row's partials: 1 folds them in ascending order starting from init;
+// more (many partials of few rows: the k ranges of a middle-axis reduction) take every lanes-th partial each and meet
+// by shuffles, init joining last.
 template <class Post, int COMBINE>
 __global__ void __launch_bounds__(128)
 chain_split_finish(const float* __restrict__ partials, float* __restrict__ out, u32 rows, u32 splits, float init,
-                   Caps caps) {
+                   Caps caps, u32 lanes) {
   typedef Comb<COMBINE> C;
-  const u32 row = blockIdx.x * 128 + threadIdx.x;
-  if (row >= rows) return;
-  float a = init;
-  for (u32 s = 0; s < splits; ++s) a = C::apply(a, partials[static_cast<u64>(row) * splits + s]);
-  float r[1] = {a};
-  out[row] = Post::apply(r, caps.c + 8);
+  const u32 t = blockIdx.x * 128 + threadIdx.x;
+  const u32 row = t / lanes, l = t % lanes;
+  float a = lanes == 1 ? init : C::identity();
+  if (row < rows) {
+#pragma unroll 4
+    for (u32 s = l; s < splits; s += lanes) a = C::apply(a, partials[static_cast<u64>(row) * splits + s]);
+  }
+  if (lanes > 1) {
+    for (u32 off = lanes >> 1; off > 0; off >>= 1) a = C::apply(a, __shfl_xor_sync(0xffffffffu, a, off));
+    a = C::apply(init, a);
+  }
+  if (row < rows && l == 0) {
+    float r[1] = {a};
+    out[row] = Post::apply(r, caps.c + 8);
+  }
 }
 
 // Reduce over a MIDDLE axis: operands are [nb, nk, nc]; a CTA owns (one b, a
@@ -582,11 +594,26 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0, int CELL = 0>
 __global__ void __launch_bounds__(256)
 chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, u32 g, float init,
-                 Caps caps) {
+                 Caps caps, u32 ksplit, u32 klen, float* __restrict__ partials) {
+  // ksplit > 1 (few tiles, a long reduced axis): a CTA takes range blockIdx % ksplit of klen rows of ONE (b, column
+  // tile); its eight warps interleave step by step, so that the CTA streams one contiguous piece of memory, and it
+  // writes the fold of its rows -- without init and without the piped map -- to partials[cell * ksplit + range] for
+  // chain_split_finish.
   typedef Comb<COMBINE> C;
-  const u32 lane = threadIdx.x & 31;
-  const u64 work = static_cast<u64>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (work >= static_cast<u64>(nb) * tiles_per_b) return;  // the whole warp leaves
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  u64 work;
+  u32 kbeg = 0, kend = nk, kstep = (32 / g) * UNROLL, ks = 0;
+  if (ksplit > 1) {
+    work = blockIdx.x / ksplit;
+    ks = blockIdx.x % ksplit;
+    kend = nk - ks * klen < klen ? nk : (ks + 1) * klen;
+    kbeg = ks * klen + warp * kstep;
+    if (kbeg > kend) kbeg = kend;
+    kstep *= 8;
+  } else {
+    work = static_cast<u64>(blockIdx.x) * 8 + warp;
+    if (work >= static_cast<u64>(nb) * tiles_per_b) return;  // the whole warp leaves
+  }
   const u32 b = static_cast<u32>(work / tiles_per_b), tile = static_cast<u32>(work % tiles_per_b);
   const u32 rows_per_step = 32 / g;
   const u32 cg = lane % g, kr = lane / g;  // this lane's column group, and its row inside a step
@@ -601,17 +628,17 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
   if (colok) {
     float cellval[NIN][4];  // operands that lack the reduced axis: one value per output cell, loaded once
     LoadOuterAll<4, BF, CELL, NIN>::cells(ins.p, (static_cast<u64>(b) * nc + col) / 4, cellval);
-    for (u32 k0 = kr; k0 < nk; k0 += rows_per_step * UNROLL) {
+    for (u32 k0 = kbeg + kr; k0 < kend; k0 += kstep) {
       float f[UNROLL][NIN][4];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const u32 k = k0 + u * rows_per_step;
-        if (k < nk) LoadOuterAll<4, BF, CELL, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, cellval, f[u]);
+        if (k < kend) LoadOuterAll<4, BF, CELL, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, cellval, f[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const u32 k = k0 + u * rows_per_step;
-        if (k < nk) {
+        if (k < kend) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float p[NIN];
@@ -626,6 +653,22 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
   for (u32 off = 16; off >= g; off >>= 1) {  // lanes that differ in the row bits hold the same column group
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[j] = C::apply(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+  }
+  if (ksplit > 1) {  // the CTA's warps meet in shared memory, in warp order: one partial per range and cell
+    __shared__ float s_part[8][128];
+    if (lane < g) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s_part[warp][cg * 4 + j] = acc[j];
+    }
+    __syncthreads();
+    const u32 c = threadIdx.x, tile_col = tile * 128 + c;
+    if (c < 4 * g && tile_col < nc) {
+      float a = s_part[0][c];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) a = C::apply(a, s_part[w][c]);
+      partials[(static_cast<u64>(b) * nc + tile_col) * ksplit + ks] = a;
+    }
+    return;
   }
   if (lane < g && colok) {
     const u64 cell = static_cast<u64>(b) * nc + col;

@@ -185,6 +185,19 @@ int launch_inner_flat(const Args& a, uint32_t nvec) {
   return launch_inner_flat_vpl<Map, Post, COMBINE, 2>(a, nvec);
 }
 
+// The second launch of a split reduction: folds `splits` partials per output, several threads per output when there
+// are many (finish_lanes).
+template <class Post, int COMBINE>
+int launch_finish(const float* scratch, float* out, uint32_t rows, uint32_t splits, float init, const Caps& caps,
+                  cudaStream_t stream) {
+  const uint32_t lanes = finish_lanes(splits);
+  const uint64_t threads = static_cast<uint64_t>(rows) * lanes;
+  tcabk::chain_split_finish<Post, COMBINE>
+      <<<static_cast<unsigned>((threads + 127) / 128), 128, 0, stream>>>(scratch, out, rows, splits, init, caps, lanes);
+  count_launch();
+  return check_launch("chain_split_finish");
+}
+
 template <class Map, class Post, int COMBINE>
 int launch_outer_flat(const Args& a, uint32_t g) {
   constexpr int NIN = Map::kIn;
@@ -195,10 +208,20 @@ int launch_outer_flat(const Args& a, uint32_t g) {
   const uint32_t tiles_per_b = (nc + 127) / 128;
   const uint64_t work = a.outer * tiles_per_b;
   if (work > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
-  fn<<<static_cast<unsigned>((work + 7) / 8), 256, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc,
-                                                                  tiles_per_b, g, a.init, a.caps);
+  uint32_t klen = a.nk;
+  uint32_t ksplit = outer_flat_ranges(a.outer, a.nk, nc, g, sm_count(), kMaxSplitPartials, &klen);
+  float* scratch = ksplit > 1 ? split_scratch(a.stream) : nullptr;
+  if (scratch == nullptr) {
+    ksplit = 1;
+    klen = a.nk;
+  }
+  const uint64_t grid = ksplit > 1 ? work * ksplit : (work + 7) / 8;  // a CTA per range, or eight tiles per CTA
+  fn<<<static_cast<unsigned>(grid), 256, 0, a.stream>>>(ptrs, a.out, static_cast<uint32_t>(a.outer), a.nk, nc, tiles_per_b, g,
+                                                        a.init, a.caps, ksplit, klen, scratch);
   count_launch();
-  return check_launch("chain_outer_flat");
+  int rc = check_launch("chain_outer_flat");
+  if (rc != TCAB_OK || ksplit == 1) return rc;
+  return launch_finish<Post, COMBINE>(scratch, a.out, static_cast<uint32_t>(a.outer * nc), ksplit, a.init, a.caps, a.stream);
 }
 
 template <class Map, class Post, int COMBINE, int V>
@@ -227,11 +250,7 @@ int launch_outer(const Args& a) {
   count_launch();
   int rc = check_launch("chain_outer");
   if (rc != TCAB_OK || ksplit == 1) return rc;
-  const uint32_t rows = static_cast<uint32_t>(cells);
-  tcabk::chain_split_finish<Post, COMBINE>
-      <<<(rows + 127) / 128, 128, 0, a.stream>>>(scratch, a.out, rows, ksplit, a.init, a.caps);
-  count_launch();
-  return check_launch("chain_split_finish");
+  return launch_finish<Post, COMBINE>(scratch, a.out, static_cast<uint32_t>(cells), ksplit, a.init, a.caps, a.stream);
 }
 
 // How many CTAs share one row: 1 = no split. A split pays off when there are fewer rows than SMs and
@@ -265,10 +284,7 @@ int launch_split(const Args& a, float* scratch, uint32_t nvec, uint32_t splits) 
   count_launch();
   int rc = check_launch("chain_inner_split");
   if (rc != TCAB_OK) return rc;
-  tcabk::chain_split_finish<Post, COMBINE>
-      <<<(rows + 127) / 128, 128, 0, a.stream>>>(scratch, a.out, rows, splits, a.init, a.caps);
-  count_launch();
-  return check_launch("chain_split_finish");
+  return launch_finish<Post, COMBINE>(scratch, a.out, rows, splits, a.init, a.caps, a.stream);
 }
 
 template <class Map, class Post, int COMBINE>

@@ -132,12 +132,45 @@ inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm)
   if (nc < 128 && (g & (g - 1)) != 0) return 0;       // 4, 8, 16, 32, 64 columns: the whole row is one tile
   if (nc > 64 && nc < 128) return 0;
   const uint64_t work = nb * ((nc + 127) / 128);  // warps
-  if (work < 4ull * static_cast<uint64_t>(sm) && nk > 4096) return 0;  // few long columns: chain_outer cuts k over CTAs
+  // few long narrow columns (column statistics of a tall matrix): CTAs of these warps share the k axis, see
+  // outer_flat_ranges; from 128 columns on a CTA per tile already uses every lane
+  if (work < 8ull * static_cast<uint64_t>(sm) && nk >= 1024) return nc <= 64 ? g : 0;
   if (nc <= 32) return g;
   // 64 columns use half the lanes of a CTA's tile: the warps win only when there are enough of them to keep an
   // SM's memory pipeline full (measured [1024, 4096, 64]: 6.6 TB/s with a CTA per tile, 3.4 with 1024 warps)
   if (nc == 64 && work >= 32ull * static_cast<uint64_t>(sm)) return g;
   return nk < 64 ? g : 0;
+}
+
+// The warp-per-tile kernels on few tiles and a long reduced axis: into how many ranges the k axis of one (b, column
+// tile) is cut, a CTA of eight warps each -- eight CTAs per SM in total, every warp with at least 16 steps, within
+// `max_partials` partial cells (one per range and output cell) -- and how many k rows a range has. 1 = no split.
+// (Column statistics of a tall matrix, measured with CTAs of 128-column tiles sharing k: [1, 2^23, 16], where 16 of
+// the 128 columns exist, 1.2 - 1.8 TB/s; [1, 2^25, 4]: 0.3 - 0.5.)
+inline uint32_t outer_flat_ranges(uint64_t nb, uint32_t nk, uint32_t nc, uint32_t g, int sm, uint64_t max_partials,
+                                  uint32_t* klen) {
+  const uint64_t work = nb * ((nc + 127) / 128), cells = nb * nc;
+  const uint64_t target = 8ull * static_cast<uint64_t>(sm);
+  uint64_t ranges = 1;
+  if (work < target && cells > 0 && cells * 2 <= max_partials) {
+    ranges = (target + work - 1) / work;
+    const uint64_t rows_per_step = 32 / g, by_len = nk / (rows_per_step * 8 * 16);
+    if (ranges > by_len) ranges = by_len;
+    if (ranges > max_partials / cells) ranges = max_partials / cells;
+    if (ranges < 2) ranges = 1;
+  }
+  uint32_t len = static_cast<uint32_t>((nk + ranges - 1) / ranges);
+  ranges = (nk + len - 1) / len;  // no empty range
+  *klen = len;
+  return static_cast<uint32_t>(ranges);
+}
+
+// Threads that share the partials of one output of a split reduction in its finishing launch: a power of two that
+// leaves each at most 16 of them.
+inline uint32_t finish_lanes(uint32_t partials_per_out) {
+  uint32_t lanes = 1;
+  while (lanes < 32 && partials_per_out > 16 * lanes) lanes *= 2;
+  return lanes;
 }
 
 // Innermost-axis chains: the row length (in vectors) from which a CTA of 256 threads takes a row instead of a warp.

@@ -162,10 +162,25 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
 template <int UNROLL>
 __global__ void __launch_bounds__(256)
 reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* __restrict__ mx, int32_t* __restrict__ amax,
-                  uint32_t nb, uint32_t nk, uint32_t nc, uint32_t tiles_per_b, uint32_t g) {
-  const uint32_t lane = threadIdx.x & 31;
-  const uint64_t work = static_cast<uint64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (work >= static_cast<uint64_t>(nb) * tiles_per_b) return;  // the whole warp leaves
+                  uint32_t nb, uint32_t nk, uint32_t nc, uint32_t tiles_per_b, uint32_t g, uint32_t ksplit, uint32_t klen,
+                  float* __restrict__ part) {
+  // ksplit > 1 (few tiles, a long reduced axis): a CTA takes range blockIdx % ksplit of klen rows of ONE (b, column
+  // tile); its eight warps interleave step by step, so that the CTA streams one contiguous piece of memory, meet in
+  // shared memory, and the CTA writes its state to part[3][ksplit][nb * nc] for reduce_outer_finish.
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint64_t work;
+  uint32_t kbeg = 0, kend = nk, kstep = (32 / g) * UNROLL, ks = 0;
+  if (ksplit > 1) {
+    work = blockIdx.x / ksplit;
+    ks = blockIdx.x % ksplit;
+    kend = nk - ks * klen < klen ? nk : (ks + 1) * klen;
+    kbeg = ks * klen + warp * kstep;
+    if (kbeg > kend) kbeg = kend;
+    kstep *= 8;
+  } else {
+    work = static_cast<uint64_t>(blockIdx.x) * 8 + warp;
+    if (work >= static_cast<uint64_t>(nb) * tiles_per_b) return;  // the whole warp leaves
+  }
   const uint32_t b = static_cast<uint32_t>(work / tiles_per_b), tile = static_cast<uint32_t>(work % tiles_per_b);
   const uint32_t rows_per_step = 32 / g;
   const uint32_t cg = lane % g, kr = lane / g;
@@ -182,17 +197,17 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
     bidx[j] = 0;
   }
   if (colok) {
-    for (uint32_t k0 = kr; k0 < nk; k0 += rows_per_step * UNROLL) {
+    for (uint32_t k0 = kbeg + kr; k0 < kend; k0 += kstep) {
       float f[UNROLL][4];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * rows_per_step;
-        if (k < nk) ColVec<4>::load(base + static_cast<size_t>(k) * nc, f[u]);
+        if (k < kend) ColVec<4>::load(base + static_cast<size_t>(k) * nc, f[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * rows_per_step;
-        if (k < nk) {
+        if (k < kend) {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const float v = f[u][j];
@@ -218,6 +233,40 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
       }
     }
   }
+  if (ksplit > 1) {
+    __shared__ float s_sum[8][128], s_max[8][128];
+    __shared__ int32_t s_idx[8][128];
+    if (lane < g) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s_sum[warp][cg * 4 + j] = acc[j];
+        s_max[warp][cg * 4 + j] = best[j];
+        s_idx[warp][cg * 4 + j] = bidx[j];
+      }
+    }
+    __syncthreads();
+    const uint32_t c = threadIdx.x, tile_col = tile * 128 + c;
+    if (c < 4 * g && tile_col < nc) {
+      float a = 0.0f, bv = -INFINITY;
+      int32_t bi = 0x7fffffff;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        a += s_sum[w][c];
+        const float v = s_max[w][c];
+        const int32_t vi = s_idx[w][c];
+        if (v > bv || (v == bv && vi < bi)) {
+          bv = v;
+          bi = vi;
+        }
+      }
+      const size_t cells = static_cast<size_t>(nb) * nc, plane = ksplit * cells;
+      const size_t po = ks * cells + static_cast<size_t>(b) * nc + tile_col;
+      part[po] = a;
+      part[plane + po] = bv;
+      part[2 * plane + po] = __int_as_float(bi);
+    }
+    return;
+  }
   if (lane < g && colok) {
     const size_t o = static_cast<size_t>(b) * nc + col;
 #pragma unroll
@@ -229,29 +278,45 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
   }
 }
 
-// Folds the partial states of the k ranges, ascending: the same rule as the cross-warp combine above, so
-// the lowest index among equal maxima survives whichever range it came from.
+// Folds the partial states of the k ranges under the rule of the cross-warp combine above -- greater value, or equal
+// value and lower index -- so the lowest index among equal maxima survives whichever range it came from. `lanes` (a
+// power of two up to 32) threads share a cell: each folds every lanes-th state in ascending order, then they meet by
+// shuffles.
 __global__ void __launch_bounds__(256)
 reduce_outer_finish(const float* __restrict__ part, float* __restrict__ sum, float* __restrict__ mx,
-                    int32_t* __restrict__ amax, uint32_t cells, uint32_t ksplit) {
-  const uint32_t o = blockIdx.x * 256 + threadIdx.x;
-  if (o >= cells) return;
+                    int32_t* __restrict__ amax, uint32_t cells, uint32_t ksplit, uint32_t lanes) {
+  const uint32_t t = blockIdx.x * 256 + threadIdx.x;
+  const uint32_t o = t / lanes, l = t % lanes;
   const size_t plane = static_cast<size_t>(ksplit) * cells;
   float a = 0.0f, bv = -INFINITY;
-  int32_t bi = 0;
-  for (uint32_t ks = 0; ks < ksplit; ++ks) {
-    const size_t po = static_cast<size_t>(ks) * cells + o;
-    a += part[po];
-    const float v = part[plane + po];
-    const int32_t vi = __float_as_int(part[2 * plane + po]);
+  int32_t bi = 0x7fffffff;  // no state seen yet: any real index is lower
+  if (o < cells) {
+#pragma unroll 4
+    for (uint32_t ks = l; ks < ksplit; ks += lanes) {
+      const size_t po = static_cast<size_t>(ks) * cells + o;
+      a += part[po];
+      const float v = part[plane + po];
+      const int32_t vi = __float_as_int(part[2 * plane + po]);
+      if (v > bv || (v == bv && vi < bi)) {
+        bv = v;
+        bi = vi;
+      }
+    }
+  }
+  for (uint32_t off = lanes >> 1; off > 0; off >>= 1) {
+    a += __shfl_xor_sync(0xffffffffu, a, off);
+    const float v = __shfl_xor_sync(0xffffffffu, bv, off);
+    const int32_t vi = __shfl_xor_sync(0xffffffffu, bi, off);
     if (v > bv || (v == bv && vi < bi)) {
       bv = v;
       bi = vi;
     }
   }
-  if (sum) sum[o] = a;
-  if (mx) mx[o] = bv;
-  if (amax) amax[o] = bi;
+  if (o < cells && l == 0) {
+    if (sum) sum[o] = a;
+    if (mx) mx[o] = bv;
+    if (amax) amax[o] = bi;
+  }
 }
 
 // Scratch for the partial states: kMaxPartialCells cells x 3 values per (device, stream), allocated the
@@ -281,6 +346,14 @@ uint32_t choose_ksplit(uint64_t tiles, uint32_t nb, uint32_t nk, uint32_t nc, ui
   return want < 2 ? 1 : static_cast<uint32_t>(want);
 }
 
+int launch_finish(const float* part, float* sum, float* mx, int32_t* amax, uint32_t cells, uint32_t states, cudaStream_t s) {
+  const uint32_t lanes = finish_lanes(states);
+  const uint64_t threads = static_cast<uint64_t>(cells) * lanes;
+  reduce_outer_finish<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(part, sum, mx, amax, cells, states, lanes);
+  count_launch();
+  return check_launch("reduce_outer_finish");
+}
+
 template <int V, int CV, int KW, int UNROLL>
 int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, uint32_t nk, uint32_t nc,
            int ctas_per_sm, int forced_ksplit, cudaStream_t s) {
@@ -308,10 +381,7 @@ int launch(const float* t, float* sum, float* mx, int32_t* amax, uint32_t nb, ui
   count_launch();
   int rc = check_launch("reduce_outer_kernel");
   if (rc != TCAB_OK || ksplit == 1) return rc;
-  const uint32_t cells = nb * nc;
-  reduce_outer_finish<<<(cells + 255) / 256, 256, 0, s>>>(part, sum, mx, amax, cells, ksplit);
-  count_launch();
-  return check_launch("reduce_outer_finish");
+  return launch_finish(part, sum, mx, amax, nb * nc, ksplit, s);
 }
 
 }  // namespace
@@ -331,9 +401,20 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
     if (g != 0) {
       const uint32_t tiles_per_b = (nc + 127) / 128;
       const uint64_t work = static_cast<uint64_t>(nb) * tiles_per_b;
-      reduce_outer_flat<4><<<static_cast<unsigned>((work + 7) / 8), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g);
+      uint32_t klen = nk;
+      uint32_t ksplit = outer_flat_ranges(nb, nk, nc, g, sm_count(), kMaxPartialCells, &klen);
+      float* part = ksplit > 1 ? outer_scratch(s) : nullptr;
+      if (part == nullptr) {
+        ksplit = 1;
+        klen = nk;
+      }
+      const uint64_t grid = ksplit > 1 ? work * ksplit : (work + 7) / 8;  // a CTA per range, or eight tiles per CTA
+      reduce_outer_flat<4><<<static_cast<unsigned>(grid), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g, ksplit,
+                                                                       klen, part);
       count_launch();
-      return check_launch("reduce_outer_flat");
+      int rc = check_launch("reduce_outer_flat");
+      if (rc != TCAB_OK || ksplit == 1) return rc;
+      return launch_finish(part, sum, mx, amax, nb * nc, ksplit, s);
     }
   }
   if (vec) {

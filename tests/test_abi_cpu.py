@@ -291,6 +291,31 @@ def test_lambdas_over_operands_that_bind_a_subset_of_the_axes_compile(tcab_lib, 
     assert tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, rb, cb, cells) == _lib.OK, _err(tcab_lib)
 
 
+def test_outer_flat_ranges(tcab_lib):
+    """Few narrow column tiles and a long reduced axis: CTAs of the warp-per-tile kernels cut k into ranges that cover it,
+    none empty, within the scratch for the partial cells (one per range); many tiles, wide tiles or a short axis are
+    never cut."""
+    def plan(nb, nk, nc, sms=148, cap=262144):
+        g, r, kl = C.c_uint32(), C.c_uint32(), C.c_uint32()
+        assert tcab_lib.tcab_plan_outer_flat_ranges(nb, nk, nc, sms, cap, C.byref(g), C.byref(r), C.byref(kl)) == 0
+        return g.value, r.value, kl.value
+    for nb, nk, nc in [(1, 1 << 25, 4), (1, 1 << 23, 16), (1, 1 << 20, 64), (4, 524288, 64), (700, 5000, 32),
+                       (3, 100003, 8), (1, 1025, 4), (2, 5000, 16), (1000, 1 << 16, 64)]:
+        g, r, kl = plan(nb, nk, nc)
+        assert g == nc // 4 and r >= 1 and kl >= 1
+        assert (r - 1) * kl < nk <= r * kl                      # the ranges cover k and the last one is not empty
+        assert r == 1 or nb * nc * r <= 262144                  # partial cells fit the scratch
+        assert r == 1 or kl >= (32 // g) * 8 * 16               # at least 16 steps per warp of a range
+    assert plan(1, 1 << 25, 4)[1] == 1184 and plan(1, 1 << 20, 64)[1] == 1184  # eight CTAs per SM
+    assert plan(700, 5000, 8)[1] == 2 and plan(1000, 1 << 16, 16)[1] == 2      # rounded up to fill the GPU
+    assert plan(700, 5000, 32)[1] == 2 and plan(1000, 1 << 16, 64)[1] == 2
+    assert plan(1000, 1 << 16, 64, cap=100000)[1] == 1          # 64000 cells: two ranges would overrun this scratch
+    assert plan(1, 1025, 4)[1] == 1                             # too short for two ranges
+    assert plan(100000, 256, 16)[1] == 1 and plan(2000, 1 << 16, 32)[1] == 1   # many tiles: one warp per tile
+    assert plan(1, 1 << 20, 128) == (0, 1, 1 << 20) and plan(1, 1 << 20, 512)[0] == 0   # wide tiles: a CTA per tile
+    assert plan(1, 1 << 20, 16, cap=128)[1] == 8                # a small scratch bounds the ranges
+
+
 def test_row_kernel_shape_rules(tcab_lib):
     """The launchers' choices that are pure arithmetic: which middle-axis shapes a warp per (b, column tile) takes, how
     many CTAs stream a long row, how many warps the thread-per-row kernel gets."""
@@ -305,8 +330,9 @@ def test_row_kernel_shape_rules(tcab_lib):
     assert plan(rows=100000, nk=256, nc=6)[0] == 0                                                # not whole vectors
     # short reduced axes with wide rows: 32 groups of a 128-column tile; long axes keep a CTA per tile
     assert plan(rows=65536, nk=4, nc=1024)[0] == 32 and plan(rows=65536, nk=64, nc=1024)[0] == 0
-    # a handful of long columns needs the k split over CTAs instead
-    assert plan(rows=8, nk=1 << 20, nc=8)[0] == 0 and plan(rows=8, nk=4096, nc=8)[0] == 2
+    # a handful of long columns: the warps share the k axis as well (test_outer_flat_ranges)
+    assert plan(rows=8, nk=1 << 20, nc=8)[0] == 2 and plan(rows=8, nk=4096, nc=8)[0] == 2
+    assert plan(rows=1, nk=1 << 20, nc=512)[0] == 0 and plan(rows=1, nk=1 << 20, nc=96)[0] == 0
     # streaming clusters: four steps with the smallest cluster, three full steps where a larger one gives them
     assert plan(nvec=6144)[1] == 2 and plan(nvec=8192)[1] == 4 and plan(nvec=12564)[1] == 4 and plan(nvec=32768)[1] == 8
     assert plan(nvec=8192, three=0)[1] == 2 and plan(nvec=100)[1] == 2 and plan(nvec=10**6, per_step=4096)[1] == 8

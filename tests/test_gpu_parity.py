@@ -1181,6 +1181,52 @@ def test_middle_axis_chains_warp_per_tile(oracle, cuda, nb, nk, nc):
 
 
 # ----------------------------------------------------------------------------
+# column statistics of tall matrices: few column tiles, a long reduced axis -- the warps share the k axis too
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("nb,nk,nc", [(1, 1 << 20, 8), (1, 262144, 128), (4, 131072, 64), (3, 100003, 16), (1, 70001, 512),
+                                      (2, 40000, 1024), (1, 1 << 21, 4), (1, 1025, 32), (5, 30011, 260)])
+def test_column_statistics_of_tall_matrices(oracle, cuda, nb, nk, nc):
+    rng = np.random.default_rng(nb + nk + nc)
+    x = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
+    xd = dev_f32(x, cuda)
+    x64 = x.astype(np.float64)
+    mag = np.abs(x64).sum(1)
+    buf, out = guarded((nb, nc), torch.float32, cuda)
+    n0 = T.launch_count()
+    T.chain_reduce([xd], "p0", axis=1, out=out)
+    assert T.launch_count() - n0 == 2          # the ranges, then their fold
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    assert (np.abs(got - x64.sum(1)) <= 1e-6 * mag + 1e-30).all()
+    # max with init and a piped map: bit-exact whatever the ranges
+    got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.999, axis=1, post_expr="p0 * 2.0f").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x.max(1), np.float32(0.999)) * np.float32(2))
+    # a run-time compiled lambda with a per-cell operand and an init (column variance around a given centre)
+    c = rng.uniform(-0.1, 0.1, (nb, 1, nc)).astype(np.float32)
+    got = T.chain_reduce([xd, dev_f32(c, cuda)], "(p0 - p1) * (p0 - p1)", init=0.5, axis=1).cpu().numpy()
+    d = x64 - c.astype(np.float64)
+    want = (d * d).sum(1) + 0.5
+    assert (np.abs(got - want) <= 2e-6 * want).all()
+    # sum, max and argmax in one pass; ties on purpose: the lowest index wins whichever range holds it
+    xt = np.round(x * 8).astype(np.float32) / 8
+    xtd = dev_f32(xt, cuda)
+    n0 = T.launch_count()
+    got = T.reduce_outer(xtd)
+    assert T.launch_count() - n0 == 2
+    assert np.array_equal(got["max"].cpu().numpy(), xt.max(1))
+    assert np.array_equal(got["argmax"].cpu().numpy(), xt.argmax(1).astype(np.int32))
+    assert (np.abs(got["sum"].cpu().numpy() - xt.astype(np.float64).sum(1)) <= 1e-6 * np.abs(xt).sum(1) + 1e-30).all()
+    try:
+        T.tune("reduce_outer", 1, 0, 0, 0)      # a CTA per column tile
+        old = T.reduce_outer(xtd)
+    finally:
+        T.tune("reduce_outer")
+    assert torch.equal(old["max"], got["max"]) and torch.equal(old["argmax"], got["argmax"])
+    only = T.reduce_outer(xtd, want=("sum",))
+    assert torch.equal(only["sum"], got["sum"])
+
+
+# ----------------------------------------------------------------------------
 # several problems of one shape in one launch
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nprob,rows,cols", [(16, 4096, 1024), (1, 5, 7), (3, 33, 130), (32, 17, 64), (2, 3, 9000), (5, 2, 4096)])
