@@ -376,7 +376,7 @@ class MapRowsum(Workload):
     full_units, cols = 4096, 1024
     copies = 16  # distinct input buffers per step: 256 MiB in total, larger than L2
     launches_per_step = 1
-    chunks = 2
+    chunks = 1   # end to end, a 16 MiB step is one upload, one launch, one 16 KiB download; successive steps overlap
     shape = ("x fp32 [4096, 1024] ~ U(-1,1) -> y[i] = sum_j (0.5*x+0.25)^2 fp32 [4096]; one step = 16 such problems "
              "on 16 distinct inputs handed over as ONE batched launch (a lone 16 MB launch is bounded by launch latency "
              "and the wait for its predecessor, and L2-resident when repeated; see roofline.one_launch_each and "
@@ -772,7 +772,10 @@ def measure_e2e(wl, steps, world, dev) -> dict:
     and downloads its result inside the timed region; steps follow each other without a join, one join before
     the closing event."""
     wl.host_setup()
-    ms = timed(wl.e2e_step, steps, 1, world, dev, after=wl.e2e_join)
+    # a small problem (C1 moves 16 MiB per step) gets as many steps as move 1 GiB: ten of them are a 3 ms region that
+    # mostly measures how the copy engines start up
+    steps = max(steps, min(200, -(-(1 << 30) // max(1, wl.h2d + wl.d2h))))
+    ms = timed(wl.e2e_step, steps, 3, world, dev, after=wl.e2e_join)
     return {"value": wl.e2e_work() * steps * world / (ms * 1e-3) / scale_of(wl), "unit": wl.unit,
             "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": steps, "ms_per_step": ms / steps,
             "copy_gbs": (wl.h2d + wl.d2h) * steps * world / (ms * 1e-3) / 1e9,

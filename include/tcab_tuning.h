@@ -25,11 +25,13 @@ extern "C" {
  *       kernel, 2 always, 3 the shared-memory kernel, 6 no 16-byte vectors for rows that are not a multiple of
  *       four columns; layernorm: 1 gamma/beta in registers, 2 no cluster kernel,
  *       3 always, 4 the shared-memory kernel, 6 no 16-byte vectors for rows that are not whole vectors).
- *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256), p1 = CTAs per row of the
+ *   "reduce_inner" (tcab_chain_reduce): p0 = threads per row (1, 4, 32, 256; middle-axis reductions: 32 = a warp per
+ *       column tile whatever the shape), p1 = CTAs per row of the
  *       split path, p2 = 2 launches without programmatic dependent launch, 3 no 1024-thread CTAs for small problems, p3 = CTAs sharing the k axis of a
  *       middle-axis reduction (any value, 1 included, also keeps the kernel with a CTA per column tile where the
  *       library would take a warp per tile).
- *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16), p2 = CTAs per SM,
+ *   "reduce_outer": p0 = vectors per lane (1, 2), p1 = warps splitting k (4, 8, 16; 1 = a warp per column tile
+ *       whatever the shape), p2 = CTAs per SM,
  *       p3 = CTAs sharing the k axis (any of p0, p1, p3 keeps the kernel with a CTA per column tile).
  *   "gemm": p0 = CTAs of the persistent grid, p1 = kernel of tcab_gemm_bias_act (2 CTA pairs with
  *       512 x 256 tiles, 3 double-buffered accumulators on 128 x 256 tiles, 4 the same on CTA pairs, 5 one
@@ -53,7 +55,8 @@ TCAB_API int tcab_plan_outer_split(uint64_t tiles, uint64_t cells, uint32_t nk, 
 
 /* The launchers' shape rules that are pure arithmetic, for tests without a device:
  *   outer_flat_g   - middle-axis reduction over [rows_or_batches, nk, nc]: column groups per tile when a warp takes a
- *                    (b, column tile) instead of a CTA (0 = a CTA per tile);
+ *                    (b, column tile) instead of a CTA (0 = a CTA per tile); groups of four columns when nc is a
+ *                    multiple of four (aligned operands assumed), of one column otherwise;
  *   stream_cluster - CTAs per row of a streaming cluster for a row of nvec vectors at per_step vectors per CTA and step;
  *   rows32         - warps per CTA of the thread-per-row kernel for rows of nvec vectors and n_in operands (its shared
  *                    memory stays within 48 KiB; fewer than 2: not used). */

@@ -351,7 +351,7 @@ int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32_t nc, in
   if (outer_flat_g == nullptr || stream_cluster == nullptr || rows32 == nullptr)
     return fail(TCAB_ERR_INVALID_ARG, "plan_row_kernels: null output");
   if (sms < 1 || per_step < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_row_kernels: sms and per_step must be positive");
-  *outer_flat_g = outer_flat_groups(rows_or_batches, nk, nc, sms);
+  *outer_flat_g = outer_flat_groups(rows_or_batches, nk, nc, sms, nc % 4 == 0);
   *stream_cluster = stream_cluster_size(nvec, per_step, prefer_three != 0);
   *rows32 = rows32_warps(nvec, n_in);
   return TCAB_OK;
@@ -362,10 +362,10 @@ int tcab_plan_outer_flat_ranges(uint64_t batches, uint32_t nk, uint32_t nc, int 
   if (groups == nullptr || ranges == nullptr || klen == nullptr)
     return fail(TCAB_ERR_INVALID_ARG, "plan_outer_flat_ranges: null output");
   if (sms < 1) return fail(TCAB_ERR_INVALID_ARG, "plan_outer_flat_ranges: sms must be positive");
-  *groups = outer_flat_groups(batches, nk, nc, sms);
+  *groups = outer_flat_groups(batches, nk, nc, sms, nc % 4 == 0);
   *ranges = 1;
   *klen = nk;
-  if (*groups != 0) *ranges = outer_flat_ranges(batches, nk, nc, *groups, sms, max_partials, klen);
+  if (*groups != 0) *ranges = outer_flat_ranges(batches, nk, nc, *groups, nc % 4 == 0, sms, max_partials, klen);
   return TCAB_OK;
 }
 

@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kOuterFlat1, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
 };
 
 struct JitChain {
@@ -150,6 +150,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
       names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + cm + ">";
       names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 8, " + bf + cm + ">";
       names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + cm + ">";
+      names[kOuterFlat1] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 16, " + bf + cm + ", 1>";
     } else if ((sp.rb_mask | sp.cb_mask) != 0) {  // broadcast operands: the innermost-axis kernels only
       names.assign(kSlots, std::string());
       for (int v = 0; v < 2; ++v)
@@ -165,6 +166,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kOuterV4] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, 4, " + bf + ">";
     names[kOuterV1] = "tcabk::chain_outer<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 1, 8, 8, " + bf + ">";
     names[kOuterFlat] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
+    names[kOuterFlat1] = "tcabk::chain_outer_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 16, " + bf + ", 0, 1>";
     names[kInnerFlat] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat2] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ", 2>";
     names[kInnerRows32] = "tcabk::chain_inner_rows32<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
@@ -352,17 +354,19 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
   const uint64_t tiles = static_cast<uint64_t>(nb) * tiles_per_b;
   if (tiles > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
   // narrow rows and short reduced axes: a warp per (b, column tile) (same policy as the ahead-of-time path)
-  if (vec && jc->k[kOuterFlat] != nullptr && tune(kReduceInner).p3 <= 0) {
-    const uint32_t g = outer_flat_groups(nb, nk, nc, sm_count());
+  const cudaKernel_t flat = jc->k[vec ? kOuterFlat : kOuterFlat1];
+  if (flat != nullptr && tune(kReduceInner).p3 <= 0) {
+    const uint32_t g = tune(kReduceInner).p0 == 32 ? outer_flat_width(nc, vec) : outer_flat_groups(nb, nk, nc, sm_count(), vec);
     if (g != 0) {
-      uint32_t tpb = (nc + 127) / 128;
+      uint32_t tpb = (nc + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
       const uint64_t work = static_cast<uint64_t>(nb) * tpb;
       uint32_t klen = nk;
-      uint32_t ksplit = split_scratch_or_null == nullptr ? 1u : outer_flat_ranges(nb, nk, nc, g, sm_count(), 262144, &klen);
+      uint32_t ksplit =
+          split_scratch_or_null == nullptr ? 1u : outer_flat_ranges(nb, nk, nc, g, vec, sm_count(), 262144, &klen);
       if (ksplit == 1) klen = nk;
       void* af[] = {ptrs, &out, &nb, &nk, &nc, &tpb, const_cast<uint32_t*>(&g), &init, &caps, &ksplit, &klen, &split_scratch_or_null};
       // a CTA per range, or eight tiles per CTA
-      int rc = launch(jc->k[kOuterFlat], ksplit > 1 ? work * ksplit : (work + 7) / 8, 256, af, s, "chain_outer_flat");
+      int rc = launch(flat, ksplit > 1 ? work * ksplit : (work + 7) / 8, 256, af, s, "chain_outer_flat");
       if (rc != TCAB_OK || ksplit == 1) return rc;
       return launch_jit_finish(jc, split_scratch_or_null, out, nb * nc, ksplit, init, caps, s);
     }

@@ -585,13 +585,14 @@ chain_outer(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 
 }
 
 // Reduce over a MIDDLE axis with a WARP per (b, column tile), for the shapes on which chain_outer idles: narrow
-// rows (nc = 4, 8, ... 64: most lanes of a 128-column tile would have no column) and short reduced axes (a CTA per
-// tile would do a few hundred bytes of work between two barriers). The warp's 32 lanes cover g = tile columns / 4
-// column groups of four and 32 / g consecutive k rows per step; when the tile is the whole row (nc = 4 g < 128) the
-// 32 vectors of a step are contiguous in memory. Every lane folds the k rows it sees (ascending), lanes with the
-// same column group then meet by shuffles, and lanes 0..g-1 store. No shared memory, no barrier; eight independent
-// warps per CTA. 16-byte vectors only (nc % 4 == 0, aligned operands).
-template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0, int CELL = 0>
+// rows (most lanes of a CTA's column tile would have no column) and short reduced axes (a CTA per tile would do a
+// few hundred bytes of work between two barriers). A lane loads V columns at once (V = 4: 16-byte vectors, nc % 4
+// == 0 and aligned operands; V = 1: any nc, any alignment). The warp's lanes cover g column groups of V and 32 / g
+// consecutive k rows per step (lanes beyond g * (32 / g) idle when g does not divide 32); when the tile is the whole
+// row (nc = V g < 32 V) what a step loads is contiguous in memory. Every lane folds the k rows it sees (ascending),
+// lanes with the same column group then meet by shuffles, and lanes 0..g-1 store. No shared memory, no barrier;
+// eight independent warps per CTA.
+template <class Map, class Post, int COMBINE, int NIN, int UNROLL, int BF = 0, int CELL = 0, int V = 4>
 __global__ void __launch_bounds__(256)
 chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc, u32 tiles_per_b, u32 g, float init,
                  Caps caps, u32 ksplit, u32 klen, float* __restrict__ partials) {
@@ -616,31 +617,50 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
   }
   const u32 b = static_cast<u32>(work / tiles_per_b), tile = static_cast<u32>(work % tiles_per_b);
   const u32 rows_per_step = 32 / g;
-  const u32 cg = lane % g, kr = lane / g;  // this lane's column group, and its row inside a step
-  const u32 col = tile * 128 + cg * 4;     // g < 32 only when one tile is the whole row
-  const bool colok = col < nc;
-  const u64 rowvecs = nc / 4;
-  const u64 base = static_cast<u64>(b) * nk * rowvecs + col / 4;
+  const u32 cg = lane % g, kr = lane / g;    // this lane's column group, and its row inside a step
+  const u32 col = tile * (32 * V) + cg * V;  // g < 32 only when one tile is the whole row
+  const bool colok = col < nc && kr < rows_per_step;
+  const u64 rowvecs = nc / V;
+  const u64 base = static_cast<u64>(b) * nk * rowvecs + col / V;
 
-  float acc[4];
+  float acc[V];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) acc[j] = C::identity();
+  for (int j = 0; j < V; ++j) acc[j] = C::identity();
   if (colok) {
-    float cellval[NIN][4];  // operands that lack the reduced axis: one value per output cell, loaded once
-    LoadOuterAll<4, BF, CELL, NIN>::cells(ins.p, (static_cast<u64>(b) * nc + col) / 4, cellval);
-    for (u32 k0 = kbeg + kr; k0 < kend; k0 += kstep) {
-      float f[UNROLL][NIN][4];
+    float cellval[NIN][V];  // operands that lack the reduced axis: one value per output cell, loaded once
+    LoadOuterAll<V, BF, CELL, NIN>::cells(ins.p, (static_cast<u64>(b) * nc + col) / V, cellval);
+    u32 k0 = kbeg + kr;
+    const u64 ustride = static_cast<u64>(rows_per_step) * rowvecs;
+    // iterations whose UNROLL rows all exist: no predicates
+    for (; kend > (UNROLL - 1) * rows_per_step && k0 < kend - (UNROLL - 1) * rows_per_step; k0 += kstep) {
+      float f[UNROLL][NIN][V];
+      const u64 at = base + static_cast<u64>(k0) * rowvecs;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) LoadOuterAll<V, BF, CELL, NIN>::at(ins.p, at + u * ustride, cellval, f[u]);
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float p[NIN];
+#pragma unroll
+          for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
+          acc[j] = C::apply(acc[j], Map::apply(p, caps.c));
+        }
+      }
+    }
+    for (; k0 < kend; k0 += kstep) {  // the ragged end of this lane's rows
+      float f[UNROLL][NIN][V];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const u32 k = k0 + u * rows_per_step;
-        if (k < kend) LoadOuterAll<4, BF, CELL, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, cellval, f[u]);
+        if (k < kend) LoadOuterAll<V, BF, CELL, NIN>::at(ins.p, base + static_cast<u64>(k) * rowvecs, cellval, f[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const u32 k = k0 + u * rows_per_step;
         if (k < kend) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < V; ++j) {
             float p[NIN];
 #pragma unroll
             for (int a = 0; a < NIN; ++a) p[a] = f[u][a][j];
@@ -650,19 +670,29 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
       }
     }
   }
-  for (u32 off = 16; off >= g; off >>= 1) {  // lanes that differ in the row bits hold the same column group
+  if ((g & (g - 1)) == 0) {
+    for (u32 off = 16; off >= g; off >>= 1) {  // lanes that differ in the row bits hold the same column group
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[j] = C::apply(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+      for (int j = 0; j < V; ++j) acc[j] = C::apply(acc[j], __shfl_xor_sync(0xffffffffu, acc[j], off));
+    }
+  } else {  // lanes cg, cg + g, cg + 2 g, ... hold column group cg: lanes 0..g-1 collect them in row order
+    for (u32 r = 1; r < rows_per_step; ++r) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float v = __shfl_sync(0xffffffffu, acc[j], (lane + r * g) & 31);
+        if (lane < g) acc[j] = C::apply(acc[j], v);
+      }
+    }
   }
   if (ksplit > 1) {  // the CTA's warps meet in shared memory, in warp order: one partial per range and cell
     __shared__ float s_part[8][128];
     if (lane < g) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s_part[warp][cg * 4 + j] = acc[j];
+      for (int j = 0; j < V; ++j) s_part[warp][cg * V + j] = acc[j];
     }
     __syncthreads();
-    const u32 c = threadIdx.x, tile_col = tile * 128 + c;
-    if (c < 4 * g && tile_col < nc) {
+    const u32 c = threadIdx.x, tile_col = tile * (32 * V) + c;
+    if (c < V * g && tile_col < nc) {
       float a = s_part[0][c];
 #pragma unroll
       for (int w = 1; w < 8; ++w) a = C::apply(a, s_part[w][c]);
@@ -673,7 +703,7 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
   if (lane < g && colok) {
     const u64 cell = static_cast<u64>(b) * nc + col;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < V; ++j) {
       float r[1] = {C::apply(init, acc[j])};
       out[cell + j] = Post::apply(r, caps.c + 8);
     }

@@ -198,18 +198,19 @@ int launch_finish(const float* scratch, float* out, uint32_t rows, uint32_t spli
   return check_launch("chain_split_finish");
 }
 
-template <class Map, class Post, int COMBINE>
+template <class Map, class Post, int COMBINE, int V>
 int launch_outer_flat(const Args& a, uint32_t g) {
   constexpr int NIN = Map::kIn;
-  auto* fn = tcabk::chain_outer_flat<Map, Post, COMBINE, NIN, 4>;
+  // 4-byte loads need more of them in flight for the same bytes
+  auto* fn = tcabk::chain_outer_flat<Map, Post, COMBINE, NIN, V == 4 ? 4 : 16, 0, 0, V>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
   const uint32_t nc = static_cast<uint32_t>(a.inner);
-  const uint32_t tiles_per_b = (nc + 127) / 128;
+  const uint32_t tiles_per_b = (nc + 32 * V - 1) / (32 * V);
   const uint64_t work = a.outer * tiles_per_b;
   if (work > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many column tiles");
   uint32_t klen = a.nk;
-  uint32_t ksplit = outer_flat_ranges(a.outer, a.nk, nc, g, sm_count(), kMaxSplitPartials, &klen);
+  uint32_t ksplit = outer_flat_ranges(a.outer, a.nk, nc, g, V == 4, sm_count(), kMaxSplitPartials, &klen);
   float* scratch = ksplit > 1 ? split_scratch(a.stream) : nullptr;
   if (scratch == nullptr) {
     ksplit = 1;
@@ -337,10 +338,11 @@ int launch_chain(const Args& a) {
   if (a.inner > 0xffffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: inner extent beyond 2^32");
   const bool vec = al && (a.inner % 4 == 0);
   // narrow rows and short reduced axes: a warp per (b, column tile) (outer_flat_groups has the rule and the
-  // measurements). tune("reduce_inner", _, _, _, p3 = 1) keeps chain_outer.
-  if (vec && tune(kReduceInner).p3 <= 0) {
-    const uint32_t g = outer_flat_groups(a.outer, a.nk, static_cast<uint32_t>(a.inner), sm_count());
-    if (g != 0) return launch_outer_flat<Map, Post, COMBINE>(a, g);
+  // measurements). tune("reduce_inner", _, _, _, p3 = 1) keeps chain_outer, p0 = 32 takes the warps whatever the shape.
+  if (tune(kReduceInner).p3 <= 0) {
+    const uint32_t nc = static_cast<uint32_t>(a.inner);
+    const uint32_t g = tune(kReduceInner).p0 == 32 ? outer_flat_width(nc, vec) : outer_flat_groups(a.outer, a.nk, nc, sm_count(), vec);
+    if (g != 0) return vec ? launch_outer_flat<Map, Post, COMBINE, 4>(a, g) : launch_outer_flat<Map, Post, COMBINE, 1>(a, g);
   }
   return vec ? launch_outer<Map, Post, COMBINE, 4>(a) : launch_outer<Map, Post, COMBINE, 1>(a);
 }
@@ -628,7 +630,7 @@ int launch_chain_reduce(const PreparedChain& pc, const float* const* ins, uint64
       for (int i = 0; i < pc.spec.n_in; ++i) al = al && aligned16(ins[i]);
       splits = (pc.spec.rb_mask | pc.spec.cb_mask) ? 1 : choose_splits(outer, (al && nk % 4 == 0) ? nk / 4 : nk);
       if (splits > 1) scratch = split_scratch(s);
-    } else if (outer * ((inner + 127) / 128) < static_cast<uint64_t>(sm_count()) && nk >= 512) {
+    } else if (outer * ((inner + 31) / 32) < 8ull * static_cast<uint64_t>(sm_count()) && nk >= 512) {
       scratch = split_scratch(s);  // a middle-axis reduction that may split k over CTAs (decided at launch)
     }
     return jit_launch(h, ins, outer, nk, inner, pc.init, pc.caps, out, scratch, splits, s);

@@ -120,26 +120,36 @@ int launch_contract_bf16_tc(const __nv_bfloat16* a, const __nv_bfloat16* b, int 
                             uint32_t n, uint32_t k, cudaStream_t s, uint64_t c_pitch = 0);  // tensor cores, fp32 out (gemm_bias_act.cu)
 
 // chain_outer_flat (a warp per (b, column tile)) instead of chain_outer (a CTA per tile) for a middle-axis
-// reduction over [nb, nk, nc] with 16-byte vectors: rows of at most 32 columns, rows of 64 columns when there are
-// many of them, or a reduced axis shorter than 64 with rows of 4 * 2^i <= 64 or of at least 128 columns. Returns
-// the column groups per tile (1..32), or 0 for a CTA per tile. Measured (fp32 sum over 2^28 elements, TB/s, a CTA
-// per tile -> a warp per tile): [262144, 256, 4] 0.58 -> 7.1, [131072, 256, 8] 1.2 -> 6.9, [65536, 256, 16] 2.3 ->
-// 6.9, [32768, 256, 32] 4.4 -> 6.9, [65536, 4, 1024] 1.6 -> 5.5, [131072, 8, 256] 2.6 -> 5.9, [262144, 16, 64]
-// 2.6 -> 6.4; the fused sum / max / argmax kernel 0.36 -> 5.6, 0.73 -> 6.3, 1.4 -> 6.6, 2.7 -> 6.6 on the first four.
-inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm) {
-  if (nc == 0 || nc % 4 != 0 || nk == 0) return 0;
-  const uint32_t g = nc >= 128 ? 32u : nc / 4;
-  if (nc < 128 && (g & (g - 1)) != 0) return 0;       // 4, 8, 16, 32, 64 columns: the whole row is one tile
-  if (nc > 64 && nc < 128) return 0;
-  const uint64_t work = nb * ((nc + 127) / 128);  // warps
+// reduction over [nb, nk, nc]. `vec`: 16-byte vectors (nc % 4 == 0, aligned operands: tiles of 128 columns, groups of
+// four columns); otherwise 4-byte loads (tiles of 32 columns, groups of one). The warps take rows of at most 32
+// columns, rows of up to 64 columns when there are many of them or few long ones, any row when the reduced axis is
+// shorter than 64, and any row on 4-byte loads. Returns the column groups per tile (1..32), or 0 for a CTA per tile. Measured (fp32 sum over
+// 2^28 elements, TB/s, a CTA per tile -> a warp per tile): [262144, 256, 4] 0.58 -> 7.1, [131072, 256, 8] 1.2 -> 6.9,
+// [65536, 256, 16] 2.3 -> 6.9, [32768, 256, 32] 4.4 -> 6.9, [65536, 4, 1024] 1.6 -> 5.5, [131072, 8, 256] 2.6 ->
+// 5.9, [262144, 16, 64] 2.6 -> 6.4; the fused sum / max / argmax kernel 0.36 -> 5.6, 0.73 -> 6.3, 1.4 -> 6.6, 2.7 ->
+// 6.6 on the first four.
+inline uint32_t outer_flat_width(uint32_t nc, bool vec) {  // the groups such a warp would use, whatever the rule says
+  if (vec) return nc >= 128 ? 32u : nc / 4;
+  return nc >= 32 ? 32u : nc;
+}
+
+inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm, bool vec) {
+  if (nc == 0 || nk == 0 || (vec && nc % 4 != 0)) return 0;
+  const uint32_t g = outer_flat_width(nc, vec);
+  const uint32_t tile = vec ? 128u : 32u;
+  const uint64_t work = nb * ((nc + tile - 1) / tile);  // warps
   // few long narrow columns (column statistics of a tall matrix): CTAs of these warps share the k axis, see
-  // outer_flat_ranges; from 128 columns on a CTA per tile already uses every lane
-  if (work < 8ull * static_cast<uint64_t>(sm) && nk >= 1024) return nc <= 64 ? g : 0;
+  // outer_flat_ranges; from a full tile on a CTA per tile already uses every lane
+  if (work < 8ull * static_cast<uint64_t>(sm) && nk >= 1024) return nc <= tile / 2 ? g : 0;
   if (nc <= 32) return g;
-  // 64 columns use half the lanes of a CTA's tile: the warps win only when there are enough of them to keep an
-  // SM's memory pipeline full (measured [1024, 4096, 64]: 6.6 TB/s with a CTA per tile, 3.4 with 1024 warps)
-  if (nc == 64 && work >= 32ull * static_cast<uint64_t>(sm)) return g;
-  return nk < 64 ? g : 0;
+  if (nk < 64) return g;
+  // 4-byte loads: the warps are ahead on every shape measured ([128, 1024, 1022] 4.8 -> 5.8 TB/s, [4032, 256, 130]
+  // 3.8 -> 5.6, [15887, 256, 33] 2.5 -> 4.9, [2052, 64, 1022] 3.6 -> 6.5)
+  if (!vec) return g;
+  // 36 ... 64 columns use at most half the lanes of a CTA's tile: the warps win only when there are enough of them to
+  // keep an SM's memory pipeline full (measured [1024, 4096, 64]: 6.6 TB/s with a CTA per tile, 3.4 with 1024 warps)
+  if (nc <= 64 && work >= 32ull * static_cast<uint64_t>(sm)) return g;
+  return 0;
 }
 
 // The warp-per-tile kernels on few tiles and a long reduced axis: into how many ranges the k axis of one (b, column
@@ -147,9 +157,10 @@ inline uint32_t outer_flat_groups(uint64_t nb, uint32_t nk, uint32_t nc, int sm)
 // `max_partials` partial cells (one per range and output cell) -- and how many k rows a range has. 1 = no split.
 // (Column statistics of a tall matrix, measured with CTAs of 128-column tiles sharing k: [1, 2^23, 16], where 16 of
 // the 128 columns exist, 1.2 - 1.8 TB/s; [1, 2^25, 4]: 0.3 - 0.5.)
-inline uint32_t outer_flat_ranges(uint64_t nb, uint32_t nk, uint32_t nc, uint32_t g, int sm, uint64_t max_partials,
-                                  uint32_t* klen) {
-  const uint64_t work = nb * ((nc + 127) / 128), cells = nb * nc;
+inline uint32_t outer_flat_ranges(uint64_t nb, uint32_t nk, uint32_t nc, uint32_t g, bool vec, int sm,
+                                  uint64_t max_partials, uint32_t* klen) {
+  const uint32_t tile = vec ? 128u : 32u;
+  const uint64_t work = nb * ((nc + tile - 1) / tile), cells = nb * nc;
   const uint64_t target = 8ull * static_cast<uint64_t>(sm);
   uint64_t ranges = 1;
   if (work < target && cells > 0 && cells * 2 <= max_partials) {

@@ -153,13 +153,14 @@ reduce_outer_kernel(const float* __restrict__ t, float* __restrict__ sum, float*
   }
 }
 
-// The same reduction with a WARP per (b, column tile), for narrow rows (nc = 4 ... 64: most lanes of a 128-column
-// tile would own no column) and short reduced axes (a CTA per tile would do a few hundred bytes of work between two
-// barriers). The 32 lanes cover g column groups of four and 32 / g consecutive k rows per step (contiguous in memory
-// when the tile is the whole row); a lane folds the rows it sees in ascending order, lanes with the same column
-// group then meet by shuffles under the same rule -- greater value, or equal value and lower index -- and lanes
-// 0..g-1 store. No shared memory, no barrier.
-template <int UNROLL>
+// The same reduction with a WARP per (b, column tile), for narrow rows (most lanes of a CTA's column tile would own
+// no column) and short reduced axes (a CTA per tile would do a few hundred bytes of work between two barriers). A
+// lane loads V columns at once (4: 16-byte vectors; 1: any nc and alignment). The lanes cover g column groups of V
+// and 32 / g consecutive k rows per step (contiguous in memory when the tile is the whole row; lanes beyond
+// g * (32 / g) idle); a lane folds the rows it sees in ascending order, lanes with the same column group then meet
+// by shuffles under the same rule -- greater value, or equal value and lower index -- and lanes 0..g-1 store. No
+// shared memory, no barrier.
+template <int UNROLL, int V>
 __global__ void __launch_bounds__(256)
 reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* __restrict__ mx, int32_t* __restrict__ amax,
                   uint32_t nb, uint32_t nk, uint32_t nc, uint32_t tiles_per_b, uint32_t g, uint32_t ksplit, uint32_t klen,
@@ -184,32 +185,74 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
   const uint32_t b = static_cast<uint32_t>(work / tiles_per_b), tile = static_cast<uint32_t>(work % tiles_per_b);
   const uint32_t rows_per_step = 32 / g;
   const uint32_t cg = lane % g, kr = lane / g;
-  const uint32_t col = tile * 128 + cg * 4;  // g < 32 only when one tile is the whole row
-  const bool colok = col < nc;
+  const uint32_t col = tile * (32 * V) + cg * V;  // g < 32 only when one tile is the whole row
+  const bool colok = col < nc && kr < rows_per_step;
   const float* base = t + static_cast<size_t>(b) * nk * nc + col;
 
-  float acc[4], best[4];
-  int32_t bidx[4];
+  float acc[V], best[V];
+  int32_t bidx[V];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
+  for (int j = 0; j < V; ++j) {
     acc[j] = 0.0f;
     best[j] = -INFINITY;
     bidx[j] = 0;
   }
   if (colok) {
-    for (uint32_t k0 = kbeg + kr; k0 < kend; k0 += kstep) {
-      float f[UNROLL][4];
+    uint32_t k0 = kbeg + kr;
+    const size_t ustride = static_cast<size_t>(rows_per_step) * nc;
+    // Iterations whose UNROLL rows all exist: no predicates. With 4-byte loads the running maximum meets the maximum
+    // of the iteration's rows instead of every row -- a new maximum is rare after the first few rows, and only then is
+    // the row looked up (the first one that holds it, so the lowest index among equals survives as below).
+    for (; kend > (UNROLL - 1) * rows_per_step && k0 < kend - (UNROLL - 1) * rows_per_step; k0 += kstep) {
+      float f[UNROLL][V];
+      const float* at = base + static_cast<size_t>(k0) * nc;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) ColVec<V>::load(at + u * ustride, f[u]);
+      if constexpr (V == 1) {  // 16 rows of one column per iteration
+        float m = f[0][0];
+        acc[0] += f[0][0];
+#pragma unroll
+        for (int u = 1; u < UNROLL; ++u) {
+          acc[0] += f[u][0];
+          m = fmaxf(m, f[u][0]);  // ignores NaN, as a comparison does
+        }
+        if (m > best[0]) {
+          int first = UNROLL - 1;
+#pragma unroll
+          for (int u = UNROLL - 2; u >= 0; --u) first = f[u][0] == m ? u : first;
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u)
+            if (u == first) best[0] = f[u][0];  // the element itself: -0.0 and 0.0 compare equal
+          bidx[0] = static_cast<int32_t>(k0 + first * rows_per_step);
+        }
+      } else {  // four rows of four columns: comparing every element is cheaper than the detour (measured)
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            const float v = f[u][j];
+            acc[j] += v;
+            if (v > best[j]) {  // strict: the lowest index among equals survives
+              best[j] = v;
+              bidx[j] = static_cast<int32_t>(k0 + u * rows_per_step);
+            }
+          }
+        }
+      }
+    }
+    for (; k0 < kend; k0 += kstep) {  // the ragged end of this lane's rows
+      float f[UNROLL][V];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * rows_per_step;
-        if (k < kend) ColVec<4>::load(base + static_cast<size_t>(k) * nc, f[u]);
+        if (k < kend) ColVec<V>::load(base + static_cast<size_t>(k) * nc, f[u]);
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
         const uint32_t k = k0 + u * rows_per_step;
         if (k < kend) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < V; ++j) {
             const float v = f[u][j];
             acc[j] += v;
             if (v > best[j]) {  // strict: the lowest index among equals survives
@@ -221,15 +264,34 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
       }
     }
   }
-  for (uint32_t off = 16; off >= g; off >>= 1) {
+  if ((g & (g - 1)) == 0) {
+    for (uint32_t off = 16; off >= g; off >>= 1) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
-      const float v = __shfl_xor_sync(0xffffffffu, best[j], off);
-      const int32_t vi = __shfl_xor_sync(0xffffffffu, bidx[j], off);
-      if (v > best[j] || (v == best[j] && vi < bidx[j])) {  // a lane that saw no row holds (-inf, 0): the initial state
-        best[j] = v;
-        bidx[j] = vi;
+      for (int j = 0; j < V; ++j) {
+        acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+        const float v = __shfl_xor_sync(0xffffffffu, best[j], off);
+        const int32_t vi = __shfl_xor_sync(0xffffffffu, bidx[j], off);
+        if (v > best[j] || (v == best[j] && vi < bidx[j])) {  // a lane that saw no row holds (-inf, 0): the initial state
+          best[j] = v;
+          bidx[j] = vi;
+        }
+      }
+    }
+  } else {  // lanes cg, cg + g, cg + 2 g, ... hold column group cg: lanes 0..g-1 collect them
+    for (uint32_t r = 1; r < rows_per_step; ++r) {
+      const uint32_t src = (lane + r * g) & 31;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float a = __shfl_sync(0xffffffffu, acc[j], src);
+        const float v = __shfl_sync(0xffffffffu, best[j], src);
+        const int32_t vi = __shfl_sync(0xffffffffu, bidx[j], src);
+        if (lane < g) {
+          acc[j] += a;
+          if (v > best[j] || (v == best[j] && vi < bidx[j])) {
+            best[j] = v;
+            bidx[j] = vi;
+          }
+        }
       }
     }
   }
@@ -238,15 +300,15 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
     __shared__ int32_t s_idx[8][128];
     if (lane < g) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        s_sum[warp][cg * 4 + j] = acc[j];
-        s_max[warp][cg * 4 + j] = best[j];
-        s_idx[warp][cg * 4 + j] = bidx[j];
+      for (int j = 0; j < V; ++j) {
+        s_sum[warp][cg * V + j] = acc[j];
+        s_max[warp][cg * V + j] = best[j];
+        s_idx[warp][cg * V + j] = bidx[j];
       }
     }
     __syncthreads();
-    const uint32_t c = threadIdx.x, tile_col = tile * 128 + c;
-    if (c < 4 * g && tile_col < nc) {
+    const uint32_t c = threadIdx.x, tile_col = tile * (32 * V) + c;
+    if (c < V * g && tile_col < nc) {
       float a = 0.0f, bv = -INFINITY;
       int32_t bi = 0x7fffffff;
 #pragma unroll
@@ -270,7 +332,7 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
   if (lane < g && colok) {
     const size_t o = static_cast<size_t>(b) * nc + col;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < V; ++j) {
       if (sum) sum[o + j] = acc[j];
       if (mx) mx[o + j] = best[j];
       if (amax) amax[o + j] = bidx[j];
@@ -396,21 +458,28 @@ int launch_reduce_outer(const float* t, float* sum, float* mx, int32_t* amax, ui
   // p0: vectors per lane (1|2), p1: warps splitting k (4|8|16), p2: CTAs per SM, p3: CTAs splitting k (forced).
   const int cv = tn.p0 > 0 ? tn.p0 : 1;
   const int kw = tn.p1 > 0 ? tn.p1 : 8;
-  if (vec && tn.p0 <= 0 && tn.p1 <= 0 && tn.p3 <= 0) {  // narrow rows, short reduced axes: a warp per (b, column tile)
-    const uint32_t g = outer_flat_groups(nb, nk, nc, sm_count());
+  // narrow rows, short reduced axes: a warp per (b, column tile); p1 == 1 takes the warps whatever the shape
+  if (tn.p0 <= 0 && (tn.p1 <= 0 || tn.p1 == 1) && tn.p3 <= 0) {
+    const uint32_t g = tn.p1 == 1 ? outer_flat_width(nc, vec) : outer_flat_groups(nb, nk, nc, sm_count(), vec);
     if (g != 0) {
-      const uint32_t tiles_per_b = (nc + 127) / 128;
+      const uint32_t tile = vec ? 128 : 32;
+      const uint32_t tiles_per_b = (nc + tile - 1) / tile;
       const uint64_t work = static_cast<uint64_t>(nb) * tiles_per_b;
       uint32_t klen = nk;
-      uint32_t ksplit = outer_flat_ranges(nb, nk, nc, g, sm_count(), kMaxPartialCells, &klen);
+      uint32_t ksplit = outer_flat_ranges(nb, nk, nc, g, vec, sm_count(), kMaxPartialCells, &klen);
       float* part = ksplit > 1 ? outer_scratch(s) : nullptr;
       if (part == nullptr) {
         ksplit = 1;
         klen = nk;
       }
       const uint64_t grid = ksplit > 1 ? work * ksplit : (work + 7) / 8;  // a CTA per range, or eight tiles per CTA
-      reduce_outer_flat<4><<<static_cast<unsigned>(grid), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g, ksplit,
-                                                                       klen, part);
+      if (vec) {
+        reduce_outer_flat<4, 4><<<static_cast<unsigned>(grid), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g,
+                                                                            ksplit, klen, part);
+      } else {  // 4-byte loads need more of them in flight for the same bytes
+        reduce_outer_flat<16, 1><<<static_cast<unsigned>(grid), 256, 0, s>>>(t, sum, mx, amax, nb, nk, nc, tiles_per_b, g,
+                                                                             ksplit, klen, part);
+      }
       count_launch();
       int rc = check_launch("reduce_outer_flat");
       if (rc != TCAB_OK || ksplit == 1) return rc;

@@ -326,8 +326,12 @@ def test_row_kernel_shape_rules(tcab_lib):
     # narrow rows: the whole row is one tile of nc / 4 column groups
     assert [plan(rows=100000, nk=256, nc=c)[0] for c in (4, 8, 16, 32)] == [1, 2, 4, 8]
     assert plan(rows=100000, nk=256, nc=64)[0] == 16 and plan(rows=1000, nk=256, nc=64)[0] == 0   # 64 columns: only with many warps
-    assert plan(rows=100000, nk=256, nc=12)[0] == 0 and plan(rows=100000, nk=256, nc=96)[0] == 0  # not 4 * 2^i / between 64 and 128
-    assert plan(rows=100000, nk=256, nc=6)[0] == 0                                                # not whole vectors
+    assert plan(rows=100000, nk=256, nc=12)[0] == 3 and plan(rows=100000, nk=256, nc=48)[0] == 12  # any number of groups
+    assert plan(rows=100000, nk=256, nc=96)[0] == 0 and plan(rows=100000, nk=16, nc=96)[0] == 24   # 65 ... 127 columns: short axes
+    # rows that are not whole vectors: groups of one column, tiles of 32 columns
+    assert [plan(rows=100000, nk=256, nc=c)[0] for c in (1, 3, 6, 7, 31)] == [1, 3, 6, 7, 31]
+    assert plan(rows=100000, nk=256, nc=33)[0] == 32 and plan(rows=100000, nk=8, nc=2050)[0] == 32
+    assert plan(rows=2, nk=1 << 20, nc=33)[0] == 0 and plan(rows=2, nk=1 << 20, nc=15)[0] == 15   # few long columns
     # short reduced axes with wide rows: 32 groups of a 128-column tile; long axes keep a CTA per tile
     assert plan(rows=65536, nk=4, nc=1024)[0] == 32 and plan(rows=65536, nk=64, nc=1024)[0] == 0
     # a handful of long columns: the warps share the k axis as well (test_outer_flat_ranges)

@@ -1130,7 +1130,11 @@ def test_short_rows(oracle, cuda, rows, cols):
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nb,nk,nc", [(3000, 256, 4), (2500, 300, 8), (1300, 77, 16), (700, 1000, 32), (4000, 4, 1024),
                                       (2000, 8, 256), (900, 33, 64), (5000, 1, 4), (1200, 63, 132), (600, 5, 2052),
-                                      (1, 7, 8), (3, 2, 4)])
+                                      (1, 7, 8), (3, 2, 4),
+                                      # any number of column groups; rows that are not whole vectors (4-byte loads)
+                                      (2000, 256, 12), (1100, 90, 20), (800, 300, 48), (900, 40, 100), (3000, 64, 6),
+                                      (1500, 100, 7), (2500, 33, 3), (4000, 17, 1), (700, 8, 2050), (900, 31, 33),
+                                      (1200, 200, 31), (5, 3, 2)])
 def test_middle_axis_chains_warp_per_tile(oracle, cuda, nb, nk, nc):
     rng = np.random.default_rng(nb + nk + nc)
     x = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
@@ -1180,11 +1184,36 @@ def test_middle_axis_chains_warp_per_tile(oracle, cuda, nb, nk, nc):
     assert torch.equal(only["argmax"], got["argmax"])
 
 
+@pytest.mark.parametrize("nb,nk,nc", [(600, 300, 130), (40, 1000, 1023), (300, 500, 68), (2000, 70, 33), (50, 2000, 256)])
+def test_middle_axis_warps_forced_on_other_shapes(oracle, cuda, nb, nk, nc):
+    """The warp-per-tile kernels on shapes the library gives to a CTA per tile: same results."""
+    rng = np.random.default_rng(nb + nk + nc)
+    x = np.round(rng.uniform(-1, 1, (nb, nk, nc)) * 16).astype(np.float32) / 16
+    xd = dev_f32(x, cuda)
+    want = T.reduce_outer(xd)
+    wsum = T.chain_reduce([xd], "p0 * p0", axis=1, init=0.25)
+    try:
+        T.tune("reduce_outer", 0, 1, 0, 0)
+        T.tune("reduce_inner", 32, 0, 0, 0)
+        got = T.reduce_outer(xd)
+        gsum = T.chain_reduce([xd], "p0 * p0", axis=1, init=0.25)
+    finally:
+        T.tune("reduce_outer")
+        T.tune("reduce_inner")
+    assert torch.equal(got["max"], want["max"]) and torch.equal(got["argmax"], want["argmax"])
+    assert np.array_equal(got["argmax"].cpu().numpy(), x.argmax(1).astype(np.int32))
+    x64 = x.astype(np.float64)
+    assert (np.abs(got["sum"].cpu().numpy() - x64.sum(1)) <= 1e-5 * np.abs(x64).sum(1) + 1e-30).all()
+    ref = (x64 * x64).sum(1) + 0.25
+    assert (np.abs(gsum.cpu().numpy() - ref) <= 1e-5 * ref).all() and (np.abs(wsum.cpu().numpy() - ref) <= 1e-5 * ref).all()
+
+
 # ----------------------------------------------------------------------------
 # column statistics of tall matrices: few column tiles, a long reduced axis -- the warps share the k axis too
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nb,nk,nc", [(1, 1 << 20, 8), (1, 262144, 128), (4, 131072, 64), (3, 100003, 16), (1, 70001, 512),
-                                      (2, 40000, 1024), (1, 1 << 21, 4), (1, 1025, 32), (5, 30011, 260)])
+                                      (2, 40000, 1024), (1, 1 << 21, 4), (1, 1025, 32), (5, 30011, 260),
+                                      (1, 700001, 3), (2, 100001, 7), (1, 150000, 20), (3, 50001, 30)])
 def test_column_statistics_of_tall_matrices(oracle, cuda, nb, nk, nc):
     rng = np.random.default_rng(nb + nk + nc)
     x = rng.uniform(-1, 1, (nb, nk, nc)).astype(np.float32)
