@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kOuterFlat1, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kOuterFlat1, kInnerRag4, kInnerRag32, kInnerRag256, kInnerRows32e, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
 };
 
 struct JitChain {
@@ -170,6 +170,10 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kInnerFlat] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat2] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ", 2>";
     names[kInnerRows32] = "tcabk::chain_inner_rows32<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
+    names[kInnerRows32e] = "tcabk::chain_inner_rows32e<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
+    names[kInnerRag4] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 4, " + bf + ", 128, 0, 0, 1>";
+    names[kInnerRag32] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 128, 0, 0, 1>";
+    names[kInnerRag256] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 256, 4, " + bf + ", 256, 0, 0, 1>";
     }
   } else if (sp.kind == 'B') {
     const char* shapes[4] = {"32, 4", "256, 4", "32, 1", "256, 1"};
@@ -326,6 +330,19 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
       void* af[] = {ptrs, &out, &outer, &nv, &init, &caps};
       return launch(jc->k[kInnerRows32], (outer + warps * 32ull - 1) / (warps * 32ull), 32 * warps, af, s, "chain_inner_rows32",
                     static_cast<size_t>(warps) * jc->n_in * 32 * (nvec + 1) * 16);
+    }
+    // rows that are not whole vectors on aligned operands (same policy as the ahead-of-time path)
+    if (al && !vec && tune(kReduceInner).p0 <= 0 && jc->k[kInnerRows32e] != nullptr) {
+      const uint32_t warps = rows32e_warps(nk, jc->n_in);
+      void* af[] = {ptrs, &out, &outer, &nk, &init, &caps};
+      if (nk <= 64 && outer >= 1024 && warps >= 1)
+        return launch(jc->k[kInnerRows32e], (outer + warps * 32ull - 1) / (warps * 32ull), 32 * warps, af, s,
+                      "chain_inner_rows32e", static_cast<size_t>(warps) * jc->n_in * 32 * nk * 4);
+      if (nk > 64) {  // the thresholds of whole-vector rows
+        if (nk / 4 <= 64) return launch(jc->k[kInnerRag4], (outer + 31) / 32, 128, af, s, "chain_inner");
+        const bool cta = nk / 4 >= inner_cta_per_row_from(jc->n_in);
+        return launch(jc->k[cta ? kInnerRag256 : kInnerRag32], cta ? outer : (outer + 3) / 4, cta ? 256 : 128, af, s, "chain_inner");
+      }
     }
     if (vec && nvec >= 1 && (nvec <= 32 || (nvec > 48 && nvec <= 64)) && outer >= 1024 && jc->k[kInnerFlat] != nullptr &&
         tune(kReduceInner).p0 <= 0) {

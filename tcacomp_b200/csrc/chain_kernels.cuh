@@ -221,6 +221,49 @@ __device__ __forceinline__ float fold_row_share(const float* const* p, u64 row, 
   return acc;
 }
 
+// The same for rows that are not whole 16-byte vectors although the operands are aligned (nk % 4 != 0): a row then
+// starts 0 ... 3 elements before a vector boundary. The thread takes the row's whole vectors as above; the up to six
+// elements before the first and after the last of them go to threads 0, 1, ... one each (two with four threads),
+// loaded before the vector loop so that their latency overlaps with it. TPR >= 4.
+template <class Map, class C, int NIN, int TPR, int BF>
+__device__ __forceinline__ float fold_row_share_ragged(const float* const* p, u64 row, u32 nk, int t, const float* caps) {
+  constexpr int EDGES = TPR >= 6 ? 1 : 2;  // edge elements a thread may get
+  const u64 e0 = row * nk;
+  u32 head = (4u - static_cast<u32>(e0 & 3u)) & 3u;
+  if (head > nk) head = nk;
+  const u64 v0 = (e0 + head) >> 2;
+  const u32 nfull = (nk - head) >> 2, tail = nk - head - 4 * nfull;
+  float edge[EDGES][NIN][1];
+#pragma unroll
+  for (int q = 0; q < EDGES; ++q) {
+    const u32 e = t + q * TPR;
+    if (e < head + tail) LoadAll<1, BF, NIN>::at(p, e < head ? e0 + e : e0 + 4 * nfull + e, edge[q]);  // tail: e0 + head + 4 nfull + (e - head)
+  }
+  float acc = C::identity();
+#pragma unroll 8
+  for (u32 idx = t; idx < nfull; idx += TPR) {
+    float f[NIN][4];
+    LoadAll<4, BF, NIN>::at(p, v0 + idx, f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) v[a] = f[a][j];
+      acc = C::apply(acc, Map::apply(v, caps));
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < EDGES; ++q) {
+    if (t + q * TPR < head + tail) {
+      float v[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) v[a] = edge[q][a][0];
+      acc = C::apply(acc, Map::apply(v, caps));
+    }
+  }
+  return acc;
+}
+
 // The partials of the TPR threads of a row group meet: every thread returns the row's fold. `slots` is
 // 2 x 32 floats of shared memory, alternated by `iter` so that a slot is rewritten only after everyone read it.
 template <class C, int TPR>
@@ -243,8 +286,9 @@ __device__ __forceinline__ float fold_row_group(float acc, float (*slots)[32], u
 // thread (bit-identical to the reference's SeqReducer order). THREADS is the CTA size: 128 (256 for a CTA
 // per row) by default; small problems take 1024-thread CTAs, because a launch costs by the CTA (measured in a
 // graph of dependent launches: an empty grid of 1024 x 128 threads 1.7 us, of 148 x 1024 threads 0.8 us).
+// RAG: rows that are not whole vectors on aligned operands (V == 4, no broadcast operands): fold_row_share_ragged.
 template <class Map, class Post, int COMBINE, int NIN, int TPR, int V, int BF = 0, int THREADS = inner_cta_threads(TPR),
-          int RB = 0, int CB = 0>
+          int RB = 0, int CB = 0, int RAG = 0>
 __global__ void __launch_bounds__(THREADS)
 chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
   typedef Comb<COMBINE> C;
@@ -263,7 +307,7 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
   // it cannot observe a stale value even if the previous grid is still writing that row; it turns the
   // DRAM latency of a short kernel's first loads into overlap with the previous kernel's tail.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if constexpr (V == 4) {
+  if constexpr (V == 4 && RAG == 0) {
     const u64 first = static_cast<u64>(blockIdx.x) * GROUPS + g;
     if (t == 0 && first < rows && nk >= 4) {
       const u32 bytes = nk * 4u < 65536u ? nk * 4u : 65536u;  // nk % 4 == 0 and 16-byte aligned rows on this path
@@ -280,7 +324,11 @@ chain_inner(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init
     const u64 row = row0 + g;
     const bool live = row < rows;
     float acc = C::identity();
-    if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF, RB, CB>(ins.p, row, nvec, t, caps.c);  // nk % V == 0
+    if constexpr (RAG != 0) {
+      if (live) acc = fold_row_share_ragged<Map, C, NIN, TPR, BF>(ins.p, row, nk, t, caps.c);
+    } else {
+      if (live) acc = fold_row_share<Map, C, NIN, TPR, V, BF, RB, CB>(ins.p, row, nvec, t, caps.c);  // nk % V == 0
+    }
     acc = fold_row_group<C, TPR>(acc, slots, iter);
     if (live && t == 0) {
       float r[1] = {C::apply(init, acc)};
@@ -398,6 +446,74 @@ chain_inner_rows32(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nvec, f
         for (int a = 0; a < NIN; ++a) p[a] = f[a][e];
         acc = C::apply(acc, Map::apply(p, caps.c));
       }
+    }
+    float res[1] = {C::apply(init, acc)};
+    out[row_base + lane] = Post::apply(res, caps.c + 8);
+  }
+}
+
+// The same for short rows that are not whole vectors (nk % 4 != 0, aligned operands, nk <= 64): the 32 rows of a warp
+// start at element 32 m nk -- a 128-byte boundary -- and are 8 nk whole vectors, whatever nk is, so the warp copies
+// them as they lie (cp.async, 16 bytes; the last, shorter group of rows ends with up to three single elements) and
+// lane r folds elements r nk ... r nk + nk - 1 of the copy in ascending order. Rows of an odd length fall on
+// different banks; nk = 2 (mod 4) costs two-way conflicts.
+// Dynamic shared memory: warps * NIN * 32 * nk * 4 bytes; blockDim.x = 32 * warps.
+template <class Map, class Post, int COMBINE, int NIN, int BF = 0>
+__global__ void __launch_bounds__(256)
+chain_inner_rows32e(Ptrs<NIN> ins, float* __restrict__ out, u64 rows, u32 nk, float init, Caps caps) {
+  typedef Comb<COMBINE> C;
+  extern __shared__ __align__(16) unsigned char rows32_smem[];
+  const u32 lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const u64 row_base = (static_cast<u64>(blockIdx.x) * warps + warp) * 32;
+  if (row_base >= rows) return;  // the whole warp leaves
+  const u32 nrows = rows - row_base < 32 ? static_cast<u32>(rows - row_base) : 32u;
+  unsigned char* area = rows32_smem + static_cast<size_t>(warp) * NIN * 32 * nk * 4;
+  const u32 total = nrows * nk, nvec = total >> 2;
+  const u64 e0 = row_base * nk;  // a multiple of 32 elements
+  for (u32 v = lane; v < nvec; v += 32) {
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      unsigned char* slab = area + static_cast<size_t>(a) * 32 * nk * 4;
+      if ((BF >> a) & 1) {
+        const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(slab + static_cast<size_t>(v) * 8));
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(ins.p[a]) + (e0 + 4ull * v) * 2;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+      } else {
+        const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(slab + static_cast<size_t>(v) * 16));
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(ins.p[a]) + (e0 + 4ull * v) * 4;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
+    }
+  }
+  if (lane < (total & 3u)) {  // the end of the last group of rows
+    const u32 e = 4 * nvec + lane;
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      unsigned char* slab = area + static_cast<size_t>(a) * 32 * nk * 4;
+      if ((BF >> a) & 1) {
+        reinterpret_cast<unsigned short*>(slab)[e] = reinterpret_cast<const unsigned short*>(ins.p[a])[e0 + e];
+      } else {
+        reinterpret_cast<float*>(slab)[e] = ins.p[a][e0 + e];
+      }
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncwarp();
+  if (lane < nrows) {
+    float acc = C::identity();
+    const u32 first = lane * nk;
+    for (u32 j = 0; j < nk; ++j) {
+      float p[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        const unsigned char* slab = area + static_cast<size_t>(a) * 32 * nk * 4;
+        if ((BF >> a) & 1) {
+          p[a] = bf16_bits_to_float(reinterpret_cast<const unsigned short*>(slab)[first + j]);
+        } else {
+          p[a] = reinterpret_cast<const float*>(slab)[first + j];
+        }
+      }
+      acc = C::apply(acc, Map::apply(p, caps.c));
     }
     float res[1] = {C::apply(init, acc)};
     out[row_base + lane] = Post::apply(res, caps.c + 8);

@@ -115,11 +115,11 @@ struct Args {
   cudaStream_t stream;
 };
 
-template <class Map, class Post, int COMBINE, int TPR, int V, int THREADS = tcabk::inner_cta_threads(TPR)>
+template <class Map, class Post, int COMBINE, int TPR, int V, int THREADS = tcabk::inner_cta_threads(TPR), int RAG = 0>
 int launch_inner(const Args& a) {
   constexpr int NIN = Map::kIn;
   constexpr int GROUPS = THREADS / TPR;
-  auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V, 0, THREADS>;
+  auto* fn = tcabk::chain_inner<Map, Post, COMBINE, NIN, TPR, V, 0, THREADS, 0, 0, RAG>;
   Ptrs<NIN> ptrs;
   for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
   // one CTA per group of rows; the kernel's row loop only matters beyond 2^31 - 1 CTAs
@@ -160,6 +160,22 @@ int launch_inner_rows32(const Args& a, uint32_t nvec, uint32_t warps) {
   fn<<<static_cast<unsigned>(grid), 32 * warps, smem, a.stream>>>(ptrs, a.out, a.outer, nvec, a.init, a.caps);
   count_launch();
   return check_launch("chain_inner_rows32");
+}
+
+// Short rows that are not whole vectors, a thread per row over a copy of the rows as they lie: chain_inner_rows32e.
+template <class Map, class Post, int COMBINE>
+int launch_inner_rows32e(const Args& a, uint32_t warps) {
+  constexpr int NIN = Map::kIn;
+  auto* fn = tcabk::chain_inner_rows32e<Map, Post, COMBINE, NIN>;
+  Ptrs<NIN> ptrs;
+  for (int i = 0; i < NIN; ++i) ptrs.p[i] = a.ins[i];
+  const uint64_t rows_per_cta = static_cast<uint64_t>(warps) * 32;
+  const uint64_t grid = (a.outer + rows_per_cta - 1) / rows_per_cta;
+  if (grid > 0x7fffffffull) return fail(TCAB_ERR_TOO_LARGE, "chain_reduce: too many rows");
+  const size_t smem = static_cast<size_t>(warps) * NIN * 32 * a.nk * 4;
+  fn<<<static_cast<unsigned>(grid), 32 * warps, smem, a.stream>>>(ptrs, a.out, a.outer, a.nk, a.init, a.caps);
+  count_launch();
+  return check_launch("chain_inner_rows32e");
 }
 
 // Short rows (at most 128 vectors): g lanes per row, VPL vectors per lane beyond 32, see chain_inner_flat.
@@ -315,6 +331,16 @@ int launch_chain(const Args& a) {
     // measured: a warp per row for mid-length rows, a CTA per row for long ones (8192 columns: 4.6 -> 7.1 TB/s)
     // (a CTA per row from 640 vectors, from 384 with two or more operands: 3072 columns 6.4 -> 7.1 TB/s, 4092 5.1 -> 6.8,
     //  two operands at 1536 columns 6.9 -> 7.4)
+    // rows that are not whole vectors on aligned operands: up to 64 elements a thread per row over a copy of the rows
+    // as they lie; longer rows with 16-byte loads between their ragged ends (tune p0 keeps the 4-byte kernels)
+    if (al && !vec && tune(kReduceInner).p0 <= 0) {
+      if (a.nk <= 64 && a.outer >= 1024 && rows32e_warps(a.nk, NIN) >= 1)
+        return launch_inner_rows32e<Map, Post, COMBINE>(a, rows32e_warps(a.nk, NIN));
+      if (a.nk > 64)  // the thresholds of whole-vector rows
+        return a.nk / 4 <= 64                            ? launch_inner<Map, Post, COMBINE, 4, 4, 128, 1>(a)
+               : a.nk / 4 < inner_cta_per_row_from(NIN) ? launch_inner<Map, Post, COMBINE, 32, 4, 128, 1>(a)
+                                                        : launch_inner<Map, Post, COMBINE, 256, 4, 256, 1>(a);
+    }
     int tpr = nvec <= 16 ? 1 : nvec <= 64 ? 4 : nvec < (vec ? inner_cta_per_row_from(NIN) : 1024u) ? 32 : 256;
     const Tune& tn = tune(kReduceInner);
     if (tn.p0 == 1 || tn.p0 == 4 || tn.p0 == 32 || tn.p0 == 256) tpr = tn.p0;

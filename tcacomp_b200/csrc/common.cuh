@@ -195,6 +195,13 @@ inline uint32_t rows32_warps(uint32_t nvec, int n_in) {
   return w >= 8 ? 8u : static_cast<uint32_t>(w);
 }
 
+// chain_inner_rows32e (rows of nk elements that are not whole vectors): the same bound.
+inline uint32_t rows32e_warps(uint32_t nk, int n_in) {
+  const uint64_t per_warp = static_cast<uint64_t>(n_in) * 32 * nk * 4;
+  const uint64_t w = per_warp ? (48 * 1024) / per_warp : 0;
+  return w >= 8 ? 8u : static_cast<uint32_t>(w);
+}
+
 // fp32 operands, plain product: each operand is cut into three bf16 pieces and the six significant piece products
 // run as ONE bf16 tensor-core contraction over 6 K. Returns TCAB_ERR_UNSUPPORTED (without a message) when the shape
 // does not qualify or the workspace would exceed its cap: the caller keeps the scalar kernel.

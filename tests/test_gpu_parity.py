@@ -1126,6 +1126,51 @@ def test_short_rows(oracle, cuda, rows, cols):
 
 
 # ----------------------------------------------------------------------------
+# innermost-axis chains on rows that are not whole 16-byte vectors (aligned operands)
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(5000, 1), (4001, 2), (3000, 3), (2049, 5), (2500, 7), (1500, 13), (1200, 33),
+                                       (1025, 63), (1024, 62), (1100, 65), (1300, 127), (1111, 129), (1030, 255),
+                                       (1500, 1023), (1026, 1025), (300, 2563), (200, 4097), (40, 30001), (500, 7),
+                                       (33, 3), (7, 129)])
+def test_innermost_rows_that_are_not_whole_vectors(oracle, cuda, rows, cols):
+    rng = np.random.default_rng(rows + cols)
+    x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)
+    z = rng.uniform(0, 1, (rows, cols)).astype(np.float32)
+    xd, zd = dev_f32(x, cuda), dev_f32(z, cuda)
+    x64 = x.astype(np.float64)
+    expr = "(0.5f * p0 + 0.25f) * (0.5f * p0 + 0.25f)"
+    buf, out = guarded((rows,), torch.float32, cuda)
+    n0 = T.launch_count()
+    T.chain_reduce([xd], expr, axis=1, out=out)
+    assert T.launch_count() - n0 <= 2          # two when few long rows are split over CTAs
+    got = out.cpu().numpy()
+    check_guards(buf, torch.float32)
+    from oracle import checks
+    assert checks.rowsum_close(got, x)
+    try:        # the kernels on 4-byte loads: a thread per row (the reference's order), a warp per row
+        T.tune("reduce_inner", 1)
+        seq = T.chain_reduce([xd], expr, axis=1).cpu().numpy()
+        T.tune("reduce_inner", 32)
+        old = T.chain_reduce([xd], expr, axis=1).cpu().numpy()
+    finally:
+        T.tune("reduce_inner")
+    assert (np.abs(got - old) <= 2e-5 * np.abs(old) + 1e-30).all()
+    if cols <= 64 and rows >= 1024:   # a thread folds its row in ascending order: the same BITS as the sequential kernel
+        assert np.array_equal(got, seq)
+    # max with init and a piped map: bit-exact
+    got = T.chain_reduce([xd], "p0", combine_expr="fmaxf(p0, p1)", init=0.25, axis=1, post_expr="p0 + 1.0f").cpu().numpy()
+    assert np.array_equal(got, np.maximum(x.max(1), np.float32(0.25)) + np.float32(1))
+    # run-time compiled, two operands, one of them bf16; then three fp32 operands
+    zb = oracle.f32_to_bf16(z)
+    got = T.chain_reduce([xd, dev_bf16(zb, cuda)], "expf(p0) * f32(p1)", axis=1).cpu().numpy()
+    want = (np.exp(x64) * oracle.bf16_to_f32(zb)).sum(1)
+    assert (np.abs(got - want) <= 1e-5 * want + 1e-30).all()
+    got = T.chain_reduce([xd, zd, xd], "p0 * p1 + p2 * p2", init=2.0, axis=1).cpu().numpy()
+    want = (x64 * z + x64 * x64).sum(1) + 2.0
+    assert (np.abs(got - want) <= 1e-5 * (np.abs(x64 * z) + x64 * x64).sum(1) + 1e-5).all()
+
+
+# ----------------------------------------------------------------------------
 # middle-axis chains on narrow rows and short reduced axes: a warp per (b, column tile)
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("nb,nk,nc", [(3000, 256, 4), (2500, 300, 8), (1300, 77, 16), (700, 1000, 32), (4000, 4, 1024),
