@@ -370,6 +370,17 @@ class ReduceOuterNarrow(ReduceOuter):
     profile = "reduce_outer_flat_reduce_outer_f32_65536x256x16.md"
 
 
+class ReduceOuterColumnStats(ReduceOuter):
+    """Column statistics of a tall narrow matrix: one batch, 2^23 rows of 16 columns. CTAs of the warp-per-tile
+    kernel share the reduced axis and a second launch folds their partial states; selectable only (one unit: it
+    does not shard)."""
+    name = "reduce_outer_f32_1x8388608x16"
+    full_units, nk, nc = 1, 8388608, 16
+    launches_per_step = 2
+    shape = "t fp32 [1, 8388608, 16] ~ U(-100,100) -> sum f32, max f32, argmax i32 [1, 16] in one pass over t"
+    profile = "reduce_outer_flat_reduce_outer_f32_1x8388608x16.md"
+
+
 class MapRowsum(Workload):
     name = "map_rowsum_f32_4096x1024"
     dtype = "f32"
@@ -597,7 +608,7 @@ class ShortRowsum(Workload):
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
 SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows,
                                 LayernormHeadRows.name: LayernormHeadRows, ReduceOuterNarrow.name: ReduceOuterNarrow,
-                                ShortRowsum.name: ShortRowsum})
+                                ReduceOuterColumnStats.name: ReduceOuterColumnStats, ShortRowsum.name: ShortRowsum})
 DEFAULT = SoftmaxRows.name
 
 
