@@ -350,8 +350,11 @@ gemm_bias_act_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (i < 4 && num_kb > 0) ptx::tmem_ld_32x32(tm_warp + UMMA_N + q * 32, r[q]);  // refill from accumulator 1
         ptx::fence_proxy_async();  // the TMA engine reads what the threads just wrote
         __syncwarp();
-        if (lane == 0 && row0 < M && col0 < N) {  // a box that starts inside the tensor; the hardware clips its edges
-          ptx::tma_store_2d(&tmap_c, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
+        if (lane == 0) {
+          // a box that starts inside the tensor; the hardware clips its edges. A box that lies outside still commits
+          // an (empty) group: the wait above counts groups, and with a group missing it would let this warp restage
+          // a buffer whose store is still being read (N = 256 j + 129 ... 160: a stored box, then three skipped ones)
+          if (row0 < M && col0 < N) ptx::tma_store_2d(&tmap_c, buf, static_cast<int32_t>(col0), static_cast<int32_t>(row0));
           ptx::tma_store_commit();
         }
       }

@@ -834,6 +834,25 @@ def test_gemm_without_bias_and_empty_k(oracle, cuda):
     assert np.array_equal(c0, np.broadcast_to(want0, (64, 64)))
 
 
+@pytest.mark.parametrize("m,n,k", [(4000, 5000, 3000), (4096, 2440, 256), (2304, 2184, 1024), (4096, 5064, 512)])
+def test_gemm_large_ragged_shapes_exact_on_small_integers(cuda, m, n, k):
+    """Many 256 x 256 tiles with ragged edges in every dimension, small integers so that every element is exact: the
+    last tile column holds boxes that start inside N followed by boxes that lie outside (N = 256 j + 136, + 184: a
+    warp's staging buffers must not be refilled while a store of the previous box still reads them)."""
+    gen = torch.Generator(device=cuda).manual_seed(m + n + k)
+    a = torch.randint(-2, 3, (m, k), generator=gen, device=cuda).to(torch.bfloat16)
+    b = torch.randint(-2, 3, (k, n), generator=gen, device=cuda).to(torch.bfloat16)
+    bias = torch.randint(-4, 5, (n,), generator=gen, device=cuda).float()
+    want = (a.float() @ b.float() + bias).to(torch.bfloat16)      # |sums| < 2^24: exact in fp32
+    for _ in range(3):                                             # a race does not show every time
+        buf, out = guarded((m, n), torch.bfloat16, cuda)
+        T.gemm_bias_act(a, b, bias, "none", out=out)
+        check_guards(buf, torch.bfloat16)
+        bad = (out != want)
+        assert not bool(bad.any()), f"{int(bad.sum())} mismatches, first at {bad.nonzero()[0].tolist()}"
+    assert T.device_status() == 0
+
+
 def test_gemm_exact_on_small_integers(oracle, cuda):
     # products and sums of small integers are exact in bf16/fp32: every accumulation order agrees bit for bit
     rng = np.random.default_rng(3)
