@@ -206,7 +206,7 @@ __device__ __forceinline__ float fold_row_share(const float* const* p, u64 row, 
   float acc = C::identity();
   float rowval[NIN];
   LoadRowAll<V, BF, RB, CB, NIN>::row_values(p, row, rowval);
-#pragma unroll 8
+#pragma unroll(V == 1 ? 16 : 8)
   for (u32 idx = t; idx < nvec; idx += TPR) {
     float f[NIN][V];
     LoadRowAll<V, BF, RB, CB, NIN>::at(p, row, nvec, idx, rowval, f);
@@ -578,7 +578,7 @@ chain_inner_split(Ptrs<NIN> ins, float* __restrict__ partials, u32 nk, u32 split
   const u32 v1 = (nvec - v0 < vec_per_split) ? nvec : v0 + vec_per_split;
   float acc = C::identity();
   if (v0 < nvec) {
-#pragma unroll 4
+#pragma unroll(V == 1 ? 16 : 4)  // 4-byte loads need more of them in flight for the same bytes
     for (u32 idx = v0 + threadIdx.x; idx < v1; idx += 256) {
       float f[NIN][V];
       LoadAll<V, BF, NIN>::at(ins.p, vbase + idx, f);

@@ -1145,6 +1145,37 @@ def test_short_rows(oracle, cuda, rows, cols):
 
 
 # ----------------------------------------------------------------------------
+# element counts just below 2^32 (the reference's index type): byte offsets beyond 2^32
+# ----------------------------------------------------------------------------
+def test_element_counts_just_below_two_to_the_32(cuda):
+    free, _ = torch.cuda.mem_get_info(cuda)
+    if free < 60 * 2**30:
+        pytest.skip("needs 40 GB of free device memory")
+    rows, cols = (1 << 20) - 3, 4092                       # 4,290,760,716 elements, 17 GB
+    x = torch.empty((rows, cols), device=cuda)
+    for lo in range(0, rows, 1 << 16):
+        x[lo:lo + (1 << 16)].uniform_(-1, 1)
+    s = T.chain_reduce([x], "p0 * p0")
+    for lo in range(0, rows, 1 << 17):                     # every row, the last ones included
+        ref = (x[lo:lo + (1 << 17)].double() ** 2).sum(1)
+        assert bool(((s[lo:lo + (1 << 17)].double() - ref).abs() <= 1e-5 * ref).all())
+    y = T.map([x], "p0 * 2.0f + 1.0f")
+    assert torch.equal(y[-4096:], x[-4096:] * 2 + 1) and torch.equal(y[:4096], x[:4096] * 2 + 1)
+    pr = torch.tensor([0, rows // 2, rows - 2, rows - 1], device=cuda)
+    T.softmax_rows(x, out=y)
+    ref = torch.softmax(x[pr].double(), dim=1)
+    assert bool(((y[pr].double() - ref).abs() <= 2e-5 * ref).all())
+    del y
+    t = x.view(-1)[:65000 * 256 * 256].view(65000, 256, 256)
+    got = T.reduce_outer(t)
+    pb = torch.tensor([0, 33333, 64999], device=cuda)
+    assert torch.equal(got["max"][pb], t[pb].max(1).values)
+    first = (t[pb] == t[pb].max(1, keepdim=True).values).float().argmax(1).int()
+    assert torch.equal(got["argmax"][pb], first)
+    assert T.device_status() == 0
+
+
+# ----------------------------------------------------------------------------
 # innermost-axis chains on rows that are not whole 16-byte vectors (aligned operands)
 # ----------------------------------------------------------------------------
 @pytest.mark.parametrize("rows,cols", [(5000, 1), (4001, 2), (3000, 3), (2049, 5), (2500, 7), (1500, 13), (1200, 33),
