@@ -786,6 +786,13 @@ def measure_e2e(wl, steps, world, dev) -> dict:
     # a small problem (C1 moves 16 MiB per step) gets as many steps as move 1 GiB: ten of them are a 3 ms region that
     # mostly measures how the copy engines start up
     steps = max(steps, min(200, -(-(1 << 30) // max(1, wl.h2d + wl.d2h))))
+    # untimed: 0.1 s of the same steps. The phases before this one leave the GPU idle for seconds (parity checks and
+    # the CPU baseline run on the host) and the first copies after that run well below the link's rate.
+    t0 = time.perf_counter()
+    while time.perf_counter() - t0 < 0.1:
+        wl.e2e_step()
+        wl.e2e_join()
+        torch.cuda.synchronize()
     ms = timed(wl.e2e_step, steps, 3, world, dev, after=wl.e2e_join)
     return {"value": wl.e2e_work() * steps * world / (ms * 1e-3) / scale_of(wl), "unit": wl.unit,
             "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h, "steps": steps, "ms_per_step": ms / steps,
@@ -833,8 +840,11 @@ def copy_ceiling(world: int, dev, mib: int = 256, reps: int = 6) -> dict:
             cur.wait_stream(s_up)
             cur.wait_stream(s_dn)
 
-        once()
-        join()
+        t0 = time.perf_counter()   # untimed: 0.1 s of the same copies (measure_e2e warms up the same way)
+        while time.perf_counter() - t0 < 0.1:
+            once()
+            join()
+            torch.cuda.synchronize()
         barrier(world)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
