@@ -723,8 +723,9 @@ chain_outer_flat(Ptrs<NIN> ins, float* __restrict__ out, u32 nb, u32 nk, u32 nc,
   if (ksplit > 1) {
     work = blockIdx.x / ksplit;
     ks = blockIdx.x % ksplit;
-    kend = nk - ks * klen < klen ? nk : (ks + 1) * klen;
-    kbeg = ks * klen + warp * kstep;
+    const u32 first = ks * klen < nk ? ks * klen : nk;  // a range that would start past the end is empty
+    kend = nk - first < klen ? nk : first + klen;
+    kbeg = first + warp * kstep;
     if (kbeg > kend) kbeg = kend;
     kstep *= 8;
   } else {

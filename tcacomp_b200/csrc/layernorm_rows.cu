@@ -660,7 +660,8 @@ int launch_reg(const T* x, const T* gamma, const T* beta, float eps, T* y, uint6
   X(1, 1) X(2, 1) X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
   X(1024, 8) X(1024, 16)
 #define TCAB_LN_SHAPES_EXTRA(X) \
-  X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(1024, 1) X(256, 8) X(512, 8) X(64, 8) X(128, 2) X(256, 2)
+  X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(1024, 1) X(256, 8) X(512, 8) X(64, 8) X(128, 2) X(256, 2) \
+  X(16, 5) X(32, 5) X(64, 5) X(128, 5) X(256, 5) X(16, 3) X(32, 3) X(64, 3) X(128, 3) X(256, 3) X(512, 3)
 
 inline int launch_smem(const __nv_bfloat16* x, const __nv_bfloat16* gamma, const __nv_bfloat16* beta, float eps,
                        __nv_bfloat16* y, uint64_t rows, uint32_t cols, cudaStream_t s) {
@@ -696,7 +697,8 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
   // fp32 rows: eight slots per thread (32 row values) cost resident rows; four slots on twice the threads measured
   // ahead even when a quarter of them idle (1280 columns 5.4 -> 6.2 TB/s, 5120 4.8 -> 5.7, 7168 5.7 -> 6.4)
   bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt, /*small=*/true,
-                                   /*wide_penalty=*/sizeof(T) == 4 ? 0.25 : 0.03);
+                                   /*wide_penalty=*/sizeof(T) == 4 ? 0.25 : 0.03, /*odd_slots=*/vec,
+                                   /*five_slots_max_threads=*/sizeof(T) == 4 ? 32 : 256);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;

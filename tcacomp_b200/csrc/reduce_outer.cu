@@ -174,8 +174,9 @@ reduce_outer_flat(const float* __restrict__ t, float* __restrict__ sum, float* _
   if (ksplit > 1) {
     work = blockIdx.x / ksplit;
     ks = blockIdx.x % ksplit;
-    kend = nk - ks * klen < klen ? nk : (ks + 1) * klen;
-    kbeg = ks * klen + warp * kstep;
+    const uint32_t first = ks * klen < nk ? ks * klen : nk;  // a range that would start past the end is empty
+    kend = nk - first < klen ? nk : first + klen;
+    kbeg = first + warp * kstep;
     if (kbeg > kend) kbeg = kend;
     kstep *= 8;
   } else {

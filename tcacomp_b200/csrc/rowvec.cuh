@@ -147,10 +147,16 @@ inline bool choose_row_shape(uint32_t nvec, int vpt_target, int* tpr, int* vpt) 
 // (1024, 8..32) and, for 16-byte vectors, (128, 8), (256, 8), (64, 16), (32, 32) [plus (512, 8) and (64, 8)
 // where `wide8`] -- this picks the least waste, preferring fewer slots and 128..512 threads on a tie, and
 // staying at 32 row values per thread unless that wastes more than a third.
+// `odd_slots`: the caller also has (16..256, 5) and (16..512, 3) -- rows of 5 * 2^k and 3 * 2^k vectors (hidden sizes
+// 640, 768, 1280, 1536, 2560, 3072, 5120, 6144 ...) then fit exactly with every slot used (bf16 layer-norm, TB/s,
+// best power-of-two shape -> exact fit: 1280 columns 5.1 -> 6.1, 5120 5.1 -> 5.9, 1536 5.7 -> 6.1, 3072 5.9 -> 6.3).
+// fp32 rows gain from three slots everywhere but from five only with 32 threads per row (640 columns 6.4 -> 6.9; 64 x 5
+// at 1280 columns 6.4 -> 6.2, 256 x 5 at 5120 columns 5.8 -> 5.0): `five_slots_max_threads`.
 inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values_per_vector, int* tpr, int* vpt,
-                                 bool small = false, double wide_penalty = 0.03) {
+                                 bool small = false, double wide_penalty = 0.03, bool odd_slots = false,
+                                 int five_slots_max_threads = 256) {
   if (nvec == 0) nvec = 1;
-  struct Shape { int t, v; bool vec_only, wide_only; };
+  struct Shape { int t, v; bool vec_only, wide_only, odd_only; };
   // rows of one to four vectors: one, two or four threads per row (`small`: the aligned register kernels have
   // these shapes; with eight threads per row a 4-column softmax ran at 0.95 TB/s, seven of eight threads idle)
   if (small && nvec <= 4) {
@@ -163,16 +169,23 @@ inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values
       {32, 4, false, false},  {64, 4, false, false},   {128, 4, false, false},  {256, 4, false, false},
       {512, 4, false, false}, {1024, 4, false, false}, {1024, 8, false, false}, {1024, 16, false, false},
       {1024, 32, false, false}, {128, 8, true, false}, {256, 8, true, false},   {64, 16, true, false},
-      {32, 32, true, false},  {512, 8, true, true},    {64, 8, true, true}};
+      {32, 32, true, false},  {512, 8, true, true},    {64, 8, true, true},
+      {16, 3, true, false, true},  {32, 3, true, false, true},  {64, 3, true, false, true}, {128, 3, true, false, true},
+      {256, 3, true, false, true}, {512, 3, true, false, true}, {16, 5, true, false, true}, {32, 5, true, false, true},
+      {64, 5, true, false, true},  {128, 5, true, false, true}, {256, 5, true, false, true}};
   double best = 1e30;
   bool found = false;
   for (const Shape& sh : kShapes) {
-    if ((sh.vec_only && !vec) || (sh.wide_only && !wide8)) continue;
+    if ((sh.vec_only && !vec) || (sh.wide_only && !wide8) || (sh.odd_only && !odd_slots)) continue;
     if (static_cast<uint64_t>(sh.t) * sh.v < nvec) continue;
     const uint32_t used = (nvec + sh.t - 1) / sh.t;
+    if (sh.odd_only && used != static_cast<uint32_t>(sh.v)) continue;   // three or five slots only when all are used
+    if (sh.odd_only && sh.v == 5 && sh.t > five_slots_max_threads) continue;
     double score = static_cast<double>(used) * sh.t / nvec;        // 1.0 = exact fit
-    score *= 1.0 + wide_penalty * (sh.v > 4 ? (sh.v > 8 ? 2 : 1) : 0);  // more slots: more registers, fewer resident rows
-    if (sh.v * values_per_vector > 32) score *= 1.35;              // beyond 32 row values per thread the kernels lose occupancy
+    // more slots: more registers, fewer resident rows (five slots: a fifth of the penalty of eight)
+    score *= 1.0 + wide_penalty * (sh.v > 4 ? (sh.v > 8 ? 2.0 : sh.v > 5 ? 1.0 : 0.2) : 0.0);
+    score *= 1.0 + 0.02 * (sh.v - static_cast<int>(used));         // empty slots still cost their registers
+    if (sh.v * values_per_vector > (odd_slots ? 40 : 32)) score *= 1.35;  // beyond that many row values per thread the kernels lose occupancy
     if (sh.t >= 1024) score *= 1.15;                               // 1024-thread CTAs move in lock step
     else if (sh.t < 16 && nvec > 32) score *= 1.10;                // short groups: strided 16-byte loads (16 threads x
                                                                    // 4 slots measured AHEAD of 32 x 2 on 64-vector rows:

@@ -662,7 +662,9 @@ int launch_reg(const float* x, float* y, uint64_t rows, uint32_t cols, int ctas_
 #define TCAB_ROW_SHAPES_BASE(X) \
   X(1, 1) X(2, 1) X(4, 1) X(8, 1) X(8, 2) X(8, 4) X(16, 4) X(32, 4) X(64, 4) X(128, 4) X(256, 4) X(512, 4) X(1024, 4) \
   X(1024, 8) X(1024, 16) X(1024, 32)
-#define TCAB_ROW_SHAPES_EXTRA(X) X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(256, 8) X(1024, 1)
+#define TCAB_ROW_SHAPES_EXTRA(X) \
+  X(32, 32) X(64, 16) X(128, 8) X(512, 2) X(256, 8) X(1024, 1) \
+  X(16, 5) X(32, 5) X(16, 3) X(32, 3) X(64, 3) X(128, 3) X(256, 3) X(512, 3)
 
 }  // namespace
 
@@ -697,7 +699,8 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
     }
   }
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, &tpr, &vpt, /*small=*/true);
+  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, &tpr, &vpt, /*small=*/true, /*wide_penalty=*/0.03,
+                                   /*odd_slots=*/vec, /*five_slots_max_threads=*/32);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;
