@@ -1281,13 +1281,15 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
   if (m == 0 || n == 0) return TCAB_OK;
   const Tune& tn = tune(kGemm);
   // Which kernel: the 256 x 256 single-CTA kernel while its tiles fill the GPU; below that the double-buffered
-  // kernels, whose 128-row shares give twice the CTAs (measured 2048^3: 620 -> 820 TFLOP/s), single CTAs for one
-  // 128-row band, CTA pairs otherwise. tune p1 forces a kernel.
+  // kernels, whose 128-row tiles give twice the CTAs (measured 2048^3: 620 -> 820 TFLOP/s with CTA pairs, 905 with
+  // single CTAs). tune p1 forces a kernel.
   int variant = tn.p1;
   if (variant == 5) variant = m <= 128 ? 3 : 4;  // the cluster K split where it applies, else what these shapes get
   if (variant <= 0 && k > 0) {
     const uint64_t tiles256 = static_cast<uint64_t>((m + BM - 1) / BM) * ((n + BN - 1) / BN);
-    if (2 * tiles256 <= static_cast<uint64_t>(sm_count())) variant = m <= 128 ? 3 : 4;  // 128 tiles on 148 SMs: the default is faster
+    // (128 tiles on 148 SMs: the default is faster.) Single CTAs, not pairs: 2048^3 905 against 811 TFLOP/s,
+    // 1024 x 4096 x 4096 863 against 826, 1024^3 the same
+    if (2 * tiles256 <= static_cast<uint64_t>(sm_count())) variant = 3;
   }
   const bool default_kernel = !(variant == 3 || variant == 4 || (variant == 2 && k > 0));
   CUtensorMap ta, tb, tcm;
