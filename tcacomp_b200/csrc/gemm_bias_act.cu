@@ -1290,6 +1290,16 @@ int launch_gemm_bias_act(const __nv_bfloat16* a, const __nv_bfloat16* b, const f
     // (128 tiles on 148 SMs: the default is faster.) Single CTAs, not pairs: 2048^3 905 against 811 TFLOP/s,
     // 1024 x 4096 x 4096 863 against 826, 1024^3 the same
     if (2 * tiles256 <= static_cast<uint64_t>(sm_count())) variant = 3;
+    // A tile count just above a whole number of rounds leaves the last round nearly empty (320 tiles on 148 SMs:
+    // three rounds, 72 % of the CTA slots used). CTA pairs take a 256 x 256 tile per PAIR, so their rounds are half as
+    // long and the count rounds up to a multiple of 74 instead of 148; their K loop runs at about 0.88 of the
+    // single-CTA kernel's rate. Pairs where that trade pays (4000 x 5000 x 3000: 970 -> 1,100 TFLOP/s).
+    else {
+      const uint64_t sms = static_cast<uint64_t>(sm_count()), pairs = sms / 2;
+      const double fill1 = static_cast<double>(tiles256) / static_cast<double>((tiles256 + sms - 1) / sms * sms);
+      const double fill4 = static_cast<double>(tiles256) / static_cast<double>((tiles256 + pairs - 1) / pairs * pairs);
+      if (pairs > 0 && fill4 * 0.88 > fill1 * 1.02) variant = 4;
+    }
   }
   const bool default_kernel = !(variant == 3 || variant == 4 || (variant == 2 && k > 0));
   CUtensorMap ta, tb, tcm;

@@ -844,12 +844,16 @@ def test_gemm_large_ragged_shapes_exact_on_small_integers(cuda, m, n, k):
     b = torch.randint(-2, 3, (k, n), generator=gen, device=cuda).to(torch.bfloat16)
     bias = torch.randint(-4, 5, (n,), generator=gen, device=cuda).float()
     want = (a.float() @ b.float() + bias).to(torch.bfloat16)      # |sums| < 2^24: exact in fp32
-    for _ in range(3):                                             # a race does not show every time
-        buf, out = guarded((m, n), torch.bfloat16, cuda)
-        T.gemm_bias_act(a, b, bias, "none", out=out)
+    for variant in (0, 1, 0, 1, 4):                                # what the library picks, the 256 x 256 kernel, CTA pairs;
+        buf, out = guarded((m, n), torch.bfloat16, cuda)           # more than once: a race does not show every time
+        try:
+            T.tune("gemm", 0, variant, 0, 1 if variant else 0)
+            T.gemm_bias_act(a, b, bias, "none", out=out)
+        finally:
+            T.tune("gemm")
         check_guards(buf, torch.bfloat16)
         bad = (out != want)
-        assert not bool(bad.any()), f"{int(bad.sum())} mismatches, first at {bad.nonzero()[0].tolist()}"
+        assert not bool(bad.any()), f"variant {variant}: {int(bad.sum())} mismatches, first at {bad.nonzero()[0].tolist()}"
     assert T.device_status() == 0
 
 
