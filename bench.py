@@ -405,6 +405,7 @@ class MapRowsum(Workload):
         self.xs = [torch.rand((self.units, self.cols), generator=g, device=dev) * 2 - 1 for _ in range(self.copies)]
         self.ys = [torch.empty((self.units,), device=dev) for _ in range(self.copies)]
         self.y = self.ys[0]
+        self.bound_call = T.BoundChainReduce([self.xs[0]], self.EXPR, out=self.ys[0])
         self._launch_all()              # first calls outside capture (occupancy queries are cached)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
@@ -434,8 +435,9 @@ class MapRowsum(Workload):
 
     def step_as_specified(self):
         """The configuration exactly as stated: ONE [4096, 1024] buffer, one ordinary launch per step, no graph.
-        16.8 MB stay resident in the 126 MB L2 between steps, and every step pays the host's launch path."""
-        self.T.chain_reduce([self.xs[0]], self.EXPR, out=self.y)
+        16.8 MB stay resident in the 126 MB L2 between steps, and every step pays the host's launch path: one
+        tcab_chain_reduce call over descriptors built once, as a host of the reference keeps its tca::Tensor views."""
+        self.bound_call()
 
     def e2e_work(self):
         return self.work() / self.copies   # the end-to-end step moves and reduces ONE [4096, 1024] input
@@ -946,7 +948,8 @@ def run_workload(cls, args, rank, world, dev, peaks, peak_src, oracle, headline:
         n = max(steps, 50)
         per = wl.work() / wl.copies
         roofline["as_specified"] = {
-            "what": "one [4096, 1024] buffer (L2-resident after the first step), one ordinary launch per step, no CUDA graph",
+            "what": "one [4096, 1024] buffer (L2-resident after the first step), one ordinary launch per step (one "
+                    "tcab_chain_reduce call over descriptors built once), no CUDA graph",
             "ms_per_launch": a_ms / n, "achieved": per * n / (a_ms * 1e-3) / 1e9, "unit": "GB/s (L2-resident: not an HBM figure)",
             "frac_of_hbm_peak": per * n / (a_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     out.update({"value": value, "ms_per_step": ms / steps, "steps": steps, "roofline": roofline, "parity": parity,

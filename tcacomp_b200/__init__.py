@@ -6,9 +6,9 @@ streams, every operator below is one C-ABI call. Nothing here computes on the
 CPU and nothing falls back to torch.
 """
 from . import _lib
-from .ops import (chain_contract, chain_prepare, chain_reduce, chain_reduce_batched, release_all, release_stream, chain_reduce_noalloc, device_status, gemm_bias_act, launch_count, layernorm_rows, map, reduce_outer,
+from .ops import (BoundChainReduce, chain_contract, chain_prepare, chain_reduce, chain_reduce_batched, release_all, release_stream, chain_reduce_noalloc, device_status, gemm_bias_act, launch_count, layernorm_rows, map, reduce_outer,
                   softmax_rows, tune)
 from ._lib import TcabError
 
-__all__ = ["chain_contract", "chain_prepare", "chain_reduce", "chain_reduce_batched", "release_all", "release_stream", "chain_reduce_noalloc", "device_status", "gemm_bias_act", "launch_count", "layernorm_rows", "map", "reduce_outer",
+__all__ = ["BoundChainReduce", "chain_contract", "chain_prepare", "chain_reduce", "chain_reduce_batched", "release_all", "release_stream", "chain_reduce_noalloc", "device_status", "gemm_bias_act", "launch_count", "layernorm_rows", "map", "reduce_outer",
            "softmax_rows", "tune", "TcabError"]

@@ -252,6 +252,44 @@ def chain_reduce(ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str =
     return out
 
 
+class BoundChainReduce:
+    """tcab_chain_reduce with its descriptors built once and launched many times: the counterpart of a host that keeps
+    its tca::Tensor views (runtime/tca/tensor.h:16-40) and calls the generated launcher in a loop, as the reference's
+    runners do (testing/runners/common.cuh). Every call is one library call on the current (or the given) stream; the
+    object keeps the operands and the output alive, and the caller must not resize them while it is in use."""
+
+    def __init__(self, ins: Sequence[torch.Tensor], map_expr: str, combine_expr: str = "(p0 + p1)", init: float = 0.0,
+                 post_expr: Optional[str] = None, captures: Sequence[float] = (), axis: int = -1,
+                 out: Optional[torch.Tensor] = None):
+        ins = list(ins)
+        if not 1 <= len(ins) <= _lib.MAX_INPUTS:
+            raise ValueError(f"between 1 and {_lib.MAX_INPUTS} operands are required")
+        t0 = ins[0]
+        ax = axis % t0.dim()
+        if out is None:
+            full = [max(t.shape[i] for t in ins if t.dim() == t0.dim()) for i in range(t0.dim())]
+            out = torch.empty([d for i, d in enumerate(full) if i != ax] or [1], device=t0.device, dtype=torch.float32)
+        self._chain = _chain(map_expr, combine_expr, post_expr, init, captures)
+        self._arr = (_lib.Tensor * len(ins))(*[_view(t, i) for i, t in enumerate(ins)])
+        self._ov = _view(out, "out")
+        _operands_on_one_device(ins, out)
+        self._ins, self.out = ins, out
+        self._dev = t0.device.index
+        self._fn = _lib.load().tcab_chain_reduce
+        self._args = (C.byref(self._chain), self._arr, len(ins), ax, C.byref(self._ov))
+
+    def __call__(self, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        raw = stream.cuda_stream if stream is not None else torch._C._cuda_getCurrentRawStream(self._dev)
+        if torch.cuda.current_device() == self._dev:
+            rc = self._fn(*self._args, C.c_void_p(raw))
+        else:
+            with torch.cuda.device(self._dev):
+                rc = self._fn(*self._args, C.c_void_p(raw))
+        if rc:
+            _lib.check(rc)
+        return self.out
+
+
 def map(ins: Sequence[torch.Tensor], map_expr: str, captures: Sequence[float] = (),  # noqa: A001 (the operator's name)
         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
         stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:

@@ -426,3 +426,23 @@ def test_middle_axis_reduction_reads_a_value_per_output_cell(cuda, nb, nk, nc):
     with pytest.raises(T.TcabError) as e:       # the value per row of the innermost-axis kernels is not a value per cell
         T.chain_reduce([xd, torch.zeros((nb, nk, 1), device=cuda)], "p0 * p1", axis=1)
     assert e.value.status == T._lib.ERR_SHAPE
+
+
+def test_bound_chain_reduce_is_the_same_call(cuda):
+    """Descriptors built once, launched many times: the same results and one launch per call."""
+    rng = np.random.default_rng(11)
+    x = to_dev(rng.uniform(-1, 1, (300, 1001)).astype(np.float32), cuda)
+    z = to_dev(rng.uniform(0, 1, (300, 1001)).astype(np.float32), cuda)
+    want = T.chain_reduce([x, z], "p0 * p1 + c0", captures=(0.5,), init=1.0, post_expr="p0 * 2.0f")
+    call = T.BoundChainReduce([x, z], "p0 * p1 + c0", captures=(0.5,), init=1.0, post_expr="p0 * 2.0f")
+    n0 = T.launch_count()
+    for _ in range(3):
+        got = call()
+    assert T.launch_count() - n0 == 3
+    assert torch.equal(got, want)
+    x.mul_(2.0)                                     # the operands are read at every call
+    assert torch.equal(call(), T.chain_reduce([x, z], "p0 * p1 + c0", captures=(0.5,), init=1.0, post_expr="p0 * 2.0f"))
+    mid = T.BoundChainReduce([x.view(3, 100, 1001)], "p0", combine_expr="fmaxf(p0, p1)", init=-10.0, axis=1)
+    assert torch.equal(mid(), x.view(3, 100, 1001).max(1).values)
+    with pytest.raises(ValueError):
+        T.BoundChainReduce([x, z.cpu()], "p0 * p1")
