@@ -71,7 +71,7 @@ const Nvrtc& nvrtc() {
 enum Slot {
   kInner1V4, kInner4V4, kInner32V4, kInner256V4, kInner1V1, kInner4V1, kInner32V1, kInner256V1,
   kSplitV4, kSplitV1, kFinish, kOuterV4, kOuterV1, kContractKN, kContractNK, kContractKN8, kContractNK8, kMap8, kMap1,
-  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kOuterFlat1, kInnerRag4, kInnerRag32, kInnerRag256, kInnerRows32e, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
+  kInner32V4Big, kBatch32V4, kBatch256V4, kBatch32V1, kBatch256V1, kOuterFlat, kOuterFlat1, kInner4V8, kInner32V8, kInner256V8, kSplitV8, kInnerRag4, kInnerRag32, kInnerRag256, kInnerRows32e, kInnerFlat, kInnerFlat2, kInnerRows32, kSlots
 };
 
 struct JitChain {
@@ -81,6 +81,7 @@ struct JitChain {
   char kind = 'R';
   bool broadcast = false;  // an operand is not indexed by every axis: innermost-axis kernels only
   bool cells = false;      // an operand lacks the reduced middle axis: middle-axis kernels only
+  bool all_bf16 = false;   // every operand is bf16: kernels on vectors of eight exist
 };
 
 std::mutex g_mu;
@@ -97,7 +98,7 @@ std::string functor(const char* name, const std::string& expr, int n_in, const i
   for (int i = 0; i < n_in; ++i) {
     const std::string pi = "p" + std::to_string(i), src = "p[" + std::to_string(i) + "]";
     switch (in_types ? in_types[i] : TCAB_F32) {
-      case TCAB_BF16: s += "    const __nv_bfloat16 " + pi + " = __nv_bfloat16(" + src + ");\n"; break;
+      case TCAB_BF16: s += "    const __nv_bfloat16 " + pi + " = __nv_bfloat16::widened(" + src + ");\n"; break;
       case TCAB_I32: s += "    const int32_t " + pi + " = __float_as_int(" + src + ");\n"; break;
       case TCAB_U32: s += "    const uint32_t " + pi + " = __float_as_uint(" + src + ");\n"; break;
       default: s += "    const float " + pi + " = " + src + ";\n"; break;
@@ -170,6 +171,12 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
     names[kInnerFlat] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ">";
     names[kInnerFlat2] = "tcabk::chain_inner_flat<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, " + bf + ", 2>";
     names[kInnerRows32] = "tcabk::chain_inner_rows32<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
+    if (sp.n_in > 0 && sp.bf_mask() == (1 << sp.n_in) - 1) {  // every operand bf16: 16-byte loads are vectors of eight
+      names[kInner4V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, " + bf + ", 128>";
+      names[kInner32V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 8, " + bf + ", 128>";
+      names[kInner256V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 256, 8, " + bf + ", 256>";
+      names[kSplitV8] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 8, " + bf + ">";
+    }
     names[kInnerRows32e] = "tcabk::chain_inner_rows32e<tcabj::Map, tcabj::Post, " + c + ", " + n + ", " + bf + ">";
     names[kInnerRag4] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 4, " + bf + ", 128, 0, 0, 1>";
     names[kInnerRag32] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 128, 0, 0, 1>";
@@ -220,6 +227,7 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
   jc->kind = sp.kind;
   jc->broadcast = (sp.rb_mask | sp.cb_mask) != 0;
   jc->cells = sp.cell_mask != 0;
+  jc->all_bf16 = sp.n_in > 0 && sp.bf_mask() == (1 << sp.n_in) - 1;
   cudaError_t e = cudaLibraryLoadData(&jc->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
   for (int i = 0; e == cudaSuccess && i < static_cast<int>(names.size()); ++i) {
     if (names[i].empty()) continue;
@@ -314,14 +322,25 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
     const uint32_t nvec = vec ? nk / 4 : nk;
     const bool force_split = (splits & 0x80000000u) != 0;  // the entry point that allocates nothing
     splits &= 0x7fffffffu;
+    // every operand bf16 and rows of whole 16-byte vectors: vectors of eight (rows from 128 columns; shorter ones
+    // keep the kernels for short rows below)
+    const bool vec8 = vec && jc->all_bf16 && nk % 8 == 0 && nk >= 128 && jc->k[kInner32V8] != nullptr;
     if ((splits > 1 || force_split) && split_scratch_or_null != nullptr) {
       const uint32_t rows = static_cast<uint32_t>(outer);
-      uint32_t sp = splits > nvec ? (nvec ? nvec : 1) : splits;
-      uint32_t vec_per_split = (nvec + sp - 1) / sp;
+      const uint32_t nv = vec8 && !force_split ? nk / 8 : nvec;
+      uint32_t sp = splits > nv ? (nv ? nv : 1) : splits;
+      uint32_t vec_per_split = (nv + sp - 1) / sp;
       void* a1[] = {ptrs, &split_scratch_or_null, &nk, &sp, &vec_per_split, &caps};
-      int rc = launch(jc->k[vec ? kSplitV4 : kSplitV1], static_cast<uint64_t>(rows) * sp, 256, a1, s, "chain_inner_split");
+      int rc = launch(jc->k[vec8 && !force_split ? kSplitV8 : vec ? kSplitV4 : kSplitV1], static_cast<uint64_t>(rows) * sp, 256, a1, s,
+                      "chain_inner_split");
       if (rc != TCAB_OK) return rc;
       return launch_jit_finish(jc, split_scratch_or_null, out, rows, sp, init, caps, s);
+    }
+    if (vec8 && tune(kReduceInner).p0 <= 0) {  // a warp or a CTA per row, the thresholds counted in 16-byte vectors
+      const bool cta = nk / 8 >= inner_cta_per_row_from(jc->n_in);
+      void* a8[] = {ptrs, &out, &outer, &nk, &init, &caps};
+      if (nk / 8 <= 64) return launch(jc->k[kInner4V8], (outer + 31) / 32, 128, a8, s, "chain_inner");  // four threads per row
+      return launch(jc->k[cta ? kInner256V8 : kInner32V8], cta ? outer : (outer + 3) / 4, cta ? 256 : 128, a8, s, "chain_inner");
     }
     if (vec && nvec >= 2 && nvec <= 16 && outer >= 1024 && jc->k[kInnerRows32] != nullptr && tune(kReduceInner).p0 <= 0 &&
         rows32_warps(nvec, jc->n_in) >= 2) {  // a thread per row over a coalesced copy (same policy as ahead of time)
@@ -389,6 +408,7 @@ int jit_launch(void* handle, const float* const* ins, uint64_t outer, uint32_t n
     }
   }
   // few column tiles and a long k: the k axis is split over CTAs too (same policy as the ahead-of-time path)
+  // (vectors of eight for bf16 operands were measured here too: behind the 8-byte loads of this kernel on most shapes)
   const cudaKernel_t kern = jc->k[vec ? kOuterV4 : kOuterV1];
   const int occ = occupancy(reinterpret_cast<const void*>(kern), 256, 0);
   uint32_t ksplit = split_scratch_or_null == nullptr

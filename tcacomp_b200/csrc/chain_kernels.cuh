@@ -81,14 +81,33 @@ struct Ld<1> {
 // compiles at run time without any include path.
 __device__ __forceinline__ float bf16_bits_to_float(unsigned int h) { return __uint_as_float(h << 16); }
 __device__ __forceinline__ unsigned int float_to_bf16_bits(float f) {  // round to nearest even, quiet NaN kept
-  const unsigned int u = __float_as_uint(f);
-  if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x0040u;
-  return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+  // the conversion instruction rounds to nearest even and keeps infinities; it turns every NaN into 0x7fff, so a NaN
+  // is written here with its sign and payload, quieted (in integer arithmetic this function was eight instructions
+  // per value, and a chain over bf16 operands was bound by them, not by memory)
+  unsigned short h;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
+  if (f != f) h = static_cast<unsigned short>((__float_as_uint(f) >> 16) | 0x0040u);
+  return h;
+}
+// Two values at once with the conversion instruction (round to nearest even, as above); it turns every NaN into
+// 0x7fff, so a NaN is put back as float_to_bf16_bits writes it (sign and payload kept, quieted).
+__device__ __forceinline__ unsigned int pack_bf16x2(float lo, float hi) {
+  unsigned int d;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  if (lo != lo) d = (d & 0xffff0000u) | ((__float_as_uint(lo) >> 16) | 0x0040u);
+  if (hi != hi) d = (d & 0x0000ffffu) | (((__float_as_uint(hi) >> 16) | 0x0040u) << 16);
+  return d;
 }
 struct bf16 {  // the value type a bf16 operand has inside a lambda: convertible, not arithmetic
   unsigned short bits;
   __device__ __forceinline__ bf16() : bits(0) {}
   __device__ __forceinline__ explicit bf16(float f) : bits(static_cast<unsigned short>(float_to_bf16_bits(f))) {}
+  // from the f32 register a kernel widened a bf16 operand into: the low half is zero, nothing to round
+  static __device__ __forceinline__ bf16 widened(float f) {
+    bf16 r;
+    r.bits = static_cast<unsigned short>(__float_as_uint(f) >> 16);
+    return r;
+  }
   __device__ __forceinline__ explicit operator float() const { return bf16_bits_to_float(bits); }
   __device__ __forceinline__ explicit operator int() const { return static_cast<int>(bf16_bits_to_float(bits)); }
   __device__ __forceinline__ explicit operator unsigned int() const { return static_cast<unsigned int>(bf16_bits_to_float(bits)); }
@@ -117,6 +136,27 @@ template <>
 struct LdT<1, true> {
   static __device__ __forceinline__ void load(const float* base, u64 index, float* f) {
     f[0] = bf16_bits_to_float(__ldcs(reinterpret_cast<const unsigned short*>(base) + index));
+  }
+};
+// Vectors of eight: one 16-byte load of a bf16 operand (chains whose operands are all bf16 would otherwise move 8 bytes
+// per load and reach their thresholds, which count vectors, at half the bytes), two of an f32 operand.
+template <>
+struct LdT<8, true> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) {
+    const uint4 q = __ldcs(reinterpret_cast<const uint4*>(base) + index);
+    const unsigned int w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <>
+struct LdT<8, false> {
+  static __device__ __forceinline__ void load(const float* base, u64 index, float* f) {
+    Ld<4>::load(base, 2 * index, f);
+    Ld<4>::load(base, 2 * index + 1, f + 4);
   }
 };
 template <int V, int BF, int A>
@@ -1139,10 +1179,10 @@ chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
       }
       if constexpr (OUT_BF16) {
         uint4 q;
-        q.x = float_to_bf16_bits(r[0]) | (float_to_bf16_bits(r[1]) << 16);
-        q.y = float_to_bf16_bits(r[2]) | (float_to_bf16_bits(r[3]) << 16);
-        q.z = float_to_bf16_bits(r[4]) | (float_to_bf16_bits(r[5]) << 16);
-        q.w = float_to_bf16_bits(r[6]) | (float_to_bf16_bits(r[7]) << 16);
+        q.x = pack_bf16x2(r[0], r[1]);
+        q.y = pack_bf16x2(r[2], r[3]);
+        q.z = pack_bf16x2(r[4], r[5]);
+        q.w = pack_bf16x2(r[6], r[7]);
         __stcs(static_cast<uint4*>(out) + tid, q);
       } else {
         __stcs(static_cast<float4*>(out) + 2 * tid, make_float4(r[0], r[1], r[2], r[3]));

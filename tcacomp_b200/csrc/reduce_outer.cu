@@ -400,7 +400,7 @@ uint32_t choose_ksplit(uint64_t tiles, uint32_t nb, uint32_t nk, uint32_t nc, ui
   if (forced > 0) {
     want = static_cast<uint64_t>(forced);
   } else {
-    if (tiles >= static_cast<uint64_t>(sm_count())) return 1;
+    if (tiles * 2 > resident || tiles >= 4 * static_cast<uint64_t>(sm_count())) return 1;  // as plan_outer_splits
     want = resident / tiles;
     if (want > nk / 256) want = nk / 256;
   }

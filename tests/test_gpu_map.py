@@ -446,3 +446,37 @@ def test_bound_chain_reduce_is_the_same_call(cuda):
     assert torch.equal(mid(), x.view(3, 100, 1001).max(1).values)
     with pytest.raises(ValueError):
         T.BoundChainReduce([x, z.cpu()], "p0 * p1")
+
+
+@pytest.mark.parametrize("shape,axis", [((3000, 1024), 1), ((700, 8192), 1), ((5, 400000), 1), ((2000, 520), 1), ((1500, 1032), 1),
+                                        ((40, 300, 512), 1), ((3, 5000, 256), 1), ((200, 64, 1024), 1), ((9, 100, 264), 1)])
+def test_chains_whose_operands_are_all_bf16(cuda, shape, axis):
+    """Every operand bf16: rows of whole 16-byte vectors are read as vectors of eight (innermost axis beyond 512 columns,
+    middle axis from 256 columns), everything else as before; sums against fp64, max bit-exact."""
+    from oracle import binding as O
+    rng = np.random.default_rng(sum(shape))
+    xb = O.f32_to_bf16(rng.uniform(-1, 1, shape).astype(np.float32))
+    zb = O.f32_to_bf16(rng.uniform(0, 1, shape).astype(np.float32))
+    x64, z64 = O.bf16_to_f32(xb).astype(np.float64), O.bf16_to_f32(zb).astype(np.float64)
+    xd, zd = to_dev(xb, cuda), to_dev(zb, cuda)
+    got = T.chain_reduce([xd], "f32(p0)", axis=axis).cpu().numpy()
+    assert (np.abs(got - x64.sum(axis)) <= 1e-5 * np.abs(x64).sum(axis) + 1e-30).all()
+    got = T.chain_reduce([xd, zd], "f32(p0) * f32(p1) + c0", captures=(0.25,), init=1.0, axis=axis, post_expr="p0 * 0.5f").cpu().numpy()
+    want = ((x64 * z64 + 0.25).sum(axis) + 1.0) * 0.5
+    assert (np.abs(got - want) <= 1e-5 * (np.abs(x64 * z64) + 0.25).sum(axis) + 1e-5).all()
+    got = T.chain_reduce([xd], "f32(p0)", combine_expr="fmaxf(p0, p1)", init=-2.0, axis=axis).cpu().numpy()
+    assert np.array_equal(got, O.bf16_to_f32(xb).max(axis))
+
+
+def test_bf16_map_results_round_like_the_oracle(cuda):
+    """The map kernels convert two results at a time with the conversion instruction: round to nearest even on every
+    value, infinities kept, and a NaN keeps its sign and payload as the oracle's conversion does."""
+    from oracle import binding as O
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 1, (257, 1000)).astype(np.float32)
+    x[0, :8] = [np.inf, -np.inf, np.nan, -np.nan, 3.3895314e38, -3.3895314e38, 1e-40, -1e-45]   # the last four: overflow to inf, denormals
+    x.view(np.uint32)[1, :4] = [0x7FC12345, 0xFF812345, 0x7F800001, 0x3F808000]               # NaN payloads; a tie
+    x.view(np.uint32)[2, :1000] = (0x3F800000 + rng.integers(0, 1 << 17, 1000)).astype(np.uint32)  # values around the ties
+    got = T.map([to_dev(x, cuda)], "bf16(p0)", out_dtype=torch.bfloat16)
+    bits = got.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(bits, O.f32_to_bf16(x))
