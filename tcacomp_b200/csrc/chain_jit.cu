@@ -160,6 +160,11 @@ int compile(const std::string& key, const JitSpec& sp, JitChain** out, bool load
                                                         std::to_string(tprs[t]) + ", " + (v == 0 ? "4" : "1") + ", " + bf + ", " +
                                                         std::to_string(tprs[t] > 128 ? tprs[t] : 128) + bc + ">";
       names[kInner32V4Big] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 4, " + bf + ", 1024" + bc + ">";
+      if (sp.bf_mask() == (1 << sp.n_in) - 1) {  // every operand bf16: vectors of eight, as without broadcast operands
+        names[kInner4V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 4, 8, " + bf + ", 128" + bc + ">";
+        names[kInner32V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 32, 8, " + bf + ", 128" + bc + ">";
+        names[kInner256V8] = "tcabk::chain_inner<tcabj::Map, tcabj::Post, " + c + ", " + n + ", 256, 8, " + bf + ", 256" + bc + ">";
+      }
     } else {
     names[kSplitV4] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 4, " + bf + ">";
     names[kSplitV1] = "tcabk::chain_inner_split<tcabj::Map, " + c + ", " + n + ", 1, " + bf + ">";

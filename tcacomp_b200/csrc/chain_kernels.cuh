@@ -1163,11 +1163,12 @@ chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
     if (tid < groups) {
       float f[NIN][8];
       if ((RB | CB) != 0 && cols % 8 != 0) {        // a group may straddle rows
-        const u64 first = tid * 8, row0 = first / cols;
-        MapLoadRagged<BF, RB, CB, NIN>::at(ins.p, tid, row0, static_cast<u32>(first - row0 * cols), cols, f);
+        const u32 first = static_cast<u32>(tid) * 8, row0 = first / cols;  // element counts are below 2^32
+        MapLoadRagged<BF, RB, CB, NIN>::at(ins.p, tid, row0, first - row0 * cols, cols, f);
       } else {
-        const u64 gpr = (RB | CB) ? cols / 8 : 1;   // groups per row
-        MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, (RB | CB) ? tid / gpr : 0, (RB | CB) ? tid % gpr : 0, f);
+        // groups per row; element counts are below 2^32 (the entry points refuse more), so 32-bit division will do
+        const u32 gpr = (RB | CB) ? cols / 8 : 1, t32 = static_cast<u32>(tid), row = (RB | CB) ? t32 / gpr : 0;
+        MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, row, (RB | CB) ? t32 - row * gpr : 0, f);
       }
       float r[8];
 #pragma unroll
