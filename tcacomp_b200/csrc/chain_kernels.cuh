@@ -99,18 +99,20 @@ __device__ __forceinline__ unsigned int pack_bf16x2(float lo, float hi) {
   return d;
 }
 struct bf16 {  // the value type a bf16 operand has inside a lambda: convertible, not arithmetic
-  unsigned short bits;
-  __device__ __forceinline__ bf16() : bits(0) {}
-  __device__ __forceinline__ explicit bf16(float f) : bits(static_cast<unsigned short>(float_to_bf16_bits(f))) {}
-  // from the f32 register a kernel widened a bf16 operand into: the low half is zero, nothing to round
+  // kept WIDENED (an f32 whose low 16 bits are zero): operands arrive that way from the kernels' loads and leave
+  // that way for their stores, so converting to and from f32 inside a lambda costs nothing; only bf16(f32) rounds
+  float w;
+  __device__ __forceinline__ bf16() : w(0.0f) {}
+  __device__ __forceinline__ explicit bf16(float f) : w(bf16_bits_to_float(float_to_bf16_bits(f))) {}
+  // from the f32 register a kernel widened a bf16 operand into: nothing to round
   static __device__ __forceinline__ bf16 widened(float f) {
     bf16 r;
-    r.bits = static_cast<unsigned short>(__float_as_uint(f) >> 16);
+    r.w = f;
     return r;
   }
-  __device__ __forceinline__ explicit operator float() const { return bf16_bits_to_float(bits); }
-  __device__ __forceinline__ explicit operator int() const { return static_cast<int>(bf16_bits_to_float(bits)); }
-  __device__ __forceinline__ explicit operator unsigned int() const { return static_cast<unsigned int>(bf16_bits_to_float(bits)); }
+  __device__ __forceinline__ explicit operator float() const { return w; }
+  __device__ __forceinline__ explicit operator int() const { return static_cast<int>(w); }
+  __device__ __forceinline__ explicit operator unsigned int() const { return static_cast<unsigned int>(w); }
 };
 
 // Operand `a` of a kernel: element size by the BF mask. `index` counts vectors of V elements.
