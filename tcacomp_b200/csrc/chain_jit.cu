@@ -463,6 +463,7 @@ int jit_launch_map(void* handle, const void* const* ins, void* out, uint64_t n, 
   bool al = aligned16(out);
   for (int i = 0; i < jc->n_in; ++i) al = al && aligned16(ins[i]);
   void* a[] = {ptrs, &out, &n, &caps, &cols};
+  // one more group index than groups: the thread that gets it takes the ragged end
   if (al) return launch(jc->k[kMap8], (n / 8 + 1 + 255) / 256, 256, a, s, "chain_map");
   return launch(jc->k[kMap1], (n + 255) / 256, 256, a, s, "chain_map");
 }

@@ -1152,47 +1152,68 @@ __device__ __forceinline__ void map_one(const float* const* p, void* out, u64 i,
   else __stcs(static_cast<float*>(out) + i, r);
 }
 
+// One group of eight elements of a map: the operands' loads ...
+template <int NIN, int BF, int RB, int CB>
+__device__ __forceinline__ void map_load_group(const float* const* p, u64 group, u32 cols, float (*f)[8]) {
+  if ((RB | CB) != 0 && cols % 8 != 0) {        // a group may straddle rows
+    const u32 first = static_cast<u32>(group) * 8, row0 = first / cols;  // element counts are below 2^32
+    MapLoadRagged<BF, RB, CB, NIN>::at(p, group, row0, first - row0 * cols, cols, f);
+  } else {
+    // groups per row; element counts are below 2^32 (the entry points refuse more), so 32-bit division will do
+    const u32 gpr = (RB | CB) ? cols / 8 : 1, t32 = static_cast<u32>(group), row = (RB | CB) ? t32 / gpr : 0;
+    MapLoadAll<8, BF, RB, CB, NIN>::at(p, group, row, (RB | CB) ? t32 - row * gpr : 0, f);
+  }
+}
+// ... and the lambda on them with the store of its results.
+template <class Map, int NIN, bool OUT_BF16>
+__device__ __forceinline__ void map_apply_group(const float (*f)[8], void* out, u64 group, const float* caps) {
+  float r[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float v[NIN];
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) v[a] = f[a][j];
+    r[j] = Map::apply(v, caps);
+  }
+  if constexpr (OUT_BF16) {
+    uint4 q;
+    q.x = pack_bf16x2(r[0], r[1]);
+    q.y = pack_bf16x2(r[2], r[3]);
+    q.z = pack_bf16x2(r[4], r[5]);
+    q.w = pack_bf16x2(r[6], r[7]);
+    __stcs(static_cast<uint4*>(out) + group, q);
+  } else {
+    __stcs(static_cast<float4*>(out) + 2 * group, make_float4(r[0], r[1], r[2], r[3]));
+    __stcs(static_cast<float4*>(out) + 2 * group + 1, make_float4(r[4], r[5], r[6], r[7]));
+  }
+}
+
 // cols: the innermost extent; only read when an operand is broadcast (RB | CB != 0). A group of eight that
-// straddles rows (cols % 8 != 0) reads its broadcast operands element by element.
-template <class Map, int NIN, int BF, bool OUT_BF16, int EPT, int RB = 0, int CB = 0>
+// straddles rows (cols % 8 != 0) reads its broadcast operands element by element. GPT: groups per thread, 256 apart
+// (a CTA covers 256 GPT consecutive groups), the loads of all of them issued before the first lambda runs. Every
+// launcher uses one: two were measured for maps over bf16 operands, whose group is 16 bytes per operand where an f32
+// group is 32, and were slower (bias + ReLU on bf16 4.1 -> 3.6 TB/s: those maps are bound by instructions).
+template <class Map, int NIN, int BF, bool OUT_BF16, int EPT, int RB = 0, int CB = 0, int GPT = 1>
 __global__ void __launch_bounds__(256)
 chain_map(Ptrs<NIN> ins, void* __restrict__ out, u64 n, Caps caps, u32 cols) {
-  const u64 tid = static_cast<u64>(blockIdx.x) * 256 + threadIdx.x;
   if constexpr (EPT == 1) {
+    const u64 tid = static_cast<u64>(blockIdx.x) * 256 + threadIdx.x;
     if (tid < n) map_one<NIN, BF, RB, CB, OUT_BF16, Map>(ins.p, out, tid, cols, caps.c);
   } else {
     const u64 groups = n / 8;
-    if (tid < groups) {
-      float f[NIN][8];
-      if ((RB | CB) != 0 && cols % 8 != 0) {        // a group may straddle rows
-        const u32 first = static_cast<u32>(tid) * 8, row0 = first / cols;  // element counts are below 2^32
-        MapLoadRagged<BF, RB, CB, NIN>::at(ins.p, tid, row0, first - row0 * cols, cols, f);
-      } else {
-        // groups per row; element counts are below 2^32 (the entry points refuse more), so 32-bit division will do
-        const u32 gpr = (RB | CB) ? cols / 8 : 1, t32 = static_cast<u32>(tid), row = (RB | CB) ? t32 / gpr : 0;
-        MapLoadAll<8, BF, RB, CB, NIN>::at(ins.p, tid, row, (RB | CB) ? t32 - row * gpr : 0, f);
-      }
-      float r[8];
+    const u64 first = static_cast<u64>(blockIdx.x) * (256 * GPT) + threadIdx.x;
+    float f[GPT][NIN][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float v[NIN];
+    for (int q = 0; q < GPT; ++q)
+      if (first + q * 256 < groups) map_load_group<NIN, BF, RB, CB>(ins.p, first + q * 256, cols, f[q]);
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) v[a] = f[a][j];
-        r[j] = Map::apply(v, caps.c);
+    for (int q = 0; q < GPT; ++q) {
+      const u64 g = first + q * 256;
+      if (g < groups) {
+        map_apply_group<Map, NIN, OUT_BF16>(f[q], out, g, caps.c);
+      } else if (g == groups) {  // the ragged end, fewer than eight elements
+        for (u64 i = groups * 8; i < n; ++i) map_one<NIN, BF, RB, CB, OUT_BF16, Map>(ins.p, out, i, cols, caps.c);
       }
-      if constexpr (OUT_BF16) {
-        uint4 q;
-        q.x = pack_bf16x2(r[0], r[1]);
-        q.y = pack_bf16x2(r[2], r[3]);
-        q.z = pack_bf16x2(r[4], r[5]);
-        q.w = pack_bf16x2(r[6], r[7]);
-        __stcs(static_cast<uint4*>(out) + tid, q);
-      } else {
-        __stcs(static_cast<float4*>(out) + 2 * tid, make_float4(r[0], r[1], r[2], r[3]));
-        __stcs(static_cast<float4*>(out) + 2 * tid + 1, make_float4(r[4], r[5], r[6], r[7]));
-      }
-    } else if (tid == groups) {  // the ragged end, fewer than eight elements
-      for (u64 i = groups * 8; i < n; ++i) map_one<NIN, BF, RB, CB, OUT_BF16, Map>(ins.p, out, i, cols, caps.c);
     }
   }
 }
