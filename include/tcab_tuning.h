@@ -72,6 +72,12 @@ TCAB_API int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32
 TCAB_API int tcab_plan_outer_flat_ranges(uint64_t batches, uint32_t nk, uint32_t nc, int sms, uint64_t max_partials,
                                          uint32_t* groups, uint32_t* ranges, uint32_t* klen);
 
+/* The register-row kernel shape the softmax (op 0, fp32) and layer-norm (op 1, elem_bytes 2 or 4) launchers ask for on
+ * aligned rows of nvec 16-byte vectors: threads per row and vector slots per thread, 0 / 0 when no compiled shape
+ * holds the row. Pure arithmetic. Other kernels (shared-memory rows, clusters) may still take the row. */
+TCAB_API int tcab_plan_row_shape(int op, int elem_bytes, uint32_t nvec, uint32_t* threads_per_row,
+                                 uint32_t* slots_per_thread);
+
 /* Validates a chain exactly as tcab_chain_prepare does and runs the run-time compiler on it for sm_100a, but
  * loads nothing: works on a host without a GPU (needs libnvrtc). A chain that has an ahead-of-time kernel is
  * compiled all the same. Arguments as tcab_chain_prepare, plus the bit masks of the operands that have one

@@ -105,6 +105,7 @@ TUNING_SYMBOLS = [
     ("tcab_plan_row_kernels", C.c_int,
      [C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, C.c_uint32, C.c_uint32, C.c_int, C.c_int, C.POINTER(C.c_uint32),
       C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    ("tcab_plan_row_shape", C.c_int, [C.c_int, C.c_int, C.c_uint32, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
     ("tcab_plan_outer_flat_ranges", C.c_int,
      [C.c_uint64, C.c_uint32, C.c_uint32, C.c_int, C.c_uint64, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32),
       C.POINTER(C.c_uint32)]),

@@ -357,6 +357,17 @@ int tcab_plan_row_kernels(uint64_t rows_or_batches, uint32_t nk, uint32_t nc, in
   return TCAB_OK;
 }
 
+int tcab_plan_row_shape(int op, int elem_bytes, uint32_t nvec, uint32_t* threads_per_row, uint32_t* slots_per_thread) {
+  if (threads_per_row == nullptr || slots_per_thread == nullptr) return fail(TCAB_ERR_INVALID_ARG, "plan_row_shape: null output");
+  if ((op != 0 && op != 1) || (elem_bytes != 2 && elem_bytes != 4) || (op == 0 && elem_bytes != 4))
+    return fail(TCAB_ERR_INVALID_ARG, "plan_row_shape: op 0 (softmax, 4-byte elements) or 1 (layer-norm, 2 or 4)");
+  int t = 0, v = 0;
+  const bool fits = op == 0 ? tcab::softmax_row_shape(nvec, true, &t, &v) : tcab::layernorm_row_shape(nvec, true, elem_bytes, &t, &v);
+  *threads_per_row = fits ? static_cast<uint32_t>(t) : 0;
+  *slots_per_thread = fits ? static_cast<uint32_t>(v) : 0;
+  return TCAB_OK;
+}
+
 int tcab_plan_outer_flat_ranges(uint64_t batches, uint32_t nk, uint32_t nc, int sms, uint64_t max_partials,
                                 uint32_t* groups, uint32_t* ranges, uint32_t* klen) {
   if (groups == nullptr || ranges == nullptr || klen == nullptr)

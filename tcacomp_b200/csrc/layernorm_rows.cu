@@ -694,11 +694,7 @@ int dispatch(const T* x, const T* gamma, const T* beta, float eps, T* y, uint64_
     }
   }
   int tpr = 0, vpt = 0;
-  // fp32 rows: eight slots per thread (32 row values) cost resident rows; four slots on twice the threads measured
-  // ahead even when a quarter of them idle (1280 columns 5.4 -> 6.2 TB/s, 5120 4.8 -> 5.7, 7168 5.7 -> 6.4)
-  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/true, vec ? VW : 1, &tpr, &vpt, /*small=*/true,
-                                   /*wide_penalty=*/sizeof(T) == 4 ? 0.25 : 0.03, /*odd_slots=*/vec,
-                                   /*five_slots_max_threads=*/sizeof(T) == 4 ? 32 : 256);
+  bool fits = layernorm_row_shape(nvec, vec, static_cast<int>(sizeof(T)), &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;

@@ -200,6 +200,21 @@ inline bool choose_row_shape_fit(uint32_t nvec, bool vec, bool wide8, int values
   return found;
 }
 
+// The register-row shape each operator asks for on aligned rows of nvec 16-byte vectors (the calls the dispatchers
+// make, in one place so that a host without a device can sweep them): softmax (fp32), layer-norm fp32 / bf16.
+inline bool softmax_row_shape(uint32_t nvec, bool vec, int* tpr, int* vpt) {
+  return choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, tpr, vpt, /*small=*/true, /*wide_penalty=*/0.03,
+                              /*odd_slots=*/vec, /*five_slots_max_threads=*/32);
+}
+inline bool layernorm_row_shape(uint32_t nvec, bool vec, int elem_bytes, int* tpr, int* vpt) {
+  // fp32 rows: eight slots per thread (32 row values) cost resident rows; four slots on twice the threads measured
+  // ahead even when a quarter of them idle (1280 columns 5.4 -> 6.2 TB/s, 5120 4.8 -> 5.7, 7168 5.7 -> 6.4)
+  const int values_per_vector = vec ? 16 / elem_bytes : 1;
+  return choose_row_shape_fit(nvec, vec, /*wide8=*/true, values_per_vector, tpr, vpt, /*small=*/true,
+                              /*wide_penalty=*/elem_bytes == 4 ? 0.25 : 0.03, /*odd_slots=*/vec,
+                              /*five_slots_max_threads=*/elem_bytes == 4 ? 32 : 256);
+}
+
 // Streaming clusters (softmax_rows_cluster_stream, layernorm_rows_cluster_stream): CTAs per row for a row of
 // nvec vectors when a CTA takes per_step vectors per step. Four steps per CTA with the smallest cluster that allows
 // it; where that leaves exactly-filled CTAs behind, a larger cluster that covers the row in at most three nearly

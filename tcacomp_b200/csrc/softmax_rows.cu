@@ -699,8 +699,7 @@ int launch_softmax_rows(const float* x, float* y, uint64_t rows, uint32_t cols, 
     }
   }
   int tpr = 0, vpt = 0;
-  bool fits = choose_row_shape_fit(nvec, vec, /*wide8=*/false, vec ? 4 : 1, &tpr, &vpt, /*small=*/true, /*wide_penalty=*/0.03,
-                                   /*odd_slots=*/vec, /*five_slots_max_threads=*/32);
+  bool fits = softmax_row_shape(nvec, vec, &tpr, &vpt);
   if (tn.p0 > 0 && tn.p1 > 0 && static_cast<uint64_t>(tn.p0) * tn.p1 >= nvec) {
     tpr = tn.p0;
     vpt = tn.p1;

@@ -291,6 +291,30 @@ def test_lambdas_over_operands_that_bind_a_subset_of_the_axes_compile(tcab_lib, 
     assert tcab_lib.tcab_compile_check(C.byref(ch), arr, len(types), _use(use), out, rb, cb, cells) == _lib.OK, _err(tcab_lib)
 
 
+def test_register_row_shapes(tcab_lib):
+    """The shape a register-row kernel gets: every row is covered, rows of 3 * 2^k and 5 * 2^k vectors (hidden sizes
+    768, 1280, 1536, 2560, 3072, 5120 ...) fit exactly with every slot used, powers of two keep four slots."""
+    def shape(op, eb, nvec):
+        t, v = C.c_uint32(), C.c_uint32()
+        assert tcab_lib.tcab_plan_row_shape(op, eb, nvec, C.byref(t), C.byref(v)) == 0
+        return t.value, v.value
+    for op, eb in ((0, 4), (1, 4), (1, 2)):
+        for nvec in list(range(1, 600)) + [640, 768, 1000, 1024, 1280, 1536, 2048, 2560, 3000, 4096]:
+            t, v = shape(op, eb, nvec)
+            assert t * v >= nvec and t >= 1 and (t & (t - 1)) == 0, (op, eb, nvec, t, v)
+            assert -(-nvec // t) > v - (2 if v <= 4 else v // 2), (op, eb, nvec, t, v)     # no shape mostly empty
+    # bf16 layer-norm: 640, 768, 1280, 1536, 2560, 3072, 5120, 6144, 10240, 12288 columns
+    assert [shape(1, 2, n) for n in (80, 96, 160, 192, 320, 384, 640, 768, 1280, 1536)] == \
+        [(16, 5), (32, 3), (32, 5), (64, 3), (64, 5), (128, 3), (128, 5), (256, 3), (256, 5), (512, 3)]
+    # fp32 layer-norm and softmax: three slots everywhere, five only with at most 32 threads per row
+    assert shape(1, 4, 160) == (32, 5) and shape(1, 4, 320) != (64, 5) and shape(1, 4, 1280) != (256, 5)
+    assert shape(1, 4, 192) == (64, 3) and shape(1, 4, 1536) == (512, 3) and shape(0, 4, 384) == (128, 3)
+    # powers of two: four slots (bf16 C3: 8192 columns = 1024 vectors; fp32 C2: 4096 columns = 1024 vectors)
+    assert shape(1, 2, 1024) == (256, 4) and shape(0, 4, 1024) == (256, 4) and shape(1, 4, 256) == (64, 4)
+    assert tcab_lib.tcab_plan_row_shape(0, 2, 64, C.byref(C.c_uint32()), C.byref(C.c_uint32())) != 0    # softmax is fp32
+    assert tcab_lib.tcab_plan_row_shape(2, 4, 64, C.byref(C.c_uint32()), C.byref(C.c_uint32())) != 0
+
+
 def test_outer_flat_ranges(tcab_lib):
     """Few narrow column tiles and a long reduced axis: CTAs of the warp-per-tile kernels cut k into ranges that cover it,
     none empty, within the scratch for the partial cells (one per range); many tiles, wide tiles or a short axis are
