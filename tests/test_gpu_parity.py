@@ -1149,6 +1149,33 @@ def test_short_rows(oracle, cuda, rows, cols):
 
 
 # ----------------------------------------------------------------------------
+# rows of 3 * 2^k and 5 * 2^k vectors: register shapes with three and five slots per thread
+# ----------------------------------------------------------------------------
+@pytest.mark.parametrize("cols", [160, 192, 320, 384, 640, 768, 1280, 1536, 2560, 3072, 5120, 6144])
+def test_rows_of_three_and_five_slots(oracle, cuda, cols):
+    rows = 333
+    rng = np.random.default_rng(cols)
+    x = rng.normal(0, 1, (rows, cols)).astype(np.float32)
+    g = rng.normal(1, 0.1, cols).astype(np.float32)
+    b = rng.normal(0, 0.1, cols).astype(np.float32)
+    x64 = x.astype(np.float64)
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    T.softmax_rows(dev_f32(4 * x, cuda), out=out)
+    check_guards(buf, torch.float32)
+    assert_softmax_close(out.cpu().numpy(), oracle.softmax_rows(4 * x), 4 * x)
+    buf, out = guarded((rows, cols), torch.float32, cuda)
+    T.layernorm_rows(dev_f32(x, cuda), dev_f32(g, cuda), dev_f32(b, cuda), 1e-5, out=out)
+    check_guards(buf, torch.float32)
+    y64 = (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5) * g + b
+    assert np.abs(out.cpu().numpy() - y64).max() <= 1e-5 * np.abs(y64).max()
+    xb, gb, bb = oracle.f32_to_bf16(x), oracle.f32_to_bf16(g), oracle.f32_to_bf16(b)
+    buf, outb = guarded((rows, cols), torch.bfloat16, cuda)
+    T.layernorm_rows(dev_bf16(xb, cuda), dev_bf16(gb, cuda), dev_bf16(bb, cuda), 1e-5, out=outb)
+    check_guards(buf, torch.bfloat16)
+    assert_layernorm_bf16_close(oracle, host_bits(outb), oracle.layernorm_rows_bf16(xb, gb, bb, 1e-5), xb, gb, bb)
+
+
+# ----------------------------------------------------------------------------
 # element counts just below 2^32 (the reference's index type): byte offsets beyond 2^32
 # ----------------------------------------------------------------------------
 def test_element_counts_just_below_two_to_the_32(cuda):
