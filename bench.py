@@ -607,10 +607,48 @@ class ShortRowsum(Workload):
         return rep.as_dict()
 
 
+class RowsumBf16(ShortRowsum):
+    """The C1 chain over a bf16 operand (run-time compiled: the ahead-of-time table is fp32): rows read as 16-byte
+    vectors of eight, fp32 arithmetic and output; selectable only."""
+    name = "map_rowsum_bf16_65536x4096"
+    dtype = "f32"
+    full_units, cols = 65536, 4096
+    shape = "x bf16 [65536, 4096] ~ U(-1,1) -> y[i] = sum_j (0.5*f32(x)+0.25)^2 fp32 [65536]"
+    EXPR = "(0.5f*f32(p0) + 0.25f) * (0.5f*f32(p0) + 0.25f)"
+    profile = "chain_inner_map_rowsum_bf16_65536x4096.md"
+
+    def work(self):
+        return self.units * self.cols * 2.0 + self.units * 4
+
+    def make(self, dev, seed):
+        import tcacomp_b200 as T
+        self.T = T
+        g = torch.Generator(device=dev).manual_seed(seed)
+        self.x = (torch.rand((self.units, self.cols), generator=g, device=dev) * 2 - 1).to(torch.bfloat16)
+        self.y = torch.empty((self.units,), device=dev)
+
+    def pipeline_spec(self, chunk_units):
+        from tcacomp_b200.pipeline import PipelineSpec
+        return PipelineSpec("chain_reduce", self.x.device, chunk_units, (self.cols,), torch.bfloat16, map_expr=self.EXPR,
+                            out_dtype=torch.float32)
+
+    def cpu_sample(self, oracle):
+        x = self.x[:min(16384, self.units)].float().cpu().numpy()      # widening bf16 is exact
+        return (lambda: oracle.map_rowsum_affine_sq(x, 0.5, 0.25)), x.size * 2.0 + x.shape[0] * 4, f"first {x.shape[0]} of {self.units} rows per pass"
+
+    def check(self, oracle, full):
+        from oracle import checks
+        rows = self.units if full else min(self.units, 16384)
+        rep = checks.rowsum_report(self.y[:rows].cpu().numpy(), self.x[:rows].float().cpu().numpy())
+        assert rep.ok, f"row-sum parity check failed: {rep}"
+        return rep.as_dict()
+
+
 WORKLOADS = {w.name: w for w in (SoftmaxRows, LayernormRows, ReduceOuter, MapRowsum, GemmBiasRelu, MapOnly)}
 SELECTABLE = dict(WORKLOADS, **{SoftmaxLongRows.name: SoftmaxLongRows, SoftmaxVocabRows.name: SoftmaxVocabRows,
                                 LayernormHeadRows.name: LayernormHeadRows, ReduceOuterNarrow.name: ReduceOuterNarrow,
-                                ReduceOuterColumnStats.name: ReduceOuterColumnStats, ShortRowsum.name: ShortRowsum})
+                                ReduceOuterColumnStats.name: ReduceOuterColumnStats, ShortRowsum.name: ShortRowsum,
+                                RowsumBf16.name: RowsumBf16})
 DEFAULT = SoftmaxRows.name
 
 

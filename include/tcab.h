@@ -297,7 +297,7 @@ typedef enum tcab_op {
   TCAB_OP_SOFTMAX_ROWS = 0,   /* unit: a row [cols] f32                -> y row, resident: none             */
   TCAB_OP_LAYERNORM_ROWS = 1, /* unit: a row [cols] f32 / bf16         -> y row, resident: gamma, beta; eps */
   TCAB_OP_REDUCE_OUTER = 2,   /* unit: one batch [k, c] f32            -> sum, max, argmax [c] (by `outputs`) */
-  TCAB_OP_CHAIN_REDUCE = 3,   /* unit: a row [cols] f32 of each of n_streamed operands -> one f32; chain     */
+  TCAB_OP_CHAIN_REDUCE = 3,   /* unit: a row [cols] f32 / bf16 of each of n_streamed operands -> one f32; chain */
   TCAB_OP_GEMM_BIAS_ACT = 4,  /* unit: a row of a [K] bf16             -> row of c [N] bf16, resident: b [K,N], bias [N] or none; act */
   TCAB_OP_MAP = 5             /* unit: any shape, n_streamed operands of in_dtype -> same shape, out_dtype; chain */
 } tcab_op;

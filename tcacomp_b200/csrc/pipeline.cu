@@ -133,8 +133,8 @@ int plan_outputs(tcab_pipeline* p) {
       return TCAB_OK;
     }
     case TCAB_OP_CHAIN_REDUCE: {
-      if (d.unit_rank != 1 || d.in_dtype != TCAB_F32)
-        return fail(TCAB_ERR_SHAPE, "pipeline: chain_reduce streams f32 rows (unit rank 1), reduced along the row");
+      if (d.unit_rank != 1 || (d.in_dtype != TCAB_F32 && d.in_dtype != TCAB_BF16))
+        return fail(TCAB_ERR_SHAPE, "pipeline: chain_reduce streams f32 or bf16 rows (unit rank 1), reduced along the row");
       if (d.chain == nullptr) return fail(TCAB_ERR_INVALID_ARG, "pipeline: chain_reduce needs a chain");
       OutSpec o;  // one scalar per row
       p->outs[p->n_outs++] = o;

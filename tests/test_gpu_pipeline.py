@@ -87,6 +87,14 @@ def test_every_operator_class_through_the_pipeline(oracle, cuda):
     p.sync()
     assert torch.equal(hr, T.chain_reduce([hxs[0].to(cuda), hxs[1].to(cuda)], "p0 * p1").cpu())
 
+    # the same with bf16 rows (fp32 arithmetic and result)
+    hbs = [t.to(torch.bfloat16).pin_memory() for t in hxs]
+    hr = torch.empty((777,)).pin_memory()
+    p = Pipeline(PipelineSpec("chain_reduce", cuda, 100, (260,), torch.bfloat16, n_streamed=2, map_expr="f32(p0) * f32(p1)"))
+    p.run(hbs, [hr])
+    p.sync()
+    assert torch.equal(hr, T.chain_reduce([hbs[0].to(cuda), hbs[1].to(cuda)], "f32(p0) * f32(p1)").cpu())
+
     # contraction: rows of a streamed, b and bias resident
     a_ = oracle.f32_to_bf16((rng.normal(0, 1, (300, 256)) / 16).astype(np.float32))
     b_ = dev_bf16(oracle.f32_to_bf16((rng.normal(0, 1, (256, 128)) / 16).astype(np.float32)), cuda)
